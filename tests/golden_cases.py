@@ -1,0 +1,63 @@
+"""Seeded small cases shared by the golden generator, the CPU oracle tests and the GPU parity
+tests. Inputs are always rebuilt from these seeds; tests/golden/reference_vectors.npz stores only
+the reference's outputs for them."""
+import numpy as np
+
+from yvex_b200 import synth
+
+CASES = {
+    # name: (qtype, rows, width, seed). Odd block counts give rows that start on 2-, 4- and
+    # 8-byte boundaries, which the 128-bit load paths must survive.
+    "matvec": {
+        "iq2_xxs": (synth.IQ2_XXS, 64, 1024, 11),
+        "iq2_xxs_ragged": (synth.IQ2_XXS, 37, 1792, 12),
+        "q8_0": (synth.Q8_0, 64, 1024, 13),
+        "q8_0_ragged": (synth.Q8_0, 19, 96, 14),
+        "q2_k": (synth.Q2_K, 64, 1024, 15),
+        "q2_k_ragged": (synth.Q2_K, 21, 768, 16),
+    },
+    # name: (hidden, experts, topk, inter, tokens, router: "weights"|"logits", seed)
+    "layer": {
+        "small_router": (512, 8, 2, 256, 4, "weights", 21),
+        "small_logits": (256, 16, 4, 256, 6, "logits", 22),
+        "c2_shape": (4096, 64, 6, 1536, 1, "weights", 23),
+    },
+    # name: (sessions, q_heads, kv_heads, head_dim, context, position, seed)
+    "attention": {
+        "small": (2, 8, 2, 128, 512, 511, 31),
+        "masked": (1, 4, 4, 64, 300, 123, 32),
+    },
+}
+
+
+def layer_inputs(name, down_qtype=synth.Q2_K):
+    """(spec, weights, router or None, x [tokens, hidden], logits or None) for a layer case.
+    Only the experts a token routes to are materialised for the C2-sized case."""
+    H, E, k, I, T, mode, seed = CASES["layer"][name]
+    spec = synth.MoELayerSpec(H, E, k, I, down_qtype=down_qtype)
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    router = logits = None
+    if mode == "weights":
+        router = (rng.standard_normal((E, H)) * 0.02).astype(np.float32)
+        lg = (synth.bf16_round(x).astype(np.float64) @ router.astype(np.float64).T)
+    else:
+        logits = rng.standard_normal((T, E)).astype(np.float32)
+        lg = logits.astype(np.float64)
+    needed = None
+    if E * spec.weight_bytes_per_expert() > (64 << 20):
+        # sqrt(softplus) is monotonic, zero bias: top-k of the logits are the selected experts;
+        # take a margin so float ties cannot miss one.
+        needed = set(np.argsort(-lg, axis=1)[:, :k + 2].ravel().tolist())
+    weights = synth.moe_weights(spec, seed, experts=needed)
+    return spec, weights, router, x, logits
+
+
+def attention_inputs(name):
+    """(q [S,Hq,D] f32, k/v [S,Hkv,ctx,D] f32 - all exactly bf16-representable - position, scale)"""
+    S, Hq, Hkv, D, ctx, pos, seed = CASES["attention"][name]
+    rng = np.random.default_rng(seed)
+    q = synth.bf16_round(rng.standard_normal((S, Hq, D)).astype(np.float32))
+    k = synth.bf16_round(rng.standard_normal((S, Hkv, ctx, D)).astype(np.float32))
+    v = synth.bf16_round(rng.standard_normal((S, Hkv, ctx, D)).astype(np.float32))
+    return q, k, v, pos, float(D) ** -0.5
