@@ -1,0 +1,306 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized MoE hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference] [--workload c2|c3|c5]
+
+One "step" is one pass of the MoE FFN layer over one batch of synthetic tokens. Prints ONE JSON
+line (rank 0). `value` is device-timed throughput with inputs resident in HBM; `e2e` is the same
+metric through the host-buffer call (pinned host rows in, host rows out, copies inside the timed
+region). L2 is flushed between timed steps (a 256 MiB buffer is rewritten outside the timed
+region). `--impl reference` times the reference's own CPU implementation of the same layer on
+the host cores (the compiled reference when oracle/_ref is present, else the plain-C port).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def oracle_backend(prefer_reference):
+    """The CPU checker used as a timed baseline: the compiled reference when asked for and
+    present, else this repository's plain-C port of it."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    from oracle_lib import Port, Ref
+    if prefer_reference and Ref.available():
+        return Ref(), "reference"
+    return Port(), "port"
+
+
+def cpu_layer_tokens_per_s(workload, tokens_per_step, steps, threads, prefer_reference=False):
+    """Times the CPU path on `tokens_per_step` tokens per step with `threads` host threads."""
+    backend, kind = oracle_backend(prefer_reference)
+    w, router = workload.host_copy()
+    L = backend.layer(workload.spec, w, router=router, allow_q4k=True)
+    x, logits = workload.tokens(tokens_per_step)
+    x = x.cpu().numpy()
+    logits = None if logits is None else logits.cpu().numpy()
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        rc, _, _, _ = backend.moe_tokens(L, x, logits=logits, threads=threads)
+        times.append(time.perf_counter() - t0)
+        if rc != 0:
+            raise RuntimeError(f"CPU path refused with status {rc}")
+    return tokens_per_step * len(times) / sum(times), kind, sum(times) / len(times)
+
+
+def run_reference(args):
+    """`--impl reference`: the reference's CPU implementation on the host cores, rank 0 only."""
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from yvex_b200 import synth
+    from yvex_b200.workloads import MoEWorkload
+    cores = os.cpu_count() or 1
+    # The reference has no Q4_K decoder (src/gguf/quant_registry.c:67): when the compiled
+    # reference is present its arm runs the Q2_K-down twin of the layer, the qtype its own MoE
+    # path ships with; otherwise the port runs the layer exactly as configured.
+    _, kind = oracle_backend(True)
+    down = synth.Q2_K if kind == "reference" else synth.Q4_K
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    wl = MoEWorkload(args.workload, 1, device=dev, down_qtype=down)
+    per_step = max(cores, 1)
+    tps, kind, sec = cpu_layer_tokens_per_s(wl, per_step, max(1, min(args.steps, 3)), cores, True)
+    line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": min(args.steps, 3), "warmup": 0, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f64-accum (reference CPU path)", "data": "synthetic",
+            "config": {"workload": wl.name + ("-q2k-down" if down == synth.Q2_K else ""), **wl.cfg,
+                       "tokens_per_step": per_step},
+            "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": kind,
+                             "sample": f"{per_step} tokens per step, one thread per token"},
+            "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_native(args):
+    import torch
+    import torch.distributed as dist
+    from yvex_b200 import lib, synth
+    from yvex_b200.workloads import MoEWorkload
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    peaks = measured_peaks()
+
+    wl = MoEWorkload(args.workload, 1, device=dev)
+    geom = lib.geometry_of(wl.spec)
+    weights = lib.weights_of(wl.tensors)
+    tokens = wl.cfg["tokens"]
+    wide = tokens > 64
+    pool = 16 if not wide else 1
+    xs = [wl.tokens(tokens) for _ in range(pool)]
+    ws = torch.empty(lib.moe_workspace_bytes(geom, tokens), dtype=torch.uint8, device=dev)
+    out = torch.empty((tokens, wl.cfg["hidden"]), dtype=torch.float32, device=dev)
+    sel = torch.empty((tokens, wl.spec.topk), dtype=torch.int32, device=dev)
+    wts = torch.empty((tokens, wl.spec.topk), dtype=torch.float32, device=dev)
+    status = lib.Status(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    host_in = [torch.empty((tokens, wl.cfg["hidden"]), dtype=torch.float32).pin_memory() for _ in range(pool)]
+    host_lg = []
+    for i, (x, lg) in enumerate(xs):
+        host_in[i].copy_(x)
+        host_lg.append(None if lg is None else lg.cpu().pin_memory())
+    host_out = torch.empty((tokens, wl.cfg["hidden"]), dtype=torch.float32).pin_memory()
+    dev_in = torch.empty_like(out)
+    dev_lg = None if xs[0][1] is None else torch.empty_like(xs[0][1])
+
+    def step(i):
+        x, lg = xs[i % pool]
+        lib.moe_layer(geom, weights, x, status, logits=lg, wide=wide, workspace=ws, out=out, selected=sel, wts=wts)
+
+    def step_e2e(i):
+        dev_in.copy_(host_in[i % pool], non_blocking=True)
+        if dev_lg is not None:
+            dev_lg.copy_(host_lg[i % pool], non_blocking=True)
+        lib.moe_layer(geom, weights, dev_in, status, logits=dev_lg, wide=wide, workspace=ws, out=out,
+                      selected=sel, wts=wts)
+        host_out.copy_(out, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(steps):
+            flush.fill_(i & 0xFF)          # evict L2 between timed steps (outside the timed span)
+            starts[i].record()
+            fn(i)
+            stops[i].record()
+        torch.cuda.synchronize()
+        return [a.elapsed_time(b) for a, b in zip(starts, stops)]
+
+    for i in range(args.warmup):
+        step(i)
+        step_e2e(i)
+    barrier()
+    launches0 = lib.lib.yvex_b200_launch_count()
+    with ClockSampler(local) as clocks:
+        ms = timed(step, args.steps)
+        launches = lib.lib.yvex_b200_launch_count() - launches0
+        barrier()
+        ms_e2e = timed(step_e2e, args.steps)
+        barrier()
+        # per-phase timing for the roofline of the dominant kernel
+        n_ph = 5
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(n_ph)] for _ in range(args.steps)]
+        for row in evs:
+            for e in row:
+                e.record()
+        torch.cuda.synchronize()
+        import ctypes as C
+        phase_ms = [[] for _ in range(n_ph - 1)]
+        arr_t = C.c_void_p * n_ph
+        for i in range(args.steps):
+            arr = arr_t(*[e.cuda_event for e in evs[i]])
+            flush.fill_(i & 0xFF)
+            lib.lib.yvex_b200_phase_events(arr, n_ph)
+            step(i)
+            lib.lib.yvex_b200_phase_events(None, 0)
+        torch.cuda.synchronize()
+        used = 4 if not wide else 5
+        for i in range(args.steps):
+            for p in range(used - 1):
+                phase_ms[p].append(evs[i][p].elapsed_time(evs[i][p + 1]))
+    if status.read() != 0:
+        raise RuntimeError(f"device status word = {status.read()} after the timed region")
+
+    total = torch.tensor([sum(ms), sum(ms_e2e)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.MAX)
+    t_dev, t_e2e = total.tolist()
+    value = world * tokens * args.steps / (t_dev / 1e3)
+    e2e = world * tokens * args.steps / (t_e2e / 1e3)
+    phases = [sum(p) / len(p) for p in phase_ms[:used - 1]]
+    names = ["route", "gate_up", "down_combine"] if not wide else ["route_permute", "gate_up", "down", "combine"]
+    roofline = None
+    if not wide:
+        pb = wl.phase_bytes_decode()
+        cand = {"gate_up": (pb["gate_up"], phases[1]), "down": (pb["down"], phases[2])}
+        top = max(cand, key=lambda k: cand[k][1])
+        ach = cand[top][0] / (cand[top][1] * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": top, "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                    "layer_achieved": wl.bytes_per_token_decode() / (t_dev / args.steps * 1e-3) / 1e9}
+    if rank == 0:
+        cpu = None
+        if world == 1:
+            cores = os.cpu_count() or 1
+            try:
+                tps, kind, _ = cpu_layer_tokens_per_s(wl, cores if not wide else max(cores, 8), 1, cores)
+                cpu = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
+                       "sample": f"{cores} tokens of the same layer, one thread per token (plain-C port; the "
+                                 "reference has no Q4_K decoder)"}
+            except Exception as exc:  # the baseline must never take the GPU number down with it
+                cpu = {"value": None, "unit": UNIT, "cores": cores, "kind": "port", "sample": f"failed: {exc}"}
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": t_dev / args.steps, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f16-mma/f32-accum, bf16 rounding points",
+                "data": "synthetic",
+                "config": {"workload": wl.name, **wl.cfg, "gate_up_qtype": "IQ2_XXS", "down_qtype": "Q4_K",
+                           "l2": "flushed between steps (256 MiB rewrite)", "parallelism": f"replicas x{world}"},
+                "clocks": clocks.summary(),
+                "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(tokens * wl.cfg["hidden"] * 4 + (0 if dev_lg is None else dev_lg.numel() * 4)),
+                        "d2h_bytes_per_step": int(tokens * wl.cfg["hidden"] * 4)},
+                "gpu_launches": int(launches),
+                "phases_ms": dict(zip(names, phases)),
+                "roofline": roofline, "cpu_baseline": cpu}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c5"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

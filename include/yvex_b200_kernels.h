@@ -1,0 +1,166 @@
+/*
+ * yvex_b200 device layer: the thin C-ABI shim over the hand-written sm_100a kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void* so C11
+ * callers need no CUDA headers), enqueues its kernels on that stream and returns immediately
+ * with a yvex_status value (0 ok, negative = refusal BEFORE any launch). Nothing here allocates,
+ * synchronises or copies to the host. Numerical and argument faults found on the device are
+ * reported through the caller's `int *status` word with the reference's convention
+ * (src/backend/cuda/moe.c:293-295): 0 ok, 1 non-finite numerics, 2 invalid arguments,
+ * 3 bounded wait expired; kernels return early once it is non-zero.
+ *
+ * Unsupported qtypes fail closed at entry with YVEX_ERR_UNSUPPORTED (-5): the admitted set is
+ * the reference's registry (src/gguf/quant_registry.c:50-103) - F32, F16, BF16, Q8_0, Q2_K,
+ * IQ2_XXS - plus Q4_K, which the reference stores but cannot decode; Q4_K is this library's
+ * declared extension and is compiled in only because the benchmark configs name it.
+ */
+#ifndef YVEX_B200_KERNELS_H
+#define YVEX_B200_KERNELS_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define YVEX_B200_STATUS_OK 0
+#define YVEX_B200_STATUS_NUMERIC 1
+#define YVEX_B200_STATUS_ARGUMENT 2
+#define YVEX_B200_STATUS_TIMEOUT 3
+
+/* Library identity; also the cheapest way to prove the shared object loaded. */
+const char *yvex_b200_version(void);
+/* 1 if `qtype` has a device decoder/dot in this library, else 0 (fail-closed answer). */
+int yvex_b200_qtype_supported(unsigned int qtype);
+/* Block geometry of the reference's table (src/gguf/qtype.c:15-104); 0 on unknown id. */
+int yvex_b200_qtype_geometry(unsigned int qtype, unsigned int *block_elements,
+                             unsigned int *block_bytes);
+
+/*
+ * Accounting the reference keeps in yvex_backend_cuda_operation_facts.kernel_launches
+ * (include/yvex/internal/backend.h:325-331): kernels this library has enqueued since load.
+ */
+unsigned long long yvex_b200_launch_count(void);
+/*
+ * Optional per-phase timing, the device-side counterpart of the reference's per-phase
+ * nanosecond counters (include/yvex/internal/moe.h:209-210). While `events` (an array of
+ * `count` cudaEvent_t handles owned by the caller) is registered, the MoE entry points record
+ * events[0] when they start and events[i] after phase i (1 route, 2 gate/up, 3 down+combine for
+ * the narrow path; 1 route+permute, 2 gate/up GEMM, 3 down GEMM, 4 combine for the wide path).
+ * Pass count 0 to unregister. Process-wide; not meant for concurrent callers.
+ */
+int yvex_b200_phase_events(void **events, int count);
+
+/*
+ * Elementwise decode of encoded rows to f32, bit-exact with yvex_quant_decode_block
+ * (src/gguf/quant_block.c:769-881). Replaces yvex_encoded_row_decode
+ * (src/backend/cuda/kernels.cu:784-800). out is [rows x width].
+ */
+int yvex_b200_dequant_rows(unsigned int qtype, const void *encoded, uint64_t rows, uint64_t width,
+                           uint64_t row_bytes, float *out, int *status, void *stream);
+
+/*
+ * Dequant-fused matvec: out[i][r] = dot(row r, input[i]) (+ additive[i][r]), optional bf16
+ * rounding of the result. Replaces yvex_qtype_matvec (src/backend/cuda/kernels.cu:529-626);
+ * CPU meaning: a loop of yvex_quant_cpu_dot (src/gguf/quant_compute.c:116-181).
+ * input is [input_rows x width] f32, out is [input_rows x rows] f32.
+ */
+int yvex_b200_gemv(unsigned int qtype, const void *encoded, uint64_t rows, uint64_t width,
+                   uint64_t row_bytes, const float *input, uint64_t input_rows,
+                   const float *additive, float *out, int round_bf16, int *status, void *stream);
+
+/* Geometry and policy of one MoE FFN layer: the fields of yvex_moe_layer_plan
+ * (include/yvex/internal/moe.h:54-84) that the execution path reads. */
+typedef struct {
+    uint64_t hidden, experts, topk, inter, shared_inter;
+    double scaling, limit;          /* routed_scaling_factor, activation_limit */
+    int normalize;                  /* normalize_topk_probabilities */
+    int router_class;               /* 1 learned hidden-state, 0 token-id hash table */
+    unsigned int gate_qtype, up_qtype, down_qtype;
+    uint64_t hash_rows, hash_stored_rows;
+} yvex_b200_moe_geometry;
+
+/* Device addresses of the layer's weights (canonical row layout, routed packs expert-major:
+ * expert e at byte offset e * rows_per_expert * row_bytes, src/backend/cuda/moe.c:617-619). */
+typedef struct {
+    const float *router;            /* [experts x hidden] f32, NULL when logits are supplied */
+    const float *bias;              /* [experts] f32 or NULL */
+    const int32_t *hash_table;      /* [hash_stored_rows x topk] or NULL */
+    const void *gate, *up, *down;
+    const void *shared_gate, *shared_up, *shared_down;
+} yvex_b200_moe_weights;
+
+/* Bytes of 256-byte-aligned device scratch the MoE entry points need for `rows` tokens. */
+uint64_t yvex_b200_moe_workspace_bytes(const yvex_b200_moe_geometry *g, uint64_t rows);
+
+/*
+ * Router only: sqrt(softplus(logit)) scoring, bias-corrected top-k with lowest-index tie-break
+ * (or the hash table row of the token id), weights = unbiased scores normalised over the
+ * selection times the scaling factor. Replaces yvex_moe_route_rows
+ * (src/backend/cuda/moe_kernels.cu:180-291); CPU meaning yvex_moe_route_cpu
+ * (src/graph/moe.c:520-585). `rows_f32` is the bf16-exact hidden rows [rows x hidden] when the
+ * router projection is computed here, otherwise `logits` [rows x experts] is read.
+ * selected is [rows x topk] int32, weights [rows x topk] f32.
+ */
+int yvex_b200_moe_route(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w,
+                        const float *rows_f32, const float *logits, const uint32_t *token_ids,
+                        uint64_t rows, int32_t *selected, float *weights, float *logits_out,
+                        void *workspace, uint64_t workspace_bytes, int *status, void *stream);
+
+/*
+ * One MoE FFN layer for a narrow batch (decode): ingress bf16 rounding, router, k routed experts
+ * + the shared expert as dequant-fused matvecs with the SwiGLU*weight->bf16 epilogue, per-pair
+ * bf16 down outputs summed in rank order, bf16(routed + shared). Replaces the kernel sequence of
+ * moe_cuda_graph_enqueue (src/backend/cuda/moe.c:1619-1643) for a layer without the mHC
+ * envelope; CPU meaning src/runtime/moe.c:596-632. rows <= 64.
+ * x and out are [rows x hidden] f32 on the device.
+ */
+int yvex_b200_moe_decode(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w,
+                         const float *x, const float *logits, const uint32_t *token_ids,
+                         uint64_t rows, float *out, int32_t *selected_out, float *weights_out,
+                         void *workspace, uint64_t workspace_bytes, int *status, void *stream);
+
+/*
+ * The same layer for a wide batch (prefill / expert-parallel shard): route, expert-major
+ * counting sort (permute), grouped dequant GEMM on the tensor cores (gate/up -> SwiGLU*weight
+ * -> bf16 -> down -> bf16), rank-ordered unpermute + shared + bf16. No reference counterpart
+ * admits more than 62 rows (src/graph/worklist.c:316); semantics per token are those of
+ * yvex_b200_moe_decode. `expert_begin/expert_count` restrict routed work to a contiguous
+ * expert range (an expert-parallel shard); pairs outside it are left to other ranks.
+ */
+int yvex_b200_moe_wide(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w,
+                       const float *x, const float *logits, const uint32_t *token_ids,
+                       uint64_t rows, float *out, int32_t *selected_out, float *weights_out,
+                       void *workspace, uint64_t workspace_bytes, int *status, void *stream);
+
+/*
+ * Online-softmax causal GQA attention at decode: one query position per session against a bf16
+ * KV cache, f32 accumulation and output. q [sessions][q_heads][head_dim] bf16, k/v
+ * [sessions][kv_heads][context][head_dim] bf16, out [sessions][q_heads][head_dim] f32; keys
+ * 0..position are visible. Replaces the online-softmax core of yvex_attention_reduce_native
+ * (src/backend/cuda/attention_kernels.cu:259-406) and yvex_gqa_causal_f32
+ * (src/backend/cuda/transformer_kernels.cu:85-145); CPU meaning: cpu_op_attention
+ * (src/backend/cpu.c:319-411) per (session, q head). scratch holds the split-KV partials.
+ */
+uint64_t yvex_b200_attention_workspace_bytes(uint64_t sessions, uint64_t q_heads,
+                                             uint64_t kv_heads, uint64_t head_dim,
+                                             uint64_t context);
+int yvex_b200_attention_gqa_decode(const void *q_bf16, const void *k_bf16, const void *v_bf16,
+                                   uint64_t sessions, uint64_t q_heads, uint64_t kv_heads,
+                                   uint64_t head_dim, uint64_t context, uint64_t position,
+                                   float scale, float *out, void *workspace,
+                                   uint64_t workspace_bytes, int *status, void *stream);
+
+/*
+ * Single-head f32 attention, the public op of the reference vtable (op_attention,
+ * src/backend/cpu.c:319-411, src/backend/cuda/kernels.cu:362-435): q [d], keys/values
+ * [seq_len x d] f32, scores/probabilities [seq_len] written like the reference does.
+ */
+int yvex_b200_attention_f32(const float *q, const float *keys, const float *values,
+                            uint64_t seq_len, uint64_t head_dim, uint64_t position, float scale,
+                            int causal, float *scores, float *probabilities, float *out,
+                            int *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -14,8 +14,8 @@ import subprocess
 
 import numpy as np
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-ORACLE = os.path.join(ROOT, "oracle")
+ORACLE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(ORACLE)
 u64, u32, f32p = C.c_uint64, C.c_uint32, C.POINTER(C.c_float)
 
 

@@ -1,0 +1,87 @@
+"""CPU-side checks of the drop-in boundary: the shared library loads, exports every symbol the
+public headers declare, and refuses bad arguments / unsupported qtypes before touching a device."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from yvex_b200 import build
+    build.build()
+    from yvex_b200 import lib as L
+    return L
+
+
+def declared_symbols():
+    names = set()
+    inc = os.path.join(ROOT, "include")
+    for f in sorted(os.listdir(inc)):
+        text = open(os.path.join(inc, f)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(yvex_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
+
+
+def test_library_exports_every_declared_symbol(lib):
+    missing = [n for n in declared_symbols() if not hasattr(lib.lib, n)]
+    assert not missing, missing
+    assert len(declared_symbols()) >= 12
+    assert b"sm_100a" in lib.lib.yvex_b200_version()
+
+
+def test_qtype_registry_is_fail_closed(lib):
+    supported = [q for q in range(0, 64) if lib.lib.yvex_b200_qtype_supported(q)]
+    assert supported == [0, 1, 8, 10, 12, 16, 30]
+    e, b = C.c_uint(), C.c_uint()
+    assert lib.lib.yvex_b200_qtype_geometry(16, C.byref(e), C.byref(b)) == 1 and (e.value, b.value) == (256, 66)
+    assert lib.lib.yvex_b200_qtype_geometry(12, C.byref(e), C.byref(b)) == 1 and (e.value, b.value) == (256, 144)
+    assert lib.lib.yvex_b200_qtype_geometry(43, C.byref(e), C.byref(b)) == 0
+
+
+def test_entry_points_refuse_before_launch(lib):
+    # No device is needed: every refusal below happens before the first CUDA call. Pointers are
+    # dummies that must never be dereferenced.
+    dummy = C.c_void_p(0x1000)
+    L = lib.lib
+    # unsupported qtype ids (Q3_K = 11, MXFP4 = 39 has no kernel here, 43 unknown)
+    for q in (11, 39, 43):
+        assert L.yvex_b200_gemv(q, dummy, 8, 256, 110, dummy, 1, None, dummy, 0, dummy, None) == -5
+        assert L.yvex_b200_dequant_rows(q, dummy, 8, 256, 110, dummy, dummy, None) == -5
+    # row width not block divisible / inconsistent row bytes -> bounds
+    assert L.yvex_b200_gemv(16, dummy, 8, 200, 66, dummy, 1, None, dummy, 0, dummy, None) == -7
+    assert L.yvex_b200_gemv(16, dummy, 8, 256, 64, dummy, 1, None, dummy, 0, dummy, None) == -7
+    # missing pointers -> invalid argument
+    assert L.yvex_b200_gemv(16, None, 8, 256, 66, dummy, 1, None, dummy, 0, dummy, None) == -10
+    # attention: bad scale, position out of range
+    assert L.yvex_b200_attention_gqa_decode(dummy, dummy, dummy, 1, 4, 1, 128, 64, 64, 1.0, dummy, dummy, 1 << 20,
+                                            dummy, None) == -7
+    assert L.yvex_b200_attention_gqa_decode(dummy, dummy, dummy, 1, 4, 1, 128, 64, 3, -1.0, dummy, dummy, 1 << 20,
+                                            dummy, None) == -10
+    g = lib.MoeGeometry()
+    g.hidden, g.experts, g.topk, g.inter, g.shared_inter = 512, 8, 2, 256, 256
+    g.scaling, g.limit, g.normalize, g.router_class = 1.5, 10.0, 1, 1
+    g.gate_qtype, g.up_qtype, g.down_qtype = 16, 16, 11          # Q3_K down: admitted storage, no codec
+    w = lib.MoeWeights()
+    for name, _ in lib.MoeWeights._fields_:
+        setattr(w, name, 0x1000)
+    assert L.yvex_b200_moe_decode(C.byref(g), C.byref(w), dummy, None, None, 1, dummy, None, None, dummy, 1 << 30,
+                                  dummy, None) == -5
+    g.down_qtype = 10
+    assert L.yvex_b200_moe_decode(C.byref(g), C.byref(w), dummy, None, None, 65, dummy, None, None, dummy, 1 << 30,
+                                  dummy, None) == -5      # narrow entry refuses wide batches
+    assert L.yvex_b200_moe_decode(C.byref(g), C.byref(w), dummy, None, None, 1, dummy, None, None, dummy, 16,
+                                  dummy, None) == -2      # workspace too small
+    assert lib.moe_workspace_bytes(g, 1) % 256 == 0 and lib.moe_workspace_bytes(g, 1) > 0
+
+
+def test_compute_without_device_fails_loudly(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("device present")
+    with pytest.raises(RuntimeError):
+        lib.Status()

@@ -1,0 +1,306 @@
+// MoE FFN layer: ingress rounding, router scoring + top-k, expert matvecs with the SwiGLU epilogue,
+// rank-ordered combine. Numerics follow the reference CPU path step by step:
+//   ingress  bf16(x)                               src/graph/moe.c:487-489
+//   router   logits (double dot) -> sqrt(softplus) -> biased top-k, lowest index wins ties ->
+//            unbiased scores normalised over the selection * scaling     src/graph/moe.c:497-585
+//   expert   g=min(gate.x,L) u=clamp(up.x,+-L) mid=bf16(silu(g)*u*w) y=bf16(down.mid)   :587-622
+//   combine  routed = sum over ranks in rank order (f32), out = bf16(routed + shared)
+//                                                                src/runtime/moe.c:607-632
+#include "moe_common.cuh"
+
+namespace yb {
+
+// ---- ingress: x -> bf16-exact f32 rows ----------------------------------------------------------
+__global__ void ingress_round_kernel(const float *x, float *xr, uint64_t n, int *status) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n;
+         i += (uint64_t)gridDim.x * blockDim.x) {
+        float v = x[i];
+        if (!isfinite(v)) raise(status, YVEX_B200_STATUS_NUMERIC);
+        xr[i] = bf16_round(v);
+    }
+}
+
+// ---- router projection: one warp per (row, expert), double accumulation -------------------------
+__global__ void router_logits_kernel(const float *router, const float *xr, uint64_t rows,
+                                     uint64_t experts, uint64_t hidden, float *logits, int *status) {
+    const int lane = threadIdx.x & 31;
+    const uint64_t warps = (uint64_t)gridDim.x * (blockDim.x >> 5);
+    for (uint64_t job = blockIdx.x * (uint64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+         job < rows * experts; job += warps) {
+        const float *w = router + (job % experts) * hidden, *x = xr + (job / experts) * hidden;
+        double acc = 0.0;
+        for (uint64_t c = lane; c < hidden; c += 32) acc += (double)__ldg(w + c) * (double)__ldg(x + c);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) {
+            float v = (float)acc;
+            if (!isfinite(v)) raise(status, YVEX_B200_STATUS_NUMERIC);
+            logits[job] = v;
+        }
+    }
+}
+
+// ---- scoring + top-k: one warp per row, experts <= 256 (8 per lane), topk <= 16 ------------------
+__global__ void route_rows_kernel(MoeGeom g, const float *logits, const float *bias,
+                                  const int32_t *hash_table, const uint32_t *token_ids,
+                                  uint64_t rows, int32_t *selected, float *weights, int *status) {
+    const int lane = threadIdx.x & 31;
+    const uint64_t row = blockIdx.x * (uint64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    float score[8], biased[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint64_t e = lane + 32u * i;
+        score[i] = 0.0f;
+        biased[i] = -INFINITY;
+        if (e < g.experts) {
+            double v = logits[row * g.experts + e];
+            double sp = v > 0.0 ? v + log1p(exp(-v)) : log1p(exp(v));
+            double s = sqrt(sp);
+            if (!isfinite(s)) raise(status, YVEX_B200_STATUS_NUMERIC);
+            score[i] = (float)s;
+            biased[i] = (bias ? bias[e] : 0.0f) + score[i];
+        }
+    }
+    int32_t mine = -1;       // lane r keeps the expert selected at rank r
+    float mine_w = 0.0f;
+    if (g.router_class == 0) {
+        bool ok = token_ids && hash_table && token_ids[row] < g.hash_rows;
+        if (!ok) { raise(status, YVEX_B200_STATUS_ARGUMENT); return; }
+        const int32_t *tr = hash_table + (g.hash_stored_rows == 1 ? 0 : (uint64_t)token_ids[row] * g.topk);
+        if ((uint64_t)lane < g.topk) {
+            mine = tr[lane];
+            if (mine < 0 || (uint64_t)mine >= g.experts) { raise(status, YVEX_B200_STATUS_ARGUMENT); mine = 0; }
+        }
+        // duplicate selection is an error in the reference (src/graph/moe.c:566-570)
+        for (uint64_t r = 0; r < g.topk; ++r) {
+            int32_t other = __shfl_sync(0xffffffffu, mine, (int)r);
+            if ((uint64_t)lane < g.topk && (uint64_t)lane > r && other == mine) raise(status, YVEX_B200_STATUS_ARGUMENT);
+        }
+    } else {
+        for (uint64_t r = 0; r < g.topk; ++r) {
+            float best = -INFINITY;
+            int best_e = 0x7fffffff;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int e = lane + 32 * i;
+                if ((uint64_t)e < g.experts && (biased[i] > best || (biased[i] == best && e < best_e))) {
+                    best = biased[i];
+                    best_e = e;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+            }
+            if (best_e == 0x7fffffff) { raise(status, YVEX_B200_STATUS_NUMERIC); best_e = 0; }
+            if ((best_e & 31) == lane) biased[best_e >> 5] = -INFINITY;   // consumed (scores are finite)
+            if ((uint64_t)lane == r) mine = best_e;
+        }
+    }
+    // weight of rank r = unbiased score of its expert; total accumulated in rank order in double
+    for (uint64_t r = 0; r < g.topk; ++r) {
+        int32_t e = __shfl_sync(0xffffffffu, mine, (int)r);
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) if (e == lane + 32 * i) s = score[i];
+        s = __shfl_sync(0xffffffffu, s, e & 31);
+        if ((uint64_t)lane == r) mine_w = s;
+    }
+    double total = 0.0;
+    for (uint64_t r = 0; r < g.topk; ++r) total += (double)__shfl_sync(0xffffffffu, mine_w, (int)r);
+    if (g.normalize && (!isfinite(total) || total <= 0.0)) raise(status, YVEX_B200_STATUS_NUMERIC);
+    if ((uint64_t)lane < g.topk) {
+        double v = mine_w;
+        if (g.normalize) v /= total;
+        v *= g.scaling;
+        selected[row * g.topk + lane] = mine;
+        weights[row * g.topk + lane] = (float)v;
+    }
+}
+
+// ---- reference-shaped expert kernels (any supported qtype): one warp per output element ---------
+// pair p of row r: p < topk -> routed expert selected[r][p] with weights[r][p]; p == topk -> shared.
+__global__ void expert_up_rows_kernel(MoeGeom g, MoeWeights w, const float *xr, const int32_t *selected,
+                                      const float *weights, uint64_t rows, float *mid, int *status) {
+    const int lane = threadIdx.x & 31;
+    const uint64_t ppr = g.topk + 1, imax = max(g.inter, g.shared_inter);
+    const uint64_t warps = (uint64_t)gridDim.x * (blockDim.x >> 5);
+    const Geometry gg = geometry_of(g.gate_qtype), ug = geometry_of(g.up_qtype);
+    const uint64_t grb = g.hidden / gg.elems * gg.bytes, urb = g.hidden / ug.elems * ug.bytes;
+    for (uint64_t job = blockIdx.x * (uint64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+         job < rows * ppr * imax; job += warps) {
+        const uint64_t i = job % imax, pair = job / imax, r = pair / ppr, p = pair % ppr;
+        const bool shared = p == g.topk;
+        const uint64_t width = shared ? g.shared_inter : g.inter;
+        if (i >= width) continue;
+        const uint8_t *gate, *up;
+        float rw = 1.0f;
+        if (shared) {
+            gate = (const uint8_t *)w.shared_gate + i * grb;
+            up = (const uint8_t *)w.shared_up + i * urb;
+        } else {
+            const uint64_t e = (uint64_t)selected[r * g.topk + p];
+            gate = (const uint8_t *)w.gate + (e * g.inter + i) * grb;
+            up = (const uint8_t *)w.up + (e * g.inter + i) * urb;
+            rw = weights[r * g.topk + p];
+        }
+        const float *x = xr + r * g.hidden;
+        float ga = 0.0f, ua = 0.0f;
+        for (uint64_t c = lane; c < g.hidden; c += 32) {
+            const float xv = __ldg(x + c);
+            ga = fmaf(decode_element(g.gate_qtype, gate + (c / gg.elems) * gg.bytes, (unsigned)(c % gg.elems), status), xv, ga);
+            ua = fmaf(decode_element(g.up_qtype, up + (c / ug.elems) * ug.bytes, (unsigned)(c % ug.elems), status), xv, ua);
+        }
+        ga = warp_sum(ga);
+        ua = warp_sum(ua);
+        if (lane == 0) mid[pair * imax + i] = swiglu_mid(ga, ua, rw, (float)g.limit, status);
+    }
+}
+
+__global__ void expert_down_rows_kernel(MoeGeom g, MoeWeights w, const int32_t *selected, const float *mid,
+                                        uint64_t rows, float *out, int *status) {
+    const int lane = threadIdx.x & 31;
+    const uint64_t ppr = g.topk + 1, imax = max(g.inter, g.shared_inter);
+    const uint64_t warps = (uint64_t)gridDim.x * (blockDim.x >> 5);
+    const Geometry dg = geometry_of(g.down_qtype);
+    for (uint64_t job = blockIdx.x * (uint64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+         job < rows * g.hidden; job += warps) {
+        const uint64_t h = job % g.hidden, r = job / g.hidden;
+        float routed = 0.0f, shared = 0.0f;
+        for (uint64_t p = 0; p < ppr; ++p) {
+            const bool is_shared = p == g.topk;
+            const uint64_t width = is_shared ? g.shared_inter : g.inter;
+            const uint64_t rb = width / dg.elems * dg.bytes;
+            const uint8_t *row = is_shared ? (const uint8_t *)w.shared_down + h * rb
+                                           : (const uint8_t *)w.down + ((uint64_t)selected[r * g.topk + p] * g.hidden + h) * rb;
+            const float *m = mid + (r * ppr + p) * imax;
+            float acc = 0.0f;
+            for (uint64_t c = lane; c < width; c += 32)
+                acc = fmaf(decode_element(g.down_qtype, row + (c / dg.elems) * dg.bytes, (unsigned)(c % dg.elems), status), m[c], acc);
+            acc = warp_sum(acc);
+            if (!isfinite(acc)) raise(status, YVEX_B200_STATUS_NUMERIC);
+            acc = bf16_round(acc);
+            if (is_shared) shared = acc; else routed += acc;
+        }
+        if (lane == 0) out[job] = bf16_round(routed + shared);
+    }
+}
+
+}  // namespace yb
+
+using namespace yb;
+
+static int check_geometry(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w) {
+    if (!g || !w) return ERR_INVALID_ARG;
+    if (!g->hidden || !g->experts || !g->topk || !g->inter || !g->shared_inter) return ERR_INVALID_ARG;
+    if (g->experts > 256 || g->topk > 16 || g->topk > g->experts) return ERR_INVALID_ARG;   // src/graph/moe.c:529
+    if (g->inter > 4096 || g->shared_inter > 4096) return ERR_BOUNDS;                       // src/graph/moe.c:600
+    const unsigned q[3] = {g->gate_qtype, g->up_qtype, g->down_qtype};
+    for (unsigned i = 0; i < 3; ++i)
+        if (!qtype_supported(q[i])) return ERR_UNSUPPORTED;
+    if (g->hidden % geometry_of(g->gate_qtype).elems || g->hidden % geometry_of(g->up_qtype).elems ||
+        g->inter % geometry_of(g->down_qtype).elems || g->shared_inter % geometry_of(g->down_qtype).elems)
+        return ERR_BOUNDS;
+    if (!w->gate || !w->up || !w->down || !w->shared_gate || !w->shared_up || !w->shared_down)
+        return ERR_INVALID_ARG;
+    if (g->router_class == 0 && (!w->hash_table || !g->hash_rows)) return ERR_INVALID_ARG;
+    if (!(g->limit > 0.0) || !isfinite(g->scaling)) return ERR_INVALID_ARG;
+    return OK;
+}
+
+extern "C" uint64_t yvex_b200_moe_workspace_bytes(const yvex_b200_moe_geometry *g, uint64_t rows) {
+    return g ? moe_workspace_layout(*g, rows, nullptr) : 0;
+}
+
+static int route_into(const MoeGeom &g, const yvex_b200_moe_weights *w, const float *xr,
+                      const float *logits_in, const uint32_t *token_ids, uint64_t rows,
+                      float *logits_ws, int32_t *selected, float *weights, int *status, cudaStream_t s) {
+    const float *logits = logits_in;
+    int launches = 1;
+    if (w->router) {
+        uint64_t jobs = rows * g.experts;
+        unsigned grid = grid_for(jobs, 8, 8);
+        router_logits_kernel<<<grid, 256, 0, s>>>(w->router, xr, rows, g.experts, g.hidden, logits_ws, status);
+        logits = logits_ws;
+        ++launches;
+    } else if (!logits_in) {
+        return ERR_INVALID_ARG;
+    }
+    route_rows_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(g, logits, w->bias, w->hash_table, token_ids, rows,
+                                                                selected, weights, status);
+    return launch_status(launches);
+}
+
+int yb::moe_ingress_and_route(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, const float *x,
+                              const float *logits, const uint32_t *token_ids, uint64_t rows, int *status,
+                              cudaStream_t s) {
+    const uint64_t n = rows * g.hidden;
+    ingress_round_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>(x, ws.xr, n, status);
+    int rc = launch_status(1);
+    if (rc != OK) return rc;
+    return route_into(g, &w, ws.xr, logits, token_ids, rows, ws.logits, ws.selected, ws.weights, status, s);
+}
+
+int yb::moe_check_geometry(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w) {
+    return check_geometry(g, w);
+}
+
+extern "C" int yvex_b200_moe_route(const yvex_b200_moe_geometry *geom, const yvex_b200_moe_weights *w,
+                                   const float *rows_f32, const float *logits, const uint32_t *token_ids,
+                                   uint64_t rows, int32_t *selected, float *weights, float *logits_out,
+                                   void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
+    if (!geom || !w || !selected || !weights || !status || !rows) return ERR_INVALID_ARG;
+    if (geom->experts > 256 || geom->topk > 16 || geom->topk > geom->experts || !geom->experts || !geom->topk)
+        return ERR_INVALID_ARG;
+    MoeGeom g = *geom;
+    float *lw = logits_out;
+    if (w->router) {
+        if (!rows_f32) return ERR_INVALID_ARG;
+        if (!lw) {
+            if (!workspace || workspace_bytes < rows * g.experts * sizeof(float)) return ERR_NOMEM;
+            lw = static_cast<float *>(workspace);
+        }
+    }
+    return route_into(g, w, rows_f32, logits, token_ids, rows, lw, selected, weights, status, as_stream(stream));
+}
+
+extern "C" int yvex_b200_moe_decode(const yvex_b200_moe_geometry *geom, const yvex_b200_moe_weights *w,
+                                    const float *x, const float *logits, const uint32_t *token_ids,
+                                    uint64_t rows, float *out, int32_t *selected_out, float *weights_out,
+                                    void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
+    int rc = check_geometry(geom, w);
+    if (rc != OK) return rc;
+    if (!x || !out || !status || !rows || rows > 64) return rows > 64 ? ERR_UNSUPPORTED : ERR_INVALID_ARG;
+    MoeGeom g = *geom;
+    MoeWorkspace ws;
+    if (!workspace || workspace_bytes < moe_workspace_layout(g, rows, &ws)) return ERR_NOMEM;
+    ws.rebase(workspace);
+    cudaStream_t s = as_stream(stream);
+    mark_phase(0, s);
+    rc = moe_ingress_and_route(g, *w, ws, x, logits, token_ids, rows, status, s);
+    if (rc != OK) return rc;
+    mark_phase(1, s);
+    rc = moe_experts_narrow(g, *w, ws, rows, out, status, s);
+    if (rc != OK) return rc;
+    if (selected_out) cudaMemcpyAsync(selected_out, ws.selected, rows * g.topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, s);
+    if (weights_out) cudaMemcpyAsync(weights_out, ws.weights, rows * g.topk * sizeof(float), cudaMemcpyDeviceToDevice, s);
+    return launch_status(0);
+}
+
+// Reference-shaped expert execution: used when no streaming decoder covers the layer's qtypes.
+int yb::moe_experts_rows(const MoeGeom &g, const yvex_b200_moe_weights &w, const MoeWorkspace &ws,
+                         uint64_t rows, float *out, int *status, cudaStream_t s) {
+    const uint64_t imax = g.inter > g.shared_inter ? g.inter : g.shared_inter;
+    uint64_t jobs = rows * (g.topk + 1) * imax;
+    expert_up_rows_kernel<<<grid_for(jobs, 8, 16), 256, 0, s>>>(
+        g, w, ws.xr, ws.selected, ws.weights, rows, ws.mid, status);
+    mark_phase(2, s);
+    jobs = rows * g.hidden;
+    expert_down_rows_kernel<<<grid_for(jobs, 8, 16), 256, 0, s>>>(
+        g, w, ws.selected, ws.mid, rows, out, status);
+    mark_phase(3, s);
+    return launch_status(2);
+}

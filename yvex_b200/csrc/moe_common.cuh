@@ -1,0 +1,67 @@
+// Types and helpers shared by the MoE kernels (router, narrow/decode path, wide/prefill path).
+#pragma once
+#include "qtype_decode.cuh"
+
+namespace yb {
+
+using MoeGeom = yvex_b200_moe_geometry;
+using MoeWeights = yvex_b200_moe_weights;
+
+// SwiGLU with the reference's clamps and its single bf16 rounding point after the route weight
+// (src/graph/moe.c:605-613).
+__device__ __forceinline__ float swiglu_mid(float g, float u, float route_weight, float limit, int *status) {
+    g = fminf(g, limit);
+    u = fmaxf(-limit, fminf(u, limit));
+    float silu = g >= 0.0f ? g / (1.0f + expf(-g)) : g * expf(g) / (1.0f + expf(g));
+    float mid = silu * u * route_weight;
+    if (!isfinite(mid)) raise(status, YVEX_B200_STATUS_NUMERIC);
+    return bf16_round(mid);
+}
+
+// Device scratch of the MoE entry points, carved from the caller's workspace in 256-byte
+// aligned ranges like the reference's bump allocator (src/backend/cuda/moe.c:78-88).
+struct MoeWorkspace {
+    float *xr;          // [rows x hidden]  bf16-exact ingress rows
+    float *logits;      // [rows x experts]
+    int32_t *selected;  // [rows x topk]
+    float *weights;     // [rows x topk]
+    float *mid;         // [rows x (topk+1) x max(inter, shared_inter)]  SwiGLU intermediates
+    void rebase(void *base) {
+        auto b = reinterpret_cast<uintptr_t>(base);
+        xr = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(xr));
+        logits = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(logits));
+        selected = reinterpret_cast<int32_t *>(b + reinterpret_cast<uintptr_t>(selected));
+        weights = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(weights));
+        mid = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(mid));
+    }
+};
+
+// Fills `ws` with OFFSETS (rebase() turns them into pointers) and returns the total bytes.
+inline uint64_t moe_workspace_layout(const MoeGeom &g, uint64_t rows, MoeWorkspace *ws) {
+    uint64_t off = 0;
+    auto take = [&](uint64_t bytes) { uint64_t at = off; off = (off + bytes + 255) & ~255ull; return at; };
+    const uint64_t imax = g.inter > g.shared_inter ? g.inter : g.shared_inter;
+    MoeWorkspace l;
+    l.xr = reinterpret_cast<float *>(take(rows * g.hidden * 4));
+    l.logits = reinterpret_cast<float *>(take(rows * g.experts * 4));
+    l.selected = reinterpret_cast<int32_t *>(take(rows * g.topk * 4));
+    l.weights = reinterpret_cast<float *>(take(rows * g.topk * 4));
+    l.mid = reinterpret_cast<float *>(take(rows * (g.topk + 1) * imax * 4));
+    if (ws) *ws = l;
+    return off;
+}
+
+// Expert execution for a narrow batch; picks the streaming tensor-core matvec kernels when the
+// layer's qtypes have decoders for them and the reference-shaped kernels otherwise.
+int moe_experts_narrow(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, uint64_t rows,
+                       float *out, int *status, cudaStream_t s);
+int moe_experts_rows(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, uint64_t rows,
+                     float *out, int *status, cudaStream_t s);
+// Ingress bf16 rounding of x into ws.xr, then router (projection or supplied logits) + top-k.
+int moe_ingress_and_route(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, const float *x,
+                          const float *logits, const uint32_t *token_ids, uint64_t rows, int *status,
+                          cudaStream_t s);
+// Entry-point validation shared by the narrow and wide paths (fail-closed qtype check included).
+int moe_check_geometry(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w);
+
+}  // namespace yb

@@ -1,0 +1,204 @@
+"""ctypes loader and torch-tensor front-end for libyvex_b200.so (device layer C-ABI,
+include/yvex_b200_kernels.h). PyTorch is used only for device memory and streams."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libyvex_b200.so")
+
+u64, u32, vp = C.c_uint64, C.c_uint32, C.c_void_p
+
+STATUS_NAMES = {0: "ok", -1: "error", -2: "nomem", -4: "format", -5: "unsupported", -6: "backend",
+                -7: "bounds", -8: "state", -9: "cancelled", -10: "invalid-arg", -11: "timeout"}
+
+
+class YvexError(RuntimeError):
+    def __init__(self, code, where):
+        super().__init__(f"{where}: {STATUS_NAMES.get(code, code)} ({code})")
+        self.code = code
+
+
+class MoeGeometry(C.Structure):
+    _fields_ = [("hidden", u64), ("experts", u64), ("topk", u64), ("inter", u64), ("shared_inter", u64),
+                ("scaling", C.c_double), ("limit", C.c_double), ("normalize", C.c_int),
+                ("router_class", C.c_int), ("gate_qtype", C.c_uint), ("up_qtype", C.c_uint),
+                ("down_qtype", C.c_uint), ("hash_rows", u64), ("hash_stored_rows", u64)]
+
+
+class MoeWeights(C.Structure):
+    _fields_ = [("router", vp), ("bias", vp), ("hash_table", vp), ("gate", vp), ("up", vp), ("down", vp),
+                ("shared_gate", vp), ("shared_up", vp), ("shared_down", vp)]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: run `python -m yvex_b200.build` (there is no fallback path)")
+    lib = C.CDLL(LIB_PATH)
+    lib.yvex_b200_version.restype = C.c_char_p
+    lib.yvex_b200_moe_workspace_bytes.restype = u64
+    lib.yvex_b200_moe_workspace_bytes.argtypes = [C.POINTER(MoeGeometry), u64]
+    lib.yvex_b200_attention_workspace_bytes.restype = u64
+    lib.yvex_b200_attention_workspace_bytes.argtypes = [u64] * 5
+    lib.yvex_b200_dequant_rows.argtypes = [C.c_uint, vp, u64, u64, u64, vp, vp, vp]
+    lib.yvex_b200_gemv.argtypes = [C.c_uint, vp, u64, u64, u64, vp, u64, vp, vp, C.c_int, vp, vp]
+    moe_args = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights), vp, vp, vp, u64, vp, vp, vp, vp, u64, vp, vp]
+    lib.yvex_b200_moe_route.argtypes = moe_args
+    lib.yvex_b200_moe_decode.argtypes = moe_args
+    lib.yvex_b200_moe_wide.argtypes = moe_args
+    lib.yvex_b200_attention_gqa_decode.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, C.c_float,
+                                                   vp, vp, u64, vp, vp]
+    lib.yvex_b200_attention_f32.argtypes = [vp, vp, vp, u64, u64, u64, C.c_float, C.c_int, vp, vp, vp, vp, vp]
+    return lib
+
+
+lib = _load()
+
+EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_geometry",
+           "yvex_b200_dequant_rows", "yvex_b200_gemv", "yvex_b200_moe_workspace_bytes",
+           "yvex_b200_moe_route", "yvex_b200_moe_decode", "yvex_b200_moe_wide",
+           "yvex_b200_attention_workspace_bytes", "yvex_b200_attention_gqa_decode",
+           "yvex_b200_attention_f32"]
+
+
+def _torch():
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("yvex_b200 compute entry points need a CUDA device; there is no CPU fallback")
+    return torch
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc, where):
+    if rc != 0:
+        raise YvexError(rc, where)
+
+
+class Status:
+    """Device status word (0 ok / 1 numerics / 2 arguments / 3 timeout) with a host read-out."""
+
+    def __init__(self, device="cuda"):
+        torch = _torch()
+        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def read(self):
+        return int(self.word.item())
+
+    def reset(self):
+        self.word.zero_()
+
+
+def geometry_of(spec, router_class=1, hash_rows=0, hash_stored_rows=0):
+    g = MoeGeometry()
+    g.hidden, g.experts, g.topk, g.inter, g.shared_inter = (spec.hidden, spec.experts, spec.topk, spec.inter,
+                                                           spec.shared_inter)
+    g.scaling, g.limit, g.normalize, g.router_class = spec.scaling, spec.limit, spec.normalize, router_class
+    g.gate_qtype, g.up_qtype, g.down_qtype = spec.gate_qtype, spec.up_qtype, spec.down_qtype
+    g.hash_rows, g.hash_stored_rows = hash_rows, hash_stored_rows
+    return g
+
+
+def weights_of(tensors):
+    """tensors: dict name -> device torch tensor (router/bias/hash_table optional)."""
+    w = MoeWeights()
+    for name, _ in MoeWeights._fields_:
+        setattr(w, name, _p(tensors.get(name)))
+    w._keep = tensors
+    return w
+
+
+def dequant_rows(qtype, enc, rows, width, status):
+    torch = _torch()
+    out = torch.empty((rows, width), dtype=torch.float32, device=enc.device)
+    row_bytes = enc.numel() // rows
+    _check(lib.yvex_b200_dequant_rows(qtype, _p(enc), rows, width, row_bytes, _p(out), _p(status.word), _stream()),
+           "dequant_rows")
+    return out
+
+
+def gemv(qtype, enc, rows, width, x, status, additive=None, round_bf16=False, out=None, row_bytes=None):
+    torch = _torch()
+    x2 = x.reshape(-1, width)
+    if out is None:
+        out = torch.empty((x2.shape[0], rows), dtype=torch.float32, device=x.device)
+    rb = row_bytes if row_bytes is not None else enc.numel() // rows
+    _check(lib.yvex_b200_gemv(qtype, _p(enc), rows, width, rb, _p(x2), x2.shape[0], _p(additive), _p(out),
+                              int(round_bf16), _p(status.word), _stream()), "gemv")
+    return out
+
+
+def moe_workspace_bytes(geom, rows):
+    return int(lib.yvex_b200_moe_workspace_bytes(C.byref(geom), rows))
+
+
+def _moe_call(fn, name, geom, weights, x, logits, token_ids, rows, out, selected, wts, workspace, status):
+    _check(fn(C.byref(geom), C.byref(weights), _p(x), _p(logits), _p(token_ids), rows, _p(out), _p(selected),
+              _p(wts), _p(workspace), workspace.numel() if workspace is not None else 0, _p(status.word),
+              _stream()), name)
+
+
+def moe_layer(geom, weights, x, status, logits=None, token_ids=None, wide=False, workspace=None,
+              out=None, selected=None, wts=None):
+    """One MoE FFN layer on device rows x [rows, hidden] f32 -> out [rows, hidden] f32."""
+    torch = _torch()
+    rows = x.shape[0]
+    if workspace is None:
+        workspace = torch.empty(moe_workspace_bytes(geom, rows), dtype=torch.uint8, device=x.device)
+    if out is None:
+        out = torch.empty_like(x)
+    if selected is None:
+        selected = torch.empty((rows, geom.topk), dtype=torch.int32, device=x.device)
+    if wts is None:
+        wts = torch.empty((rows, geom.topk), dtype=torch.float32, device=x.device)
+    fn = lib.yvex_b200_moe_wide if wide else lib.yvex_b200_moe_decode
+    _moe_call(fn, "moe_wide" if wide else "moe_decode", geom, weights, x, logits, token_ids, rows, out,
+              selected, wts, workspace, status)
+    return out, selected, wts
+
+
+def moe_route(geom, weights, status, rows_f32=None, logits=None, token_ids=None):
+    torch = _torch()
+    ref = rows_f32 if rows_f32 is not None else logits
+    rows = ref.shape[0]
+    selected = torch.empty((rows, geom.topk), dtype=torch.int32, device=ref.device)
+    wts = torch.empty((rows, geom.topk), dtype=torch.float32, device=ref.device)
+    lg = torch.empty((rows, geom.experts), dtype=torch.float32, device=ref.device)
+    _check(lib.yvex_b200_moe_route(C.byref(geom), C.byref(weights), _p(rows_f32), _p(logits), _p(token_ids), rows,
+                                   _p(selected), _p(wts), _p(lg), None, 0, _p(status.word), _stream()), "moe_route")
+    return selected, wts, lg
+
+
+def attention_gqa_decode(q, k, v, position, scale, status, workspace=None, out=None):
+    """q [S,Hq,D] bf16, k/v [S,Hkv,ctx,D] bf16 -> out [S,Hq,D] f32."""
+    torch = _torch()
+    S, Hq, D = q.shape
+    _, Hkv, ctx, _ = k.shape
+    if workspace is None:
+        workspace = torch.empty(int(lib.yvex_b200_attention_workspace_bytes(S, Hq, Hkv, D, ctx)),
+                                dtype=torch.uint8, device=q.device)
+    if out is None:
+        out = torch.empty((S, Hq, D), dtype=torch.float32, device=q.device)
+    _check(lib.yvex_b200_attention_gqa_decode(_p(q), _p(k), _p(v), S, Hq, Hkv, D, ctx, position, scale, _p(out),
+                                              _p(workspace), workspace.numel(), _p(status.word), _stream()),
+           "attention_gqa_decode")
+    return out
+
+
+def attention_f32(q, keys, values, position, scale, causal, status):
+    torch = _torch()
+    seq, D = keys.shape
+    scores = torch.zeros(seq, dtype=torch.float32, device=q.device)
+    probs = torch.zeros(seq, dtype=torch.float32, device=q.device)
+    out = torch.zeros(D, dtype=torch.float32, device=q.device)
+    _check(lib.yvex_b200_attention_f32(_p(q), _p(keys), _p(values), seq, D, position, scale, int(causal),
+                                       _p(scores), _p(probs), _p(out), _p(status.word), _stream()), "attention_f32")
+    return out, scores, probs
