@@ -192,6 +192,7 @@ def test_router_selection_identical_to_oracle(L, port, experts, topk, rows):
     logits = rng.standard_normal((rows, experts)).astype(np.float32)
     logits[0, :] = 0.25                        # full tie: lowest indices must win
     bias = (rng.standard_normal(experts) * 0.1).astype(np.float32)
+    bias[:topk + 1] = 0.5                      # ... among the experts the bias leaves tied
     st = L.Status()
     sel, w, _ = L.moe_route(L.geometry_of(spec), L.weights_of({"bias": dev(bias)}), st, logits=dev(logits))
     sel, w = sel.cpu().numpy(), w.cpu().numpy()

@@ -35,6 +35,9 @@ gqa_decode_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k
     constexpr int NW = kAttnThreads / 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int sub = lane / LPK, ll = lane % LPK;     // key slot inside the warp, chunk inside the row
+    // Key slots of one warp may run different trip counts at the ragged end of a split, so the
+    // score reduction synchronises only the lanes of its own slot.
+    const unsigned slot_mask = static_cast<unsigned>(((1ull << LPK) - 1ull) << (sub * LPK));
     const int split = blockIdx.x % splits;
     const uint64_t sk = blockIdx.x / splits;           // session * kv_heads + kv head
     const uint64_t session = sk / kv_heads, kvh = sk % kv_heads;
@@ -79,7 +82,7 @@ gqa_decode_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k
 #pragma unroll
                 for (int i = 0; i < 8; ++i) d = fmaf(qf[h][i], kf[i], d);
 #pragma unroll
-                for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(slot_mask, d, o);
                 s[j][h] = base + j < end ? d : -INFINITY;
             }
         }

@@ -11,12 +11,14 @@
 namespace yb {
 
 // ---- ingress: x -> bf16-exact f32 rows ----------------------------------------------------------
-__global__ void ingress_round_kernel(const float *x, float *xr, uint64_t n, int *status) {
+__global__ void ingress_round_kernel(const float *x, float *xr, __half *xr_h, uint64_t n, int *status) {
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n;
          i += (uint64_t)gridDim.x * blockDim.x) {
         float v = x[i];
         if (!isfinite(v)) raise(status, YVEX_B200_STATUS_NUMERIC);
-        xr[i] = bf16_round(v);
+        v = bf16_round(v);
+        xr[i] = v;
+        xr_h[i] = __float2half_rn(v);      // exact for |v| in [2^-14, 65504]; below that < 2^-25 absolute
     }
 }
 
@@ -124,7 +126,8 @@ __global__ void route_rows_kernel(MoeGeom g, const float *logits, const float *b
 // ---- reference-shaped expert kernels (any supported qtype): one warp per output element ---------
 // pair p of row r: p < topk -> routed expert selected[r][p] with weights[r][p]; p == topk -> shared.
 __global__ void expert_up_rows_kernel(MoeGeom g, MoeWeights w, const float *xr, const int32_t *selected,
-                                      const float *weights, uint64_t rows, float *mid, int *status) {
+                                      const float *weights, uint64_t rows, float *mid, __half *mid_h,
+                                      int *status) {
     const int lane = threadIdx.x & 31;
     const uint64_t ppr = g.topk + 1, imax = max(g.inter, g.shared_inter);
     const uint64_t warps = (uint64_t)gridDim.x * (blockDim.x >> 5);
@@ -156,7 +159,11 @@ __global__ void expert_up_rows_kernel(MoeGeom g, MoeWeights w, const float *xr, 
         }
         ga = warp_sum(ga);
         ua = warp_sum(ua);
-        if (lane == 0) mid[pair * imax + i] = swiglu_mid(ga, ua, rw, (float)g.limit, status);
+        if (lane == 0) {
+            const float v = swiglu_mid(ga, ua, rw, (float)g.limit, status);
+            mid[pair * imax + i] = v;
+            mid_h[pair * imax + i] = __float2half_rn(v);
+        }
     }
 }
 
@@ -238,7 +245,7 @@ int yb::moe_ingress_and_route(const MoeGeom &g, const MoeWeights &w, const MoeWo
                               const float *logits, const uint32_t *token_ids, uint64_t rows, int *status,
                               cudaStream_t s) {
     const uint64_t n = rows * g.hidden;
-    ingress_round_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>(x, ws.xr, n, status);
+    ingress_round_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>(x, ws.xr, ws.xr_h, n, status);
     int rc = launch_status(1);
     if (rc != OK) return rc;
     return route_into(g, &w, ws.xr, logits, token_ids, rows, ws.logits, ws.selected, ws.weights, status, s);
@@ -291,16 +298,29 @@ extern "C" int yvex_b200_moe_decode(const yvex_b200_moe_geometry *geom, const yv
 }
 
 // Reference-shaped expert execution: used when no streaming decoder covers the layer's qtypes.
-int yb::moe_experts_rows(const MoeGeom &g, const yvex_b200_moe_weights &w, const MoeWorkspace &ws,
-                         uint64_t rows, float *out, int *status, cudaStream_t s) {
+int yb::moe_up_rows(const MoeGeom &g, const yvex_b200_moe_weights &w, const MoeWorkspace &ws,
+                    uint64_t rows, int *status, cudaStream_t s) {
     const uint64_t imax = g.inter > g.shared_inter ? g.inter : g.shared_inter;
-    uint64_t jobs = rows * (g.topk + 1) * imax;
+    const uint64_t jobs = rows * (g.topk + 1) * imax;
     expert_up_rows_kernel<<<grid_for(jobs, 8, 16), 256, 0, s>>>(
-        g, w, ws.xr, ws.selected, ws.weights, rows, ws.mid, status);
-    mark_phase(2, s);
-    jobs = rows * g.hidden;
+        g, w, ws.xr, ws.selected, ws.weights, rows, ws.mid, ws.mid_h, status);
+    return launch_status(1);
+}
+
+int yb::moe_down_rows(const MoeGeom &g, const yvex_b200_moe_weights &w, const MoeWorkspace &ws,
+                      uint64_t rows, float *out, int *status, cudaStream_t s) {
+    const uint64_t jobs = rows * g.hidden;
     expert_down_rows_kernel<<<grid_for(jobs, 8, 16), 256, 0, s>>>(
         g, w, ws.selected, ws.mid, rows, out, status);
+    return launch_status(1);
+}
+
+int yb::moe_experts_rows(const MoeGeom &g, const yvex_b200_moe_weights &w, const MoeWorkspace &ws,
+                         uint64_t rows, float *out, int *status, cudaStream_t s) {
+    int rc = moe_up_rows(g, w, ws, rows, status, s);
+    if (rc != OK) return rc;
+    mark_phase(2, s);
+    rc = moe_down_rows(g, w, ws, rows, out, status, s);
     mark_phase(3, s);
-    return launch_status(2);
+    return rc;
 }

@@ -26,8 +26,12 @@ struct MoeWorkspace {
     int32_t *selected;  // [rows x topk]
     float *weights;     // [rows x topk]
     float *mid;         // [rows x (topk+1) x max(inter, shared_inter)]  SwiGLU intermediates
+    __half *xr_h;       // fp16 image of xr (bf16-exact values; B operand of the tensor-core matvecs)
+    __half *mid_h;      // fp16 image of mid
     void rebase(void *base) {
         auto b = reinterpret_cast<uintptr_t>(base);
+        xr_h = reinterpret_cast<__half *>(b + reinterpret_cast<uintptr_t>(xr_h));
+        mid_h = reinterpret_cast<__half *>(b + reinterpret_cast<uintptr_t>(mid_h));
         xr = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(xr));
         logits = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(logits));
         selected = reinterpret_cast<int32_t *>(b + reinterpret_cast<uintptr_t>(selected));
@@ -47,6 +51,8 @@ inline uint64_t moe_workspace_layout(const MoeGeom &g, uint64_t rows, MoeWorkspa
     l.selected = reinterpret_cast<int32_t *>(take(rows * g.topk * 4));
     l.weights = reinterpret_cast<float *>(take(rows * g.topk * 4));
     l.mid = reinterpret_cast<float *>(take(rows * (g.topk + 1) * imax * 4));
+    l.xr_h = reinterpret_cast<__half *>(take(rows * g.hidden * 2));
+    l.mid_h = reinterpret_cast<__half *>(take(rows * (g.topk + 1) * imax * 2));
     if (ws) *ws = l;
     return off;
 }
@@ -57,6 +63,10 @@ int moe_experts_narrow(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace
                        float *out, int *status, cudaStream_t s);
 int moe_experts_rows(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, uint64_t rows,
                      float *out, int *status, cudaStream_t s);
+int moe_up_rows(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, uint64_t rows, int *status,
+                cudaStream_t s);
+int moe_down_rows(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, uint64_t rows, float *out,
+                  int *status, cudaStream_t s);
 // Ingress bf16 rounding of x into ws.xr, then router (projection or supplied logits) + top-k.
 int moe_ingress_and_route(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, const float *x,
                           const float *logits, const uint32_t *token_ids, uint64_t rows, int *status,
