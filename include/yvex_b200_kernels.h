@@ -127,6 +127,7 @@ int yvex_b200_moe_decode(const yvex_b200_moe_geometry *g, const yvex_b200_moe_we
  * yvex_b200_moe_decode. `expert_begin/expert_count` restrict routed work to a contiguous
  * expert range (an expert-parallel shard); pairs outside it are left to other ranks.
  */
+uint64_t yvex_b200_moe_wide_workspace_bytes(const yvex_b200_moe_geometry *g, uint64_t rows);
 int yvex_b200_moe_wide(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w,
                        const float *x, const float *logits, const uint32_t *token_ids,
                        uint64_t rows, float *out, int32_t *selected_out, float *weights_out,

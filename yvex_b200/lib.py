@@ -39,6 +39,9 @@ def _load():
     lib.yvex_b200_version.restype = C.c_char_p
     lib.yvex_b200_moe_workspace_bytes.restype = u64
     lib.yvex_b200_moe_workspace_bytes.argtypes = [C.POINTER(MoeGeometry), u64]
+    lib.yvex_b200_moe_wide_workspace_bytes.restype = u64
+    lib.yvex_b200_moe_wide_workspace_bytes.argtypes = [C.POINTER(MoeGeometry), u64]
+    lib.yvex_b200_launch_count.restype = C.c_ulonglong
     lib.yvex_b200_attention_workspace_bytes.restype = u64
     lib.yvex_b200_attention_workspace_bytes.argtypes = [u64] * 5
     lib.yvex_b200_dequant_rows.argtypes = [C.c_uint, vp, u64, u64, u64, vp, vp, vp]
@@ -58,6 +61,7 @@ lib = _load()
 EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_geometry",
            "yvex_b200_dequant_rows", "yvex_b200_gemv", "yvex_b200_moe_workspace_bytes",
            "yvex_b200_moe_route", "yvex_b200_moe_decode", "yvex_b200_moe_wide",
+           "yvex_b200_moe_wide_workspace_bytes", "yvex_b200_launch_count", "yvex_b200_phase_events",
            "yvex_b200_attention_workspace_bytes", "yvex_b200_attention_gqa_decode",
            "yvex_b200_attention_f32"]
 
@@ -136,8 +140,9 @@ def gemv(qtype, enc, rows, width, x, status, additive=None, round_bf16=False, ou
     return out
 
 
-def moe_workspace_bytes(geom, rows):
-    return int(lib.yvex_b200_moe_workspace_bytes(C.byref(geom), rows))
+def moe_workspace_bytes(geom, rows, wide=False):
+    fn = lib.yvex_b200_moe_wide_workspace_bytes if wide else lib.yvex_b200_moe_workspace_bytes
+    return int(fn(C.byref(geom), rows))
 
 
 def _moe_call(fn, name, geom, weights, x, logits, token_ids, rows, out, selected, wts, workspace, status):
@@ -152,7 +157,7 @@ def moe_layer(geom, weights, x, status, logits=None, token_ids=None, wide=False,
     torch = _torch()
     rows = x.shape[0]
     if workspace is None:
-        workspace = torch.empty(moe_workspace_bytes(geom, rows), dtype=torch.uint8, device=x.device)
+        workspace = torch.empty(moe_workspace_bytes(geom, rows, wide), dtype=torch.uint8, device=x.device)
     if out is None:
         out = torch.empty_like(x)
     if selected is None:
