@@ -164,7 +164,7 @@ def run_native(args):
     wide = tokens > 64
     pool = 16 if not wide else 1
     xs = [wl.tokens(tokens) for _ in range(pool)]
-    ws = torch.empty(lib.moe_workspace_bytes(geom, tokens), dtype=torch.uint8, device=dev)
+    ws = torch.empty(lib.moe_workspace_bytes(geom, tokens, wide), dtype=torch.uint8, device=dev)
     out = torch.empty((tokens, wl.cfg["hidden"]), dtype=torch.float32, device=dev)
     sel = torch.empty((tokens, wl.spec.topk), dtype=torch.int32, device=dev)
     wts = torch.empty((tokens, wl.spec.topk), dtype=torch.float32, device=dev)
@@ -219,7 +219,7 @@ def run_native(args):
         ms_e2e = timed(step_e2e, args.steps)
         barrier()
         # per-phase timing for the roofline of the dominant kernel
-        n_ph = 5
+        n_ph = 6
         evs = [[torch.cuda.Event(enable_timing=True) for _ in range(n_ph)] for _ in range(args.steps)]
         for row in evs:
             for e in row:
@@ -235,7 +235,7 @@ def run_native(args):
             step(i)
             lib.lib.yvex_b200_phase_events(None, 0)
         torch.cuda.synchronize()
-        used = 4 if not wide else 5
+        used = 4 if not wide else 6
         for i in range(args.steps):
             for p in range(used - 1):
                 phase_ms[p].append(evs[i][p].elapsed_time(evs[i][p + 1]))
@@ -249,8 +249,20 @@ def run_native(args):
     value = world * tokens * args.steps / (t_dev / 1e3)
     e2e = world * tokens * args.steps / (t_e2e / 1e3)
     phases = [sum(p) / len(p) for p in phase_ms[:used - 1]]
-    names = ["route", "gate_up", "down_combine"] if not wide else ["route_permute", "gate_up", "down", "combine"]
+    names = (["route", "gate_up", "down_combine"] if not wide
+             else ["route", "permute_gather", "gate_up_gemm", "swiglu_down_gemm", "combine"])
     roofline = None
+    if wide:
+        # dense contraction: count only real (token, expert) pairs, the shared expert included
+        pairs = tokens * (wl.spec.topk + 1)
+        flops = {"gate_up_gemm": pairs * 4.0 * wl.cfg["hidden"] * wl.cfg["inter"],
+                 "swiglu_down_gemm": pairs * 2.0 * wl.cfg["hidden"] * wl.cfg["inter"]}
+        top = max(flops, key=lambda k: phases[names.index(k)])
+        ach = flops[top] / (phases[names.index(top)] * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": ach / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"],
+                    "peak_sustained": peaks["bf16_tflops_sustained"],
+                    "layer_achieved": pairs * 6.0 * wl.cfg["hidden"] * wl.cfg["inter"] / (t_dev / args.steps * 1e-3) / 1e12}
     if not wide:
         pb = wl.phase_bytes_decode()
         cand = {"gate_up": (pb["gate_up"], phases[1]), "down": (pb["down"], phases[2])}
@@ -264,7 +276,7 @@ def run_native(args):
         if world == 1:
             cores = os.cpu_count() or 1
             try:
-                tps, kind, _ = cpu_layer_tokens_per_s(wl, cores if not wide else max(cores, 8), 1, cores)
+                tps, kind, _ = cpu_layer_tokens_per_s(wl, cores, 1, cores)
                 cpu = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
                        "sample": f"{cores} tokens of the same layer, one thread per token (plain-C port; the "
                                  "reference has no Q4_K decoder)"}
@@ -287,17 +299,174 @@ def run_native(args):
         dist.destroy_process_group()
 
 
+def run_native_ep(args):
+    """Config 5: the expert-parallel layer. Total work is fixed (16384 tokens, 256 experts) and
+    split over the ranks (strong scaling): tokens by home rank, experts in contiguous shards."""
+    import ctypes as C
+
+    import torch
+    import torch.distributed as dist
+    from yvex_b200 import lib
+    from yvex_b200.ep import DeviceOps, ExpertParallelLayer
+    from yvex_b200.workloads import MoEWorkload
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = measured_peaks()
+    wl = MoEWorkload(args.workload, 1, device=dev)            # same seed on every rank: identical packs
+    spec, cfg = wl.spec, wl.cfg
+    T, E, H, I = cfg["tokens"], cfg["experts"], cfg["hidden"], cfg["inter"]
+    e_loc, t_loc = E // world, T // world
+    x_all, lg_all = wl.tokens(T)
+    x = x_all[rank * t_loc:(rank + 1) * t_loc].contiguous()
+    lg = lg_all[rank * t_loc:(rank + 1) * t_loc].contiguous()
+    del x_all, lg_all
+    shard = {}
+    for name, rows in (("gate", I), ("up", I), ("down", H)):
+        per = wl.tensors[name].numel() // E
+        shard[name] = wl.tensors[name][rank * e_loc * per:(rank + 1) * e_loc * per]
+    for name in ("shared_gate", "shared_up", "shared_down"):
+        shard[name] = wl.tensors[name]
+    geom_full = lib.geometry_of(spec)
+    spec_local = type(spec)(H, e_loc, spec.topk, I, down_qtype=spec.down_qtype)
+    geom_local = lib.geometry_of(spec_local)
+    status = lib.Status(dev)
+    ops = DeviceOps(geom_full, geom_local, lib.weights_of(shard), status)
+    layer = ExpertParallelLayer(E, spec.topk, ops)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    host_x, host_lg = x.cpu().pin_memory(), lg.cpu().pin_memory()
+    host_out = torch.empty((t_loc, H), dtype=torch.float32).pin_memory()
+    dev_x, dev_lg = torch.empty_like(x), torch.empty_like(lg)
+
+    def step(i):
+        return layer.forward(x, lg)[0]
+
+    def step_e2e(i):
+        dev_x.copy_(host_x, non_blocking=True)
+        dev_lg.copy_(host_lg, non_blocking=True)
+        host_out.copy_(layer.forward(dev_x, dev_lg)[0], non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        out = []
+        for i in range(steps):
+            flush.fill_(i & 0xFF)
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn(i)
+            b.record()
+            torch.cuda.synchronize()
+            out.append(a.elapsed_time(b))
+        return out
+
+    for i in range(args.warmup):
+        step(i)
+        step_e2e(i)
+    barrier()
+    launches0 = lib.lib.yvex_b200_launch_count()
+    with ClockSampler(local) as clocks:
+        ms = timed(step, args.steps)
+        launches = lib.lib.yvex_b200_launch_count() - launches0
+        ms_e2e = timed(step_e2e, args.steps)
+        # GEMM phases of the routed pair list, timed with the library's phase events
+        n_ph, gemm_ms, pair_counts = 6, [[], []], []
+        real_rows = ops.expert_rows
+
+        def probed(rows_h, ids, wts):
+            if rows_h.shape[0] and not probed.done:
+                probed.done = True
+                evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_ph)]
+                for e in evs:
+                    e.record()
+                arr = (C.c_void_p * n_ph)(*[e.cuda_event for e in evs])
+                lib.lib.yvex_b200_phase_events(arr, n_ph)
+                y = real_rows(rows_h, ids, wts)
+                lib.lib.yvex_b200_phase_events(None, 0)
+                torch.cuda.synchronize()
+                gemm_ms[0].append(evs[2].elapsed_time(evs[3]))
+                gemm_ms[1].append(evs[3].elapsed_time(evs[4]))
+                pair_counts.append(rows_h.shape[0])
+                return y
+            return real_rows(rows_h, ids, wts)
+
+        ops.expert_rows = probed
+        for i in range(min(args.steps, 5)):
+            probed.done = False
+            flush.fill_(i & 0xFF)
+            step(i)
+        ops.expert_rows = real_rows
+        torch.cuda.synchronize()
+    if status.read() != 0:
+        raise RuntimeError(f"device status word = {status.read()} after the timed region")
+    # per-step max over ranks, then summed: every step is bracketed by a barrier
+    tm = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+    t_dev, t_e2e = tm.sum(dim=1).tolist()
+    value = T * args.steps / (t_dev / 1e3)
+    e2e = T * args.steps / (t_e2e / 1e3)
+    if rank == 0:
+        gu = sum(gemm_ms[0]) / len(gemm_ms[0])
+        dn = sum(gemm_ms[1]) / len(gemm_ms[1])
+        pairs = sum(pair_counts) / len(pair_counts)
+        top, t_top, fl = ("gate_up_gemm", gu, pairs * 4.0 * H * I) if gu >= dn else ("swiglu_down_gemm", dn, pairs * 2.0 * H * I)
+        ach = fl / (t_top * 1e-3) / 1e12
+        peak = peaks["bf16_tflops_sustained"]
+        roofline = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                    "traffic": None, "peak_source": peaks["source"] + " (sustained; burst %.1f)" % peaks["bf16_tflops"],
+                    "pairs_per_launch": pairs,
+                    "layer_achieved": T * (spec.topk + 1) * 6.0 * H * I / world / (t_dev / args.steps * 1e-3) / 1e12}
+        cpu = None
+        if world == 1:
+            cores = os.cpu_count() or 1
+            try:
+                tps, kind, _ = cpu_layer_tokens_per_s(wl, cores, 1, cores)
+                cpu = {"value": tps, "unit": UNIT, "cores": cores, "kind": "port",
+                       "sample": f"{cores} tokens of the same layer, one thread per token (plain-C port; the "
+                                 "reference has no Q4_K decoder)"}
+            except Exception as exc:
+                cpu = {"value": None, "unit": UNIT, "cores": cores, "kind": "port", "sample": f"failed: {exc}"}
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": t_dev / args.steps, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f16-mma/f32-accum, bf16 rounding points",
+                "data": "synthetic",
+                "config": {"workload": wl.name, **cfg, "gate_up_qtype": "IQ2_XXS", "down_qtype": "Q4_K",
+                           "l2": "flushed between steps (256 MiB rewrite)",
+                           "parallelism": f"ep{world}: {e_loc} experts and {t_loc} tokens per rank, NCCL all-to-all-v"},
+                "clocks": clocks.summary(),
+                "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(T * (H + E) * 4),
+                        "d2h_bytes_per_step": int(T * H * 4)},
+                "gpu_launches": int(launches * world),
+                "phases_ms": {"gate_up_gemm": gu, "swiglu_down_gemm": dn},
+                "roofline": roofline, "cpu_baseline": cpu}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=40)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c5"])
+    ap.add_argument("--workload", default="c5", choices=["c2", "c3", "c5"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "c5":
+        run_native_ep(args)
     else:
         run_native(args)
 

@@ -45,7 +45,8 @@ unsigned long long yvex_b200_launch_count(void);
  * nanosecond counters (include/yvex/internal/moe.h:209-210). While `events` (an array of
  * `count` cudaEvent_t handles owned by the caller) is registered, the MoE entry points record
  * events[0] when they start and events[i] after phase i (1 route, 2 gate/up, 3 down+combine for
- * the narrow path; 1 route+permute, 2 gate/up GEMM, 3 down GEMM, 4 combine for the wide path).
+ * the narrow path; 1 route, 2 permute+gather, 3 gate/up GEMM, 4 SwiGLU + down GEMM, 5 combine
+ * for the wide path).
  * Pass count 0 to unregister. Process-wide; not meant for concurrent callers.
  */
 int yvex_b200_phase_events(void **events, int count);
@@ -132,6 +133,28 @@ int yvex_b200_moe_wide(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weig
                        const float *x, const float *logits, const uint32_t *token_ids,
                        uint64_t rows, float *out, int32_t *selected_out, float *weights_out,
                        void *workspace, uint64_t workspace_bytes, int *status, void *stream);
+
+/*
+ * Expert-parallel building blocks (no reference counterpart: the reference is single-device,
+ * src/runtime/moe.c; per-pair semantics are yvex_moe_expert_cpu, src/graph/moe.c:587-622).
+ *
+ * yvex_b200_moe_expert_rows runs a caller-made pair list on this device's expert shard: pair p is
+ * (input row p of rows_f16 [pairs x hidden] - the fp16 image of a bf16-exact row -, expert
+ * expert_ids[p] in [0, g->experts) relative to the shard the weight pointers name, or negative
+ * for the shared expert, route weight route_weights[p]) and yields y_bf16[p] = bf16(down(bf16(
+ * SwiGLU(gate.x, up.x) * weight))) as bf16 bit patterns [pairs x hidden]. g->experts is the
+ * number of experts in the shard.
+ *
+ * yvex_b200_moe_combine is the home rank's unpermute: out[t] = bf16(sum over rank r of
+ * y_routed[t*topk + r] in rank order (f32) + y_shared[t]) (src/runtime/moe.c:619-632).
+ */
+uint64_t yvex_b200_moe_expert_rows_workspace_bytes(const yvex_b200_moe_geometry *g, uint64_t pairs);
+int yvex_b200_moe_expert_rows(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w,
+                              const void *rows_f16, const int32_t *expert_ids, const float *route_weights,
+                              uint64_t pairs, void *y_bf16, void *workspace, uint64_t workspace_bytes,
+                              int *status, void *stream);
+int yvex_b200_moe_combine(const void *y_routed_bf16, const void *y_shared_bf16, uint64_t tokens,
+                          uint64_t topk, uint64_t hidden, float *out, int *status, void *stream);
 
 /*
  * Online-softmax causal GQA attention at decode: one query position per session against a bf16

@@ -1,0 +1,86 @@
+"""Host-side logic of the expert-parallel layer (dispatch / combine permutations, split sizes,
+expert sharding) on CPU: two gloo ranks with stand-in compute ops must reproduce the one-process
+result bit for bit, including a rank that receives no pair at all."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from yvex_b200.ep import ExpertParallelLayer
+
+E, K, H, T = 8, 3, 32, 10
+
+
+class FakeOps:
+    """Deterministic stand-ins: expert e multiplies a row by (e + 1) * weight, shared by 0.5."""
+
+    def __init__(self, rank, per_rank):
+        self.rank, self.per_rank = rank, per_rank
+
+    def ingress(self, x):
+        return x.to(torch.bfloat16).to(torch.float16)
+
+    def route(self, x, logits):
+        w, sel = torch.topk(logits, K, dim=1)
+        return sel.to(torch.int32), torch.sigmoid(w).to(torch.float32)
+
+    def expert_rows(self, rows_h, ids, wts):
+        glob = torch.where(ids < 0, torch.full_like(ids, -1), ids + self.rank * self.per_rank)
+        factor = torch.where(glob < 0, torch.full_like(wts, 0.5), (glob + 1).float() * wts)
+        return (rows_h.float() * factor[:, None]).to(torch.bfloat16)
+
+    def combine(self, y_routed, y_shared, topk):
+        acc = torch.zeros(y_shared.shape, dtype=torch.float32)
+        yr = y_routed.float().reshape(-1, topk, y_shared.shape[1])
+        for r in range(topk):
+            acc = acc + yr[:, r]
+        return (acc + y_shared.float()).to(torch.bfloat16).float()
+
+
+def inputs(skew):
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn((T, H), generator=g)
+    logits = torch.randn((T, E), generator=g)
+    if skew:
+        logits[:, E // 2:] -= 100.0          # every pair goes to rank 0's experts
+    return x, logits
+
+
+def single(skew):
+    x, logits = inputs(skew)
+    out, sel, _ = ExpertParallelLayer(E, K, FakeOps(0, E)).forward(x, logits)
+    return out, sel
+
+
+def worker(rank, world, port, skew, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    x, logits = inputs(skew)
+    lo, hi = rank * T // world, (rank + 1) * T // world
+    layer = ExpertParallelLayer(E, K, FakeOps(rank, E // world))
+    out, sel, _ = layer.forward(x[lo:hi].contiguous(), logits[lo:hi].contiguous())
+    ret[rank] = (out, sel)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("skew", [False, True])
+def test_two_rank_layer_matches_single_process_bit_for_bit(skew):
+    world = 2
+    ret = mp.Manager().dict()
+    mp.spawn(worker, args=(world, free_port(), skew, ret), nprocs=world, join=True)
+    want, want_sel = single(skew)
+    got = torch.cat([ret[r][0] for r in range(world)])
+    got_sel = torch.cat([ret[r][1] for r in range(world)])
+    assert torch.equal(got_sel, want_sel)
+    assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+

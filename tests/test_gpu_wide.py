@@ -73,6 +73,46 @@ def test_wide_layer_ragged_groups_vs_oracle(L, port, down):
     assert per_token.max() <= 4e-3, per_token.max()
 
 
+def test_expert_parallel_building_blocks_match_single_device_layer_bit_for_bit(L):
+    """The expert-parallel decomposition (route -> per-pair rows on the expert shard -> combine on
+    the home rank), run here on one rank that owns every expert, and again with the experts split
+    into two shards executed one after the other, must equal the fused wide layer exactly: pairs
+    travel as whole bf16 rows and are summed in rank order."""
+    import torch
+    from yvex_b200.ep import DeviceOps, ExpertParallelLayer
+    H, E, k, I, T = 512, 8, 2, 256, 200
+    spec = synth.MoELayerSpec(H, E, k, I, down_qtype=synth.Q4_K)
+    rng = np.random.default_rng(5)
+    x, logits = dev(rng.standard_normal((T, H)).astype(np.float32)), dev(rng.standard_normal((T, E)).astype(np.float32))
+    t = {kk: dev(v.reshape(-1)) for kk, v in synth.moe_weights(spec, 9).items()}
+    st = L.Status()
+    g, w = L.geometry_of(spec), L.weights_of(t)
+    want, sel0, _ = L.moe_layer(g, w, x, st, logits=logits, wide=True)
+    layer = ExpertParallelLayer(E, k, DeviceOps(g, g, w, st))
+    got, sel, _ = layer.forward(x, logits)
+    assert st.read() == 0 and torch.equal(sel, sel0)
+    assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+    # two shards of 4 experts, pairs routed to each by hand
+    xh = x.to(torch.bfloat16).to(torch.float16)
+    sel, wts, _ = L.moe_route(g, w, st, logits=logits)
+    y = torch.empty((T * k, H), dtype=torch.bfloat16, device="cuda")
+    half = synth.MoELayerSpec(H, E // 2, k, I, down_qtype=synth.Q4_K)
+    for shard in range(2):
+        ts = dict(t)
+        for name in ("gate", "up", "down"):
+            per = t[name].numel() // E
+            ts[name] = t[name][shard * 4 * per:(shard + 1) * 4 * per]
+        mask = (sel.reshape(-1) // 4) == shard
+        idx = mask.nonzero().reshape(-1)
+        rows = xh.index_select(0, idx // k)
+        y[idx] = L.moe_expert_rows(L.geometry_of(half), L.weights_of(ts), rows, (sel.reshape(-1)[idx] % 4).contiguous(),
+                                   wts.reshape(-1)[idx].contiguous(), st)
+    ysh = L.moe_expert_rows(g, w, xh, torch.full((T,), -1, dtype=torch.int32, device="cuda"),
+                            torch.ones(T, device="cuda"), st)
+    out2 = L.moe_combine(y, ysh, k, st)
+    assert st.read() == 0 and torch.equal(out2.view(torch.int32), want.view(torch.int32))
+
+
 def test_wide_matches_narrow_path_at_prefill_size(L, port):
     """Config-3 geometry (2048 tokens, hidden 4096, 64 experts top-6, inter 1536, IQ2_XXS + Q4_K):
     a sample of rows must agree with the narrow path run on those rows alone (rows are

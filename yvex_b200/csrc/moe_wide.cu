@@ -1,10 +1,16 @@
-// Wide-batch (prefill / expert-parallel shard) MoE layer:
-//   ingress + route  ->  expert-major stable counting sort (the reference's worklist order,
-//   src/graph/worklist.c:369-441)  ->  gather rows to expert-major fp16  ->  grouped dequant GEMM
-//   gate & up (tcgen05)  ->  SwiGLU * route weight -> bf16 (+ sub-block sums for affine down
-//   qtypes)  ->  grouped dequant GEMM down -> bf16 per pair  ->  unpermute: routed rows summed in
-//   rank order in f32, + shared, -> bf16 (src/runtime/moe.c:619-632).
-// The shared expert is one more group holding every token in token order.
+// Wide-batch (prefill / expert-parallel shard) MoE execution.
+//
+// The unit of work is a PAIR LIST: pair p = (source row src[p], expert e[p], route weight w[p]),
+// e[p] == experts meaning the shared expert. The pipeline is
+//   expert-major stable counting sort (the reference's worklist order, src/graph/worklist.c:369-441)
+//   -> gather source rows to expert-major fp16 -> grouped dequant GEMM gate & up (tcgen05)
+//   -> SwiGLU * route weight -> bf16 (+ sub-block sums for affine down qtypes)
+//   -> grouped dequant GEMM down -> one bf16 row per pair.
+// yvex_b200_moe_wide builds the list from its own router output (T*k routed pairs + T shared
+// pairs) and finishes with the rank-ordered unpermute: routed rows summed in rank order in f32,
+// + shared, -> bf16 (src/runtime/moe.c:619-632). yvex_b200_moe_expert_rows runs a caller-made
+// list (an expert-parallel rank's received rows) and returns the per-pair rows in list order;
+// yvex_b200_moe_combine is the unpermute on its own.
 #include <cudaTypedefs.h>
 
 #include <type_traits>
@@ -13,49 +19,68 @@
 
 namespace yb {
 
+// ---- pair list of the single-device layer ----------------------------------------------------------
+__global__ void wide_pairs_kernel(const int32_t *selected, const float *weights, uint64_t tokens, uint64_t topk, int experts,
+                                  int *expert_of_pair, int *src_of_pair, float *weight_of_pair) {
+    const uint64_t routed = tokens * topk, total = routed + tokens;
+    for (uint64_t p = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; p < total; p += (uint64_t)gridDim.x * blockDim.x) {
+        const bool r = p < routed;
+        expert_of_pair[p] = r ? selected[p] : experts;
+        src_of_pair[p] = (int)(r ? p / topk : p - routed);
+        weight_of_pair[p] = r ? weights[p] : 1.0f;
+    }
+}
+
+// Pair list handed in by the caller: pair p reads source row p; a negative id is the shared expert.
+__global__ void wide_list_kernel(const int32_t *ids, const float *weights, uint64_t pairs, int experts, int *expert_of_pair,
+                                 int *src_of_pair, float *weight_of_pair) {
+    for (uint64_t p = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; p < pairs; p += (uint64_t)gridDim.x * blockDim.x) {
+        expert_of_pair[p] = ids[p] < 0 ? experts : ids[p];      // ids >= experts are refused by the count kernel
+        src_of_pair[p] = (int)p;
+        weight_of_pair[p] = weights[p];
+    }
+}
+
 // ---- permute ---------------------------------------------------------------------------------------
-__global__ void wide_count_kernel(const int32_t *selected, uint64_t pairs, int experts, int *counts, int *status) {
+__global__ void wide_count_kernel(const int *expert_of_pair, uint64_t pairs, int bins, int *counts, int *status) {
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < pairs; i += (uint64_t)gridDim.x * blockDim.x) {
-        const int e = selected[i];
-        if (e < 0 || e >= experts) raise(status, YVEX_B200_STATUS_ARGUMENT);
+        const int e = expert_of_pair[i];
+        if (e < 0 || e >= bins) raise(status, YVEX_B200_STATUS_ARGUMENT);
         else atomicAdd(&counts[e], 1);
     }
 }
 
-// One thread: exclusive scan of the group sizes and the column-block list (routed groups in
-// expert order, then the shared expert's token blocks).
-__global__ void wide_plan_kernel(const int *counts, int experts, uint64_t tokens, uint64_t pairs, int *offsets,
-                                 ColBlock *blocks, int *num_blocks, int max_blocks, int *status) {
+// One thread: exclusive scan of the group sizes and the column-block list in expert order
+// (bin `experts` is the shared expert, published as expert -1).
+__global__ void wide_plan_kernel(const int *counts, int experts, uint64_t pairs, int *offsets, ColBlock *blocks,
+                                 int *num_blocks, int max_blocks, int *status) {
     if (threadIdx.x || blockIdx.x) return;
     int off = 0, nb = 0;
-    for (int e = 0; e < experts; ++e) {
+    for (int e = 0; e <= experts; ++e) {
         offsets[e] = off;
         for (int c = 0; c < counts[e]; c += kTileN) {
-            if (nb < max_blocks) blocks[nb] = ColBlock{off + c, min(kTileN, counts[e] - c), e, 0};
+            if (nb < max_blocks) blocks[nb] = ColBlock{off + c, min(kTileN, counts[e] - c), e < experts ? e : -1, 0};
             ++nb;
         }
         off += counts[e];
     }
-    offsets[experts] = off;
+    offsets[experts + 1] = off;
     if ((uint64_t)off != pairs) raise(status, YVEX_B200_STATUS_ARGUMENT);
-    for (uint64_t c = 0; c < tokens; c += kTileN) {
-        if (nb < max_blocks) blocks[nb] = ColBlock{(int)(pairs + c), (int)min((uint64_t)kTileN, tokens - c), -1, 0};
-        ++nb;
-    }
     if (nb > max_blocks) { raise(status, YVEX_B200_STATUS_ARGUMENT); nb = max_blocks; }
     *num_blocks = nb;
 }
 
-// One CTA per expert: stable compaction of the pairs routed to it (ascending pair index).
-__global__ void wide_scatter_kernel(const int32_t *selected, uint64_t pairs, const int *offsets, int *perm, int *pos_of_pair) {
+// One CTA per bin: stable compaction of the pairs routed to it (ascending pair index).
+__global__ void wide_scatter_kernel(const int *expert_of_pair, uint64_t pairs, const int *offsets, int *perm, int *pos_of_pair) {
     const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     __shared__ int warp_count[32];
     __shared__ int base;
     if (threadIdx.x == 0) base = offsets[e];
     __syncthreads();
+    if (offsets[e + 1] == offsets[e]) return;          // empty bin (uniform across the CTA)
     for (uint64_t start = 0; start < pairs; start += blockDim.x) {
         const uint64_t i = start + threadIdx.x;
-        const bool hit = i < pairs && selected[i] == e;
+        const bool hit = i < pairs && expert_of_pair[i] == e;
         const unsigned ballot = __ballot_sync(0xffffffffu, hit);
         if (lane == 0) warp_count[warp] = __popc(ballot);
         __syncthreads();
@@ -72,28 +97,29 @@ __global__ void wide_scatter_kernel(const int32_t *selected, uint64_t pairs, con
     }
 }
 
-// act_h[pos] = fp16 row of the pair's token (routed, expert-major) and of every token (shared).
-__global__ void wide_gather_kernel(const __half *xr_h, const int *perm, uint64_t pairs, uint64_t tokens, uint64_t topk,
+// act_h[pos] = fp16 source row of the pair sorted to position pos.
+__global__ void wide_gather_kernel(const __half *rows_h, const int *perm, const int *src_of_pair, uint64_t pairs,
                                    uint64_t hidden, __half *act_h) {
     const uint64_t chunks = hidden / 8;           // 16-byte chunks per row
-    const uint64_t total = (pairs + tokens) * chunks;
+    const uint64_t total = pairs * chunks;
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t row = i / chunks, c = i % chunks;
-        const uint64_t tok = row < pairs ? (uint64_t)perm[row] / topk : row - pairs;
-        reinterpret_cast<uint4 *>(act_h)[row * chunks + c] = __ldg(reinterpret_cast<const uint4 *>(xr_h) + tok * chunks + c);
+        const uint64_t src = (uint64_t)src_of_pair[perm[row]];
+        reinterpret_cast<uint4 *>(act_h)[row * chunks + c] = __ldg(reinterpret_cast<const uint4 *>(rows_h) + src * chunks + c);
     }
 }
 
 // mid = bf16(silu(min(g,L)) * clamp(u,+-L) * w) as fp16, plus hi/lo fp16 sums over `group`
 // consecutive intermediates (32 for Q4_K, 16 for Q2_K, 0 = none) for the down GEMM's min term.
-__global__ void wide_swiglu_kernel(const float *gate, const float *up, const int *perm, const float *weights, uint64_t pairs,
+__global__ void wide_swiglu_kernel(const float *gate, const float *up, const int *perm, const float *weight_of_pair,
                                    uint64_t rows, uint64_t inter, float limit, int group, __half *mid_h, __half *sums,
                                    int *status) {
     const int lane = threadIdx.x & 31;
     const uint64_t total = rows * inter;          // inter is a multiple of 256, so warps never straddle rows
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t row = i / inter, col = i % inter;
-        const float w = row < pairs ? weights[perm[row]] : 1.0f;
+        const float w = weight_of_pair[perm[row]];
+        if (!isfinite(w)) raise(status, YVEX_B200_STATUS_NUMERIC);
         const float v = swiglu_mid(gate[i], up[i], w, limit, status);
         mid_h[i] = __float2half_rn(v);
         if (group) {
@@ -110,54 +136,77 @@ __global__ void wide_swiglu_kernel(const float *gate, const float *up, const int
     }
 }
 
-// out[t] = bf16( sum_{rank} y[pos(t, rank)] (rank order, f32) + y[pairs + t] )
-__global__ void wide_combine_kernel(const uint16_t *y, const int *pos_of_pair, uint64_t tokens, uint64_t topk, uint64_t pairs,
-                                    uint64_t hidden, float *out) {
+// out[t] = bf16( sum_{rank} y[row(t, rank)] (rank order, f32) + y_shared[row(t)] ); `pos` maps a
+// pair index to its row in y (nullptr = identity).
+__global__ void wide_combine_kernel(const uint16_t *y, const uint16_t *y_shared, const int *pos, const int *pos_shared,
+                                    uint64_t tokens, uint64_t topk, uint64_t hidden, float *out) {
     const uint64_t total = tokens * hidden;
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t t = i / hidden, h = i % hidden;
         float routed = 0.0f;
-        for (uint64_t r = 0; r < topk; ++r)
-            routed += __uint_as_float((uint32_t)y[(uint64_t)pos_of_pair[t * topk + r] * hidden + h] << 16);
-        const float shared = __uint_as_float((uint32_t)y[(pairs + t) * hidden + h] << 16);
-        out[i] = bf16_round(routed + shared);
+        for (uint64_t r = 0; r < topk; ++r) {
+            const uint64_t row = pos ? (uint64_t)pos[t * topk + r] : t * topk + r;
+            routed += __uint_as_float((uint32_t)y[row * hidden + h] << 16);
+        }
+        const uint64_t srow = pos_shared ? (uint64_t)pos_shared[t] : t;
+        out[i] = bf16_round(routed + __uint_as_float((uint32_t)y_shared[srow * hidden + h] << 16));
+    }
+}
+
+// y_out[p] = y[pos_of_pair[p]] (16-byte chunks of bf16 rows)
+__global__ void wide_unsort_kernel(const uint16_t *y, const int *pos_of_pair, uint64_t pairs, uint64_t hidden, uint16_t *y_out) {
+    const uint64_t chunks = hidden / 8, total = pairs * chunks;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t p = i / chunks, c = i % chunks;
+        reinterpret_cast<uint4 *>(y_out)[p * chunks + c] =
+            reinterpret_cast<const uint4 *>(y)[(uint64_t)pos_of_pair[p] * chunks + c];
     }
 }
 
 // ---- workspace -------------------------------------------------------------------------------------
-struct WideWorkspace {
-    int *counts, *offsets, *perm, *pos_of_pair, *num_blocks;
+struct PairWorkspace {
+    int *counts, *offsets, *perm, *pos_of_pair, *num_blocks, *expert_of_pair, *src_of_pair;
+    float *weight_of_pair;
     ColBlock *blocks;
     __half *act_h, *mid_h, *sums;
     float *gate, *up;
     uint16_t *y;
     int max_blocks;
+    void rebase(void *base) {
+        auto fix = [&](auto *&ptr) { ptr = reinterpret_cast<std::remove_reference_t<decltype(ptr)>>(
+                                         reinterpret_cast<uintptr_t>(base) + reinterpret_cast<uintptr_t>(ptr)); };
+        fix(counts); fix(offsets); fix(perm); fix(pos_of_pair); fix(num_blocks); fix(expert_of_pair); fix(src_of_pair);
+        fix(weight_of_pair); fix(blocks); fix(act_h); fix(mid_h); fix(sums); fix(gate); fix(up); fix(y);
+    }
 };
 
-static uint64_t wide_layout(const MoeGeom &g, uint64_t rows, uint64_t base_off, WideWorkspace *ws) {
+// Offsets of the pair pipeline's scratch for `pairs` pairs, starting at base_off.
+static uint64_t pair_layout(const MoeGeom &g, uint64_t pairs, uint64_t base_off, PairWorkspace *ws) {
     uint64_t off = base_off;
     auto take = [&](uint64_t bytes) { uint64_t at = off; off = (off + bytes + 255) & ~255ull; return at; };
-    const uint64_t pairs = rows * g.topk, all = pairs + rows;
-    WideWorkspace l{};
-    l.max_blocks = (int)(pairs / kTileN + g.experts + rows / kTileN + 2);
-    l.counts = reinterpret_cast<int *>(take((g.experts + 1) * 4));
-    l.offsets = reinterpret_cast<int *>(take((g.experts + 2) * 4));
+    PairWorkspace l{};
+    l.max_blocks = (int)(pairs / kTileN + g.experts + 2);
+    l.counts = reinterpret_cast<int *>(take((g.experts + 2) * 4));
+    l.offsets = reinterpret_cast<int *>(take((g.experts + 3) * 4));
     l.num_blocks = reinterpret_cast<int *>(take(4));
     l.perm = reinterpret_cast<int *>(take(pairs * 4));
     l.pos_of_pair = reinterpret_cast<int *>(take(pairs * 4));
+    l.expert_of_pair = reinterpret_cast<int *>(take(pairs * 4));
+    l.src_of_pair = reinterpret_cast<int *>(take(pairs * 4));
+    l.weight_of_pair = reinterpret_cast<float *>(take(pairs * 4));
     l.blocks = reinterpret_cast<ColBlock *>(take((uint64_t)l.max_blocks * sizeof(ColBlock)));
-    l.act_h = reinterpret_cast<__half *>(take((all + kTileN) * g.hidden * 2));
-    l.mid_h = reinterpret_cast<__half *>(take((all + kTileN) * g.inter * 2));
-    l.sums = reinterpret_cast<__half *>(take((all + kTileN) * (g.inter / 256) * 64));
-    l.gate = reinterpret_cast<float *>(take(all * g.inter * 4));
-    l.up = reinterpret_cast<float *>(take(all * g.inter * 4));
-    l.y = reinterpret_cast<uint16_t *>(take(all * g.hidden * 2));
+    l.act_h = reinterpret_cast<__half *>(take(pairs * g.hidden * 2));
+    l.mid_h = reinterpret_cast<__half *>(take(pairs * g.inter * 2));
+    l.sums = reinterpret_cast<__half *>(take(pairs * (g.inter / 256) * 64));
+    l.gate = reinterpret_cast<float *>(take(pairs * g.inter * 4));
+    l.up = reinterpret_cast<float *>(take(pairs * g.inter * 4));
+    l.y = reinterpret_cast<uint16_t *>(take(pairs * g.hidden * 2));
     if (ws) *ws = l;
     return off;
 }
 
 uint64_t moe_wide_workspace_bytes(const MoeGeom &g, uint64_t rows) {
-    return wide_layout(g, rows, moe_workspace_layout(g, rows, nullptr), nullptr);
+    return pair_layout(g, rows * (g.topk + 1), moe_workspace_layout(g, rows, nullptr), nullptr);
 }
 
 static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
@@ -212,60 +261,53 @@ bool moe_wide_gemm_eligible(const MoeGeom &g, const MoeWeights &w) {
     const uintptr_t ptrs = (uintptr_t)w.gate | (uintptr_t)w.up | (uintptr_t)w.down | (uintptr_t)w.shared_gate |
                            (uintptr_t)w.shared_up | (uintptr_t)w.shared_down;
     return g.gate_qtype == g.up_qtype && gemm_qtype(g.gate_qtype) && gemm_qtype(g.down_qtype) &&
-           g.inter == g.shared_inter && g.hidden % 256 == 0 && g.inter % 256 == 0 && (ptrs & 15u) == 0;
+           g.inter == g.shared_inter && g.hidden % 256 == 0 && g.inter % 256 == 0 && g.inter % kTileM == 0 &&
+           g.hidden % kTileM == 0 && (ptrs & 15u) == 0;
 }
 
-int moe_experts_wide(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, void *workspace, uint64_t rows,
-                     float *out, int *status, cudaStream_t s) {
-    WideWorkspace ww;
-    wide_layout(g, rows, moe_workspace_layout(g, rows, nullptr), &ww);
-    auto rebase = [&](auto *&ptr) { ptr = reinterpret_cast<std::remove_reference_t<decltype(ptr)>>(
-                                        reinterpret_cast<uintptr_t>(workspace) + reinterpret_cast<uintptr_t>(ptr)); };
-    rebase(ww.counts); rebase(ww.offsets); rebase(ww.perm); rebase(ww.pos_of_pair); rebase(ww.num_blocks);
-    rebase(ww.blocks); rebase(ww.act_h); rebase(ww.mid_h); rebase(ww.sums); rebase(ww.gate); rebase(ww.up); rebase(ww.y);
-    const uint64_t pairs = rows * g.topk, all = pairs + rows;
+// Runs the pair list already stored in pw.{expert,src,weight}_of_pair; leaves one bf16 row per
+// pair in pw.y at row pw.pos_of_pair[pair]. rows_h: the fp16 source rows the list indexes.
+static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorkspace &pw, const __half *rows_h, uint64_t pairs,
+                         int *status, cudaStream_t s) {
     const Geometry gg = geometry_of(g.gate_qtype), dg = geometry_of(g.down_qtype);
-
-    cudaMemsetAsync(ww.counts, 0, (g.experts + 1) * 4, s);
-    wide_count_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(ws.selected, pairs, (int)g.experts, ww.counts, status);
-    wide_plan_kernel<<<1, 32, 0, s>>>(ww.counts, (int)g.experts, rows, pairs, ww.offsets, ww.blocks, ww.num_blocks,
-                                      ww.max_blocks, status);
-    wide_scatter_kernel<<<(unsigned)g.experts, 512, 0, s>>>(ws.selected, pairs, ww.offsets, ww.perm, ww.pos_of_pair);
-    wide_gather_kernel<<<grid_for(all * (g.hidden / 8), 256, 16), 256, 0, s>>>(ws.xr_h, ww.perm, pairs, rows, g.topk, g.hidden,
-                                                                               ww.act_h);
+    const int bins = (int)g.experts + 1;
+    cudaMemsetAsync(pw.counts, 0, (g.experts + 2) * 4, s);
+    wide_count_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(pw.expert_of_pair, pairs, bins, pw.counts, status);
+    wide_plan_kernel<<<1, 32, 0, s>>>(pw.counts, (int)g.experts, pairs, pw.offsets, pw.blocks, pw.num_blocks, pw.max_blocks, status);
+    wide_scatter_kernel<<<(unsigned)bins, 512, 0, s>>>(pw.expert_of_pair, pairs, pw.offsets, pw.perm, pw.pos_of_pair);
+    wide_gather_kernel<<<grid_for(pairs * (g.hidden / 8), 256, 16), 256, 0, s>>>(rows_h, pw.perm, pw.src_of_pair, pairs, g.hidden,
+                                                                                 pw.act_h);
     int rc = launch_status(4);
     if (rc != OK) return rc;
     mark_phase(2, s);
 
     CUtensorMap act_map, mid_map;
-    if (make_act_map(&act_map, ww.act_h, all, g.hidden) != OK || make_act_map(&mid_map, ww.mid_h, all, g.inter) != OK)
+    if (make_act_map(&act_map, pw.act_h, pairs, g.hidden) != OK || make_act_map(&mid_map, pw.mid_h, pairs, g.inter) != OK)
         return ERR_BACKEND;
     GemmParams gu{};
     gu.w_routed[0] = (const uint8_t *)w.gate; gu.w_routed[1] = (const uint8_t *)w.up;
     gu.w_shared[0] = (const uint8_t *)w.shared_gate; gu.w_shared[1] = (const uint8_t *)w.shared_up;
     gu.row_bytes = g.hidden / gg.elems * gg.bytes;
     gu.M = (int)g.inter; gu.K = (int)g.hidden; gu.nmat = 2;
-    gu.colblocks = ww.blocks; gu.num_colblocks = ww.num_blocks;
-    gu.out_f32[0] = ww.gate; gu.out_f32[1] = ww.up; gu.out_bf16 = nullptr; gu.sums = nullptr; gu.status = status;
-    if (g.inter % kTileM || g.hidden % kTileM) return ERR_BOUNDS;
+    gu.colblocks = pw.blocks; gu.num_colblocks = pw.num_blocks;
+    gu.out_f32[0] = pw.gate; gu.out_f32[1] = pw.up; gu.out_bf16 = nullptr; gu.sums = nullptr; gu.status = status;
     rc = run_gemm(g.gate_qtype, act_map, gu, s);
     if (rc != OK) return rc;
     mark_phase(3, s);
 
     const int group = g.down_qtype == Q_Q4_K ? 32 : g.down_qtype == Q_Q2_K ? 16 : 0;
-    wide_swiglu_kernel<<<grid_for(all * g.inter, 256, 16), 256, 0, s>>>(ww.gate, ww.up, ww.perm, ws.weights, pairs, all, g.inter,
-                                                                       (float)g.limit, group, ww.mid_h, ww.sums, status);
+    wide_swiglu_kernel<<<grid_for(pairs * g.inter, 256, 16), 256, 0, s>>>(pw.gate, pw.up, pw.perm, pw.weight_of_pair, pairs, g.inter,
+                                                                         (float)g.limit, group, pw.mid_h, pw.sums, status);
     GemmParams dn{};
     dn.w_routed[0] = (const uint8_t *)w.down; dn.w_shared[0] = (const uint8_t *)w.shared_down;
     dn.row_bytes = g.inter / dg.elems * dg.bytes;
     dn.M = (int)g.hidden; dn.K = (int)g.inter; dn.nmat = 1;
-    dn.colblocks = ww.blocks; dn.num_colblocks = ww.num_blocks;
-    dn.out_bf16 = ww.y; dn.sums = ww.sums; dn.status = status;
+    dn.colblocks = pw.blocks; dn.num_colblocks = pw.num_blocks;
+    dn.out_bf16 = pw.y; dn.sums = pw.sums; dn.status = status;
     rc = run_gemm(g.down_qtype, mid_map, dn, s);
     if (rc != OK) return rc;
     mark_phase(4, s);
-    wide_combine_kernel<<<grid_for(rows * g.hidden, 256, 16), 256, 0, s>>>(ww.y, ww.pos_of_pair, rows, g.topk, pairs, g.hidden, out);
-    return launch_status(2);
+    return launch_status(1);
 }
 
 }  // namespace yb
@@ -283,8 +325,8 @@ extern "C" int yvex_b200_moe_wide(const yvex_b200_moe_geometry *geom, const yvex
     MoeGeom g = *geom;
     MoeWorkspace ws;
     const bool gemm = moe_wide_gemm_eligible(g, *w);
-    const uint64_t need = gemm ? moe_wide_workspace_bytes(g, rows) : moe_workspace_layout(g, rows, nullptr);
-    moe_workspace_layout(g, rows, &ws);
+    const uint64_t base = moe_workspace_layout(g, rows, &ws);
+    const uint64_t need = gemm ? moe_wide_workspace_bytes(g, rows) : base;
     if (!workspace || workspace_bytes < need) return ERR_NOMEM;
     ws.rebase(workspace);
     cudaStream_t s = as_stream(stream);
@@ -292,7 +334,22 @@ extern "C" int yvex_b200_moe_wide(const yvex_b200_moe_geometry *geom, const yvex
     rc = moe_ingress_and_route(g, *w, ws, x, logits, token_ids, rows, status, s);
     if (rc != OK) return rc;
     mark_phase(1, s);
-    rc = gemm ? moe_experts_wide(g, *w, ws, workspace, rows, out, status, s) : moe_experts_rows(g, *w, ws, rows, out, status, s);
+    if (gemm) {
+        PairWorkspace pw;
+        const uint64_t pairs = rows * (g.topk + 1), routed = rows * g.topk;
+        pair_layout(g, pairs, base, &pw);
+        pw.rebase(workspace);
+        wide_pairs_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(ws.selected, ws.weights, rows, g.topk, (int)g.experts,
+                                                                pw.expert_of_pair, pw.src_of_pair, pw.weight_of_pair);
+        rc = run_pair_list(g, *w, pw, ws.xr_h, pairs, status, s);
+        if (rc != OK) return rc;
+        wide_combine_kernel<<<grid_for(rows * g.hidden, 256, 16), 256, 0, s>>>(pw.y, pw.y, pw.pos_of_pair, pw.pos_of_pair + routed,
+                                                                             rows, g.topk, g.hidden, out);
+        mark_phase(5, s);
+        rc = launch_status(2);
+    } else {
+        rc = moe_experts_rows(g, *w, ws, rows, out, status, s);
+    }
     if (rc != OK) return rc;
     if (selected_out) cudaMemcpyAsync(selected_out, ws.selected, rows * g.topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, s);
     if (weights_out) cudaMemcpyAsync(weights_out, ws.weights, rows * g.topk * sizeof(float), cudaMemcpyDeviceToDevice, s);
@@ -301,4 +358,46 @@ extern "C" int yvex_b200_moe_wide(const yvex_b200_moe_geometry *geom, const yvex
 
 extern "C" uint64_t yvex_b200_moe_wide_workspace_bytes(const yvex_b200_moe_geometry *g, uint64_t rows) {
     return g ? moe_wide_workspace_bytes(*g, rows) : 0;
+}
+
+extern "C" uint64_t yvex_b200_moe_expert_rows_workspace_bytes(const yvex_b200_moe_geometry *g, uint64_t pairs) {
+    return g ? pair_layout(*g, pairs, 0, nullptr) : 0;
+}
+
+extern "C" int yvex_b200_moe_expert_rows(const yvex_b200_moe_geometry *geom, const yvex_b200_moe_weights *w,
+                                         const void *rows_f16, const int32_t *expert_ids, const float *route_weights,
+                                         uint64_t pairs, void *y_bf16, void *workspace, uint64_t workspace_bytes,
+                                         int *status, void *stream) {
+    int rc = moe_check_geometry(geom, w);
+    if (rc != OK) return rc;
+    if (!pairs) return OK;
+    if (!rows_f16 || !expert_ids || !route_weights || !y_bf16 || !status) return ERR_INVALID_ARG;
+    if (pairs > 0x7fffff00ull / 2 || (reinterpret_cast<uintptr_t>(rows_f16) & 15u) || (reinterpret_cast<uintptr_t>(y_bf16) & 15u))
+        return ERR_BOUNDS;
+    MoeGeom g = *geom;
+    if (!moe_wide_gemm_eligible(g, *w)) return ERR_UNSUPPORTED;
+    PairWorkspace pw;
+    if (!workspace || workspace_bytes < pair_layout(g, pairs, 0, &pw)) return ERR_NOMEM;
+    pw.rebase(workspace);
+    cudaStream_t s = as_stream(stream);
+    // the caller's list: source row of pair p is row p; a negative id names the shared expert
+    mark_phase(0, s);
+    wide_list_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(expert_ids, route_weights, pairs, (int)g.experts,
+                                                           pw.expert_of_pair, pw.src_of_pair, pw.weight_of_pair);
+    mark_phase(1, s);
+    rc = run_pair_list(g, *w, pw, static_cast<const __half *>(rows_f16), pairs, status, s);
+    if (rc != OK) return rc;
+    wide_unsort_kernel<<<grid_for(pairs * (g.hidden / 8), 256, 16), 256, 0, s>>>(pw.y, pw.pos_of_pair, pairs, g.hidden,
+                                                                                 static_cast<uint16_t *>(y_bf16));
+    mark_phase(5, s);
+    return launch_status(2);
+}
+
+extern "C" int yvex_b200_moe_combine(const void *y_routed_bf16, const void *y_shared_bf16, uint64_t tokens, uint64_t topk,
+                                     uint64_t hidden, float *out, int *status, void *stream) {
+    if (!y_routed_bf16 || !y_shared_bf16 || !out || !status || !tokens || !topk || !hidden) return ERR_INVALID_ARG;
+    wide_combine_kernel<<<grid_for(tokens * hidden, 256, 16), 256, 0, as_stream(stream)>>>(
+        static_cast<const uint16_t *>(y_routed_bf16), static_cast<const uint16_t *>(y_shared_bf16), nullptr, nullptr, tokens, topk,
+        hidden, out);
+    return launch_status(1);
 }

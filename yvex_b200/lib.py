@@ -42,6 +42,11 @@ def _load():
     lib.yvex_b200_moe_wide_workspace_bytes.restype = u64
     lib.yvex_b200_moe_wide_workspace_bytes.argtypes = [C.POINTER(MoeGeometry), u64]
     lib.yvex_b200_launch_count.restype = C.c_ulonglong
+    lib.yvex_b200_moe_expert_rows_workspace_bytes.restype = u64
+    lib.yvex_b200_moe_expert_rows_workspace_bytes.argtypes = [C.POINTER(MoeGeometry), u64]
+    lib.yvex_b200_moe_expert_rows.argtypes = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights), vp, vp, vp, u64, vp,
+                                              vp, u64, vp, vp]
+    lib.yvex_b200_moe_combine.argtypes = [vp, vp, u64, u64, u64, vp, vp, vp]
     lib.yvex_b200_attention_workspace_bytes.restype = u64
     lib.yvex_b200_attention_workspace_bytes.argtypes = [u64] * 5
     lib.yvex_b200_dequant_rows.argtypes = [C.c_uint, vp, u64, u64, u64, vp, vp, vp]
@@ -62,6 +67,7 @@ EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_ge
            "yvex_b200_dequant_rows", "yvex_b200_gemv", "yvex_b200_moe_workspace_bytes",
            "yvex_b200_moe_route", "yvex_b200_moe_decode", "yvex_b200_moe_wide",
            "yvex_b200_moe_wide_workspace_bytes", "yvex_b200_launch_count", "yvex_b200_phase_events",
+           "yvex_b200_moe_expert_rows_workspace_bytes", "yvex_b200_moe_expert_rows", "yvex_b200_moe_combine",
            "yvex_b200_attention_workspace_bytes", "yvex_b200_attention_gqa_decode",
            "yvex_b200_attention_f32"]
 
@@ -168,6 +174,35 @@ def moe_layer(geom, weights, x, status, logits=None, token_ids=None, wide=False,
     _moe_call(fn, "moe_wide" if wide else "moe_decode", geom, weights, x, logits, token_ids, rows, out,
               selected, wts, workspace, status)
     return out, selected, wts
+
+
+def moe_expert_rows(geom, weights, rows_f16, expert_ids, route_weights, status, workspace=None, out=None):
+    """Pair list on this device's expert shard: rows_f16 [P, hidden] fp16, expert_ids [P] int32
+    (negative = shared expert), route_weights [P] f32 -> bf16 rows [P, hidden]."""
+    torch = _torch()
+    pairs = rows_f16.shape[0]
+    if out is None:
+        out = torch.empty((pairs, geom.hidden), dtype=torch.bfloat16, device=rows_f16.device)
+    if pairs == 0:
+        return out
+    if workspace is None:
+        workspace = torch.empty(int(lib.yvex_b200_moe_expert_rows_workspace_bytes(C.byref(geom), pairs)),
+                                dtype=torch.uint8, device=rows_f16.device)
+    _check(lib.yvex_b200_moe_expert_rows(C.byref(geom), C.byref(weights), _p(rows_f16), _p(expert_ids),
+                                         _p(route_weights), pairs, _p(out), _p(workspace), workspace.numel(),
+                                         _p(status.word), _stream()), "moe_expert_rows")
+    return out
+
+
+def moe_combine(y_routed, y_shared, topk, status, out=None):
+    """y_routed [T*topk, hidden] bf16 in (token, rank) order, y_shared [T, hidden] bf16 -> f32 [T, hidden]."""
+    torch = _torch()
+    tokens, hidden = y_shared.shape
+    if out is None:
+        out = torch.empty((tokens, hidden), dtype=torch.float32, device=y_shared.device)
+    _check(lib.yvex_b200_moe_combine(_p(y_routed), _p(y_shared), tokens, topk, hidden, _p(out), _p(status.word),
+                                     _stream()), "moe_combine")
+    return out
 
 
 def moe_route(geom, weights, status, rows_f32=None, logits=None, token_ids=None):
