@@ -1,0 +1,242 @@
+/*
+ * yvex_b200 host boundary (C11): the slice of libyvex's backend operator surface that the
+ * quantized MoE execution path crosses, re-implemented over the sm_100a device layer
+ * (yvex_b200_kernels.h). Names, argument meaning, ownership rules and error behaviour follow the
+ * reference so that its runtime (src/runtime/moe.c, src/runtime/logits.c) could call this library
+ * for that path; every entry cites the reference interface it replaces.
+ *
+ * Conventions (reference: include/yvex/core.h:13-48, include/yvex/backend.h:1-3):
+ *   - every fallible call returns a yvex_status (0 ok, negative error) and fills the caller's
+ *     optional yvex_error {code, where, message};
+ *   - unsupported work is refused with YVEX_ERR_UNSUPPORTED before any launch; there is no
+ *     fallback across backend kinds and no CPU path in this library;
+ *   - outputs are published only on success (tensor->is_written, result structs zeroed on failure);
+ *   - a backend object and its stream belong to one caller at a time (src/server/scheduler.c:1-8).
+ *
+ * Struct layouts carry the fields this path reads, under the reference's field names; they are
+ * not binary-identical to the reference's structs (those embed planner / identity state that
+ * never reaches the backend). INTEGRATION.md shows the field-by-field adapter.
+ */
+#ifndef YVEX_B200_BACKEND_H
+#define YVEX_B200_BACKEND_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status and errors: include/yvex/core.h:13-48 ---------------------------------------- */
+typedef enum {
+    YVEX_OK = 0, YVEX_ERR = -1, YVEX_ERR_NOMEM = -2, YVEX_ERR_IO = -3, YVEX_ERR_FORMAT = -4,
+    YVEX_ERR_UNSUPPORTED = -5, YVEX_ERR_BACKEND = -6, YVEX_ERR_BOUNDS = -7, YVEX_ERR_STATE = -8,
+    YVEX_ERR_CANCELLED = -9, YVEX_ERR_INVALID_ARG = -10, YVEX_ERR_TIMEOUT = -11
+} yvex_status;
+typedef struct { yvex_status code; char where[96]; char message[256]; } yvex_error;
+void yvex_error_clear(yvex_error *err);
+void yvex_error_set(yvex_error *err, yvex_status code, const char *where, const char *message);
+const char *yvex_status_name(yvex_status status);
+
+/* ---- backend object: include/yvex/backend.h:16-152 ---------------------------------------- */
+typedef struct yvex_backend yvex_backend;
+typedef enum { YVEX_BACKEND_KIND_CPU = 0, YVEX_BACKEND_KIND_CUDA, YVEX_BACKEND_KIND_METAL, YVEX_BACKEND_KIND_ROCM } yvex_backend_kind;
+typedef enum { YVEX_BACKEND_STATUS_READY = 0, YVEX_BACKEND_STATUS_CONTEXT_READY, YVEX_BACKEND_STATUS_UNSUPPORTED,
+               YVEX_BACKEND_STATUS_FAILED } yvex_backend_status;
+typedef struct { yvex_backend_kind kind; const char *device; unsigned long long memory_limit_bytes; } yvex_backend_options;
+typedef struct {
+    unsigned long long allocated_bytes, allocation_count, allocation_events, release_events;
+    unsigned long long h2d_bytes, d2h_bytes, peak_allocated_bytes, memory_limit_bytes;
+} yvex_backend_memory_stats;
+/* Only YVEX_BACKEND_KIND_CUDA opens (device = "cuda:N" or NULL); every other kind is refused with
+ * YVEX_ERR_UNSUPPORTED like the reference does for METAL/ROCM (src/backend/core.c:176-205). */
+int yvex_backend_open(yvex_backend **out, const yvex_backend_options *options, yvex_error *err);
+int yvex_backend_close_checked(yvex_backend **backend, yvex_error *err);
+void yvex_backend_close(yvex_backend *backend);
+yvex_backend_kind yvex_backend_kind_of(const yvex_backend *backend);
+yvex_backend_status yvex_backend_status_of(const yvex_backend *backend);
+int yvex_backend_get_memory_stats(const yvex_backend *backend, yvex_backend_memory_stats *out, yvex_error *err);
+int yvex_backend_sync(yvex_backend *backend, yvex_error *err);
+/* The CUDA stream the backend enqueues on (for callers that interleave their own work). */
+void *yvex_backend_stream(const yvex_backend *backend);
+
+/* ---- tensors: include/yvex/backend.h:44-52,169-192, include/yvex/internal/backend.h:256-269 -- */
+typedef enum { YVEX_DTYPE_UNKNOWN = 0, YVEX_DTYPE_F32, YVEX_DTYPE_F16, YVEX_DTYPE_BF16, YVEX_DTYPE_I32, YVEX_DTYPE_U8 } yvex_dtype;
+#define YVEX_TENSOR_MAX_DIMS 4
+typedef struct {
+    const char *name;
+    yvex_dtype dtype;
+    unsigned int rank;
+    unsigned long long dims[YVEX_TENSOR_MAX_DIMS];
+    unsigned long long bytes;
+} yvex_backend_tensor_desc;
+typedef struct yvex_device_tensor {
+    yvex_backend *owner;
+    unsigned long long owner_id;
+    yvex_dtype dtype;
+    unsigned int rank;
+    unsigned long long dims[YVEX_TENSOR_MAX_DIMS];
+    unsigned long long bytes;
+    unsigned char *data;          /* device address */
+    unsigned char *host_data;     /* pinned staging copy for resident tensors, else NULL */
+    int is_written;
+} yvex_device_tensor;
+int yvex_backend_tensor_alloc(yvex_backend *backend, const yvex_backend_tensor_desc *desc, yvex_device_tensor **out, yvex_error *err);
+void yvex_backend_tensor_free(yvex_backend *backend, yvex_device_tensor *tensor);
+int yvex_backend_tensor_write(yvex_backend *backend, yvex_device_tensor *tensor, const void *src, unsigned long long len, yvex_error *err);
+int yvex_backend_tensor_read(yvex_backend *backend, const yvex_device_tensor *tensor, void *dst, unsigned long long len, yvex_error *err);
+unsigned long long yvex_device_tensor_bytes(const yvex_device_tensor *tensor);
+int yvex_device_tensor_is_written(const yvex_device_tensor *tensor);
+
+/* ---- resident weights and workspace: include/yvex/internal/backend.h:311-324, src/backend/residency.c:24-112,
+ *      src/backend/private.h:159-162 ----------------------------------------------------------------------- */
+typedef enum { YVEX_BACKEND_RESIDENT_INVALID = -1, YVEX_BACKEND_RESIDENT_MISS = 0, YVEX_BACKEND_RESIDENT_HIT = 1 } yvex_backend_resident_result;
+/* On a discrete GPU the arena is a pinned host staging buffer (host) plus an HBM tensor (out);
+ * callers keep naming weights by HOST pointers into the arena, as the reference runtime does. */
+int yvex_backend_resident_alloc(yvex_backend *backend, const yvex_backend_tensor_desc *desc, yvex_device_tensor **out,
+                                unsigned char **host, yvex_error *err);
+/* One H2D copy of the whole arena; synchronous (reference: resident_prefetch). */
+int yvex_backend_resident_prefetch(yvex_backend *backend, yvex_device_tensor *tensor, unsigned long long *prefetched_bytes, yvex_error *err);
+int yvex_backend_resident_attach(yvex_backend *backend, const unsigned char *host_base, unsigned long long bytes,
+                                 const yvex_device_tensor *device_tensor, unsigned long long generation, yvex_error *err);
+int yvex_backend_resident_detach(yvex_backend *backend, yvex_error *err);
+int yvex_backend_resident_resolve(const yvex_backend *backend, const unsigned char *host, unsigned long long bytes,
+                                  unsigned long long *device_address);
+int yvex_backend_workspace_attach(yvex_backend *backend, yvex_device_tensor *workspace, yvex_error *err);
+int yvex_backend_workspace_detach(yvex_backend *backend, yvex_error *err);
+
+/* ---- capability: include/yvex/backend.h:77-129 ------------------------------------------------------------ */
+typedef enum {
+    YVEX_BACKEND_VARIANT_ATTENTION_CAUSAL_F32 = 13, YVEX_BACKEND_VARIANT_ATTENTION_NONCAUSAL_F32 = 14,
+    YVEX_BACKEND_VARIANT_QTYPE_ROW_DOT = 15, YVEX_BACKEND_VARIANT_ATTENTION_ENCODED = 16, YVEX_BACKEND_VARIANT_COUNT = 17
+} yvex_backend_operation_variant;
+typedef enum { YVEX_BACKEND_CAPABILITY_UNSUPPORTED = 0, YVEX_BACKEND_CAPABILITY_SUPPORTED, YVEX_BACKEND_CAPABILITY_FAILED } yvex_backend_capability_state;
+typedef struct { yvex_backend_kind backend_kind; int variant; yvex_backend_capability_state state; int context_available, function_available; } yvex_backend_capability_result;
+int yvex_backend_query_capability(const yvex_backend *backend, int variant, yvex_backend_capability_result *out, yvex_error *err);
+/* 1 if qtype has decode + device compute here (the reference's dedicated_cuda_compute_available,
+ * src/gguf/quant_registry.c:50-103, plus the declared Q4_K extension). */
+int yvex_backend_qtype_supported(const yvex_backend *backend, unsigned int qtype);
+
+/* ---- vtable ops that are NOT on this path fail closed: src/backend/core.c:954-958 -------------------------- */
+int yvex_backend_op_embed(yvex_backend *backend, const yvex_device_tensor *embedding, const unsigned int *token_ids,
+                          unsigned long long token_count, yvex_device_tensor *out, yvex_error *err);
+int yvex_backend_op_rms_norm(yvex_backend *backend, const yvex_device_tensor *input, const yvex_device_tensor *weight, float epsilon,
+                             yvex_device_tensor *out, yvex_error *err);
+int yvex_backend_op_matmul(yvex_backend *backend, const yvex_device_tensor *input, const yvex_device_tensor *weight,
+                           yvex_device_tensor *out, yvex_error *err);
+
+/* ---- encoded matvec: include/yvex/internal/backend.h:325-337, src/backend/cuda/qtype.c:220-405 ------------- */
+typedef struct yvex_backend_cuda_operation_facts {
+    unsigned long long h2d_bytes, d2h_bytes, d2d_bytes, kernel_launches, upload_count;
+    unsigned long long download_count, stream_synchronizations, device_synchronizations;
+    unsigned long long active_weight_bytes, state_bytes;
+    unsigned long long activation_bytes, temporary_bytes, tensor_core_launches;
+    int compulsory_memory_facts_available;
+} yvex_backend_cuda_operation_facts;
+/* output[input_row][row] = dot(row, input[input_row]) (+ additive). resident_encoded is a HOST pointer
+ * into the attached resident arena. input_tail / activation_q8 = 1 (the reference's split-input and
+ * Q8_K-activation variants) are refused with YVEX_ERR_UNSUPPORTED. Synchronises like the reference. */
+int yvex_backend_cuda_encoded_matvec(yvex_backend *backend, const unsigned char *resident_encoded,
+    unsigned long long encoded_bytes, unsigned int qtype, unsigned long long row_count,
+    unsigned long long row_width, unsigned long long row_bytes, unsigned long long input_rows,
+    const yvex_device_tensor *input, const yvex_device_tensor *input_tail, unsigned long long input_head_width,
+    const yvex_device_tensor *additive, yvex_device_tensor *output, int activation_q8,
+    yvex_backend_cuda_operation_facts *facts, yvex_error *err);
+
+/* ---- attention: include/yvex/backend.h:246-257 (public op) ------------------------------------------------- */
+int yvex_backend_op_attention(yvex_backend *backend, const yvex_device_tensor *query, const yvex_device_tensor *keys,
+                              const yvex_device_tensor *values, unsigned long long seq_len, unsigned long long position,
+                              float scale, int causal, yvex_device_tensor *score_scratch,
+                              yvex_device_tensor *probability_scratch, yvex_device_tensor *out, yvex_error *err);
+/* Extension (the reference's GQA exists only as the text-encoder prefill kernel,
+ * src/backend/cuda/transformer_kernels.cu:85-145): decode-time GQA over a bf16 KV cache.
+ * query [sessions][q_heads][head_dim] bf16, keys/values [sessions][kv_heads][context][head_dim] bf16,
+ * out [sessions][q_heads][head_dim] f32. Scratch comes from the attached workspace. */
+int yvex_backend_attention_gqa_decode(yvex_backend *backend, const yvex_device_tensor *query, const yvex_device_tensor *keys,
+                                      const yvex_device_tensor *values, unsigned long long sessions, unsigned long long q_heads,
+                                      unsigned long long kv_heads, unsigned long long head_dim, unsigned long long context,
+                                      unsigned long long position, float scale, yvex_device_tensor *out, yvex_error *err);
+
+/* ---- MoE op table: include/yvex/internal/moe.h:36-84,161-166,221-297 --------------------------------------- */
+#define YVEX_MOE_MAX_SELECTED 16u
+#define YVEX_MOE_KERNEL_SM100_DEQUANT_GEMV "sm100-dequant-gemv"
+#define YVEX_MOE_KERNEL_SM100_TCGEN05_EXPERT "sm100-f16-tcgen05-expert"
+typedef enum { YVEX_MOE_ROUTER_HASH_TOKEN_ID = 0, YVEX_MOE_ROUTER_LEARNED_HIDDEN_STATE } yvex_moe_router_class;
+typedef enum {
+    YVEX_MOE_WEIGHT_FFN_NORM = 0, YVEX_MOE_WEIGHT_MHC_FUNCTION, YVEX_MOE_WEIGHT_MHC_BASE, YVEX_MOE_WEIGHT_MHC_SCALE,
+    YVEX_MOE_WEIGHT_ROUTER, YVEX_MOE_WEIGHT_ROUTER_TABLE, YVEX_MOE_WEIGHT_ROUTER_BIAS, YVEX_MOE_WEIGHT_ROUTED_GATE,
+    YVEX_MOE_WEIGHT_ROUTED_UP, YVEX_MOE_WEIGHT_ROUTED_DOWN, YVEX_MOE_WEIGHT_SHARED_GATE, YVEX_MOE_WEIGHT_SHARED_UP,
+    YVEX_MOE_WEIGHT_SHARED_DOWN, YVEX_MOE_WEIGHT_COUNT
+} yvex_moe_weight_slot;
+typedef struct {
+    unsigned int qtype;
+    const char *kernel_family;           /* NULL or one of the YVEX_MOE_KERNEL_SM100_* names; others are refused */
+    const unsigned char *encoded;        /* HOST pointer into the resident arena */
+    size_t encoded_bytes;
+    unsigned long long row_bytes, row_width, row_count;
+} yvex_moe_weight_view;
+typedef struct {
+    yvex_moe_router_class router_class;
+    unsigned long long hidden_width, residual_streams, expanded_width;
+    unsigned long long routed_experts, shared_experts, experts_per_token;
+    unsigned long long expert_intermediate_width, shared_intermediate_width;
+    unsigned long long hash_table_rows;
+    double routed_scaling_factor, activation_limit;
+    int normalize_topk_probabilities;
+} yvex_moe_layer_plan;
+typedef struct { int status, pending; unsigned long long row_count, row_expert_pairs; } yvex_moe_device_completion_slot;
+typedef struct { int defer; yvex_moe_device_completion_slot *host; } yvex_moe_device_completion;
+typedef struct {
+    const yvex_moe_layer_plan *layer;
+    yvex_moe_weight_view weights[YVEX_MOE_WEIGHT_COUNT];
+    int (*cancel_requested)(void *context);
+    void *cancel_context;
+    const yvex_moe_device_completion *device_completion;
+} yvex_moe_layer_job;
+typedef struct {
+    unsigned long long row_count, row_width, row_stride;
+    const float *expanded_rows;                /* host rows (copied in), or NULL when device_rows is given */
+    const yvex_device_tensor *device_rows;     /* f32 [row_count x row_stride] */
+    yvex_device_tensor *device_outputs;        /* f32 [row_count x row_stride], optional when host output is given */
+    const float *router_logits;                /* extension: host logits [row_count x routed_experts] replacing the router projection */
+    const yvex_device_tensor *device_router_logits;
+    const unsigned int *token_ids;
+    int token_ids_present;
+} yvex_moe_row_batch;
+typedef struct {
+    float *combined_rows;                      /* host [row_count x hidden_width], optional */
+    unsigned long long combined_capacity;
+    unsigned long long *selected_experts;      /* host [row_count x experts_per_token], optional */
+    float *selected_weights;
+    unsigned long long selection_capacity;
+} yvex_moe_row_batch_output;
+typedef struct {
+    int completed, device_completion_pending;
+    unsigned long long row_count, row_expert_pairs;
+    unsigned long long grouped_expert_operations, shared_expert_operations;
+    unsigned long long expert_subviews_accessed, encoded_bytes_read;
+    unsigned long long h2d_bytes, d2h_bytes, d2d_bytes, kernel_launches, tensor_core_launches;
+    unsigned long long stream_synchronizations;
+    unsigned long long active_weight_base_bytes, active_weight_per_unique_expert_bytes;
+    unsigned long long activation_bytes, temporary_bytes;
+} yvex_moe_row_batch_result;
+typedef struct {
+    /* Derived layouts are not offered: both return YVEX_ERR_UNSUPPORTED and the canonical row layout is used. */
+    int (*derived_layout_plan)(const void *decision, unsigned long long *storage_bytes, yvex_error *err);
+    int (*derived_layout_build)(const void *decision, const unsigned char *canonical, unsigned long long canonical_bytes,
+                                unsigned char *derived, unsigned long long storage_bytes, yvex_error *err);
+    int (*workspace_required)(const yvex_moe_layer_plan *layer, unsigned long long row_count, unsigned long long *bytes, yvex_error *err);
+    /* <= 62 rows, like moe_cuda_execute_rows (src/backend/cuda/moe.c:1826-1923). */
+    int (*execute_rows)(yvex_backend *backend, const yvex_moe_layer_job *job, const yvex_moe_row_batch *batch,
+                        const yvex_moe_row_batch_output *output, yvex_moe_row_batch_result *result, yvex_error *err);
+    int (*complete_rows)(yvex_backend *backend, int barrier_observed, yvex_moe_row_batch_result *result, yvex_error *err);
+    /* Extension: the same contract without the row limit (prefill); workspace_required_wide sizes it. */
+    int (*workspace_required_wide)(const yvex_moe_layer_plan *layer, unsigned long long row_count, unsigned long long *bytes, yvex_error *err);
+    int (*execute_rows_wide)(yvex_backend *backend, const yvex_moe_layer_job *job, const yvex_moe_row_batch *batch,
+                             const yvex_moe_row_batch_output *output, yvex_moe_row_batch_result *result, yvex_error *err);
+} yvex_backend_moe_operations;
+/* NULL unless the backend is an open CUDA backend (src/backend/cuda/moe.c:1968-1981). */
+const yvex_backend_moe_operations *yvex_backend_moe_operations_get(const yvex_backend *backend);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

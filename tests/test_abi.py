@@ -79,6 +79,21 @@ def test_entry_points_refuse_before_launch(lib):
     assert lib.moe_workspace_bytes(g, 1) % 256 == 0 and lib.moe_workspace_bytes(g, 1) > 0
 
 
+def test_host_boundary_refuses_other_backend_kinds_and_missing_devices(lib):
+    import torch
+    from yvex_b200 import backend as B
+    for kind in (B.KIND_CPU, B.KIND_METAL):
+        be = B.Backend(kind=kind)
+        assert be.rc == B.UNSUPPORTED and not be.handle.value        # no CPU path, no cross-backend fallback
+    assert B.moe_ops(B.Backend(kind=B.KIND_CPU)) is None
+    assert lib.lib.yvex_status_name(-5) == b"unsupported"
+    if not torch.cuda.is_available():
+        be = B.Backend()
+        assert be.rc == B.BACKEND and not be.handle.value            # fails loudly without a device
+    bad = B.Backend(device=b"tpu:0")
+    assert bad.rc == B.INVALID_ARG
+
+
 def test_compute_without_device_fails_loudly(lib):
     import torch
     if torch.cuda.is_available():

@@ -1,0 +1,254 @@
+"""The C11 host boundary on a B200: the calls the reference runtime makes on its backend for this
+path (resident weights named by host pointers, workspace attach, execute_rows / complete_rows,
+encoded matvec, op_attention), their outputs against the CPU oracle, and their refusals
+(src/backend/cuda/moe.c:1826-1923, src/backend/cuda/qtype.c:220-405, src/backend/core.c:990-1036)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from golden_cases import attention_inputs, layer_inputs
+from yvex_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def B():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from yvex_b200 import backend
+    return backend
+
+
+def rel_l2(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def layer_setup(B, name, down=synth.Q2_K, **job_kw):
+    spec, weights, router, x, logits = layer_inputs(name, down_qtype=down)
+    be = B.Backend()
+    assert be.rc == B.OK, be.message()
+    arrays = dict(weights)
+    if router is not None:
+        arrays["router"] = router
+    arena = B.ResidentArena(be, arrays)
+    job = B.moe_job(arena, spec, router=router is not None, **job_kw)
+    return be, arena, job, spec, x, logits
+
+
+def attach_workspace(B, be, job, rows, wide=False, shrink=0):
+    ops = B.moe_ops(be)
+    need = B.ull()
+    fn = ops.workspace_required_wide if wide else ops.workspace_required
+    assert fn(job.layer, rows, C.byref(need), C.byref(be.err)) == B.OK
+    rc, ws, _ = be.tensor(need.value - shrink)
+    assert rc == B.OK
+    assert B._lib.yvex_backend_workspace_attach(be.h, ws, C.byref(be.err)) == B.OK
+    return ops, ws
+
+
+def run_rows(B, be, ops, job, x, logits, wide=False, selection=True):
+    rows, H = x.shape
+    k = job._plan.experts_per_token
+    out = np.zeros((rows, H), np.float32)
+    sel = np.zeros((rows, k), np.uint64)
+    wts = np.zeros((rows, k), np.float32)
+    batch = B.RowBatch(rows, H, H, x.ctypes.data_as(B.vp), None, None,
+                       None if logits is None else logits.ctypes.data_as(B.vp), None, None, 0)
+    o = B.RowBatchOutput(out.ctypes.data_as(B.vp), out.size, sel.ctypes.data_as(B.vp) if selection else None,
+                         wts.ctypes.data_as(B.vp) if selection else None, sel.size)
+    res = B.RowBatchResult()
+    fn = ops.execute_rows_wide if wide else ops.execute_rows
+    rc = fn(be.h, C.byref(job), C.byref(batch), C.byref(o), C.byref(res), C.byref(be.err))
+    return rc, out, sel, wts, res
+
+
+@pytest.mark.parametrize("name", ["small_router", "small_logits", "c2_shape"])
+def test_execute_rows_host_buffers_vs_frozen_reference(B, golden, name):
+    be, arena, job, spec, x, logits = layer_setup(B, name)
+    ops, _ = attach_workspace(B, be, job, x.shape[0])
+    rc, out, sel, wts, res = run_rows(B, be, ops, job, x, logits)
+    assert rc == B.OK, be.message()
+    assert (sel == golden[f"layer_{name}_sel"]).all()
+    assert np.abs(wts - golden[f"layer_{name}_w"].view(np.float32)).max() <= 2e-7
+    assert rel_l2(out, golden[f"layer_{name}_out"].view(np.float32)) <= 1e-3
+    assert res.completed == 1 and res.row_count == x.shape[0] and res.row_expert_pairs == x.shape[0] * spec.topk
+    assert res.kernel_launches >= 3 and res.h2d_bytes >= x.nbytes and res.d2h_bytes >= out.nbytes
+    assert res.active_weight_per_unique_expert_bytes == spec.weight_bytes_per_expert()
+    assert be.close() == B.OK
+
+
+def test_execute_rows_device_tensors_and_deferred_completion(B, golden):
+    be, arena, job, spec, x, logits = layer_setup(B, "small_router")
+    ops, _ = attach_workspace(B, be, job, x.shape[0])
+    rows, H = x.shape
+    tin = be.from_array(x, B.F32)
+    rc, tout, _ = be.tensor(x.nbytes, B.F32, [rows, H])
+    slot = B.CompletionSlot()
+    comp = B.Completion(1, C.pointer(slot))
+    job.device_completion = C.pointer(comp)
+    batch = B.RowBatch(rows, H, H, None, tin, tout, None, None, None, 0)
+    res = B.RowBatchResult()
+    rc = ops.execute_rows(be.h, C.byref(job), C.byref(batch), None, C.byref(res), C.byref(be.err))
+    assert rc == B.OK and res.device_completion_pending == 1 and res.completed == 0
+    # a second layer may not start on this backend until the first is completed
+    assert ops.execute_rows(be.h, C.byref(job), C.byref(batch), None, C.byref(B.RowBatchResult()), C.byref(be.err)) == B.STATE
+    assert ops.complete_rows(be.h, 0, C.byref(res), C.byref(be.err)) == B.OK
+    assert res.completed == 1 and slot.pending == 0 and slot.status == 0
+    assert ops.complete_rows(be.h, 0, C.byref(res), C.byref(be.err)) == B.STATE
+    rc, out = be.read(tout, np.float32, rows * H)
+    assert rc == B.OK and rel_l2(out.reshape(rows, H), golden["layer_small_router_out"].view(np.float32)) <= 1e-3
+    assert be.close() == B.OK
+
+
+def test_execute_rows_refusals(B):
+    be, arena, job, spec, x, logits = layer_setup(B, "small_logits")
+    ops = B.moe_ops(be)
+    # no workspace attached / too small -> NOMEM
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.NOMEM
+    ops, ws = attach_workspace(B, be, job, x.shape[0], shrink=4096)
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.NOMEM
+    be.free(ws)
+    ops, ws = attach_workspace(B, be, job, x.shape[0])
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.OK
+    # 63 rows is outside the narrow contract
+    big = np.zeros((63, spec.hidden), np.float32)
+    assert run_rows(B, be, ops, job, big, np.zeros((63, spec.experts), np.float32))[0] == B.UNSUPPORTED
+    need = B.ull()
+    assert ops.workspace_required(job.layer, 63, C.byref(need), C.byref(be.err)) == B.UNSUPPORTED
+    # unknown kernel family
+    job.weights[B.W_GATE].kernel_family = b"sm121-int8-tensorcore-expert"
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.UNSUPPORTED
+    job.weights[B.W_GATE].kernel_family = b"sm100-dequant-gemv"
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.OK
+    # a qtype without a decoder (Q3_K) never reaches the device
+    job.weights[B.W_DOWN].qtype = 11
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.UNSUPPORTED
+    job.weights[B.W_DOWN].qtype = spec.down_qtype
+    # the mHC envelope is not built: refused, not skipped
+    job._plan.residual_streams = 4
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.UNSUPPORTED
+    job._plan.residual_streams = 1
+    # cancellation callback
+    job.cancel_requested = B.CANCEL_FN(lambda ctx: 1)
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.CANCELLED
+    job.cancel_requested = B.CANCEL_FN(0)
+    # weights outside the resident arena -> STATE
+    stray = np.zeros(job.weights[B.W_UP].encoded_bytes, np.uint8)
+    keep = job.weights[B.W_UP].encoded
+    job.weights[B.W_UP].encoded = stray.ctypes.data
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.STATE
+    job.weights[B.W_UP].encoded = keep
+    # non-finite input surfaces as a backend error and publishes nothing
+    bad = x.copy()
+    bad[0, 0] = np.nan
+    rc, out, _, _, res = run_rows(B, be, ops, job, bad, logits)
+    assert rc == B.BACKEND and res.completed == 0
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.OK            # the status word was cleared
+    # derived layouts are not offered
+    assert ops.derived_layout_plan(None, C.byref(need), C.byref(be.err)) == B.UNSUPPORTED
+    assert be.close() == B.OK
+
+
+def test_execute_rows_wide_vs_oracle(B, port):
+    H, E, k, I, T = 512, 8, 2, 256, 150
+    spec = synth.MoELayerSpec(H, E, k, I, down_qtype=synth.Q4_K)
+    rng = np.random.default_rng(77)
+    x, logits = rng.standard_normal((T, H)).astype(np.float32), rng.standard_normal((T, E)).astype(np.float32)
+    weights = synth.moe_weights(spec, 78)
+    be = B.Backend()
+    arena = B.ResidentArena(be, weights)
+    job = B.moe_job(arena, spec, router=False, family=b"sm100-f16-tcgen05-expert")
+    ops, _ = attach_workspace(B, be, job, T, wide=True)
+    rc, out, sel, wts, res = run_rows(B, be, ops, job, x, logits, wide=True)
+    assert rc == B.OK, be.message()
+    rcp, want, sel0, _ = port.moe_tokens(port.layer(spec, weights, allow_q4k=True), x, logits=logits, threads=8)
+    assert rcp == 0 and (sel == sel0).all() and rel_l2(out, want) <= 1e-3
+    assert be.close() == B.OK
+
+
+def test_encoded_matvec_resident_pointer_contract(B, port):
+    rows, width = 300, 4096
+    w = synth.random_blocks(synth.IQ2_XXS, rows, width, 5)
+    x = np.random.default_rng(6).standard_normal((2, width)).astype(np.float32)
+    be = B.Backend()
+    arena = B.ResidentArena(be, {"w": w})
+    tin = be.from_array(x, B.F32)
+    rc, tout, _ = be.tensor(2 * rows * 4, B.F32, [2, rows])
+    facts = B.Facts()
+    args = (arena.host_ptr("w"), w.size, synth.IQ2_XXS, rows, width, w.shape[1], 2, tin, None, 0, None, tout, 0, C.byref(facts),
+            C.byref(be.err))
+    assert B._lib.yvex_backend_cuda_encoded_matvec(be.h, *args) == B.OK, be.message()
+    rc, y = be.read(tout, np.float32, 2 * rows)
+    for i in range(2):
+        _, want = port.matvec(synth.IQ2_XXS, w, rows, width, x[i], threads=4)
+        assert rel_l2(y.reshape(2, rows)[i], want) <= 1e-5
+    assert facts.kernel_launches == 2 and facts.active_weight_bytes == w.size and facts.stream_synchronizations == 1
+    # refusals: Q4_0 has no codec anywhere; Q8_K activations are not built; a pointer outside the arena
+    bad = list(args)
+    bad[2] = 2
+    assert B._lib.yvex_backend_cuda_encoded_matvec(be.h, *bad) == B.UNSUPPORTED
+    bad = list(args)
+    bad[12] = 1
+    assert B._lib.yvex_backend_cuda_encoded_matvec(be.h, *bad) == B.UNSUPPORTED
+    bad = list(args)
+    bad[12] = 2
+    assert B._lib.yvex_backend_cuda_encoded_matvec(be.h, *bad) == B.INVALID_ARG
+    bad = list(args)
+    bad[0] = w.ctypes.data
+    assert B._lib.yvex_backend_cuda_encoded_matvec(be.h, *bad) == B.FORMAT
+    unwritten = be.tensor(x.nbytes, B.F32, [2, width])[1]
+    bad = list(args)
+    bad[7] = unwritten
+    assert B._lib.yvex_backend_cuda_encoded_matvec(be.h, *bad) == B.FORMAT
+    assert be.close() == B.OK
+
+
+def test_op_attention_and_gqa_decode(B, port, golden):
+    be = B.Backend()
+    rng = np.random.default_rng(3)
+    q, k, v = (rng.standard_normal(s).astype(np.float32) for s in ((64,), (90, 64), (90, 64)))
+    tq, tk, tv = be.from_array(q, B.F32), be.from_array(k, B.F32), be.from_array(v, B.F32)
+    ts, tp, to = (be.tensor(n * 4, B.F32, [n])[1] for n in (90, 90, 64))
+    A = B._lib.yvex_backend_op_attention
+    assert A(be.h, tq, tk, tv, 90, 40, 0.125, 1, ts, tp, to, C.byref(be.err)) == B.OK, be.message()
+    rc, out = be.read(to, np.float32, 64)
+    _, want = port.attention_head(q, k, v, 40, 0.125, 1)
+    assert rel_l2(out, want) <= 1e-5
+    assert A(be.h, tq, tk, tv, 90, 90, 0.125, 1, ts, tp, to, C.byref(be.err)) == B.BOUNDS       # position-out-of-range
+    assert A(be.h, tq, tk, tv, 90, 40, -1.0, 1, ts, tp, to, C.byref(be.err)) == B.INVALID_ARG
+    assert A(be.h, tq, tk, tv, 91, 40, 0.125, 1, ts, tp, to, C.byref(be.err)) == B.FORMAT       # dims mismatch
+    # GQA decode through the boundary
+    import torch
+    qf, kf, vf, pos, scale = attention_inputs("small")
+    bits = lambda a: synth.bf16_bits(a).reshape(a.shape)
+    gq, gk, gv = (be.from_array(bits(a), B.BF16) for a in (qf, kf, vf))
+    S, Hq, D = qf.shape
+    gout = be.tensor(qf.size * 4, B.F32, list(qf.shape))[1]
+    G = B._lib.yvex_backend_attention_gqa_decode
+    args = (gq, gk, gv, S, Hq, kf.shape[1], D, kf.shape[2], pos, scale, gout, C.byref(be.err))
+    assert G(be.h, *args) == B.NOMEM                                  # no workspace attached yet
+    ws = be.tensor(1 << 22)[1]
+    assert B._lib.yvex_backend_workspace_attach(be.h, ws, C.byref(be.err)) == B.OK
+    assert G(be.h, *args) == B.OK, be.message()
+    rc, o = be.read(gout, np.float32, qf.size)
+    assert rel_l2(o.reshape(qf.shape), golden["attention_small"].view(np.float32)) <= 1e-4
+    # ops outside the path fail closed
+    assert B._lib.yvex_backend_op_matmul(be.h, tq, tk, to, C.byref(be.err)) == B.UNSUPPORTED
+    assert torch.cuda.is_available() and be.close() == B.OK
+
+
+def test_backend_lifecycle_and_ownership(B):
+    be = B.Backend()
+    other = B.Backend()
+    rc, t, _ = be.tensor(1024)
+    assert other.write(t, np.zeros(16, np.uint8)) == B.INVALID_ARG           # foreign tensor
+    assert be.read(t, np.uint8, 16)[0] == B.STATE                            # never written
+    assert B._lib.yvex_backend_close_checked(C.byref(be.handle), C.byref(be.err)) == B.STATE   # still owns a tensor
+    assert be.handle.value                                                   # owner retained for retry
+    assert be.close() == B.OK and other.close() == B.OK
+    limited = B.Backend(memory_limit=4096)
+    assert limited.tensor(8192)[0] == B.NOMEM and limited.close() == B.OK

@@ -1,0 +1,253 @@
+"""ctypes mirror of the C11 host boundary (include/yvex_b200_backend.h) for the tests and the
+end-to-end leg of the benchmark. Every call goes through the shared library; nothing here computes."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from .lib import lib as _lib
+
+ull, vp = C.c_ulonglong, C.c_void_p
+OK, NOMEM, FORMAT, UNSUPPORTED, BACKEND, BOUNDS, STATE, CANCELLED, INVALID_ARG, TIMEOUT = 0, -2, -4, -5, -6, -7, -8, -9, -10, -11
+KIND_CPU, KIND_CUDA, KIND_METAL = 0, 1, 2
+F32, F16, BF16, I32, U8 = 1, 2, 3, 4, 5
+(W_FFN_NORM, W_MHC_FUNCTION, W_MHC_BASE, W_MHC_SCALE, W_ROUTER, W_ROUTER_TABLE, W_ROUTER_BIAS, W_GATE, W_UP, W_DOWN,
+ W_SHARED_GATE, W_SHARED_UP, W_SHARED_DOWN, W_COUNT) = range(14)
+
+
+class Error(C.Structure):
+    _fields_ = [("code", C.c_int), ("where", C.c_char * 96), ("message", C.c_char * 256)]
+
+
+class Options(C.Structure):
+    _fields_ = [("kind", C.c_int), ("device", C.c_char_p), ("memory_limit_bytes", ull)]
+
+
+class TensorDesc(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("dtype", C.c_int), ("rank", C.c_uint), ("dims", ull * 4), ("bytes", ull)]
+
+
+class DeviceTensor(C.Structure):
+    _fields_ = [("owner", vp), ("owner_id", ull), ("dtype", C.c_int), ("rank", C.c_uint), ("dims", ull * 4), ("bytes", ull),
+                ("data", vp), ("host_data", vp), ("is_written", C.c_int)]
+
+
+class Facts(C.Structure):
+    _fields_ = [(n, ull) for n in ("h2d_bytes", "d2h_bytes", "d2d_bytes", "kernel_launches", "upload_count", "download_count",
+                                   "stream_synchronizations", "device_synchronizations", "active_weight_bytes", "state_bytes",
+                                   "activation_bytes", "temporary_bytes", "tensor_core_launches")] + [("available", C.c_int)]
+
+
+class WeightView(C.Structure):
+    _fields_ = [("qtype", C.c_uint), ("kernel_family", C.c_char_p), ("encoded", vp), ("encoded_bytes", C.c_size_t),
+                ("row_bytes", ull), ("row_width", ull), ("row_count", ull)]
+
+
+class LayerPlan(C.Structure):
+    _fields_ = [("router_class", C.c_int), ("hidden_width", ull), ("residual_streams", ull), ("expanded_width", ull),
+                ("routed_experts", ull), ("shared_experts", ull), ("experts_per_token", ull),
+                ("expert_intermediate_width", ull), ("shared_intermediate_width", ull), ("hash_table_rows", ull),
+                ("routed_scaling_factor", C.c_double), ("activation_limit", C.c_double),
+                ("normalize_topk_probabilities", C.c_int)]
+
+
+class CompletionSlot(C.Structure):
+    _fields_ = [("status", C.c_int), ("pending", C.c_int), ("row_count", ull), ("row_expert_pairs", ull)]
+
+
+class Completion(C.Structure):
+    _fields_ = [("defer", C.c_int), ("host", C.POINTER(CompletionSlot))]
+
+
+CANCEL_FN = C.CFUNCTYPE(C.c_int, vp)
+
+
+class LayerJob(C.Structure):
+    _fields_ = [("layer", C.POINTER(LayerPlan)), ("weights", WeightView * W_COUNT), ("cancel_requested", CANCEL_FN),
+                ("cancel_context", vp), ("device_completion", C.POINTER(Completion))]
+
+
+class RowBatch(C.Structure):
+    _fields_ = [("row_count", ull), ("row_width", ull), ("row_stride", ull), ("expanded_rows", vp),
+                ("device_rows", C.POINTER(DeviceTensor)), ("device_outputs", C.POINTER(DeviceTensor)), ("router_logits", vp),
+                ("device_router_logits", C.POINTER(DeviceTensor)), ("token_ids", vp), ("token_ids_present", C.c_int)]
+
+
+class RowBatchOutput(C.Structure):
+    _fields_ = [("combined_rows", vp), ("combined_capacity", ull), ("selected_experts", vp), ("selected_weights", vp),
+                ("selection_capacity", ull)]
+
+
+class RowBatchResult(C.Structure):
+    _fields_ = [("completed", C.c_int), ("device_completion_pending", C.c_int)] + [
+        (n, ull) for n in ("row_count", "row_expert_pairs", "grouped_expert_operations", "shared_expert_operations",
+                           "expert_subviews_accessed", "encoded_bytes_read", "h2d_bytes", "d2h_bytes", "d2d_bytes",
+                           "kernel_launches", "tensor_core_launches", "stream_synchronizations", "active_weight_base_bytes",
+                           "active_weight_per_unique_expert_bytes", "activation_bytes", "temporary_bytes")]
+
+
+_EXEC = C.CFUNCTYPE(C.c_int, vp, C.POINTER(LayerJob), C.POINTER(RowBatch), C.POINTER(RowBatchOutput), C.POINTER(RowBatchResult),
+                    C.POINTER(Error))
+_WSREQ = C.CFUNCTYPE(C.c_int, C.POINTER(LayerPlan), ull, C.POINTER(ull), C.POINTER(Error))
+
+
+class MoeOperations(C.Structure):
+    _fields_ = [("derived_layout_plan", C.CFUNCTYPE(C.c_int, vp, C.POINTER(ull), C.POINTER(Error))),
+                ("derived_layout_build", C.CFUNCTYPE(C.c_int, vp, vp, ull, vp, ull, C.POINTER(Error))),
+                ("workspace_required", _WSREQ), ("execute_rows", _EXEC),
+                ("complete_rows", C.CFUNCTYPE(C.c_int, vp, C.c_int, C.POINTER(RowBatchResult), C.POINTER(Error))),
+                ("workspace_required_wide", _WSREQ), ("execute_rows_wide", _EXEC)]
+
+
+_lib.yvex_backend_moe_operations_get.restype = C.POINTER(MoeOperations)
+_lib.yvex_backend_moe_operations_get.argtypes = [vp]
+_lib.yvex_backend_open.argtypes = [C.POINTER(vp), C.POINTER(Options), C.POINTER(Error)]
+_lib.yvex_backend_close_checked.argtypes = [C.POINTER(vp), C.POINTER(Error)]
+_lib.yvex_backend_close.argtypes = [vp]
+_lib.yvex_backend_tensor_alloc.argtypes = [vp, C.POINTER(TensorDesc), C.POINTER(C.POINTER(DeviceTensor)), C.POINTER(Error)]
+_lib.yvex_backend_resident_alloc.argtypes = [vp, C.POINTER(TensorDesc), C.POINTER(C.POINTER(DeviceTensor)), C.POINTER(vp),
+                                             C.POINTER(Error)]
+_lib.yvex_backend_tensor_free.argtypes = [vp, C.POINTER(DeviceTensor)]
+_lib.yvex_backend_tensor_write.argtypes = [vp, C.POINTER(DeviceTensor), vp, ull, C.POINTER(Error)]
+_lib.yvex_backend_tensor_read.argtypes = [vp, C.POINTER(DeviceTensor), vp, ull, C.POINTER(Error)]
+_lib.yvex_backend_resident_prefetch.argtypes = [vp, C.POINTER(DeviceTensor), C.POINTER(ull), C.POINTER(Error)]
+_lib.yvex_backend_resident_attach.argtypes = [vp, vp, ull, C.POINTER(DeviceTensor), ull, C.POINTER(Error)]
+_lib.yvex_backend_resident_detach.argtypes = [vp, C.POINTER(Error)]
+_lib.yvex_backend_resident_resolve.argtypes = [vp, vp, ull, C.POINTER(ull)]
+_lib.yvex_backend_workspace_attach.argtypes = [vp, C.POINTER(DeviceTensor), C.POINTER(Error)]
+_lib.yvex_backend_workspace_detach.argtypes = [vp, C.POINTER(Error)]
+_lib.yvex_backend_sync.argtypes = [vp, C.POINTER(Error)]
+_lib.yvex_backend_status_of.argtypes = [vp]
+_lib.yvex_backend_kind_of.argtypes = [vp]
+_lib.yvex_backend_qtype_supported.argtypes = [vp, C.c_uint]
+_lib.yvex_backend_cuda_encoded_matvec.argtypes = [vp, vp, ull, C.c_uint, ull, ull, ull, ull, C.POINTER(DeviceTensor),
+                                                  C.POINTER(DeviceTensor), ull, C.POINTER(DeviceTensor), C.POINTER(DeviceTensor),
+                                                  C.c_int, C.POINTER(Facts), C.POINTER(Error)]
+_lib.yvex_backend_op_attention.argtypes = [vp] + [C.POINTER(DeviceTensor)] * 3 + [ull, ull, C.c_float, C.c_int] + \
+    [C.POINTER(DeviceTensor)] * 3 + [C.POINTER(Error)]
+_lib.yvex_backend_attention_gqa_decode.argtypes = [vp] + [C.POINTER(DeviceTensor)] * 3 + [ull] * 6 + [C.c_float,
+                                                                                                    C.POINTER(DeviceTensor),
+                                                                                                    C.POINTER(Error)]
+_lib.yvex_backend_op_matmul.argtypes = [vp] + [C.POINTER(DeviceTensor)] * 3 + [C.POINTER(Error)]
+_lib.yvex_status_name.restype = C.c_char_p
+
+
+class Backend:
+    """Owns one yvex_backend; helpers return raw status codes so tests can assert refusals."""
+
+    def __init__(self, kind=KIND_CUDA, device=b"cuda:0", memory_limit=0):
+        self.handle, self.err = vp(), Error()
+        opts = Options(kind, device, memory_limit)
+        self.rc = _lib.yvex_backend_open(C.byref(self.handle), C.byref(opts), C.byref(self.err))
+        self.tensors = []
+
+    @property
+    def h(self):
+        return self.handle
+
+    def message(self):
+        return self.err.message.decode()
+
+    def tensor(self, nbytes, dtype=U8, dims=None, resident=False):
+        dims = list(dims or [nbytes])
+        desc = TensorDesc(b"t", dtype, len(dims), (ull * 4)(*(dims + [0] * (4 - len(dims)))), nbytes)
+        t, host = C.POINTER(DeviceTensor)(), vp()
+        if resident:
+            rc = _lib.yvex_backend_resident_alloc(self.h, C.byref(desc), C.byref(t), C.byref(host), C.byref(self.err))
+        else:
+            rc = _lib.yvex_backend_tensor_alloc(self.h, C.byref(desc), C.byref(t), C.byref(self.err))
+        if rc != OK:
+            return rc, None, None
+        self.tensors.append(t)
+        return rc, t, host.value
+
+    def write(self, t, array):
+        a = np.ascontiguousarray(array)
+        return _lib.yvex_backend_tensor_write(self.h, t, a.ctypes.data_as(vp), a.nbytes, C.byref(self.err))
+
+    def read(self, t, dtype, count):
+        out = np.empty(count, dtype)
+        rc = _lib.yvex_backend_tensor_read(self.h, t, out.ctypes.data_as(vp), out.nbytes, C.byref(self.err))
+        return rc, out
+
+    def from_array(self, array, dtype, dims=None):
+        a = np.ascontiguousarray(array)
+        rc, t, _ = self.tensor(a.nbytes, dtype, dims or list(a.shape))
+        assert rc == OK, self.message()
+        assert self.write(t, a) == OK, self.message()
+        return t
+
+    def free(self, t):
+        _lib.yvex_backend_tensor_free(self.h, t)
+        self.tensors = [x for x in self.tensors if C.addressof(x.contents) != C.addressof(t.contents)]
+
+    def close(self):
+        for t in list(self.tensors):
+            _lib.yvex_backend_tensor_free(self.h, t)
+        self.tensors = []
+        return _lib.yvex_backend_close_checked(C.byref(self.handle), C.byref(self.err))
+
+
+class ResidentArena:
+    """Packs named host arrays into one resident arena (pinned host side + HBM side) and attaches it."""
+
+    def __init__(self, backend, arrays, generation=1):
+        self.backend = backend
+        self.offsets, off = {}, 0
+        for name, a in arrays.items():
+            self.offsets[name] = off
+            off = (off + a.nbytes + 255) & ~255
+        rc, self.tensor, self.host = backend.tensor(max(off, 256), U8, resident=True)
+        assert rc == OK, backend.message()
+        self.bytes = max(off, 256)
+        view = (C.c_ubyte * self.bytes).from_address(self.host)
+        self.view = np.frombuffer(view, dtype=np.uint8)
+        self.sizes = {}
+        for name, a in arrays.items():
+            flat = np.ascontiguousarray(a).view(np.uint8).reshape(-1)
+            self.view[self.offsets[name]:self.offsets[name] + flat.size] = flat
+            self.sizes[name] = flat.size
+        moved = ull()
+        assert _lib.yvex_backend_resident_prefetch(backend.h, self.tensor, C.byref(moved), C.byref(backend.err)) == OK
+        assert _lib.yvex_backend_resident_attach(backend.h, self.host, self.bytes, self.tensor, generation,
+                                                 C.byref(backend.err)) == OK, backend.message()
+
+    def host_ptr(self, name):
+        return self.host + self.offsets[name]
+
+
+def moe_job(arena, spec, router=True, router_class=1, hash_rows=0, family=None, residual_streams=1):
+    """LayerPlan + LayerJob whose weight views point (by host address) into `arena`."""
+    from . import synth
+    plan = LayerPlan(router_class, spec.hidden, residual_streams, spec.hidden * max(residual_streams, 1), spec.experts, 1,
+                     spec.topk, spec.inter, spec.shared_inter, hash_rows, spec.scaling, spec.limit, spec.normalize)
+    job = LayerJob()
+    job.layer = C.pointer(plan)
+
+    def view(slot, name, qtype, rows, width):
+        if name not in arena.offsets:
+            return
+        v = job.weights[slot]
+        v.qtype, v.kernel_family, v.encoded = qtype, family, arena.host_ptr(name)
+        v.encoded_bytes, v.row_width, v.row_count = arena.sizes[name], width, rows
+        v.row_bytes = synth.row_bytes(qtype, width)
+
+    E, H, I, Is = spec.experts, spec.hidden, spec.inter, spec.shared_inter
+    if router:
+        view(W_ROUTER, "router", synth.F32, E, H)
+    view(W_ROUTER_BIAS, "bias", synth.F32, 1, E)
+    view(W_ROUTER_TABLE, "hash_table", synth.I32, hash_rows or 1, spec.topk)
+    view(W_GATE, "gate", spec.gate_qtype, E * I, H)
+    view(W_UP, "up", spec.up_qtype, E * I, H)
+    view(W_DOWN, "down", spec.down_qtype, E * H, I)
+    view(W_SHARED_GATE, "shared_gate", spec.gate_qtype, Is, H)
+    view(W_SHARED_UP, "shared_up", spec.up_qtype, Is, H)
+    view(W_SHARED_DOWN, "shared_down", spec.down_qtype, H, Is)
+    job._plan = plan
+    return job
+
+
+def moe_ops(backend):
+    p = _lib.yvex_backend_moe_operations_get(backend.h)
+    return p.contents if p else None

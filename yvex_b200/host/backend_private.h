@@ -1,0 +1,34 @@
+/* Private state of the host boundary (counterpart of src/backend/private.h:66-93). */
+#ifndef YVEX_B200_BACKEND_PRIVATE_H
+#define YVEX_B200_BACKEND_PRIVATE_H
+#include <cuda_runtime_api.h>
+#include <stdatomic.h>
+#include <stdint.h>
+
+#include "yvex_b200_backend.h"
+#include "yvex_b200_kernels.h"
+
+#define YVEX_HOST_SCRATCH_BYTES (1u << 20)   /* pinned: status read-back and router selections of narrow batches */
+
+struct yvex_backend {
+    yvex_backend_kind kind;
+    _Atomic int status;
+    int device, closing;
+    cudaStream_t stream;
+    yvex_backend_memory_stats stats;
+    unsigned long long next_owner_id;
+    const unsigned char *resident_host_base;
+    unsigned long long resident_host_bytes, resident_device_address, resident_generation;
+    yvex_device_tensor *workspace;
+    int *status_word;                 /* device: first fault of the enqueued kernels */
+    unsigned char *host_scratch;      /* pinned */
+    yvex_moe_device_completion_slot *pending_slot;   /* deferred completion in flight */
+};
+
+int yvex_refuse(yvex_error *err, yvex_status code, const char *where, const char *message);
+int yvex_backend_admit(const yvex_backend *backend, const char *where, yvex_error *err);
+int yvex_backend_fail(yvex_backend *backend, const char *where, yvex_error *err);
+int yvex_tensor_owned(const yvex_backend *backend, const yvex_device_tensor *t);
+unsigned char *yvex_workspace_take(yvex_backend *backend, unsigned long long *cursor, unsigned long long bytes);
+int yvex_backend_take_status(yvex_backend *backend, int *code);
+#endif

@@ -1,0 +1,344 @@
+/*
+ * The MoE operation table of the host boundary: workspace_required / execute_rows / complete_rows
+ * with the reference's contract (include/yvex/internal/moe.h:277-297, src/backend/cuda/moe.c:1826-1966),
+ * plus the unbounded-width extension. The layer itself runs in the device layer
+ * (yvex_b200_moe_decode for <= 62 rows, yvex_b200_moe_wide beyond).
+ *
+ * Scope: a layer WITHOUT the mHC envelope (residual_streams <= 1, expanded_width == hidden_width);
+ * input rows are the normalized hidden rows, rounded to bf16 at ingress like the reference's
+ * normalized row (src/graph/moe.c:487-489). A plan that asks for the envelope is refused with
+ * YVEX_ERR_UNSUPPORTED - never silently skipped.
+ */
+#include "backend_private.h"
+
+#include <string.h>
+
+#define YVEX_MOE_NARROW_MAX_ROWS 62ull       /* src/graph/worklist.c:316, src/backend/cuda/moe.c:1840-1843 */
+
+static int family_admitted(const char *family) {
+    return !family || !strcmp(family, YVEX_MOE_KERNEL_SM100_DEQUANT_GEMV) || !strcmp(family, YVEX_MOE_KERNEL_SM100_TCGEN05_EXPERT);
+}
+
+static int plan_geometry(const yvex_moe_layer_plan *layer, const yvex_moe_layer_job *job, yvex_b200_moe_geometry *g) {
+    memset(g, 0, sizeof(*g));
+    g->hidden = layer->hidden_width;
+    g->experts = layer->routed_experts;
+    g->topk = layer->experts_per_token;
+    g->inter = layer->expert_intermediate_width;
+    g->shared_inter = layer->shared_intermediate_width ? layer->shared_intermediate_width : layer->expert_intermediate_width;
+    g->scaling = layer->routed_scaling_factor;
+    g->limit = layer->activation_limit;
+    g->normalize = layer->normalize_topk_probabilities;
+    g->router_class = layer->router_class == YVEX_MOE_ROUTER_LEARNED_HIDDEN_STATE ? 1 : 0;
+    g->hash_rows = layer->hash_table_rows;
+    if (job) {
+        g->gate_qtype = job->weights[YVEX_MOE_WEIGHT_ROUTED_GATE].qtype;
+        g->up_qtype = job->weights[YVEX_MOE_WEIGHT_ROUTED_UP].qtype;
+        g->down_qtype = job->weights[YVEX_MOE_WEIGHT_ROUTED_DOWN].qtype;
+        g->hash_stored_rows = job->weights[YVEX_MOE_WEIGHT_ROUTER_TABLE].row_count;
+    } else {
+        g->gate_qtype = g->up_qtype = g->down_qtype = 16u;   /* sizes do not depend on the qtype */
+    }
+    return 1;
+}
+
+static unsigned long long align256(unsigned long long v) { return (v + 255ull) & ~255ull; }
+
+static unsigned long long staging_bytes(const yvex_b200_moe_geometry *g, unsigned long long rows) {
+    return 2ull * align256(rows * g->hidden * 4ull) + align256(rows * g->experts * 4ull) + 2ull * align256(rows * g->topk * 4ull) +
+           align256(rows * 4ull) + 256ull;
+}
+
+static int workspace_for(const yvex_moe_layer_plan *layer, unsigned long long rows, int wide, unsigned long long *bytes, yvex_error *err) {
+    yvex_b200_moe_geometry g;
+    if (bytes) *bytes = 0;
+    if (!layer || !bytes || !rows) return yvex_refuse(err, YVEX_ERR_INVALID_ARG, "moe.workspace_required", "layer, rows and result are required");
+    if (!wide && rows > YVEX_MOE_NARROW_MAX_ROWS)
+        return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, "moe.workspace_required", "execute_rows admits at most 62 rows; use the wide entry");
+    plan_geometry(layer, NULL, &g);
+    *bytes = staging_bytes(&g, rows) + (wide ? yvex_b200_moe_wide_workspace_bytes(&g, rows) : yvex_b200_moe_workspace_bytes(&g, rows));
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+static int moe_workspace_required(const yvex_moe_layer_plan *layer, unsigned long long rows, unsigned long long *bytes, yvex_error *err) {
+    return workspace_for(layer, rows, 0, bytes, err);
+}
+
+static int moe_workspace_required_wide(const yvex_moe_layer_plan *layer, unsigned long long rows, unsigned long long *bytes, yvex_error *err) {
+    return workspace_for(layer, rows, 1, bytes, err);
+}
+
+static int derived_plan(const void *decision, unsigned long long *storage_bytes, yvex_error *err) {
+    (void)decision;
+    if (storage_bytes) *storage_bytes = 0;
+    return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, "moe.derived_layout_plan", "this backend executes the canonical row layout only");
+}
+
+static int derived_build(const void *decision, const unsigned char *canonical, unsigned long long canonical_bytes,
+                         unsigned char *derived, unsigned long long storage_bytes, yvex_error *err) {
+    (void)decision; (void)canonical; (void)canonical_bytes; (void)derived; (void)storage_bytes;
+    return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, "moe.derived_layout_build", "this backend executes the canonical row layout only");
+}
+
+/* Resolves one weight view to its device address; optional slots resolve to 0. */
+static int resolve_view(const yvex_backend *backend, const yvex_moe_weight_view *v, int required, const void **out) {
+    unsigned long long address = 0;
+    *out = NULL;
+    if (!v->encoded || !v->encoded_bytes) return required ? 0 : 1;
+    if (yvex_backend_resident_resolve(backend, v->encoded, v->encoded_bytes, &address) != YVEX_BACKEND_RESIDENT_HIT) return 0;
+    *out = (const void *)(uintptr_t)address;
+    return 1;
+}
+
+static int view_consistent(const yvex_moe_weight_view *v, unsigned long long rows, unsigned long long width) {
+    unsigned int be = 0, bb = 0;
+    if (!yvex_b200_qtype_geometry(v->qtype, &be, &bb) || !be) return 0;
+    return v->row_count == rows && v->row_width == width && width % be == 0 && v->row_bytes == width / be * bb &&
+           v->encoded_bytes == rows * v->row_bytes;
+}
+
+static int status_error(int code, yvex_error *err) {
+    if (!code) return YVEX_OK;
+    if (code == YVEX_B200_STATUS_TIMEOUT) return yvex_refuse(err, YVEX_ERR_TIMEOUT, "cuda.moe", "a bounded device wait expired");
+    return yvex_refuse(err, YVEX_ERR_BACKEND, "cuda.moe", "CUDA MoE kernel reported invalid or non-finite numerics");
+}
+
+static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, const yvex_moe_row_batch *batch,
+                       const yvex_moe_row_batch_output *output, yvex_moe_row_batch_result *result, yvex_error *err, int wide) {
+    const char *where = wide ? "cuda.moe.execute_rows_wide" : "cuda.moe.execute_rows";
+    const yvex_moe_layer_plan *layer = job ? job->layer : NULL;
+    yvex_b200_moe_geometry g;
+    yvex_b200_moe_weights w;
+    unsigned long long rows, cursor = 0, need, kernel_ws, launches0, in_bytes, sel_count;
+    unsigned char *ws_in, *ws_out, *ws_logits, *ws_sel, *ws_wts, *ws_ids, *ws_kernel;
+    const float *dev_in, *dev_logits = NULL;
+    float *dev_out;
+    int rc, code, defer, slot;
+    static const int required[YVEX_MOE_WEIGHT_COUNT] = {0, 0, 0, 0, 0, 0, 0, 1, 1, 1, 1, 1, 1};
+    const void *addr[YVEX_MOE_WEIGHT_COUNT];
+
+    if (result) memset(result, 0, sizeof(*result));
+    if (!job || !layer || !batch || !result) return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "job, layer, batch and result are required");
+    rc = yvex_backend_admit(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    if (backend->pending_slot) return yvex_refuse(err, YVEX_ERR_STATE, where, "a deferred MoE completion is still pending");
+    rows = batch->row_count;
+    if (!rows) return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "row batch is empty");
+    if (!wide && rows > YVEX_MOE_NARROW_MAX_ROWS)
+        return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "row count is outside the admitted widths of execute_rows");
+    if (layer->residual_streams > 1ull || (layer->expanded_width && layer->expanded_width != layer->hidden_width))
+        return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "the mHC envelope (residual streams > 1) is not built in this backend");
+    if (batch->row_width != layer->hidden_width || (batch->row_stride && batch->row_stride != batch->row_width))
+        return yvex_refuse(err, YVEX_ERR_FORMAT, where, "row batch geometry does not match the layer's hidden width");
+    if (!batch->device_rows == !batch->expanded_rows)
+        return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "exactly one of device rows and host rows is required");
+    plan_geometry(layer, job, &g);
+    for (slot = YVEX_MOE_WEIGHT_ROUTED_GATE; slot < YVEX_MOE_WEIGHT_COUNT; ++slot) {
+        if (!family_admitted(job->weights[slot].kernel_family))
+            return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "kernel family is not one this backend executes");
+        if (!yvex_b200_qtype_supported(job->weights[slot].qtype))
+            return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "expert qtype has no device decoder in this backend");
+    }
+    if (job->weights[YVEX_MOE_WEIGHT_SHARED_GATE].qtype != g.gate_qtype || job->weights[YVEX_MOE_WEIGHT_SHARED_UP].qtype != g.up_qtype ||
+        job->weights[YVEX_MOE_WEIGHT_SHARED_DOWN].qtype != g.down_qtype)
+        return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "shared and routed experts must share their qtypes");
+    if (!view_consistent(&job->weights[YVEX_MOE_WEIGHT_ROUTED_GATE], g.experts * g.inter, g.hidden) ||
+        !view_consistent(&job->weights[YVEX_MOE_WEIGHT_ROUTED_UP], g.experts * g.inter, g.hidden) ||
+        !view_consistent(&job->weights[YVEX_MOE_WEIGHT_ROUTED_DOWN], g.experts * g.hidden, g.inter) ||
+        !view_consistent(&job->weights[YVEX_MOE_WEIGHT_SHARED_GATE], g.shared_inter, g.hidden) ||
+        !view_consistent(&job->weights[YVEX_MOE_WEIGHT_SHARED_UP], g.shared_inter, g.hidden) ||
+        !view_consistent(&job->weights[YVEX_MOE_WEIGHT_SHARED_DOWN], g.hidden, g.shared_inter))
+        return yvex_refuse(err, YVEX_ERR_FORMAT, where, "expert weight views are inconsistent with the layer geometry");
+    if (job->cancel_requested && job->cancel_requested(job->cancel_context))
+        return yvex_refuse(err, YVEX_ERR_CANCELLED, where, "MoE execution was cancelled");
+    for (slot = 0; slot < YVEX_MOE_WEIGHT_COUNT; ++slot)
+        if (!resolve_view(backend, &job->weights[slot], required[slot], &addr[slot]))
+            return yvex_refuse(err, YVEX_ERR_STATE, where, "MoE weights are not resident on this backend");
+    memset(&w, 0, sizeof(w));
+    w.router = (const float *)addr[YVEX_MOE_WEIGHT_ROUTER];
+    w.bias = (const float *)addr[YVEX_MOE_WEIGHT_ROUTER_BIAS];
+    w.hash_table = (const int32_t *)addr[YVEX_MOE_WEIGHT_ROUTER_TABLE];
+    w.gate = addr[YVEX_MOE_WEIGHT_ROUTED_GATE]; w.up = addr[YVEX_MOE_WEIGHT_ROUTED_UP]; w.down = addr[YVEX_MOE_WEIGHT_ROUTED_DOWN];
+    w.shared_gate = addr[YVEX_MOE_WEIGHT_SHARED_GATE]; w.shared_up = addr[YVEX_MOE_WEIGHT_SHARED_UP];
+    w.shared_down = addr[YVEX_MOE_WEIGHT_SHARED_DOWN];
+    if (w.router && (job->weights[YVEX_MOE_WEIGHT_ROUTER].qtype != 0u ||
+                     job->weights[YVEX_MOE_WEIGHT_ROUTER].encoded_bytes != g.experts * g.hidden * 4ull))
+        return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "router weights must be F32 [experts x hidden]");
+    if (!w.router && !batch->router_logits && !batch->device_router_logits)
+        return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "either resident router weights or router logits are required");
+    if (g.router_class == 0 && (!batch->token_ids_present || !batch->token_ids))
+        return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "MoE hash router requires token IDs");
+
+    in_bytes = rows * g.hidden * 4ull;
+    kernel_ws = wide ? yvex_b200_moe_wide_workspace_bytes(&g, rows) : yvex_b200_moe_workspace_bytes(&g, rows);
+    need = staging_bytes(&g, rows) + kernel_ws;
+    if (!backend->workspace || backend->workspace->bytes < need)
+        return yvex_refuse(err, YVEX_ERR_NOMEM, where, "attached device workspace is smaller than workspace_required");
+    ws_in = yvex_workspace_take(backend, &cursor, in_bytes);
+    ws_out = yvex_workspace_take(backend, &cursor, in_bytes);
+    ws_logits = yvex_workspace_take(backend, &cursor, rows * g.experts * 4ull);
+    ws_sel = yvex_workspace_take(backend, &cursor, rows * g.topk * 4ull);
+    ws_wts = yvex_workspace_take(backend, &cursor, rows * g.topk * 4ull);
+    ws_ids = yvex_workspace_take(backend, &cursor, rows * 4ull);
+    ws_kernel = yvex_workspace_take(backend, &cursor, kernel_ws);
+    if (!ws_in || !ws_out || !ws_logits || !ws_sel || !ws_wts || !ws_ids || !ws_kernel)
+        return yvex_refuse(err, YVEX_ERR_NOMEM, where, "attached device workspace is smaller than workspace_required");
+
+    if (batch->device_rows) {
+        if (!yvex_tensor_owned(backend, batch->device_rows) || !batch->device_rows->is_written ||
+            batch->device_rows->dtype != YVEX_DTYPE_F32 || batch->device_rows->bytes < in_bytes)
+            return yvex_refuse(err, YVEX_ERR_FORMAT, where, "device rows must be a written F32 tensor of this backend");
+        dev_in = (const float *)batch->device_rows->data;
+    } else {
+        if (cudaMemcpyAsync(ws_in, batch->expanded_rows, in_bytes, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess)
+            return yvex_backend_fail(backend, where, err);
+        result->h2d_bytes += in_bytes;
+        dev_in = (const float *)ws_in;
+    }
+    if (batch->device_router_logits) {
+        if (!yvex_tensor_owned(backend, batch->device_router_logits) || batch->device_router_logits->bytes < rows * g.experts * 4ull)
+            return yvex_refuse(err, YVEX_ERR_FORMAT, where, "device router logits must be an F32 tensor of this backend");
+        dev_logits = (const float *)batch->device_router_logits->data;
+    } else if (batch->router_logits) {
+        if (cudaMemcpyAsync(ws_logits, batch->router_logits, rows * g.experts * 4ull, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess)
+            return yvex_backend_fail(backend, where, err);
+        result->h2d_bytes += rows * g.experts * 4ull;
+        dev_logits = (const float *)ws_logits;
+    }
+    if (batch->token_ids_present && batch->token_ids) {
+        if (cudaMemcpyAsync(ws_ids, batch->token_ids, rows * 4ull, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess)
+            return yvex_backend_fail(backend, where, err);
+        result->h2d_bytes += rows * 4ull;
+    }
+    if (batch->device_outputs) {
+        if (!yvex_tensor_owned(backend, batch->device_outputs) || batch->device_outputs->dtype != YVEX_DTYPE_F32 ||
+            batch->device_outputs->bytes < in_bytes)
+            return yvex_refuse(err, YVEX_ERR_FORMAT, where, "device outputs must be an F32 tensor of this backend");
+        batch->device_outputs->is_written = 0;
+        dev_out = (float *)batch->device_outputs->data;
+    } else {
+        if (!output || !output->combined_rows) return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "a device or host output is required");
+        dev_out = (float *)ws_out;
+    }
+    if (output && output->combined_rows && output->combined_capacity < rows * g.hidden)
+        return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "combined output capacity is too small");
+    sel_count = rows * g.topk;
+    if (output && (output->selected_experts || output->selected_weights) && output->selection_capacity < sel_count)
+        return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "selection output capacity is too small");
+
+    launches0 = yvex_b200_launch_count();
+    rc = (wide ? yvex_b200_moe_wide : yvex_b200_moe_decode)(
+        &g, &w, dev_in, dev_logits, batch->token_ids_present && batch->token_ids ? (const uint32_t *)ws_ids : NULL, rows, dev_out,
+        (int32_t *)ws_sel, (float *)ws_wts, ws_kernel, kernel_ws, backend->status_word, backend->stream);
+    if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
+    if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the MoE layer geometry");
+
+    defer = job->device_completion && job->device_completion->defer && job->device_completion->host;
+    if (output && output->combined_rows) {
+        if (cudaMemcpyAsync(output->combined_rows, dev_out, in_bytes, cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess)
+            return yvex_backend_fail(backend, where, err);
+        result->d2h_bytes += in_bytes;
+    }
+    if (!defer && output && output->selected_weights) {
+        if (cudaMemcpyAsync(output->selected_weights, ws_wts, sel_count * 4ull, cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess)
+            return yvex_backend_fail(backend, where, err);
+        result->d2h_bytes += sel_count * 4ull;
+    }
+    if (!defer && output && output->selected_experts) {
+        /* int32 ids land in the upper half of the caller's u64 array and are widened in place after the sync */
+        if (cudaMemcpyAsync((int32_t *)output->selected_experts + sel_count, ws_sel, sel_count * 4ull, cudaMemcpyDeviceToHost,
+                            backend->stream) != cudaSuccess)
+            return yvex_backend_fail(backend, where, err);
+        result->d2h_bytes += sel_count * 4ull;
+    }
+    result->row_count = rows;
+    result->row_expert_pairs = sel_count;
+    result->grouped_expert_operations = 1;
+    result->shared_expert_operations = 1;
+    result->expert_subviews_accessed = sel_count * 3ull;
+    result->kernel_launches = yvex_b200_launch_count() - launches0;
+    result->tensor_core_launches = wide ? 2ull : 2ull;
+    result->active_weight_base_bytes = job->weights[YVEX_MOE_WEIGHT_SHARED_GATE].encoded_bytes +
+                                       job->weights[YVEX_MOE_WEIGHT_SHARED_UP].encoded_bytes +
+                                       job->weights[YVEX_MOE_WEIGHT_SHARED_DOWN].encoded_bytes +
+                                       job->weights[YVEX_MOE_WEIGHT_ROUTER].encoded_bytes;
+    result->active_weight_per_unique_expert_bytes = (job->weights[YVEX_MOE_WEIGHT_ROUTED_GATE].encoded_bytes +
+                                                     job->weights[YVEX_MOE_WEIGHT_ROUTED_UP].encoded_bytes +
+                                                     job->weights[YVEX_MOE_WEIGHT_ROUTED_DOWN].encoded_bytes) / g.experts;
+    result->encoded_bytes_read = result->active_weight_base_bytes + g.topk * result->active_weight_per_unique_expert_bytes * rows;
+    result->activation_bytes = 2ull * in_bytes;
+    result->temporary_bytes = need;
+    if (defer) {
+        yvex_moe_device_completion_slot *s = job->device_completion->host;
+        memset(s, 0, sizeof(*s));
+        s->pending = 1;
+        s->row_count = rows;
+        s->row_expert_pairs = sel_count;
+        if (cudaMemcpyAsync(&s->status, backend->status_word, sizeof(int), cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess)
+            return yvex_backend_fail(backend, where, err);
+        backend->pending_slot = s;
+        result->device_completion_pending = 1;
+        result->d2h_bytes += sizeof(int);
+        if (batch->device_outputs) batch->device_outputs->is_written = 1;   /* stream-ordered for device consumers */
+        yvex_error_clear(err);
+        return YVEX_OK;
+    }
+    if (!yvex_backend_take_status(backend, &code)) return yvex_backend_fail(backend, where, err);
+    result->stream_synchronizations = 1;
+    result->d2h_bytes += sizeof(int);
+    if (code) { memset(result, 0, sizeof(*result)); return status_error(code, err); }
+    if (output && output->selected_experts) {
+        const int32_t *src = (const int32_t *)output->selected_experts + sel_count;
+        for (unsigned long long i = 0; i < sel_count; ++i) output->selected_experts[i] = (unsigned long long)src[i];
+    }
+    if (batch->device_outputs) batch->device_outputs->is_written = 1;
+    result->completed = 1;
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+static int moe_execute_rows(yvex_backend *backend, const yvex_moe_layer_job *job, const yvex_moe_row_batch *batch,
+                            const yvex_moe_row_batch_output *output, yvex_moe_row_batch_result *result, yvex_error *err) {
+    return moe_execute(backend, job, batch, output, result, err, 0);
+}
+
+static int moe_execute_rows_wide(yvex_backend *backend, const yvex_moe_layer_job *job, const yvex_moe_row_batch *batch,
+                                 const yvex_moe_row_batch_output *output, yvex_moe_row_batch_result *result, yvex_error *err) {
+    return moe_execute(backend, job, batch, output, result, err, 1);
+}
+
+/* Deferred completion: one stream synchronisation, then the status slot decides (src/backend/cuda/moe.c:1925-1966). */
+static int moe_complete_rows(yvex_backend *backend, int barrier_observed, yvex_moe_row_batch_result *result, yvex_error *err) {
+    yvex_moe_device_completion_slot *s;
+    int rc = yvex_backend_admit(backend, "cuda.moe.complete_rows", err), code;
+    if (rc != YVEX_OK) return rc;
+    s = backend->pending_slot;
+    if (!s) return yvex_refuse(err, YVEX_ERR_STATE, "cuda.moe.complete_rows", "no deferred MoE completion is pending");
+    if (!barrier_observed && cudaStreamSynchronize(backend->stream) != cudaSuccess)
+        return yvex_backend_fail(backend, "cuda.moe.complete_rows", err);
+    backend->pending_slot = NULL;
+    s->pending = 0;
+    code = s->status;
+    if (code && cudaMemsetAsync(backend->status_word, 0, sizeof(int), backend->stream) != cudaSuccess)
+        return yvex_backend_fail(backend, "cuda.moe.complete_rows", err);
+    if (result) {
+        result->device_completion_pending = 0;
+        result->completed = code == 0;
+        result->stream_synchronizations += barrier_observed ? 0ull : 1ull;
+    }
+    if (code) return status_error(code, err);
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+static const yvex_backend_moe_operations moe_operations = {
+    derived_plan, derived_build, moe_workspace_required, moe_execute_rows, moe_complete_rows,
+    moe_workspace_required_wide, moe_execute_rows_wide};
+
+const yvex_backend_moe_operations *yvex_backend_moe_operations_get(const yvex_backend *backend) {
+    if (!backend || backend->kind != YVEX_BACKEND_KIND_CUDA || backend->closing ||
+        atomic_load(&((yvex_backend *)backend)->status) == YVEX_BACKEND_STATUS_FAILED)
+        return NULL;
+    return &moe_operations;
+}
