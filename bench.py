@@ -351,16 +351,45 @@ def run_native_ep(args):
         dev_lg.copy_(host_lg, non_blocking=True)
         host_out.copy_(layer.forward(dev_x, dev_lg)[0], non_blocking=True)
 
+    e2e_api = "ExpertParallelLayer.forward (C-ABI device layer + NCCL), pinned host rows in/out"
+    if world == 1:
+        # One GPU: the end-to-end leg goes through the C11 host boundary itself - resident weights
+        # named by host pointers, host rows in, host rows out, one synchronous execute_rows_wide.
+        from yvex_b200 import backend as B
+        be = B.Backend(device=f"cuda:{local}".encode())
+        if be.rc != B.OK:
+            raise RuntimeError("host boundary failed to open: " + be.message())
+        arena = B.ResidentArena(be, {k: v.cpu().numpy() for k, v in wl.tensors.items()})
+        job = B.moe_job(arena, spec, router=False, family=b"sm100-f16-tcgen05-expert")
+        bops, need = B.moe_ops(be), B.ull()
+        assert bops.workspace_required_wide(job.layer, T, C.byref(need), C.byref(be.err)) == B.OK
+        rcw, bws, _ = be.tensor(need.value)
+        assert rcw == B.OK and B._lib.yvex_backend_workspace_attach(be.h, bws, C.byref(be.err)) == B.OK
+        batch = B.RowBatch(T, H, H, host_x.data_ptr(), None, None, host_lg.data_ptr(), None, None, 0)
+        bout = B.RowBatchOutput(host_out.data_ptr(), T * H, None, None, 0)
+        bres = B.RowBatchResult()
+        e2e_api = "yvex_backend_moe_operations.execute_rows_wide (C11 host boundary), pinned host rows in/out"
+
+        def step_e2e(i):  # noqa: F811
+            rc_b = bops.execute_rows_wide(be.h, C.byref(job), C.byref(batch), C.byref(bout), C.byref(bres), C.byref(be.err))
+            if rc_b != B.OK:
+                raise RuntimeError("execute_rows_wide: " + be.message())
+
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, steps, wall=False):
         out = []
         for i in range(steps):
             flush.fill_(i & 0xFF)
             barrier()
+            if wall:                       # the boundary call synchronises its own stream before it returns
+                t0 = time.perf_counter()
+                fn(i)
+                out.append((time.perf_counter() - t0) * 1e3)
+                continue
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             fn(i)
@@ -377,7 +406,7 @@ def run_native_ep(args):
     with ClockSampler(local) as clocks:
         ms = timed(step, args.steps)
         launches = lib.lib.yvex_b200_launch_count() - launches0
-        ms_e2e = timed(step_e2e, args.steps)
+        ms_e2e = timed(step_e2e, args.steps, wall=world == 1)
         # GEMM phases of the routed pair list, timed with the library's phase events
         n_ph, gemm_ms, pair_counts = 6, [[], []], []
         real_rows = ops.expert_rows
@@ -445,7 +474,7 @@ def run_native_ep(args):
                            "parallelism": f"ep{world}: {e_loc} experts and {t_loc} tokens per rank, NCCL all-to-all-v"},
                 "clocks": clocks.summary(),
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(T * (H + E) * 4),
-                        "d2h_bytes_per_step": int(T * H * 4)},
+                        "d2h_bytes_per_step": int(T * H * 4), "api": e2e_api},
                 "gpu_launches": int(launches * world),
                 "phases_ms": {"gate_up_gemm": gu, "swiglu_down_gemm": dn},
                 "roofline": roofline, "cpu_baseline": cpu}

@@ -8,16 +8,22 @@
 // Q4_K / Q2_K: code * sub-scale), the B operand the fp16 image of bf16-exact activations, so
 // every product is exact and only the f32 accumulation in TMEM rounds. The per-superblock f16
 // scale d cannot ride inside the MMA; the accumulator is therefore drained once per 256 K by the
-// epilogue warps (acc[row][n] += d[row][block] * tmem[row][n]) while the MMA warp fills the other
-// TMEM buffer. Affine qtypes add one more K=16/32 MMA per superblock: A' = integer mins,
+// epilogue warps (acc[row][n] += d[row][block] * tmem[row][n]) while the other TMEM buffer is
+// being filled. Affine qtypes add one more K=16/32 MMA per superblock: A' = integer mins,
 // B' = per-sub-block activation sums (hi/lo fp16 split), drained as acc -= dmin * tmem'.
 //
 // CTA = 20 warps, persistent over a device-built tile list:
 //   warp 0      TMA producer: activation tiles [N x 64] fp16, 128-byte swizzle, mbarrier tx
-//   warp 1      MMA issuer (one elected lane): 4 x tcgen05.mma (K=16) per 64-K chunk
-//   warps 2-3   min-term tiles (A' from the packed scale bytes, B' from the sums array)
-//   warps 4-11  dequant producers: thread = (weight row, half of a 64-K chunk); decode 32 weights
-//               to fp16 and store four 16-byte chunks into the swizzled A tile
+//   warps 1-2   MMA issuers (one elected lane each, alternating superblocks / TMEM buffers):
+//               4 x tcgen05.mma (K=16) per 64-K chunk
+//   warp 3      B' tiles of the min term (copies the activation sums into the swizzled tile)
+//   warps 4-11  dequant producers. Each warp owns 16 weight rows of the tile. It copies the raw
+//               superblock bytes of its rows global -> registers -> shared with lanes running
+//               along a row (coalesced: every load instruction touches two or three lines; a
+//               thread-per-row load touches 32 and saturates the L1 data pipe), one superblock
+//               ahead of the decode; then thread = (row, half of a 64-K chunk) decodes 32 weights
+//               to fp16 and stores four 16-byte chunks into the swizzled A tile. The same warps
+//               write the A' rows and the per-row block scales for the epilogue.
 //   warps 12-19 epilogue: TMEM -> registers (tcgen05.ld), scale, accumulate, final store
 // Every mbarrier wait is bounded; on expiry the CTA sets status 3, unwinds and frees its TMEM.
 #pragma once
@@ -29,9 +35,11 @@ namespace yb {
 
 constexpr int kGemmThreads = 640;
 constexpr int kTileM = 128, kTileN = 128, kChunkK = 64;
-constexpr int kStages = 4;                                  // ring of {A, B} 64-K chunks
+constexpr int kStages = 4;                                  // {A, B} 64-K chunk stages: two rings of two
 constexpr uint32_t kTileBytes = kTileM * kChunkK * 2;        // 16 KiB, both A and B chunks
 constexpr uint32_t kTmemCols = 512;
+constexpr int kProducerWarps = 8, kRowsPerWarp = kTileM / kProducerWarps;
+constexpr int kScaleRing = 4;                               // superblocks of per-row scales kept for the epilogue
 
 struct ColBlock { int row0, ncols, expert, pad; };          // expert < 0: the shared expert
 
@@ -48,13 +56,27 @@ struct GemmParams {
 };
 
 struct GemmSmem {
-    uint64_t full_a[kStages], full_b[kStages], empty[kStages];
+    uint64_t full[kStages], empty[kStages];
     uint64_t acc_full[2], acc_empty[2], min_full[2], min_empty[2];
     uint32_t tmem_base;
     int abort;
 };
 
-// ---- per-qtype chunk decoders: 32 weights (row, k = 64*c + 32*h ..) -> four 16-byte fp16 chunks ----
+// Chunk `it` (four per superblock, counted over the CTA's whole tile sequence) -> stage and phase.
+// Even superblocks cycle through stages 0-1, odd ones through stages 2-3, so each MMA issuer
+// only ever waits on stages whose fills it consumes itself, in order. (With one shared ring an
+// issuer that skips the other's superblock could test a barrier that is still a whole phase
+// behind, and a parity wait cannot tell "one phase behind" from "done".)
+__device__ __forceinline__ uint32_t stage_of(uint32_t it) { return ((it >> 1) & 2u) | (it & 1u); }
+__device__ __forceinline__ uint32_t phase_of(uint32_t it) { return (it >> 1) & 1u; }     // fills per stage: 2 per own superblock
+
+// ---- per-qtype decoders -----------------------------------------------------------------------------
+// A decoder sees one superblock of one weight row as kRawWords 32-bit words in shared memory,
+// copied from the 4-byte aligned address at or below the block (`mis` = bytes skipped, 0 or 2).
+//   load_word  one word of that run from global memory (the caller spreads words over lanes)
+//   store      32 weights (k = 64*c + 32*h ..) -> four 16-byte fp16 chunks of the A tile row
+//   scales     {d, dmin} of the block, and whether they are acceptable
+//   mins       this thread's share of the A' row (affine qtypes)
 __device__ __forceinline__ void store_scaled8(uint8_t *tile, uint32_t row, uint32_t chunk, uint32_t bytes_lo,
                                               uint32_t bytes_hi, __half2 sc2, __half2 nb2) {
     uint32_t a = __byte_perm(bytes_lo, 0x64646464u, 0x4140), b = __byte_perm(bytes_lo, 0x64646464u, 0x4342);
@@ -66,15 +88,29 @@ __device__ __forceinline__ void store_scaled8(uint8_t *tile, uint32_t row, uint3
     *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, chunk)) = v;
 }
 
-__device__ __forceinline__ __half2 half2_of(float v) { return __float2half2_rn(v); }
+__device__ __forceinline__ float2 checked_scales(uint32_t d_bits, uint32_t dmin_bits, float d_mul, bool &bad) {
+    const float d = f16_bits_to_float((uint16_t)d_bits), dmin = f16_bits_to_float((uint16_t)dmin_bits);
+    bad = !isfinite(d) || !isfinite(dmin) || d < 0.0f || dmin < 0.0f;
+    return make_float2(d * d_mul, dmin);
+}
 
 struct GemmIq2 {
-    static constexpr int kBlockBytes = 66, kMinSlots = 0;
+    static constexpr int kBlockBytes = 66, kMinSlots = 0, kRawWords = 17;     // 66 bytes from a 2-byte aligned start
     static constexpr float kBias = 1152.0f;
-    // blk: the row's superblock in global memory (2-byte aligned)
-    __device__ static void chunk(const uint8_t *blk, int c, int h, uint8_t *tile, uint32_t row, const MmaTables *tab) {
-        const uint8_t *p = blk + 2 + 8 * (2 * c + h);
-        const uint32_t grids = ld_u32_unaligned2(p), ss = ld_u32_unaligned2(p + 4);
+    __device__ static uint32_t load_word(const uint8_t *blk, int word) {
+        const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(blk) & 3u);
+        const uint8_t *p = blk - mis + 4 * word;
+        // an aligned block ends in the middle of word 16: the upper half lies past the block (and,
+        // for the last row of a pack, past the allocation), so only the lower half is read
+        if (word == 16 && mis == 0) return ldg_u16(p);
+        return __ldg(reinterpret_cast<const uint32_t *>(p));
+    }
+    __device__ static void store(const uint32_t *raw, uint32_t mis, int c, int h, uint8_t *tile, uint32_t row,
+                                 const MmaTables *tab) {
+        const uint32_t o = mis + 2u + 8u * (2 * c + h), sh = 8u * (o & 3u);
+        const uint32_t *w = raw + (o >> 2);
+        const uint32_t w1 = w[1];
+        const uint32_t grids = __funnelshift_r(w[0], w1, sh), ss = __funnelshift_r(w1, w[2], sh);
         const uint2 sc = tab->scale[2u * (ss >> 28) + 1u];
         const __half2 sc2 = *reinterpret_cast<const __half2 *>(&sc.x), nb2 = *reinterpret_cast<const __half2 *>(&sc.y);
         constexpr uint32_t kLo = (8u + 128u) | ((25u + 128u) << 8) | ((43u + 128u) << 16);
@@ -85,29 +121,29 @@ struct GemmIq2 {
             store_scaled8(tile, row, 4 * h + j, __byte_perm(kLo, kHi, sel), __byte_perm(kLo, kHi, sel >> 16), sc2, nb2);
         }
     }
-    __device__ static float scale(const uint8_t *blk, float &dmin, bool &bad) {
-        float d = f16_bits_to_float(ldg_u16(blk));
-        bad = !isfinite(d) || d < 0.0f;
-        dmin = 0.0f;
-        return d * 0.125f;
+    __device__ static float2 scales(const uint32_t *raw, uint32_t mis, bool &bad) {
+        return checked_scales(raw[0] >> (8u * mis), 0u, 0.125f, bad);
     }
-    __device__ static void mins(const uint8_t *, int, uint8_t *, uint32_t) {}
+    __device__ static void mins(const uint32_t *, int, uint8_t *, uint32_t) {}
 };
 
 struct GemmQ4k {
-    static constexpr int kBlockBytes = 144, kMinSlots = 16;       // 8 mins x (hi, lo)
+    static constexpr int kBlockBytes = 144, kMinSlots = 16, kRawWords = 36;    // 8 mins x (hi, lo)
     static constexpr float kBias = 1024.0f;
-    __device__ static void scale_min(const uint8_t *s, int j, uint32_t &sc, uint32_t &m) {
-        if (j < 4) { sc = __ldg(s + j) & 63u; m = __ldg(s + j + 4) & 63u; }
-        else { sc = (__ldg(s + j + 4) & 15u) | ((__ldg(s + j - 4) >> 6) << 4); m = (__ldg(s + j + 4) >> 4) | ((__ldg(s + j) >> 6) << 4); }
+    __device__ static uint32_t load_word(const uint8_t *blk, int word) { return __ldg(reinterpret_cast<const uint32_t *>(blk) + word); }
+    // 6-bit (scale, min) of sub-block j from the 12 packed bytes held as three little-endian words
+    __device__ static void scale_min_words(uint32_t s0, uint32_t s1, uint32_t s2, int j, uint32_t &sc, uint32_t &m) {
+        const uint32_t w[3] = {s0, s1, s2};
+        auto byte = [&](int i) { return (w[i >> 2] >> (8 * (i & 3))) & 255u; };
+        if (j < 4) { sc = byte(j) & 63u; m = byte(j + 4) & 63u; }
+        else { sc = (byte(j + 4) & 15u) | ((byte(j - 4) >> 6) << 4); m = (byte(j + 4) >> 4) | ((byte(j) >> 6) << 4); }
     }
-    __device__ static void chunk(const uint8_t *blk, int c, int h, uint8_t *tile, uint32_t row, const MmaTables *tab) {
+    __device__ static void store(const uint32_t *raw, uint32_t, int c, int h, uint8_t *tile, uint32_t row, const MmaTables *tab) {
         uint32_t sc, m;
-        scale_min(blk + 4, 2 * c + h, sc, m);
+        scale_min_words(raw[1], raw[2], raw[3], 2 * c + h, sc, m);
         const uint2 s = tab->scale[sc];
         const __half2 sc2 = *reinterpret_cast<const __half2 *>(&s.x), nb2 = *reinterpret_cast<const __half2 *>(&s.y);
-        const uint4 *q = reinterpret_cast<const uint4 *>(blk + 16 + 32 * c);
-        const uint4 q0 = __ldg(q), q1 = __ldg(q + 1);
+        const uint4 q0 = *reinterpret_cast<const uint4 *>(raw + 4 + 8 * c), q1 = *reinterpret_cast<const uint4 *>(raw + 8 + 8 * c);
         const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -116,75 +152,92 @@ struct GemmQ4k {
             store_scaled8(tile, row, 4 * h + j, a, b, sc2, nb2);
         }
     }
-    __device__ static float scale(const uint8_t *blk, float &dmin, bool &bad) {
-        float d = f16_bits_to_float(ldg_u16(blk));
-        dmin = f16_bits_to_float(ldg_u16(blk + 2));
-        bad = !isfinite(d) || !isfinite(dmin) || d < 0.0f || dmin < 0.0f;
-        return d;
+    __device__ static float2 scales(const uint32_t *raw, uint32_t, bool &bad) {
+        return checked_scales(raw[0], raw[0] >> 16, 1.0f, bad);
     }
-    // A' row: slots 0..7 = mins (paired with the hi sums), 8..15 = the same mins (lo sums).
-    __device__ static void mins(const uint8_t *blk, int part, uint8_t *tile, uint32_t row) {
+    // A' row: slots 0..7 = the eight mins (paired with the hi sums), 8..15 = the same mins (lo sums);
+    // thread h writes 16-byte part h.
+    __device__ static void mins(const uint32_t *raw, int h, uint8_t *tile, uint32_t row) {
         __half v[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             uint32_t sc, m;
-            scale_min(blk + 4, j, sc, m);
+            scale_min_words(raw[1], raw[2], raw[3], j, sc, m);
             v[j] = __float2half_rn(static_cast<float>(m));
         }
-        *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, part)) = *reinterpret_cast<uint4 *>(v);
+        *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, h)) = *reinterpret_cast<uint4 *>(v);
     }
 };
 
 struct GemmQ2k {
-    static constexpr int kBlockBytes = 84, kMinSlots = 32;        // 16 mins x (hi, lo)
+    static constexpr int kBlockBytes = 84, kMinSlots = 32, kRawWords = 21;     // 16 mins x (hi, lo)
     static constexpr float kBias = 1024.0f;
-    __device__ static void chunk(const uint8_t *blk, int c, int h, uint8_t *tile, uint32_t row, const MmaTables *tab) {
+    __device__ static uint32_t load_word(const uint8_t *blk, int word) { return __ldg(reinterpret_cast<const uint32_t *>(blk) + word); }
+    __device__ static void store(const uint32_t *raw, uint32_t, int c, int h, uint8_t *tile, uint32_t row, const MmaTables *tab) {
         const int hf = c >> 1, plane = 2 * (c & 1) + h;
-        const uint2 s0 = tab->scale[__ldg(blk + 8 * hf + 2 * plane) & 15u], s1 = tab->scale[__ldg(blk + 8 * hf + 2 * plane + 1) & 15u];
-        const uint32_t *q = reinterpret_cast<const uint32_t *>(blk + 16 + 32 * hf);     // 4-byte aligned
+        const uint32_t *q = raw + 4 + 8 * hf;
+        const uint32_t sbytes = raw[2 * hf + (plane >> 1)] >> (16 * (plane & 1));   // scale bytes 8*hf + 2*plane, +1
+        const uint2 s0 = tab->scale[sbytes & 15u], s1 = tab->scale[(sbytes >> 8) & 15u];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint2 s = j < 2 ? s0 : s1;                                            // bytes 0..15 / 16..31
-            const uint32_t a = (__ldg(q + 2 * j) >> (2 * plane)) & 0x03030303u, b = (__ldg(q + 2 * j + 1) >> (2 * plane)) & 0x03030303u;
+            const uint32_t a = (q[2 * j] >> (2 * plane)) & 0x03030303u, b = (q[2 * j + 1] >> (2 * plane)) & 0x03030303u;
             store_scaled8(tile, row, 4 * h + j, a, b, *reinterpret_cast<const __half2 *>(&s.x), *reinterpret_cast<const __half2 *>(&s.y));
         }
     }
-    __device__ static float scale(const uint8_t *blk, float &dmin, bool &bad) {
-        float d = f16_bits_to_float(ldg_u16(blk + 80));
-        dmin = f16_bits_to_float(ldg_u16(blk + 82));
-        bad = !isfinite(d) || !isfinite(dmin) || d < 0.0f || dmin < 0.0f;
-        return d;
+    __device__ static float2 scales(const uint32_t *raw, uint32_t, bool &bad) {
+        return checked_scales(raw[20], raw[20] >> 16, 1.0f, bad);
     }
-    // A' row: slots 0..15 = mins (hi sums), 16..31 = the same mins (lo sums); `part` = 16-byte chunk 0..3.
-    __device__ static void mins(const uint8_t *blk, int part, uint8_t *tile, uint32_t row) {
+    // A' row: slots 0..15 = the sixteen mins (hi sums), 16..31 = the same mins (lo sums); thread h
+    // converts mins 8h..8h+7 and writes them to parts h and h + 2.
+    __device__ static void mins(const uint32_t *raw, int h, uint8_t *tile, uint32_t row) {
         __half v[8];
+        const uint32_t w[2] = {raw[2 * h], raw[2 * h + 1]};
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = __float2half_rn(static_cast<float>(__ldg(blk + 8 * (part & 1) + j) >> 4));
-        *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, part)) = *reinterpret_cast<uint4 *>(v);
+        for (int j = 0; j < 8; ++j) v[j] = __float2half_rn(static_cast<float>((w[j >> 2] >> (8 * (j & 3) + 4)) & 15u));
+        *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, h)) = *reinterpret_cast<uint4 *>(v);
+        *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, h + 2)) = *reinterpret_cast<uint4 *>(v);
     }
+};
+
+// ---- shared-memory plan -----------------------------------------------------------------------------
+// tiles (1024-byte aligned): A ring, B ring, [min tiles: A' in 16-byte parts 0..3 of each row, B'
+// in parts 4..7], then the producers' raw staging (two superblocks per warp), the scale ring, the
+// decode tables and the barriers.
+template <class Dec> struct GemmPlan {
+    static constexpr bool kHasMin = Dec::kMinSlots > 0;
+    static constexpr uint32_t kRawBuf = kRowsPerWarp * Dec::kRawWords + 4;          // words; +4: funnel reads run one word over
+    static constexpr uint32_t kLoads = (kRowsPerWarp * Dec::kRawWords + 31) / 32;   // words per lane per superblock
+    static constexpr size_t kTilesBytes = (size_t)(2 * kStages + (kHasMin ? 2 : 0)) * kTileBytes;
+    static constexpr size_t kRawBytes = (size_t)kProducerWarps * 2 * kRawBuf * 4;
+    static constexpr size_t kScaleBytes = (size_t)kScaleRing * kTileM * sizeof(float2);
+    static constexpr size_t kBytes = 1024 + kTilesBytes + kRawBytes + kScaleBytes + sizeof(MmaTables) + sizeof(GemmSmem) + 64;
 };
 
 template <class Dec>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
     using namespace sm100;
+    using Plan = GemmPlan<Dec>;
+    constexpr bool kHasMin = Plan::kHasMin;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    // 1024-byte aligned tiles first, bookkeeping after them
     uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t *a_tiles = tiles;                                   // [kStages][16 KiB]
     uint8_t *b_tiles = tiles + kStages * kTileBytes;            // [kStages][16 KiB]
-    uint8_t *amin_tiles = b_tiles + kStages * kTileBytes;       // [2][16 KiB]
-    uint8_t *bmin_tiles = amin_tiles + 2 * kTileBytes;          // [2][16 KiB]
-    MmaTables *tab = reinterpret_cast<MmaTables *>(bmin_tiles + 2 * kTileBytes);
+    uint8_t *min_tiles = b_tiles + kStages * kTileBytes;        // [2][16 KiB] when the qtype has mins
+    uint32_t *raw_stage = reinterpret_cast<uint32_t *>(tiles + Plan::kTilesBytes);
+    float2 *dscale = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(raw_stage) + Plan::kRawBytes);
+    MmaTables *tab = reinterpret_cast<MmaTables *>(reinterpret_cast<uint8_t *>(dscale) + Plan::kScaleBytes);
     GemmSmem *sm = reinterpret_cast<GemmSmem *>(reinterpret_cast<uint8_t *>(tab) + sizeof(MmaTables));
-    constexpr bool kHasMin = Dec::kMinSlots > 0;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full_a[s], 8); mbar_init(&sm->full_b[s], 1); mbar_init(&sm->empty[s], 1); }
+        // full[s]: 8 producer warps + the TMA thread's expect_tx arrival (and its bytes) complete a stage,
+        // so an MMA issuer pays for one wait per 64-K chunk, not two.
+        for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], kProducerWarps + 1); mbar_init(&sm->empty[s], 1); }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&sm->acc_full[b], 1); mbar_init(&sm->acc_empty[b], 8);
-            mbar_init(&sm->min_full[b], 2); mbar_init(&sm->min_empty[b], 1);
+            mbar_init(&sm->min_full[b], kProducerWarps + 1); mbar_init(&sm->min_empty[b], 1);
         }
         sm->abort = 0;
         fence_barrier_init();
@@ -223,75 +276,77 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
                 ColBlock cb; int mat, mt;
                 tile_of(t, cb, mat, mt);
                 for (int kc = 0; kc < p.K / kChunkK; ++kc, ++it) {
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    const uint32_t s = stage_of(it), ph = phase_of(it);
                     if (!mbar_wait(&sm->empty[s], ph ^ 1u, abort)) break;
-                    mbar_expect_tx(&sm->full_b[s], kTileBytes);
-                    tma_load_2d(b_tiles + s * kTileBytes, &act_map, kc * kChunkK, cb.row0, &sm->full_b[s]);
+                    mbar_expect_tx(&sm->full[s], kTileBytes);
+                    tma_load_2d(b_tiles + s * kTileBytes, &act_map, kc * kChunkK, cb.row0, &sm->full[s]);
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
+    } else if (warp < 3) {
+        // ---------------- MMA issuers ----------------
+        // Issuing is latency-bound in the issuing thread (barrier wait + four tcgen05.mma + commit cost
+        // more cycles than the MMAs execute), so two threads alternate superblocks: warp 1 fills TMEM
+        // buffer 0 with the even ones, warp 2 buffer 1 with the odd ones. The buffers are independent
+        // accumulators, so no ordering between the two instruction streams is needed.
         if (lane == 0) {
-            uint32_t it = 0, sb_it = 0;
+            const uint32_t mine = (uint32_t)(warp - 1);
+            const uint64_t adesc0 = smem_desc_sw128(smem_u32(a_tiles)), bdesc0 = smem_desc_sw128(smem_u32(b_tiles));
+            const uint64_t amin0 = smem_desc_sw128(smem_u32(min_tiles + mine * kTileBytes));
+            const uint64_t bmin0 = amin0 + 4;                  // parts 4..7 of the same rows (64 bytes along K)
+            uint32_t sb_it = 0;
             for (long long t = blockIdx.x; t < tiles_total && !*abort; t += gridDim.x) {
                 ColBlock cb; int mat, mt;
                 tile_of(t, cb, mat, mt);
                 const uint32_t n = (uint32_t)((cb.ncols + 15) & ~15);
                 const uint32_t idesc = idesc_f16(n);
                 for (int sb = 0; sb < nsb; ++sb, ++sb_it) {
-                    const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
-                    if (!mbar_wait(&sm->acc_empty[buf], bph ^ 1u, abort)) break;
+                    if ((sb_it & 1u) != mine) continue;
+                    const uint32_t bph = (sb_it >> 1) & 1u;
+                    if (!mbar_wait(&sm->acc_empty[mine], bph ^ 1u, abort)) break;
                     tc_fence_after();
-                    for (int c = 0; c < 4; ++c, ++it) {
-                        const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-                        if (!mbar_wait(&sm->full_a[s], ph, abort) || !mbar_wait(&sm->full_b[s], ph, abort)) break;
+                    for (int c = 0; c < 4; ++c) {
+                        const uint32_t it = 4u * sb_it + c, s = stage_of(it), ph = phase_of(it);
+                        if (!mbar_wait(&sm->full[s], ph, abort)) break;
                         tc_fence_after();
-                        const uint32_t a0 = smem_u32(a_tiles + s * kTileBytes), b0 = smem_u32(b_tiles + s * kTileBytes);
+                        // descriptors differ from the stage-0 ones only in the start-address field (16-byte units)
+                        const uint64_t ad = adesc0 + (uint64_t)(s * (kTileBytes >> 4)), bd = bdesc0 + (uint64_t)(s * (kTileBytes >> 4));
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            umma_f16(tmem + buf * kTileN, smem_desc_sw128(a0 + 32 * k), smem_desc_sw128(b0 + 32 * k), idesc,
-                                     (c | k) ? 1u : 0u);
+                            umma_f16(tmem + mine * kTileN, ad + 2 * k, bd + 2 * k, idesc, (c | k) ? 1u : 0u);
                         umma_commit(&sm->empty[s]);
                     }
                     if (kHasMin) {
-                        if (!mbar_wait(&sm->min_full[buf], bph, abort)) break;
+                        if (!mbar_wait(&sm->min_full[mine], bph, abort)) break;
                         tc_fence_after();
-                        const uint32_t a0 = smem_u32(amin_tiles + buf * kTileBytes), b0 = smem_u32(bmin_tiles + buf * kTileBytes);
 #pragma unroll
                         for (int k = 0; k < Dec::kMinSlots / 16; ++k)
-                            umma_f16(tmem + 256 + buf * kTileN, smem_desc_sw128(a0 + 32 * k), smem_desc_sw128(b0 + 32 * k), idesc,
-                                     k ? 1u : 0u);
-                        umma_commit(&sm->min_empty[buf]);
+                            umma_f16(tmem + 256 + mine * kTileN, amin0 + 2 * k, bmin0 + 2 * k, idesc, k ? 1u : 0u);
+                        umma_commit(&sm->min_empty[mine]);
                     }
-                    umma_commit(&sm->acc_full[buf]);
+                    umma_commit(&sm->acc_full[mine]);
                 }
             }
         }
     } else if (warp < 4) {
-        // ---------------- min-term tiles (affine qtypes only) ----------------
+        // ---------------- B' tiles of the min term (affine qtypes only) ----------------
         if (kHasMin) {
-            const int tid = threadIdx.x - 64;                   // 0..63: two weight rows / two token rows each
+            constexpr int kParts = kHasMin ? Dec::kMinSlots / 8 : 1, kRowsPerPass = 32 / kParts;
+            const int part = lane % kParts, rsub = lane / kParts;
             uint32_t sb_it = 0;
             for (long long t = blockIdx.x; t < tiles_total && !*abort; t += gridDim.x) {
                 ColBlock cb; int mat, mt;
                 tile_of(t, cb, mat, mt);
-                const uint8_t *wbase = weights_of(cb, mat, mt);
                 for (int sb = 0; sb < nsb; ++sb, ++sb_it) {
                     const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
                     if (!mbar_wait(&sm->min_empty[buf], bph ^ 1u, abort)) break;
-                    uint8_t *at = amin_tiles + buf * kTileBytes, *bt = bmin_tiles + buf * kTileBytes;
-                    for (int r = tid; r < kTileM; r += 64) {
-                        const uint8_t *blk = wbase + (uint64_t)r * p.row_bytes + (uint64_t)sb * Dec::kBlockBytes;
-#pragma unroll
-                        for (int part = 0; part < Dec::kMinSlots / 8; ++part) Dec::mins(blk, part, at, r);
-                        // B': this token row's sums for the superblock (zero rows past the block's tail)
+                    uint8_t *tile = min_tiles + buf * kTileBytes;
+                    // this token row's sums for the superblock (zero rows past the block's tail)
+#pragma unroll 4
+                    for (int r = rsub; r < kTileM; r += kRowsPerPass) {
                         const uint4 *src = reinterpret_cast<const uint4 *>(p.sums + ((uint64_t)(cb.row0 + r) * nsb + sb) * 32);
-#pragma unroll
-                        for (int part = 0; part < Dec::kMinSlots / 8; ++part) {
-                            uint4 v = r < cb.ncols ? __ldg(src + part) : make_uint4(0, 0, 0, 0);
-                            *reinterpret_cast<uint4 *>(bt + sw128_offset(r, part)) = v;
-                        }
+                        const uint4 v = r < cb.ncols ? __ldg(src + part) : make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4 *>(tile + sw128_offset(r, 4 + part)) = v;
                     }
                     fence_proxy_async();
                     __syncwarp();
@@ -299,25 +354,80 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
                 }
             }
         }
-    } else if (warp < 12) {
+    } else if (warp < 4 + kProducerWarps) {
         // ---------------- dequant producers ----------------
-        const int tid = threadIdx.x - 128, row = tid & 127, h = tid >> 7;
-        uint32_t it = 0;
-        for (long long t = blockIdx.x; t < tiles_total && !*abort; t += gridDim.x) {
-            ColBlock cb; int mat, mt;
-            tile_of(t, cb, mat, mt);
-            const uint8_t *wrow = weights_of(cb, mat, mt) + (uint64_t)row * p.row_bytes;
-            for (int sb = 0; sb < nsb; ++sb) {
-                const uint8_t *blk = wrow + (uint64_t)sb * Dec::kBlockBytes;
-                for (int c = 0; c < 4; ++c, ++it) {
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-                    if (!mbar_wait(&sm->empty[s], ph ^ 1u, abort)) goto done;
-                    Dec::chunk(blk, c, h, a_tiles + s * kTileBytes, row, tab);
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&sm->full_a[s]);
+        const int pw = warp - 4, rl = lane & 15, h = lane >> 4;
+        const uint32_t row = (uint32_t)(kRowsPerWarp * pw + rl);
+        uint32_t *bufs = raw_stage + (size_t)pw * 2 * Plan::kRawBuf;
+        struct Cursor { long long t; int sb; const uint8_t *wrows; };        // wrows: first of this warp's 16 rows
+        auto open_tile = [&](Cursor &cur) {
+            if (cur.t < tiles_total) {
+                ColBlock cb; int mat, mt;
+                tile_of(cur.t, cb, mat, mt);
+                cur.wrows = weights_of(cb, mat, mt) + (uint64_t)(kRowsPerWarp * pw) * p.row_bytes;
+            }
+        };
+        auto advance = [&](Cursor &cur) {
+            if (++cur.sb == nsb) { cur.sb = 0; cur.t += gridDim.x; open_tile(cur); }
+        };
+        uint32_t regs[Plan::kLoads];
+        // lanes run along the rows: item = (row of the warp's 16, word of the row's run)
+        auto load_raw = [&](const Cursor &cur) {
+#pragma unroll
+            for (int i = 0; i < (int)Plan::kLoads; ++i) {
+                const int item = 32 * i + lane;
+                if (item < kRowsPerWarp * Dec::kRawWords) {
+                    const int r = item / Dec::kRawWords, word = item - r * Dec::kRawWords;
+                    regs[i] = Dec::load_word(cur.wrows + (uint64_t)r * p.row_bytes + (uint64_t)cur.sb * Dec::kBlockBytes, word);
                 }
             }
+        };
+        auto store_raw = [&](uint32_t *buf) {
+#pragma unroll
+            for (int i = 0; i < (int)Plan::kLoads; ++i) {
+                const int item = 32 * i + lane;
+                if (item < kRowsPerWarp * Dec::kRawWords) buf[item] = regs[i];
+            }
+        };
+        Cursor at{(long long)blockIdx.x, 0, nullptr};
+        open_tile(at);
+        if (at.t < tiles_total) { load_raw(at); store_raw(bufs); }
+        __syncwarp();
+        uint32_t cur = 0, sb_it = 0;
+        for (; at.t < tiles_total && !*abort; ++sb_it) {
+            Cursor ahead = at;
+            advance(ahead);
+            const bool more = ahead.t < tiles_total;
+            if (more) load_raw(ahead);                          // in flight while this superblock is decoded
+            const uint32_t *raw = bufs + cur * Plan::kRawBuf + rl * Dec::kRawWords;
+            const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(at.wrows + (uint64_t)rl * p.row_bytes +
+                                                                         (uint64_t)at.sb * Dec::kBlockBytes) & 3u);
+            if (h == 0) {
+                bool bad;
+                dscale[(sb_it % kScaleRing) * kTileM + row] = Dec::scales(raw, mis, bad);
+                if (bad) raise(p.status, YVEX_B200_STATUS_NUMERIC);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t it = 4u * sb_it + c, s = stage_of(it), ph = phase_of(it);
+                if (!mbar_wait(&sm->empty[s], ph ^ 1u, abort)) goto done;
+                Dec::store(raw, mis, c, h, a_tiles + s * kTileBytes, row, tab);
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm->full[s]);
+            }
+            if (kHasMin) {
+                const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
+                if (!mbar_wait(&sm->min_empty[buf], bph ^ 1u, abort)) goto done;
+                Dec::mins(raw, h, min_tiles + buf * kTileBytes, row);
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm->min_full[buf]);
+            }
+            if (more) store_raw(bufs + (cur ^ 1u) * Plan::kRawBuf);
+            __syncwarp();
+            cur ^= 1u;
+            at = ahead;
         }
     } else {
         // ---------------- epilogue ----------------
@@ -328,19 +438,17 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
         for (long long t = blockIdx.x; t < tiles_total && !*abort; t += gridDim.x) {
             ColBlock cb; int mat, mt;
             tile_of(t, cb, mat, mt);
-            const uint8_t *wrow = weights_of(cb, mat, mt) + (uint64_t)row * p.row_bytes;
             float acc[64];
 #pragma unroll
             for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
             const int ncols_here = cb.ncols - 64 * colhalf;       // columns this warp owns that are real
             for (int sb = 0; sb < nsb; ++sb, ++sb_it) {
                 const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
-                float dmin;
-                bool bad;
-                const float d = Dec::scale(wrow + (uint64_t)sb * Dec::kBlockBytes, dmin, bad);
-                if (bad) raise(p.status, YVEX_B200_STATUS_NUMERIC);
                 if (!mbar_wait(&sm->acc_full[buf], bph, abort)) goto done;
                 tc_fence_after();
+                // written by the row's producer before its last chunk of this superblock was published
+                const float2 dd = dscale[(sb_it % kScaleRing) * kTileM + row];
+                const float d = dd.x, dmin = dd.y;
                 if (ncols_here > 0) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {

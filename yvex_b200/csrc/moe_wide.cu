@@ -235,7 +235,7 @@ static int make_act_map(CUtensorMap *map, const __half *base, uint64_t rows, uin
 
 template <class Dec>
 static int launch_gemm(const CUtensorMap &map, const GemmParams &p, cudaStream_t s) {
-    const size_t smem = (size_t)(2 * kStages + 4) * kTileBytes + sizeof(MmaTables) + sizeof(GemmSmem) + 1024 + 64;
+    const size_t smem = GemmPlan<Dec>::kBytes;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(moe_grouped_gemm_kernel<Dec>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
