@@ -175,6 +175,23 @@ int yvex_b200_attention_gqa_decode(const void *q_bf16, const void *k_bf16, const
                                    uint64_t workspace_bytes, int *status, void *stream);
 
 /*
+ * The same operation for callers that can pass no workspace and must not cause a device-memory
+ * allocation (a runtime whose device bytes are all planned up front, or a latency-critical path
+ * that may not enter the allocator). This entry point has no counterpart in the reference. The
+ * split-KV partials live in one fixed 8 MiB device array per device
+ * (yvex_b200_attention_static_scratch_bytes()); a problem whose partials do not fit is refused
+ * with YVEX_ERR_BOUNDS (-7) before any launch. The first call on a device resolves the array's
+ * address and should be made during start-up, before any stream capture; calls that overlap in
+ * time on one device race on the array and must be serialised by the caller. Results are
+ * identical to yvex_b200_attention_gqa_decode.
+ */
+uint64_t yvex_b200_attention_static_scratch_bytes(void);
+int yvex_b200_attention_gqa_decode_static(const void *q_bf16, const void *k_bf16, const void *v_bf16,
+                                          uint64_t sessions, uint64_t q_heads, uint64_t kv_heads,
+                                          uint64_t head_dim, uint64_t context, uint64_t position,
+                                          float scale, float *out, int *status, void *stream);
+
+/*
  * Single-head f32 attention, the public op of the reference vtable (op_attention,
  * src/backend/cpu.c:319-411, src/backend/cuda/kernels.cu:362-435): q [d], keys/values
  * [seq_len x d] f32, scores/probabilities [seq_len] written like the reference does.

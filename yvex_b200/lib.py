@@ -58,6 +58,10 @@ def _load():
     lib.yvex_b200_attention_gqa_decode.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, C.c_float,
                                                    vp, vp, u64, vp, vp]
     lib.yvex_b200_attention_f32.argtypes = [vp, vp, vp, u64, u64, u64, C.c_float, C.c_int, vp, vp, vp, vp, vp]
+    lib.yvex_b200_attention_static_scratch_bytes.restype = u64
+    lib.yvex_b200_attention_static_scratch_bytes.argtypes = []
+    lib.yvex_b200_attention_gqa_decode_static.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, C.c_float,
+                                                          vp, vp, vp]
     return lib
 
 
@@ -69,7 +73,8 @@ EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_ge
            "yvex_b200_moe_wide_workspace_bytes", "yvex_b200_launch_count", "yvex_b200_phase_events",
            "yvex_b200_moe_expert_rows_workspace_bytes", "yvex_b200_moe_expert_rows", "yvex_b200_moe_combine",
            "yvex_b200_attention_workspace_bytes", "yvex_b200_attention_gqa_decode",
-           "yvex_b200_attention_f32"]
+           "yvex_b200_attention_f32", "yvex_b200_attention_static_scratch_bytes",
+           "yvex_b200_attention_gqa_decode_static"]
 
 
 def _torch():
