@@ -20,6 +20,8 @@ import sys
 import threading
 import time
 
+import numpy as np
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
@@ -37,15 +39,52 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and clock-event reasons while the timed region runs: NVML queries from a
+    thread every 10 ms (read-only), or `nvidia-smi -lms 100` when the NVML module is missing."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    REASONS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, index):
         self.rows, self.proc, self.index = [], None, index
+        self.stop, self.thread, self.handle, self.nvml = threading.Event(), None, None, None
+
+    def _nvml_handle(self):
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(self.index).uuid)
+                handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except Exception:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.nvml, self.handle = pynvml, handle
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            return True
+        except Exception:
+            return False
+
+    def _poll(self):
+        n, h = self.nvml, self.handle
+        reasons_fn = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        while True:
+            try:
+                mask = int(reasons_fn(h))
+                self.rows.append([str(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)), str(self.max_mhz), "",
+                                  *["Active" if mask & self.REASONS[k] else "Not Active"
+                                    for k in ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")]])
+            except Exception:
+                pass
+            if self.stop.wait(0.01):
+                return
 
     def __enter__(self):
+        if self._nvml_handle():
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return self
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -61,6 +100,9 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def __exit__(self, *a):
+        self.stop.set()
+        if self.handle is not None and self.thread:
+            self.thread.join(timeout=2)
         if self.proc:
             self.proc.terminate()
             try:
@@ -483,17 +525,239 @@ def run_native_ep(args):
         dist.destroy_process_group()
 
 
+def _timed_events(torch, fn, steps, before=None):
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        if before:
+            before(i)
+        starts[i].record()
+        fn(i)
+        stops[i].record()
+    torch.cuda.synchronize()
+    return [a.elapsed_time(b) for a, b in zip(starts, stops)]
+
+
+def run_gemv_stream(args):
+    """Config 1: the 4096 x 4096 IQ2_XXS dequant GEMV. One matrix (4.3 MB) fits in L2, so a step is
+    256 DIFFERENT matrices back to back (1.1 GB streamed once, no reuse), replayed from one CUDA
+    graph; GB/s = algorithmic bytes of the 256 products / step time. Q4_K and Q8_0 variants and the
+    latency of a single launch are reported beside it."""
+    import ctypes as C
+    import torch
+    from yvex_b200 import backend as B
+    from yvex_b200 import lib, synth
+    from yvex_b200.workloads import device_blocks
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if int(os.environ.get("RANK", "0")) != 0:
+        return                                         # replicas only: one rank measures
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    peaks = measured_peaks()
+    rows = width = 4096
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(synth.BASE_SEED + 0)
+    status = lib.Status(dev)
+
+    def stream_case(qtype, count):
+        rb = synth.row_bytes(qtype, width)
+        enc = device_blocks(torch, qtype, rows * count, width, gen, dev)
+        xs = torch.randn((count, width), device=dev, generator=gen)
+        ys = torch.empty((count, rows), dtype=torch.float32, device=dev)
+        mats = [enc[i * rows * rb:(i + 1) * rows * rb] for i in range(count)]
+
+        def launch_all():
+            for i in range(count):
+                lib.gemv(qtype, mats[i], rows, width, xs[i], status, out=ys[i:i + 1], row_bytes=rb)
+        launch_all()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            launch_all()
+        algo = count * (rows * rb + 4 * width + 4 * rows)
+        return enc, xs, ys, mats, graph, algo, rb
+
+    count = 256
+    enc, xs, ys, mats, graph, algo, rb = stream_case(synth.IQ2_XXS, count)
+    for _ in range(args.warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    with ClockSampler(local) as clocks:
+        ms = _timed_events(torch, lambda i: graph.replay(), args.steps)
+        # latency of one launch of one matrix (L2-warm after the first)
+        one = _timed_events(torch, lambda i: lib.gemv(synth.IQ2_XXS, mats[i % count], rows, width, xs[i % count], status,
+                                                       out=ys[0:1], row_bytes=rb), 50)
+    if status.read() != 0:
+        raise RuntimeError(f"device status word = {status.read()}")
+    t = sum(ms) / len(ms) * 1e-3
+    gbs = algo / t / 1e9
+    variants = {}
+    for name, q, n in (("Q4_K", synth.Q4_K, 128), ("Q8_0", synth.Q8_0, 64)):
+        _, _, _, _, g2, algo2, _ = stream_case(q, n)
+        for _ in range(3):
+            g2.replay()
+        m2 = _timed_events(torch, lambda i: g2.replay(), args.steps)
+        variants[name] = {"GB/s": algo2 / (sum(m2) / len(m2) * 1e-3) / 1e9, "matrices_per_step": n}
+        del g2
+    # end to end through the host boundary: host x in, resident weights, host y out, one call per matrix
+    be = B.Backend(device=f"cuda:{local}".encode())
+    e2e_n = 64
+    arena = B.ResidentArena(be, {"w": enc[:e2e_n * rows * rb].cpu().numpy()})
+    hx = xs[:e2e_n].cpu().numpy()
+    tin = be.from_array(hx[0:1], B.F32, [1, width])
+    tout = be.tensor(rows * 4, B.F32, [1, rows])[1]
+    facts = B.Facts()
+
+    def e2e_step():
+        for i in range(e2e_n):
+            be.write(tin, hx[i:i + 1])
+            rc = B._lib.yvex_backend_cuda_encoded_matvec(be.h, arena.host_ptr("w") + i * rows * rb, rows * rb, synth.IQ2_XXS,
+                                                         rows, width, rb, 1, tin, None, 0, None, tout, 0, C.byref(facts),
+                                                         C.byref(be.err))
+            if rc != B.OK:
+                raise RuntimeError(be.message())
+            be.read(tout, np.float32, rows)
+    e2e_step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    t_e2e = (time.perf_counter() - t0) / args.steps
+    e2e_algo = e2e_n * (rows * rb + 4 * width + 4 * rows)
+    be.close()
+    # CPU baseline: the port's matvec on one matrix, all cores over rows
+    port, kind = oracle_backend(False)
+    cores = os.cpu_count() or 1
+    w0 = mats[0].cpu().numpy()
+    x0 = xs[0].cpu().numpy()
+    t0 = time.perf_counter()
+    port.matvec(synth.IQ2_XXS, w0, rows, width, x0, threads=cores)
+    t_cpu = time.perf_counter() - t0
+    line = {"metric": "dequant_gemv_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16-mma/f32-accum (exact-integer weights), f32 in/out", "data": "synthetic",
+            "config": {"workload": "c1", "rows": rows, "width": width, "qtype": "IQ2_XXS", "matrices_per_step": count,
+                       "l2": "inputs larger than L2: 256 distinct matrices (1.1 GB) per step, one CUDA graph",
+                       "parallelism": f"replicas only (1 of {world} ranks measures)"},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_algo / t_e2e / 1e9, "unit": "GB/s", "h2d_bytes_per_step": e2e_n * width * 4,
+                    "d2h_bytes_per_step": e2e_n * rows * 4,
+                    "api": f"yvex_backend_cuda_encoded_matvec, {e2e_n} calls per step, host x in / host y out per call"},
+            "gpu_launches": count * args.steps,
+            "single_launch_us": sorted(one)[len(one) // 2] * 1e3,
+            "variants": variants,
+            "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<Iq2Decoder>", "achieved": gbs, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                         "frac_of_nominal_8TBs": gbs / 8000.0},
+            "cpu_baseline": {"value": (rows * rb + 4 * width + 4 * rows) / t_cpu / 1e9, "unit": "GB/s", "cores": cores,
+                             "kind": kind, "sample": "one 4096x4096 IQ2_XXS matvec, rows split over all cores"}}
+    print(json.dumps(line), flush=True)
+
+
+def run_attention(args):
+    """Config 4: GQA decode attention, 16 sessions x 32 q heads / 8 kv heads x d128 over a bf16 KV
+    cache of 32768 positions (2.1 GB read per step, larger than L2)."""
+    import ctypes as C
+    import torch
+    from yvex_b200 import backend as B
+    from yvex_b200 import lib, synth
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    peaks = measured_peaks()
+    S, Hq, Hkv, D, ctx = 16, 32, 8, 128, 32768
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(synth.BASE_SEED + 3)
+    q = torch.randn((S, Hq, D), device=dev, generator=gen).to(torch.bfloat16)
+    k = torch.randn((S, Hkv, ctx, D), device=dev, generator=gen).to(torch.bfloat16)
+    v = torch.randn((S, Hkv, ctx, D), device=dev, generator=gen).to(torch.bfloat16)
+    out = torch.empty((S, Hq, D), dtype=torch.float32, device=dev)
+    ws = torch.empty(int(lib.lib.yvex_b200_attention_workspace_bytes(S, Hq, Hkv, D, ctx)), dtype=torch.uint8, device=dev)
+    status = lib.Status(dev)
+    scale, pos = D ** -0.5, ctx - 1
+    algo = 2 * k.numel() * 2 + q.numel() * 2 + out.numel() * 4
+
+    def step(i):
+        lib.attention_gqa_decode(q, k, v, pos, scale, status, workspace=ws, out=out)
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    l0 = lib.lib.yvex_b200_launch_count()
+    with ClockSampler(local) as clocks:
+        ms = _timed_events(torch, step, args.steps)
+    launches = lib.lib.yvex_b200_launch_count() - l0
+    if status.read() != 0:
+        raise RuntimeError(f"device status word = {status.read()}")
+    t = sum(ms) / len(ms) * 1e-3
+    gbs = algo / t / 1e9
+    # end to end through the host boundary: the KV cache is resident (as in serving), q comes from
+    # the host and the output goes back to the host every step
+    be = B.Backend(device=f"cuda:{local}".encode())
+    bits = lambda a: a.view(torch.int16).cpu().numpy().view(np.uint16)
+    tq, tk, tv = be.from_array(bits(q), B.BF16), be.from_array(bits(k), B.BF16), be.from_array(bits(v), B.BF16)
+    tout = be.tensor(out.numel() * 4, B.F32, list(out.shape))[1]
+    tws = be.tensor(max(ws.numel(), 256))[1]
+    assert B._lib.yvex_backend_workspace_attach(be.h, tws, C.byref(be.err)) == B.OK
+    hq = bits(q)
+
+    def e2e_step():
+        be.write(tq, hq)
+        rc = B._lib.yvex_backend_attention_gqa_decode(be.h, tq, tk, tv, S, Hq, Hkv, D, ctx, pos, scale, tout, C.byref(be.err))
+        if rc != B.OK:
+            raise RuntimeError(be.message())
+        return be.read(tout, np.float32, out.numel())[1]
+    got = e2e_step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    t_e2e = (time.perf_counter() - t0) / args.steps
+    if not np.array_equal(got.view(np.uint32), out.cpu().numpy().reshape(-1).view(np.uint32)):
+        raise RuntimeError("host-boundary result differs from the device-layer result")
+    B._lib.yvex_backend_workspace_detach(be.h, C.byref(be.err))
+    be.close()
+    # CPU baseline: the port on one session (1/16 of the work), all cores over heads
+    port, kind = oracle_backend(False)
+    cores = os.cpu_count() or 1
+    t0 = time.perf_counter()
+    port.attention_gqa_decode(bits(q[:1]), bits(k[:1]), bits(v[:1]), pos, scale, threads=cores)
+    t_cpu = time.perf_counter() - t0
+    line = {"metric": "attention_decode_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 in, f32 accumulate and out", "data": "synthetic",
+            "config": {"workload": "c4", "sessions": S, "q_heads": Hq, "kv_heads": Hkv, "head_dim": D, "context": ctx,
+                       "l2": "inputs larger than L2 (2.1 GB of K/V per step)",
+                       "parallelism": f"replicas only (1 of {world} ranks measures)"},
+            "clocks": clocks.summary(),
+            "e2e": {"value": algo / t_e2e / 1e9, "unit": "GB/s", "h2d_bytes_per_step": q.numel() * 2,
+                    "d2h_bytes_per_step": out.numel() * 4,
+                    "api": "yvex_backend_attention_gqa_decode; KV cache resident, q from host, out to host"},
+            "gpu_launches": int(launches),
+            "sessions_per_s": S / t,
+            "roofline": {"bound": "hbm", "kernel": "gqa_decode_kernel<128,4>", "achieved": gbs, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]},
+            "cpu_baseline": {"value": (algo / S) / t_cpu / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
+                             "sample": "one of the 16 sessions (32 heads x 32768 keys), heads split over all cores"}}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default="c5", choices=["c2", "c3", "c5"])
+    ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "c1":
+        run_gemv_stream(args)
+    elif args.workload == "c4":
+        run_attention(args)
     elif args.workload == "c5":
         run_native_ep(args)
     else:
