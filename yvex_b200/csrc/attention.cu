@@ -2,142 +2,186 @@
 //
 // gqa_decode: one query position per session against a bf16 KV cache. The cache is the only
 // traffic that matters (2 x context x head_dim x 2 bytes per KV head), so the kernel is built to
-// stream it once: a CTA owns one (session, KV head) and one slice of the context, all q heads of
-// the GQA group share every K/V load, D/8 lanes read one 16-byte chunk each of a key row
-// (fully coalesced 128-bit loads), scores are kept in f32 and the running (max, sum, accumulator)
-// triple is rescaled once per 8-key block. Slices are merged by a second tiny kernel
-// (log-sum-exp merge). Math per (session, q head) is the reference CPU op's: scores =
-// scale * q.k, softmax over keys 0..position, out = sum p*v (src/backend/cpu.c:319-411).
+// stream it once and to spend as few issue slots per key as possible: a CTA owns one (session,
+// KV head) and one slice of the context; each warp walks 16-key blocks of the slice and does both
+// contractions on the tensor cores (mma.sync m16n8k16, bf16 x bf16 -> f32):
+//   S = Q K^T   M = heads of the GQA group (rows 0..G-1 of 16), N = 8 keys, K = 16 dims
+//   O += P V    M = heads, K = 16 keys, N = 8 dims; P is split into hi + lo bf16 so the
+//               probabilities keep ~16 mantissa bits
+// Operands are built straight from coalesced 16-byte global loads without a shared-memory
+// transpose: a dot product does not care in which order its terms are summed, so the k-slots of
+// the MMA are assigned to whatever dims (for S) or keys (for O) a lane happens to hold, as long as
+// both operands use the same assignment; the n-slots of O are a fixed permutation of the dims
+// that the epilogue undoes. Scores stay in f32; the running (max, sum, accumulator) triple is
+// rescaled once per 16-key block. Warps, then slices, are merged by log-sum-exp.
+// Math per (session, q head) is the reference CPU op's: scores = scale * q.k, softmax over keys
+// 0..position, out = sum p*v (src/backend/cpu.c:319-411).
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace yb {
 
-constexpr int kAttnThreads = 256;
-constexpr int kKeyBlock = 8;
+constexpr int kAttnThreads = 128;
+constexpr int kAttnWarps = kAttnThreads / 32;
+constexpr int kKeyBlock = 16;
+constexpr int kMaxGroup = 8;                  // q heads per kv head that fit the 8 usable MMA rows
 
-__device__ __forceinline__ void bf16x8_to_float(const uint4 &raw, float (&f)[8]) {
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        f[2 * i] = __uint_as_float(w[i] << 16);
-        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
+// D(16x8, f32) = A(16x16, bf16, row) * B(16x8, bf16, col) + C. Rows 8..15 of A are zero (a1 = a3 = 0):
+// only d0, d1 (row lane/4) are kept.
+__device__ __forceinline__ void mma_bf16_rows8(float &d0, float &d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float z0, z1;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};"
+        : "+f"(d0), "+f"(d1), "=f"(z0), "=f"(z1)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const uint16_t *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
 }
 
 // Partial layout per (session, kv head, split): G heads x (m, l, acc[D]).
-template <int D, int G>
-__global__ void __launch_bounds__(kAttnThreads)
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, 3)
 gqa_decode_kernel(const uint16_t *__restrict__ q, const uint16_t *__restrict__ k,
-                  const uint16_t *__restrict__ v, int kv_heads, uint64_t context, uint64_t visible,
-                  float scale, int splits, float *__restrict__ partial, int *status) {
-    constexpr int LPK = D / 8;                 // lanes per key row
-    constexpr int KPW = 32 / LPK;              // keys a warp reads per load instruction
-    constexpr int NW = kAttnThreads / 32;
+                  const uint16_t *__restrict__ v, int kv_heads, int G, uint64_t context, uint64_t visible,
+                  float scale, int splits, uint64_t keys_per_split, float *__restrict__ partial, int *status) {
+    constexpr int KL = D / 32;                 // 16-byte K chunks a lane loads per key (chunks c, c+4, ...)
+    constexpr int VU = D / 64;                 // 16-byte V chunks a lane loads per key (chunks g, g+8, ...)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int sub = lane / LPK, ll = lane % LPK;     // key slot inside the warp, chunk inside the row
-    // Key slots of one warp may run different trip counts at the ragged end of a split, so the
-    // score reduction synchronises only the lanes of its own slot.
-    const unsigned slot_mask = static_cast<unsigned>(((1ull << LPK) - 1ull) << (sub * LPK));
+    const int g = lane >> 2, c = lane & 3;
     const int split = blockIdx.x % splits;
     const uint64_t sk = blockIdx.x / splits;           // session * kv_heads + kv head
     const uint64_t session = sk / kv_heads, kvh = sk % kv_heads;
     const uint16_t *kb = k + sk * context * D, *vb = v + sk * context * D;
     const uint16_t *qb = q + (session * (uint64_t)kv_heads * G + kvh * G) * D;
 
-    float qf[G][8];
+    // A fragments of Q: lane (g, c) holds head g, chunks c + 4i; rows >= G are zero.
+    uint32_t qa[KL][4];
 #pragma unroll
-    for (int h = 0; h < G; ++h) {
-        uint4 raw = __ldg(reinterpret_cast<const uint4 *>(qb + h * D) + ll);
-        bf16x8_to_float(raw, qf[h]);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) qf[h][i] *= scale;
+    for (int i = 0; i < KL; ++i) {
+        uint4 raw = g < G ? __ldg(reinterpret_cast<const uint4 *>(qb + g * D) + c + 4 * i) : make_uint4(0, 0, 0, 0);
+        qa[i][0] = raw.x; qa[i][1] = raw.y; qa[i][2] = raw.z; qa[i][3] = raw.w;
     }
-    float m[G], l[G], acc[G][8];
+    float m = -INFINITY, l = 0.0f;             // head g; l is this lane's share (4 keys of every 16)
+    float acc[VU][8][2];                       // head g, dims 8*(2c + 8u) + 8*e + j  <-  acc[u][j][e]
 #pragma unroll
-    for (int h = 0; h < G; ++h) {
-        m[h] = -INFINITY; l[h] = 0.0f;
+    for (int u = 0; u < VU; ++u)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[h][i] = 0.0f;
-    }
-    // This split's key range, in units of kKeyBlock*KPW*NW keys so every slot stays balanced.
-    const uint64_t per_split = (visible + splits - 1) / splits;
-    const uint64_t begin = (uint64_t)split * per_split;
-    const uint64_t end = begin + per_split < visible ? begin + per_split : visible;
-    const uint64_t stride = (uint64_t)NW * KPW * kKeyBlock;
-    for (uint64_t base = begin + ((uint64_t)warp * KPW + sub) * kKeyBlock; base < end; base += stride) {
-        float s[kKeyBlock][G];
-        uint4 kraw[kKeyBlock];
+        for (int j = 0; j < 8; ++j) acc[u][j][0] = acc[u][j][1] = 0.0f;
+
+    const uint64_t begin = (uint64_t)split * keys_per_split;
+    const uint64_t end = begin + keys_per_split < visible ? begin + keys_per_split : visible;
+    for (uint64_t base = begin + (uint64_t)warp * kKeyBlock; base < end; base += (uint64_t)kAttnWarps * kKeyBlock) {
+        // ---- loads: K rows base+g and base+8+g (chunks c+4i); V rows base+{2c, 2c+1, 2c+8, 2c+9} (chunks g+8u)
+        uint4 kr[2][KL], vr[4][VU];
 #pragma unroll
-        for (int j = 0; j < kKeyBlock; ++j) {
-            const uint64_t key = base + j;
-            kraw[j] = key < end ? __ldg(reinterpret_cast<const uint4 *>(kb + key * D) + ll) : make_uint4(0, 0, 0, 0);
+        for (int half = 0; half < 2; ++half) {
+            const uint64_t key = base + 8 * half + g;
+#pragma unroll
+            for (int i = 0; i < KL; ++i)
+                kr[half][i] = key < end ? ldg_stream(kb + key * D + 8 * (c + 4 * i)) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int j = 0; j < kKeyBlock; ++j) {
-            float kf[8];
-            bf16x8_to_float(kraw[j], kf);
+        for (int r = 0; r < 4; ++r) {
+            const uint64_t key = base + 2 * c + (r & 1) + 8 * (r >> 1);
 #pragma unroll
-            for (int h = 0; h < G; ++h) {
-                float d = 0.0f;
+            for (int u = 0; u < VU; ++u)
+                vr[r][u] = key < end ? ldg_stream(vb + key * D + 8 * (g + 8 * u)) : make_uint4(0, 0, 0, 0);
+        }
+        // ---- S = Q K^T: sc[half][e] = score of head g, key base + 8*half + 2c + e
+        float sc[2][2];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) d = fmaf(qf[h][i], kf[i], d);
+        for (int half = 0; half < 2; ++half) {
+            sc[half][0] = sc[half][1] = 0.0f;
 #pragma unroll
-                for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(slot_mask, d, o);
-                s[j][h] = base + j < end ? d : -INFINITY;
+            for (int i = 0; i < KL; ++i) {
+                const uint32_t w[4] = {kr[half][i].x, kr[half][i].y, kr[half][i].z, kr[half][i].w};
+                mma_bf16_rows8(sc[half][0], sc[half][1], qa[i][0], qa[i][1], w[0], w[1]);
+                mma_bf16_rows8(sc[half][0], sc[half][1], qa[i][2], qa[i][3], w[2], w[3]);
             }
         }
-        uint4 vraw[kKeyBlock];
+        float bm = m;
 #pragma unroll
-        for (int j = 0; j < kKeyBlock; ++j) {
-            const uint64_t key = base + j;
-            vraw[j] = key < end ? __ldg(reinterpret_cast<const uint4 *>(vb + key * D) + ll) : make_uint4(0, 0, 0, 0);
+        for (int half = 0; half < 2; ++half)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const uint64_t key = base + 8 * half + 2 * c + e;
+                sc[half][e] = key < end ? sc[half][e] * scale : -INFINITY;
+                bm = fmaxf(bm, sc[half][e]);
+            }
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+        const float corr = __expf(m - bm);          // m = -inf on the first block -> 0
+        m = bm;
+        l *= corr;
+        if (corr != 1.0f) {
+#pragma unroll
+            for (int u = 0; u < VU; ++u)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { acc[u][j][0] *= corr; acc[u][j][1] *= corr; }
         }
+        // ---- P as A fragments (hi + lo bf16), keys 2c, 2c+1 (k-slots 2c..) and 2c+8, 2c+9 (k-slots 2c+8..)
+        uint32_t ph[2], pl[2];
 #pragma unroll
-        for (int h = 0; h < G; ++h) {
-            float bm = m[h];
-#pragma unroll
-            for (int j = 0; j < kKeyBlock; ++j) bm = fmaxf(bm, s[j][h]);
-            const float corr = __expf(m[h] - bm);     // m = -inf on the first block -> 0
-            m[h] = bm;
-            l[h] *= corr;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[h][i] *= corr;
-#pragma unroll
-            for (int j = 0; j < kKeyBlock; ++j) s[j][h] = __expf(s[j][h] - bm);
+        for (int half = 0; half < 2; ++half) {
+            const float p0 = __expf(sc[half][0] - bm), p1 = __expf(sc[half][1] - bm);
+            ph[half] = pack_bf16(p0, p1);
+            const float r0 = p0 - __uint_as_float(ph[half] << 16), r1 = p1 - __uint_as_float(ph[half] & 0xffff0000u);
+            pl[half] = pack_bf16(r0, r1);
+            l += p0 + p1;
         }
+        // ---- O += P V: n-tile (u, j) covers dim j of chunks 8u..8u+7; B pairs two keys of one dim
 #pragma unroll
-        for (int j = 0; j < kKeyBlock; ++j) {
-            float vf[8];
-            bf16x8_to_float(vraw[j], vf);
+        for (int u = 0; u < VU; ++u) {
+            const uint32_t r0[4] = {vr[0][u].x, vr[0][u].y, vr[0][u].z, vr[0][u].w};
+            const uint32_t r1[4] = {vr[1][u].x, vr[1][u].y, vr[1][u].z, vr[1][u].w};
+            const uint32_t r2[4] = {vr[2][u].x, vr[2][u].y, vr[2][u].z, vr[2][u].w};
+            const uint32_t r3[4] = {vr[3][u].x, vr[3][u].y, vr[3][u].z, vr[3][u].w};
 #pragma unroll
-            for (int h = 0; h < G; ++h) {
-                l[h] += s[j][h];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc[h][i] = fmaf(s[j][h], vf[i], acc[h][i]);
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+                const uint32_t b0 = __byte_perm(r0[j >> 1], r1[j >> 1], sel), b1 = __byte_perm(r2[j >> 1], r3[j >> 1], sel);
+                mma_bf16_rows8(acc[u][j][0], acc[u][j][1], ph[0], ph[1], b0, b1);
+                mma_bf16_rows8(acc[u][j][0], acc[u][j][1], pl[0], pl[1], b0, b1);
             }
         }
     }
-    // Merge the NW*KPW key slots of the CTA through shared memory.
-    __shared__ float sm_m[NW * KPW][G], sm_l[NW * KPW][G];
-    __shared__ float sm_acc[NW * KPW][G][D];
-    const int slot = warp * KPW + sub;
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+
+    // Merge the warps of the CTA through shared memory.
+    __shared__ float sm_m[kAttnWarps][kMaxGroup], sm_l[kAttnWarps][kMaxGroup];
+    __shared__ float sm_acc[kAttnWarps][kMaxGroup][D];
+    if (g < G) {
+        if (c == 0) { sm_m[warp][g] = m; sm_l[warp][g] = l; }
 #pragma unroll
-    for (int h = 0; h < G; ++h) {
-        if (ll == 0) { sm_m[slot][h] = m[h]; sm_l[slot][h] = l[h]; }
+        for (int u = 0; u < VU; ++u)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sm_acc[slot][h][ll * 8 + i] = acc[h][i];
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) sm_acc[warp][g][8 * (2 * c + e + 8 * u) + j] = acc[u][j][e];
     }
     __syncthreads();
     float *po = partial + ((sk * splits + split) * G) * (uint64_t)(D + 2);
     for (int idx = threadIdx.x; idx < G * D; idx += kAttnThreads) {
         const int h = idx / D, d = idx % D;
         float gm = -INFINITY;
-        for (int sidx = 0; sidx < NW * KPW; ++sidx) gm = fmaxf(gm, sm_m[sidx][h]);
+        for (int w = 0; w < kAttnWarps; ++w) gm = fmaxf(gm, sm_m[w][h]);
         float gl = 0.0f, ga = 0.0f;
-        for (int sidx = 0; sidx < NW * KPW; ++sidx) {
-            const float c = sm_m[sidx][h] == -INFINITY ? 0.0f : __expf(sm_m[sidx][h] - gm);
-            gl += sm_l[sidx][h] * c;
-            ga += sm_acc[sidx][h][d] * c;
+        for (int w = 0; w < kAttnWarps; ++w) {
+            const float f = sm_m[w][h] == -INFINITY ? 0.0f : __expf(sm_m[w][h] - gm);
+            gl += sm_l[w][h] * f;
+            ga += sm_acc[w][h][d] * f;
         }
         if (d == 0) { po[h * (D + 2)] = gm; po[h * (D + 2) + 1] = gl; }
         po[h * (D + 2) + 2 + d] = ga;
@@ -218,20 +262,27 @@ __global__ void attention_f32_kernel(const float *q, const float *keys, const fl
 }
 
 static int pick_splits(uint64_t groups, uint64_t visible) {
-    // enough CTAs to fill 148 SMs a few times over, but at least ~512 keys per split
-    uint64_t want = ((uint64_t)kSmCount * 4 + groups - 1) / groups;
-    uint64_t cap = (visible + 511) / 512;
+    // Enough CTAs to fill 148 SMs a few times over with at least ~256 keys per slice; among those
+    // prefer a count that makes groups * splits a whole number of waves (a multiple of the SM count).
+    const uint64_t want = ((uint64_t)kSmCount * 4 + groups - 1) / groups;
+    const uint64_t cap = (visible + 255) / 256;
     uint64_t s = want < cap ? want : cap;
-    return (int)(s < 1 ? 1 : s > 64 ? 64 : s);
+    s = s < 1 ? 1 : s;
+    for (uint64_t t = s; t <= s + 40 && t <= cap && t <= 64; ++t)
+        if ((groups * t) % kSmCount == 0) { s = t; break; }
+    return (int)(s > 64 ? 64 : s);
 }
 
 template <int D, int G>
 static int launch_gqa(const uint16_t *q, const uint16_t *k, const uint16_t *v, uint64_t sessions, int kv_heads,
                       uint64_t context, uint64_t visible, float scale, float *out, float *partial, int splits,
                       int *status, cudaStream_t s) {
+    static_assert(G <= kMaxGroup, "GQA group does not fit the MMA rows");
     const uint64_t groups = sessions * kv_heads;
-    gqa_decode_kernel<D, G><<<(unsigned)(groups * splits), kAttnThreads, 0, s>>>(q, k, v, kv_heads, context, visible,
-                                                                                   scale, splits, partial, status);
+    uint64_t per_split = (visible + splits - 1) / splits;
+    per_split = (per_split + kKeyBlock - 1) / kKeyBlock * kKeyBlock;       // slices start on 16-key blocks
+    gqa_decode_kernel<D><<<(unsigned)(groups * splits), kAttnThreads, 0, s>>>(q, k, v, kv_heads, G, context, visible,
+                                                                              scale, splits, per_split, partial, status);
     gqa_merge_kernel<D, G><<<(unsigned)groups, 128, 0, s>>>(partial, splits, groups, out, status);
     return launch_status(2);
 }
