@@ -3,10 +3,11 @@
 // Two matvec paths:
 //   * gemv_rows_kernel  - any supported qtype, one warp per output row, f32 FMA. Used for the
 //     scalar qtypes (router weights are F32) and as the reference-shaped fallback.
-//   * gemv_mma_kernel   - the streaming path for block qtypes (gemv_mma.cuh): rows are staged
-//     into shared memory with 16-byte cp.async copies, decoded to exact small-integer fp16
-//     fragments and multiplied on the tensor cores against a 3-way fp16 split of the f32
-//     activation, with the per-superblock f16 scale applied to the drained accumulator.
+//   * gemv_mma_kernel   - the streaming path for block qtypes (gemv_mma.cuh): every warp stages
+//     its rows into shared memory with 16-byte cp.async copies, decodes them to exact
+//     small-integer fp16 fragments and multiplies them on the tensor cores against a 3-way fp16
+//     split of the f32 activation, with the per-superblock f16 scale applied to the drained
+//     accumulator.
 #include "gemv_mma.cuh"
 #include "qtype_decode.cuh"
 
@@ -82,13 +83,8 @@ extern "C" int yvex_b200_gemv(unsigned int qtype, const void *encoded, uint64_t 
     const uint8_t *enc = static_cast<const uint8_t *>(encoded);
     if (gemv_mma_eligible(qtype, rows, width, enc) &&
         (reinterpret_cast<uintptr_t>(input) & 15u) == 0) {
-        for (uint64_t in = 0; in < input_rows; ++in) {
-            rc = gemv_mma_launch(qtype, enc, rows, width, row_bytes, input + in * width,
-                                 additive ? additive + in * rows : nullptr, out + in * rows,
-                                 round_bf16, status, as_stream(stream));
-            if (rc != OK) return rc;
-        }
-        return OK;
+        return gemv_mma_launch(qtype, enc, rows, width, row_bytes, input, input_rows, additive, out, round_bf16, status,
+                               as_stream(stream));
     }
     uint64_t jobs = rows * input_rows;
     int grid = (int)((jobs + 7) / 8 < (uint64_t)kSmCount * 8 ? (jobs + 7) / 8

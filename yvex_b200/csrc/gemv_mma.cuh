@@ -16,19 +16,23 @@
 // any 8 weights of its block to any MMA slot as long as the B fragment uses the same
 // permutation (Decoder::k_of); that is what keeps the per-weight instruction count low.
 //
-// Data movement: a CTA walks tiles of 8*RG contiguous rows, copies each tile into shared memory
-// with 16-byte cp.async chunks through a ring of stages and decodes from there; chunks that
-// would cross the ends of the tensor are copied with guarded 2-byte loads, so no byte outside
-// [encoded, encoded + rows*row_bytes) is ever read.
+// Data movement: every warp owns a private ring of staging slots in shared memory. A unit is 8
+// rows x up to 4 superblocks; the warp copies it with 16-byte cp.async chunks (lanes 4 wide along
+// a row, 8 rows per instruction), keeps two units in flight while it decodes a third, and needs
+// only __syncwarp between copy and use. Chunks that would cross the ends of the tensor are copied
+// with guarded 2-byte loads, so no byte outside [encoded, encoded + rows*row_bytes) is ever read.
+// The activation (B operand) lives in shared memory once per CTA - the fp16 image of a bf16-exact
+// row, or the three fp16 pieces of an f32 row - and each MMA fetches its fragment from there.
+// K is split over the warps of a CTA when a matrix has too few rows to occupy the device
+// otherwise; the partial dots meet in shared memory once per 8*RG rows.
 #pragma once
 #include "qtype_decode.cuh"
 
 namespace yb {
 
-constexpr int kGemvStages = 4;
-constexpr int kSliceBlocks = 2;                    // 512 weights per warp K-slice
-constexpr int kMaxSlices = 16;                     // K <= 8192 on this path
-constexpr int kMaxSums = 8192 / 16;
+constexpr int kChunkBlocks = 4;                    // superblocks per staged unit (1024 weights x 8 rows)
+constexpr int kRingDepth = 3;                      // staged units per warp: one in use, two in flight
+constexpr int kMaxK = 8192;                        // widest row on this path
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
     uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -48,25 +52,18 @@ __device__ __forceinline__ void mma_f16(float (&d)[4], const uint32_t (&a)[4], u
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Copies global bytes [src, src+bytes) so that byte `src` lands at dst + (src & 15); only bytes
-// inside [lo, hi) are dereferenced. All threads of the CTA take part; the caller commits.
-__device__ __forceinline__ void stage_span(uint8_t *dst, const uint8_t *src, uint64_t bytes,
-                                           const uint8_t *lo, const uint8_t *hi) {
-    const uint8_t *first = src - (reinterpret_cast<uintptr_t>(src) & 15u);
-    const uint64_t chunks = (static_cast<uint64_t>(src - first) + bytes + 15u) >> 4;
-    for (uint64_t c = threadIdx.x; c < chunks; c += blockDim.x) {
-        const uint8_t *g = first + (c << 4);
-        uint8_t *s = dst + (c << 4);
-        if (g >= lo && g + 16 <= hi) {
-            cp_async16(s, g);
-        } else {
-#pragma unroll
-            for (int b = 0; b < 16; b += 2)
-                if (g + b >= lo && g + b + 2 <= hi)
-                    *reinterpret_cast<uint16_t *>(s + b) = ldg_u16(g + b);
-        }
+// The activation fragment source of one lane: `p` points at this lane's fp16 piece array at the
+// first k of the current superblock and moves on by `stride` halves per superblock; lanes that
+// own a zero column of B point at a block of zeros and stand still (stride 0), so the fetch needs
+// no branch. `hi` selects the second half of each 8-weight group.
+struct BLane {
+    const __half *p;
+    int stride, t, hi;
+    template <class Dec> __device__ __forceinline__ uint2 get(int half, int j) const {
+        return *reinterpret_cast<const uint2 *>(p + Dec::k_of(half, t, j, hi));
     }
-}
+};
+constexpr int kZeroHalves = 256;                   // zeros every k_of() offset of one superblock can index
 
 // Lookup tables every decoder shares, resident in shared memory for the life of the CTA.
 struct MmaTables {
@@ -113,7 +110,7 @@ struct Iq2Decoder {
     __device__ static int k_of(int half, int t, int j, int hi) { return 128 * half + 32 * t + 8 * j + 4 * hi; }
 
     __device__ static void half_block(const uint8_t *blk, int half, int t, const MmaTables *tab,
-                                      const uint32_t (*bfrag)[2], float (&d)[4], float &, const float *) {
+                                      const BLane &b, float (&d)[4], float &, const float *) {
         const uint8_t *p = blk + 2 + 8 * (4 * half + t);
         const uintptr_t a = reinterpret_cast<uintptr_t>(p);
         const uint32_t *w = reinterpret_cast<const uint32_t *>(a & ~static_cast<uintptr_t>(3));
@@ -132,7 +129,8 @@ struct Iq2Decoder {
             uint32_t afrag[4];
             bytes_to_scaled_half2(u_lo, sc2, nb2, afrag[0], afrag[2]);
             bytes_to_scaled_half2(u_hi, sc2, nb2, afrag[1], afrag[3]);
-            mma_f16(d, afrag, bfrag[4 * half + j][0], bfrag[4 * half + j][1]);
+            const uint2 bf = b.get<Iq2Decoder>(half, j);
+            mma_f16(d, afrag, bf.x, bf.y);
         }
     }
 
@@ -163,7 +161,7 @@ struct Q4kDecoder {
     }
 
     __device__ static void half_block(const uint8_t *blk, int half, int t, const MmaTables *tab,
-                                      const uint32_t (*bfrag)[2], float (&d)[4], float &minacc, const float *sums) {
+                                      const BLane &b, float (&d)[4], float &minacc, const float *sums) {
         const int c = 2 * half + (t >> 1);
         uint32_t sc0, m0, sc1, m1;
         scale_min(blk + 4, 2 * c, sc0, m0);
@@ -178,7 +176,8 @@ struct Q4kDecoder {
                                   *reinterpret_cast<const __half2 *>(&s0.y), afrag[0], afrag[2]);
             bytes_to_scaled_half2((w[j] >> 4) & 0x0f0f0f0fu, *reinterpret_cast<const __half2 *>(&s1.x),
                                   *reinterpret_cast<const __half2 *>(&s1.y), afrag[1], afrag[3]);
-            mma_f16(d, afrag, bfrag[4 * half + j][0], bfrag[4 * half + j][1]);
+            const uint2 bf = b.get<Q4kDecoder>(half, j);
+            mma_f16(d, afrag, bf.x, bf.y);
         }
         // one quad thread per sub-block carries its min term: even t -> 2c, odd t -> 2c+1
         minacc = fmaf(static_cast<float>((t & 1) ? m1 : m0), sums[2 * c + (t & 1)], minacc);
@@ -207,7 +206,7 @@ struct Q2kDecoder {
     }
 
     __device__ static void half_block(const uint8_t *blk, int half, int t, const MmaTables *tab,
-                                      const uint32_t (*bfrag)[2], float (&d)[4], float &minacc, const float *sums) {
+                                      const BLane &b, float (&d)[4], float &minacc, const float *sums) {
         const uint32_t *q = reinterpret_cast<const uint32_t *>(blk + 16 + 32 * half + 8 * t);   // 4-byte aligned
         const uint32_t w[2] = {q[0], q[1]};
         uint32_t sb[4];                     // scale bytes of planes 0..3: sub-block 8*half + 2*plane + (t>>1)
@@ -223,7 +222,8 @@ struct Q2kDecoder {
                                   *reinterpret_cast<const __half2 *>(&s0.y), afrag[0], afrag[2]);
             bytes_to_scaled_half2((word >> (2 * p0 + 2)) & 0x03030303u, *reinterpret_cast<const __half2 *>(&s1.x),
                                   *reinterpret_cast<const __half2 *>(&s1.y), afrag[1], afrag[3]);
-            mma_f16(d, afrag, bfrag[4 * half + j][0], bfrag[4 * half + j][1]);
+            const uint2 bf = b.get<Q2kDecoder>(half, j);
+            mma_f16(d, afrag, bf.x, bf.y);
         }
         // min terms: even t carries planes 0,1, odd t planes 2,3 of sub-block column (t>>1)
         const int pb = 2 * (t & 1);
@@ -239,44 +239,95 @@ struct Q2kDecoder {
     }
 };
 
-// ---- B fragments -----------------------------------------------------------------------------------
-// kHalfB = false: x is an f32 row, each thread builds the fp16 piece of its column (3-way split).
-// kHalfB = true : xh is the fp16 image of a bf16-exact row; only columns 0 and 4 are non-zero.
-template <class Dec, bool kHalfB>
-__device__ __forceinline__ void build_bfrag(uint32_t (&bfrag)[8 * kSliceBlocks][2], const float *x, const __half *xh,
-                                            int kbase, int K, int g, int t, int *status) {
+// ---- activation vectors in shared memory ---------------------------------------------------------------
+// Both helpers give each thread 16 consecutive elements per pass, issue all of its global loads
+// before touching the data, and also produce the per-sub-block sums the affine qtypes need
+// (G = 16 or 32 elements per sum, 0 = none). All threads of the CTA take part, every lane runs
+// the same number of passes, the caller synchronises.
+
+// f32 row -> three fp16 piece arrays pieces[0..3K): x = hi + mid*2^-11 + lo*2^-22 (~33 bits).
+template <int G>
+__device__ __forceinline__ void prepare_row_f32(__half *pieces, float *sums, const float *x, int K, int *status) {
+    const int per_pass = 16 * blockDim.x;
+    bool bad = false;
+    for (int base = 0; base < K; base += per_pass) {
+        const int k0 = base + 16 * threadIdx.x;
+        const bool active = k0 < K;
+        float4 v4[4];
 #pragma unroll
-    for (int bl = 0; bl < kSliceBlocks; ++bl)
+        for (int i = 0; i < 4; ++i)
+            v4[i] = active ? __ldg(reinterpret_cast<const float4 *>(x + k0) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float *v = reinterpret_cast<const float *>(v4);
+        __align__(16) __half h[3][16];
+        float s = 0.0f;
 #pragma unroll
-        for (int half = 0; half < 2; ++half)
+        for (int i = 0; i < 16; ++i) {
+            const __half hi = __float2half_rn(v[i]);
+            bad |= !isfinite(v[i]) || __hisinf(hi);
+            const float r1 = (v[i] - __half2float(hi)) * 2048.0f;
+            const __half mid = __float2half_rn(r1);
+            const float r2 = (r1 - __half2float(mid)) * 2048.0f;
+            h[0][i] = hi; h[1][i] = mid; h[2][i] = __float2half_rn(r2);
+            s += v[i];
+        }
+        if (active) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int k = kbase + 256 * bl + Dec::k_of(half, t, j, g >> 2);
-                uint32_t r0 = 0u, r1 = 0u;
-                if (kHalfB) {
-                    if ((g & 3) == 0 && k + 3 < K) {
-                        uint2 v = __ldg(reinterpret_cast<const uint2 *>(xh + k));
-                        r0 = v.x; r1 = v.y;
-                    }
-                } else if ((g & 3) != 3 && k + 3 < K) {
-                    const float4 f = __ldg(reinterpret_cast<const float4 *>(x + k));
-                    const float v[4] = {f.x, f.y, f.z, f.w};
-                    __half h[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        __half hi = __float2half_rn(v[i]);
-                        if (!isfinite(v[i]) || __hisinf(hi)) raise(status, YVEX_B200_STATUS_NUMERIC);
-                        float r1f = (v[i] - __half2float(hi)) * 2048.0f;
-                        __half mid = __float2half_rn(r1f);
-                        float r2f = (r1f - __half2float(mid)) * 2048.0f;
-                        h[i] = (g & 3) == 0 ? hi : (g & 3) == 1 ? mid : __float2half_rn(r2f);
-                    }
-                    r0 = (uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16);
-                    r1 = (uint32_t)__half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16);
-                }
-                bfrag[8 * bl + 4 * half + j][0] = r0;
-                bfrag[8 * bl + 4 * half + j][1] = r1;
+            for (int pc = 0; pc < 3; ++pc) {
+                *reinterpret_cast<uint4 *>(pieces + pc * K + k0) = *reinterpret_cast<const uint4 *>(&h[pc][0]);
+                *reinterpret_cast<uint4 *>(pieces + pc * K + k0 + 8) = *reinterpret_cast<const uint4 *>(&h[pc][8]);
             }
+        }
+        if (G == 16 && active) sums[k0 / 16] = s;
+        if (G == 32) {
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            if (active && !(threadIdx.x & 1)) sums[k0 / 32] = s;
+        }
+    }
+    if (bad) raise(status, YVEX_B200_STATUS_NUMERIC);
+}
+
+// fp16 rows (16-byte aligned, `halves` a multiple of 16, bf16-exact values) -> shared memory.
+template <int G>
+__device__ __forceinline__ void prepare_row_half(__half *dst, float *sums, const __half *src, int halves) {
+    const int per_pass = 16 * blockDim.x;
+    for (int base = 0; base < halves; base += per_pass) {
+        const int k0 = base + 16 * threadIdx.x;
+        const bool active = k0 < halves;
+        uint4 raw[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            raw[i] = active ? __ldg(reinterpret_cast<const uint4 *>(src + k0) + i) : make_uint4(0u, 0u, 0u, 0u);
+        if (active) {
+            *reinterpret_cast<uint4 *>(dst + k0) = raw[0];
+            *reinterpret_cast<uint4 *>(dst + k0 + 8) = raw[1];
+        }
+        if (G != 0) {
+            const __half2 *h2 = reinterpret_cast<const __half2 *>(raw);
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 f = __half22float2(h2[i]);
+                s += f.x + f.y;
+            }
+            if (G == 16 && active) sums[k0 / 16] = s;
+            if (G == 32) {
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                if (active && !(threadIdx.x & 1)) sums[k0 / 32] = s;
+            }
+        }
+    }
+}
+
+// This lane's B source. f32 rows: columns 0-2 / 4-6 carry the three pieces, 3 and 7 are zero.
+// bf16-exact rows: only columns 0 and 4 are non-zero. `zeros`: kZeroHalves zero halves.
+template <bool kHalfB> __device__ __forceinline__ BLane lane_b(const __half *vec, const __half *zeros, int K, int g, int t) {
+    BLane b;
+    b.t = t;
+    b.hi = g >> 2;
+    const bool active = kHalfB ? (g & 3) == 0 : (g & 3) != 3;
+    b.p = !active ? zeros : kHalfB ? vec : vec + (g & 3) * K;
+    b.stride = active ? 256 : 0;
+    return b;
 }
 
 // This thread's share of its matrix row's block dot product, from the drained accumulator.
@@ -286,126 +337,203 @@ template <bool kHalfB> __device__ __forceinline__ float drain(const float (&d)[4
     return t == 0 ? d[0] + d[1] * k11 : t == 1 ? d[0] * k22 : t == 2 ? d[2] + d[3] * k11 : d[2] * k22;
 }
 
-// Per-sub-block sums of an activation row into shared memory (all warps of the CTA cooperate;
-// the caller synchronises before use). G = 32 or 16 elements per sum.
-template <int G> __device__ __forceinline__ void build_sums(float *sums, const float *x, int K) {
-    if (G == 0) return;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    constexpr int GG = G == 0 ? 32 : G;
-    for (int i = warp; i < K / GG; i += nw) {
-        float v = lane < GG ? x[i * GG + lane] : 0.0f;
-        v = warp_sum(v);
-        if (lane == 0) sums[i] = v;
+// ---- per-warp staging ring ---------------------------------------------------------------------------
+template <class Dec> struct UnitGeom {
+    static constexpr int kSlot = (15 + kChunkBlocks * Dec::kBlockBytes + 15) & ~15;   // one row: misalignment + 4 blocks
+    static constexpr int kUnitBytes = 8 * kSlot;
+    static constexpr int kRingBytes = kRingDepth * kUnitBytes;
+    static constexpr int kSumsPerBlock = Dec::kSumGroup ? 256 / Dec::kSumGroup : 0;
+};
+
+// One unit of work of a warp: rows src, src + row_bytes, ... (nrows <= 8 of them are real),
+// nblocks <= kChunkBlocks superblocks each; [lo, hi) bounds the tensor the rows belong to.
+struct Unit {
+    const uint8_t *src, *lo, *hi;
+    uint64_t row_bytes;
+    int nrows, nblocks;
+};
+
+// Copies the unit into `slot`; the byte at address a of row r lands at slot + r*kSlot + (a - a16)
+// where a16 is the row start rounded down to 16. The caller commits the cp.async group.
+template <class Dec>
+__device__ __forceinline__ void stage_unit(uint8_t *slot, const Unit &u, int lane) {
+    const int r = lane >> 2;
+    if (r < u.nrows) {
+        const uint8_t *s = u.src + (uint64_t)r * u.row_bytes;
+        const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(s) & 15u);
+        const uint8_t *first = s - mis;
+        const int chunks = (int)((mis + (uint32_t)u.nblocks * Dec::kBlockBytes + 15u) >> 4);
+        uint8_t *d = slot + r * UnitGeom<Dec>::kSlot;
+        for (int c = lane & 3; c < chunks; c += 4) {
+            const uint8_t *gp = first + 16 * c;
+            if (gp >= u.lo && gp + 16 <= u.hi) {
+                cp_async16(d + 16 * c, gp);
+            } else {
+#pragma unroll
+                for (int b = 0; b < 16; b += 2)
+                    if (gp + b >= u.lo && gp + b + 2 <= u.hi)
+                        *reinterpret_cast<uint16_t *>(d + 16 * c + b) = ldg_u16(gp + b);
+            }
+        }
     }
 }
 
-// One warp: partial dots of its 8 rows over its K-slice, read from the staged tile. `sums` points
-// at the activation sums of the slice's first block.
+// Partial dot products of the unit's 8 rows with the activation: the return value is this
+// thread's share of row g (sum the four threads of a quad). `b` and `sums` point at the unit's
+// first superblock.
 template <class Dec, bool kHalfB>
-__device__ __forceinline__ float warp_slice_dot(const uint8_t *row, int blocks, const MmaTables *tab,
-                                                const uint32_t (&bfrag)[8 * kSliceBlocks][2], const float *sums,
-                                                int t, bool row_valid, int *status) {
-    constexpr int kSumsPerBlock = Dec::kSumGroup ? 256 / Dec::kSumGroup : 0;
+__device__ __forceinline__ float unit_dot(const uint8_t *slot, const Unit &u, const MmaTables *tab, BLane b,
+                                          const float *sums, int g, int t, int *status) {
+    const uint8_t *row = slot + g * UnitGeom<Dec>::kSlot +
+                         (reinterpret_cast<uintptr_t>(u.src + (uint64_t)g * u.row_bytes) & 15u);
     float acc = 0.0f;
 #pragma unroll
-    for (int bl = 0; bl < kSliceBlocks; ++bl) {
-        if (bl < blocks) {
+    for (int bl = 0; bl < kChunkBlocks; ++bl) {
+        if (bl < u.nblocks) {
             const uint8_t *blk = row + bl * Dec::kBlockBytes;
             float d[4] = {0.f, 0.f, 0.f, 0.f}, minacc = 0.0f;
-            Dec::half_block(blk, 0, t, tab, &bfrag[8 * bl], d, minacc, sums + bl * kSumsPerBlock);
-            Dec::half_block(blk, 1, t, tab, &bfrag[8 * bl], d, minacc, sums + bl * kSumsPerBlock);
+            Dec::half_block(blk, 0, t, tab, b, d, minacc, sums);
+            Dec::half_block(blk, 1, t, tab, b, d, minacc, sums);
             bool bad;
             acc += Dec::finish(blk, drain<kHalfB>(d, t), minacc, bad);
-            if (bad && row_valid) raise(status, YVEX_B200_STATUS_NUMERIC);
+            if (bad && g < u.nrows) raise(status, YVEX_B200_STATUS_NUMERIC);
+            b.p += b.stride;
+            sums += UnitGeom<Dec>::kSumsPerBlock;
         }
     }
     return acc;
 }
 
+// The ring itself: issue() stages the next unit (or nothing) and commits one group; front() waits
+// until the oldest staged unit has landed; pop() lets its slot be reused.
+template <class Dec> struct WarpRing {
+    uint8_t *base;
+    int head, tail, lane;
+    __device__ __forceinline__ void init(uint8_t *b, int l) { base = b; head = tail = 0; lane = l; }
+    __device__ __forceinline__ void issue(const Unit *u) {
+        if (u) stage_unit<Dec>(base + head * UnitGeom<Dec>::kUnitBytes, *u, lane);
+        cp_async_commit();
+        head = head + 1 == kRingDepth ? 0 : head + 1;
+    }
+    __device__ __forceinline__ const uint8_t *front() {
+        cp_async_wait<kRingDepth - 1>();
+        __syncwarp();
+        return base + tail * UnitGeom<Dec>::kUnitBytes;
+    }
+    __device__ __forceinline__ void pop() {
+        __syncwarp();
+        tail = tail + 1 == kRingDepth ? 0 : tail + 1;
+    }
+};
+
+// ---- plain matvec ------------------------------------------------------------------------------------
 struct GemvMmaParams {
     const uint8_t *enc;
     uint64_t rows, row_bytes;
-    int K, slices, row_groups;
-    const float *x, *additive;
+    int K, slices, slice_blocks, row_groups;
+    const float *x, *additive;          // blockIdx.y selects the input row: x + y*K, additive/out + y*rows
     float *out;
     int round_bf16;
     int *status;
-    uint32_t stage_bytes;
 };
 
-// Shared-memory carve-up common to the kernels built on this engine.
-struct MmaSmem {
-    MmaTables tab;
-    float red[8 * kMaxSlices * 4];     // [row_groups][slices][8] partial dots
-    float sums[kMaxSums];              // activation sums per sub-block (affine qtypes)
-};
+// Shared memory: tables | zeros | activation pieces [3][K] fp16 | sums [K/16] f32 | red [2][warps*8] f32 | rings
+__host__ __device__ inline size_t gemv_smem_fixed(int K, int warps) {
+    return sizeof(MmaTables) + kZeroHalves * 2 + (size_t)3 * K * 2 + (size_t)(K / 16) * 4 + (size_t)2 * warps * 8 * 4;
+}
 
 template <class Dec>
 __global__ void __launch_bounds__(512) gemv_mma_kernel(GemvMmaParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
-    MmaSmem *sm = reinterpret_cast<MmaSmem *>(smem);
-    uint8_t *stages = smem + sizeof(MmaSmem);
+    MmaTables *tab = reinterpret_cast<MmaTables *>(smem);
+    __half *zeros = reinterpret_cast<__half *>(smem + sizeof(MmaTables));
+    __half *pieces = zeros + kZeroHalves;
+    float *sums = reinterpret_cast<float *>(pieces + 3 * p.K);
+    const int warps = blockDim.x >> 5;
+    float *red = sums + p.K / 16;
+    uint8_t *rings = reinterpret_cast<uint8_t *>(red + 2 * warps * 8);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int slice = warp % p.slices, rg = warp / p.slices;
-    const int tile_rows = 8 * p.row_groups;
-    const uint64_t tiles = (p.rows + tile_rows - 1) / tile_rows;
+    const int sl = warp % p.slices, rg = warp / p.slices;
+    const int nblk = p.K / 256;
+    const int my_first = sl * p.slice_blocks;
+    const int my_blocks = min(p.slice_blocks, nblk - my_first);
+    const int nu = (my_blocks + kChunkBlocks - 1) / kChunkBlocks;             // units per task for this warp
+    const uint64_t octets = (p.rows + 7) / 8, ctasks = (octets + p.row_groups - 1) / p.row_groups;
+    const float *x = p.x + (uint64_t)blockIdx.y * p.K;
+    const float *additive = p.additive ? p.additive + (uint64_t)blockIdx.y * p.rows : nullptr;
+    float *out = p.out + (uint64_t)blockIdx.y * p.rows;
     const uint8_t *lo = p.enc, *hi = p.enc + p.rows * p.row_bytes;
-    load_tables(&sm->tab, Dec::kBias);
-    build_sums<Dec::kSumGroup>(sm->sums, p.x, p.K);
-    uint32_t bfrag[8 * kSliceBlocks][2];
-    build_bfrag<Dec, false>(bfrag, p.x, nullptr, slice * 256 * kSliceBlocks, p.K, g, t, p.status);
-    const int nblocks = p.K / 256;
-    const int my_blocks = min(kSliceBlocks, nblocks - slice * kSliceBlocks);
-    constexpr int kSumsPerBlock = Dec::kSumGroup ? 256 / Dec::kSumGroup : 0;
 
-    auto issue = [&](uint64_t tile, int stage) {
-        if (tile < tiles) {
-            uint64_t r0 = tile * tile_rows;
-            uint64_t n = p.rows - r0 < (uint64_t)tile_rows ? p.rows - r0 : (uint64_t)tile_rows;
-            stage_span(stages + (size_t)stage * p.stage_bytes, p.enc + r0 * p.row_bytes, n * p.row_bytes, lo, hi);
-        }
-        cp_async_commit();
+    auto unit_at = [&](uint64_t ct, int ui, Unit &u) {
+        const uint64_t r0 = (ct * p.row_groups + rg) * 8;
+        if (ct >= ctasks || r0 >= p.rows) return false;
+        u.nrows = (int)(p.rows - r0 < 8 ? p.rows - r0 : 8);
+        u.nblocks = min(kChunkBlocks, my_blocks - ui * kChunkBlocks);
+        u.row_bytes = p.row_bytes;
+        u.src = p.enc + r0 * p.row_bytes + (uint64_t)(my_first + ui * kChunkBlocks) * Dec::kBlockBytes;
+        u.lo = lo; u.hi = hi;
+        return true;
     };
-    uint64_t tile = blockIdx.x;
+    // weight bytes first: the staging ring fills while the tables and the activation are prepared
+    WarpRing<Dec> ring;
+    ring.init(rings + (size_t)warp * UnitGeom<Dec>::kRingBytes, lane);
+    uint64_t ict = blockIdx.x;
+    int iui = 0;
+    auto issue_next = [&]() {
+        Unit u;
+        const bool any = nu > 0 && unit_at(ict, iui, u);
+        ring.issue(any ? &u : nullptr);
+        if (++iui >= nu) { iui = 0; ict += gridDim.x; }
+    };
 #pragma unroll
-    for (int s = 0; s < kGemvStages - 1; ++s) issue(tile + (uint64_t)s * gridDim.x, s);
-    for (int it = 0; tile < tiles; tile += gridDim.x, ++it) {
-        issue(tile + (uint64_t)(kGemvStages - 1) * gridDim.x, (it + kGemvStages - 1) % kGemvStages);
-        cp_async_wait<kGemvStages - 1>();
+    for (int d = 0; d < kRingDepth - 1; ++d) issue_next();
+    load_tables(tab, Dec::kBias);
+    for (int i = threadIdx.x; i < kZeroHalves / 2; i += blockDim.x) reinterpret_cast<uint32_t *>(zeros)[i] = 0u;
+    prepare_row_f32<Dec::kSumGroup>(pieces, sums, x, p.K, p.status);
+    __syncthreads();
+    const BLane b0 = lane_b<false>(pieces, zeros, p.K, g, t);
+
+    int par = 0;
+    for (uint64_t ct = blockIdx.x; ct < ctasks; ct += gridDim.x, par ^= 1) {
+        float acc = 0.0f;
+        for (int ui = 0; ui < nu; ++ui) {
+            issue_next();
+            const uint8_t *slot = ring.front();
+            Unit u;
+            if (unit_at(ct, ui, u)) {
+                BLane b = b0;
+                const int kb = my_first + ui * kChunkBlocks;
+                b.p += b.stride * kb;
+                acc += unit_dot<Dec, false>(slot, u, tab, b, sums + kb * UnitGeom<Dec>::kSumsPerBlock, g, t, p.status);
+            }
+            ring.pop();
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        if (t == 0) red[(par * warps + warp) * 8 + g] = acc;
         __syncthreads();
-        const uint64_t r0 = tile * tile_rows;
-        const uint8_t *src = p.enc + r0 * p.row_bytes;
-        const uint8_t *base = stages + (size_t)(it % kGemvStages) * p.stage_bytes +
-                              (reinterpret_cast<uintptr_t>(src) & 15u);
-        const uint64_t row = r0 + 8 * rg + g;
-        const bool valid = row < p.rows;
-        const uint8_t *rowp = base + (size_t)(8 * rg + g) * p.row_bytes +
-                              (size_t)slice * kSliceBlocks * Dec::kBlockBytes;
-        float part = warp_slice_dot<Dec, false>(rowp, my_blocks, &sm->tab, bfrag,
-                                                sm->sums + slice * kSliceBlocks * kSumsPerBlock, t, valid, p.status);
-        part += __shfl_xor_sync(0xffffffffu, part, 1);
-        part += __shfl_xor_sync(0xffffffffu, part, 2);
-        if (t == 0) sm->red[(rg * p.slices + slice) * 8 + g] = part;
-        __syncthreads();
-        if (threadIdx.x < tile_rows) {
+        if (threadIdx.x < 8 * p.row_groups) {
             const int rrg = threadIdx.x >> 3, rgi = threadIdx.x & 7;
-            const uint64_t orow = r0 + threadIdx.x;
+            const uint64_t orow = (ct * p.row_groups + rrg) * 8 + rgi;
             if (orow < p.rows) {
                 float sum = 0.0f;
-                for (int s = 0; s < p.slices; ++s) sum += sm->red[(rrg * p.slices + s) * 8 + rgi];
-                if (p.additive) sum += p.additive[orow];
+                for (int s = 0; s < p.slices; ++s) sum += red[(par * warps + rrg * p.slices + s) * 8 + rgi];
+                if (additive) sum += additive[orow];
                 if (!isfinite(sum)) raise(p.status, YVEX_B200_STATUS_NUMERIC);
-                p.out[orow] = p.round_bf16 ? bf16_round(sum) : sum;
+                out[orow] = p.round_bf16 ? bf16_round(sum) : sum;
             }
         }
     }
     cp_async_wait<0>();
 }
 
-// K-slices (warps along K) and row groups (8-row sets per CTA) for a row width.
-inline void mma_shape(uint64_t width, int &slices, int &row_groups) {
-    slices = (int)((width / 256 + kSliceBlocks - 1) / kSliceBlocks);
-    row_groups = slices >= 8 ? 1 : slices >= 4 ? 2 : 4;
+// K-slices (warps along K), superblocks per slice and row groups (8-row sets per CTA task).
+inline void mma_shape(uint64_t width, int &slices, int &slice_blocks, int &row_groups) {
+    const int nblk = (int)(width / 256);
+    slice_blocks = kChunkBlocks;
+    slices = (nblk + slice_blocks - 1) / slice_blocks;
+    slice_blocks = (nblk + slices - 1) / slices;            // even the slices out (6 blocks -> 3 + 3)
+    row_groups = slices >= 8 ? 1 : slices >= 4 ? 2 : slices >= 2 ? 4 : 8;
 }
 
 inline bool mma_decoder_for(unsigned q) { return q == Q_IQ2_XXS || q == Q_Q4_K || q == Q_Q2_K; }
@@ -413,8 +541,8 @@ inline bool mma_decoder_for(unsigned q) { return q == Q_IQ2_XXS || q == Q_Q4_K |
 inline bool gemv_mma_eligible(unsigned q, uint64_t rows, uint64_t width, const uint8_t *enc) {
     (void)rows;
     const uintptr_t align = q == Q_Q4_K ? 15u : q == Q_Q2_K ? 3u : 1u;
-    return mma_decoder_for(q) && width % 256 == 0 && width / 256 <= kMaxSlices * kSliceBlocks &&
-           (reinterpret_cast<uintptr_t>(enc) & align) == 0;   // callers also need a 16-byte aligned x
+    return mma_decoder_for(q) && width % 256 == 0 && width <= (uint64_t)kMaxK &&
+           (reinterpret_cast<uintptr_t>(enc) & align) == 0;
 }
 
 template <class Kernel> inline int mma_opt_in(Kernel kernel) {
@@ -424,37 +552,38 @@ template <class Kernel> inline int mma_opt_in(Kernel kernel) {
 
 template <class Dec>
 inline int gemv_mma_launch_t(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row_bytes,
-                             const float *x, const float *additive, float *out, int round_bf16,
+                             const float *x, uint64_t input_rows, const float *additive, float *out, int round_bf16,
                              int *status, cudaStream_t stream) {
     GemvMmaParams p{};
     p.enc = enc; p.rows = rows; p.row_bytes = row_bytes; p.K = (int)width;
-    mma_shape(width, p.slices, p.row_groups);
+    mma_shape(width, p.slices, p.slice_blocks, p.row_groups);
     p.x = x; p.additive = additive; p.out = out; p.round_bf16 = round_bf16; p.status = status;
-    const int tile_rows = 8 * p.row_groups;
-    p.stage_bytes = (uint32_t)(((uint64_t)tile_rows * row_bytes + 16 + 15) & ~15ull);
-    size_t smem = sizeof(MmaSmem) + (size_t)kGemvStages * p.stage_bytes;
+    const int warps = p.slices * p.row_groups;
+    const size_t smem = ((gemv_smem_fixed(p.K, warps) + 15) & ~(size_t)15) + (size_t)warps * UnitGeom<Dec>::kRingBytes;
     static bool configured = false;
     if (!configured) {
         if (mma_opt_in(gemv_mma_kernel<Dec>) != OK) return ERR_BACKEND;
         configured = true;
     }
-    if (smem > 200 * 1024) return ERR_BOUNDS;
-    uint64_t tiles = (rows + tile_rows - 1) / tile_rows;
-    int grid = (int)(tiles < (uint64_t)kSmCount * 2 ? tiles : (uint64_t)kSmCount * 2);
-    gemv_mma_kernel<Dec><<<grid, 32 * p.slices * p.row_groups, smem, stream>>>(p);
+    if (smem > 200 * 1024 || warps > 16 || input_rows > 65535) return ERR_BOUNDS;
+    const uint64_t ctasks = ((rows + 7) / 8 + p.row_groups - 1) / p.row_groups;
+    const int per_sm = smem > 100 * 1024 ? 1 : 2;
+    const uint64_t cap = (uint64_t)kSmCount * per_sm;
+    dim3 grid((unsigned)(ctasks < cap ? ctasks : cap), (unsigned)input_rows);
+    gemv_mma_kernel<Dec><<<grid, 32 * warps, smem, stream>>>(p);
     return launch_status();
 }
 
 inline int gemv_mma_launch(unsigned q, const uint8_t *enc, uint64_t rows, uint64_t width,
-                           uint64_t row_bytes, const float *x, const float *additive, float *out,
+                           uint64_t row_bytes, const float *x, uint64_t input_rows, const float *additive, float *out,
                            int round_bf16, int *status, cudaStream_t stream) {
     switch (q) {
     case Q_IQ2_XXS:
-        return gemv_mma_launch_t<Iq2Decoder>(enc, rows, width, row_bytes, x, additive, out, round_bf16, status, stream);
+        return gemv_mma_launch_t<Iq2Decoder>(enc, rows, width, row_bytes, x, input_rows, additive, out, round_bf16, status, stream);
     case Q_Q4_K:
-        return gemv_mma_launch_t<Q4kDecoder>(enc, rows, width, row_bytes, x, additive, out, round_bf16, status, stream);
+        return gemv_mma_launch_t<Q4kDecoder>(enc, rows, width, row_bytes, x, input_rows, additive, out, round_bf16, status, stream);
     case Q_Q2_K:
-        return gemv_mma_launch_t<Q2kDecoder>(enc, rows, width, row_bytes, x, additive, out, round_bf16, status, stream);
+        return gemv_mma_launch_t<Q2kDecoder>(enc, rows, width, row_bytes, x, input_rows, additive, out, round_bf16, status, stream);
     default:
         return ERR_UNSUPPORTED;
     }
