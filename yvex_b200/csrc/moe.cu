@@ -42,8 +42,65 @@ __global__ void router_logits_kernel(const float *router, const float *xr, uint6
     }
 }
 
+// ---- decode-width router: ingress rounding + projection + score in one launch ---------------------
+// One CTA per (expert, row): dot of the expert's router row with the bf16-rounded input in double
+// (same arithmetic as router_logits_kernel), then score = sqrt(softplus(logit)) in double
+// (src/graph/moe.c:497-512) so that the top-k kernel only compares. Every CTA also writes its
+// interleaved share of the rounded row (f32 and its fp16 image) for the expert kernels.
+constexpr int kRouterThreads = 128;
+__global__ void __launch_bounds__(kRouterThreads)
+ingress_router_kernel(const float *router, const float *x, uint64_t experts, uint64_t hidden, float *xr, __half *xr_h,
+                      float *logits, float *scores, int *status) {
+    const uint64_t e = blockIdx.x, r = blockIdx.y;
+    const float *w = router + e * hidden, *xrow = x + r * hidden;
+    bool bad = false;
+    for (uint64_t k = e * kRouterThreads + threadIdx.x; k < hidden; k += experts * kRouterThreads) {
+        float v = xrow[k];
+        bad |= !isfinite(v);
+        v = bf16_round(v);
+        xr[r * hidden + k] = v;
+        xr_h[r * hidden + k] = __float2half_rn(v);
+    }
+    double acc = 0.0;
+    const uint64_t vec = hidden / 4;            // float4 groups (hidden is a multiple of the block width)
+    for (uint64_t base = 0; base < vec; base += 4 * kRouterThreads) {
+        float4 wv[4], xv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint64_t at = base + (uint64_t)i * kRouterThreads + threadIdx.x;
+            const bool in = at < vec;
+            wv[i] = in ? __ldg(reinterpret_cast<const float4 *>(w) + at) : make_float4(0.f, 0.f, 0.f, 0.f);
+            xv[i] = in ? __ldg(reinterpret_cast<const float4 *>(xrow) + at) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            acc += (double)wv[i].x * (double)bf16_round(xv[i].x);
+            acc += (double)wv[i].y * (double)bf16_round(xv[i].y);
+            acc += (double)wv[i].z * (double)bf16_round(xv[i].z);
+            acc += (double)wv[i].w * (double)bf16_round(xv[i].w);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    __shared__ double part[kRouterThreads / 32];
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+    if (bad) raise(status, YVEX_B200_STATUS_NUMERIC);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double total = 0.0;
+        for (int i = 0; i < kRouterThreads / 32; ++i) total += part[i];
+        const float logit = (float)total;
+        const double v = logit;
+        const double sp = v > 0.0 ? v + log1p(exp(-v)) : log1p(exp(v));
+        const double sc = sqrt(sp);
+        if (!isfinite(logit) || !isfinite(sc)) raise(status, YVEX_B200_STATUS_NUMERIC);
+        logits[r * experts + e] = logit;
+        scores[r * experts + e] = (float)sc;
+    }
+}
+
 // ---- scoring + top-k: one warp per row, experts <= 256 (8 per lane), topk <= 16 ------------------
-__global__ void route_rows_kernel(MoeGeom g, const float *logits, const float *bias,
+__global__ void route_rows_kernel(MoeGeom g, const float *logits, const float *scores_in, const float *bias,
                                   const int32_t *hash_table, const uint32_t *token_ids,
                                   uint64_t rows, int32_t *selected, float *weights, int *status) {
     const int lane = threadIdx.x & 31;
@@ -56,11 +113,15 @@ __global__ void route_rows_kernel(MoeGeom g, const float *logits, const float *b
         score[i] = 0.0f;
         biased[i] = -INFINITY;
         if (e < g.experts) {
-            double v = logits[row * g.experts + e];
-            double sp = v > 0.0 ? v + log1p(exp(-v)) : log1p(exp(v));
-            double s = sqrt(sp);
-            if (!isfinite(s)) raise(status, YVEX_B200_STATUS_NUMERIC);
-            score[i] = (float)s;
+            if (scores_in) {
+                score[i] = scores_in[row * g.experts + e];
+            } else {
+                double v = logits[row * g.experts + e];
+                double sp = v > 0.0 ? v + log1p(exp(-v)) : log1p(exp(v));
+                double s = sqrt(sp);
+                if (!isfinite(s)) raise(status, YVEX_B200_STATUS_NUMERIC);
+                score[i] = (float)s;
+            }
             biased[i] = (bias ? bias[e] : 0.0f) + score[i];
         }
     }
@@ -236,7 +297,7 @@ static int route_into(const MoeGeom &g, const yvex_b200_moe_weights *w, const fl
     } else if (!logits_in) {
         return ERR_INVALID_ARG;
     }
-    route_rows_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(g, logits, w->bias, w->hash_table, token_ids, rows,
+    route_rows_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(g, logits, nullptr, w->bias, w->hash_table, token_ids, rows,
                                                                 selected, weights, status);
     return launch_status(launches);
 }
@@ -245,6 +306,15 @@ int yb::moe_ingress_and_route(const MoeGeom &g, const MoeWeights &w, const MoeWo
                               const float *logits, const uint32_t *token_ids, uint64_t rows, int *status,
                               cudaStream_t s) {
     const uint64_t n = rows * g.hidden;
+    if (w.router && rows <= 64 && g.hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+        (reinterpret_cast<uintptr_t>(w.router) & 15u) == 0) {
+        // decode width: two launches (projection with ingress rounding and scoring fused; top-k)
+        ingress_router_kernel<<<dim3((unsigned)g.experts, (unsigned)rows), kRouterThreads, 0, s>>>(
+            w.router, x, g.experts, g.hidden, ws.xr, ws.xr_h, ws.logits, ws.scores, status);
+        route_rows_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(g, ws.logits, ws.scores, w.bias, w.hash_table, token_ids,
+                                                                    rows, ws.selected, ws.weights, status);
+        return launch_status(2);
+    }
     ingress_round_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>(x, ws.xr, ws.xr_h, n, status);
     int rc = launch_status(1);
     if (rc != OK) return rc;

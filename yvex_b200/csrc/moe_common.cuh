@@ -23,6 +23,7 @@ __device__ __forceinline__ float swiglu_mid(float g, float u, float route_weight
 struct MoeWorkspace {
     float *xr;          // [rows x hidden]  bf16-exact ingress rows
     float *logits;      // [rows x experts]
+    float *scores;      // [rows x experts]  sqrt(softplus(logit)) when the router projection ran on device
     int32_t *selected;  // [rows x topk]
     float *weights;     // [rows x topk]
     float *mid;         // [rows x (topk+1) x max(inter, shared_inter)]  SwiGLU intermediates
@@ -34,6 +35,7 @@ struct MoeWorkspace {
         mid_h = reinterpret_cast<__half *>(b + reinterpret_cast<uintptr_t>(mid_h));
         xr = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(xr));
         logits = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(logits));
+        scores = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(scores));
         selected = reinterpret_cast<int32_t *>(b + reinterpret_cast<uintptr_t>(selected));
         weights = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(weights));
         mid = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(mid));
@@ -48,6 +50,7 @@ inline uint64_t moe_workspace_layout(const MoeGeom &g, uint64_t rows, MoeWorkspa
     MoeWorkspace l;
     l.xr = reinterpret_cast<float *>(take(rows * g.hidden * 4));
     l.logits = reinterpret_cast<float *>(take(rows * g.experts * 4));
+    l.scores = reinterpret_cast<float *>(take(rows * g.experts * 4));
     l.selected = reinterpret_cast<int32_t *>(take(rows * g.topk * 4));
     l.weights = reinterpret_cast<float *>(take(rows * g.topk * 4));
     l.mid = reinterpret_cast<float *>(take(rows * (g.topk + 1) * imax * 4));
