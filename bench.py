@@ -388,6 +388,17 @@ def run_native_ep(args):
     def step(i):
         return layer.forward(x, lg)[0]
 
+    if world == 1:
+        # One GPU owns every expert: nothing to exchange, so the step is the single-device wide layer
+        # (routed and shared experts in the same grouped GEMM launches).
+        weights_full = lib.weights_of(wl.tensors)
+        ws_wide = torch.empty(lib.moe_workspace_bytes(geom_full, T, True), dtype=torch.uint8, device=dev)
+        out_dev = torch.empty((T, H), dtype=torch.float32, device=dev)
+
+        def step(i):  # noqa: F811
+            lib.moe_layer(geom_full, weights_full, x, status, logits=lg, wide=True, workspace=ws_wide, out=out_dev)
+            return out_dev
+
     def step_e2e(i):
         dev_x.copy_(host_x, non_blocking=True)
         dev_lg.copy_(host_lg, non_blocking=True)
@@ -470,12 +481,27 @@ def run_native_ep(args):
                 return y
             return real_rows(rows_h, ids, wts)
 
-        ops.expert_rows = probed
-        for i in range(min(args.steps, 5)):
-            probed.done = False
-            flush.fill_(i & 0xFF)
-            step(i)
-        ops.expert_rows = real_rows
+        if world == 1:
+            for i in range(min(args.steps, 5)):
+                evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_ph)]
+                for e in evs:
+                    e.record()
+                arr = (C.c_void_p * n_ph)(*[e.cuda_event for e in evs])
+                flush.fill_(i & 0xFF)
+                lib.lib.yvex_b200_phase_events(arr, n_ph)
+                step(i)
+                lib.lib.yvex_b200_phase_events(None, 0)
+                torch.cuda.synchronize()
+                gemm_ms[0].append(evs[2].elapsed_time(evs[3]))
+                gemm_ms[1].append(evs[3].elapsed_time(evs[4]))
+                pair_counts.append(T * (spec.topk + 1))
+        else:
+            ops.expert_rows = probed
+            for i in range(min(args.steps, 5)):
+                probed.done = False
+                flush.fill_(i & 0xFF)
+                step(i)
+            ops.expert_rows = real_rows
         torch.cuda.synchronize()
     if status.read() != 0:
         raise RuntimeError(f"device status word = {status.read()} after the timed region")
@@ -513,7 +539,8 @@ def run_native_ep(args):
                 "data": "synthetic",
                 "config": {"workload": wl.name, **cfg, "gate_up_qtype": "IQ2_XXS", "down_qtype": "Q4_K",
                            "l2": "flushed between steps (256 MiB rewrite)",
-                           "parallelism": f"ep{world}: {e_loc} experts and {t_loc} tokens per rank, NCCL all-to-all-v"},
+                           "parallelism": (f"ep{world}: {e_loc} experts and {t_loc} tokens per rank, NCCL all-to-all-v" if world > 1
+                                           else "ep1: all experts on one device, fused wide layer, no exchange")},
                 "clocks": clocks.summary(),
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(T * (H + E) * 4),
                         "d2h_bytes_per_step": int(T * H * 4), "api": e2e_api},
