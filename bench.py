@@ -29,6 +29,11 @@ METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 
 
+# DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
+# profiles/ (dram__bytes_read.sum + dram__bytes_write.sum, one capture per workload).
+TRAFFIC = {"c1": 4389376, "c2": 22777600, "c3": 483481856, "c4": 2160352104, "c5": 10273500672}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -302,7 +307,8 @@ def run_native(args):
         top = max(flops, key=lambda k: phases[names.index(k)])
         ach = flops[top] / (phases[names.index(top)] * 1e-3) / 1e12
         roofline = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": ach / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"],
+                    "frac": ach / peaks["bf16_tflops"], "traffic": TRAFFIC.get(wl.name) if top == "gate_up_gemm" else None,
+                    "algorithmic_bytes": None, "peak_source": peaks["source"],
                     "peak_sustained": peaks["bf16_tflops_sustained"],
                     "layer_achieved": pairs * 6.0 * wl.cfg["hidden"] * wl.cfg["inter"] / (t_dev / args.steps * 1e-3) / 1e12}
     if not wide:
@@ -311,7 +317,8 @@ def run_native(args):
         top = max(cand, key=lambda k: cand[k][1])
         ach = cand[top][0] / (cand[top][1] * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": top, "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                    "frac": ach / peaks["hbm_gbs"], "traffic": TRAFFIC.get(wl.name) if top == "gate_up" else None,
+                    "algorithmic_bytes": cand[top][0], "peak_source": peaks["source"],
                     "layer_achieved": wl.bytes_per_token_decode() / (t_dev / args.steps * 1e-3) / 1e9}
     if rank == 0:
         cpu = None
@@ -520,7 +527,8 @@ def run_native_ep(args):
         ach = fl / (t_top * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
         roofline = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
-                    "traffic": None, "peak_source": peaks["source"] + " (sustained; burst %.1f)" % peaks["bf16_tflops"],
+                    "traffic": TRAFFIC["c5"] if world == 1 and top == "gate_up_gemm" else None,
+                    "peak_source": peaks["source"] + " (sustained; burst %.1f)" % peaks["bf16_tflops"],
                     "pairs_per_launch": pairs,
                     "layer_achieved": T * (spec.topk + 1) * 6.0 * H * I / world / (t_dev / args.steps * 1e-3) / 1e12}
         cpu = None
@@ -674,7 +682,8 @@ def run_gemv_stream(args):
             "single_launch_us": sorted(one)[len(one) // 2] * 1e3,
             "variants": variants,
             "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<Iq2Decoder>", "achieved": gbs, "peak": peaks["hbm_gbs"],
-                         "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                         "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": TRAFFIC["c1"],
+                         "algorithmic_bytes": rows * rb + 4 * width + 4 * rows, "peak_source": peaks["source"],
                          "frac_of_nominal_8TBs": gbs / 8000.0},
             "cpu_baseline": {"value": (rows * rb + 4 * width + 4 * rows) / t_cpu / 1e9, "unit": "GB/s", "cores": cores,
                              "kind": kind, "sample": "one 4096x4096 IQ2_XXS matvec, rows split over all cores"}}
@@ -764,7 +773,8 @@ def run_attention(args):
             "gpu_launches": int(launches),
             "sessions_per_s": S / t,
             "roofline": {"bound": "hbm", "kernel": "gqa_decode_kernel<128,4>", "achieved": gbs, "peak": peaks["hbm_gbs"],
-                         "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]},
+                         "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": TRAFFIC["c4"], "algorithmic_bytes": algo,
+                         "peak_source": peaks["source"]},
             "cpu_baseline": {"value": (algo / S) / t_cpu / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
                              "sample": "one of the 16 sessions (32 heads x 32768 keys), heads split over all cores"}}
     print(json.dumps(line), flush=True)

@@ -41,7 +41,12 @@ constexpr uint32_t kTmemCols = 512;
 constexpr int kProducerWarps = 8, kRowsPerWarp = kTileM / kProducerWarps;
 constexpr int kScaleRing = 4;                               // superblocks of per-row scales kept for the epilogue
 
-struct ColBlock { int row0, ncols, expert, pad; };          // expert < 0: the shared expert
+// <=128 token rows of one expert (expert < 0: the shared expert). Column blocks of the same expert
+// form groups of at most kGroupBlocks consecutive entries [first, first + count): the tiles of a
+// group are walked weight tile by weight tile, so the CTAs running side by side share one weight
+// tile (read from DRAM once) while the group's activation rows stay in L2.
+struct ColBlock { int row0, ncols, expert, first, count, pad; };
+constexpr int kGroupBlocks = 8;
 
 struct GemmParams {
     const uint8_t *w_routed[2], *w_shared[2];   // packs; 2 matrices (gate, up) or 1 (down)
@@ -254,11 +259,13 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
     const int mtiles = p.M / kTileM, nsb = p.K / 256;
     const long long tiles_total = (long long)ncb * mtiles * p.nmat;
 
-    // Every role walks the same tile sequence: tile -> (column block, matrix, m tile), m fastest.
+    // Every role walks the same tile sequence: group of column blocks -> (matrix, m tile) -> column block.
     auto tile_of = [&](long long t, ColBlock &cb, int &mat, int &mt) {
         const int per_cb = mtiles * p.nmat;
-        cb = p.colblocks[t / per_cb];
-        const int r = (int)(t % per_cb);
+        const ColBlock g0 = p.colblocks[t / per_cb];            // any block of the group names the group
+        const int local = (int)(t - (long long)g0.first * per_cb);
+        const int r = local / g0.count;
+        cb = p.colblocks[g0.first + local % g0.count];
         mat = r / mtiles;
         mt = r % mtiles;
     };
@@ -477,8 +484,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
                     const uint64_t orow = (uint64_t)cb.row0 + 64 * colhalf + i;
                     float v = acc[i];
                     if (!isfinite(v)) raise(p.status, YVEX_B200_STATUS_NUMERIC);
-                    if (p.out_bf16) p.out_bf16[orow * p.M + m] = bf16_bits(v);
-                    else p.out_f32[mat][orow * p.M + m] = v;
+                    // streaming stores: the results are not read again by this kernel and must not push the
+                    // activation tiles and weight rows that other CTAs are about to reuse out of L2
+                    if (p.out_bf16) __stcs(p.out_bf16 + orow * p.M + m, bf16_bits(v));
+                    else __stcs(p.out_f32[mat] + orow * p.M + m, v);
                 }
             }
         }

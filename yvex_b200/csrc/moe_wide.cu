@@ -58,8 +58,12 @@ __global__ void wide_plan_kernel(const int *counts, int experts, uint64_t pairs,
     int off = 0, nb = 0;
     for (int e = 0; e <= experts; ++e) {
         offsets[e] = off;
-        for (int c = 0; c < counts[e]; c += kTileN) {
-            if (nb < max_blocks) blocks[nb] = ColBlock{off + c, min(kTileN, counts[e] - c), e < experts ? e : -1, 0};
+        const int nblocks = (counts[e] + kTileN - 1) / kTileN;
+        for (int b = 0; b < nblocks; ++b) {
+            const int first = nb - b % kGroupBlocks;                        // groups of <= kGroupBlocks blocks
+            const int count = min(kGroupBlocks, nblocks - (b - b % kGroupBlocks));
+            if (nb < max_blocks)
+                blocks[nb] = ColBlock{off + b * kTileN, min(kTileN, counts[e] - b * kTileN), e < experts ? e : -1, first, count, 0};
             ++nb;
         }
         off += counts[e];
