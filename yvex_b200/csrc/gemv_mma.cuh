@@ -31,7 +31,7 @@
 namespace yb {
 
 constexpr int kChunkBlocks = 4;                    // superblocks per staged unit (1024 weights x 8 rows)
-constexpr int kRingDepth = 3;                      // staged units per warp: one in use, two in flight
+constexpr int kRingDepth = 2;                      // staged units per warp: one in use, one in flight (many warps per SM)
 constexpr int kMaxK = 8192;                        // widest row on this path
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
@@ -443,7 +443,7 @@ __host__ __device__ inline size_t gemv_smem_fixed(int K, int warps) {
 }
 
 template <class Dec>
-__global__ void __launch_bounds__(512) gemv_mma_kernel(GemvMmaParams p) {
+__global__ void __launch_bounds__(512, 2) gemv_mma_kernel(GemvMmaParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     MmaTables *tab = reinterpret_cast<MmaTables *>(smem);
     __half *zeros = reinterpret_cast<__half *>(smem + sizeof(MmaTables));
@@ -545,6 +545,15 @@ inline bool gemv_mma_eligible(unsigned q, uint64_t rows, uint64_t width, const u
            (reinterpret_cast<uintptr_t>(enc) & align) == 0;
 }
 
+// Resident CTAs per SM the launch should count on: shared memory and the 64-registers-per-thread
+// budget of these kernels (65536 / (64 * threads)) bound it.
+inline int ctas_per_sm(size_t smem, int threads) {
+    int by_smem = (int)((size_t)(227 * 1024) / (smem + 1024));
+    int by_regs = 65536 / (64 * threads);
+    int n = by_smem < by_regs ? by_smem : by_regs;
+    return n < 1 ? 1 : n > 4 ? 4 : n;
+}
+
 template <class Kernel> inline int mma_opt_in(Kernel kernel) {
     return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess
                ? OK : ERR_BACKEND;
@@ -567,8 +576,7 @@ inline int gemv_mma_launch_t(const uint8_t *enc, uint64_t rows, uint64_t width, 
     }
     if (smem > 200 * 1024 || warps > 16 || input_rows > 65535) return ERR_BOUNDS;
     const uint64_t ctasks = ((rows + 7) / 8 + p.row_groups - 1) / p.row_groups;
-    const int per_sm = smem > 100 * 1024 ? 1 : 2;
-    const uint64_t cap = (uint64_t)kSmCount * per_sm;
+    const uint64_t cap = (uint64_t)kSmCount * ctas_per_sm(smem, 32 * warps);
     dim3 grid((unsigned)(ctasks < cap ? ctasks : cap), (unsigned)input_rows);
     gemv_mma_kernel<Dec><<<grid, 32 * warps, smem, stream>>>(p);
     return launch_status();

@@ -43,7 +43,7 @@ __host__ __device__ inline size_t narrow_smem_fixed(size_t vec_halves, size_t su
 }
 
 template <class Dec>
-__global__ void __launch_bounds__(512) moe_gate_up_mma_kernel(NarrowParams p) {
+__global__ void __launch_bounds__(512, 2) moe_gate_up_mma_kernel(NarrowParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const MoeGeom &g = p.g;
     const int K = (int)g.hidden, nblk = K / 256, warps = blockDim.x >> 5;
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(512) moe_gate_up_mma_kernel(NarrowParams p) {
 }
 
 template <class Dec>
-__global__ void __launch_bounds__(512) moe_down_mma_kernel(NarrowParams p) {
+__global__ void __launch_bounds__(512, 2) moe_down_mma_kernel(NarrowParams p) {
     extern __shared__ __align__(16) uint8_t smem[];
     const MoeGeom &g = p.g;
     const int K = (int)g.inter, nblk = K / 256, warps = blockDim.x >> 5;      // inter == shared_inter on this path
@@ -269,7 +269,7 @@ static int launch_gate_up(NarrowParams &p, cudaStream_t s) {
     if (smem > 200 * 1024 || warps > 16 || p.rows > 65535) return ERR_BOUNDS;
     const uint64_t imax = p.g.inter > p.g.shared_inter ? p.g.inter : p.g.shared_inter;
     const uint64_t tasks = (p.g.topk + 1) * ((imax + 7) / 8);
-    dim3 grid((unsigned)ctas_per_row(p.rows, tasks, smem > 100 * 1024 ? 1 : 2), (unsigned)p.rows);
+    dim3 grid((unsigned)ctas_per_row(p.rows, tasks, ctas_per_sm(smem, 32 * warps)), (unsigned)p.rows);
     moe_gate_up_mma_kernel<Dec><<<grid, 32 * warps, smem, s>>>(p);
     return launch_status(1);
 }
@@ -294,7 +294,7 @@ static int launch_down(NarrowParams &p, cudaStream_t s) {
     if (smem > 200 * 1024 || p.rows > 65535) return ERR_BOUNDS;
     p.down_warps = warps;
     const uint64_t tasks = (p.g.hidden + 7) / 8;
-    dim3 grid((unsigned)ctas_per_row(p.rows, tasks, smem > 100 * 1024 ? 1 : 2), (unsigned)p.rows);
+    dim3 grid((unsigned)ctas_per_row(p.rows, tasks, ctas_per_sm(smem, 32 * warps)), (unsigned)p.rows);
     moe_down_mma_kernel<Dec><<<grid, 32 * warps, smem, s>>>(p);
     return launch_status(1);
 }
