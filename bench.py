@@ -169,6 +169,8 @@ def run_reference(args):
     from yvex_b200 import synth
     from yvex_b200.workloads import MoEWorkload
     cores = os.cpu_count() or 1
+    if args.workload in ("c1", "c4"):
+        return run_reference_kernel(args, cores)
     # The reference has no Q4_K decoder (src/gguf/quant_registry.c:67): when the compiled
     # reference is present its arm runs the Q2_K-down twin of the layer, the qtype its own MoE
     # path ships with; otherwise the port runs the layer exactly as configured.
@@ -186,6 +188,51 @@ def run_reference(args):
             "cpu_baseline": {"value": tps, "unit": UNIT, "cores": cores, "kind": kind,
                              "sample": f"{per_step} tokens per step, one thread per token"},
             "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_reference_kernel(args, cores):
+    """Reference arm of the single-kernel workloads: the reference's CPU matvec (config 1) or CPU
+    attention (config 4) on the host cores, on a bounded sample of the workload."""
+    oracle, kind = oracle_backend(True)
+    from yvex_b200 import synth
+    rng = np.random.default_rng(synth.BASE_SEED)
+    steps = max(1, min(args.steps, 3))
+    if args.workload == "c1":
+        rows = width = 4096
+        w = synth.random_blocks(synth.IQ2_XXS, rows, width, 1)
+        x = rng.standard_normal(width).astype(np.float32)
+        algo = w.size + 4 * width + 4 * rows
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            oracle.matvec(synth.IQ2_XXS, w, rows, width, x, threads=cores)
+        sec = (time.perf_counter() - t0) / steps
+        metric, cfg, sample = "dequant_gemv_hbm_gbs", {"workload": "c1", "rows": rows, "width": width, "qtype": "IQ2_XXS"}, \
+            "one 4096x4096 IQ2_XXS matvec per step, rows split over all cores"
+    else:
+        if not hasattr(oracle, "attention_gqa_decode"):
+            # the compiled reference exposes its attention one f32 head at a time; the port runs the
+            # same arithmetic (src/backend/cpu.c:319-411) over a bf16 GQA cache with threads over heads
+            oracle, kind = oracle_backend(False)
+        S, Hq, Hkv, D, ctx = 1, 32, 8, 128, 32768
+        bits = lambda a: synth.bf16_bits(a).reshape(a.shape)
+        q = bits(rng.standard_normal((S, Hq, D)).astype(np.float32))
+        k = bits(rng.standard_normal((S, Hkv, ctx, D)).astype(np.float32))
+        v = bits(rng.standard_normal((S, Hkv, ctx, D)).astype(np.float32))
+        algo = 2 * k.size * 2 + q.size * 2 + S * Hq * D * 4
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            oracle.attention_gqa_decode(q, k, v, ctx - 1, D ** -0.5, threads=cores)
+        sec = (time.perf_counter() - t0) / steps
+        metric, cfg, sample = "attention_decode_hbm_gbs", {"workload": "c4", "sessions": S, "q_heads": Hq, "kv_heads": Hkv,
+                                                          "head_dim": D, "context": ctx}, \
+            "one of the 16 sessions per step, heads split over all cores"
+    value = algo / sec / 1e9
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
+            "warmup": 0, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f64-accum (reference CPU path)", "data": "synthetic", "config": cfg,
+            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
