@@ -175,10 +175,15 @@ typedef struct {
 } yvex_moe_weight_view;
 typedef struct {
     yvex_moe_router_class router_class;
+    /* residual_streams > 1 selects the mHC envelope: rows are expanded_width = residual_streams *
+     * hidden_width wide on both sides, the FFN_NORM / MHC_FUNCTION / MHC_BASE / MHC_SCALE weight slots
+     * (F32) are required and mhc_mixing_rows = (residual_streams + 2) * residual_streams. */
     unsigned long long hidden_width, residual_streams, expanded_width;
+    unsigned long long mhc_mixing_rows, mhc_sinkhorn_iterations;
     unsigned long long routed_experts, shared_experts, experts_per_token;
     unsigned long long expert_intermediate_width, shared_intermediate_width;
     unsigned long long hash_table_rows;
+    double rms_epsilon, mhc_epsilon, mhc_post_multiplier;
     double routed_scaling_factor, activation_limit;
     int normalize_topk_probabilities;
 } yvex_moe_layer_plan;

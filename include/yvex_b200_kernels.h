@@ -157,6 +157,32 @@ int yvex_b200_moe_combine(const void *y_routed_bf16, const void *y_shared_bf16, 
                           uint64_t topk, uint64_t hidden, float *out, int *status, void *stream);
 
 /*
+ * mHC envelope of the MoE FFN: the layer's rows carry `streams` residual streams
+ * (expanded width = streams * hidden). yvex_b200_mhc_prepare is yvex_moe_ffn_prepare_cpu
+ * (src/graph/moe.c:446-495: mixing projection, yvex_attention_mhc_pre of
+ * src/graph/numeric.c:752-824, RMSNorm * weight, bf16 rounding) and the device twin of
+ * yvex_residual_mhc_pre + yvex_attention_weighted_norm (src/backend/cuda/kernels.cu:1243-1388,
+ * 867-911): expanded [rows x streams*hidden] f32 -> normalized [rows x hidden] (the FFN input),
+ * post [rows x streams], combination [rows x streams*streams]. yvex_b200_mhc_post is
+ * yvex_attention_mhc_post (src/graph/numeric.c:826-875; CUDA twin yvex_residual_mhc_post,
+ * src/backend/cuda/kernels.cu:1389-1421): core [rows x hidden] -> out [rows x streams*hidden].
+ * Coefficients are device F32 arrays: mhc_fn [(streams+2)*streams x streams*hidden], scale [3],
+ * base [(streams+2)*streams], norm [hidden]. Limits of the reference: (streams+2)*streams <= 64,
+ * hidden <= 16384.
+ */
+typedef struct yvex_b200_mhc {
+    uint64_t hidden, streams, sinkhorn_iterations;
+    double rms_epsilon, mhc_epsilon, post_multiplier;
+    const float *mhc_fn, *scale, *base, *norm;
+} yvex_b200_mhc;
+uint64_t yvex_b200_mhc_workspace_bytes(uint64_t streams, uint64_t rows);
+int yvex_b200_mhc_prepare(const yvex_b200_mhc *m, const float *expanded, uint64_t rows, float *normalized,
+                          float *post, float *combination, void *workspace, uint64_t workspace_bytes,
+                          int *status, void *stream);
+int yvex_b200_mhc_post(const yvex_b200_mhc *m, const float *core, const float *expanded, const float *post,
+                       const float *combination, uint64_t rows, float *out, int *status, void *stream);
+
+/*
  * Online-softmax causal GQA attention at decode: one query position per session against a bf16
  * KV cache, f32 accumulation and output. q [sessions][q_heads][head_dim] bf16, k/v
  * [sessions][kv_heads][context][head_dim] bf16, out [sessions][q_heads][head_dim] f32; keys

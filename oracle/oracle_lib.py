@@ -35,6 +35,12 @@ class _Layer(C.Structure):
                 ("shared_down", C.c_void_p), ("allow_q4k", C.c_int)]
 
 
+class _Mhc(C.Structure):
+    _fields_ = [("hidden", u64), ("streams", u64), ("sinkhorn_iterations", u64), ("rms_epsilon", C.c_double),
+                ("mhc_epsilon", C.c_double), ("post_multiplier", C.c_double), ("mhc_fn", C.c_void_p),
+                ("scale", C.c_void_p), ("base", C.c_void_p), ("norm", C.c_void_p)]
+
+
 class _Base:
     prefix = ""
     takes_allow = False
@@ -66,6 +72,29 @@ class _Base:
         L.allow_q4k = int(allow_q4k)
         L._keep = keep
         return L
+
+    # -- mHC envelope of the MoE FFN ---------------------------------------------------------
+    def mhc(self, hidden, streams, mhc_fn, scale, base, norm, sinkhorn_iterations=20, rms_epsilon=1e-6,
+            mhc_epsilon=1e-6, post_multiplier=2.0):
+        M = _Mhc(hidden, streams, sinkhorn_iterations, rms_epsilon, mhc_epsilon, post_multiplier)
+        arrays = [np.ascontiguousarray(a, np.float32) for a in (mhc_fn, scale, base, norm)]
+        M.mhc_fn, M.scale, M.base, M.norm = (_ptr(a) for a in arrays)
+        M._keep = arrays
+        return M
+
+    def mhc_prepare(self, M, expanded):
+        expanded = np.ascontiguousarray(expanded, np.float32)
+        normalized = np.zeros(M.hidden, np.float32)
+        post = np.zeros(M.streams, np.float32)
+        combination = np.zeros(M.streams * M.streams, np.float32)
+        rc = self._fn("mhc_prepare")(C.byref(M), _ptr(expanded), _ptr(normalized), _ptr(post), _ptr(combination))
+        return rc, normalized, post, combination
+
+    def mhc_post(self, M, core, expanded, post, combination):
+        out = np.zeros(M.streams * M.hidden, np.float32)
+        args = [np.ascontiguousarray(a, np.float32) for a in (core, expanded, post, combination)]
+        rc = self._fn("mhc_post")(C.byref(M), *[_ptr(a) for a in args], _ptr(out))
+        return rc, out
 
     # -- codecs ------------------------------------------------------------------------------
     def decode_rows(self, qtype, encoded, rows, width, allow_q4k=False):

@@ -30,6 +30,7 @@
 #include <yvex/internal/backend.h>
 #include <yvex/internal/moe.h>
 #include <yvex/internal/quant_numeric.h>
+#include "src/graph/private.h"      /* yvex_attention_mhc_post and its argument struct */
 
 #define REF_MAX_THREADS 256
 
@@ -347,6 +348,74 @@ int ref_moe_tokens(const ref_moe_layer *L, unsigned long long tokens, const floa
         if (spans[t].rc != YVEX_OK) rc = spans[t].rc;
     }
     return rc;
+}
+
+/* ---- mHC envelope of the MoE FFN ----------------------------------------------------------- */
+typedef struct {
+    unsigned long long hidden, streams, sinkhorn_iterations;
+    double rms_epsilon, mhc_epsilon, post_multiplier;
+    const float *mhc_fn, *scale, *base, *norm;
+} ref_mhc;
+
+static void ref_mhc_plan(const ref_mhc *M, yvex_moe_layer_plan *plan) {
+    memset(plan, 0, sizeof(*plan));
+    plan->hidden_width = M->hidden;
+    plan->residual_streams = M->streams;
+    plan->expanded_width = M->streams * M->hidden;
+    plan->mhc_mixing_rows = (M->streams + 2ull) * M->streams;
+    plan->mhc_sinkhorn_iterations = M->sinkhorn_iterations;
+    plan->rms_epsilon = M->rms_epsilon;
+    plan->mhc_epsilon = M->mhc_epsilon;
+    plan->mhc_post_multiplier = M->post_multiplier;
+}
+
+/* yvex_moe_ffn_prepare_cpu (src/graph/moe.c:446-495): expanded row -> normalized FFN input,
+ * post gates and the Sinkhorn-normalised stream combination. */
+int ref_mhc_prepare(const ref_mhc *M, const float *expanded, float *normalized, float *post,
+                    float *combination) {
+    yvex_moe_layer_plan plan;
+    yvex_moe_layer_job job;
+    yvex_error err;
+    memset(&err, 0, sizeof(err));
+    memset(&job, 0, sizeof(job));
+    ref_mhc_plan(M, &plan);
+    job.layer = &plan;
+    job.expanded_input = expanded;
+    job.weights[YVEX_MOE_WEIGHT_MHC_FUNCTION] = ref_view(
+        YVEX_GGUF_QTYPE_F32, (const unsigned char *)M->mhc_fn, plan.mhc_mixing_rows, plan.expanded_width);
+    job.weights[YVEX_MOE_WEIGHT_MHC_SCALE] = ref_view(YVEX_GGUF_QTYPE_F32, (const unsigned char *)M->scale, 1, 3);
+    job.weights[YVEX_MOE_WEIGHT_MHC_BASE] =
+        ref_view(YVEX_GGUF_QTYPE_F32, (const unsigned char *)M->base, 1, plan.mhc_mixing_rows);
+    job.weights[YVEX_MOE_WEIGHT_FFN_NORM] = ref_view(YVEX_GGUF_QTYPE_F32, (const unsigned char *)M->norm, 1, M->hidden);
+    return yvex_moe_ffn_prepare_cpu(&job, normalized, post, combination, &err);
+}
+
+/* yvex_attention_mhc_post (src/graph/numeric.c:826-875) with the geometry the MoE FFN uses. */
+int ref_mhc_post(const ref_mhc *M, const float *core, const float *expanded, const float *post,
+                 const float *combination, float *out) {
+    yvex_attention_layer_plan geometry;
+    yvex_attention_mhc_post_args args;
+    yvex_attention_failure failure;
+    yvex_error err;
+    const unsigned long long S = M->streams, H = M->hidden;
+    memset(&err, 0, sizeof(err));
+    memset(&failure, 0, sizeof(failure));
+    memset(&geometry, 0, sizeof(geometry));
+    geometry.compute_contract = YVEX_ATTENTION_COMPUTE_BF16_F32_RNE_V1;
+    geometry.residual_stream_count = S;
+    geometry.residual_stream_width = H;
+    geometry.residual_expanded_width = S * H;
+    geometry.mhc_mixing_rows = (S + 2ull) * S;
+    geometry.mhc_mixing_columns = S * H;
+    geometry.mhc_base_width = (S + 2ull) * S;
+    geometry.mhc_scale_width = 3ull;
+    geometry.mhc_sinkhorn_iterations = M->sinkhorn_iterations;
+    geometry.rms_norm_epsilon = M->rms_epsilon;
+    geometry.mhc_epsilon = M->mhc_epsilon;
+    geometry.mhc_residual_post_multiplier = M->post_multiplier;
+    geometry.mhc_attention_pre_and_post = 1;
+    args = (yvex_attention_mhc_post_args){&geometry, core, expanded, post, combination, 1ull, H, S * H, S, S * S, out, S * H};
+    return yvex_attention_mhc_post(&args, &failure, &err);
 }
 
 /* One attention head through the reference's public op on its CPU backend. */

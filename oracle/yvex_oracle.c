@@ -441,6 +441,107 @@ int oq_moe_tokens(const oq_moe_layer *L, uint64_t tokens, const float *x, const 
     return rc;
 }
 
+/* ---- mHC envelope: src/graph/moe.c:446-495, src/graph/numeric.c:630-659,694-875 -------------- */
+
+static double oq_sigmoid(double v) {                          /* numeric.c:694-704 */
+    if (v >= 0.0) return 1.0 / (1.0 + exp(-v));
+    double d = exp(v);
+    return d / (1.0 + d);
+}
+
+static int oq_sinkhorn(float *m, uint64_t n, uint64_t iterations, double eps) {   /* numeric.c:706-750 */
+    for (uint64_t r = 0; r < n; ++r) {
+        double mx = -(double)INFINITY, total = 0.0;
+        for (uint64_t c = 0; c < n; ++c) mx = fmax(mx, m[r * n + c]);
+        for (uint64_t c = 0; c < n; ++c) {
+            double v = exp((double)m[r * n + c] - mx);
+            m[r * n + c] = (float)v;
+            total += v;
+        }
+        if (!isfinite(total) || total <= 0.0) return 0;
+        for (uint64_t c = 0; c < n; ++c) m[r * n + c] = (float)((double)m[r * n + c] / total + eps);
+    }
+    for (uint64_t it = 0; it < iterations; ++it) {
+        if (it != 0) {
+            for (uint64_t r = 0; r < n; ++r) {
+                double total = 0.0;
+                for (uint64_t c = 0; c < n; ++c) total += m[r * n + c];
+                if (!isfinite(total)) return 0;
+                for (uint64_t c = 0; c < n; ++c) m[r * n + c] = (float)((double)m[r * n + c] / (total + eps));
+            }
+        }
+        for (uint64_t c = 0; c < n; ++c) {
+            double total = 0.0;
+            for (uint64_t r = 0; r < n; ++r) total += m[r * n + c];
+            if (!isfinite(total)) return 0;
+            for (uint64_t r = 0; r < n; ++r) m[r * n + c] = (float)((double)m[r * n + c] / (total + eps));
+        }
+    }
+    return 1;
+}
+
+int oq_mhc_prepare(const oq_mhc *M, const float *expanded, float *normalized, float *post,
+                   float *combination) {
+    const uint64_t S = M->streams, H = M->hidden, W = S * H, rows = (S + 2) * S;
+    float mix[64];
+    if (!S || !H || rows > 64 || H > 16384) return OQ_ERR_INVALID_ARG;        /* moe.c:455-457 */
+    int rc = oq_matvec(OQ_F32, (const uint8_t *)M->mhc_fn, rows, W, expanded, mix, 1, 0);
+    if (rc != OQ_OK) return rc;
+    for (uint64_t i = 0; i < 3; ++i) if (!isfinite(M->scale[i])) return OQ_ERR_FORMAT;
+    for (uint64_t i = 0; i < rows; ++i) if (!isfinite(M->base[i])) return OQ_ERR_FORMAT;
+    double squares = 0.0;
+    memset(normalized, 0, (size_t)H * sizeof(float));
+    for (uint64_t i = 0; i < W; ++i) {
+        if (!isfinite(expanded[i])) return OQ_ERR_FORMAT;
+        squares += (double)expanded[i] * (double)expanded[i];
+    }
+    double inv = 1.0 / sqrt(squares / (double)W + M->rms_epsilon);
+    if (!isfinite(inv)) return OQ_ERR_FORMAT;
+    for (uint64_t s = 0; s < S; ++s) {                                        /* numeric.c:794-813 */
+        double pre = oq_sigmoid((double)mix[s] * inv * (double)M->scale[0] + (double)M->base[s]);
+        post[s] = (float)(M->post_multiplier *
+                          oq_sigmoid((double)mix[S + s] * inv * (double)M->scale[1] + (double)M->base[S + s]));
+        for (uint64_t t = 0; t < S; ++t) {
+            uint64_t idx = 2 * S + s * S + t;
+            combination[s * S + t] = (float)((double)mix[idx] * inv * (double)M->scale[2] + (double)M->base[idx]);
+        }
+        for (uint64_t i = 0; i < H; ++i)
+            normalized[i] += (float)((pre + M->mhc_epsilon) * (double)expanded[s * H + i]);
+    }
+    if (!oq_sinkhorn(combination, S, M->sinkhorn_iterations, M->mhc_epsilon)) return OQ_ERR_FORMAT;
+    for (uint64_t i = 0; i < H; ++i) {
+        if (!isfinite(normalized[i])) return OQ_ERR_FORMAT;
+        normalized[i] = oq_bf16_round(normalized[i]);
+    }
+    double mean = 0.0;                                                        /* numeric.c:630-659 */
+    for (uint64_t i = 0; i < H; ++i) {
+        if (!isfinite(M->norm[i])) return OQ_ERR_FORMAT;
+        mean += (double)normalized[i] * (double)normalized[i];
+    }
+    mean /= (double)H;
+    double ninv = 1.0 / sqrt(mean + M->rms_epsilon);
+    if (!isfinite(ninv)) return OQ_ERR_FORMAT;
+    for (uint64_t i = 0; i < H; ++i) {
+        double v = (double)normalized[i] * ninv * (double)M->norm[i];
+        if (!isfinite(v)) return OQ_ERR_FORMAT;
+        normalized[i] = oq_bf16_round((float)v);
+    }
+    return OQ_OK;
+}
+
+int oq_mhc_post(const oq_mhc *M, const float *core, const float *expanded, const float *post,
+                const float *combination, float *out) {                       /* numeric.c:826-875 */
+    const uint64_t S = M->streams, H = M->hidden;
+    for (uint64_t t = 0; t < S; ++t)
+        for (uint64_t i = 0; i < H; ++i) {
+            double v = (double)post[t] * (double)core[i];
+            for (uint64_t s = 0; s < S; ++s) v += (double)combination[s * S + t] * (double)expanded[s * H + i];
+            if (!isfinite(v)) return OQ_ERR_FORMAT;
+            out[t * H + i] = oq_bf16_round((float)v);
+        }
+    return OQ_OK;
+}
+
 /* ---- expert worklist: src/graph/worklist.c:369-441 ------------------------------------------- */
 
 int oq_worklist(const uint64_t *selected, uint64_t rows, uint64_t topk, uint64_t experts,

@@ -73,6 +73,24 @@ int oq_moe_tokens(const oq_moe_layer *L, uint64_t tokens, const float *x, const 
                   const uint32_t *token_ids, float *combined, uint64_t *selected, float *weights,
                   int threads);
 
+/* ---- mHC envelope of the MoE FFN (4 residual streams around the layer) -------------------------
+ * prepare: mix = mhc_fn . expanded (double dots), sigmoid gates, Sinkhorn-normalised stream
+ * combination, collapse of the streams to one bf16-rounded row, RMSNorm * weight, bf16 round
+ * (src/graph/moe.c:446-495, src/graph/numeric.c:630-659,694-824). post: re-expansion
+ * out[t] = bf16(post[t]*core + sum_s combination[s][t]*residual[s]) (src/graph/numeric.c:826-875). */
+typedef struct {
+    uint64_t hidden, streams, sinkhorn_iterations;
+    double rms_epsilon, mhc_epsilon, post_multiplier;
+    const float *mhc_fn; /* [(streams + 2) * streams rows x streams * hidden] f32 */
+    const float *scale;  /* [3] */
+    const float *base;   /* [(streams + 2) * streams] */
+    const float *norm;   /* [hidden] */
+} oq_mhc;
+int oq_mhc_prepare(const oq_mhc *M, const float *expanded, float *normalized, float *post,
+                   float *combination);
+int oq_mhc_post(const oq_mhc *M, const float *core, const float *expanded, const float *post,
+                const float *combination, float *out);
+
 /* Expert-major stable counting sort of (row, rank) pairs. Arrays sized pairs / experts(+1). */
 int oq_worklist(const uint64_t *selected, uint64_t rows, uint64_t topk, uint64_t experts,
                 uint32_t *order, uint32_t *source_rows, uint32_t *bucket_expert,

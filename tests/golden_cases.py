@@ -22,6 +22,13 @@ CASES = {
         "small_logits": (256, 16, 4, 256, 6, "logits", 22),
         "c2_shape": (4096, 64, 6, 1536, 1, "weights", 23),
     },
+    # name: (hidden, streams, tokens, seed): the mHC envelope around the FFN; "layer_small" wraps the
+    # "small_router" layer above (same hidden width) end to end
+    "envelope": {
+        "small": (512, 4, 3, 41),
+        "wide_hidden": (4096, 4, 2, 42),
+        "two_streams": (768, 2, 2, 43),
+    },
     # name: (sessions, q_heads, kv_heads, head_dim, context, position, seed)
     "attention": {
         "small": (2, 8, 2, 128, 512, 511, 31),
@@ -61,3 +68,19 @@ def attention_inputs(name):
     k = synth.bf16_round(rng.standard_normal((S, Hkv, ctx, D)).astype(np.float32))
     v = synth.bf16_round(rng.standard_normal((S, Hkv, ctx, D)).astype(np.float32))
     return q, k, v, pos, float(D) ** -0.5
+
+
+ENVELOPE_POLICY = dict(sinkhorn_iterations=20, rms_epsilon=1e-6, mhc_epsilon=1e-6, post_multiplier=2.0)
+
+
+def envelope_inputs(name):
+    """(mhc_fn [(S+2)S, S*H], scale [3], base [(S+2)S], norm [H], expanded [T, S*H]) - all f32."""
+    H, S, T, seed = CASES["envelope"][name]
+    rng = np.random.default_rng(seed)
+    rows = (S + 2) * S
+    fn = (rng.standard_normal((rows, S * H)) * 0.05).astype(np.float32)
+    scale = np.array([0.7, 1.3, 0.9], np.float32)
+    base = (rng.standard_normal(rows) * 0.3).astype(np.float32)
+    norm = (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    expanded = rng.standard_normal((T, S * H)).astype(np.float32)
+    return fn, scale, base, norm, expanded

@@ -7,7 +7,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
-from golden_cases import attention_inputs, layer_inputs
+from golden_cases import CASES, ENVELOPE_POLICY, attention_inputs, envelope_inputs, layer_inputs
 from yvex_b200 import synth
 
 pytestmark = pytest.mark.gpu
@@ -128,9 +128,9 @@ def test_execute_rows_refusals(B):
     job.weights[B.W_DOWN].qtype = 11
     assert run_rows(B, be, ops, job, x, logits)[0] == B.UNSUPPORTED
     job.weights[B.W_DOWN].qtype = spec.down_qtype
-    # the mHC envelope is not built: refused, not skipped
+    # a plan that asks for the mHC envelope without its geometry is refused, never run without it
     job._plan.residual_streams = 4
-    assert run_rows(B, be, ops, job, x, logits)[0] == B.UNSUPPORTED
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.FORMAT
     job._plan.residual_streams = 1
     # cancellation callback
     job.cancel_requested = B.CANCEL_FN(lambda ctx: 1)
@@ -150,6 +150,38 @@ def test_execute_rows_refusals(B):
     assert run_rows(B, be, ops, job, x, logits)[0] == B.OK            # the status word was cleared
     # derived layouts are not offered
     assert ops.derived_layout_plan(None, C.byref(need), C.byref(be.err)) == B.UNSUPPORTED
+    assert be.close() == B.OK
+
+
+def test_execute_rows_with_mhc_envelope_vs_frozen_reference(B, golden):
+    """Expanded rows in, expanded rows out (4 residual streams around the small_router layer)."""
+    H, S, T, seed = CASES["envelope"]["small"]
+    fn, scale, base, norm, expanded = envelope_inputs("small")
+    spec, weights, router, _, _ = layer_inputs("small_router")
+    be = B.Backend()
+    arrays = dict(weights, router=router, ffn_norm=norm, mhc_fn=fn, mhc_base=base, mhc_scale=scale)
+    arena = B.ResidentArena(be, arrays)
+    job = B.moe_job(arena, spec, residual_streams=S, envelope_policy=ENVELOPE_POLICY)
+    ops, _ = attach_workspace(B, be, job, T)
+    rc, out, sel, wts, res = run_rows(B, be, ops, job, expanded, None)
+    assert rc == B.OK, be.message()
+    assert (sel == golden["envelope_small_sel"]).all()
+    assert out.shape == (T, S * H) and rel_l2(out, golden["envelope_small_out"].view(np.float32)) <= 1e-3
+    assert res.completed == 1 and res.kernel_launches >= 6
+    # supplied logits bypass the router the envelope feeds: refused
+    lg = np.zeros((T, spec.experts), np.float32)
+    assert run_rows(B, be, ops, job, expanded, lg)[0] == B.UNSUPPORTED
+    # coefficients must be F32 and resident
+    job.weights[B.W_MHC_BASE].qtype = synth.BF16
+    assert run_rows(B, be, ops, job, expanded, None)[0] == B.UNSUPPORTED
+    job.weights[B.W_MHC_BASE].qtype = synth.F32
+    keep = job.weights[B.W_FFN_NORM].encoded
+    job.weights[B.W_FFN_NORM].encoded = None
+    assert run_rows(B, be, ops, job, expanded, None)[0] == B.STATE
+    job.weights[B.W_FFN_NORM].encoded = keep
+    # rows of the hidden width are no longer this layer's row shape
+    assert run_rows(B, be, ops, job, expanded[:, :H].copy(), None)[0] == B.FORMAT
+    assert run_rows(B, be, ops, job, expanded, None)[0] == B.OK
     assert be.close() == B.OK
 
 

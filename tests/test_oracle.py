@@ -11,7 +11,7 @@ import math
 import numpy as np
 import pytest
 
-from golden_cases import CASES, attention_inputs, layer_inputs
+from golden_cases import CASES, ENVELOPE_POLICY, attention_inputs, envelope_inputs, layer_inputs
 from golden.make_golden import iq2_exhaustive_blocks
 from yvex_b200 import synth
 
@@ -184,6 +184,46 @@ def test_attention_matches_frozen_reference(port, golden, name):
 
 
 # ---- 3. live comparison with the compiled reference ----------------------------------------
+
+@pytest.mark.parametrize("name", list(CASES["envelope"]))
+def test_mhc_envelope_matches_frozen_reference(port, golden, name):
+    """prepare (gates, Sinkhorn, collapse, RMSNorm, bf16 rounding) and post bit-for-bit; the "small"
+    case runs the small_router layer between the two."""
+    H, S, T, seed = CASES["envelope"][name]
+    fn, scale, base, norm, expanded = envelope_inputs(name)
+    M = port.mhc(H, S, fn, scale, base, norm, **ENVELOPE_POLICY)
+    got = [port.mhc_prepare(M, expanded[t]) for t in range(T)]
+    assert all(g[0] == 0 for g in got)
+    normalized = np.stack([g[1] for g in got])
+    posts, combs = np.stack([g[2] for g in got]), np.stack([g[3] for g in got])
+    assert np.array_equal(normalized.view(np.uint32), golden[f"envelope_{name}_norm"])
+    assert np.array_equal(posts.view(np.uint32), golden[f"envelope_{name}_post"])
+    assert np.array_equal(combs.view(np.uint32), golden[f"envelope_{name}_comb"])
+    # the stream combination is (almost) doubly stochastic after the Sinkhorn rounds
+    c = combs.reshape(T, S, S)
+    assert np.allclose(c.sum(axis=1), 1.0, atol=1e-4)
+    core = np.random.default_rng(seed + 7).standard_normal((T, H)).astype(np.float32)
+    if name == "small":
+        spec, weights, router, _, _ = layer_inputs("small_router")
+        rc, core, sel, _ = port.moe_tokens(port.layer(spec, weights, router=router), normalized, threads=4)
+        assert rc == 0 and np.array_equal(sel.astype(np.uint16), golden["envelope_small_sel"])
+    outs = np.stack([port.mhc_post(M, core[t], expanded[t], posts[t], combs[t])[1] for t in range(T)])
+    assert np.array_equal(outs.view(np.uint32), golden[f"envelope_{name}_out"])
+
+
+def test_mhc_envelope_refuses_bad_geometry_and_numerics(port):
+    fn, scale, base, norm, expanded = envelope_inputs("two_streams")
+    H, S = 768, 2
+    bad = expanded[0].copy()
+    bad[5] = np.inf
+    assert port.mhc_prepare(port.mhc(H, S, fn, scale, base, norm, **ENVELOPE_POLICY), bad)[0] == -4
+    nan_base = base.copy()
+    nan_base[1] = np.nan
+    assert port.mhc_prepare(port.mhc(H, S, fn, scale, nan_base, norm, **ENVELOPE_POLICY), expanded[0])[0] == -4
+    # (streams + 2) * streams must fit the reference's 64 mixing rows (src/graph/moe.c:455)
+    assert port.mhc_prepare(port.mhc(64, 8, np.zeros((80, 8 * 64), np.float32), scale, np.zeros(80, np.float32),
+                                     np.ones(64, np.float32), **ENVELOPE_POLICY), np.zeros(8 * 64, np.float32))[0] == -10
+
 
 def test_geometry_and_capability_table_match_reference(port, ref):
     for q in range(0, 45):

@@ -46,8 +46,10 @@ class WeightView(C.Structure):
 
 class LayerPlan(C.Structure):
     _fields_ = [("router_class", C.c_int), ("hidden_width", ull), ("residual_streams", ull), ("expanded_width", ull),
+                ("mhc_mixing_rows", ull), ("mhc_sinkhorn_iterations", ull),
                 ("routed_experts", ull), ("shared_experts", ull), ("experts_per_token", ull),
                 ("expert_intermediate_width", ull), ("shared_intermediate_width", ull), ("hash_table_rows", ull),
+                ("rms_epsilon", C.c_double), ("mhc_epsilon", C.c_double), ("mhc_post_multiplier", C.c_double),
                 ("routed_scaling_factor", C.c_double), ("activation_limit", C.c_double),
                 ("normalize_topk_probabilities", C.c_int)]
 
@@ -217,11 +219,16 @@ class ResidentArena:
         return self.host + self.offsets[name]
 
 
-def moe_job(arena, spec, router=True, router_class=1, hash_rows=0, family=None, residual_streams=1):
+def moe_job(arena, spec, router=True, router_class=1, hash_rows=0, family=None, residual_streams=1, envelope_policy=None):
     """LayerPlan + LayerJob whose weight views point (by host address) into `arena`."""
     from . import synth
-    plan = LayerPlan(router_class, spec.hidden, residual_streams, spec.hidden * max(residual_streams, 1), spec.experts, 1,
-                     spec.topk, spec.inter, spec.shared_inter, hash_rows, spec.scaling, spec.limit, spec.normalize)
+    S = max(residual_streams, 1)
+    policy = dict(sinkhorn_iterations=20, rms_epsilon=1e-6, mhc_epsilon=1e-6, post_multiplier=2.0)
+    policy.update(envelope_policy or {})
+    plan = LayerPlan(router_class, spec.hidden, residual_streams, spec.hidden * S, (S + 2) * S if residual_streams > 1 else 0,
+                     policy["sinkhorn_iterations"] if residual_streams > 1 else 0, spec.experts, 1,
+                     spec.topk, spec.inter, spec.shared_inter, hash_rows, policy["rms_epsilon"], policy["mhc_epsilon"],
+                     policy["post_multiplier"], spec.scaling, spec.limit, spec.normalize)
     job = LayerJob()
     job.layer = C.pointer(plan)
 
@@ -234,6 +241,10 @@ def moe_job(arena, spec, router=True, router_class=1, hash_rows=0, family=None, 
         v.row_bytes = synth.row_bytes(qtype, width)
 
     E, H, I, Is = spec.experts, spec.hidden, spec.inter, spec.shared_inter
+    view(W_FFN_NORM, "ffn_norm", synth.F32, 1, H)
+    view(W_MHC_FUNCTION, "mhc_fn", synth.F32, (S + 2) * S, S * H)
+    view(W_MHC_BASE, "mhc_base", synth.F32, 1, (S + 2) * S)
+    view(W_MHC_SCALE, "mhc_scale", synth.F32, 1, 3)
     if router:
         view(W_ROUTER, "router", synth.F32, E, H)
     view(W_ROUTER_BIAS, "bias", synth.F32, 1, E)

@@ -4,10 +4,13 @@
  * plus the unbounded-width extension. The layer itself runs in the device layer
  * (yvex_b200_moe_decode for <= 62 rows, yvex_b200_moe_wide beyond).
  *
- * Scope: a layer WITHOUT the mHC envelope (residual_streams <= 1, expanded_width == hidden_width);
+ * Two row shapes. Without the envelope (residual_streams <= 1, expanded_width == hidden_width) the
  * input rows are the normalized hidden rows, rounded to bf16 at ingress like the reference's
- * normalized row (src/graph/moe.c:487-489). A plan that asks for the envelope is refused with
- * YVEX_ERR_UNSUPPORTED - never silently skipped.
+ * normalized row (src/graph/moe.c:487-489). With the mHC envelope (residual_streams > 1) rows are
+ * the expanded residual rows on both sides, as in the reference's execute_rows
+ * (src/backend/cuda/moe.c:1381-1543): prepare (mixing projection, gates, Sinkhorn, collapse,
+ * RMSNorm; src/graph/moe.c:446-495) -> layer -> post (src/graph/numeric.c:826-875). The envelope's
+ * coefficient tensors must be resident F32; anything else is refused, never skipped.
  */
 #include "backend_private.h"
 
@@ -44,9 +47,19 @@ static int plan_geometry(const yvex_moe_layer_plan *layer, const yvex_moe_layer_
 
 static unsigned long long align256(unsigned long long v) { return (v + 255ull) & ~255ull; }
 
-static unsigned long long staging_bytes(const yvex_b200_moe_geometry *g, unsigned long long rows) {
-    return 2ull * align256(rows * g->hidden * 4ull) + align256(rows * g->experts * 4ull) + 2ull * align256(rows * g->topk * 4ull) +
-           align256(rows * 4ull) + 256ull;
+static unsigned long long envelope_streams(const yvex_moe_layer_plan *layer) {
+    return layer->residual_streams > 1ull ? layer->residual_streams : 1ull;
+}
+
+/* Rows in and out are `streams` times wider with the envelope, which also needs the normalized and
+ * combined hidden rows, the gates and the device layer's own scratch. */
+static unsigned long long staging_bytes(const yvex_b200_moe_geometry *g, unsigned long long rows, unsigned long long streams) {
+    unsigned long long bytes = 2ull * align256(rows * g->hidden * streams * 4ull) + align256(rows * g->experts * 4ull) +
+                               2ull * align256(rows * g->topk * 4ull) + align256(rows * 4ull) + 256ull;
+    if (streams > 1ull)
+        bytes += 2ull * align256(rows * g->hidden * 4ull) + align256(rows * streams * 4ull) + align256(rows * streams * streams * 4ull) +
+                 align256(yvex_b200_mhc_workspace_bytes(streams, rows));
+    return bytes;
 }
 
 static int workspace_for(const yvex_moe_layer_plan *layer, unsigned long long rows, int wide, unsigned long long *bytes, yvex_error *err) {
@@ -56,7 +69,7 @@ static int workspace_for(const yvex_moe_layer_plan *layer, unsigned long long ro
     if (!wide && rows > YVEX_MOE_NARROW_MAX_ROWS)
         return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, "moe.workspace_required", "execute_rows admits at most 62 rows; use the wide entry");
     plan_geometry(layer, NULL, &g);
-    *bytes = staging_bytes(&g, rows) + (wide ? yvex_b200_moe_wide_workspace_bytes(&g, rows) : yvex_b200_moe_workspace_bytes(&g, rows));
+    *bytes = staging_bytes(&g, rows, envelope_streams(layer)) + (wide ? yvex_b200_moe_wide_workspace_bytes(&g, rows) : yvex_b200_moe_workspace_bytes(&g, rows));
     yvex_error_clear(err);
     return YVEX_OK;
 }
@@ -110,10 +123,12 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     const yvex_moe_layer_plan *layer = job ? job->layer : NULL;
     yvex_b200_moe_geometry g;
     yvex_b200_moe_weights w;
-    unsigned long long rows, cursor = 0, need, kernel_ws, launches0, in_bytes, sel_count;
+    yvex_b200_mhc mhc;
+    unsigned long long rows, cursor = 0, need, kernel_ws, launches0, in_bytes, hid_bytes, sel_count, streams, mhc_ws = 0;
     unsigned char *ws_in, *ws_out, *ws_logits, *ws_sel, *ws_wts, *ws_ids, *ws_kernel;
-    const float *dev_in, *dev_logits = NULL;
-    float *dev_out;
+    unsigned char *ws_norm = NULL, *ws_core = NULL, *ws_post = NULL, *ws_comb = NULL, *ws_mhc = NULL;
+    const float *dev_in, *dev_logits = NULL, *layer_in;
+    float *dev_out, *layer_out;
     int rc, code, defer, slot;
     static const int required[YVEX_MOE_WEIGHT_COUNT] = {0, 0, 0, 0, 0, 0, 0, 1, 1, 1, 1, 1, 1};
     const void *addr[YVEX_MOE_WEIGHT_COUNT];
@@ -127,10 +142,13 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     if (!rows) return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "row batch is empty");
     if (!wide && rows > YVEX_MOE_NARROW_MAX_ROWS)
         return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "row count is outside the admitted widths of execute_rows");
-    if (layer->residual_streams > 1ull || (layer->expanded_width && layer->expanded_width != layer->hidden_width))
-        return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "the mHC envelope (residual streams > 1) is not built in this backend");
-    if (batch->row_width != layer->hidden_width || (batch->row_stride && batch->row_stride != batch->row_width))
-        return yvex_refuse(err, YVEX_ERR_FORMAT, where, "row batch geometry does not match the layer's hidden width");
+    streams = envelope_streams(layer);
+    if (layer->expanded_width && layer->expanded_width != streams * layer->hidden_width)
+        return yvex_refuse(err, YVEX_ERR_FORMAT, where, "expanded width is not residual streams x hidden width");
+    if (streams > 1ull && layer->mhc_mixing_rows != (streams + 2ull) * streams)
+        return yvex_refuse(err, YVEX_ERR_FORMAT, where, "mHC mixing rows must be (streams + 2) x streams");
+    if (batch->row_width != streams * layer->hidden_width || (batch->row_stride && batch->row_stride != batch->row_width))
+        return yvex_refuse(err, YVEX_ERR_FORMAT, where, "row batch geometry does not match the layer's row width");
     if (!batch->device_rows == !batch->expanded_rows)
         return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "exactly one of device rows and host rows is required");
     plan_geometry(layer, job, &g);
@@ -169,10 +187,33 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
         return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "either resident router weights or router logits are required");
     if (g.router_class == 0 && (!batch->token_ids_present || !batch->token_ids))
         return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "MoE hash router requires token IDs");
+    if (streams > 1ull) {
+        static const int coeff[4] = {YVEX_MOE_WEIGHT_FFN_NORM, YVEX_MOE_WEIGHT_MHC_FUNCTION, YVEX_MOE_WEIGHT_MHC_BASE,
+                                     YVEX_MOE_WEIGHT_MHC_SCALE};
+        const unsigned long long mix_rows = (streams + 2ull) * streams;
+        const unsigned long long want[4] = {g.hidden * 4ull, mix_rows * streams * g.hidden * 4ull, mix_rows * 4ull, 3ull * 4ull};
+        for (int i = 0; i < 4; ++i) {
+            const yvex_moe_weight_view *v = &job->weights[coeff[i]];
+            if (!addr[coeff[i]]) return yvex_refuse(err, YVEX_ERR_STATE, where, "mHC envelope coefficients are not resident on this backend");
+            if (v->qtype != 0u || v->encoded_bytes != want[i])
+                return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "mHC envelope coefficients must be F32 tensors of the layer's geometry");
+        }
+        if (batch->router_logits || batch->device_router_logits)
+            return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "supplied router logits cannot be combined with the mHC envelope");
+        memset(&mhc, 0, sizeof(mhc));
+        mhc.hidden = g.hidden; mhc.streams = streams; mhc.sinkhorn_iterations = layer->mhc_sinkhorn_iterations;
+        mhc.rms_epsilon = layer->rms_epsilon; mhc.mhc_epsilon = layer->mhc_epsilon; mhc.post_multiplier = layer->mhc_post_multiplier;
+        mhc.norm = (const float *)addr[YVEX_MOE_WEIGHT_FFN_NORM];
+        mhc.mhc_fn = (const float *)addr[YVEX_MOE_WEIGHT_MHC_FUNCTION];
+        mhc.base = (const float *)addr[YVEX_MOE_WEIGHT_MHC_BASE];
+        mhc.scale = (const float *)addr[YVEX_MOE_WEIGHT_MHC_SCALE];
+        mhc_ws = yvex_b200_mhc_workspace_bytes(streams, rows);
+    }
 
-    in_bytes = rows * g.hidden * 4ull;
+    hid_bytes = rows * g.hidden * 4ull;
+    in_bytes = hid_bytes * streams;
     kernel_ws = wide ? yvex_b200_moe_wide_workspace_bytes(&g, rows) : yvex_b200_moe_workspace_bytes(&g, rows);
-    need = staging_bytes(&g, rows) + kernel_ws;
+    need = staging_bytes(&g, rows, streams) + kernel_ws;
     if (!backend->workspace || backend->workspace->bytes < need)
         return yvex_refuse(err, YVEX_ERR_NOMEM, where, "attached device workspace is smaller than workspace_required");
     ws_in = yvex_workspace_take(backend, &cursor, in_bytes);
@@ -182,7 +223,15 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     ws_wts = yvex_workspace_take(backend, &cursor, rows * g.topk * 4ull);
     ws_ids = yvex_workspace_take(backend, &cursor, rows * 4ull);
     ws_kernel = yvex_workspace_take(backend, &cursor, kernel_ws);
-    if (!ws_in || !ws_out || !ws_logits || !ws_sel || !ws_wts || !ws_ids || !ws_kernel)
+    if (streams > 1ull) {
+        ws_norm = yvex_workspace_take(backend, &cursor, hid_bytes);
+        ws_core = yvex_workspace_take(backend, &cursor, hid_bytes);
+        ws_post = yvex_workspace_take(backend, &cursor, rows * streams * 4ull);
+        ws_comb = yvex_workspace_take(backend, &cursor, rows * streams * streams * 4ull);
+        ws_mhc = yvex_workspace_take(backend, &cursor, mhc_ws);
+    }
+    if (!ws_in || !ws_out || !ws_logits || !ws_sel || !ws_wts || !ws_ids || !ws_kernel ||
+        (streams > 1ull && (!ws_norm || !ws_core || !ws_post || !ws_comb || !ws_mhc)))
         return yvex_refuse(err, YVEX_ERR_NOMEM, where, "attached device workspace is smaller than workspace_required");
 
     if (batch->device_rows) {
@@ -221,18 +270,34 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
         if (!output || !output->combined_rows) return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "a device or host output is required");
         dev_out = (float *)ws_out;
     }
-    if (output && output->combined_rows && output->combined_capacity < rows * g.hidden)
+    if (output && output->combined_rows && output->combined_capacity < rows * g.hidden * streams)
         return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "combined output capacity is too small");
     sel_count = rows * g.topk;
     if (output && (output->selected_experts || output->selected_weights) && output->selection_capacity < sel_count)
         return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "selection output capacity is too small");
 
     launches0 = yvex_b200_launch_count();
+    layer_in = dev_in;
+    layer_out = dev_out;
+    if (streams > 1ull) {
+        rc = yvex_b200_mhc_prepare(&mhc, dev_in, rows, (float *)ws_norm, (float *)ws_post, (float *)ws_comb, ws_mhc, mhc_ws,
+                                   backend->status_word, backend->stream);
+        if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
+        if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the mHC envelope geometry");
+        layer_in = (const float *)ws_norm;
+        layer_out = (float *)ws_core;
+    }
     rc = (wide ? yvex_b200_moe_wide : yvex_b200_moe_decode)(
-        &g, &w, dev_in, dev_logits, batch->token_ids_present && batch->token_ids ? (const uint32_t *)ws_ids : NULL, rows, dev_out,
+        &g, &w, layer_in, dev_logits, batch->token_ids_present && batch->token_ids ? (const uint32_t *)ws_ids : NULL, rows, layer_out,
         (int32_t *)ws_sel, (float *)ws_wts, ws_kernel, kernel_ws, backend->status_word, backend->stream);
     if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
     if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the MoE layer geometry");
+    if (streams > 1ull) {
+        rc = yvex_b200_mhc_post(&mhc, (const float *)ws_core, dev_in, (const float *)ws_post, (const float *)ws_comb, rows, dev_out,
+                                backend->status_word, backend->stream);
+        if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
+        if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the mHC envelope geometry");
+    }
 
     defer = job->device_completion && job->device_completion->defer && job->device_completion->host;
     if (output && output->combined_rows) {
@@ -259,7 +324,12 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     result->expert_subviews_accessed = sel_count * 3ull;
     result->kernel_launches = yvex_b200_launch_count() - launches0;
     result->tensor_core_launches = wide ? 2ull : 2ull;
-    result->active_weight_base_bytes = job->weights[YVEX_MOE_WEIGHT_SHARED_GATE].encoded_bytes +
+    if (streams > 1ull)
+        result->active_weight_base_bytes += job->weights[YVEX_MOE_WEIGHT_FFN_NORM].encoded_bytes +
+                                            job->weights[YVEX_MOE_WEIGHT_MHC_FUNCTION].encoded_bytes +
+                                            job->weights[YVEX_MOE_WEIGHT_MHC_BASE].encoded_bytes +
+                                            job->weights[YVEX_MOE_WEIGHT_MHC_SCALE].encoded_bytes;
+    result->active_weight_base_bytes += job->weights[YVEX_MOE_WEIGHT_SHARED_GATE].encoded_bytes +
                                        job->weights[YVEX_MOE_WEIGHT_SHARED_UP].encoded_bytes +
                                        job->weights[YVEX_MOE_WEIGHT_SHARED_DOWN].encoded_bytes +
                                        job->weights[YVEX_MOE_WEIGHT_ROUTER].encoded_bytes;

@@ -32,6 +32,12 @@ class MoeWeights(C.Structure):
                 ("shared_gate", vp), ("shared_up", vp), ("shared_down", vp)]
 
 
+class Mhc(C.Structure):
+    _fields_ = [("hidden", u64), ("streams", u64), ("sinkhorn_iterations", u64), ("rms_epsilon", C.c_double),
+                ("mhc_epsilon", C.c_double), ("post_multiplier", C.c_double), ("mhc_fn", vp), ("scale", vp),
+                ("base", vp), ("norm", vp)]
+
+
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(f"{LIB_PATH} is missing: run `python -m yvex_b200.build` (there is no fallback path)")
@@ -58,6 +64,10 @@ def _load():
     lib.yvex_b200_attention_gqa_decode.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, C.c_float,
                                                    vp, vp, u64, vp, vp]
     lib.yvex_b200_attention_f32.argtypes = [vp, vp, vp, u64, u64, u64, C.c_float, C.c_int, vp, vp, vp, vp, vp]
+    lib.yvex_b200_mhc_workspace_bytes.restype = u64
+    lib.yvex_b200_mhc_workspace_bytes.argtypes = [u64, u64]
+    lib.yvex_b200_mhc_prepare.argtypes = [vp, vp, u64, vp, vp, vp, vp, u64, vp, vp]
+    lib.yvex_b200_mhc_post.argtypes = [vp, vp, vp, vp, vp, u64, vp, vp, vp]
     lib.yvex_b200_attention_static_scratch_bytes.restype = u64
     lib.yvex_b200_attention_static_scratch_bytes.argtypes = []
     lib.yvex_b200_attention_gqa_decode_static.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, C.c_float,
@@ -74,7 +84,8 @@ EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_ge
            "yvex_b200_moe_expert_rows_workspace_bytes", "yvex_b200_moe_expert_rows", "yvex_b200_moe_combine",
            "yvex_b200_attention_workspace_bytes", "yvex_b200_attention_gqa_decode",
            "yvex_b200_attention_f32", "yvex_b200_attention_static_scratch_bytes",
-           "yvex_b200_attention_gqa_decode_static"]
+           "yvex_b200_attention_gqa_decode_static", "yvex_b200_mhc_workspace_bytes", "yvex_b200_mhc_prepare",
+           "yvex_b200_mhc_post"]
 
 
 def _torch():
@@ -220,6 +231,36 @@ def moe_route(geom, weights, status, rows_f32=None, logits=None, token_ids=None)
     _check(lib.yvex_b200_moe_route(C.byref(geom), C.byref(weights), _p(rows_f32), _p(logits), _p(token_ids), rows,
                                    _p(selected), _p(wts), _p(lg), None, 0, _p(status.word), _stream()), "moe_route")
     return selected, wts, lg
+
+
+def mhc_of(hidden, streams, mhc_fn, scale, base, norm, sinkhorn_iterations=20, rms_epsilon=1e-6, mhc_epsilon=1e-6,
+           post_multiplier=2.0):
+    """Envelope description over device F32 tensors (kept alive by the returned struct)."""
+    m = Mhc(hidden, streams, sinkhorn_iterations, rms_epsilon, mhc_epsilon, post_multiplier, _p(mhc_fn), _p(scale),
+            _p(base), _p(norm))
+    m._keep = (mhc_fn, scale, base, norm)
+    return m
+
+
+def mhc_prepare(m, expanded, status):
+    """expanded [rows, streams*hidden] f32 -> (normalized [rows, hidden], post [rows, streams], combination [rows, S*S])."""
+    torch = _torch()
+    rows, S, H = expanded.shape[0], m.streams, m.hidden
+    normalized = torch.empty((rows, H), dtype=torch.float32, device=expanded.device)
+    post = torch.empty((rows, S), dtype=torch.float32, device=expanded.device)
+    comb = torch.empty((rows, S * S), dtype=torch.float32, device=expanded.device)
+    ws = torch.empty(int(lib.yvex_b200_mhc_workspace_bytes(S, rows)), dtype=torch.uint8, device=expanded.device)
+    _check(lib.yvex_b200_mhc_prepare(C.byref(m), _p(expanded), rows, _p(normalized), _p(post), _p(comb), _p(ws), ws.numel(),
+                                     _p(status.word), _stream()), "mhc_prepare")
+    return normalized, post, comb
+
+
+def mhc_post(m, core, expanded, post, comb, status):
+    torch = _torch()
+    out = torch.empty_like(expanded)
+    _check(lib.yvex_b200_mhc_post(C.byref(m), _p(core), _p(expanded), _p(post), _p(comb), expanded.shape[0], _p(out),
+                                  _p(status.word), _stream()), "mhc_post")
+    return out
 
 
 def attention_gqa_decode(q, k, v, position, scale, status, workspace=None, out=None):
