@@ -2,7 +2,10 @@
 //
 // Problem: for every expert group g with n_g token rows, OUT[row][m] = sum_k W_g[m][k] * X[row][k],
 // W_g stored as GGUF superblocks. Weights sit on the MMA M side (128-row tiles), tokens on N
-// (<=128 per tile, ragged tails padded to 16), so a small group wastes at most 15 columns.
+// (<=256 per tile for qtypes without a min term, <=128 for the affine ones whose second
+// accumulator needs the other half of TMEM; ragged tails padded to 16), so a small group wastes
+// at most 15 columns. A wider N halves the shared-memory traffic per flop of everything on the
+// weight side (decode stores, table lookups, A operand reads), which is what bounds this kernel.
 //
 // Exactness: the A operand carries EXACT small integers in fp16 (IQ2_XXS: +-{8,25,43}*(2*sub+1);
 // Q4_K / Q2_K: code * sub-scale), the B operand the fp16 image of bf16-exact activations, so
@@ -12,7 +15,7 @@
 // being filled. Affine qtypes add one more K=16/32 MMA per superblock: A' = integer mins,
 // B' = per-sub-block activation sums (hi/lo fp16 split), drained as acc -= dmin * tmem'.
 //
-// CTA = 20 warps, persistent over a device-built tile list:
+// CTA = 20 warps (N = 128) or 28 warps (N = 256), persistent over a device-built tile list:
 //   warp 0      TMA producer: activation tiles [N x 64] fp16, 128-byte swizzle, mbarrier tx
 //   warps 1-2   MMA issuers (one elected lane each, alternating superblocks / TMEM buffers):
 //               4 x tcgen05.mma (K=16) per 64-K chunk
@@ -24,7 +27,8 @@
 //               ahead of the decode; then thread = (row, half of a 64-K chunk) decodes 32 weights
 //               to fp16 and stores four 16-byte chunks into the swizzled A tile. The same warps
 //               write the A' rows and the per-row block scales for the epilogue.
-//   warps 12-19 epilogue: TMEM -> registers (tcgen05.ld), scale, accumulate, final store
+//   warps 12..  epilogue, one warp per (32 TMEM lanes, 64 columns): TMEM -> registers
+//               (tcgen05.ld), scale, accumulate, final store
 // Every mbarrier wait is bounded; on expiry the CTA sets status 3, unwinds and frees its TMEM.
 #pragma once
 #include "gemv_mma.cuh"
@@ -33,20 +37,19 @@
 
 namespace yb {
 
-constexpr int kGemmThreads = 640;
-constexpr int kTileM = 128, kTileN = 128, kChunkK = 64;
+constexpr int kTileM = 128, kBoxN = 128, kMaxTileN = 256, kChunkK = 64;
 constexpr int kStages = 4;                                  // {A, B} 64-K chunk stages: two rings of two
-constexpr uint32_t kTileBytes = kTileM * kChunkK * 2;        // 16 KiB, both A and B chunks
+constexpr uint32_t kTileBytes = kTileM * kChunkK * 2;        // 16 KiB: an A chunk, or one 128-row box of a B chunk
 constexpr uint32_t kTmemCols = 512;
 constexpr int kProducerWarps = 8, kRowsPerWarp = kTileM / kProducerWarps;
 constexpr int kScaleRing = 4;                               // superblocks of per-row scales kept for the epilogue
 
-// <=128 token rows of one expert (expert < 0: the shared expert). Column blocks of the same expert
-// form groups of at most kGroupBlocks consecutive entries [first, first + count): the tiles of a
+// <= kTileN token rows of one expert (expert < 0: the shared expert). Column blocks of the same expert
+// form groups of consecutive entries [first, first + count) covering <= kGroupRows rows: the tiles of a
 // group are walked weight tile by weight tile, so the CTAs running side by side share one weight
 // tile (read from DRAM once) while the group's activation rows stay in L2.
 struct ColBlock { int row0, ncols, expert, first, count, pad; };
-constexpr int kGroupBlocks = 8;
+constexpr int kGroupRows = 1024;
 
 struct GemmParams {
     const uint8_t *w_routed[2], *w_shared[2];   // packs; 2 matrices (gate, up) or 1 (down)
@@ -211,25 +214,31 @@ struct GemmQ2k {
 // decode tables and the barriers.
 template <class Dec> struct GemmPlan {
     static constexpr bool kHasMin = Dec::kMinSlots > 0;
+    static constexpr int kTileN = kHasMin ? 128 : 256;                              // columns per tile
+    static constexpr int kEpilogueWarps = kTileN / 16;                              // (4 lane quarters) x (kTileN / 64)
+    static constexpr int kThreads = 32 * (12 + kEpilogueWarps);
+    static constexpr uint32_t kBTileBytes = (kTileN / kBoxN) * kTileBytes;
     static constexpr uint32_t kRawBuf = kRowsPerWarp * Dec::kRawWords + 4;          // words; +4: funnel reads run one word over
     static constexpr uint32_t kLoads = (kRowsPerWarp * Dec::kRawWords + 31) / 32;   // words per lane per superblock
-    static constexpr size_t kTilesBytes = (size_t)(2 * kStages + (kHasMin ? 2 : 0)) * kTileBytes;
+    static constexpr size_t kTilesBytes = (size_t)kStages * (kTileBytes + kBTileBytes) + (kHasMin ? 2 : 0) * (size_t)kTileBytes;
     static constexpr size_t kRawBytes = (size_t)kProducerWarps * 2 * kRawBuf * 4;
     static constexpr size_t kScaleBytes = (size_t)kScaleRing * kTileM * sizeof(float2);
     static constexpr size_t kBytes = 1024 + kTilesBytes + kRawBytes + kScaleBytes + sizeof(MmaTables) + sizeof(GemmSmem) + 64;
 };
 
 template <class Dec>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(GemmPlan<Dec>::kThreads, 1)
 moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
     using namespace sm100;
     using Plan = GemmPlan<Dec>;
     constexpr bool kHasMin = Plan::kHasMin;
+    constexpr int kTileN = Plan::kTileN;
+    constexpr uint32_t kBTileBytes = Plan::kBTileBytes;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t *a_tiles = tiles;                                   // [kStages][16 KiB]
-    uint8_t *b_tiles = tiles + kStages * kTileBytes;            // [kStages][16 KiB]
-    uint8_t *min_tiles = b_tiles + kStages * kTileBytes;        // [2][16 KiB] when the qtype has mins
+    uint8_t *b_tiles = tiles + kStages * kTileBytes;            // [kStages][16 or 32 KiB]
+    uint8_t *min_tiles = b_tiles + kStages * kBTileBytes;       // [2][16 KiB] when the qtype has mins
     uint32_t *raw_stage = reinterpret_cast<uint32_t *>(tiles + Plan::kTilesBytes);
     float2 *dscale = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(raw_stage) + Plan::kRawBytes);
     MmaTables *tab = reinterpret_cast<MmaTables *>(reinterpret_cast<uint8_t *>(dscale) + Plan::kScaleBytes);
@@ -241,7 +250,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
         // so an MMA issuer pays for one wait per 64-K chunk, not two.
         for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], kProducerWarps + 1); mbar_init(&sm->empty[s], 1); }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(&sm->acc_full[b], 1); mbar_init(&sm->acc_empty[b], 8);
+            mbar_init(&sm->acc_full[b], 1); mbar_init(&sm->acc_empty[b], Plan::kEpilogueWarps);
             mbar_init(&sm->min_full[b], kProducerWarps + 1); mbar_init(&sm->min_empty[b], 1);
         }
         sm->abort = 0;
@@ -282,11 +291,13 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
             for (long long t = blockIdx.x; t < tiles_total && !*abort; t += gridDim.x) {
                 ColBlock cb; int mat, mt;
                 tile_of(t, cb, mat, mt);
+                const bool two = cb.ncols > kBoxN;             // a second 128-row box (only when kTileN = 256)
                 for (int kc = 0; kc < p.K / kChunkK; ++kc, ++it) {
                     const uint32_t s = stage_of(it), ph = phase_of(it);
                     if (!mbar_wait(&sm->empty[s], ph ^ 1u, abort)) break;
-                    mbar_expect_tx(&sm->full[s], kTileBytes);
-                    tma_load_2d(b_tiles + s * kTileBytes, &act_map, kc * kChunkK, cb.row0, &sm->full[s]);
+                    mbar_expect_tx(&sm->full[s], two ? 2 * kTileBytes : kTileBytes);
+                    tma_load_2d(b_tiles + s * kBTileBytes, &act_map, kc * kChunkK, cb.row0, &sm->full[s]);
+                    if (two) tma_load_2d(b_tiles + s * kBTileBytes + kTileBytes, &act_map, kc * kChunkK, cb.row0 + kBoxN, &sm->full[s]);
                 }
             }
         }
@@ -317,7 +328,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
                         if (!mbar_wait(&sm->full[s], ph, abort)) break;
                         tc_fence_after();
                         // descriptors differ from the stage-0 ones only in the start-address field (16-byte units)
-                        const uint64_t ad = adesc0 + (uint64_t)(s * (kTileBytes >> 4)), bd = bdesc0 + (uint64_t)(s * (kTileBytes >> 4));
+                        const uint64_t ad = adesc0 + (uint64_t)(s * (kTileBytes >> 4)), bd = bdesc0 + (uint64_t)(s * (kBTileBytes >> 4));
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             umma_f16(tmem + mine * kTileN, ad + 2 * k, bd + 2 * k, idesc, (c | k) ? 1u : 0u);
@@ -328,7 +339,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
                         tc_fence_after();
 #pragma unroll
                         for (int k = 0; k < Dec::kMinSlots / 16; ++k)
-                            umma_f16(tmem + 256 + mine * kTileN, amin0 + 2 * k, bmin0 + 2 * k, idesc, k ? 1u : 0u);
+                            umma_f16(tmem + 2 * kTileN + mine * kTileN, amin0 + 2 * k, bmin0 + 2 * k, idesc, k ? 1u : 0u);
                         umma_commit(&sm->min_empty[mine]);
                     }
                     umma_commit(&sm->acc_full[mine]);
@@ -438,7 +449,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
         }
     } else {
         // ---------------- epilogue ----------------
-        const int ew = warp - 12, quarter = warp & 3, colhalf = ew >> 2;     // TMEM lanes 32*quarter.., columns 64*colhalf..
+        const int ew = warp - 12, quarter = warp & 3, colhalf = ew >> 2;     // TMEM lanes 32*quarter.., columns 64*colhalf.. (colhalf < kTileN / 64)
         const int row = 32 * quarter + lane;
         const uint32_t lane_addr = (uint32_t)(32 * quarter) << 16;
         uint32_t sb_it = 0;
@@ -465,7 +476,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
 #pragma unroll
                         for (int i = 0; i < 16; ++i) acc[16 * q + i] = fmaf(d, __uint_as_float(v[i]), acc[16 * q + i]);
                         if (kHasMin) {
-                            tmem_ld16(tmem + lane_addr + 256 + buf * kTileN + 64 * colhalf + 16 * q, v);
+                            tmem_ld16(tmem + lane_addr + 2 * kTileN + buf * kTileN + 64 * colhalf + 16 * q, v);
                             tmem_ld_wait();
 #pragma unroll
                             for (int i = 0; i < 16; ++i) acc[16 * q + i] = fmaf(-dmin, __uint_as_float(v[i]), acc[16 * q + i]);

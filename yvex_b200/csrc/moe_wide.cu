@@ -53,17 +53,18 @@ __global__ void wide_count_kernel(const int *expert_of_pair, uint64_t pairs, int
 // One thread: exclusive scan of the group sizes and the column-block list in expert order
 // (bin `experts` is the shared expert, published as expert -1).
 __global__ void wide_plan_kernel(const int *counts, int experts, uint64_t pairs, int *offsets, ColBlock *blocks,
-                                 int *num_blocks, int max_blocks, int *status) {
+                                 int *num_blocks, int max_blocks, int tile_n, int *status) {
     if (threadIdx.x || blockIdx.x) return;
     int off = 0, nb = 0;
     for (int e = 0; e <= experts; ++e) {
         offsets[e] = off;
-        const int nblocks = (counts[e] + kTileN - 1) / kTileN;
+        const int nblocks = (counts[e] + tile_n - 1) / tile_n;
+        const int per_group = kGroupRows / tile_n;                          // groups of <= kGroupRows token rows
         for (int b = 0; b < nblocks; ++b) {
-            const int first = nb - b % kGroupBlocks;                        // groups of <= kGroupBlocks blocks
-            const int count = min(kGroupBlocks, nblocks - (b - b % kGroupBlocks));
+            const int first = nb - b % per_group;
+            const int count = min(per_group, nblocks - (b - b % per_group));
             if (nb < max_blocks)
-                blocks[nb] = ColBlock{off + b * kTileN, min(kTileN, counts[e] - b * kTileN), e < experts ? e : -1, first, count, 0};
+                blocks[nb] = ColBlock{off + b * tile_n, min(tile_n, counts[e] - b * tile_n), e < experts ? e : -1, first, count, 0};
             ++nb;
         }
         off += counts[e];
@@ -171,7 +172,7 @@ __global__ void wide_unsort_kernel(const uint16_t *y, const int *pos_of_pair, ui
 struct PairWorkspace {
     int *counts, *offsets, *perm, *pos_of_pair, *num_blocks, *expert_of_pair, *src_of_pair;
     float *weight_of_pair;
-    ColBlock *blocks;
+    ColBlock *blocks, *blocks_down;         // column-block lists of the gate/up and the down GEMM (num_blocks[0], [1])
     __half *act_h, *mid_h, *sums;
     float *gate, *up;
     uint16_t *y;
@@ -180,7 +181,7 @@ struct PairWorkspace {
         auto fix = [&](auto *&ptr) { ptr = reinterpret_cast<std::remove_reference_t<decltype(ptr)>>(
                                          reinterpret_cast<uintptr_t>(base) + reinterpret_cast<uintptr_t>(ptr)); };
         fix(counts); fix(offsets); fix(perm); fix(pos_of_pair); fix(num_blocks); fix(expert_of_pair); fix(src_of_pair);
-        fix(weight_of_pair); fix(blocks); fix(act_h); fix(mid_h); fix(sums); fix(gate); fix(up); fix(y);
+        fix(weight_of_pair); fix(blocks); fix(blocks_down); fix(act_h); fix(mid_h); fix(sums); fix(gate); fix(up); fix(y);
     }
 };
 
@@ -189,16 +190,17 @@ static uint64_t pair_layout(const MoeGeom &g, uint64_t pairs, uint64_t base_off,
     uint64_t off = base_off;
     auto take = [&](uint64_t bytes) { uint64_t at = off; off = (off + bytes + 255) & ~255ull; return at; };
     PairWorkspace l{};
-    l.max_blocks = (int)(pairs / kTileN + g.experts + 2);
+    l.max_blocks = (int)(pairs / kBoxN + g.experts + 2);
     l.counts = reinterpret_cast<int *>(take((g.experts + 2) * 4));
     l.offsets = reinterpret_cast<int *>(take((g.experts + 3) * 4));
-    l.num_blocks = reinterpret_cast<int *>(take(4));
+    l.num_blocks = reinterpret_cast<int *>(take(8));
     l.perm = reinterpret_cast<int *>(take(pairs * 4));
     l.pos_of_pair = reinterpret_cast<int *>(take(pairs * 4));
     l.expert_of_pair = reinterpret_cast<int *>(take(pairs * 4));
     l.src_of_pair = reinterpret_cast<int *>(take(pairs * 4));
     l.weight_of_pair = reinterpret_cast<float *>(take(pairs * 4));
     l.blocks = reinterpret_cast<ColBlock *>(take((uint64_t)l.max_blocks * sizeof(ColBlock)));
+    l.blocks_down = reinterpret_cast<ColBlock *>(take((uint64_t)l.max_blocks * sizeof(ColBlock)));
     l.act_h = reinterpret_cast<__half *>(take(pairs * g.hidden * 2));
     l.mid_h = reinterpret_cast<__half *>(take(pairs * g.inter * 2));
     l.sums = reinterpret_cast<__half *>(take(pairs * (g.inter / 256) * 64));
@@ -225,12 +227,12 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
     return fn;
 }
 
-// Row-major fp16 [rows][width] -> tiles of [kTileN rows][64 columns], 128-byte swizzle, zero fill.
+// Row-major fp16 [rows][width] -> boxes of [kBoxN rows][64 columns], 128-byte swizzle, zero fill.
 static int make_act_map(CUtensorMap *map, const __half *base, uint64_t rows, uint64_t width) {
     auto fn = encode_fn();
     if (!fn) return ERR_BACKEND;
     cuuint64_t dims[2] = {width, rows}, strides[1] = {width * 2};
-    cuuint32_t box[2] = {kChunkK, kTileN}, estr[2] = {1, 1};
+    cuuint32_t box[2] = {kChunkK, kBoxN}, estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -246,7 +248,7 @@ static int launch_gemm(const CUtensorMap &map, const GemmParams &p, cudaStream_t
             return ERR_BACKEND;
         configured = true;
     }
-    moe_grouped_gemm_kernel<Dec><<<kSmCount, kGemmThreads, smem, s>>>(map, p);
+    moe_grouped_gemm_kernel<Dec><<<kSmCount, GemmPlan<Dec>::kThreads, smem, s>>>(map, p);
     return launch_status(1);
 }
 
@@ -260,6 +262,8 @@ static int run_gemm(unsigned qtype, const CUtensorMap &map, const GemmParams &p,
 }
 
 static bool gemm_qtype(unsigned q) { return q == Q_IQ2_XXS || q == Q_Q4_K || q == Q_Q2_K; }
+// Token columns per GEMM tile: 256 unless the qtype's min term needs the second accumulator.
+static int gemm_tile_n(unsigned q) { return q == Q_IQ2_XXS ? GemmPlan<GemmIq2>::kTileN : q == Q_Q4_K ? GemmPlan<GemmQ4k>::kTileN : GemmPlan<GemmQ2k>::kTileN; }
 
 bool moe_wide_gemm_eligible(const MoeGeom &g, const MoeWeights &w) {
     const uintptr_t ptrs = (uintptr_t)w.gate | (uintptr_t)w.up | (uintptr_t)w.down | (uintptr_t)w.shared_gate |
@@ -277,11 +281,14 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     const int bins = (int)g.experts + 1;
     cudaMemsetAsync(pw.counts, 0, (g.experts + 2) * 4, s);
     wide_count_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(pw.expert_of_pair, pairs, bins, pw.counts, status);
-    wide_plan_kernel<<<1, 32, 0, s>>>(pw.counts, (int)g.experts, pairs, pw.offsets, pw.blocks, pw.num_blocks, pw.max_blocks, status);
+    wide_plan_kernel<<<1, 32, 0, s>>>(pw.counts, (int)g.experts, pairs, pw.offsets, pw.blocks, pw.num_blocks, pw.max_blocks,
+                                      gemm_tile_n(g.gate_qtype), status);
+    wide_plan_kernel<<<1, 32, 0, s>>>(pw.counts, (int)g.experts, pairs, pw.offsets, pw.blocks_down, pw.num_blocks + 1, pw.max_blocks,
+                                      gemm_tile_n(g.down_qtype), status);
     wide_scatter_kernel<<<(unsigned)bins, 512, 0, s>>>(pw.expert_of_pair, pairs, pw.offsets, pw.perm, pw.pos_of_pair);
     wide_gather_kernel<<<grid_for(pairs * (g.hidden / 8), 256, 16), 256, 0, s>>>(rows_h, pw.perm, pw.src_of_pair, pairs, g.hidden,
                                                                                  pw.act_h);
-    int rc = launch_status(4);
+    int rc = launch_status(5);
     if (rc != OK) return rc;
     mark_phase(2, s);
 
@@ -306,7 +313,7 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     dn.w_routed[0] = (const uint8_t *)w.down; dn.w_shared[0] = (const uint8_t *)w.shared_down;
     dn.row_bytes = g.inter / dg.elems * dg.bytes;
     dn.M = (int)g.hidden; dn.K = (int)g.inter; dn.nmat = 1;
-    dn.colblocks = pw.blocks; dn.num_colblocks = pw.num_blocks;
+    dn.colblocks = pw.blocks_down; dn.num_colblocks = pw.num_blocks + 1;
     dn.out_bf16 = pw.y; dn.sums = pw.sums; dn.status = status;
     rc = run_gemm(g.down_qtype, mid_map, dn, s);
     if (rc != OK) return rc;
