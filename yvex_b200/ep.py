@@ -82,11 +82,16 @@ class ExpertParallelLayer:
         recv_rows = self._all_to_all(send_rows, send_counts, recv_counts)
         recv_meta = self._all_to_all(meta, send_counts, recv_counts)
 
-        y_recv = ops.expert_rows(recv_rows, recv_meta[:, 0].contiguous(), recv_meta[:, 1].contiguous().view(torch.float32))
-        shared_ids = torch.full((t,), -1, dtype=torch.int32, device=x.device)
-        y_shared = ops.expert_rows(xh, shared_ids, torch.ones(t, dtype=torch.float32, device=x.device))
+        # One pair list per rank: the received routed pairs, then this rank's own tokens for the (replicated)
+        # shared expert as pairs of expert -1 with weight 1 - one set of grouped GEMM launches instead of two.
+        n_recv = recv_rows.shape[0]
+        ids = torch.cat((recv_meta[:, 0], torch.full((t,), -1, dtype=torch.int32, device=x.device)))
+        pair_w = torch.cat((recv_meta[:, 1].contiguous().view(torch.float32), torch.ones(t, dtype=torch.float32, device=x.device)))
+        y_all = ops.expert_rows(torch.cat((recv_rows, xh)), ids, pair_w)
+        y_recv, y_shared = y_all[:n_recv], y_all[n_recv:]
 
         y_back = self._all_to_all(y_recv, recv_counts, send_counts)      # reverse direction, same splits
-        y_pairs = torch.empty_like(y_back)
-        y_pairs.index_copy_(0, order, y_back)                             # back to (token, rank) order
+        inverse = torch.empty_like(order)
+        inverse[order] = torch.arange(order.numel(), device=order.device)
+        y_pairs = y_back.index_select(0, inverse)                         # back to (token, rank) order
         return ops.combine(y_pairs, y_shared, k), sel, wts
