@@ -15,7 +15,7 @@
  *
  * Struct layouts carry the fields this path reads, under the reference's field names; they are
  * not binary-identical to the reference's structs (those embed planner / identity state that
- * never reaches the backend). INTEGRATION.md shows the field-by-field adapter.
+ * never reaches the backend); a caller inside the reference copies them field by field.
  */
 #ifndef YVEX_B200_BACKEND_H
 #define YVEX_B200_BACKEND_H
