@@ -185,6 +185,30 @@ def test_execute_rows_with_mhc_envelope_vs_frozen_reference(B, golden):
     assert be.close() == B.OK
 
 
+def test_execute_rows_envelope_with_bf16_coefficients_vs_oracle(B, port):
+    """BF16 coefficient tensors (the other flat format the reference decodes, src/graph/moe.c:416-419)."""
+    H, S, T, seed = CASES["envelope"]["small"]
+    fn, scale, base, norm, expanded = envelope_inputs("small")
+    spec, weights, router, _, _ = layer_inputs("small_router")
+    coeff = {"ffn_norm": norm, "mhc_fn": fn, "mhc_base": base, "mhc_scale": scale}
+    rounded = {k: synth.bf16_round(v) for k, v in coeff.items()}
+    be = B.Backend()
+    arena = B.ResidentArena(be, dict(weights, router=router, **{k: synth.bf16_bits(v).reshape(v.shape) for k, v in coeff.items()}))
+    job = B.moe_job(arena, spec, residual_streams=S, envelope_policy=ENVELOPE_POLICY)
+    for slot in (B.W_FFN_NORM, B.W_MHC_FUNCTION, B.W_MHC_BASE, B.W_MHC_SCALE):
+        job.weights[slot].qtype = synth.BF16
+    ops, _ = attach_workspace(B, be, job, T)
+    rc, out, sel, _, _ = run_rows(B, be, ops, job, expanded, None)
+    assert rc == B.OK, be.message()
+    M = port.mhc(H, S, rounded["mhc_fn"], rounded["mhc_scale"], rounded["mhc_base"], rounded["ffn_norm"], **ENVELOPE_POLICY)
+    prep = [port.mhc_prepare(M, expanded[t]) for t in range(T)]
+    normalized = np.stack([p[1] for p in prep])
+    rcp, core, sel0, _ = port.moe_tokens(port.layer(spec, weights, router=router), normalized, threads=4)
+    want = np.stack([port.mhc_post(M, core[t], expanded[t], prep[t][2], prep[t][3])[1] for t in range(T)])
+    assert rcp == 0 and (sel == sel0).all() and rel_l2(out, want) <= 1e-3
+    assert be.close() == B.OK
+
+
 def test_execute_rows_wide_vs_oracle(B, port):
     H, E, k, I, T = 512, 8, 2, 256, 150
     spec = synth.MoELayerSpec(H, E, k, I, down_qtype=synth.Q4_K)

@@ -56,9 +56,13 @@ static unsigned long long envelope_streams(const yvex_moe_layer_plan *layer) {
 static unsigned long long staging_bytes(const yvex_b200_moe_geometry *g, unsigned long long rows, unsigned long long streams) {
     unsigned long long bytes = 2ull * align256(rows * g->hidden * streams * 4ull) + align256(rows * g->experts * 4ull) +
                                2ull * align256(rows * g->topk * 4ull) + align256(rows * 4ull) + 256ull;
-    if (streams > 1ull)
+    if (streams > 1ull) {
+        const unsigned long long mix_rows = (streams + 2ull) * streams;
         bytes += 2ull * align256(rows * g->hidden * 4ull) + align256(rows * streams * 4ull) + align256(rows * streams * streams * 4ull) +
                  align256(yvex_b200_mhc_workspace_bytes(streams, rows));
+        /* F32 images of BF16 coefficient tensors (norm, mixing function, base, scale) */
+        bytes += align256(g->hidden * 4ull) + align256(mix_rows * streams * g->hidden * 4ull) + align256(mix_rows * 4ull) + align256(12ull);
+    }
     return bytes;
 }
 
@@ -126,7 +130,9 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     yvex_b200_mhc mhc;
     unsigned long long rows, cursor = 0, need, kernel_ws, launches0, in_bytes, hid_bytes, sel_count, streams, mhc_ws = 0;
     unsigned char *ws_in, *ws_out, *ws_logits, *ws_sel, *ws_wts, *ws_ids, *ws_kernel;
-    unsigned char *ws_norm = NULL, *ws_core = NULL, *ws_post = NULL, *ws_comb = NULL, *ws_mhc = NULL;
+    unsigned char *ws_norm = NULL, *ws_core = NULL, *ws_post = NULL, *ws_comb = NULL, *ws_mhc = NULL, *ws_coeff[4] = {NULL, NULL, NULL, NULL};
+    unsigned long long coeff_count[4] = {0, 0, 0, 0};
+    static const int coeff[4] = {YVEX_MOE_WEIGHT_FFN_NORM, YVEX_MOE_WEIGHT_MHC_FUNCTION, YVEX_MOE_WEIGHT_MHC_BASE, YVEX_MOE_WEIGHT_MHC_SCALE};
     const float *dev_in, *dev_logits = NULL, *layer_in;
     float *dev_out, *layer_out;
     int rc, code, defer, slot;
@@ -188,15 +194,14 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     if (g.router_class == 0 && (!batch->token_ids_present || !batch->token_ids))
         return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "MoE hash router requires token IDs");
     if (streams > 1ull) {
-        static const int coeff[4] = {YVEX_MOE_WEIGHT_FFN_NORM, YVEX_MOE_WEIGHT_MHC_FUNCTION, YVEX_MOE_WEIGHT_MHC_BASE,
-                                     YVEX_MOE_WEIGHT_MHC_SCALE};
         const unsigned long long mix_rows = (streams + 2ull) * streams;
-        const unsigned long long want[4] = {g.hidden * 4ull, mix_rows * streams * g.hidden * 4ull, mix_rows * 4ull, 3ull * 4ull};
+        coeff_count[0] = g.hidden; coeff_count[1] = mix_rows * streams * g.hidden; coeff_count[2] = mix_rows; coeff_count[3] = 3ull;
         for (int i = 0; i < 4; ++i) {
+            /* F32 or BF16, like the reference's flat coefficient decoder (src/graph/moe.c:405-428) */
             const yvex_moe_weight_view *v = &job->weights[coeff[i]];
             if (!addr[coeff[i]]) return yvex_refuse(err, YVEX_ERR_STATE, where, "mHC envelope coefficients are not resident on this backend");
-            if (v->qtype != 0u || v->encoded_bytes != want[i])
-                return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "mHC envelope coefficients must be F32 tensors of the layer's geometry");
+            if (!((v->qtype == 0u && v->encoded_bytes == coeff_count[i] * 4ull) || (v->qtype == 30u && v->encoded_bytes == coeff_count[i] * 2ull)))
+                return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "mHC envelope coefficients must be F32 or BF16 tensors of the layer's geometry");
         }
         if (batch->router_logits || batch->device_router_logits)
             return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "supplied router logits cannot be combined with the mHC envelope");
@@ -229,9 +234,10 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
         ws_post = yvex_workspace_take(backend, &cursor, rows * streams * 4ull);
         ws_comb = yvex_workspace_take(backend, &cursor, rows * streams * streams * 4ull);
         ws_mhc = yvex_workspace_take(backend, &cursor, mhc_ws);
+        for (int i = 0; i < 4; ++i) ws_coeff[i] = yvex_workspace_take(backend, &cursor, coeff_count[i] * 4ull);
     }
     if (!ws_in || !ws_out || !ws_logits || !ws_sel || !ws_wts || !ws_ids || !ws_kernel ||
-        (streams > 1ull && (!ws_norm || !ws_core || !ws_post || !ws_comb || !ws_mhc)))
+        (streams > 1ull && (!ws_norm || !ws_core || !ws_post || !ws_comb || !ws_mhc || !ws_coeff[0] || !ws_coeff[1] || !ws_coeff[2] || !ws_coeff[3])))
         return yvex_refuse(err, YVEX_ERR_NOMEM, where, "attached device workspace is smaller than workspace_required");
 
     if (batch->device_rows) {
@@ -280,6 +286,15 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     layer_in = dev_in;
     layer_out = dev_out;
     if (streams > 1ull) {
+        const float **slot_ptr[4] = {&mhc.norm, &mhc.mhc_fn, &mhc.base, &mhc.scale};
+        for (int i = 0; i < 4; ++i) {
+            if (job->weights[coeff[i]].qtype != 30u) continue;
+            rc = yvex_b200_dequant_rows(30u, addr[coeff[i]], 1ull, coeff_count[i], coeff_count[i] * 2ull, (float *)ws_coeff[i],
+                                        backend->status_word, backend->stream);
+            if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
+            if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused an mHC coefficient tensor");
+            *slot_ptr[i] = (const float *)ws_coeff[i];
+        }
         rc = yvex_b200_mhc_prepare(&mhc, dev_in, rows, (float *)ws_norm, (float *)ws_post, (float *)ws_comb, ws_mhc, mhc_ws,
                                    backend->status_word, backend->stream);
         if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
