@@ -116,23 +116,28 @@ __global__ void wide_gather_kernel(const __half *rows_h, const int *perm, const 
 
 // mid = bf16(silu(min(g,L)) * clamp(u,+-L) * w) as fp16, plus hi/lo fp16 sums over `group`
 // consecutive intermediates (32 for Q4_K, 16 for Q2_K, 0 = none) for the down GEMM's min term.
-__global__ void wide_swiglu_kernel(const float *gate, const float *up, const int *perm, const float *weight_of_pair,
-                                   uint64_t rows, uint64_t inter, float limit, int group, __half *mid_h, __half *sums,
-                                   int *status) {
-    const int lane = threadIdx.x & 31;
-    const uint64_t total = rows * inter;          // inter is a multiple of 256, so warps never straddle rows
-    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t row = i / inter, col = i % inter;
+// blockIdx.x covers a row in 4-element pieces (inter is a multiple of 256, blocks of 64 threads
+// are therefore always full), blockIdx.y strides the rows: no per-element division.
+__global__ void __launch_bounds__(64)
+wide_swiglu_kernel(const float *gate, const float *up, const int *perm, const float *weight_of_pair,
+                   uint64_t rows, uint64_t inter, float limit, int group, __half *mid_h, __half *sums, int *status) {
+    const uint32_t q = (uint32_t)(inter / 4), col4 = blockIdx.x * blockDim.x + threadIdx.x, col = 4 * col4;
+    for (uint64_t row = blockIdx.y; row < rows; row += gridDim.y) {
         const float w = weight_of_pair[perm[row]];
         if (!isfinite(w)) raise(status, YVEX_B200_STATUS_NUMERIC);
-        const float v = swiglu_mid(gate[i], up[i], w, limit, status);
-        mid_h[i] = __float2half_rn(v);
+        const float4 g4 = __ldcs(reinterpret_cast<const float4 *>(gate) + row * q + col4);
+        const float4 u4 = __ldcs(reinterpret_cast<const float4 *>(up) + row * q + col4);
+        const float v0 = swiglu_mid(g4.x, u4.x, w, limit, status), v1 = swiglu_mid(g4.y, u4.y, w, limit, status);
+        const float v2 = swiglu_mid(g4.z, u4.z, w, limit, status), v3 = swiglu_mid(g4.w, u4.w, w, limit, status);
+        const __half2 h01 = __floats2half2_rn(v0, v1), h23 = __floats2half2_rn(v2, v3);
+        *reinterpret_cast<uint2 *>(mid_h + row * inter + col) =
+            make_uint2(*reinterpret_cast<const uint32_t *>(&h01), *reinterpret_cast<const uint32_t *>(&h23));
         if (group) {
-            float s = v;
-            for (int o = group / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            if ((lane & (group - 1)) == 0) {
+            float s = (v0 + v1) + (v2 + v3);
+            for (int o = group / 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);     // group / 4 lanes per sum
+            if ((threadIdx.x & (group / 4 - 1)) == 0) {
                 const __half hi = __float2half_rn(s), lo = __float2half_rn(s - __half2float(hi));
-                const uint64_t sb = col / 256, sub = (col % 256) / group, per = 256 / group;
+                const uint32_t sb = col / 256, sub = (col % 256) / group, per = 256 / group;
                 __half *dst = sums + (row * (inter / 256) + sb) * 32;
                 dst[sub] = hi;
                 dst[per + sub] = lo;
@@ -142,19 +147,42 @@ __global__ void wide_swiglu_kernel(const float *gate, const float *up, const int
 }
 
 // out[t] = bf16( sum_{rank} y[row(t, rank)] (rank order, f32) + y_shared[row(t)] ); `pos` maps a
-// pair index to its row in y (nullptr = identity).
-__global__ void wide_combine_kernel(const uint16_t *y, const uint16_t *y_shared, const int *pos, const int *pos_shared,
-                                    uint64_t tokens, uint64_t topk, uint64_t hidden, float *out) {
-    const uint64_t total = tokens * hidden;
-    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t t = i / hidden, h = i % hidden;
-        float routed = 0.0f;
+// pair index to its row in y (nullptr = identity). Threads take 8 columns (one 16-byte load per
+// source row); blockIdx.y strides the tokens.
+__global__ void __launch_bounds__(128)
+wide_combine_kernel(const uint16_t *y, const uint16_t *y_shared, const int *pos, const int *pos_shared,
+                    uint64_t tokens, uint64_t topk, uint64_t hidden, float *out) {
+    const uint32_t chunks = (uint32_t)(hidden / 8), c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= chunks) return;
+    for (uint64_t t = blockIdx.y; t < tokens; t += gridDim.y) {
+        float routed[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) routed[i] = 0.0f;
         for (uint64_t r = 0; r < topk; ++r) {
             const uint64_t row = pos ? (uint64_t)pos[t * topk + r] : t * topk + r;
-            routed += __uint_as_float((uint32_t)y[row * hidden + h] << 16);
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(y + row * hidden) + c);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                routed[2 * i] += __uint_as_float(w[i] << 16);
+                routed[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+            }
         }
         const uint64_t srow = pos_shared ? (uint64_t)pos_shared[t] : t;
-        out[i] = bf16_round(routed + __uint_as_float((uint32_t)y_shared[srow * hidden + h] << 16));
+        const uint4 sv = __ldg(reinterpret_cast<const uint4 *>(y_shared + srow * hidden) + c);
+        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+        float4 o0, o1;
+        o0.x = bf16_round(routed[0] + __uint_as_float(sw[0] << 16));
+        o0.y = bf16_round(routed[1] + __uint_as_float(sw[0] & 0xffff0000u));
+        o0.z = bf16_round(routed[2] + __uint_as_float(sw[1] << 16));
+        o0.w = bf16_round(routed[3] + __uint_as_float(sw[1] & 0xffff0000u));
+        o1.x = bf16_round(routed[4] + __uint_as_float(sw[2] << 16));
+        o1.y = bf16_round(routed[5] + __uint_as_float(sw[2] & 0xffff0000u));
+        o1.z = bf16_round(routed[6] + __uint_as_float(sw[3] << 16));
+        o1.w = bf16_round(routed[7] + __uint_as_float(sw[3] & 0xffff0000u));
+        float4 *dst = reinterpret_cast<float4 *>(out + t * hidden) + 2 * c;
+        dst[0] = o0;
+        dst[1] = o1;
     }
 }
 
@@ -307,8 +335,8 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     mark_phase(3, s);
 
     const int group = g.down_qtype == Q_Q4_K ? 32 : g.down_qtype == Q_Q2_K ? 16 : 0;
-    wide_swiglu_kernel<<<grid_for(pairs * g.inter, 256, 16), 256, 0, s>>>(pw.gate, pw.up, pw.perm, pw.weight_of_pair, pairs, g.inter,
-                                                                         (float)g.limit, group, pw.mid_h, pw.sums, status);
+    wide_swiglu_kernel<<<dim3((unsigned)(g.inter / 256), (unsigned)grid_for(pairs, 1, 16)), 64, 0, s>>>(
+        pw.gate, pw.up, pw.perm, pw.weight_of_pair, pairs, g.inter, (float)g.limit, group, pw.mid_h, pw.sums, status);
     GemmParams dn{};
     dn.w_routed[0] = (const uint8_t *)w.down; dn.w_shared[0] = (const uint8_t *)w.shared_down;
     dn.row_bytes = g.inter / dg.elems * dg.bytes;
@@ -354,8 +382,8 @@ extern "C" int yvex_b200_moe_wide(const yvex_b200_moe_geometry *geom, const yvex
                                                                 pw.expert_of_pair, pw.src_of_pair, pw.weight_of_pair);
         rc = run_pair_list(g, *w, pw, ws.xr_h, pairs, status, s);
         if (rc != OK) return rc;
-        wide_combine_kernel<<<grid_for(rows * g.hidden, 256, 16), 256, 0, s>>>(pw.y, pw.y, pw.pos_of_pair, pw.pos_of_pair + routed,
-                                                                             rows, g.topk, g.hidden, out);
+        wide_combine_kernel<<<dim3((unsigned)((g.hidden / 8 + 127) / 128), (unsigned)grid_for(rows, 1, 16)), 128, 0, s>>>(
+            pw.y, pw.y, pw.pos_of_pair, pw.pos_of_pair + routed, rows, g.topk, g.hidden, out);
         mark_phase(5, s);
         rc = launch_status(2);
     } else {
@@ -407,7 +435,10 @@ extern "C" int yvex_b200_moe_expert_rows(const yvex_b200_moe_geometry *geom, con
 extern "C" int yvex_b200_moe_combine(const void *y_routed_bf16, const void *y_shared_bf16, uint64_t tokens, uint64_t topk,
                                      uint64_t hidden, float *out, int *status, void *stream) {
     if (!y_routed_bf16 || !y_shared_bf16 || !out || !status || !tokens || !topk || !hidden) return ERR_INVALID_ARG;
-    wide_combine_kernel<<<grid_for(tokens * hidden, 256, 16), 256, 0, as_stream(stream)>>>(
+    if (hidden % 8 || ((reinterpret_cast<uintptr_t>(y_routed_bf16) | reinterpret_cast<uintptr_t>(y_shared_bf16) |
+                        reinterpret_cast<uintptr_t>(out)) & 15u))
+        return ERR_INVALID_ARG;
+    wide_combine_kernel<<<dim3((unsigned)((hidden / 8 + 127) / 128), (unsigned)grid_for(tokens, 1, 16)), 128, 0, as_stream(stream)>>>(
         static_cast<const uint16_t *>(y_routed_bf16), static_cast<const uint16_t *>(y_shared_bf16), nullptr, nullptr, tokens, topk,
         hidden, out);
     return launch_status(1);
