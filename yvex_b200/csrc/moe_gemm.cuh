@@ -226,6 +226,10 @@ template <class Dec> struct GemmPlan {
     static constexpr size_t kBytes = 1024 + kTilesBytes + kRawBytes + kScaleBytes + sizeof(MmaTables) + sizeof(GemmSmem) + 64;
 };
 
+constexpr int kCtlRegs = 32, kProdRegs = 56, kEpiRegs = 88;
+template <int N> __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
 template <class Dec>
 __global__ void __launch_bounds__(GemmPlan<Dec>::kThreads, 1)
 moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
@@ -283,6 +287,17 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
         return base + (uint64_t)mt * kTileM * p.row_bytes;
     };
 
+    // Register budget per role (256-column tiles only: 28 warps leave 72 registers per thread, and the
+    // epilogue's 64 partial sums per thread do not fit in that): the control warps hand registers back
+    // and the epilogue warpgroups take them. Warps 0-3, 4-11 and 12+ are whole warpgroups.
+    if (kTileN == 256) {
+        static_assert(kTileN != 256 || 4 * kCtlRegs + kProducerWarps * kProdRegs + Plan::kEpilogueWarps * kEpiRegs <=
+                                           ((65536 / Plan::kThreads) & ~7) * (Plan::kThreads / 32),
+                      "the role budgets must fit in the registers the CTA was launched with, or the increase never returns");
+        if (warp < 4) reg_dealloc<kCtlRegs>();
+        else if (warp < 4 + kProducerWarps) reg_dealloc<kProdRegs>();
+        else reg_alloc<kEpiRegs>();
+    }
     if (warp == 0) {
         // ---------------- TMA producer: activation tiles ----------------
         if (lane == 0) {
