@@ -283,7 +283,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
         mt = r % mtiles;
     };
     auto weights_of = [&](const ColBlock &cb, int mat, int mt) {
-        const uint8_t *base = cb.expert < 0 ? p.w_shared[mat] : p.w_routed[mat] + (uint64_t)cb.expert * p.M * p.row_bytes;
+        // selects, not p.w_routed[mat]: a dynamically indexed parameter array makes the compiler copy the
+        // whole parameter block to local memory, and every later p.field read becomes a local load
+        const uint8_t *shared = mat ? p.w_shared[1] : p.w_shared[0], *routed = mat ? p.w_routed[1] : p.w_routed[0];
+        const uint8_t *base = cb.expert < 0 ? shared : routed + (uint64_t)cb.expert * p.M * p.row_bytes;
         return base + (uint64_t)mt * kTileM * p.row_bytes;
     };
 
@@ -502,18 +505,39 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm->acc_empty[buf]);
             }
-            // store: out[(row0 + n)][mt*128 + row]
-            const uint64_t m = (uint64_t)mt * kTileM + row;
+            // store: out[(row0 + n)][mt*128 + row]. A thread holds 64 token columns of ONE weight row, so a
+            // direct store is one instruction per column and 2 or 4 bytes per lane; the store path then takes
+            // longer than two superblocks of MMA work and the pipeline drains at every tile end. Instead
+            // every aligned group of four lanes transposes 4 x 4 blocks with shuffles: lane 4a+j ends up
+            // with weight rows 4a..4a+3 of token column 4b+j and stores them as one 8- or 16-byte vector
+            // (a quarter of the store instructions).
+            uint32_t nonfinite = 0;
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                if (i < ncols_here) {
-                    const uint64_t orow = (uint64_t)cb.row0 + 64 * colhalf + i;
-                    float v = acc[i];
-                    if (!isfinite(v)) raise(p.status, YVEX_B200_STATUS_NUMERIC);
+            for (int i = 0; i < 64; ++i) nonfinite |= (~__float_as_uint(acc[i]) & 0x7f800000u) == 0u;
+            if (nonfinite) raise(p.status, YVEX_B200_STATUS_NUMERIC);
+            const bool odd = lane & 1, hi = lane & 2;
+            const int j4 = lane & 3;
+            const uint64_t m0 = (uint64_t)mt * kTileM + 32 * quarter + (lane & ~3);
+            float *out_f32 = mat ? p.out_f32[1] : p.out_f32[0];
+#pragma unroll
+            for (int b = 0; b < 16; ++b) {
+                float r0 = acc[4 * b], r1 = acc[4 * b + 1], r2 = acc[4 * b + 2], r3 = acc[4 * b + 3];
+                float s0 = __shfl_xor_sync(0xffffffffu, odd ? r0 : r1, 1), s1 = __shfl_xor_sync(0xffffffffu, odd ? r2 : r3, 1);
+                if (odd) { r0 = s0; r2 = s1; } else { r1 = s0; r3 = s1; }
+                s0 = __shfl_xor_sync(0xffffffffu, hi ? r0 : r2, 2);
+                s1 = __shfl_xor_sync(0xffffffffu, hi ? r1 : r3, 2);
+                if (hi) { r0 = s0; r1 = s1; } else { r2 = s0; r3 = s1; }
+                const int col = 4 * b + j4;
+                if (col < ncols_here) {
+                    const uint64_t at = ((uint64_t)cb.row0 + 64 * colhalf + col) * p.M + m0;
                     // streaming stores: the results are not read again by this kernel and must not push the
                     // activation tiles and weight rows that other CTAs are about to reuse out of L2
-                    if (p.out_bf16) __stcs(p.out_bf16 + orow * p.M + m, bf16_bits(v));
-                    else __stcs(p.out_f32[mat] + orow * p.M + m, v);
+                    if (p.out_bf16) {
+                        const uint2 v = make_uint2(bf16_bits(r0) | ((uint32_t)bf16_bits(r1) << 16), bf16_bits(r2) | ((uint32_t)bf16_bits(r3) << 16));
+                        __stcs(reinterpret_cast<uint2 *>(p.out_bf16 + at), v);
+                    } else {
+                        __stcs(reinterpret_cast<float4 *>(out_f32 + at), make_float4(r0, r1, r2, r3));
+                    }
                 }
             }
         }
