@@ -16,21 +16,22 @@
 // B' = per-sub-block activation sums (hi/lo fp16 split), drained as acc -= dmin * tmem'.
 //
 // CTA = 20 warps (N = 128) or 28 warps (N = 256), persistent over a device-built tile list:
-//   warp 0      TMA producer: activation tiles [N x 64] fp16, 128-byte swizzle, mbarrier tx
+//   warp 0      TMA producer: activation tiles [N x 64] fp16, 128-byte swizzle, mbarrier tx; and the raw
+//               weight superblocks of the tile's 128 rows (u8 boxes, three superblocks in flight)
 //   warps 1-2   MMA issuers (one elected lane each, alternating superblocks / TMEM buffers):
 //               4 x tcgen05.mma (K=16) per 64-K chunk
 //   warp 3      B' tiles of the min term (copies the activation sums into the swizzled tile)
-//   warps 4-11  dequant producers. Each warp owns 16 weight rows of the tile. It copies the raw
-//               superblock bytes of its rows global -> registers -> shared with lanes running
-//               along a row (coalesced: every load instruction touches two or three lines; a
-//               thread-per-row load touches 32 and saturates the L1 data pipe), one superblock
-//               ahead of the decode; then thread = (row, half of a 64-K chunk) decodes 32 weights
-//               to fp16 and stores four 16-byte chunks into the swizzled A tile. The same warps
-//               write the A' rows and the per-row block scales for the epilogue.
+//   warps 4-11  dequant producers. Each warp owns 16 weight rows of the tile; thread = (row, half of
+//               a 64-K chunk) decodes 32 weights of the staged superblock to fp16 and stores four
+//               16-byte chunks into the swizzled A tile. The same warps write the A' rows and the
+//               per-row block scales for the epilogue. (Staging the raw bytes through these warps'
+//               registers cost them about as many instructions as the decode itself.)
 //   warps 12..  epilogue, one warp per (32 TMEM lanes, 64 columns): TMEM -> registers
 //               (tcgen05.ld), scale, accumulate, final store
 // Every mbarrier wait is bounded; on expiry the CTA sets status 3, unwinds and frees its TMEM.
 #pragma once
+#include <type_traits>
+
 #include "gemv_mma.cuh"
 #include "moe_common.cuh"
 #include "tcgen05.cuh"
@@ -43,6 +44,7 @@ constexpr uint32_t kTileBytes = kTileM * kChunkK * 2;        // 16 KiB: an A chu
 constexpr uint32_t kTmemCols = 512;
 constexpr int kProducerWarps = 8, kRowsPerWarp = kTileM / kProducerWarps;
 constexpr int kScaleRing = 4;                               // superblocks of per-row scales kept for the epilogue
+constexpr int kRawStages = 3;                               // raw weight superblocks in flight
 
 // <= kTileN token rows of one expert (expert < 0: the shared expert). Column blocks of the same expert
 // form groups of consecutive entries [first, first + count) covering <= kGroupRows rows: the tiles of a
@@ -51,9 +53,17 @@ constexpr int kScaleRing = 4;                               // superblocks of pe
 struct ColBlock { int row0, ncols, expert, first, count, pad; };
 constexpr int kGroupRows = 1024;
 
+// Tensor maps of one launch. A weight pack is described as u8 [rows / fuse][fuse * row_bytes] with
+// `fuse` consecutive rows joined into one tensor row, so that the row pitch is a multiple of 16
+// bytes whatever the block size (66-byte IQ2_XXS blocks give pitches that are only multiples of 2).
+struct GemmMaps {
+    CUtensorMap act;
+    CUtensorMap w_routed[2], w_shared[2];
+};
+
 struct GemmParams {
-    const uint8_t *w_routed[2], *w_shared[2];   // packs; 2 matrices (gate, up) or 1 (down)
-    uint64_t row_bytes;
+    uint32_t row_bytes;
+    int fuse;                                   // rows per tensor row of the weight maps: 1, 2, 4 or 8
     int M, K, nmat;
     const ColBlock *colblocks;
     const int *num_colblocks;
@@ -65,6 +75,7 @@ struct GemmParams {
 
 struct GemmSmem {
     uint64_t full[kStages], empty[kStages];
+    uint64_t raw_full[kRawStages], raw_empty[kRawStages];
     uint64_t acc_full[2], acc_empty[2], min_full[2], min_empty[2];
     uint32_t tmem_base;
     int abort;
@@ -79,9 +90,10 @@ __device__ __forceinline__ uint32_t stage_of(uint32_t it) { return ((it >> 1) & 
 __device__ __forceinline__ uint32_t phase_of(uint32_t it) { return (it >> 1) & 1u; }     // fills per stage: 2 per own superblock
 
 // ---- per-qtype decoders -----------------------------------------------------------------------------
-// A decoder sees one superblock of one weight row as kRawWords 32-bit words in shared memory,
-// copied from the 4-byte aligned address at or below the block (`mis` = bytes skipped, 0 or 2).
-//   load_word  one word of that run from global memory (the caller spreads words over lanes)
+// A decoder sees one superblock of one weight row as 32-bit words in shared memory, starting at the
+// 4-byte aligned address at or below the block (`mis` = bytes skipped, 0 or 2). kBoxBytes is the
+// width of the TMA box that fetches it: the block plus the most its start can lie above a 16-byte
+// boundary (block sizes are multiples of 2, 4 or 16 bytes), rounded up to 16.
 //   store      32 weights (k = 64*c + 32*h ..) -> four 16-byte fp16 chunks of the A tile row
 //   scales     {d, dmin} of the block, and whether they are acceptable
 //   mins       this thread's share of the A' row (affine qtypes)
@@ -103,16 +115,8 @@ __device__ __forceinline__ float2 checked_scales(uint32_t d_bits, uint32_t dmin_
 }
 
 struct GemmIq2 {
-    static constexpr int kBlockBytes = 66, kMinSlots = 0, kRawWords = 17;     // 66 bytes from a 2-byte aligned start
+    static constexpr int kBlockBytes = 66, kMinSlots = 0, kBoxBytes = 80;     // 66 bytes from a 2-byte aligned start
     static constexpr float kBias = 1152.0f;
-    __device__ static uint32_t load_word(const uint8_t *blk, int word) {
-        const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(blk) & 3u);
-        const uint8_t *p = blk - mis + 4 * word;
-        // an aligned block ends in the middle of word 16: the upper half lies past the block (and,
-        // for the last row of a pack, past the allocation), so only the lower half is read
-        if (word == 16 && mis == 0) return ldg_u16(p);
-        return __ldg(reinterpret_cast<const uint32_t *>(p));
-    }
     __device__ static void store(const uint32_t *raw, uint32_t mis, int c, int h, uint8_t *tile, uint32_t row,
                                  const MmaTables *tab) {
         const uint32_t o = mis + 2u + 8u * (2 * c + h), sh = 8u * (o & 3u);
@@ -136,9 +140,8 @@ struct GemmIq2 {
 };
 
 struct GemmQ4k {
-    static constexpr int kBlockBytes = 144, kMinSlots = 16, kRawWords = 36;    // 8 mins x (hi, lo)
+    static constexpr int kBlockBytes = 144, kMinSlots = 16, kBoxBytes = 144;   // 8 mins x (hi, lo); blocks are 16-byte aligned
     static constexpr float kBias = 1024.0f;
-    __device__ static uint32_t load_word(const uint8_t *blk, int word) { return __ldg(reinterpret_cast<const uint32_t *>(blk) + word); }
     // 6-bit (scale, min) of sub-block j from the 12 packed bytes held as three little-endian words
     __device__ static void scale_min_words(uint32_t s0, uint32_t s1, uint32_t s2, int j, uint32_t &sc, uint32_t &m) {
         const uint32_t w[3] = {s0, s1, s2};
@@ -178,9 +181,8 @@ struct GemmQ4k {
 };
 
 struct GemmQ2k {
-    static constexpr int kBlockBytes = 84, kMinSlots = 32, kRawWords = 21;     // 16 mins x (hi, lo)
+    static constexpr int kBlockBytes = 84, kMinSlots = 32, kBoxBytes = 96;     // 16 mins x (hi, lo); 4-byte aligned start
     static constexpr float kBias = 1024.0f;
-    __device__ static uint32_t load_word(const uint8_t *blk, int word) { return __ldg(reinterpret_cast<const uint32_t *>(blk) + word); }
     __device__ static void store(const uint32_t *raw, uint32_t, int c, int h, uint8_t *tile, uint32_t row, const MmaTables *tab) {
         const int hf = c >> 1, plane = 2 * (c & 1) + h;
         const uint32_t *q = raw + 4 + 8 * hf;
@@ -209,42 +211,49 @@ struct GemmQ2k {
 };
 
 // ---- shared-memory plan -----------------------------------------------------------------------------
-// tiles (1024-byte aligned): A ring, B ring, [min tiles: A' in 16-byte parts 0..3 of each row, B'
-// in parts 4..7], then the producers' raw staging (two superblocks per warp), the scale ring, the
-// decode tables and the barriers.
+// tiles (1024-byte aligned; the kernel refuses to run if the dynamic shared memory does not start on
+// such a boundary): A ring, B ring, [min tiles: A' in 16-byte parts 0..3 of each row, B' in parts
+// 4..7], then the raw superblock ring (kRawStages x 128 rows x kBoxBytes, plus a pad: the decoders'
+// funnel reads run one word over), the scale ring, the decode tables and the barriers.
 template <class Dec> struct GemmPlan {
     static constexpr bool kHasMin = Dec::kMinSlots > 0;
     static constexpr int kTileN = kHasMin ? 128 : 256;                              // columns per tile
     static constexpr int kEpilogueWarps = kTileN / 16;                              // (4 lane quarters) x (kTileN / 64)
     static constexpr int kThreads = 32 * (12 + kEpilogueWarps);
     static constexpr uint32_t kBTileBytes = (kTileN / kBoxN) * kTileBytes;
-    static constexpr uint32_t kRawBuf = kRowsPerWarp * Dec::kRawWords + 4;          // words; +4: funnel reads run one word over
-    static constexpr uint32_t kLoads = (kRowsPerWarp * Dec::kRawWords + 31) / 32;   // words per lane per superblock
+    static constexpr uint32_t kRawStageBytes = kTileM * Dec::kBoxBytes;
+    using Scale = typename std::conditional<kHasMin, float2, float>::type;          // {d, dmin} or d per row and superblock
     static constexpr size_t kTilesBytes = (size_t)kStages * (kTileBytes + kBTileBytes) + (kHasMin ? 2 : 0) * (size_t)kTileBytes;
-    static constexpr size_t kRawBytes = (size_t)kProducerWarps * 2 * kRawBuf * 4;
-    static constexpr size_t kScaleBytes = (size_t)kScaleRing * kTileM * sizeof(float2);
-    static constexpr size_t kBytes = 1024 + kTilesBytes + kRawBytes + kScaleBytes + sizeof(MmaTables) + sizeof(GemmSmem) + 64;
+    static constexpr size_t kRawBytes = (size_t)kRawStages * kRawStageBytes + 128;
+    static constexpr size_t kScaleBytes = (size_t)kScaleRing * kTileM * sizeof(Scale);
+    static constexpr size_t kBytes = kTilesBytes + kRawBytes + kScaleBytes + sizeof(MmaTables) + sizeof(GemmSmem);
+    static_assert(kBytes <= 227 * 1024, "shared memory plan exceeds the 227 KiB a CTA can have");
+    static_assert(kRawStageBytes % 128 == 0 && (kTileM / 8) * Dec::kBoxBytes % 128 == 0, "TMA destinations are 128-byte aligned");
 };
 
-constexpr int kCtlRegs = 32, kProdRegs = 56, kEpiRegs = 88;
+constexpr int kCtlRegs = 48, kProdRegs = 48, kEpiRegs = 88;
 template <int N> __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N> __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 template <class Dec>
 __global__ void __launch_bounds__(GemmPlan<Dec>::kThreads, 1)
-moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams p) {
+moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
     using namespace sm100;
     using Plan = GemmPlan<Dec>;
     constexpr bool kHasMin = Plan::kHasMin;
     constexpr int kTileN = Plan::kTileN;
     constexpr uint32_t kBTileBytes = Plan::kBTileBytes;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t *tiles = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    if (smem_u32(smem_raw) & 1023u) {                           // uniform: nothing has been set up yet
+        if (threadIdx.x == 0) raise(p.status, YVEX_B200_STATUS_TIMEOUT);
+        return;
+    }
+    uint8_t *tiles = smem_raw;
     uint8_t *a_tiles = tiles;                                   // [kStages][16 KiB]
     uint8_t *b_tiles = tiles + kStages * kTileBytes;            // [kStages][16 or 32 KiB]
     uint8_t *min_tiles = b_tiles + kStages * kBTileBytes;       // [2][16 KiB] when the qtype has mins
-    uint32_t *raw_stage = reinterpret_cast<uint32_t *>(tiles + Plan::kTilesBytes);
-    float2 *dscale = reinterpret_cast<float2 *>(reinterpret_cast<uint8_t *>(raw_stage) + Plan::kRawBytes);
+    uint8_t *raw_stage = tiles + Plan::kTilesBytes;             // [kRawStages][fuse][128 / fuse rows][kBoxBytes]
+    typename Plan::Scale *dscale = reinterpret_cast<typename Plan::Scale *>(raw_stage + Plan::kRawBytes);
     MmaTables *tab = reinterpret_cast<MmaTables *>(reinterpret_cast<uint8_t *>(dscale) + Plan::kScaleBytes);
     GemmSmem *sm = reinterpret_cast<GemmSmem *>(reinterpret_cast<uint8_t *>(tab) + sizeof(MmaTables));
 
@@ -253,6 +262,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
         // full[s]: 8 producer warps + the TMA thread's expect_tx arrival (and its bytes) complete a stage,
         // so an MMA issuer pays for one wait per 64-K chunk, not two.
         for (int s = 0; s < kStages; ++s) { mbar_init(&sm->full[s], kProducerWarps + 1); mbar_init(&sm->empty[s], 1); }
+        for (int s = 0; s < kRawStages; ++s) { mbar_init(&sm->raw_full[s], 1); mbar_init(&sm->raw_empty[s], kProducerWarps); }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&sm->acc_full[b], 1); mbar_init(&sm->acc_empty[b], Plan::kEpilogueWarps);
             mbar_init(&sm->min_full[b], kProducerWarps + 1); mbar_init(&sm->min_empty[b], 1);
@@ -282,12 +292,12 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
         mat = r / mtiles;
         mt = r % mtiles;
     };
-    auto weights_of = [&](const ColBlock &cb, int mat, int mt) {
-        // selects, not p.w_routed[mat]: a dynamically indexed parameter array makes the compiler copy the
-        // whole parameter block to local memory, and every later p.field read becomes a local load
-        const uint8_t *shared = mat ? p.w_shared[1] : p.w_shared[0], *routed = mat ? p.w_routed[1] : p.w_routed[0];
-        const uint8_t *base = cb.expert < 0 ? shared : routed + (uint64_t)cb.expert * p.M * p.row_bytes;
-        return base + (uint64_t)mt * kTileM * p.row_bytes;
+    // Weight map and first tensor row of a tile. (Selects, not maps.w_routed[mat]: a dynamically
+    // indexed parameter array makes the compiler copy the parameter block to local memory.)
+    auto weights_of = [&](const ColBlock &cb, int mat, int mt, int &y) {
+        const CUtensorMap *shared = mat ? &maps.w_shared[1] : &maps.w_shared[0], *routed = mat ? &maps.w_routed[1] : &maps.w_routed[0];
+        y = ((cb.expert < 0 ? 0 : cb.expert * p.M) + mt * kTileM) / p.fuse;
+        return cb.expert < 0 ? shared : routed;
     };
 
     // Register budget per role (256-column tiles only: 28 warps leave 72 registers per thread, and the
@@ -304,18 +314,45 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
     if (warp == 0) {
         // ---------------- TMA producer: activation tiles ----------------
         if (lane == 0) {
-            prefetch_tensormap(&act_map);
+            prefetch_tensormap(&maps.act);
+            // Raw weight superblocks run kRawStages - 1 ahead of the producers: one box per fused row
+            // r, [128 / fuse tensor rows] x [kBoxBytes from the 16-byte boundary at or below the block].
+            struct { long long t; int sb, y; uint32_t n; const CUtensorMap *map; } raw{(long long)blockIdx.x, 0, 0, 0u, nullptr};
+            auto issue_raw = [&]() -> bool {
+                if (raw.t >= tiles_total) return true;
+                if (raw.sb == 0) {
+                    ColBlock cb; int mat, mt;
+                    tile_of(raw.t, cb, mat, mt);
+                    raw.map = weights_of(cb, mat, mt, raw.y);
+                }
+                const uint32_t s = raw.n % kRawStages, ph = (raw.n / kRawStages) & 1u;
+                if (!mbar_wait(&sm->raw_empty[s], ph ^ 1u, abort)) return false;
+                mbar_expect_tx(&sm->raw_full[s], Plan::kRawStageBytes);
+                const int rows = kTileM / p.fuse;
+                for (int r = 0; r < p.fuse; ++r) {
+                    const int x = (int)(r * p.row_bytes + raw.sb * Dec::kBlockBytes) & ~15;
+                    tma_load_2d(raw_stage + s * Plan::kRawStageBytes + r * rows * Dec::kBoxBytes, raw.map, x, raw.y, &sm->raw_full[s]);
+                }
+                ++raw.n;
+                if (++raw.sb == nsb) { raw.sb = 0; raw.t += gridDim.x; }
+                return true;
+            };
+            bool ok = true;
+            for (int i = 0; i < kRawStages - 1 && ok; ++i) ok = issue_raw();
             uint32_t it = 0;
-            for (long long t = blockIdx.x; t < tiles_total && !*abort; t += gridDim.x) {
+            for (long long t = blockIdx.x; t < tiles_total && !*abort && ok; t += gridDim.x) {
                 ColBlock cb; int mat, mt;
                 tile_of(t, cb, mat, mt);
                 const bool two = cb.ncols > kBoxN;             // a second 128-row box (only when kTileN = 256)
                 for (int kc = 0; kc < p.K / kChunkK; ++kc, ++it) {
                     const uint32_t s = stage_of(it), ph = phase_of(it);
-                    if (!mbar_wait(&sm->empty[s], ph ^ 1u, abort)) break;
+                    if (!mbar_wait(&sm->empty[s], ph ^ 1u, abort)) { ok = false; break; }
                     mbar_expect_tx(&sm->full[s], two ? 2 * kTileBytes : kTileBytes);
-                    tma_load_2d(b_tiles + s * kBTileBytes, &act_map, kc * kChunkK, cb.row0, &sm->full[s]);
-                    if (two) tma_load_2d(b_tiles + s * kBTileBytes + kTileBytes, &act_map, kc * kChunkK, cb.row0 + kBoxN, &sm->full[s]);
+                    tma_load_2d(b_tiles + s * kBTileBytes, &maps.act, kc * kChunkK, cb.row0, &sm->full[s]);
+                    if (two) tma_load_2d(b_tiles + s * kBTileBytes + kTileBytes, &maps.act, kc * kChunkK, cb.row0 + kBoxN, &sm->full[s]);
+                    // after the second chunk of a superblock: by then the producers have finished the
+                    // superblock before it, whose stage the next raw load reuses, so this wait is short
+                    if ((kc & 3) == 1 && !issue_raw()) { ok = false; break; }
                 }
             }
         }
@@ -375,15 +412,20 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
                 tile_of(t, cb, mat, mt);
                 for (int sb = 0; sb < nsb; ++sb, ++sb_it) {
                     const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
+                    // this token row's sums for the superblock (zero rows past the block's tail); all the
+                    // loads are in flight together, and before the wait for the tile
+                    uint4 v[kTileM / kRowsPerPass];
+#pragma unroll
+                    for (int i = 0; i < kTileM / kRowsPerPass; ++i) {
+                        const int r = rsub + i * kRowsPerPass;
+                        const uint4 *src = reinterpret_cast<const uint4 *>(p.sums + ((uint64_t)(cb.row0 + r) * nsb + sb) * 32);
+                        v[i] = r < cb.ncols ? __ldg(src + part) : make_uint4(0, 0, 0, 0);
+                    }
                     if (!mbar_wait(&sm->min_empty[buf], bph ^ 1u, abort)) break;
                     uint8_t *tile = min_tiles + buf * kTileBytes;
-                    // this token row's sums for the superblock (zero rows past the block's tail)
-#pragma unroll 4
-                    for (int r = rsub; r < kTileM; r += kRowsPerPass) {
-                        const uint4 *src = reinterpret_cast<const uint4 *>(p.sums + ((uint64_t)(cb.row0 + r) * nsb + sb) * 32);
-                        const uint4 v = r < cb.ncols ? __ldg(src + part) : make_uint4(0, 0, 0, 0);
-                        *reinterpret_cast<uint4 *>(tile + sw128_offset(r, 4 + part)) = v;
-                    }
+#pragma unroll
+                    for (int i = 0; i < kTileM / kRowsPerPass; ++i)
+                        *reinterpret_cast<uint4 *>(tile + sw128_offset(rsub + i * kRowsPerPass, 4 + part)) = v[i];
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm->min_full[buf]);
@@ -394,76 +436,45 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
         // ---------------- dequant producers ----------------
         const int pw = warp - 4, rl = lane & 15, h = lane >> 4;
         const uint32_t row = (uint32_t)(kRowsPerWarp * pw + rl);
-        uint32_t *bufs = raw_stage + (size_t)pw * 2 * Plan::kRawBuf;
-        struct Cursor { long long t; int sb; const uint8_t *wrows; };        // wrows: first of this warp's 16 rows
-        auto open_tile = [&](Cursor &cur) {
-            if (cur.t < tiles_total) {
-                ColBlock cb; int mat, mt;
-                tile_of(cur.t, cb, mat, mt);
-                cur.wrows = weights_of(cb, mat, mt) + (uint64_t)(kRowsPerWarp * pw) * p.row_bytes;
-            }
-        };
-        auto advance = [&](Cursor &cur) {
-            if (++cur.sb == nsb) { cur.sb = 0; cur.t += gridDim.x; open_tile(cur); }
-        };
-        uint32_t regs[Plan::kLoads];
-        // lanes run along the rows: item = (row of the warp's 16, word of the row's run)
-        auto load_raw = [&](const Cursor &cur) {
-#pragma unroll
-            for (int i = 0; i < (int)Plan::kLoads; ++i) {
-                const int item = 32 * i + lane;
-                if (item < kRowsPerWarp * Dec::kRawWords) {
-                    const int r = item / Dec::kRawWords, word = item - r * Dec::kRawWords;
-                    regs[i] = Dec::load_word(cur.wrows + (uint64_t)r * p.row_bytes + (uint64_t)cur.sb * Dec::kBlockBytes, word);
+        // where the row's bytes land in a raw stage, and where its superblock 0 starts in the tensor row
+        const uint32_t sub = row % (uint32_t)p.fuse;
+        const uint32_t slot = (sub * (uint32_t)(kTileM / p.fuse) + row / (uint32_t)p.fuse) * Dec::kBoxBytes;
+        const uint32_t x_row = sub * p.row_bytes;
+        const long long my_tiles = tiles_total > blockIdx.x ? (tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        uint32_t sb_it = 0;
+        for (long long tile = 0; tile < my_tiles && !*abort; ++tile) {
+            for (int sb = 0; sb < nsb; ++sb, ++sb_it) {
+                const uint32_t rs = sb_it % kRawStages, rph = (sb_it / kRawStages) & 1u;
+                if (!mbar_wait(&sm->raw_full[rs], rph, abort)) goto done;
+                const uint32_t off = (x_row + (uint32_t)sb * Dec::kBlockBytes) & 15u, mis = off & 3u;
+                const uint32_t *raw = reinterpret_cast<const uint32_t *>(raw_stage + rs * Plan::kRawStageBytes + slot + (off & ~3u));
+                if (h == 0) {
+                    bool bad;
+                    const float2 dd = Dec::scales(raw, mis, bad);
+                    if constexpr (kHasMin) dscale[(sb_it % kScaleRing) * kTileM + row] = dd;
+                    else dscale[(sb_it % kScaleRing) * kTileM + row] = dd.x;
+                    if (bad) raise(p.status, YVEX_B200_STATUS_NUMERIC);
                 }
-            }
-        };
-        auto store_raw = [&](uint32_t *buf) {
 #pragma unroll
-            for (int i = 0; i < (int)Plan::kLoads; ++i) {
-                const int item = 32 * i + lane;
-                if (item < kRowsPerWarp * Dec::kRawWords) buf[item] = regs[i];
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t it = 4u * sb_it + c, s = stage_of(it), ph = phase_of(it);
+                    if (!mbar_wait(&sm->empty[s], ph ^ 1u, abort)) goto done;
+                    Dec::store(raw, mis, c, h, a_tiles + s * kTileBytes, row, tab);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sm->full[s]);
+                }
+                if (kHasMin) {
+                    const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
+                    if (!mbar_wait(&sm->min_empty[buf], bph ^ 1u, abort)) goto done;
+                    Dec::mins(raw, h, min_tiles + buf * kTileBytes, row);
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sm->min_full[buf]);
+                }
+                __syncwarp();                                   // every lane is done reading the stage
+                if (lane == 0) mbar_arrive(&sm->raw_empty[rs]);
             }
-        };
-        Cursor at{(long long)blockIdx.x, 0, nullptr};
-        open_tile(at);
-        if (at.t < tiles_total) { load_raw(at); store_raw(bufs); }
-        __syncwarp();
-        uint32_t cur = 0, sb_it = 0;
-        for (; at.t < tiles_total && !*abort; ++sb_it) {
-            Cursor ahead = at;
-            advance(ahead);
-            const bool more = ahead.t < tiles_total;
-            if (more) load_raw(ahead);                          // in flight while this superblock is decoded
-            const uint32_t *raw = bufs + cur * Plan::kRawBuf + rl * Dec::kRawWords;
-            const uint32_t mis = (uint32_t)(reinterpret_cast<uintptr_t>(at.wrows + (uint64_t)rl * p.row_bytes +
-                                                                         (uint64_t)at.sb * Dec::kBlockBytes) & 3u);
-            if (h == 0) {
-                bool bad;
-                dscale[(sb_it % kScaleRing) * kTileM + row] = Dec::scales(raw, mis, bad);
-                if (bad) raise(p.status, YVEX_B200_STATUS_NUMERIC);
-            }
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const uint32_t it = 4u * sb_it + c, s = stage_of(it), ph = phase_of(it);
-                if (!mbar_wait(&sm->empty[s], ph ^ 1u, abort)) goto done;
-                Dec::store(raw, mis, c, h, a_tiles + s * kTileBytes, row, tab);
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm->full[s]);
-            }
-            if (kHasMin) {
-                const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
-                if (!mbar_wait(&sm->min_empty[buf], bph ^ 1u, abort)) goto done;
-                Dec::mins(raw, h, min_tiles + buf * kTileBytes, row);
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm->min_full[buf]);
-            }
-            if (more) store_raw(bufs + (cur ^ 1u) * Plan::kRawBuf);
-            __syncwarp();
-            cur ^= 1u;
-            at = ahead;
         }
     } else {
         // ---------------- epilogue ----------------
@@ -483,8 +494,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap act_map, GemmParams 
                 if (!mbar_wait(&sm->acc_full[buf], bph, abort)) goto done;
                 tc_fence_after();
                 // written by the row's producer before its last chunk of this superblock was published
-                const float2 dd = dscale[(sb_it % kScaleRing) * kTileM + row];
-                const float d = dd.x, dmin = dd.y;
+                float d, dmin = 0.0f;
+                if constexpr (kHasMin) { const float2 dd = dscale[(sb_it % kScaleRing) * kTileM + row]; d = dd.x; dmin = dd.y; }
+                else d = dscale[(sb_it % kScaleRing) * kTileM + row];
                 if (ncols_here > 0) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {

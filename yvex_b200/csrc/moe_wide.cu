@@ -267,8 +267,28 @@ static int make_act_map(CUtensorMap *map, const __half *base, uint64_t rows, uin
     return r == CUDA_SUCCESS ? OK : ERR_BACKEND;
 }
 
+// A weight pack of `rows` rows as u8 [rows / fuse][fuse * row_bytes], boxes of [128 / fuse][box_bytes].
+static int make_weight_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes, int fuse, uint32_t box_bytes) {
+    auto fn = encode_fn();
+    if (!fn) return ERR_BACKEND;
+    if (reinterpret_cast<uintptr_t>(base) & 15u) return ERR_INVALID_ARG;        // weight packs must start on a 16-byte boundary
+    cuuint64_t dims[2] = {fuse * row_bytes, rows / fuse}, strides[1] = {fuse * row_bytes};
+    cuuint32_t box[2] = {box_bytes, (cuuint32_t)(kTileM / fuse)}, estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? OK : ERR_BACKEND;
+}
+
+// Rows fused into one tensor row so that its pitch is a multiple of 16 bytes (block sizes are even).
+static int fuse_of(uint64_t row_bytes) {
+    int fuse = 1;
+    while ((fuse * row_bytes) % 16) fuse *= 2;
+    return fuse;
+}
+
 template <class Dec>
-static int launch_gemm(const CUtensorMap &map, const GemmParams &p, cudaStream_t s) {
+static int launch_gemm(const GemmMaps &map, const GemmParams &p, cudaStream_t s) {
     const size_t smem = GemmPlan<Dec>::kBytes;
     static bool configured = false;
     if (!configured) {
@@ -280,7 +300,25 @@ static int launch_gemm(const CUtensorMap &map, const GemmParams &p, cudaStream_t
     return launch_status(1);
 }
 
-static int run_gemm(unsigned qtype, const CUtensorMap &map, const GemmParams &p, cudaStream_t s) {
+static uint32_t gemm_box_bytes(unsigned qtype) {
+    return qtype == Q_IQ2_XXS ? GemmIq2::kBoxBytes : qtype == Q_Q4_K ? GemmQ4k::kBoxBytes : GemmQ2k::kBoxBytes;
+}
+
+// The weight maps of one GEMM: routed and shared packs of its one or two matrices.
+static int make_weight_maps(GemmMaps *maps, unsigned qtype, const void *const routed[2], const void *const shared[2], int nmat,
+                            uint64_t routed_rows, uint64_t shared_rows, const GemmParams &p) {
+    for (int m = 0; m < 2; ++m) {
+        const int src = m < nmat ? m : 0;              // unused slots repeat matrix 0 so every map is valid
+        int rc = make_weight_map(&maps->w_routed[m], routed[src], routed_rows, p.row_bytes, p.fuse, gemm_box_bytes(qtype));
+        if (rc != OK) return rc;
+        rc = make_weight_map(&maps->w_shared[m], shared[src] ? shared[src] : routed[src], shared[src] ? shared_rows : routed_rows,
+                             p.row_bytes, p.fuse, gemm_box_bytes(qtype));
+        if (rc != OK) return rc;
+    }
+    return OK;
+}
+
+static int run_gemm(unsigned qtype, const GemmMaps &map, const GemmParams &p, cudaStream_t s) {
     switch (qtype) {
     case Q_IQ2_XXS: return launch_gemm<GemmIq2>(map, p, s);
     case Q_Q4_K: return launch_gemm<GemmQ4k>(map, p, s);
@@ -320,17 +358,21 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     if (rc != OK) return rc;
     mark_phase(2, s);
 
-    CUtensorMap act_map, mid_map;
-    if (make_act_map(&act_map, pw.act_h, pairs, g.hidden) != OK || make_act_map(&mid_map, pw.mid_h, pairs, g.inter) != OK)
+    GemmMaps gu_maps, dn_maps;
+    if (make_act_map(&gu_maps.act, pw.act_h, pairs, g.hidden) != OK || make_act_map(&dn_maps.act, pw.mid_h, pairs, g.inter) != OK)
         return ERR_BACKEND;
     GemmParams gu{};
-    gu.w_routed[0] = (const uint8_t *)w.gate; gu.w_routed[1] = (const uint8_t *)w.up;
-    gu.w_shared[0] = (const uint8_t *)w.shared_gate; gu.w_shared[1] = (const uint8_t *)w.shared_up;
-    gu.row_bytes = g.hidden / gg.elems * gg.bytes;
+    gu.row_bytes = (uint32_t)(g.hidden / gg.elems * gg.bytes);
+    gu.fuse = fuse_of(gu.row_bytes);
     gu.M = (int)g.inter; gu.K = (int)g.hidden; gu.nmat = 2;
+    {
+        const void *routed[2] = {w.gate, w.up}, *shared[2] = {w.shared_gate, w.shared_up};
+        rc = make_weight_maps(&gu_maps, g.gate_qtype, routed, shared, 2, (uint64_t)g.experts * g.inter, g.inter, gu);
+        if (rc != OK) return rc;
+    }
     gu.colblocks = pw.blocks; gu.num_colblocks = pw.num_blocks;
     gu.out_f32[0] = pw.gate; gu.out_f32[1] = pw.up; gu.out_bf16 = nullptr; gu.sums = nullptr; gu.status = status;
-    rc = run_gemm(g.gate_qtype, act_map, gu, s);
+    rc = run_gemm(g.gate_qtype, gu_maps, gu, s);
     if (rc != OK) return rc;
     mark_phase(3, s);
 
@@ -338,12 +380,17 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     wide_swiglu_kernel<<<dim3((unsigned)(g.inter / 256), (unsigned)grid_for(pairs, 1, 16)), 64, 0, s>>>(
         pw.gate, pw.up, pw.perm, pw.weight_of_pair, pairs, g.inter, (float)g.limit, group, pw.mid_h, pw.sums, status);
     GemmParams dn{};
-    dn.w_routed[0] = (const uint8_t *)w.down; dn.w_shared[0] = (const uint8_t *)w.shared_down;
-    dn.row_bytes = g.inter / dg.elems * dg.bytes;
+    dn.row_bytes = (uint32_t)(g.inter / dg.elems * dg.bytes);
+    dn.fuse = fuse_of(dn.row_bytes);
     dn.M = (int)g.hidden; dn.K = (int)g.inter; dn.nmat = 1;
+    {
+        const void *routed[2] = {w.down, nullptr}, *shared[2] = {w.shared_down, nullptr};
+        rc = make_weight_maps(&dn_maps, g.down_qtype, routed, shared, 1, (uint64_t)g.experts * g.hidden, g.hidden, dn);
+        if (rc != OK) return rc;
+    }
     dn.colblocks = pw.blocks_down; dn.num_colblocks = pw.num_blocks + 1;
     dn.out_bf16 = pw.y; dn.sums = pw.sums; dn.status = status;
-    rc = run_gemm(g.down_qtype, mid_map, dn, s);
+    rc = run_gemm(g.down_qtype, dn_maps, dn, s);
     if (rc != OK) return rc;
     mark_phase(4, s);
     return launch_status(1);
