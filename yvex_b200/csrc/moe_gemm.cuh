@@ -15,18 +15,19 @@
 // being filled. Affine qtypes add one more K=16/32 MMA per superblock: A' = integer mins,
 // B' = per-sub-block activation sums (hi/lo fp16 split), drained as acc -= dmin * tmem'.
 //
-// CTA = 20 warps (N = 128) or 28 warps (N = 256), persistent over a device-built tile list:
+// CTA = 28 warps, persistent over a device-built tile list (P = 8 producer warps with N = 256, 16 with
+// N = 128, where the epilogue needs only 8 warps; the producers are what bounds the kernel):
 //   warp 0      TMA producer: activation tiles [N x 64] fp16, 128-byte swizzle, mbarrier tx; and the raw
 //               weight superblocks of the tile's 128 rows (u8 boxes, three superblocks in flight)
 //   warps 1-2   MMA issuers (one elected lane each, alternating superblocks / TMEM buffers):
 //               4 x tcgen05.mma (K=16) per 64-K chunk
 //   warp 3      B' tiles of the min term (copies the activation sums into the swizzled tile)
-//   warps 4-11  dequant producers. Each warp owns 16 weight rows of the tile; thread = (row, half of
-//               a 64-K chunk) decodes 32 weights of the staged superblock to fp16 and stores four
-//               16-byte chunks into the swizzled A tile. The same warps write the A' rows and the
+//   warps 4..   dequant producers. Each warp owns 16 (or 8) weight rows of the tile; thread = (row, half
+//               (or quarter) of a 64-K chunk) decodes 32 (16) weights of the staged superblock to fp16
+//               and stores 16-byte chunks into the swizzled A tile. The same warps write the A' rows and the
 //               per-row block scales for the epilogue. (Staging the raw bytes through these warps'
 //               registers cost them about as many instructions as the decode itself.)
-//   warps 12..  epilogue, one warp per (32 TMEM lanes, 64 columns): TMEM -> registers
+//   last warps  epilogue, one warp per (32 TMEM lanes, 64 columns): TMEM -> registers
 //               (tcgen05.ld), scale, accumulate, final store
 // Every mbarrier wait is bounded; on expiry the CTA sets status 3, unwinds and frees its TMEM.
 #pragma once
@@ -42,7 +43,6 @@ constexpr int kTileM = 128, kBoxN = 128, kMaxTileN = 256, kChunkK = 64;
 constexpr int kStages = 4;                                  // {A, B} 64-K chunk stages: two rings of two
 constexpr uint32_t kTileBytes = kTileM * kChunkK * 2;        // 16 KiB: an A chunk, or one 128-row box of a B chunk
 constexpr uint32_t kTmemCols = 512;
-constexpr int kProducerWarps = 8, kRowsPerWarp = kTileM / kProducerWarps;
 constexpr int kScaleRing = 4;                               // superblocks of per-row scales kept for the epilogue
 constexpr int kRawStages = 3;                               // raw weight superblocks in flight
 
@@ -94,7 +94,8 @@ __device__ __forceinline__ uint32_t phase_of(uint32_t it) { return (it >> 1) & 1
 // 4-byte aligned address at or below the block (`mis` = bytes skipped, 0 or 2). kBoxBytes is the
 // width of the TMA box that fetches it: the block plus the most its start can lie above a 16-byte
 // boundary (block sizes are multiples of 2, 4 or 16 bytes), rounded up to 16.
-//   store      32 weights (k = 64*c + 32*h ..) -> four 16-byte fp16 chunks of the A tile row
+//   kParts     threads per row: each decodes 64 / kParts weights of a 64-K chunk
+//   store      weights k = 64*c + (64/kParts)*part .. -> 16-byte fp16 chunks of the A tile row
 //   scales     {d, dmin} of the block, and whether they are acceptable
 //   mins       this thread's share of the A' row (affine qtypes)
 __device__ __forceinline__ void store_scaled8(uint8_t *tile, uint32_t row, uint32_t chunk, uint32_t bytes_lo,
@@ -116,6 +117,7 @@ __device__ __forceinline__ float2 checked_scales(uint32_t d_bits, uint32_t dmin_
 
 struct GemmIq2 {
     static constexpr int kBlockBytes = 66, kMinSlots = 0, kBoxBytes = 80;     // 66 bytes from a 2-byte aligned start
+    static constexpr int kParts = 2;
     static constexpr float kBias = 1152.0f;
     __device__ static void store(const uint32_t *raw, uint32_t mis, int c, int h, uint8_t *tile, uint32_t row,
                                  const MmaTables *tab) {
@@ -141,6 +143,7 @@ struct GemmIq2 {
 
 struct GemmQ4k {
     static constexpr int kBlockBytes = 144, kMinSlots = 16, kBoxBytes = 144;   // 8 mins x (hi, lo); blocks are 16-byte aligned
+    static constexpr int kParts = 4;
     static constexpr float kBias = 1024.0f;
     // 6-bit (scale, min) of sub-block j from the 12 packed bytes held as three little-endian words
     __device__ static void scale_min_words(uint32_t s0, uint32_t s1, uint32_t s2, int j, uint32_t &sc, uint32_t &m) {
@@ -149,18 +152,20 @@ struct GemmQ4k {
         if (j < 4) { sc = byte(j) & 63u; m = byte(j + 4) & 63u; }
         else { sc = (byte(j + 4) & 15u) | ((byte(j - 4) >> 6) << 4); m = (byte(j + 4) >> 4) | ((byte(j) >> 6) << 4); }
     }
-    __device__ static void store(const uint32_t *raw, uint32_t, int c, int h, uint8_t *tile, uint32_t row, const MmaTables *tab) {
+    // part = 2 * h + half: sub-block 2c + h (low or high nibbles of the chunk's 32 bytes), bytes 16*half .. +15
+    __device__ static void store(const uint32_t *raw, uint32_t, int c, int part, uint8_t *tile, uint32_t row, const MmaTables *tab) {
+        const int h = part >> 1;
         uint32_t sc, m;
         scale_min_words(raw[1], raw[2], raw[3], 2 * c + h, sc, m);
         const uint2 s = tab->scale[sc];
         const __half2 sc2 = *reinterpret_cast<const __half2 *>(&s.x), nb2 = *reinterpret_cast<const __half2 *>(&s.y);
-        const uint4 q0 = *reinterpret_cast<const uint4 *>(raw + 4 + 8 * c), q1 = *reinterpret_cast<const uint4 *>(raw + 8 + 8 * c);
-        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        const uint4 q = *reinterpret_cast<const uint4 *>(raw + 4 + 8 * c + 4 * (part & 1));
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 2; ++j) {
             const uint32_t a = h ? (w[2 * j] >> 4) & 0x0f0f0f0fu : w[2 * j] & 0x0f0f0f0fu;
             const uint32_t b = h ? (w[2 * j + 1] >> 4) & 0x0f0f0f0fu : w[2 * j + 1] & 0x0f0f0f0fu;
-            store_scaled8(tile, row, 4 * h + j, a, b, sc2, nb2);
+            store_scaled8(tile, row, 2 * part + j, a, b, sc2, nb2);
         }
     }
     __device__ static float2 scales(const uint32_t *raw, uint32_t, bool &bad) {
@@ -182,17 +187,18 @@ struct GemmQ4k {
 
 struct GemmQ2k {
     static constexpr int kBlockBytes = 84, kMinSlots = 32, kBoxBytes = 96;     // 16 mins x (hi, lo); 4-byte aligned start
+    static constexpr int kParts = 4;
     static constexpr float kBias = 1024.0f;
-    __device__ static void store(const uint32_t *raw, uint32_t, int c, int h, uint8_t *tile, uint32_t row, const MmaTables *tab) {
-        const int hf = c >> 1, plane = 2 * (c & 1) + h;
-        const uint32_t *q = raw + 4 + 8 * hf;
-        const uint32_t sbytes = raw[2 * hf + (plane >> 1)] >> (16 * (plane & 1));   // scale bytes 8*hf + 2*plane, +1
-        const uint2 s0 = tab->scale[sbytes & 15u], s1 = tab->scale[(sbytes >> 8) & 15u];
+    // part = 2 * h + half: 2-bit plane 2*(c&1) + h of the 32 bytes, bytes 16*half .. +15 (one 16-weight sub-block)
+    __device__ static void store(const uint32_t *raw, uint32_t, int c, int part, uint8_t *tile, uint32_t row, const MmaTables *tab) {
+        const int hf = c >> 1, plane = 2 * (c & 1) + (part >> 1), half = part & 1;
+        const uint32_t *q = raw + 4 + 8 * hf + 4 * half;
+        const uint32_t sbytes = raw[2 * hf + (plane >> 1)] >> (16 * (plane & 1) + 8 * half);   // scale byte 8*hf + 2*plane + half
+        const uint2 s = tab->scale[sbytes & 15u];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint2 s = j < 2 ? s0 : s1;                                            // bytes 0..15 / 16..31
+        for (int j = 0; j < 2; ++j) {
             const uint32_t a = (q[2 * j] >> (2 * plane)) & 0x03030303u, b = (q[2 * j + 1] >> (2 * plane)) & 0x03030303u;
-            store_scaled8(tile, row, 4 * h + j, a, b, *reinterpret_cast<const __half2 *>(&s.x), *reinterpret_cast<const __half2 *>(&s.y));
+            store_scaled8(tile, row, 2 * part + j, a, b, *reinterpret_cast<const __half2 *>(&s.x), *reinterpret_cast<const __half2 *>(&s.y));
         }
     }
     __device__ static float2 scales(const uint32_t *raw, uint32_t, bool &bad) {
@@ -219,7 +225,10 @@ template <class Dec> struct GemmPlan {
     static constexpr bool kHasMin = Dec::kMinSlots > 0;
     static constexpr int kTileN = kHasMin ? 128 : 256;                              // columns per tile
     static constexpr int kEpilogueWarps = kTileN / 16;                              // (4 lane quarters) x (kTileN / 64)
-    static constexpr int kThreads = 32 * (12 + kEpilogueWarps);
+    static constexpr int kProducerWarps = 4 * Dec::kParts, kRowsPerWarp = kTileM / kProducerWarps;
+    static constexpr int kThreads = 32 * (4 + kProducerWarps + kEpilogueWarps);
+    // registers per thread of each role (setmaxnreg); the B' warp of the affine qtypes holds a tile of sums
+    static constexpr int kCtlRegs = kHasMin ? 80 : 48, kProdRegs = kHasMin ? 56 : 48, kEpiRegs = 88;
     static constexpr uint32_t kBTileBytes = (kTileN / kBoxN) * kTileBytes;
     static constexpr uint32_t kRawStageBytes = kTileM * Dec::kBoxBytes;
     using Scale = typename std::conditional<kHasMin, float2, float>::type;          // {d, dmin} or d per row and superblock
@@ -231,9 +240,12 @@ template <class Dec> struct GemmPlan {
     static_assert(kRawStageBytes % 128 == 0 && (kTileM / 8) * Dec::kBoxBytes % 128 == 0, "TMA destinations are 128-byte aligned");
 };
 
-constexpr int kCtlRegs = 48, kProdRegs = 48, kEpiRegs = 88;
-template <int N> __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N> __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+// Sets this warpgroup's registers per thread to N, given the count the kernel was launched with. An
+// increase waits until other warpgroups of the CTA have handed enough registers back.
+template <int N, int kLaunched> __device__ __forceinline__ void set_registers() {
+    if constexpr (N > kLaunched) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+    else if constexpr (N < kLaunched) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
 
 template <class Dec>
 __global__ void __launch_bounds__(GemmPlan<Dec>::kThreads, 1)
@@ -243,6 +255,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
     constexpr bool kHasMin = Plan::kHasMin;
     constexpr int kTileN = Plan::kTileN;
     constexpr uint32_t kBTileBytes = Plan::kBTileBytes;
+    constexpr int kProducerWarps = Plan::kProducerWarps, kRowsPerWarp = Plan::kRowsPerWarp;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     if (smem_u32(smem_raw) & 1023u) {                           // uniform: nothing has been set up yet
         if (threadIdx.x == 0) raise(p.status, YVEX_B200_STATUS_TIMEOUT);
@@ -303,13 +316,14 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
     // Register budget per role (256-column tiles only: 28 warps leave 72 registers per thread, and the
     // epilogue's 64 partial sums per thread do not fit in that): the control warps hand registers back
     // and the epilogue warpgroups take them. Warps 0-3, 4-11 and 12+ are whole warpgroups.
-    if (kTileN == 256) {
-        static_assert(kTileN != 256 || 4 * kCtlRegs + kProducerWarps * kProdRegs + Plan::kEpilogueWarps * kEpiRegs <=
+    {
+        static_assert(4 * Plan::kCtlRegs + kProducerWarps * Plan::kProdRegs + Plan::kEpilogueWarps * Plan::kEpiRegs <=
                                            ((65536 / Plan::kThreads) & ~7) * (Plan::kThreads / 32),
                       "the role budgets must fit in the registers the CTA was launched with, or the increase never returns");
-        if (warp < 4) reg_dealloc<kCtlRegs>();
-        else if (warp < 4 + kProducerWarps) reg_dealloc<kProdRegs>();
-        else reg_alloc<kEpiRegs>();
+        constexpr int kLaunched = (65536 / Plan::kThreads) & ~7;
+        if (warp < 4) set_registers<Plan::kCtlRegs, kLaunched>();
+        else if (warp < 4 + kProducerWarps) set_registers<Plan::kProdRegs, kLaunched>();
+        else set_registers<Plan::kEpiRegs, kLaunched>();
     }
     if (warp == 0) {
         // ---------------- TMA producer: activation tiles ----------------
@@ -434,7 +448,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
         }
     } else if (warp < 4 + kProducerWarps) {
         // ---------------- dequant producers ----------------
-        const int pw = warp - 4, rl = lane & 15, h = lane >> 4;
+        const int pw = warp - 4, rl = lane % kRowsPerWarp, h = lane / kRowsPerWarp;     // h: this thread's part of a chunk
         const uint32_t row = (uint32_t)(kRowsPerWarp * pw + rl);
         // where the row's bytes land in a raw stage, and where its superblock 0 starts in the tensor row
         const uint32_t sub = row % (uint32_t)p.fuse;
@@ -467,7 +481,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
                 if (kHasMin) {
                     const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
                     if (!mbar_wait(&sm->min_empty[buf], bph ^ 1u, abort)) goto done;
-                    Dec::mins(raw, h, min_tiles + buf * kTileBytes, row);
+                    if (h < 2) Dec::mins(raw, h, min_tiles + buf * kTileBytes, row);
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm->min_full[buf]);
@@ -478,7 +492,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
         }
     } else {
         // ---------------- epilogue ----------------
-        const int ew = warp - 12, quarter = warp & 3, colhalf = ew >> 2;     // TMEM lanes 32*quarter.., columns 64*colhalf.. (colhalf < kTileN / 64)
+        const int ew = warp - (4 + kProducerWarps), quarter = warp & 3, colhalf = ew >> 2;     // TMEM lanes 32*quarter.., columns 64*colhalf.. (colhalf < kTileN / 64)
         const int row = 32 * quarter + lane;
         const uint32_t lane_addr = (uint32_t)(32 * quarter) << 16;
         uint32_t sb_it = 0;

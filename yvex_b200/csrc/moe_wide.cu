@@ -50,14 +50,18 @@ __global__ void wide_count_kernel(const int *expert_of_pair, uint64_t pairs, int
     }
 }
 
-// One thread: exclusive scan of the group sizes and the column-block list in expert order
-// (bin `experts` is the shared expert, published as expert -1).
-__global__ void wide_plan_kernel(const int *counts, int experts, uint64_t pairs, int *offsets, ColBlock *blocks,
-                                 int *num_blocks, int max_blocks, int tile_n, int *status) {
-    if (threadIdx.x || blockIdx.x) return;
+// One thread per list: exclusive scan of the group sizes and the column-block list in expert order
+// (bin `experts` is the shared expert, published as expert -1). Block 0 builds the list of the
+// gate/up GEMM (and the offsets), block 1 the list of the down GEMM, whose tiles may be narrower.
+__global__ void wide_plan_kernel(const int *counts, int experts, uint64_t pairs, int *offsets, ColBlock *blocks_gu,
+                                 ColBlock *blocks_down, int *num_blocks, int max_blocks, int tile_gu, int tile_down, int *status) {
+    if (threadIdx.x) return;
+    ColBlock *blocks = blockIdx.x ? blocks_down : blocks_gu;
+    const int tile_n = blockIdx.x ? tile_down : tile_gu;
+    num_blocks += blockIdx.x;
     int off = 0, nb = 0;
     for (int e = 0; e <= experts; ++e) {
-        offsets[e] = off;
+        if (blockIdx.x == 0) offsets[e] = off;
         const int nblocks = (counts[e] + tile_n - 1) / tile_n;
         const int per_group = kGroupRows / tile_n;                          // groups of <= kGroupRows token rows
         for (int b = 0; b < nblocks; ++b) {
@@ -69,7 +73,7 @@ __global__ void wide_plan_kernel(const int *counts, int experts, uint64_t pairs,
         }
         off += counts[e];
     }
-    offsets[experts + 1] = off;
+    if (blockIdx.x == 0) offsets[experts + 1] = off;
     if ((uint64_t)off != pairs) raise(status, YVEX_B200_STATUS_ARGUMENT);
     if (nb > max_blocks) { raise(status, YVEX_B200_STATUS_ARGUMENT); nb = max_blocks; }
     *num_blocks = nb;
@@ -105,12 +109,11 @@ __global__ void wide_scatter_kernel(const int *expert_of_pair, uint64_t pairs, c
 // act_h[pos] = fp16 source row of the pair sorted to position pos.
 __global__ void wide_gather_kernel(const __half *rows_h, const int *perm, const int *src_of_pair, uint64_t pairs,
                                    uint64_t hidden, __half *act_h) {
-    const uint64_t chunks = hidden / 8;           // 16-byte chunks per row
-    const uint64_t total = pairs * chunks;
-    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t row = i / chunks, c = i % chunks;
-        const uint64_t src = (uint64_t)src_of_pair[perm[row]];
-        reinterpret_cast<uint4 *>(act_h)[row * chunks + c] = __ldg(reinterpret_cast<const uint4 *>(rows_h) + src * chunks + c);
+    const uint32_t chunks = (uint32_t)(hidden / 8);           // 16-byte chunks per row
+    for (uint64_t row = blockIdx.x; row < pairs; row += gridDim.x) {          // a CTA copies whole rows
+        const uint4 *src = reinterpret_cast<const uint4 *>(rows_h) + (uint64_t)src_of_pair[perm[row]] * chunks;
+        uint4 *dst = reinterpret_cast<uint4 *>(act_h) + row * chunks;
+        for (uint32_t c = threadIdx.x; c < chunks; c += blockDim.x) dst[c] = __ldg(src + c);
     }
 }
 
@@ -347,14 +350,11 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     const int bins = (int)g.experts + 1;
     cudaMemsetAsync(pw.counts, 0, (g.experts + 2) * 4, s);
     wide_count_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(pw.expert_of_pair, pairs, bins, pw.counts, status);
-    wide_plan_kernel<<<1, 32, 0, s>>>(pw.counts, (int)g.experts, pairs, pw.offsets, pw.blocks, pw.num_blocks, pw.max_blocks,
-                                      gemm_tile_n(g.gate_qtype), status);
-    wide_plan_kernel<<<1, 32, 0, s>>>(pw.counts, (int)g.experts, pairs, pw.offsets, pw.blocks_down, pw.num_blocks + 1, pw.max_blocks,
-                                      gemm_tile_n(g.down_qtype), status);
+    wide_plan_kernel<<<2, 32, 0, s>>>(pw.counts, (int)g.experts, pairs, pw.offsets, pw.blocks, pw.blocks_down, pw.num_blocks,
+                                      pw.max_blocks, gemm_tile_n(g.gate_qtype), gemm_tile_n(g.down_qtype), status);
     wide_scatter_kernel<<<(unsigned)bins, 512, 0, s>>>(pw.expert_of_pair, pairs, pw.offsets, pw.perm, pw.pos_of_pair);
-    wide_gather_kernel<<<grid_for(pairs * (g.hidden / 8), 256, 16), 256, 0, s>>>(rows_h, pw.perm, pw.src_of_pair, pairs, g.hidden,
-                                                                                 pw.act_h);
-    int rc = launch_status(5);
+    wide_gather_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(rows_h, pw.perm, pw.src_of_pair, pairs, g.hidden, pw.act_h);
+    int rc = launch_status(4);
     if (rc != OK) return rc;
     mark_phase(2, s);
 
