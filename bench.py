@@ -31,7 +31,9 @@ UNIT = "tokens/s"
 
 # DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum, one capture per workload).
-TRAFFIC = {"c1": 4389376, "c2": 22777600, "c3": 483481856, "c4": 2160352104, "c5": 10273500672}
+TRAFFIC = {"c1": 4389376, "c2": 22777600, "c4": 2160352104,
+           "c3_gate_up_gemm": 462726912, "c3_down_gemm": 365073920,
+           "c5_gate_up_gemm": 13417347840, "c5_down_gemm": 4945628416}
 
 
 def measured_peaks():
@@ -313,7 +315,7 @@ def run_native(args):
         ms_e2e = timed(step_e2e, args.steps)
         barrier()
         # per-phase timing for the roofline of the dominant kernel
-        n_ph = 6
+        n_ph = 7                         # 0..5 in order; 6 = after SwiGLU (between 3 and 4, wide path only)
         evs = [[torch.cuda.Event(enable_timing=True) for _ in range(n_ph)] for _ in range(args.steps)]
         for row in evs:
             for e in row:
@@ -329,10 +331,11 @@ def run_native(args):
             step(i)
             lib.lib.yvex_b200_phase_events(None, 0)
         torch.cuda.synchronize()
-        used = 4 if not wide else 6
+        order = [0, 1, 2, 3] if not wide else [0, 1, 2, 3, 6, 4, 5]
+        used = len(order)
         for i in range(args.steps):
             for p in range(used - 1):
-                phase_ms[p].append(evs[i][p].elapsed_time(evs[i][p + 1]))
+                phase_ms[p].append(evs[i][order[p]].elapsed_time(evs[i][order[p + 1]]))
     if status.read() != 0:
         raise RuntimeError(f"device status word = {status.read()} after the timed region")
 
@@ -344,17 +347,17 @@ def run_native(args):
     e2e = world * tokens * args.steps / (t_e2e / 1e3)
     phases = [sum(p) / len(p) for p in phase_ms[:used - 1]]
     names = (["route", "gate_up", "down_combine"] if not wide
-             else ["route", "permute_gather", "gate_up_gemm", "swiglu_down_gemm", "combine"])
+             else ["route", "permute_gather", "gate_up_gemm", "swiglu", "down_gemm", "combine"])
     roofline = None
     if wide:
         # dense contraction: count only real (token, expert) pairs, the shared expert included
         pairs = tokens * (wl.spec.topk + 1)
         flops = {"gate_up_gemm": pairs * 4.0 * wl.cfg["hidden"] * wl.cfg["inter"],
-                 "swiglu_down_gemm": pairs * 2.0 * wl.cfg["hidden"] * wl.cfg["inter"]}
+                 "down_gemm": pairs * 2.0 * wl.cfg["hidden"] * wl.cfg["inter"]}
         top = max(flops, key=lambda k: phases[names.index(k)])
         ach = flops[top] / (phases[names.index(top)] * 1e-3) / 1e12
         roofline = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": ach / peaks["bf16_tflops"], "traffic": TRAFFIC.get(wl.name) if top == "gate_up_gemm" else None,
+                    "frac": ach / peaks["bf16_tflops"], "traffic": TRAFFIC.get(f"{wl.name}_{top}"),
                     "algorithmic_bytes": None, "peak_source": peaks["source"],
                     "peak_sustained": peaks["bf16_tflops_sustained"],
                     "layer_achieved": pairs * 6.0 * wl.cfg["hidden"] * wl.cfg["inter"] / (t_dev / args.steps * 1e-3) / 1e12}
@@ -515,7 +518,7 @@ def run_native_ep(args):
         launches = lib.lib.yvex_b200_launch_count() - launches0
         ms_e2e = timed(step_e2e, args.steps, wall=world == 1)
         # GEMM phases of the routed pair list, timed with the library's phase events
-        n_ph, gemm_ms, pair_counts = 6, [[], []], []
+        n_ph, gemm_ms, pair_counts = 7, [[], [], []], []       # events 0..5 in order, 6 = after SwiGLU
         real_rows = ops.expert_rows
 
         def probed(rows_h, ids, wts):
@@ -530,7 +533,8 @@ def run_native_ep(args):
                 lib.lib.yvex_b200_phase_events(None, 0)
                 torch.cuda.synchronize()
                 gemm_ms[0].append(evs[2].elapsed_time(evs[3]))
-                gemm_ms[1].append(evs[3].elapsed_time(evs[4]))
+                gemm_ms[1].append(evs[6].elapsed_time(evs[4]))
+                gemm_ms[2].append(evs[3].elapsed_time(evs[6]))
                 pair_counts.append(rows_h.shape[0])
                 return y
             return real_rows(rows_h, ids, wts)
@@ -547,7 +551,8 @@ def run_native_ep(args):
                 lib.lib.yvex_b200_phase_events(None, 0)
                 torch.cuda.synchronize()
                 gemm_ms[0].append(evs[2].elapsed_time(evs[3]))
-                gemm_ms[1].append(evs[3].elapsed_time(evs[4]))
+                gemm_ms[1].append(evs[6].elapsed_time(evs[4]))
+                gemm_ms[2].append(evs[3].elapsed_time(evs[6]))
                 pair_counts.append(T * (spec.topk + 1))
         else:
             ops.expert_rows = probed
@@ -569,12 +574,13 @@ def run_native_ep(args):
     if rank == 0:
         gu = sum(gemm_ms[0]) / len(gemm_ms[0])
         dn = sum(gemm_ms[1]) / len(gemm_ms[1])
+        sw = sum(gemm_ms[2]) / len(gemm_ms[2])
         pairs = sum(pair_counts) / len(pair_counts)
-        top, t_top, fl = ("gate_up_gemm", gu, pairs * 4.0 * H * I) if gu >= dn else ("swiglu_down_gemm", dn, pairs * 2.0 * H * I)
+        top, t_top, fl = ("gate_up_gemm", gu, pairs * 4.0 * H * I) if gu >= dn else ("down_gemm", dn, pairs * 2.0 * H * I)
         ach = fl / (t_top * 1e-3) / 1e12
         peak = peaks["bf16_tflops_sustained"]
         roofline = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
-                    "traffic": TRAFFIC["c5"] if world == 1 and top == "gate_up_gemm" else None,
+                    "traffic": TRAFFIC.get(f"c5_{top}") if world == 1 else None,
                     "peak_source": peaks["source"] + " (sustained; burst %.1f)" % peaks["bf16_tflops"],
                     "pairs_per_launch": pairs,
                     "layer_achieved": T * (spec.topk + 1) * 6.0 * H * I / world / (t_dev / args.steps * 1e-3) / 1e12}
@@ -600,7 +606,7 @@ def run_native_ep(args):
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(T * (H + E) * 4),
                         "d2h_bytes_per_step": int(T * H * 4), "api": e2e_api},
                 "gpu_launches": int(launches * world),
-                "phases_ms": {"gate_up_gemm": gu, "swiglu_down_gemm": dn},
+                "phases_ms": {"gate_up_gemm": gu, "swiglu": sw, "down_gemm": dn},
                 "roofline": roofline, "cpu_baseline": cpu}
         print(json.dumps(line), flush=True)
     if world > 1:

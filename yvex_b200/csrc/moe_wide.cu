@@ -379,6 +379,7 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     const int group = g.down_qtype == Q_Q4_K ? 32 : g.down_qtype == Q_Q2_K ? 16 : 0;
     wide_swiglu_kernel<<<dim3((unsigned)(g.inter / 256), (unsigned)grid_for(pairs, 1, 16)), 64, 0, s>>>(
         pw.gate, pw.up, pw.perm, pw.weight_of_pair, pairs, g.inter, (float)g.limit, group, pw.mid_h, pw.sums, status);
+    mark_phase(6, s);                                   // SwiGLU done (an extra probe point, outside the 0..5 sequence)
     GemmParams dn{};
     dn.row_bytes = (uint32_t)(g.inter / dg.elems * dg.bytes);
     dn.fuse = fuse_of(dn.row_bytes);
