@@ -155,6 +155,12 @@ int yvex_b200_moe_expert_rows(const yvex_b200_moe_geometry *g, const yvex_b200_m
                               int *status, void *stream);
 int yvex_b200_moe_combine(const void *y_routed_bf16, const void *y_shared_bf16, uint64_t tokens,
                           uint64_t topk, uint64_t hidden, float *out, int *status, void *stream);
+/* The same sum with the rows named by index: routed row (t, r) is y_routed[routed_rows[t*topk + r]],
+ * the shared row of token t is y_shared[shared_rows[t]]; a NULL index means the identity order.
+ * Lets an expert-parallel home rank combine straight from its receive buffer. */
+int yvex_b200_moe_combine_indexed(const void *y_routed_bf16, const int32_t *routed_rows, const void *y_shared_bf16,
+                                  const int32_t *shared_rows, uint64_t tokens, uint64_t topk, uint64_t hidden,
+                                  float *out, int *status, void *stream);
 
 /*
  * mHC envelope of the MoE FFN: the layer's rows carry `streams` residual streams

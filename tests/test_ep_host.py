@@ -32,7 +32,9 @@ class FakeOps:
         factor = torch.where(glob < 0, torch.full_like(wts, 0.5), (glob + 1).float() * wts)
         return (rows_h.float() * factor[:, None]).to(torch.bfloat16)
 
-    def combine(self, y_routed, y_shared, topk):
+    def combine(self, y_routed, y_shared, topk, routed_rows=None):
+        if routed_rows is not None:                      # rows named by index, as the device combine reads them
+            y_routed = y_routed.index_select(0, routed_rows.to(torch.int64))
         acc = torch.zeros(y_shared.shape, dtype=torch.float32)
         yr = y_routed.float().reshape(-1, topk, y_shared.shape[1])
         for r in range(topk):

@@ -69,6 +69,7 @@ struct GemmParams {
     const int *num_colblocks;
     float *out_f32[2];                          // [rows][M] f32 (gate/up results) ...
     uint16_t *out_bf16;                         // ... or [rows][M] bf16 bits (down results)
+    const int *out_rows;                        // optional: result row of sorted row r is out_rows[r] (bf16 output only)
     const __half *sums;                         // [rows][K/256][32] hi/lo sub-block sums (affine qtypes)
     int *status;
 };
@@ -555,7 +556,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
                 if (hi) { r0 = s0; r1 = s1; } else { r2 = s0; r3 = s1; }
                 const int col = 4 * b + j4;
                 if (col < ncols_here) {
-                    const uint64_t at = ((uint64_t)cb.row0 + 64 * colhalf + col) * p.M + m0;
+                    const uint64_t srow = (uint64_t)cb.row0 + 64 * colhalf + col;
+                    const uint64_t at = (p.out_rows ? (uint64_t)__ldg(p.out_rows + srow) : srow) * p.M + m0;
                     // streaming stores: the results are not read again by this kernel and must not push the
                     // activation tiles and weight rows that other CTAs are about to reuse out of L2
                     if (p.out_bf16) {

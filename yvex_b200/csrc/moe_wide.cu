@@ -189,16 +189,6 @@ wide_combine_kernel(const uint16_t *y, const uint16_t *y_shared, const int *pos,
     }
 }
 
-// y_out[p] = y[pos_of_pair[p]] (16-byte chunks of bf16 rows)
-__global__ void wide_unsort_kernel(const uint16_t *y, const int *pos_of_pair, uint64_t pairs, uint64_t hidden, uint16_t *y_out) {
-    const uint64_t chunks = hidden / 8, total = pairs * chunks;
-    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t p = i / chunks, c = i % chunks;
-        reinterpret_cast<uint4 *>(y_out)[p * chunks + c] =
-            reinterpret_cast<const uint4 *>(y)[(uint64_t)pos_of_pair[p] * chunks + c];
-    }
-}
-
 // ---- workspace -------------------------------------------------------------------------------------
 struct PairWorkspace {
     int *counts, *offsets, *perm, *pos_of_pair, *num_blocks, *expert_of_pair, *src_of_pair;
@@ -343,9 +333,11 @@ bool moe_wide_gemm_eligible(const MoeGeom &g, const MoeWeights &w) {
 }
 
 // Runs the pair list already stored in pw.{expert,src,weight}_of_pair; leaves one bf16 row per
-// pair in pw.y at row pw.pos_of_pair[pair]. rows_h: the fp16 source rows the list indexes.
+// pair in pw.y at row pw.pos_of_pair[pair] or, when y_list is given, in y_list at row `pair` (the
+// down GEMM's epilogue then stores through the permutation, so no separate unsort pass is needed).
+// rows_h: the fp16 source rows the list indexes.
 static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorkspace &pw, const __half *rows_h, uint64_t pairs,
-                         int *status, cudaStream_t s) {
+                         int *status, cudaStream_t s, uint16_t *y_list = nullptr) {
     const Geometry gg = geometry_of(g.gate_qtype), dg = geometry_of(g.down_qtype);
     const int bins = (int)g.experts + 1;
     cudaMemsetAsync(pw.counts, 0, (g.experts + 2) * 4, s);
@@ -390,7 +382,7 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
         if (rc != OK) return rc;
     }
     dn.colblocks = pw.blocks_down; dn.num_colblocks = pw.num_blocks + 1;
-    dn.out_bf16 = pw.y; dn.sums = pw.sums; dn.status = status;
+    dn.out_bf16 = y_list ? y_list : pw.y; dn.out_rows = y_list ? pw.perm : nullptr; dn.sums = pw.sums; dn.status = status;
     rc = run_gemm(g.down_qtype, dn_maps, dn, s);
     if (rc != OK) return rc;
     mark_phase(4, s);
@@ -472,22 +464,26 @@ extern "C" int yvex_b200_moe_expert_rows(const yvex_b200_moe_geometry *geom, con
     wide_list_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(expert_ids, route_weights, pairs, (int)g.experts,
                                                            pw.expert_of_pair, pw.src_of_pair, pw.weight_of_pair);
     mark_phase(1, s);
-    rc = run_pair_list(g, *w, pw, static_cast<const __half *>(rows_f16), pairs, status, s);
+    rc = run_pair_list(g, *w, pw, static_cast<const __half *>(rows_f16), pairs, status, s, static_cast<uint16_t *>(y_bf16));
     if (rc != OK) return rc;
-    wide_unsort_kernel<<<grid_for(pairs * (g.hidden / 8), 256, 16), 256, 0, s>>>(pw.y, pw.pos_of_pair, pairs, g.hidden,
-                                                                                 static_cast<uint16_t *>(y_bf16));
     mark_phase(5, s);
-    return launch_status(2);
+    return launch_status(1);
 }
 
-extern "C" int yvex_b200_moe_combine(const void *y_routed_bf16, const void *y_shared_bf16, uint64_t tokens, uint64_t topk,
-                                     uint64_t hidden, float *out, int *status, void *stream) {
+extern "C" int yvex_b200_moe_combine_indexed(const void *y_routed_bf16, const int32_t *routed_rows, const void *y_shared_bf16,
+                                             const int32_t *shared_rows, uint64_t tokens, uint64_t topk, uint64_t hidden,
+                                             float *out, int *status, void *stream) {
     if (!y_routed_bf16 || !y_shared_bf16 || !out || !status || !tokens || !topk || !hidden) return ERR_INVALID_ARG;
     if (hidden % 8 || ((reinterpret_cast<uintptr_t>(y_routed_bf16) | reinterpret_cast<uintptr_t>(y_shared_bf16) |
                         reinterpret_cast<uintptr_t>(out)) & 15u))
         return ERR_INVALID_ARG;
     wide_combine_kernel<<<dim3((unsigned)((hidden / 8 + 127) / 128), (unsigned)grid_for(tokens, 1, 16)), 128, 0, as_stream(stream)>>>(
-        static_cast<const uint16_t *>(y_routed_bf16), static_cast<const uint16_t *>(y_shared_bf16), nullptr, nullptr, tokens, topk,
-        hidden, out);
+        static_cast<const uint16_t *>(y_routed_bf16), static_cast<const uint16_t *>(y_shared_bf16), routed_rows, shared_rows, tokens,
+        topk, hidden, out);
     return launch_status(1);
+}
+
+extern "C" int yvex_b200_moe_combine(const void *y_routed_bf16, const void *y_shared_bf16, uint64_t tokens, uint64_t topk,
+                                     uint64_t hidden, float *out, int *status, void *stream) {
+    return yvex_b200_moe_combine_indexed(y_routed_bf16, nullptr, y_shared_bf16, nullptr, tokens, topk, hidden, out, status, stream);
 }

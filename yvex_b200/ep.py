@@ -39,8 +39,8 @@ class DeviceOps:
     def expert_rows(self, rows_h, ids, wts):
         return self.lib.moe_expert_rows(self.geom_local, self.weights, rows_h, ids, wts, self.status)
 
-    def combine(self, y_routed, y_shared, topk):
-        return self.lib.moe_combine(y_routed, y_shared, topk, self.status)
+    def combine(self, y_routed, y_shared, topk, routed_rows=None):
+        return self.lib.moe_combine(y_routed, y_shared, topk, self.status, routed_rows=routed_rows)
 
 
 class ExpertParallelLayer:
@@ -52,8 +52,9 @@ class ExpertParallelLayer:
             raise ValueError("experts must divide evenly over the ranks")
         self.experts, self.topk, self.per_rank, self.ops = experts, topk, experts // self.world, ops
 
-    def _all_to_all(self, send, send_counts, recv_counts):
-        recv = send.new_empty((sum(recv_counts),) + tuple(send.shape[1:]))
+    def _all_to_all(self, send, send_counts, recv_counts, recv=None):
+        if recv is None:
+            recv = send.new_empty((sum(recv_counts),) + tuple(send.shape[1:]))
         if self.world == 1:
             recv.copy_(send)
         else:
@@ -79,19 +80,21 @@ class ExpertParallelLayer:
         send_rows = xh.index_select(0, torch.div(order, k, rounding_mode="floor"))
         meta = torch.stack(((sel % self.per_rank).reshape(-1).to(torch.int32),
                             wts.reshape(-1).contiguous().view(torch.int32)), dim=1).index_select(0, order).contiguous()
-        recv_rows = self._all_to_all(send_rows, send_counts, recv_counts)
-        recv_meta = self._all_to_all(meta, send_counts, recv_counts)
-
         # One pair list per rank: the received routed pairs, then this rank's own tokens for the (replicated)
         # shared expert as pairs of expert -1 with weight 1 - one set of grouped GEMM launches instead of two.
-        n_recv = recv_rows.shape[0]
+        # The routed rows are received straight into the head of the list's row buffer.
+        n_recv = sum(recv_counts)
+        rows_all = xh.new_empty((n_recv + t, xh.shape[1]))
+        self._all_to_all(send_rows, send_counts, recv_counts, recv=rows_all[:n_recv])
+        rows_all[n_recv:].copy_(xh)
+        recv_meta = self._all_to_all(meta, send_counts, recv_counts)
         ids = torch.cat((recv_meta[:, 0], torch.full((t,), -1, dtype=torch.int32, device=x.device)))
         pair_w = torch.cat((recv_meta[:, 1].contiguous().view(torch.float32), torch.ones(t, dtype=torch.float32, device=x.device)))
-        y_all = ops.expert_rows(torch.cat((recv_rows, xh)), ids, pair_w)
+        y_all = ops.expert_rows(rows_all, ids, pair_w)
         y_recv, y_shared = y_all[:n_recv], y_all[n_recv:]
 
         y_back = self._all_to_all(y_recv, recv_counts, send_counts)      # reverse direction, same splits
-        inverse = torch.empty_like(order)
-        inverse[order] = torch.arange(order.numel(), device=order.device)
-        y_pairs = y_back.index_select(0, inverse)                         # back to (token, rank) order
-        return ops.combine(y_pairs, y_shared, k), sel, wts
+        # pair (token, rank) sits at row inverse[...] of y_back: the combine reads through that index
+        inverse = torch.empty(order.numel(), dtype=torch.int32, device=order.device)
+        inverse[order] = torch.arange(order.numel(), dtype=torch.int32, device=order.device)
+        return ops.combine(y_back, y_shared, k, routed_rows=inverse), sel, wts

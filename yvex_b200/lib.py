@@ -53,6 +53,7 @@ def _load():
     lib.yvex_b200_moe_expert_rows.argtypes = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights), vp, vp, vp, u64, vp,
                                               vp, u64, vp, vp]
     lib.yvex_b200_moe_combine.argtypes = [vp, vp, u64, u64, u64, vp, vp, vp]
+    lib.yvex_b200_moe_combine_indexed.argtypes = [vp, vp, vp, vp, u64, u64, u64, vp, vp, vp]
     lib.yvex_b200_attention_workspace_bytes.restype = u64
     lib.yvex_b200_attention_workspace_bytes.argtypes = [u64] * 5
     lib.yvex_b200_dequant_rows.argtypes = [C.c_uint, vp, u64, u64, u64, vp, vp, vp]
@@ -82,6 +83,7 @@ EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_ge
            "yvex_b200_moe_route", "yvex_b200_moe_decode", "yvex_b200_moe_wide",
            "yvex_b200_moe_wide_workspace_bytes", "yvex_b200_launch_count", "yvex_b200_phase_events",
            "yvex_b200_moe_expert_rows_workspace_bytes", "yvex_b200_moe_expert_rows", "yvex_b200_moe_combine",
+           "yvex_b200_moe_combine_indexed",
            "yvex_b200_attention_workspace_bytes", "yvex_b200_attention_gqa_decode",
            "yvex_b200_attention_f32", "yvex_b200_attention_static_scratch_bytes",
            "yvex_b200_attention_gqa_decode_static", "yvex_b200_mhc_workspace_bytes", "yvex_b200_mhc_prepare",
@@ -210,14 +212,16 @@ def moe_expert_rows(geom, weights, rows_f16, expert_ids, route_weights, status, 
     return out
 
 
-def moe_combine(y_routed, y_shared, topk, status, out=None):
-    """y_routed [T*topk, hidden] bf16 in (token, rank) order, y_shared [T, hidden] bf16 -> f32 [T, hidden]."""
+def moe_combine(y_routed, y_shared, topk, status, out=None, routed_rows=None, shared_rows=None):
+    """y_routed [T*topk, hidden] bf16 in (token, rank) order, y_shared [T, hidden] bf16 -> f32 [T, hidden].
+    With routed_rows [T*topk] / shared_rows [T] (int32) the rows are taken from those positions instead."""
     torch = _torch()
-    tokens, hidden = y_shared.shape
+    hidden = y_shared.shape[1]
+    tokens = y_shared.shape[0] if shared_rows is None else shared_rows.shape[0]
     if out is None:
         out = torch.empty((tokens, hidden), dtype=torch.float32, device=y_shared.device)
-    _check(lib.yvex_b200_moe_combine(_p(y_routed), _p(y_shared), tokens, topk, hidden, _p(out), _p(status.word),
-                                     _stream()), "moe_combine")
+    _check(lib.yvex_b200_moe_combine_indexed(_p(y_routed), _p(routed_rows), _p(y_shared), _p(shared_rows), tokens, topk,
+                                             hidden, _p(out), _p(status.word), _stream()), "moe_combine")
     return out
 
 
