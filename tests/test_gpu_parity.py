@@ -102,7 +102,9 @@ def test_gemv_vs_frozen_reference(L, golden, port, name):
 @pytest.mark.parametrize("qtype,rows,width", [(synth.IQ2_XXS, 4096, 4096), (synth.IQ2_XXS, 1, 256),
                                               (synth.IQ2_XXS, 13, 7168), (synth.IQ2_XXS, 100, 1536),
                                               (synth.Q4_K, 257, 1536), (synth.Q4_K, 64, 2048),
-                                              (synth.Q8_0, 300, 4096), (synth.Q2_K, 129, 2048)])
+                                              (synth.Q8_0, 300, 4096), (synth.Q2_K, 129, 2048),
+                                              (synth.Q8_0, 4096, 4096), (synth.Q8_0, 37, 1280), (synth.Q8_0, 5, 256),
+                                              (synth.Q8_0, 3000, 7168)])
 def test_gemv_vs_oracle_shapes(L, port, qtype, rows, width):
     """Config-1 shape (4096x4096 IQ2_XXS, f32 N(0,1) activation) and ragged row counts / widths
     that exercise tile tails and rows that start on 8-byte boundaries only."""
@@ -117,17 +119,18 @@ def test_gemv_vs_oracle_shapes(L, port, qtype, rows, width):
     assert ok.all(), (np.abs(y - want).max(), int((~ok).sum()))
 
 
-def test_gemv_input_rows_additive_and_bf16(L, port):
+@pytest.mark.parametrize("qtype", [synth.IQ2_XXS, synth.Q8_0])
+def test_gemv_input_rows_additive_and_bf16(L, port, qtype):
     rows, width = 40, 1024
-    w = synth.random_blocks(synth.IQ2_XXS, rows, width, 77)
+    w = synth.random_blocks(qtype, rows, width, 77)
     rng = np.random.default_rng(78)
     x = rng.standard_normal((3, width)).astype(np.float32)
     add = rng.standard_normal((3, rows)).astype(np.float32)
     st = L.Status()
-    y = L.gemv(synth.IQ2_XXS, dev(w), rows, width, dev(x), st, additive=dev(add), round_bf16=True).cpu().numpy()
+    y = L.gemv(qtype, dev(w), rows, width, dev(x), st, additive=dev(add), round_bf16=True).cpu().numpy()
     assert st.read() == 0
     for i in range(3):
-        _, want = port.matvec(synth.IQ2_XXS, w, rows, width, x[i])
+        _, want = port.matvec(qtype, w, rows, width, x[i])
         want = synth.bf16_round(want + add[i])
         assert rel_l2(y[i], want) < 4e-3 and (np.abs(y[i] - want) <= 2 ** -7 * np.abs(want) + 1e-6).all()
         assert (synth.bf16_round(y[i]).view(np.uint32) == y[i].view(np.uint32)).all()

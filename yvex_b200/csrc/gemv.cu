@@ -1,8 +1,9 @@
 // Dequant kernels for encoded rows: the bit-exact row decoder and the dequant-fused matvec.
 //
-// Two matvec paths:
+// Three matvec paths:
 //   * gemv_rows_kernel  - any supported qtype, one warp per output row, f32 FMA. Used for the
-//     scalar qtypes (router weights are F32) and as the reference-shaped fallback.
+//     scalar qtypes (router weights are F32) and for shapes the other two do not take.
+//   * gemv_q8_0_kernel  - Q8_0 rows streamed through shared memory by bulk copies, f32 FMA.
 //   * gemv_mma_kernel   - the streaming path for block qtypes (gemv_mma.cuh): every warp stages
 //     its rows into shared memory with 16-byte cp.async copies, decodes them to exact
 //     small-integer fp16 fragments and multiplies them on the tensor cores against a 3-way fp16
@@ -10,6 +11,7 @@
 //     accumulator.
 #include "gemv_mma.cuh"
 #include "qtype_decode.cuh"
+#include "tcgen05.cuh"
 
 namespace yb {
 
@@ -55,6 +57,136 @@ __global__ void gemv_rows_kernel(unsigned q, const uint8_t *enc, uint64_t rows, 
     }
 }
 
+// ---- Q8_0 streaming matvec ------------------------------------------------------------------------
+// A Q8_0 row is a run of 34-byte blocks (f16 d, 32 int8), so neither the blocks nor the quants are
+// 4-byte aligned and a thread-per-block global load touches 17 cache lines per instruction. A CTA
+// therefore streams groups of eight consecutive rows (one per warp) through a two-stage ring in
+// shared memory, each stage filled by ONE bulk copy that completes on an mbarrier (many small
+// copies are bound by the copy engine's per-copy cost, not by bytes); lane b of a warp decodes
+// block 32*s + b of its row from shared memory (nine 4-byte reads, a 16-bit funnel shift for the
+// even blocks) and multiplies it with its 32 activations, which sit in shared memory as
+// [element / 4][block] float4 so that the lanes read consecutive 16-byte slots. int8 -> f32 goes
+// through the 2^23 trick (XOR 0x80, PRMT into the mantissa, subtract 2^23 + 128): exact, and on
+// the ALU and FMA pipes instead of the conversion unit. d multiplies the block's f32 sum once.
+constexpr int kQ8Warps = 8, kQ8Depth = 2;
+
+struct Q8Ctl { uint64_t full[kQ8Depth], empty[kQ8Depth]; int abort; int pad[3]; };
+
+__global__ void __launch_bounds__(32 * kQ8Warps)
+gemv_q8_0_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row_bytes, const float *input,
+                 const float *additive, float *out, int round_bf16, int *status) {
+    using namespace sm100;
+    extern __shared__ __align__(128) uint8_t q8_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t nblk = (uint32_t)(width / 32), nseg = (nblk + 31) / 32;
+    const uint32_t stage_bytes = (uint32_t)(kQ8Warps * row_bytes);
+    uint8_t *ring = q8_smem;                                                  // [kQ8Depth][8 rows][row_bytes]
+    Q8Ctl *ctl = reinterpret_cast<Q8Ctl *>(q8_smem + (size_t)kQ8Depth * stage_bytes);
+    float4 *xs = reinterpret_cast<float4 *>(ctl + 1);                        // [8][nblk]
+    const float *x = input + (uint64_t)blockIdx.y * width;
+    const uint64_t groups = (rows + kQ8Warps - 1) / kQ8Warps;
+    const uint64_t mine = groups > blockIdx.x ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    auto issue = [&](uint64_t n) {                                           // thread 0 only: group n of this CTA
+        const uint64_t row0 = (blockIdx.x + n * gridDim.x) * kQ8Warps;
+        const uint32_t bytes = (uint32_t)(min((uint64_t)kQ8Warps, rows - row0) * row_bytes);
+        mbar_expect_tx(&ctl->full[n % kQ8Depth], bytes);
+        bulk_load(ring + (n % kQ8Depth) * stage_bytes, enc + row0 * row_bytes, bytes, &ctl->full[n % kQ8Depth]);
+    };
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kQ8Depth; ++i) { mbar_init(&ctl->full[i], 1); mbar_init(&ctl->empty[i], kQ8Warps); }
+        ctl->abort = 0;
+        fence_barrier_init();
+        for (uint64_t n = 0; n < mine && n < (uint64_t)kQ8Depth; ++n) issue(n);
+    }
+    // the activation row goes to shared memory while the first stages are in flight
+    for (uint32_t i = threadIdx.x; i < (uint32_t)width; i += blockDim.x) {
+        const uint32_t b = i >> 5, e = i & 31u;
+        reinterpret_cast<float *>(xs + (e >> 2) * nblk + b)[e & 3u] = __ldg(x + i);
+    }
+    __syncthreads();
+    bool bad = false;
+    for (uint64_t n = 0; n < mine; ++n) {
+        const uint32_t slot = (uint32_t)(n % kQ8Depth), ph = (uint32_t)((n / kQ8Depth) & 1u);
+        if (!mbar_wait(&ctl->full[slot], ph, &ctl->abort)) break;
+        const uint64_t r = (blockIdx.x + n * gridDim.x) * kQ8Warps + warp;
+        if (r < rows) {
+            const uint32_t *row = reinterpret_cast<const uint32_t *>(ring + slot * stage_bytes + warp * row_bytes);
+            const bool odd = lane & 1;
+            float acc = 0.0f;
+            for (uint32_t sgm = 0; sgm < nseg; ++sgm) {
+                const uint32_t blk = 32u * sgm + lane;
+                if (blk < nblk) {
+                    // block `blk` starts at byte 34*blk: word 17m for block 2m, the upper half of word 17m + 8 for 2m + 1
+                    const uint32_t *wp = row + ((34u * blk) >> 2);
+                    uint32_t w[9];
+#pragma unroll
+                    for (int k = 0; k < 9; ++k) w[k] = wp[k];
+                    const float d = f16_bits_to_float((uint16_t)(odd ? w[0] >> 16 : w[0]));
+                    bad |= !isfinite(d);
+                    const float4 *xb = xs + blk;
+                    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;          // four chains instead of one of 32 FMAs
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const uint32_t q = __funnelshift_r(odd ? w[k + 1] : w[k], w[k + 1], odd ? 0u : 16u) ^ 0x80808080u;
+                        const float4 xv = xb[k * nblk];
+                        constexpr float kBias = 8388608.0f + 128.0f;
+                        s0 = fmaf(__uint_as_float(__byte_perm(q, 0x4B000000u, 0x7540)) - kBias, xv.x, s0);
+                        s1 = fmaf(__uint_as_float(__byte_perm(q, 0x4B000000u, 0x7541)) - kBias, xv.y, s1);
+                        s2 = fmaf(__uint_as_float(__byte_perm(q, 0x4B000000u, 0x7542)) - kBias, xv.z, s2);
+                        s3 = fmaf(__uint_as_float(__byte_perm(q, 0x4B000000u, 0x7543)) - kBias, xv.w, s3);
+                    }
+                    acc = fmaf(d, (s0 + s1) + (s2 + s3), acc);
+                }
+            }
+            float total = warp_sum(acc);
+            if (lane == 0) {
+                const uint64_t job = (uint64_t)blockIdx.y * rows + r;
+                if (additive) total += additive[job];
+                if (!isfinite(total)) bad = true;
+                out[job] = round_bf16 ? bf16_round(total) : total;
+            }
+        }
+        // the stage is refilled by the async proxy: order this warp's reads before that write
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->empty[slot]);
+        if (threadIdx.x == 0 && n + kQ8Depth < mine) {
+            if (!mbar_wait(&ctl->empty[slot], ph, &ctl->abort)) break;     // every warp is done with the stage
+            issue(n + kQ8Depth);
+        }
+    }
+    if (bad) raise(status, YVEX_B200_STATUS_NUMERIC);
+    if (lane == 0 && ctl->abort) raise(status, YVEX_B200_STATUS_TIMEOUT);
+}
+
+static size_t q8_smem_bytes(uint64_t width, uint64_t row_bytes) {
+    return (size_t)kQ8Depth * kQ8Warps * row_bytes + sizeof(Q8Ctl) + (size_t)width * 4;
+}
+
+// The streaming kernel wants 16-byte aligned rows (width a multiple of 256 gives that) and two
+// stages of eight rows plus the activation row in shared memory.
+static bool gemv_q8_0_eligible(unsigned q, uint64_t width, uint64_t row_bytes, const uint8_t *enc) {
+    return q == Q_Q8_0 && width % 256 == 0 && row_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(enc) & 15u) == 0 &&
+           q8_smem_bytes(width, row_bytes) <= 200 * 1024;
+}
+
+static int gemv_q8_0_launch(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row_bytes, const float *input,
+                            uint64_t input_rows, const float *additive, float *out, int round_bf16, int *status,
+                            cudaStream_t s) {
+    const size_t smem = q8_smem_bytes(width, row_bytes);
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+            return ERR_BACKEND;
+        configured = true;
+    }
+    const uint64_t groups = (rows + kQ8Warps - 1) / kQ8Warps, per_sm = (227 * 1024) / (smem + 1024);
+    const uint64_t cap = (uint64_t)kSmCount * (per_sm < 1 ? 1 : per_sm > 4 ? 4 : per_sm);
+    gemv_q8_0_kernel<<<dim3((unsigned)(groups < cap ? groups : cap), (unsigned)input_rows), 32 * kQ8Warps, smem, s>>>(
+        enc, rows, width, row_bytes, input, additive, out, round_bf16, status);
+    return launch_status();
+}
+
 }  // namespace yb
 
 using namespace yb;
@@ -86,6 +218,8 @@ extern "C" int yvex_b200_gemv(unsigned int qtype, const void *encoded, uint64_t 
         return gemv_mma_launch(qtype, enc, rows, width, row_bytes, input, input_rows, additive, out, round_bf16, status,
                                as_stream(stream));
     }
+    if (gemv_q8_0_eligible(qtype, width, row_bytes, enc) && input_rows <= 65535)
+        return gemv_q8_0_launch(enc, rows, width, row_bytes, input, input_rows, additive, out, round_bf16, status, as_stream(stream));
     uint64_t jobs = rows * input_rows;
     int grid = (int)((jobs + 7) / 8 < (uint64_t)kSmCount * 8 ? (jobs + 7) / 8
                                                               : (uint64_t)kSmCount * 8);

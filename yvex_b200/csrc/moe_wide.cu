@@ -50,29 +50,41 @@ __global__ void wide_count_kernel(const int *expert_of_pair, uint64_t pairs, int
     }
 }
 
-// One thread per list: exclusive scan of the group sizes and the column-block list in expert order
+// One warp per list: exclusive scan of the group sizes and the column-block list in expert order
 // (bin `experts` is the shared expert, published as expert -1). Block 0 builds the list of the
 // gate/up GEMM (and the offsets), block 1 the list of the down GEMM, whose tiles may be narrower.
+// Lanes take 32 consecutive bins at a time; shuffle scans give each bin its first row and block.
 __global__ void wide_plan_kernel(const int *counts, int experts, uint64_t pairs, int *offsets, ColBlock *blocks_gu,
                                  ColBlock *blocks_down, int *num_blocks, int max_blocks, int tile_gu, int tile_down, int *status) {
-    if (threadIdx.x) return;
     ColBlock *blocks = blockIdx.x ? blocks_down : blocks_gu;
-    const int tile_n = blockIdx.x ? tile_down : tile_gu;
+    const int tile_n = blockIdx.x ? tile_down : tile_gu, lane = threadIdx.x;
+    const int per_group = kGroupRows / tile_n;                              // groups of <= kGroupRows token rows
     num_blocks += blockIdx.x;
-    int off = 0, nb = 0;
-    for (int e = 0; e <= experts; ++e) {
-        if (blockIdx.x == 0) offsets[e] = off;
-        const int nblocks = (counts[e] + tile_n - 1) / tile_n;
-        const int per_group = kGroupRows / tile_n;                          // groups of <= kGroupRows token rows
-        for (int b = 0; b < nblocks; ++b) {
-            const int first = nb - b % per_group;
-            const int count = min(per_group, nblocks - (b - b % per_group));
-            if (nb < max_blocks)
-                blocks[nb] = ColBlock{off + b * tile_n, min(tile_n, counts[e] - b * tile_n), e < experts ? e : -1, first, count, 0};
-            ++nb;
+    int off = 0, nb = 0;                                                     // running totals, the same in every lane
+    for (int base = 0; base <= experts; base += 32) {
+        const int e = base + lane;
+        const int count = e <= experts ? counts[e] : 0;
+        const int nblocks = (count + tile_n - 1) / tile_n;
+        int row_end = count, blk_end = nblocks;                              // inclusive scans over the 32 bins
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int r = __shfl_up_sync(0xffffffffu, row_end, d), b = __shfl_up_sync(0xffffffffu, blk_end, d);
+            if (lane >= d) { row_end += r; blk_end += b; }
         }
-        off += counts[e];
+        const int row0 = off + row_end - count, blk0 = nb + blk_end - nblocks;
+        if (e <= experts) {
+            if (blockIdx.x == 0) offsets[e] = row0;
+            for (int b = 0; b < nblocks; ++b) {
+                const int first = blk0 + b - b % per_group;
+                const int in_group = min(per_group, nblocks - (b - b % per_group));
+                if (blk0 + b < max_blocks)
+                    blocks[blk0 + b] = ColBlock{row0 + b * tile_n, min(tile_n, count - b * tile_n), e < experts ? e : -1, first, in_group, 0};
+            }
+        }
+        off += __shfl_sync(0xffffffffu, row_end, 31);
+        nb += __shfl_sync(0xffffffffu, blk_end, 31);
     }
+    if (lane) return;
     if (blockIdx.x == 0) offsets[experts + 1] = off;
     if ((uint64_t)off != pairs) raise(status, YVEX_B200_STATUS_ARGUMENT);
     if (nb > max_blocks) { raise(status, YVEX_B200_STATUS_ARGUMENT); nb = max_blocks; }
