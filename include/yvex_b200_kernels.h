@@ -64,6 +64,10 @@ int yvex_b200_dequant_rows(unsigned int qtype, const void *encoded, uint64_t row
  * rounding of the result. Replaces yvex_qtype_matvec (src/backend/cuda/kernels.cu:529-626);
  * CPU meaning: a loop of yvex_quant_cpu_dot (src/gguf/quant_compute.c:116-181).
  * input is [input_rows x width] f32, out is [input_rows x rows] f32.
+ * Stream order: the block-qtype kernels are launched with programmatic stream serialization and
+ * prefetch encoded rows before the kernel launched before them on the stream has finished; input,
+ * additive and out are only touched after it has. So the encoded rows must not be the output of
+ * the immediately preceding kernel on the same stream (weights resident before the step are fine).
  */
 int yvex_b200_gemv(unsigned int qtype, const void *encoded, uint64_t rows, uint64_t width,
                    uint64_t row_bytes, const float *input, uint64_t input_rows,

@@ -92,6 +92,8 @@ gemv_q8_0_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row
         mbar_expect_tx(&ctl->full[n % kQ8Depth], bytes);
         bulk_load(ring + (n % kQ8Depth) * stage_bytes, enc + row0 * row_bytes, bytes, &ctl->full[n % kQ8Depth]);
     };
+    // programmatic dependent launch, as in gemv_mma_kernel: only the encoded rows are touched before the wait
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         for (int i = 0; i < kQ8Depth; ++i) { mbar_init(&ctl->full[i], 1); mbar_init(&ctl->empty[i], kQ8Warps); }
         ctl->abort = 0;
@@ -99,6 +101,7 @@ gemv_q8_0_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row
         for (uint64_t n = 0; n < mine && n < (uint64_t)kQ8Depth; ++n) issue(n);
     }
     // the activation row goes to shared memory while the first stages are in flight
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (uint32_t i = threadIdx.x; i < (uint32_t)width; i += blockDim.x) {
         const uint32_t b = i >> 5, e = i & 31u;
         reinterpret_cast<float *>(xs + (e >> 2) * nblk + b)[e & 3u] = __ldg(x + i);
@@ -182,8 +185,15 @@ static int gemv_q8_0_launch(const uint8_t *enc, uint64_t rows, uint64_t width, u
     }
     const uint64_t groups = (rows + kQ8Warps - 1) / kQ8Warps, per_sm = (227 * 1024) / (smem + 1024);
     const uint64_t cap = (uint64_t)kSmCount * (per_sm < 1 ? 1 : per_sm > 4 ? 4 : per_sm);
-    gemv_q8_0_kernel<<<dim3((unsigned)(groups < cap ? groups : cap), (unsigned)input_rows), 32 * kQ8Warps, smem, s>>>(
-        enc, rows, width, row_bytes, input, additive, out, round_bf16, status);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(groups < cap ? groups : cap), (unsigned)input_rows);
+    cfg.blockDim = dim3(32 * kQ8Warps); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, gemv_q8_0_kernel, enc, rows, width, row_bytes, input, additive, out, round_bf16, status) != cudaSuccess)
+        return ERR_BACKEND;
     return launch_status();
 }
 
