@@ -59,6 +59,25 @@ inline unsigned grid_for(uint64_t jobs, uint64_t per_block, uint64_t waves) {
     uint64_t need = (jobs + per_block - 1) / per_block, cap = (uint64_t)kSmCount * waves;
     return (unsigned)(need < 1 ? 1 : need < cap ? need : cap);
 }
+// Programmatic dependent launch (device side). A kernel launched with launch_pdl may begin before
+// the kernel before it on the stream has finished; pdl_wait() returns once that kernel has completed
+// and its writes are visible, pdl_trigger() lets the kernel after this one begin. Both are no-ops
+// for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launch with programmatic stream serialization allowed.
+template <class... Params, class... Args>
+inline cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 // Adds `launches` to the library's kernel-launch counter and reports a failed enqueue.
 int launch_status(int launches = 1);
 // Records the caller-registered phase event `phase` on `s` (no-op when none is registered).

@@ -53,6 +53,8 @@ ingress_router_kernel(const float *router, const float *x, uint64_t experts, uin
                       float *logits, float *scores, int *status) {
     const uint64_t e = blockIdx.x, r = blockIdx.y;
     const float *w = router + e * hidden, *xrow = x + r * hidden;
+    pdl_wait();                                         // x may be the output of the kernel before
+    pdl_trigger();
     bool bad = false;
     for (uint64_t k = e * kRouterThreads + threadIdx.x; k < hidden; k += experts * kRouterThreads) {
         float v = xrow[k];
@@ -105,6 +107,8 @@ __global__ void route_rows_kernel(MoeGeom g, const float *logits, const float *s
                                   uint64_t rows, int32_t *selected, float *weights, int *status) {
     const int lane = threadIdx.x & 31;
     const uint64_t row = blockIdx.x * (uint64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    pdl_wait();                                         // logits / scores come from the kernel before
+    pdl_trigger();
     if (row >= rows) return;
     float score[8], biased[8];
 #pragma unroll
@@ -309,10 +313,12 @@ int yb::moe_ingress_and_route(const MoeGeom &g, const MoeWeights &w, const MoeWo
     if (w.router && rows <= 64 && g.hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
         (reinterpret_cast<uintptr_t>(w.router) & 15u) == 0) {
         // decode width: two launches (projection with ingress rounding and scoring fused; top-k)
-        ingress_router_kernel<<<dim3((unsigned)g.experts, (unsigned)rows), kRouterThreads, 0, s>>>(
-            w.router, x, g.experts, g.hidden, ws.xr, ws.xr_h, ws.logits, ws.scores, status);
-        route_rows_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(g, ws.logits, ws.scores, w.bias, w.hash_table, token_ids,
-                                                                    rows, ws.selected, ws.weights, status);
+        // both with programmatic stream serialization: launch latency overlaps the kernel before
+        if (launch_pdl(ingress_router_kernel, dim3((unsigned)g.experts, (unsigned)rows), dim3(kRouterThreads), 0, s,
+                       w.router, x, g.experts, g.hidden, ws.xr, ws.xr_h, ws.logits, ws.scores, status) != cudaSuccess ||
+            launch_pdl(route_rows_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, s, g, ws.logits, ws.scores, w.bias,
+                       w.hash_table, token_ids, rows, ws.selected, ws.weights, status) != cudaSuccess)
+            return ERR_BACKEND;
         return launch_status(2);
     }
     ingress_round_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>(x, ws.xr, ws.xr_h, n, status);

@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(512, 2) moe_gate_up_mma_kernel(NarrowParams p)
     const uint32_t itiles = (imax + 7) / 8, ctasks = ppr * itiles;
     const uint64_t rb = p.gate_row_bytes;
 
+    // The routing kernel runs right before this one: nothing of this row can be read earlier.
+    pdl_wait();
     if (threadIdx.x < topk) {
         route->sel[threadIdx.x] = p.ws.selected[r * topk + threadIdx.x];
         route->weight[threadIdx.x] = p.ws.weights[r * topk + threadIdx.x];
@@ -143,6 +145,9 @@ __global__ void __launch_bounds__(512, 2) moe_gate_up_mma_kernel(NarrowParams p)
             }
         }
     }
+    // The down kernel may move in now: it reads the selection (complete before this kernel started) and
+    // prefetches its experts' rows, and touches the SwiGLU rows only after this kernel has completed.
+    pdl_trigger();
     cp_async_wait<0>();
 }
 
@@ -166,6 +171,8 @@ __global__ void __launch_bounds__(512, 2) moe_down_mma_kernel(NarrowParams p) {
     const uint32_t ctasks = (uint32_t)((g.hidden + 7) / 8);
     const uint64_t rb = p.down_row_bytes;
 
+    // Read before pdl_wait(): the selection was written two kernels back, and the gate/up kernel before
+    // this one lets its successor start only after it has itself waited for the routing kernel.
     if (threadIdx.x < topk) route->sel[threadIdx.x] = p.ws.selected[r * topk + threadIdx.x];
     __syncthreads();
 
@@ -206,6 +213,8 @@ __global__ void __launch_bounds__(512, 2) moe_down_mma_kernel(NarrowParams p) {
     for (int d = 0; d < kRingDepth - 1; ++d) issue_next();
     load_tables(tab, Dec::kBias);
     for (int i = threadIdx.x; i < kZeroHalves / 2; i += blockDim.x) reinterpret_cast<uint32_t *>(zeros)[i] = 0u;
+    pdl_wait();                                         // the SwiGLU rows are the gate/up kernel's output
+    pdl_trigger();
     // all pairs' SwiGLU rows are contiguous; with K a multiple of 256 no sum straddles two pairs
     prepare_row_half<Dec::kSumGroup>(mids, sums, p.ws.mid_h + (uint64_t)r * ppr * K, (int)(ppr * K));
     __syncthreads();
@@ -270,7 +279,7 @@ static int launch_gate_up(NarrowParams &p, cudaStream_t s) {
     const uint64_t imax = p.g.inter > p.g.shared_inter ? p.g.inter : p.g.shared_inter;
     const uint64_t tasks = (p.g.topk + 1) * ((imax + 7) / 8);
     dim3 grid((unsigned)ctas_per_row(p.rows, tasks, ctas_per_sm(smem, 32 * warps)), (unsigned)p.rows);
-    moe_gate_up_mma_kernel<Dec><<<grid, 32 * warps, smem, s>>>(p);
+    if (launch_pdl(moe_gate_up_mma_kernel<Dec>, grid, dim3(32 * warps), smem, s, p) != cudaSuccess) return ERR_BACKEND;
     return launch_status(1);
 }
 
@@ -295,7 +304,7 @@ static int launch_down(NarrowParams &p, cudaStream_t s) {
     p.down_warps = warps;
     const uint64_t tasks = (p.g.hidden + 7) / 8;
     dim3 grid((unsigned)ctas_per_row(p.rows, tasks, ctas_per_sm(smem, 32 * warps)), (unsigned)p.rows);
-    moe_down_mma_kernel<Dec><<<grid, 32 * warps, smem, s>>>(p);
+    if (launch_pdl(moe_down_mma_kernel<Dec>, grid, dim3(32 * warps), smem, s, p) != cudaSuccess) return ERR_BACKEND;
     return launch_status(1);
 }
 
