@@ -60,7 +60,8 @@ __global__ void gemv_rows_kernel(unsigned q, const uint8_t *enc, uint64_t rows, 
 // ---- Q8_0 streaming matvec ------------------------------------------------------------------------
 // A Q8_0 row is a run of 34-byte blocks (f16 d, 32 int8), so neither the blocks nor the quants are
 // 4-byte aligned and a thread-per-block global load touches 17 cache lines per instruction. A CTA
-// therefore streams groups of eight consecutive rows (one per warp) through a two-stage ring in
+// therefore streams groups of eight consecutive rows (two warps per row, alternating 32-block
+// segments; the pair meets on a named barrier and adds its two partial sums) through a two-stage ring in
 // shared memory, each stage filled by ONE bulk copy that completes on an mbarrier (many small
 // copies are bound by the copy engine's per-copy cost, not by bytes); lane b of a warp decodes
 // block 32*s + b of its row from shared memory (nine 4-byte reads, a 16-bit funnel shift for the
@@ -68,9 +69,9 @@ __global__ void gemv_rows_kernel(unsigned q, const uint8_t *enc, uint64_t rows, 
 // [element / 4][block] float4 so that the lanes read consecutive 16-byte slots. int8 -> f32 goes
 // through the 2^23 trick (XOR 0x80, PRMT into the mantissa, subtract 2^23 + 128): exact, and on
 // the ALU and FMA pipes instead of the conversion unit. d multiplies the block's f32 sum once.
-constexpr int kQ8Warps = 8, kQ8Depth = 2;
+constexpr int kQ8Rows = 8, kQ8Split = 2, kQ8Warps = kQ8Rows * kQ8Split, kQ8Depth = 2;
 
-struct Q8Ctl { uint64_t full[kQ8Depth], empty[kQ8Depth]; int abort; int pad[3]; };
+struct Q8Ctl { uint64_t full[kQ8Depth], empty[kQ8Depth]; int abort; int pad[3]; float part[2][kQ8Rows][kQ8Split]; };
 
 __global__ void __launch_bounds__(32 * kQ8Warps)
 gemv_q8_0_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row_bytes, const float *input,
@@ -79,16 +80,17 @@ gemv_q8_0_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row
     extern __shared__ __align__(128) uint8_t q8_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t nblk = (uint32_t)(width / 32), nseg = (nblk + 31) / 32;
-    const uint32_t stage_bytes = (uint32_t)(kQ8Warps * row_bytes);
+    const uint32_t stage_bytes = (uint32_t)(kQ8Rows * row_bytes);
+    const int rw = warp / kQ8Split, half = warp % kQ8Split;                  // row of the group, share of its segments
     uint8_t *ring = q8_smem;                                                  // [kQ8Depth][8 rows][row_bytes]
     Q8Ctl *ctl = reinterpret_cast<Q8Ctl *>(q8_smem + (size_t)kQ8Depth * stage_bytes);
     float4 *xs = reinterpret_cast<float4 *>(ctl + 1);                        // [8][nblk]
     const float *x = input + (uint64_t)blockIdx.y * width;
-    const uint64_t groups = (rows + kQ8Warps - 1) / kQ8Warps;
+    const uint64_t groups = (rows + kQ8Rows - 1) / kQ8Rows;
     const uint64_t mine = groups > blockIdx.x ? (groups - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
     auto issue = [&](uint64_t n) {                                           // thread 0 only: group n of this CTA
-        const uint64_t row0 = (blockIdx.x + n * gridDim.x) * kQ8Warps;
-        const uint32_t bytes = (uint32_t)(min((uint64_t)kQ8Warps, rows - row0) * row_bytes);
+        const uint64_t row0 = (blockIdx.x + n * gridDim.x) * kQ8Rows;
+        const uint32_t bytes = (uint32_t)(min((uint64_t)kQ8Rows, rows - row0) * row_bytes);
         mbar_expect_tx(&ctl->full[n % kQ8Depth], bytes);
         bulk_load(ring + (n % kQ8Depth) * stage_bytes, enc + row0 * row_bytes, bytes, &ctl->full[n % kQ8Depth]);
     };
@@ -111,12 +113,12 @@ gemv_q8_0_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row
     for (uint64_t n = 0; n < mine; ++n) {
         const uint32_t slot = (uint32_t)(n % kQ8Depth), ph = (uint32_t)((n / kQ8Depth) & 1u);
         if (!mbar_wait(&ctl->full[slot], ph, &ctl->abort)) break;
-        const uint64_t r = (blockIdx.x + n * gridDim.x) * kQ8Warps + warp;
-        if (r < rows) {
-            const uint32_t *row = reinterpret_cast<const uint32_t *>(ring + slot * stage_bytes + warp * row_bytes);
+        const uint64_t r = (blockIdx.x + n * gridDim.x) * kQ8Rows + rw;
+        if (r < rows) {                                                       // uniform over the row's warp pair
+            const uint32_t *row = reinterpret_cast<const uint32_t *>(ring + slot * stage_bytes + rw * row_bytes);
             const bool odd = lane & 1;
             float acc = 0.0f;
-            for (uint32_t sgm = 0; sgm < nseg; ++sgm) {
+            for (uint32_t sgm = half; sgm < nseg; sgm += kQ8Split) {
                 const uint32_t blk = 32u * sgm + lane;
                 if (blk < nblk) {
                     // block `blk` starts at byte 34*blk: word 17m for block 2m, the upper half of word 17m + 8 for 2m + 1
@@ -141,8 +143,13 @@ gemv_q8_0_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row
                     acc = fmaf(d, (s0 + s1) + (s2 + s3), acc);
                 }
             }
-            float total = warp_sum(acc);
-            if (lane == 0) {
+            acc = warp_sum(acc);
+            if (lane == 0) ctl->part[n & 1][rw][half] = acc;
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + rw), "r"(32 * kQ8Split) : "memory");     // the row's warps
+            if (lane == 0 && half == 0) {
+                float total = 0.0f;
+#pragma unroll
+                for (int h = 0; h < kQ8Split; ++h) total += ctl->part[n & 1][rw][h];     // fixed order
                 const uint64_t job = (uint64_t)blockIdx.y * rows + r;
                 if (additive) total += additive[job];
                 if (!isfinite(total)) bad = true;
@@ -184,7 +191,7 @@ static int gemv_q8_0_launch(const uint8_t *enc, uint64_t rows, uint64_t width, u
         configured = true;
     }
     const uint64_t groups = (rows + kQ8Warps - 1) / kQ8Warps, per_sm = (227 * 1024) / (smem + 1024);
-    const uint64_t cap = (uint64_t)kSmCount * (per_sm < 1 ? 1 : per_sm > 4 ? 4 : per_sm);
+    const uint64_t cap = (uint64_t)kSmCount * (per_sm < 1 ? 1 : per_sm > 2 ? 2 : per_sm);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)(groups < cap ? groups : cap), (unsigned)input_rows);
     cfg.blockDim = dim3(32 * kQ8Warps); cfg.dynamicSmemBytes = smem; cfg.stream = s;
