@@ -135,3 +135,35 @@ def test_wide_matches_narrow_path_at_prefill_size(L, port):
     assert rc == 0 and (sel[idx[:4]].cpu().numpy() == sel0).all()
     assert rel_l2(out[idx[:4]].cpu().numpy(), want) <= 1e-3
     assert pick.size == 4
+
+
+def test_wide_config5_size_properties(L, port):
+    """Config-5 geometry on one device (16 384 tokens, hidden 7168, 256 experts top-8 + shared, inter 2048,
+    IQ2_XXS + Q4_K). Size-independent properties: rows are independent, so a permuted batch gives the
+    permuted result bit for bit (other column blocks, other tiles, same per-row arithmetic) and a
+    sample of rows agrees with the decode path run on those rows alone; two rows are checked against
+    the CPU path within the layer tolerance."""
+    import torch
+    from yvex_b200.workloads import MoEWorkload
+    wl = MoEWorkload("c5", 5)
+    T = wl.cfg["tokens"]
+    x, logits = wl.tokens(T)
+    st = L.Status()
+    g, w = L.geometry_of(wl.spec), L.weights_of(wl.tensors)
+    ws = torch.empty(L.moe_workspace_bytes(g, T, True), dtype=torch.uint8, device="cuda")
+    out, sel, wt = L.moe_layer(g, w, x, st, logits=logits, wide=True, workspace=ws)
+    assert st.read() == 0 and torch.isfinite(out).all()
+    perm = torch.randperm(T, device="cuda", generator=torch.Generator(device="cuda").manual_seed(11))
+    out_p, sel_p, _ = L.moe_layer(g, w, x[perm].contiguous(), st, logits=logits[perm].contiguous(), wide=True, workspace=ws)
+    assert st.read() == 0 and (sel_p == sel[perm]).all()
+    assert torch.equal(out_p.view(torch.int32), out[perm].view(torch.int32))
+    idx = torch.tensor([0, 255, 256, 4095, 9000, 16383], device="cuda")
+    out_n, sel_n, _ = L.moe_layer(g, w, x[idx].contiguous(), st, logits=logits[idx].contiguous(), wide=False)
+    assert st.read() == 0 and (sel[idx] == sel_n).all()
+    assert rel_l2(out[idx].cpu().numpy(), out_n.cpu().numpy()) <= 5e-4
+    hw, _ = wl.host_copy()
+    Lp = port.layer(wl.spec, hw, allow_q4k=True)
+    two = idx[:2]
+    rc, want, sel0, _ = port.moe_tokens(Lp, x[two].cpu().numpy(), logits=logits[two].cpu().numpy(), threads=2)
+    assert rc == 0 and (sel[two].cpu().numpy() == sel0).all()
+    assert rel_l2(out[two].cpu().numpy(), want) <= 1e-3
