@@ -15,19 +15,18 @@
 // being filled. Affine qtypes add one more K=16/32 MMA per superblock: A' = integer mins,
 // B' = per-sub-block activation sums (hi/lo fp16 split), drained as acc -= dmin * tmem'.
 //
-// CTA = 28 warps, persistent over a device-built tile list (P = 8 producer warps with N = 256, 16 with
-// N = 128, where the epilogue needs only 8 warps; the producers are what bounds the kernel):
+// CTA = 28 warps, persistent over a device-built tile list:
 //   warp 0      TMA producer: activation tiles [N x 64] fp16, 128-byte swizzle, mbarrier tx; and the raw
 //               weight superblocks of the tile's 128 rows (u8 boxes, three superblocks in flight)
 //   warps 1-2   MMA issuers (one elected lane each, alternating superblocks / TMEM buffers):
 //               4 x tcgen05.mma (K=16) per 64-K chunk
 //   warp 3      B' tiles of the min term (copies the activation sums into the swizzled tile)
-//   warps 4..   dequant producers. Each warp owns 16 (or 8) weight rows of the tile; thread = (row, half
-//               (or quarter) of a 64-K chunk) decodes 32 (16) weights of the staged superblock to fp16
-//               and stores 16-byte chunks into the swizzled A tile. The same warps write the A' rows and the
+//   warps 4-11  dequant producers. Each warp owns 16 weight rows of the tile; thread = (row, half of a
+//               64-K chunk) decodes 32 weights of the staged superblock to fp16 and stores 16-byte
+//               chunks into the swizzled A tile. The same warps write the A' rows and the
 //               per-row block scales for the epilogue. (Staging the raw bytes through these warps'
 //               registers cost them about as many instructions as the decode itself.)
-//   last warps  epilogue, one warp per (32 TMEM lanes, 64 columns): TMEM -> registers
+//   warps 12-27 epilogue, one warp per (32 TMEM lanes, 64 or 32 columns): TMEM -> registers
 //               (tcgen05.ld), scale, accumulate, final store
 // Every mbarrier wait is bounded; on expiry the CTA sets status 3, unwinds and frees its TMEM.
 #pragma once
@@ -225,11 +224,16 @@ struct GemmQ2k {
 template <class Dec> struct GemmPlan {
     static constexpr bool kHasMin = Dec::kMinSlots > 0;
     static constexpr int kTileN = kHasMin ? 128 : 256;                              // columns per tile
-    static constexpr int kEpilogueWarps = kTileN / 16;                              // (4 lane quarters) x (kTileN / 64)
-    static constexpr int kProducerWarps = 4 * Dec::kParts, kRowsPerWarp = kTileM / kProducerWarps;
+    // 8 producer and 16 epilogue warps: an epilogue warp owns 32 TMEM lanes x kColsPerWarp columns
+    // (64 with 256-column tiles, 32 with 128-column ones, where the shorter tile-end store matters
+    // more than more producers: with K of 1536..2048 a tile ends every six to eight superblocks)
+    static constexpr int kEpilogueWarps = 16, kColsPerWarp = kTileN / (kEpilogueWarps / 4);
+    static constexpr int kProducerWarps = 8, kRowsPerWarp = kTileM / kProducerWarps;
+    static constexpr int kPartsPerThread = Dec::kParts / (32 / kRowsPerWarp);       // chunk parts a producer thread decodes
     static constexpr int kThreads = 32 * (4 + kProducerWarps + kEpilogueWarps);
     // registers per thread of each role (setmaxnreg); the B' warp of the affine qtypes holds a tile of sums
-    static constexpr int kCtlRegs = kHasMin ? 80 : 48, kProdRegs = kHasMin ? 56 : 48, kEpiRegs = 88;
+    static constexpr int kCtlRegs = kHasMin ? 72 : 48;                               // the B' warp holds eight uint4
+    static constexpr int kProdRegs = kHasMin ? 56 : 48, kEpiRegs = kHasMin ? 80 : 88;
     static constexpr uint32_t kBTileBytes = (kTileN / kBoxN) * kTileBytes;
     static constexpr uint32_t kRawStageBytes = kTileM * Dec::kBoxBytes;
     using Scale = typename std::conditional<kHasMin, float2, float>::type;          // {d, dmin} or d per row and superblock
@@ -427,20 +431,24 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
                 tile_of(t, cb, mat, mt);
                 for (int sb = 0; sb < nsb; ++sb, ++sb_it) {
                     const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
-                    // this token row's sums for the superblock (zero rows past the block's tail); all the
-                    // loads are in flight together, and before the wait for the tile
-                    uint4 v[kTileM / kRowsPerPass];
-#pragma unroll
-                    for (int i = 0; i < kTileM / kRowsPerPass; ++i) {
-                        const int r = rsub + i * kRowsPerPass;
-                        const uint4 *src = reinterpret_cast<const uint4 *>(p.sums + ((uint64_t)(cb.row0 + r) * nsb + sb) * 32);
-                        v[i] = r < cb.ncols ? __ldg(src + part) : make_uint4(0, 0, 0, 0);
-                    }
-                    if (!mbar_wait(&sm->min_empty[buf], bph ^ 1u, abort)) break;
+                    // this token row's sums for the superblock (zero rows past the block's tail), eight rows
+                    // per lane in flight together; the first eight are loaded before the wait for the tile
+                    constexpr int kPasses = kTileM / kRowsPerPass, kBatch = 8;
                     uint8_t *tile = min_tiles + buf * kTileBytes;
 #pragma unroll
-                    for (int i = 0; i < kTileM / kRowsPerPass; ++i)
-                        *reinterpret_cast<uint4 *>(tile + sw128_offset(rsub + i * kRowsPerPass, 4 + part)) = v[i];
+                    for (int base = 0; base < kPasses; base += kBatch) {
+                        uint4 v[kBatch];
+#pragma unroll
+                        for (int i = 0; i < kBatch; ++i) {
+                            const int r = rsub + (base + i) * kRowsPerPass;
+                            const uint4 *src = reinterpret_cast<const uint4 *>(p.sums + ((uint64_t)(cb.row0 + r) * nsb + sb) * 32);
+                            v[i] = r < cb.ncols ? __ldg(src + part) : make_uint4(0, 0, 0, 0);
+                        }
+                        if (base == 0 && !mbar_wait(&sm->min_empty[buf], bph ^ 1u, abort)) goto done;
+#pragma unroll
+                        for (int i = 0; i < kBatch; ++i)
+                            *reinterpret_cast<uint4 *>(tile + sw128_offset(rsub + (base + i) * kRowsPerPass, 4 + part)) = v[i];
+                    }
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm->min_full[buf]);
@@ -474,7 +482,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
                 for (int c = 0; c < 4; ++c) {
                     const uint32_t it = 4u * sb_it + c, s = stage_of(it), ph = phase_of(it);
                     if (!mbar_wait(&sm->empty[s], ph ^ 1u, abort)) goto done;
-                    Dec::store(raw, mis, c, h, a_tiles + s * kTileBytes, row, tab);
+#pragma unroll
+                    for (int q = 0; q < Plan::kPartsPerThread; ++q)
+                        Dec::store(raw, mis, c, h * Plan::kPartsPerThread + q, a_tiles + s * kTileBytes, row, tab);
                     fence_proxy_async();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sm->full[s]);
@@ -493,17 +503,18 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
         }
     } else {
         // ---------------- epilogue ----------------
-        const int ew = warp - (4 + kProducerWarps), quarter = warp & 3, colhalf = ew >> 2;     // TMEM lanes 32*quarter.., columns 64*colhalf.. (colhalf < kTileN / 64)
+        constexpr int kCols = Plan::kColsPerWarp;
+        const int ew = warp - (4 + kProducerWarps), quarter = warp & 3, colhalf = ew >> 2;     // TMEM lanes 32*quarter.., columns kCols*colhalf..
         const int row = 32 * quarter + lane;
         const uint32_t lane_addr = (uint32_t)(32 * quarter) << 16;
         uint32_t sb_it = 0;
         for (long long t = blockIdx.x; t < tiles_total && !*abort; t += gridDim.x) {
             ColBlock cb; int mat, mt;
             tile_of(t, cb, mat, mt);
-            float acc[64];
+            float acc[kCols];
 #pragma unroll
-            for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
-            const int ncols_here = cb.ncols - 64 * colhalf;       // columns this warp owns that are real
+            for (int i = 0; i < kCols; ++i) acc[i] = 0.0f;
+            const int ncols_here = cb.ncols - kCols * colhalf;    // columns this warp owns that are real
             for (int sb = 0; sb < nsb; ++sb, ++sb_it) {
                 const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
                 if (!mbar_wait(&sm->acc_full[buf], bph, abort)) goto done;
@@ -514,14 +525,14 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
                 else d = dscale[(sb_it % kScaleRing) * kTileM + row];
                 if (ncols_here > 0) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
+                    for (int q = 0; q < kCols / 16; ++q) {
                         uint32_t v[16];
-                        tmem_ld16(tmem + lane_addr + buf * kTileN + 64 * colhalf + 16 * q, v);
+                        tmem_ld16(tmem + lane_addr + buf * kTileN + kCols * colhalf + 16 * q, v);
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 16; ++i) acc[16 * q + i] = fmaf(d, __uint_as_float(v[i]), acc[16 * q + i]);
                         if (kHasMin) {
-                            tmem_ld16(tmem + lane_addr + 2 * kTileN + buf * kTileN + 64 * colhalf + 16 * q, v);
+                            tmem_ld16(tmem + lane_addr + 2 * kTileN + buf * kTileN + kCols * colhalf + 16 * q, v);
                             tmem_ld_wait();
 #pragma unroll
                             for (int i = 0; i < 16; ++i) acc[16 * q + i] = fmaf(-dmin, __uint_as_float(v[i]), acc[16 * q + i]);
@@ -540,14 +551,14 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
             // (a quarter of the store instructions).
             uint32_t nonfinite = 0;
 #pragma unroll
-            for (int i = 0; i < 64; ++i) nonfinite |= (~__float_as_uint(acc[i]) & 0x7f800000u) == 0u;
+            for (int i = 0; i < kCols; ++i) nonfinite |= (~__float_as_uint(acc[i]) & 0x7f800000u) == 0u;
             if (nonfinite) raise(p.status, YVEX_B200_STATUS_NUMERIC);
             const bool odd = lane & 1, hi = lane & 2;
             const int j4 = lane & 3;
             const uint64_t m0 = (uint64_t)mt * kTileM + 32 * quarter + (lane & ~3);
             float *out_f32 = mat ? p.out_f32[1] : p.out_f32[0];
 #pragma unroll
-            for (int b = 0; b < 16; ++b) {
+            for (int b = 0; b < kCols / 4; ++b) {
                 float r0 = acc[4 * b], r1 = acc[4 * b + 1], r2 = acc[4 * b + 2], r3 = acc[4 * b + 3];
                 float s0 = __shfl_xor_sync(0xffffffffu, odd ? r0 : r1, 1), s1 = __shfl_xor_sync(0xffffffffu, odd ? r2 : r3, 1);
                 if (odd) { r0 = s0; r2 = s1; } else { r1 = s0; r3 = s1; }
@@ -556,7 +567,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
                 if (hi) { r0 = s0; r1 = s1; } else { r2 = s0; r3 = s1; }
                 const int col = 4 * b + j4;
                 if (col < ncols_here) {
-                    const uint64_t srow = (uint64_t)cb.row0 + 64 * colhalf + col;
+                    const uint64_t srow = (uint64_t)cb.row0 + kCols * colhalf + col;
                     const uint64_t at = (p.out_rows ? (uint64_t)__ldg(p.out_rows + srow) : srow) * p.M + m0;
                     // streaming stores: the results are not read again by this kernel and must not push the
                     // activation tiles and weight rows that other CTAs are about to reuse out of L2
