@@ -75,11 +75,14 @@ class ExpertParallelLayer:
             recv_counts_t.copy_(send_counts_t)
         else:
             dist.all_to_all_single(recv_counts_t, send_counts_t, group=self.group)
-        send_counts, recv_counts = send_counts_t.tolist(), recv_counts_t.tolist()
-
+        # the send buffers do not depend on the counts: enqueue them before the host reads the counts,
+        # so the device has work while the host waits
         send_rows = xh.index_select(0, torch.div(order, k, rounding_mode="floor"))
         meta = torch.stack(((sel % self.per_rank).reshape(-1).to(torch.int32),
                             wts.reshape(-1).contiguous().view(torch.int32)), dim=1).index_select(0, order).contiguous()
+        inverse = torch.empty(order.numel(), dtype=torch.int32, device=order.device)
+        inverse[order] = torch.arange(order.numel(), dtype=torch.int32, device=order.device)
+        send_counts, recv_counts = send_counts_t.tolist(), recv_counts_t.tolist()
         # One pair list per rank: the received routed pairs, then this rank's own tokens for the (replicated)
         # shared expert as pairs of expert -1 with weight 1 - one set of grouped GEMM launches instead of two.
         # The routed rows are received straight into the head of the list's row buffer.
@@ -95,6 +98,4 @@ class ExpertParallelLayer:
 
         y_back = self._all_to_all(y_recv, recv_counts, send_counts)      # reverse direction, same splits
         # pair (token, rank) sits at row inverse[...] of y_back: the combine reads through that index
-        inverse = torch.empty(order.numel(), dtype=torch.int32, device=order.device)
-        inverse[order] = torch.arange(order.numel(), dtype=torch.int32, device=order.device)
         return ops.combine(y_back, y_shared, k, routed_rows=inverse), sel, wts
