@@ -109,6 +109,14 @@ __device__ __forceinline__ void store_scaled8(uint8_t *tile, uint32_t row, uint3
     *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, chunk)) = v;
 }
 
+// Four bytes (each < 1024) -> four exact fp16 values: 0x6400 | b is 1024 + b, minus 1024.
+__device__ __forceinline__ uint2 bytes_to_half4(uint32_t b4) {
+    uint32_t lo = __byte_perm(b4, 0x64646464u, 0x4140), hi = __byte_perm(b4, 0x64646464u, 0x4342);
+    const __half2 k = __floats2half2_rn(1024.0f, 1024.0f);
+    const __half2 a = __hsub2(*reinterpret_cast<__half2 *>(&lo), k), b = __hsub2(*reinterpret_cast<__half2 *>(&hi), k);
+    return make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
+}
+
 __device__ __forceinline__ float2 checked_scales(uint32_t d_bits, uint32_t dmin_bits, float d_mul, bool &bad) {
     const float d = f16_bits_to_float((uint16_t)d_bits), dmin = f16_bits_to_float((uint16_t)dmin_bits);
     bad = !isfinite(d) || !isfinite(dmin) || d < 0.0f || dmin < 0.0f;
@@ -173,15 +181,13 @@ struct GemmQ4k {
     }
     // A' row: slots 0..7 = the eight mins (paired with the hi sums), 8..15 = the same mins (lo sums);
     // thread h writes 16-byte part h.
+    // (the eight 6-bit mins, four bytes at a time: mins 0..3 are bytes 4..7 & 63, mins 4..7 the high
+    // nibbles of bytes 8..11 with the top two bits of bytes 4..7 above them)
     __device__ static void mins(const uint32_t *raw, int h, uint8_t *tile, uint32_t row) {
-        __half v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            uint32_t sc, m;
-            scale_min_words(raw[1], raw[2], raw[3], j, sc, m);
-            v[j] = __float2half_rn(static_cast<float>(m));
-        }
-        *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, h)) = *reinterpret_cast<uint4 *>(v);
+        const uint32_t s1 = raw[2], s2 = raw[3];
+        const uint2 a = bytes_to_half4(s1 & 0x3f3f3f3fu);
+        const uint2 b = bytes_to_half4(((s2 >> 4) & 0x0f0f0f0fu) | (((s1 >> 6) & 0x03030303u) << 4));
+        *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, h)) = make_uint4(a.x, a.y, b.x, b.y);
     }
 };
 
@@ -207,12 +213,10 @@ struct GemmQ2k {
     // A' row: slots 0..15 = the sixteen mins (hi sums), 16..31 = the same mins (lo sums); thread h
     // converts mins 8h..8h+7 and writes them to parts h and h + 2.
     __device__ static void mins(const uint32_t *raw, int h, uint8_t *tile, uint32_t row) {
-        __half v[8];
-        const uint32_t w[2] = {raw[2 * h], raw[2 * h + 1]};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = __float2half_rn(static_cast<float>((w[j >> 2] >> (8 * (j & 3) + 4)) & 15u));
-        *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, h)) = *reinterpret_cast<uint4 *>(v);
-        *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, h + 2)) = *reinterpret_cast<uint4 *>(v);
+        const uint2 a = bytes_to_half4((raw[2 * h] >> 4) & 0x0f0f0f0fu), b = bytes_to_half4((raw[2 * h + 1] >> 4) & 0x0f0f0f0fu);
+        const uint4 v = make_uint4(a.x, a.y, b.x, b.y);
+        *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, h)) = v;
+        *reinterpret_cast<uint4 *>(tile + sm100::sw128_offset(row, h + 2)) = v;
     }
 };
 
