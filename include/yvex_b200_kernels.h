@@ -159,6 +159,19 @@ int yvex_b200_moe_expert_rows(const yvex_b200_moe_geometry *g, const yvex_b200_m
                               int *status, void *stream);
 int yvex_b200_moe_combine(const void *y_routed_bf16, const void *y_shared_bf16, uint64_t tokens,
                           uint64_t topk, uint64_t hidden, float *out, int *status, void *stream);
+/*
+ * The sending side of the expert-parallel dispatch in one call: groups the (token, rank) pairs of
+ * `selected` [tokens x topk] by destination rank e / experts_per_rank (stable: ascending pair index
+ * within a rank) and writes, in that send order, the fp16 rows (row of pair p = rows_f16[p / topk]),
+ * meta[2*pos] = expert id local to its rank and meta[2*pos + 1] = route weight bits; inverse[p] =
+ * position of pair p in the send order (what the combine later reads through), send_counts[r] =
+ * pairs for rank r (64-bit, the split sizes of the all-to-all-v). No reference counterpart.
+ */
+uint64_t yvex_b200_ep_dispatch_workspace_bytes(uint64_t pairs, uint64_t world);
+int yvex_b200_ep_dispatch(const int32_t *selected, const float *weights, const void *rows_f16, uint64_t tokens,
+                          uint64_t topk, uint64_t hidden, uint64_t experts_per_rank, uint64_t world,
+                          void *send_rows_f16, int32_t *meta, int32_t *inverse, long long *send_counts,
+                          void *workspace, uint64_t workspace_bytes, int *status, void *stream);
 /* The same sum with the rows named by index: routed row (t, r) is y_routed[routed_rows[t*topk + r]],
  * the shared row of token t is y_shared[shared_rows[t]]; a NULL index means the identity order.
  * Lets an expert-parallel home rank combine straight from its receive buffer. */

@@ -167,3 +167,32 @@ def test_wide_config5_size_properties(L, port):
     rc, want, sel0, _ = port.moe_tokens(Lp, x[two].cpu().numpy(), logits=logits[two].cpu().numpy(), threads=2)
     assert rc == 0 and (sel[two].cpu().numpy() == sel0).all()
     assert rel_l2(out[two].cpu().numpy(), want) <= 1e-3
+
+
+@pytest.mark.parametrize("world,tokens,topk,experts", [(8, 300, 8, 256), (2, 64, 6, 64), (4, 1, 4, 16)])
+def test_ep_dispatch_matches_the_tensor_formulation(L, world, tokens, topk, experts):
+    """yvex_b200_ep_dispatch against the stable-argsort formulation the layer uses without it."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(tokens)
+    per_rank, H = experts // world, 256
+    sel = torch.stack([torch.randperm(experts, device="cuda", generator=g)[:topk] for _ in range(tokens)]).to(torch.int32)
+    wts = torch.rand((tokens, topk), device="cuda", generator=g)
+    xh = torch.randn((tokens, H), device="cuda", generator=g).to(torch.float16)
+    st = L.Status()
+    send_rows, meta, inverse, counts = L.ep_dispatch(xh, sel, wts, per_rank, world, st)
+    assert st.read() == 0
+    dest = (sel // per_rank).reshape(-1).to(torch.int64)
+    order = torch.argsort(dest, stable=True)
+    assert torch.equal(counts, torch.bincount(dest, minlength=world))
+    assert torch.equal(send_rows, xh.index_select(0, torch.div(order, topk, rounding_mode="floor")))
+    want_meta = torch.stack(((sel % per_rank).reshape(-1), wts.reshape(-1).view(torch.int32)), dim=1).index_select(0, order)
+    assert torch.equal(meta, want_meta)
+    want_inv = torch.empty_like(order)
+    want_inv[order] = torch.arange(order.numel(), device="cuda")
+    assert torch.equal(inverse.to(torch.int64), want_inv)
+    # an expert id outside world * per_rank raises the argument status instead of indexing past the bins
+    bad = sel.clone()
+    bad[0, 0] = experts
+    L.ep_dispatch(xh, bad, wts, per_rank, world, st)
+    torch.cuda.synchronize()
+    assert st.read() == 2

@@ -482,6 +482,68 @@ extern "C" int yvex_b200_moe_expert_rows(const yvex_b200_moe_geometry *geom, con
     return launch_status(1);
 }
 
+// ---- expert-parallel dispatch plan -----------------------------------------------------------------
+// dest rank and source token of every (token, rank) pair, and the pairs per destination
+__global__ void ep_dest_kernel(const int32_t *selected, uint64_t pairs, uint64_t topk, int per_rank, int world, int *dest,
+                               int *src_token, int *counts, int *status) {
+    for (uint64_t p = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; p < pairs; p += (uint64_t)gridDim.x * blockDim.x) {
+        const int e = selected[p];
+        int d = e >= 0 ? e / per_rank : world;
+        src_token[p] = (int)(p / topk);
+        // an id outside the ranks' experts raises the status; the pair still gets a bin, so that the
+        // counts, the send order and everything indexed through them stay consistent and in range
+        if (d >= world) { raise(status, YVEX_B200_STATUS_ARGUMENT); d = 0; }
+        dest[p] = d;
+        atomicAdd(&counts[d], 1);
+    }
+}
+
+__global__ void ep_offsets_kernel(const int *counts, int world, int *offsets, long long *counts_out) {
+    if (threadIdx.x || blockIdx.x) return;
+    int off = 0;
+    for (int r = 0; r < world; ++r) { offsets[r] = off; off += counts[r]; counts_out[r] = counts[r]; }
+    offsets[world] = off;
+}
+
+// metadata of the pairs in send order: (expert id local to its rank, route weight bits)
+__global__ void ep_meta_kernel(const int32_t *selected, const float *weights, const int *order, uint64_t pairs, int per_rank,
+                               int32_t *meta) {
+    for (uint64_t pos = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; pos < pairs; pos += (uint64_t)gridDim.x * blockDim.x) {
+        const int p = order[pos];
+        meta[2 * pos] = selected[p] % per_rank;
+        meta[2 * pos + 1] = __float_as_int(weights[p]);
+    }
+}
+
+extern "C" uint64_t yvex_b200_ep_dispatch_workspace_bytes(uint64_t pairs, uint64_t world) {
+    return (3 * pairs + 2 * world + 8) * sizeof(int) + 256;
+}
+
+extern "C" int yvex_b200_ep_dispatch(const int32_t *selected, const float *weights, const void *rows_f16, uint64_t tokens,
+                                     uint64_t topk, uint64_t hidden, uint64_t experts_per_rank, uint64_t world,
+                                     void *send_rows_f16, int32_t *meta, int32_t *inverse, long long *send_counts,
+                                     void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
+    if (!selected || !weights || !rows_f16 || !send_rows_f16 || !meta || !inverse || !send_counts || !status || !workspace)
+        return ERR_INVALID_ARG;
+    if (!tokens || !topk || !experts_per_rank || !world || world > 1024 || hidden % 8) return ERR_INVALID_ARG;
+    const uint64_t pairs = tokens * topk;
+    if (pairs > 0x7fffff00ull || ((reinterpret_cast<uintptr_t>(rows_f16) | reinterpret_cast<uintptr_t>(send_rows_f16)) & 15u))
+        return ERR_BOUNDS;
+    if (workspace_bytes < yvex_b200_ep_dispatch_workspace_bytes(pairs, world)) return ERR_NOMEM;
+    int *dest = static_cast<int *>(workspace), *src = dest + pairs, *order = src + pairs;
+    int *counts = order + pairs, *offsets = counts + world + 1;
+    cudaStream_t s = as_stream(stream);
+    cudaMemsetAsync(counts, 0, (world + 1) * sizeof(int), s);
+    ep_dest_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(selected, pairs, topk, (int)experts_per_rank, (int)world, dest, src, counts,
+                                                          status);
+    ep_offsets_kernel<<<1, 32, 0, s>>>(counts, (int)world, offsets, send_counts);
+    wide_scatter_kernel<<<(unsigned)world, 512, 0, s>>>(dest, pairs, offsets, order, inverse);
+    ep_meta_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(selected, weights, order, pairs, (int)experts_per_rank, meta);
+    wide_gather_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(static_cast<const __half *>(rows_f16), order, src, pairs, hidden,
+                                                              static_cast<__half *>(send_rows_f16));
+    return launch_status(5);
+}
+
 extern "C" int yvex_b200_moe_combine_indexed(const void *y_routed_bf16, const int32_t *routed_rows, const void *y_shared_bf16,
                                              const int32_t *shared_rows, uint64_t tokens, uint64_t topk, uint64_t hidden,
                                              float *out, int *status, void *stream) {

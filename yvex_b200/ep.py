@@ -36,6 +36,10 @@ class DeviceOps:
                                          logits=logits)
         return sel, wts
 
+    def dispatch(self, xh, sel, wts, per_rank, world):
+        """Send order, send rows, metadata, inverse index and split sizes in one library call."""
+        return self.lib.ep_dispatch(xh, sel.contiguous(), wts.contiguous(), per_rank, world, self.status)
+
     def expert_rows(self, rows_h, ids, wts):
         return self.lib.moe_expert_rows(self.geom_local, self.weights, rows_h, ids, wts, self.status)
 
@@ -67,9 +71,13 @@ class ExpertParallelLayer:
         t = x.shape[0]
         xh = ops.ingress(x)
         sel, wts = ops.route(x, logits)                                   # [t, k] int32 / f32
-        dest = (sel // self.per_rank).reshape(-1).to(torch.int64)
-        order = torch.argsort(dest, stable=True)                          # pairs grouped by destination rank
-        send_counts_t = torch.bincount(dest, minlength=self.world)
+        fused = getattr(ops, "dispatch", None)
+        if fused is not None:                                             # one call instead of the tensor ops below
+            send_rows, meta, inverse, send_counts_t = fused(xh, sel, wts, self.per_rank, self.world)
+        else:
+            dest = (sel // self.per_rank).reshape(-1).to(torch.int64)
+            order = torch.argsort(dest, stable=True)                      # pairs grouped by destination rank
+            send_counts_t = torch.bincount(dest, minlength=self.world)
         recv_counts_t = torch.empty_like(send_counts_t)
         if self.world == 1:
             recv_counts_t.copy_(send_counts_t)
@@ -77,11 +85,12 @@ class ExpertParallelLayer:
             dist.all_to_all_single(recv_counts_t, send_counts_t, group=self.group)
         # the send buffers do not depend on the counts: enqueue them before the host reads the counts,
         # so the device has work while the host waits
-        send_rows = xh.index_select(0, torch.div(order, k, rounding_mode="floor"))
-        meta = torch.stack(((sel % self.per_rank).reshape(-1).to(torch.int32),
-                            wts.reshape(-1).contiguous().view(torch.int32)), dim=1).index_select(0, order).contiguous()
-        inverse = torch.empty(order.numel(), dtype=torch.int32, device=order.device)
-        inverse[order] = torch.arange(order.numel(), dtype=torch.int32, device=order.device)
+        if fused is None:
+            send_rows = xh.index_select(0, torch.div(order, k, rounding_mode="floor"))
+            meta = torch.stack(((sel % self.per_rank).reshape(-1).to(torch.int32),
+                                wts.reshape(-1).contiguous().view(torch.int32)), dim=1).index_select(0, order).contiguous()
+            inverse = torch.empty(order.numel(), dtype=torch.int32, device=order.device)
+            inverse[order] = torch.arange(order.numel(), dtype=torch.int32, device=order.device)
         send_counts, recv_counts = send_counts_t.tolist(), recv_counts_t.tolist()
         # One pair list per rank: the received routed pairs, then this rank's own tokens for the (replicated)
         # shared expert as pairs of expert -1 with weight 1 - one set of grouped GEMM launches instead of two.

@@ -54,6 +54,9 @@ def _load():
                                               vp, u64, vp, vp]
     lib.yvex_b200_moe_combine.argtypes = [vp, vp, u64, u64, u64, vp, vp, vp]
     lib.yvex_b200_moe_combine_indexed.argtypes = [vp, vp, vp, vp, u64, u64, u64, vp, vp, vp]
+    lib.yvex_b200_ep_dispatch_workspace_bytes.restype = u64
+    lib.yvex_b200_ep_dispatch_workspace_bytes.argtypes = [u64, u64]
+    lib.yvex_b200_ep_dispatch.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, vp, vp, vp, vp, vp, u64, vp, vp]
     lib.yvex_b200_attention_workspace_bytes.restype = u64
     lib.yvex_b200_attention_workspace_bytes.argtypes = [u64] * 5
     lib.yvex_b200_dequant_rows.argtypes = [C.c_uint, vp, u64, u64, u64, vp, vp, vp]
@@ -83,7 +86,7 @@ EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_ge
            "yvex_b200_moe_route", "yvex_b200_moe_decode", "yvex_b200_moe_wide",
            "yvex_b200_moe_wide_workspace_bytes", "yvex_b200_launch_count", "yvex_b200_phase_events",
            "yvex_b200_moe_expert_rows_workspace_bytes", "yvex_b200_moe_expert_rows", "yvex_b200_moe_combine",
-           "yvex_b200_moe_combine_indexed",
+           "yvex_b200_moe_combine_indexed", "yvex_b200_ep_dispatch_workspace_bytes", "yvex_b200_ep_dispatch",
            "yvex_b200_attention_workspace_bytes", "yvex_b200_attention_gqa_decode",
            "yvex_b200_attention_f32", "yvex_b200_attention_static_scratch_bytes",
            "yvex_b200_attention_gqa_decode_static", "yvex_b200_mhc_workspace_bytes", "yvex_b200_mhc_prepare",
@@ -223,6 +226,25 @@ def moe_combine(y_routed, y_shared, topk, status, out=None, routed_rows=None, sh
     _check(lib.yvex_b200_moe_combine_indexed(_p(y_routed), _p(routed_rows), _p(y_shared), _p(shared_rows), tokens, topk,
                                              hidden, _p(out), _p(status.word), _stream()), "moe_combine")
     return out
+
+
+def ep_dispatch(rows_f16, selected, route_weights, experts_per_rank, world, status):
+    """Sending side of the expert-parallel dispatch: rows_f16 [T, hidden] fp16, selected / route_weights [T, k]
+    -> (send_rows [T*k, hidden] fp16 grouped by destination rank, meta [T*k, 2] int32, inverse [T*k] int32,
+    send_counts [world] int64)."""
+    torch = _torch()
+    tokens, hidden = rows_f16.shape
+    topk = selected.shape[1]
+    pairs, dev = tokens * topk, rows_f16.device
+    send_rows = torch.empty((pairs, hidden), dtype=rows_f16.dtype, device=dev)
+    meta = torch.empty((pairs, 2), dtype=torch.int32, device=dev)
+    inverse = torch.empty(pairs, dtype=torch.int32, device=dev)
+    counts = torch.empty(world, dtype=torch.int64, device=dev)
+    ws = torch.empty(int(lib.yvex_b200_ep_dispatch_workspace_bytes(pairs, world)), dtype=torch.uint8, device=dev)
+    _check(lib.yvex_b200_ep_dispatch(_p(selected), _p(route_weights), _p(rows_f16), tokens, topk, hidden, experts_per_rank,
+                                     world, _p(send_rows), _p(meta), _p(inverse), _p(counts), _p(ws), ws.numel(),
+                                     _p(status.word), _stream()), "ep_dispatch")
+    return send_rows, meta, inverse, counts
 
 
 def moe_route(geom, weights, status, rows_f32=None, logits=None, token_ids=None):
