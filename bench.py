@@ -398,6 +398,65 @@ def run_native(args):
         dist.destroy_process_group()
 
 
+def ep_parity_check(torch, dist, lib, layer_out, geom_full, weights_full, x, lg, status, world, count=8):
+    """Outside the timed region: `count` of this rank's rows run once more on this rank alone, through the
+    single-device wide layer (every rank holds the full weight packs) - the sharded result must equal it
+    bit for bit, because whole bf16 pair rows travel and are summed in rank order - and through the
+    decode path (other kernels, other accumulation order): identical selection, relative L2 <= 1e-3."""
+    t_loc = x.shape[0]
+    idx = torch.linspace(0, t_loc - 1, count, device=x.device).long()
+    xs, ls = x[idx].contiguous(), lg[idx].contiguous()
+    want, sel_w, _ = lib.moe_layer(geom_full, weights_full, xs, status, logits=ls, wide=True)
+    near, sel_n, _ = lib.moe_layer(geom_full, weights_full, xs, status, logits=ls, wide=False)
+    got = layer_out[idx]
+    bad_rows = (got.view(torch.int32) != want.view(torch.int32)).any(dim=1).sum()
+    rel = (got.double() - near.double()).norm() / near.double().norm().clamp_min(1e-30)
+    sel_bad = (sel_w != sel_n).any(dim=1).sum()
+    stats = torch.stack([bad_rows.double(), sel_bad.double(), rel.double()])
+    worst = stats.clone()
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.SUM)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    mismatched, sel_mismatched, rel_max = int(stats[0].item()), int(stats[1].item()), float(worst[2].item())
+    if mismatched or sel_mismatched or not rel_max <= 1e-3 or status.read() != 0:
+        raise RuntimeError(f"parity check failed: {mismatched} rows differ bitwise from the single-device wide layer, "
+                           f"{sel_mismatched} selections differ, rel L2 vs decode path {rel_max:.3e}")
+    return {"tokens": count * world, "mismatched": mismatched, "selection_mismatched": sel_mismatched,
+            "against": "single-device wide layer on the same rows (bitwise) and decode path (rel L2 <= 1e-3)",
+            "rel_l2_vs_decode_path": rel_max}
+
+
+def pinned_twin(torch, lib, args, flush, status, dev):
+    """Config 5 with Q2_K down weights - the qtype the reference's own MoE path decodes - device-timed
+    like the main line, and checked against the compiled reference (the port where it is absent) on 4 rows."""
+    from yvex_b200 import synth
+    from yvex_b200.workloads import MoEWorkload
+    wl = MoEWorkload("c5", 1, device=dev, down_qtype=synth.Q2_K)
+    T = wl.cfg["tokens"]
+    geom, weights = lib.geometry_of(wl.spec), lib.weights_of(wl.tensors)
+    x, lg = wl.tokens(T)
+    ws = torch.empty(lib.moe_workspace_bytes(geom, T, True), dtype=torch.uint8, device=dev)
+    out = torch.empty((T, wl.cfg["hidden"]), dtype=torch.float32, device=dev)
+
+    def step(i):
+        lib.moe_layer(geom, weights, x, status, logits=lg, wide=True, workspace=ws, out=out)
+    for i in range(args.warmup):
+        step(i)
+    ms = _timed_events(torch, step, args.steps, before=lambda i: flush.fill_(i & 0xFF))
+    oracle, kind = oracle_backend(True)
+    idx = torch.tensor([0, 5461, 10922, 16383], device=dev)
+    hw, _ = wl.host_copy()
+    L = oracle.layer(wl.spec, hw)
+    rc, want, sel0, _ = oracle.moe_tokens(L, x[idx].cpu().numpy(), logits=lg[idx].cpu().numpy(), threads=4)
+    got = out[idx].cpu().numpy().astype(np.float64)
+    rel = float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+    if rc != 0 or not rel <= 1e-3 or status.read() != 0:
+        raise RuntimeError(f"Q2_K-down twin differs from the CPU {kind}: rc {rc}, rel L2 {rel:.3e}")
+    t = sum(ms) / len(ms)
+    return {"workload": "c5-q2k-down", "value": T / (t * 1e-3), "unit": UNIT, "ms_per_step": t,
+            "checked_against": kind, "checked_tokens": 4, "rel_l2": rel}
+
+
 def run_native_ep(args):
     """Config 5: the expert-parallel layer. Total work is fixed (16384 tokens, 256 experts) and
     split over the ranks (strong scaling): tokens by home rank, experts in contiguous shards."""
@@ -564,6 +623,22 @@ def run_native_ep(args):
         torch.cuda.synchronize()
     if status.read() != 0:
         raise RuntimeError(f"device status word = {status.read()} after the timed region")
+    # result check at this world size, outside the timed region
+    weights_all = lib.weights_of(wl.tensors)
+    parity = ep_parity_check(torch, dist, lib, step(0), geom_full, weights_all, x, lg, status, world)
+    if world == 1:
+        # the end-to-end leg's host rows must be the device-timed leg's rows
+        torch.cuda.synchronize()
+        if not torch.equal(host_out.view(torch.int32), step(0).cpu().view(torch.int32)):
+            raise RuntimeError("execute_rows_wide (host rows) differs from the device-resident layer")
+    twin = None
+    if world == 1 and rank == 0:
+        try:
+            twin = pinned_twin(torch, lib, args, flush, status, dev)
+        except RuntimeError:
+            raise
+        except Exception as exc:                                # e.g. out of memory beside the main workload
+            twin = {"workload": "c5-q2k-down", "value": None, "failed": str(exc)}
     # per-step max over ranks, then summed: every step is bracketed by a barrier
     tm = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
@@ -578,10 +653,14 @@ def run_native_ep(args):
         pairs = sum(pair_counts) / len(pair_counts)
         top, t_top, fl = ("gate_up_gemm", gu, pairs * 4.0 * H * I) if gu >= dn else ("down_gemm", dn, pairs * 2.0 * H * I)
         ach = fl / (t_top * 1e-3) / 1e12
-        peak = peaks["bf16_tflops_sustained"]
+        peak = peaks["bf16_tflops"]                             # burst: the timed region runs near the maximum SM clock
         roofline = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
                     "traffic": TRAFFIC.get(f"c5_{top}") if world == 1 else None,
-                    "peak_source": peaks["source"] + " (sustained; burst %.1f)" % peaks["bf16_tflops"],
+                    "peak_source": peaks["source"] + " (burst)", "peak_sustained": peaks["bf16_tflops_sustained"],
+                    "frac_of_sustained": ach / peaks["bf16_tflops_sustained"],
+                    "other_gemm": {"kernel": "down_gemm" if top == "gate_up_gemm" else "gate_up_gemm",
+                                   "achieved": (pairs * (2.0 if top == "gate_up_gemm" else 4.0) * H * I) /
+                                               ((dn if top == "gate_up_gemm" else gu) * 1e-3) / 1e12},
                     "pairs_per_launch": pairs,
                     "layer_achieved": T * (spec.topk + 1) * 6.0 * H * I / world / (t_dev / args.steps * 1e-3) / 1e12}
         cpu = None
@@ -607,6 +686,7 @@ def run_native_ep(args):
                         "d2h_bytes_per_step": int(T * H * 4), "api": e2e_api},
                 "gpu_launches": int(launches * world),
                 "phases_ms": {"gate_up_gemm": gu, "swiglu": sw, "down_gemm": dn},
+                "parity": parity, "twin": twin,
                 "roofline": roofline, "cpu_baseline": cpu}
         print(json.dumps(line), flush=True)
     if world > 1:

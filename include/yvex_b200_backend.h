@@ -21,6 +21,8 @@
 #define YVEX_B200_BACKEND_H
 #include <stddef.h>
 #include <stdint.h>
+
+#include "yvex_b200_kernels.h"
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -102,6 +104,12 @@ int yvex_backend_resident_resolve(const yvex_backend *backend, const unsigned ch
                                   unsigned long long *device_address);
 int yvex_backend_workspace_attach(yvex_backend *backend, yvex_device_tensor *workspace, yvex_error *err);
 int yvex_backend_workspace_detach(yvex_backend *backend, yvex_error *err);
+
+/* Runs the device self-test of the bounded waits (a wait nothing satisfies, `limit_ns` long) and
+ * reports it the way every expired device wait is reported: YVEX_ERR_TIMEOUT, backend still READY.
+ * Any other outcome is YVEX_ERR_BACKEND. No reference counterpart. */
+int yvex_backend_selftest_bounded_wait(yvex_backend *backend, unsigned long long limit_ns, unsigned long long *elapsed_ns,
+                                       yvex_error *err);
 
 /* ---- capability: include/yvex/backend.h:77-129 ------------------------------------------------------------ */
 typedef enum {
@@ -187,7 +195,13 @@ typedef struct {
     double routed_scaling_factor, activation_limit;
     int normalize_topk_probabilities;
 } yvex_moe_layer_plan;
-typedef struct { int status, pending; unsigned long long row_count, row_expert_pairs; } yvex_moe_device_completion_slot;
+/* Pointer-free worklist summary, laid out as include/yvex/internal/execution_batch.h:126-137. */
+typedef yvex_b200_worklist_observation yvex_expert_worklist_observation;
+typedef struct {
+    int status, pending;
+    unsigned long long row_count, row_expert_pairs;
+    yvex_expert_worklist_observation worklist;       /* copied with the status word in deferred mode (src/backend/cuda/moe.c:1710-1716) */
+} yvex_moe_device_completion_slot;
 typedef struct { int defer; yvex_moe_device_completion_slot *host; } yvex_moe_device_completion;
 typedef struct {
     const yvex_moe_layer_plan *layer;
@@ -222,6 +236,11 @@ typedef struct {
     unsigned long long stream_synchronizations;
     unsigned long long active_weight_base_bytes, active_weight_per_unique_expert_bytes;
     unsigned long long activation_bytes, temporary_bytes;
+    /* as the reference publishes them (src/backend/cuda/moe.c:1757-1786, :1905-1915): populated experts,
+     * the device-built worklist summary, copies counted, bytes of weights the batch had to read */
+    unsigned long long unique_experts, upload_count, download_count, active_weight_bytes;
+    unsigned long long pipeline_chunks;        /* row chunks whose host copies overlapped compute (wide entry, host rows) */
+    yvex_expert_worklist_observation worklists;
 } yvex_moe_row_batch_result;
 typedef struct {
     /* Derived layouts are not offered: both return YVEX_ERR_UNSUPPORTED and the canonical row layout is used. */

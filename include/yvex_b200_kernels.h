@@ -133,6 +133,12 @@ int yvex_b200_moe_decode(const yvex_b200_moe_geometry *g, const yvex_b200_moe_we
  * expert range (an expert-parallel shard); pairs outside it are left to other ranks.
  */
 uint64_t yvex_b200_moe_wide_workspace_bytes(const yvex_b200_moe_geometry *g, uint64_t rows);
+/* 1 when yvex_b200_moe_wide runs this layer on the tcgen05 grouped GEMM; 0 when its shapes, its
+ * qtypes or a weight pack that does not start on a 16-byte boundary send it to the row kernels
+ * (same results, far slower). Lets a caller report or refuse the slow path instead of meeting it. */
+int yvex_b200_moe_wide_uses_gemm(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w);
+/* Token columns of one grouped-GEMM tile for a weight qtype (0: the qtype has no GEMM decoder). */
+uint64_t yvex_b200_moe_wide_tile_columns(unsigned int qtype);
 int yvex_b200_moe_wide(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w,
                        const float *x, const float *logits, const uint32_t *token_ids,
                        uint64_t rows, float *out, int32_t *selected_out, float *weights_out,
@@ -178,6 +184,48 @@ int yvex_b200_ep_dispatch(const int32_t *selected, const float *weights, const v
 int yvex_b200_moe_combine_indexed(const void *y_routed_bf16, const int32_t *routed_rows, const void *y_shared_bf16,
                                   const int32_t *shared_rows, uint64_t tokens, uint64_t topk, uint64_t hidden,
                                   float *out, int *status, void *stream);
+
+/*
+ * Expert worklist of a routed batch: the stable expert-major counting sort of the (row, rank)
+ * pairs and its pointer-free summary. Replaces yvex_expert_worklist_build_cuda
+ * (src/backend/cuda/moe_kernels.cu:294-397); CPU meaning yvex_expert_worklist_build
+ * (src/graph/worklist.c:369-441): buckets ascending by expert id, only populated experts get a
+ * bucket, pairs ascending within a bucket, source_rows[i] = pair / topk, destination_rows[i] =
+ * pair. The observation has the layout of yvex_expert_worklist_observation
+ * (include/yvex/internal/execution_batch.h:126-137) so the host boundary can hand it on as is.
+ * Unlike the reference's builder the row count is not limited to 62. Every output pointer is
+ * optional; index arrays are int32 on the device. Batches of more than 2048 pairs need
+ * yvex_b200_expert_worklist_workspace_bytes() of scratch and run the wide path's own sort
+ * kernels; smaller ones take no scratch and one launch.
+ */
+#define YVEX_B200_WORKLIST_HISTOGRAM_CAP 17u
+#define YVEX_B200_WORKLIST_PROVENANCE_COUNT 5u
+typedef struct yvex_b200_worklist_observation {
+    unsigned int schema_version;
+    unsigned long long worklist_count, pair_count, bucket_count;
+    unsigned long long maximum_bucket_population;
+    unsigned long long tensor_core_eligible_pairs, tensor_core_executed_pairs;
+    unsigned long long narrow_pairs, tail_rows;
+    unsigned long long width_histogram[YVEX_B200_WORKLIST_HISTOGRAM_CAP];
+    unsigned long long population_histogram[YVEX_B200_WORKLIST_HISTOGRAM_CAP];
+    unsigned long long provenance_counts[YVEX_B200_WORKLIST_PROVENANCE_COUNT];
+} yvex_b200_worklist_observation;
+uint64_t yvex_b200_expert_worklist_workspace_bytes(uint64_t pairs, uint64_t experts);
+int yvex_b200_expert_worklist(const int32_t *selected, uint64_t rows, uint64_t topk, uint64_t experts,
+                              uint64_t tensor_core_minimum, uint64_t admitted_width, unsigned int provenance,
+                              int32_t *source_pairs, int32_t *source_rows, int32_t *destination_rows,
+                              int32_t *expert_ids, int32_t *bucket_offsets, int32_t *bucket_populations,
+                              yvex_b200_worklist_observation *observation, void *workspace,
+                              uint64_t workspace_bytes, int *status, void *stream);
+
+/*
+ * Self-test of the bounded device waits: one CTA waits on an mbarrier that nothing arrives on,
+ * with a limit of `limit_ns` nanoseconds of the device clock. The wait must run out: the kernel
+ * then raises status 3 (YVEX_B200_STATUS_TIMEOUT), writes the time it waited to *elapsed_ns
+ * (device memory, optional) and returns; no copy or tensor-core work is in flight, the context
+ * stays usable. No counterpart in the reference, whose kernels do not wait on one another.
+ */
+int yvex_b200_selftest_bounded_wait(uint64_t limit_ns, uint64_t *elapsed_ns, int *status, void *stream);
 
 /*
  * mHC envelope of the MoE FFN: the layer's rows carry `streams` residual streams
@@ -230,8 +278,9 @@ int yvex_b200_attention_gqa_decode(const void *q_bf16, const void *k_bf16, const
  * split-KV partials live in one fixed 8 MiB device array per device
  * (yvex_b200_attention_static_scratch_bytes()); a problem whose partials do not fit is refused
  * with YVEX_ERR_BOUNDS (-7) before any launch. The first call on a device resolves the array's
- * address and should be made during start-up, before any stream capture; calls that overlap in
- * time on one device race on the array and must be serialised by the caller. Results are
+ * address and should be made during start-up, before any stream capture; the array is that of the
+ * device current in the calling thread, and `stream` must belong to that device; calls that overlap
+ * in time on one device race on the array and must be serialised by the caller. Results are
  * identical to yvex_b200_attention_gqa_decode.
  */
 uint64_t yvex_b200_attention_static_scratch_bytes(void);

@@ -308,3 +308,136 @@ def test_backend_lifecycle_and_ownership(B):
     assert be.close() == B.OK and other.close() == B.OK
     limited = B.Backend(memory_limit=4096)
     assert limited.tensor(8192)[0] == B.NOMEM and limited.close() == B.OK
+
+
+def test_execute_rows_result_counters_match_the_reference_contract(B):
+    """The counters a caller asserts (src/runtime/moe.c:1457-1475; filled as in src/backend/cuda/moe.c:1757-1786,
+    :1905-1915): one grouped operation per pair, one shared operation per row, the populated experts
+    and the worklist summary built on the device, active bytes = replicated tensors + the experts in use."""
+    be, arena, job, spec, x, logits = layer_setup(B, "small_logits")
+    ops, _ = attach_workspace(B, be, job, x.shape[0])
+    rc, out, sel, wts, res = run_rows(B, be, ops, job, x, logits)
+    assert rc == B.OK, be.message()
+    rows, pairs = x.shape[0], x.shape[0] * spec.topk
+    counts = np.bincount(sel.reshape(-1).astype(np.int64), minlength=spec.experts)
+    unique = int((counts > 0).sum())
+    assert res.grouped_expert_operations == pairs and res.shared_expert_operations == rows
+    assert res.unique_experts == unique and res.tensor_core_launches == 2
+    w = res.worklists
+    assert (w.schema_version, w.worklist_count, w.pair_count, w.bucket_count) == (1, 1, pairs, unique)
+    assert w.maximum_bucket_population == counts.max() and w.narrow_pairs == pairs and w.tensor_core_eligible_pairs == 0
+    hist = np.bincount(np.minimum(counts[counts > 0], 16), minlength=17)
+    assert list(w.population_histogram) == hist.tolist()
+    assert list(w.width_histogram) == [1 if i == min(rows, 16) else 0 for i in range(17)]
+    base = sum(job.weights[s].encoded_bytes for s in (B.W_SHARED_GATE, B.W_SHARED_UP, B.W_SHARED_DOWN, B.W_ROUTER))
+    assert res.active_weight_base_bytes == base
+    assert res.encoded_bytes_read == base + unique * spec.weight_bytes_per_expert() == res.active_weight_bytes
+    assert be.close() == B.OK
+
+
+def test_execute_rows_wide_copy_pipeline_is_bit_identical(B):
+    """Host rows in, host rows out on the wide entry run as row ranges whose copies overlap compute
+    (rows are independent). The result must equal the same batch given as device rows, which runs in
+    one piece, bit for bit."""
+    H, E, k, I, T = 512, 8, 2, 256, 2600                    # 650 pairs per expert: four row ranges
+    spec = synth.MoELayerSpec(H, E, k, I, down_qtype=synth.Q2_K)
+    rng = np.random.default_rng(91)
+    x, logits = rng.standard_normal((T, H)).astype(np.float32), rng.standard_normal((T, E)).astype(np.float32)
+    be = B.Backend()
+    arena = B.ResidentArena(be, synth.moe_weights(spec, 92))
+    job = B.moe_job(arena, spec, router=False)
+    ops, _ = attach_workspace(B, be, job, T, wide=True)
+    rc, out, sel, wts, res = run_rows(B, be, ops, job, x, logits, wide=True)
+    assert rc == B.OK, be.message()
+    assert res.pipeline_chunks == 4 and res.tensor_core_launches == 8 and res.completed == 1
+    tin, tlg = be.from_array(x, B.F32), be.from_array(logits, B.F32)
+    tout = be.tensor(x.nbytes, B.F32, [T, H])[1]
+    sel2, wts2 = np.zeros((T, k), np.uint64), np.zeros((T, k), np.float32)
+    batch = B.RowBatch(T, H, H, None, tin, tout, None, tlg, None, 0)
+    o = B.RowBatchOutput(None, 0, sel2.ctypes.data_as(B.vp), wts2.ctypes.data_as(B.vp), sel2.size)
+    res2 = B.RowBatchResult()
+    assert ops.execute_rows_wide(be.h, C.byref(job), C.byref(batch), C.byref(o), C.byref(res2), C.byref(be.err)) == B.OK, be.message()
+    rc, whole = be.read(tout, np.float32, T * H)
+    assert res2.pipeline_chunks == 0 and res2.tensor_core_launches == 2
+    assert (sel == sel2).all() and (wts.view(np.uint32) == wts2.view(np.uint32)).all()
+    assert (out.view(np.uint32) == whole.reshape(T, H).view(np.uint32)).all()
+    assert res.unique_experts == res2.unique_experts == E
+    assert res.worklists.tensor_core_eligible_pairs == T * k and res.worklists.narrow_pairs == 0
+    assert be.close() == B.OK
+
+
+def test_bounded_device_wait_runs_out_and_maps_to_timeout(B):
+    """A device wait that nothing satisfies gives up after its limit, the kernel returns status 3, the
+    boundary reports YVEX_ERR_TIMEOUT and the backend stays usable (no trap, no hang, nothing demoted)."""
+    import time
+    be, arena, job, spec, x, logits = layer_setup(B, "small_logits")
+    elapsed = B.ull()
+    t0 = time.perf_counter()
+    rc = B._lib.yvex_backend_selftest_bounded_wait(be.h, 20_000_000, C.byref(elapsed), C.byref(be.err))
+    wall = time.perf_counter() - t0
+    assert rc == B.TIMEOUT and b"bounded device wait" in be.err.message
+    assert 20_000_000 <= elapsed.value < 1_000_000_000 and wall < 5.0, (elapsed.value, wall)
+    assert B._lib.yvex_backend_status_of(be.h) == 0                          # still READY
+    ops, _ = attach_workspace(B, be, job, x.shape[0])
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.OK                   # the status word was cleared
+    assert B._lib.yvex_backend_selftest_bounded_wait(be.h, 0, None, C.byref(be.err)) == B.INVALID_ARG
+    assert be.close() == B.OK
+
+
+def test_host_fault_seams_fail_closed(B, monkeypatch):
+    """The reference's test seams (src/backend/cuda/qtype.c:625-661, tests/unit/cuda/quant_qtype.c:1749-1811):
+    a refused copy fails the call and the backend recovers; a failed launch demotes the backend, which
+    then refuses everything with a state error until it is closed. Nothing faults on the device."""
+    rows, width = 64, 1024
+    w = synth.random_blocks(synth.Q8_0, rows, width, 5)
+    x = np.random.default_rng(6).standard_normal((1, width)).astype(np.float32)
+    be = B.Backend()
+    arena = B.ResidentArena(be, {"w": w})
+    tin = be.from_array(x, B.F32)
+    tout = be.tensor(rows * 4, B.F32, [1, rows])[1]
+    facts = B.Facts()
+    args = (arena.host_ptr("w"), w.size, synth.Q8_0, rows, width, w.shape[1], 1, tin, None, 0, None, tout, 0, C.byref(facts),
+            C.byref(be.err))
+    call = lambda: B._lib.yvex_backend_cuda_encoded_matvec(be.h, *args)
+    for where in ("input", "output"):
+        monkeypatch.setenv("YVEX_TEST_CUDA_QTYPE_COPY_FAILURE", where)
+        assert call() == B.BACKEND and tout.contents.is_written == 0
+        monkeypatch.delenv("YVEX_TEST_CUDA_QTYPE_COPY_FAILURE")
+        assert call() == B.OK and tout.contents.is_written == 1           # recovers after a copy refusal
+    monkeypatch.setenv("YVEX_TEST_CUDA_LAUNCH_FAILURE", "encoded-matvec")
+    assert call() == B.BACKEND
+    monkeypatch.delenv("YVEX_TEST_CUDA_LAUNCH_FAILURE")
+    assert B._lib.yvex_backend_status_of(be.h) == 3                          # FAILED, for good
+    assert call() == B.STATE and B.moe_ops(be) is None
+    assert be.read(tout, np.float32, rows)[0] == B.STATE
+    be.close()
+    # the MoE table has the same seam
+    be, arena, job, spec, x, logits = layer_setup(B, "small_logits")
+    ops, _ = attach_workspace(B, be, job, x.shape[0])
+    monkeypatch.setenv("YVEX_TEST_CUDA_LAUNCH_FAILURE", "moe-rows")
+    rc, _, _, _, res = run_rows(B, be, ops, job, x, logits)
+    monkeypatch.delenv("YVEX_TEST_CUDA_LAUNCH_FAILURE")
+    assert rc == B.BACKEND and res.completed == 0 and B._lib.yvex_backend_status_of(be.h) == 3
+    assert run_rows(B, be, ops, job, x, logits)[0] == B.STATE
+    be.close()
+
+
+def test_two_backends_on_two_devices(B):
+    """Kernels that opt in to more than 48 KiB of shared memory do so per device: a second backend on
+    another ordinal must run the same layer."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    spec, weights, router, x, logits = layer_inputs("small_logits")
+    outs = []
+    for dev in (b"cuda:0", b"cuda:1"):
+        be = B.Backend(device=dev)
+        assert be.rc == B.OK, be.message()
+        arena = B.ResidentArena(be, weights)
+        job = B.moe_job(arena, spec, router=False)
+        ops, _ = attach_workspace(B, be, job, x.shape[0])
+        rc, out, _, _, _ = run_rows(B, be, ops, job, x, logits)
+        assert rc == B.OK, be.message()
+        outs.append(out)
+        assert be.close() == B.OK
+    assert (outs[0].view(np.uint32) == outs[1].view(np.uint32)).all()

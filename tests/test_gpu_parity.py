@@ -119,6 +119,31 @@ def test_gemv_vs_oracle_shapes(L, port, qtype, rows, width):
     assert ok.all(), (np.abs(y - want).max(), int((~ok).sum()))
 
 
+@pytest.mark.parametrize("qtype,rows,width", [(synth.F32, 64, 4096), (synth.F16, 300, 1536), (synth.BF16, 37, 7168),
+                                              (synth.F32, 5, 96), (synth.F16, 1, 8), (synth.BF16, 129, 250)])
+def test_gemv_scalar_qtypes_vs_oracle(L, port, qtype, rows, width):
+    """F32 / F16 / BF16 rows (router weights and coefficient tensors are stored this way) on the
+    warp-per-row kernel, widths that are no multiple of 32 included."""
+    rng = np.random.default_rng(rows * 31 + width)
+    wf = (rng.standard_normal((rows, width)) * 0.02).astype(np.float32)
+    if qtype == synth.F32:
+        enc = wf.view(np.uint8)
+    elif qtype == synth.F16:
+        enc = wf.astype(np.float16).view(np.uint8)
+    else:
+        enc = synth.bf16_bits(wf).reshape(rows, width).view(np.uint8)
+    enc = np.ascontiguousarray(enc).reshape(rows, -1)
+    x = rng.standard_normal(width).astype(np.float32)
+    rc, want = port.matvec(qtype, enc, rows, width, x, threads=4)
+    rcd, dec = port.decode_rows(qtype, enc, rows, width)
+    st = L.Status()
+    out = L.dequant_rows(qtype, dev(enc), rows, width, st).cpu().numpy()
+    y = L.gemv(qtype, dev(enc), rows, width, dev(x), st).cpu().numpy()[0]
+    assert rc == 0 and rcd == 0 and st.read() == 0
+    assert (bits(out) == bits(dec)).all()
+    assert matvec_close(y, want, dec, x).all(), np.abs(y - want).max()
+
+
 @pytest.mark.parametrize("qtype", [synth.IQ2_XXS, synth.Q8_0])
 def test_gemv_input_rows_additive_and_bf16(L, port, qtype):
     rows, width = 40, 1024
@@ -205,6 +230,54 @@ def test_router_selection_identical_to_oracle(L, port, experts, topk, rows):
         assert rc == 0 and sel[r].tolist() == s0.tolist()
         assert np.abs(w[r] - w0).max() <= 2e-7
     assert st.read() == 0 and sel[0].tolist() == list(range(topk))
+
+
+# ---- expert worklist ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("rows,topk,experts", [(1, 6, 64), (62, 8, 256), (5, 3, 7), (300, 8, 256), (2048, 6, 64), (16384, 8, 256)])
+def test_expert_worklist_matches_the_reference_order(L, port, rows, topk, experts):
+    """The device sort against the reference builder's order (src/graph/worklist.c:369-441): buckets
+    ascending by expert, populated experts only, pairs ascending within a bucket, source row = pair /
+    topk, destination row = pair; and the summary the reference's device builder publishes
+    (src/backend/cuda/moe_kernels.cu:294-397). Narrow batches run the one-CTA kernel, wide ones the
+    count / plan / scatter kernels of the grouped-GEMM path itself."""
+    import torch
+    rng = np.random.default_rng(rows + experts)
+    sel = np.stack([rng.permutation(experts)[:topk] for _ in range(rows)]).astype(np.int32)
+    if rows > 4:
+        sel[sel == 3] = 4 if topk < experts - 1 else 3            # leave expert 3 (nearly) empty
+        sel = np.where((sel == 4) & (np.cumsum(sel == 4, axis=1) > 1), 3, sel).astype(np.int32)
+    st = L.Status()
+    tc_min, width = 4, 16
+    got = L.expert_worklist(torch.from_numpy(sel).cuda(), experts, st, tensor_core_minimum=tc_min, admitted_width=width,
+                            provenance=3 if rows > 62 else 2)
+    rc, order, src, be, bo, bc = port.worklist(sel.astype(np.uint64), experts)
+    assert rc == 0 and st.read() == 0
+    assert (got["order"] == order).all() and (got["source_rows"] == src).all() and (got["destination_rows"] == order).all()
+    assert (got["expert_ids"] == be).all() and (got["bucket_offsets"] == bo).all() and (got["bucket_populations"] == bc).all()
+    o = got["observation"]
+    pairs = rows * topk
+    assert (o.schema_version, o.worklist_count, o.pair_count, o.bucket_count) == (1, 1, pairs, len(be))
+    assert o.maximum_bucket_population == bc.max()
+    eligible = int(bc[bc >= tc_min].sum())
+    assert o.tensor_core_eligible_pairs == eligible and o.narrow_pairs == pairs - eligible and o.tensor_core_executed_pairs == 0
+    assert o.tail_rows == int(sum((width - n % width) % width for n in bc[bc >= tc_min]))
+    assert list(o.population_histogram) == np.bincount(np.minimum(bc, 16), minlength=17).tolist()
+    assert list(o.width_histogram) == [1 if i == min(rows, 16) else 0 for i in range(17)]
+    assert list(o.provenance_counts) == [1 if i == (3 if rows > 62 else 2) else 0 for i in range(5)]
+
+
+def test_expert_worklist_refuses_foreign_expert_ids(L):
+    import torch
+    st = L.Status()
+    sel = torch.tensor([[0, 1], [2, 9]], dtype=torch.int32, device="cuda")
+    L.expert_worklist(sel, 8, st)
+    assert st.read() == 2
+    st.reset()
+    big = torch.randint(0, 8, (4096, 2), dtype=torch.int32, device="cuda")
+    big[77, 1] = 8
+    L.expert_worklist(big, 8, st)
+    assert st.read() == 2
 
 
 # ---- MoE layer -------------------------------------------------------------------------------

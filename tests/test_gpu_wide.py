@@ -113,10 +113,29 @@ def test_expert_parallel_building_blocks_match_single_device_layer_bit_for_bit(L
     assert st.read() == 0 and torch.equal(out2.view(torch.int32), want.view(torch.int32))
 
 
+def tokens_covering_all_experts(sel, count):
+    """Indices of `count` rows of `sel` [T, k] chosen greedily so that every expert is selected by at least one."""
+    sel = np.asarray(sel)
+    need = set(np.unique(sel).tolist())
+    picked = []
+    for t in range(sel.shape[0]):
+        hit = need.intersection(sel[t].tolist())
+        if hit:
+            picked.append(t)
+            need -= hit
+        if not need:
+            break
+    rest = [t for t in range(sel.shape[0] - 1, -1, -1) if t not in set(picked)]
+    picked += rest[:max(0, count - len(picked))]
+    return np.array(sorted(picked[:max(count, len(picked))]), np.int64)
+
+
 def test_wide_matches_narrow_path_at_prefill_size(L, port):
     """Config-3 geometry (2048 tokens, hidden 4096, 64 experts top-6, inter 1536, IQ2_XXS + Q4_K):
     a sample of rows must agree with the narrow path run on those rows alone (rows are
-    independent), and a smaller sample with the CPU path."""
+    independent), and 64 rows that between them route to every one of the 64 experts must agree
+    with the CPU path (each expert's weight offsets and tile positions are then exercised)."""
+    import os
     import torch
     from yvex_b200.workloads import MoEWorkload
     wl = MoEWorkload("c3", 3)
@@ -130,19 +149,43 @@ def test_wide_matches_narrow_path_at_prefill_size(L, port):
     assert rel_l2(out[idx].cpu().numpy(), out_n.cpu().numpy()) <= 5e-4
     hw, _ = wl.host_copy()
     Lp = port.layer(wl.spec, hw, allow_q4k=True)
-    pick = idx[:4].cpu().numpy()
-    rc, want, sel0, _ = port.moe_tokens(Lp, x[idx[:4]].cpu().numpy(), logits=logits[idx[:4]].cpu().numpy(), threads=4)
-    assert rc == 0 and (sel[idx[:4]].cpu().numpy() == sel0).all()
-    assert rel_l2(out[idx[:4]].cpu().numpy(), want) <= 1e-3
-    assert pick.size == 4
+    pick = tokens_covering_all_experts(sel.cpu().numpy(), 64)
+    assert pick.size >= 64 and set(np.unique(sel.cpu().numpy()[pick]).tolist()) == set(range(64))
+    tp = torch.from_numpy(pick).cuda()
+    rc, want, sel0, _ = port.moe_tokens(Lp, x[tp].cpu().numpy(), logits=logits[tp].cpu().numpy(), threads=os.cpu_count() or 8)
+    assert rc == 0 and (sel[tp].cpu().numpy() == sel0).all()
+    got = out[tp].cpu().numpy()
+    assert rel_l2(got, want) <= 1e-3
+    per_token = np.linalg.norm(got - want, axis=1) / np.linalg.norm(want, axis=1)
+    assert per_token.max() <= 4e-3, per_token.max()
+
+
+def test_wide_config3_pinned_twin_vs_oracle(L, port):
+    """The same geometry with Q2_K down weights - the qtype the reference's own MoE path decodes - so
+    that the prefill path has a reference-pinned check at full size, on 64 rows covering all experts."""
+    import os
+    import torch
+    from yvex_b200.workloads import MoEWorkload
+    wl = MoEWorkload("c3", 3, down_qtype=synth.Q2_K)
+    x, logits = wl.tokens(2048)
+    st = L.Status()
+    out, sel, _ = L.moe_layer(L.geometry_of(wl.spec), L.weights_of(wl.tensors), x, st, logits=logits, wide=True)
+    hw, _ = wl.host_copy()
+    Lp = port.layer(wl.spec, hw)
+    pick = tokens_covering_all_experts(sel.cpu().numpy(), 64)
+    tp = torch.from_numpy(pick).cuda()
+    rc, want, sel0, _ = port.moe_tokens(Lp, x[tp].cpu().numpy(), logits=logits[tp].cpu().numpy(), threads=os.cpu_count() or 8)
+    assert rc == 0 and st.read() == 0 and (sel[tp].cpu().numpy() == sel0).all()
+    assert rel_l2(out[tp].cpu().numpy(), want) <= 1e-3
 
 
 def test_wide_config5_size_properties(L, port):
     """Config-5 geometry on one device (16 384 tokens, hidden 7168, 256 experts top-8 + shared, inter 2048,
     IQ2_XXS + Q4_K). Size-independent properties: rows are independent, so a permuted batch gives the
     permuted result bit for bit (other column blocks, other tiles, same per-row arithmetic) and a
-    sample of rows agrees with the decode path run on those rows alone; two rows are checked against
-    the CPU path within the layer tolerance."""
+    sample of rows agrees with the decode path run on those rows alone; 16 rows spread over the batch
+    are checked against the CPU path within the layer tolerance."""
+    import os
     import torch
     from yvex_b200.workloads import MoEWorkload
     wl = MoEWorkload("c5", 5)
@@ -163,10 +206,12 @@ def test_wide_config5_size_properties(L, port):
     assert rel_l2(out[idx].cpu().numpy(), out_n.cpu().numpy()) <= 5e-4
     hw, _ = wl.host_copy()
     Lp = port.layer(wl.spec, hw, allow_q4k=True)
-    two = idx[:2]
-    rc, want, sel0, _ = port.moe_tokens(Lp, x[two].cpu().numpy(), logits=logits[two].cpu().numpy(), threads=2)
-    assert rc == 0 and (sel[two].cpu().numpy() == sel0).all()
-    assert rel_l2(out[two].cpu().numpy(), want) <= 1e-3
+    some = torch.arange(16, device="cuda") * 1023 + 7                       # 16 rows across the batch: 128 pairs + 16 shared
+    rc, want, sel0, _ = port.moe_tokens(Lp, x[some].cpu().numpy(), logits=logits[some].cpu().numpy(), threads=min(16, os.cpu_count() or 8))
+    assert rc == 0 and (sel[some].cpu().numpy() == sel0).all()
+    got = out[some].cpu().numpy()
+    assert rel_l2(got, want) <= 1e-3
+    assert (np.linalg.norm(got - want, axis=1) / np.linalg.norm(want, axis=1)).max() <= 4e-3
 
 
 @pytest.mark.parametrize("world,tokens,topk,experts", [(8, 300, 8, 256), (2, 64, 6, 64), (4, 1, 4, 16)])

@@ -60,11 +60,19 @@ def test_static_scratch_matches_workspace_entry_twice_in_a_row(L):
     assert status.read() == 0
     for (_, _, _, _, _, want, out) in prepared:
         assert np.array_equal(out.cpu().numpy().view(np.uint32), want.cpu().numpy().view(np.uint32))
-    # and once more in the opposite order
-    for (q, k, v, pos, scale, want, out) in reversed(prepared):
+    # and once more in the opposite order; the set-up call is behind us, so these calls must leave the
+    # device's free memory and the tensor library's own pool exactly as they found them
+    for (_, _, _, _, _, _, out) in prepared:
         out.fill_(float("nan"))
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    pool_before = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for (q, k, v, pos, scale, want, out) in reversed(prepared):
         assert _run_static(L, torch, q, k, v, pos, scale, status, out) == 0
-        torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == pool_before
+    for (_, _, _, _, _, want, out) in prepared:
         assert np.array_equal(out.cpu().numpy().view(np.uint32), want.cpu().numpy().view(np.uint32))
     assert status.read() == 0
 

@@ -54,8 +54,17 @@ class LayerPlan(C.Structure):
                 ("normalize_topk_probabilities", C.c_int)]
 
 
+class WorklistObservation(C.Structure):
+    """yvex_expert_worklist_observation (include/yvex/internal/execution_batch.h:126-137)."""
+    _fields_ = [("schema_version", C.c_uint), ("worklist_count", ull), ("pair_count", ull), ("bucket_count", ull),
+                ("maximum_bucket_population", ull), ("tensor_core_eligible_pairs", ull), ("tensor_core_executed_pairs", ull),
+                ("narrow_pairs", ull), ("tail_rows", ull), ("width_histogram", ull * 17), ("population_histogram", ull * 17),
+                ("provenance_counts", ull * 5)]
+
+
 class CompletionSlot(C.Structure):
-    _fields_ = [("status", C.c_int), ("pending", C.c_int), ("row_count", ull), ("row_expert_pairs", ull)]
+    _fields_ = [("status", C.c_int), ("pending", C.c_int), ("row_count", ull), ("row_expert_pairs", ull),
+                ("worklist", WorklistObservation)]
 
 
 class Completion(C.Structure):
@@ -86,7 +95,9 @@ class RowBatchResult(C.Structure):
         (n, ull) for n in ("row_count", "row_expert_pairs", "grouped_expert_operations", "shared_expert_operations",
                            "expert_subviews_accessed", "encoded_bytes_read", "h2d_bytes", "d2h_bytes", "d2d_bytes",
                            "kernel_launches", "tensor_core_launches", "stream_synchronizations", "active_weight_base_bytes",
-                           "active_weight_per_unique_expert_bytes", "activation_bytes", "temporary_bytes")]
+                           "active_weight_per_unique_expert_bytes", "activation_bytes", "temporary_bytes",
+                           "unique_experts", "upload_count", "download_count", "active_weight_bytes", "pipeline_chunks")] + [
+        ("worklists", WorklistObservation)]
 
 
 _EXEC = C.CFUNCTYPE(C.c_int, vp, C.POINTER(LayerJob), C.POINTER(RowBatch), C.POINTER(RowBatchOutput), C.POINTER(RowBatchResult),
@@ -132,6 +143,7 @@ _lib.yvex_backend_attention_gqa_decode.argtypes = [vp] + [C.POINTER(DeviceTensor
                                                                                                     C.POINTER(DeviceTensor),
                                                                                                     C.POINTER(Error)]
 _lib.yvex_backend_op_matmul.argtypes = [vp] + [C.POINTER(DeviceTensor)] * 3 + [C.POINTER(Error)]
+_lib.yvex_backend_selftest_bounded_wait.argtypes = [vp, ull, C.POINTER(ull), C.POINTER(Error)]
 _lib.yvex_status_name.restype = C.c_char_p
 
 

@@ -3,6 +3,7 @@
 #include <atomic>
 
 #include "qtype_decode.cuh"
+#include "tcgen05.cuh"
 
 namespace yb {
 
@@ -18,6 +19,24 @@ int launch_status(int launches) {
 void mark_phase(int phase, cudaStream_t s) {
     if (g_phase_events && phase < g_phase_count && g_phase_events[phase])
         cudaEventRecord(static_cast<cudaEvent_t>(g_phase_events[phase]), s);
+}
+
+// One warp; lane 0 waits for a phase that never completes.
+__global__ void selftest_wait_kernel(uint64_t limit_ns, uint64_t *elapsed_ns, int *status) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        sm100::mbar_init(&bar, 1);
+        abort_flag = 0;
+        sm100::fence_barrier_init();
+    }
+    __syncwarp();
+    const uint64_t t0 = sm100::global_ns();
+    const bool done = sm100::mbar_wait_warp(&bar, 0u, &abort_flag, limit_ns);
+    if (threadIdx.x == 0) {
+        if (elapsed_ns) *elapsed_ns = sm100::global_ns() - t0;
+        if (!done) raise(status, YVEX_B200_STATUS_TIMEOUT);
+    }
 }
 
 }  // namespace yb
@@ -44,4 +63,10 @@ extern "C" int yvex_b200_phase_events(void **events, int count) {
     g_phase_events = count ? events : nullptr;
     g_phase_count = count;
     return OK;
+}
+
+extern "C" int yvex_b200_selftest_bounded_wait(uint64_t limit_ns, uint64_t *elapsed_ns, int *status, void *stream) {
+    if (!status || !limit_ns || limit_ns > 5000000000ull) return ERR_INVALID_ARG;
+    selftest_wait_kernel<<<1, 32, 0, as_stream(stream)>>>(limit_ns, elapsed_ns, status);
+    return launch_status(1);
 }

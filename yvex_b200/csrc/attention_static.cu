@@ -16,6 +16,8 @@
 //     any stream capture begins; later calls only launch kernels;
 //   * nothing in the array has to start at zero: every (session, kv head, split) slot is written
 //     by the first kernel of a call before the merge kernel of the same call reads it;
+//   * the array used is that of the device that is CURRENT in the calling thread; `stream` must be a
+//     stream of that same device (the call does not check the pairing);
 //   * there is ONE array per device. Two calls that overlap in time on the same device (different
 //     streams, threads or processes sharing the context) race on it; callers serialise them.
 #include <cuda_runtime.h>

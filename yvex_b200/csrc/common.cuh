@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/yvex_b200_kernels.h"
 
 namespace yb {
@@ -77,6 +79,22 @@ inline cudaError_t launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, 
     cfg.attrs = &attr; cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
 }
+
+// A kernel's opt-in to more than 48 KiB of dynamic shared memory is a per-DEVICE attribute of the
+// function. One of these sits beside each such kernel's launch code and remembers, per device
+// ordinal, that the attribute has been set; devices beyond the table set it on every launch.
+struct SmemOptIn {
+    static constexpr int kDevices = 64;
+    std::atomic<int> bytes[kDevices];
+    template <class Kernel> int ensure(Kernel kernel, int want) {
+        int dev = -1;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return ERR_BACKEND;
+        if (dev < kDevices && bytes[dev].load(std::memory_order_acquire) >= want) return OK;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, want) != cudaSuccess) return ERR_BACKEND;
+        if (dev < kDevices) bytes[dev].store(want, std::memory_order_release);
+        return OK;
+    }
+};
 
 // Adds `launches` to the library's kernel-launch counter and reports a failed enqueue.
 int launch_status(int launches = 1);

@@ -94,13 +94,14 @@ gemv_q8_0_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row
         mbar_expect_tx(&ctl->full[n % kQ8Depth], bytes);
         bulk_load(ring + (n % kQ8Depth) * stage_bytes, enc + row0 * row_bytes, bytes, &ctl->full[n % kQ8Depth]);
     };
+    uint64_t issued = 0, done = 0;                                         // thread 0: stages requested / consumed
     // programmatic dependent launch, as in gemv_mma_kernel: only the encoded rows are touched before the wait
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (threadIdx.x == 0) {
         for (int i = 0; i < kQ8Depth; ++i) { mbar_init(&ctl->full[i], 1); mbar_init(&ctl->empty[i], kQ8Warps); }
         ctl->abort = 0;
         fence_barrier_init();
-        for (uint64_t n = 0; n < mine && n < (uint64_t)kQ8Depth; ++n) issue(n);
+        for (uint64_t n = 0; n < mine && n < (uint64_t)kQ8Depth; ++n) { issue(n); issued = n + 1; }
     }
     // the activation row goes to shared memory while the first stages are in flight
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -112,7 +113,10 @@ gemv_q8_0_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row
     bool bad = false;
     for (uint64_t n = 0; n < mine; ++n) {
         const uint32_t slot = (uint32_t)(n % kQ8Depth), ph = (uint32_t)((n / kQ8Depth) & 1u);
-        if (!mbar_wait(&ctl->full[slot], ph, &ctl->abort)) break;
+        // Every thread of the CTA takes the same way out: a warp that left alone would leave its row
+        // partner at the pair barrier below, and lanes that left alone would break the warp shuffles.
+        const bool landed = mbar_wait(&ctl->full[slot], ph, &ctl->abort) && !ctl->abort;
+        if (!__syncthreads_and(landed)) break;
         const uint64_t r = (blockIdx.x + n * gridDim.x) * kQ8Rows + rw;
         if (r < rows) {                                                       // uniform over the row's warp pair
             const uint32_t *row = reinterpret_cast<const uint32_t *>(ring + slot * stage_bytes + rw * row_bytes);
@@ -161,9 +165,16 @@ gemv_q8_0_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl->empty[slot]);
         if (threadIdx.x == 0 && n + kQ8Depth < mine) {
-            if (!mbar_wait(&ctl->empty[slot], ph, &ctl->abort)) break;     // every warp is done with the stage
-            issue(n + kQ8Depth);
+            // every warp is done with the stage; when this wait runs out the abort flag is up and the
+            // whole CTA leaves together at the top of the next iteration
+            if (mbar_wait(&ctl->empty[slot], ph, &ctl->abort)) { issue(n + kQ8Depth); issued = n + kQ8Depth + 1; }
         }
+        done = n + 1;
+    }
+    if (threadIdx.x == 0 && ctl->abort) {
+        // copies still in flight land in this CTA's shared memory: give them a bounded time to finish
+        int ignore = 0;
+        for (uint64_t m = done; m < issued; ++m) mbar_wait(&ctl->full[m % kQ8Depth], (uint32_t)((m / kQ8Depth) & 1u), &ignore);
     }
     if (bad) raise(status, YVEX_B200_STATUS_NUMERIC);
     if (lane == 0 && ctl->abort) raise(status, YVEX_B200_STATUS_TIMEOUT);
@@ -184,12 +195,8 @@ static int gemv_q8_0_launch(const uint8_t *enc, uint64_t rows, uint64_t width, u
                             uint64_t input_rows, const float *additive, float *out, int round_bf16, int *status,
                             cudaStream_t s) {
     const size_t smem = q8_smem_bytes(width, row_bytes);
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(gemv_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
-            return ERR_BACKEND;
-        configured = true;
-    }
+    static SmemOptIn opt_in;
+    if (opt_in.ensure(gemv_q8_0_kernel, 200 * 1024) != OK) return ERR_BACKEND;
     const uint64_t groups = (rows + kQ8Warps - 1) / kQ8Warps, per_sm = (227 * 1024) / (smem + 1024);
     const uint64_t cap = (uint64_t)kSmCount * (per_sm < 1 ? 1 : per_sm > 2 ? 2 : per_sm);
     cudaLaunchConfig_t cfg{};

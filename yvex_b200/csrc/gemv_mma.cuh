@@ -568,10 +568,6 @@ inline int ctas_per_sm(size_t smem, int threads) {
     return n < 1 ? 1 : n > 4 ? 4 : n;
 }
 
-template <class Kernel> inline int mma_opt_in(Kernel kernel) {
-    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess
-               ? OK : ERR_BACKEND;
-}
 
 template <class Dec>
 inline int gemv_mma_launch_t(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row_bytes,
@@ -583,11 +579,8 @@ inline int gemv_mma_launch_t(const uint8_t *enc, uint64_t rows, uint64_t width, 
     p.x = x; p.additive = additive; p.out = out; p.round_bf16 = round_bf16; p.status = status;
     const int warps = p.slices * p.row_groups;
     const size_t smem = ((gemv_smem_fixed(p.K, warps) + 15) & ~(size_t)15) + (size_t)warps * UnitGeom<Dec>::kRingBytes;
-    static bool configured = false;
-    if (!configured) {
-        if (mma_opt_in(gemv_mma_kernel<Dec>) != OK) return ERR_BACKEND;
-        configured = true;
-    }
+    static SmemOptIn opt_in;
+    if (opt_in.ensure(gemv_mma_kernel<Dec>, 200 * 1024) != OK) return ERR_BACKEND;
     if (smem > 200 * 1024 || warps > 16 || input_rows > 65535) return ERR_BOUNDS;
     const uint64_t ctasks = ((rows + 7) / 8 + p.row_groups - 1) / p.row_groups;
     const uint64_t cap = (uint64_t)kSmCount * ctas_per_sm(smem, 32 * warps);

@@ -448,7 +448,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
                             const uint4 *src = reinterpret_cast<const uint4 *>(p.sums + ((uint64_t)(cb.row0 + r) * nsb + sb) * 32);
                             v[i] = r < cb.ncols ? __ldg(src + part) : make_uint4(0, 0, 0, 0);
                         }
-                        if (base == 0 && !mbar_wait(&sm->min_empty[buf], bph ^ 1u, abort)) goto done;
+                        if (base == 0 && !mbar_wait_warp(&sm->min_empty[buf], bph ^ 1u, abort)) goto done;
 #pragma unroll
                         for (int i = 0; i < kBatch; ++i)
                             *reinterpret_cast<uint4 *>(tile + sw128_offset(rsub + (base + i) * kRowsPerPass, 4 + part)) = v[i];
@@ -472,7 +472,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
         for (long long tile = 0; tile < my_tiles && !*abort; ++tile) {
             for (int sb = 0; sb < nsb; ++sb, ++sb_it) {
                 const uint32_t rs = sb_it % kRawStages, rph = (sb_it / kRawStages) & 1u;
-                if (!mbar_wait(&sm->raw_full[rs], rph, abort)) goto done;
+                if (!mbar_wait_warp(&sm->raw_full[rs], rph, abort)) goto done;
                 const uint32_t off = (x_row + (uint32_t)sb * Dec::kBlockBytes) & 15u, mis = off & 3u;
                 const uint32_t *raw = reinterpret_cast<const uint32_t *>(raw_stage + rs * Plan::kRawStageBytes + slot + (off & ~3u));
                 if (h == 0) {
@@ -485,7 +485,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const uint32_t it = 4u * sb_it + c, s = stage_of(it), ph = phase_of(it);
-                    if (!mbar_wait(&sm->empty[s], ph ^ 1u, abort)) goto done;
+                    if (!mbar_wait_warp(&sm->empty[s], ph ^ 1u, abort)) goto done;
 #pragma unroll
                     for (int q = 0; q < Plan::kPartsPerThread; ++q)
                         Dec::store(raw, mis, c, h * Plan::kPartsPerThread + q, a_tiles + s * kTileBytes, row, tab);
@@ -495,7 +495,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
                 }
                 if (kHasMin) {
                     const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
-                    if (!mbar_wait(&sm->min_empty[buf], bph ^ 1u, abort)) goto done;
+                    if (!mbar_wait_warp(&sm->min_empty[buf], bph ^ 1u, abort)) goto done;
                     if (h < 2) Dec::mins(raw, h, min_tiles + buf * kTileBytes, row);
                     fence_proxy_async();
                     __syncwarp();
@@ -521,7 +521,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
             const int ncols_here = cb.ncols - kCols * colhalf;    // columns this warp owns that are real
             for (int sb = 0; sb < nsb; ++sb, ++sb_it) {
                 const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
-                if (!mbar_wait(&sm->acc_full[buf], bph, abort)) goto done;
+                if (!mbar_wait_warp(&sm->acc_full[buf], bph, abort)) goto done;
                 tc_fence_after();
                 // written by the row's producer before its last chunk of this superblock was published
                 float d, dmin = 0.0f;

@@ -270,11 +270,8 @@ static int launch_gate_up(NarrowParams &p, cudaStream_t s) {
     const int warps = 2 * p.slices;
     const int K = (int)p.g.hidden;
     const size_t smem = narrow_smem_fixed(K, K / 16, warps) + (size_t)warps * UnitGeom<Dec>::kRingBytes;
-    static bool configured = false;
-    if (!configured) {
-        if (mma_opt_in(moe_gate_up_mma_kernel<Dec>) != OK) return ERR_BACKEND;
-        configured = true;
-    }
+    static SmemOptIn opt_in;
+    if (opt_in.ensure(moe_gate_up_mma_kernel<Dec>, 200 * 1024) != OK) return ERR_BACKEND;
     if (smem > 200 * 1024 || warps > 16 || p.rows > 65535) return ERR_BOUNDS;
     const uint64_t imax = p.g.inter > p.g.shared_inter ? p.g.inter : p.g.shared_inter;
     const uint64_t tasks = (p.g.topk + 1) * ((imax + 7) / 8);
@@ -295,11 +292,8 @@ static int launch_down(NarrowParams &p, cudaStream_t s) {
     int warps = ppr < 8 ? ppr : 8;
     while (warps > 1 && down_smem<Dec>(p, warps) > 200 * 1024) --warps;
     const size_t smem = down_smem<Dec>(p, warps);
-    static bool configured = false;
-    if (!configured) {
-        if (mma_opt_in(moe_down_mma_kernel<Dec>) != OK) return ERR_BACKEND;
-        configured = true;
-    }
+    static SmemOptIn opt_in;
+    if (opt_in.ensure(moe_down_mma_kernel<Dec>, 200 * 1024) != OK) return ERR_BACKEND;
     if (smem > 200 * 1024 || p.rows > 65535) return ERR_BOUNDS;
     p.down_warps = warps;
     const uint64_t tasks = (p.g.hidden + 7) / 8;

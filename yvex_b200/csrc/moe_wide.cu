@@ -295,12 +295,8 @@ static int fuse_of(uint64_t row_bytes) {
 template <class Dec>
 static int launch_gemm(const GemmMaps &map, const GemmParams &p, cudaStream_t s) {
     const size_t smem = GemmPlan<Dec>::kBytes;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(moe_grouped_gemm_kernel<Dec>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return ERR_BACKEND;
-        configured = true;
-    }
+    static SmemOptIn opt_in;
+    if (opt_in.ensure(moe_grouped_gemm_kernel<Dec>, (int)smem) != OK) return ERR_BACKEND;
     moe_grouped_gemm_kernel<Dec><<<kSmCount, GemmPlan<Dec>::kThreads, smem, s>>>(map, p);
     return launch_status(1);
 }
@@ -447,6 +443,12 @@ extern "C" int yvex_b200_moe_wide(const yvex_b200_moe_geometry *geom, const yvex
     return launch_status(0);
 }
 
+extern "C" int yvex_b200_moe_wide_uses_gemm(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w) {
+    return g && w && moe_check_geometry(g, w) == OK && moe_wide_gemm_eligible(*g, *w) ? 1 : 0;
+}
+
+extern "C" uint64_t yvex_b200_moe_wide_tile_columns(unsigned int qtype) { return gemm_qtype(qtype) ? (uint64_t)gemm_tile_n(qtype) : 0; }
+
 extern "C" uint64_t yvex_b200_moe_wide_workspace_bytes(const yvex_b200_moe_geometry *g, uint64_t rows) {
     return g ? moe_wide_workspace_bytes(*g, rows) : 0;
 }
@@ -480,6 +482,119 @@ extern "C" int yvex_b200_moe_expert_rows(const yvex_b200_moe_geometry *geom, con
     if (rc != OK) return rc;
     mark_phase(5, s);
     return launch_status(1);
+}
+
+// ---- expert worklist as a result of its own (src/graph/worklist.c:369-441) ------------------------------
+// Compact bucket list and the pointer-free observation from the per-expert counts and first rows
+// (one thread: at most 256 experts). Same arithmetic as yvex_expert_worklist_build and the summary
+// of its device twin (src/backend/cuda/moe_kernels.cu:294-397).
+__global__ void worklist_observe_kernel(const int *counts, const int *offsets, int experts, uint64_t pairs, uint64_t rows,
+                                        uint64_t tc_min, uint64_t width, unsigned provenance, yvex_b200_worklist_observation *obs,
+                                        int32_t *expert_ids, int32_t *bucket_offsets, int32_t *bucket_populations, int *status) {
+    if (threadIdx.x || blockIdx.x) return;
+    yvex_b200_worklist_observation o;
+    memset(&o, 0, sizeof(o));
+    o.schema_version = 1u;
+    o.worklist_count = 1ull;
+    o.pair_count = pairs;
+    o.width_histogram[rows < YVEX_B200_WORKLIST_HISTOGRAM_CAP ? rows : YVEX_B200_WORKLIST_HISTOGRAM_CAP - 1u] = 1ull;
+    o.provenance_counts[provenance] = 1ull;
+    uint64_t emitted = 0, unique = 0;
+    for (int e = 0; e < experts; ++e) {
+        const uint64_t n = (uint64_t)counts[e];
+        if (!n) continue;
+        if (expert_ids) expert_ids[unique] = e;
+        if (bucket_offsets) bucket_offsets[unique] = offsets[e];
+        if (bucket_populations) bucket_populations[unique] = (int32_t)n;
+        if (n > o.maximum_bucket_population) o.maximum_bucket_population = n;
+        o.population_histogram[n < YVEX_B200_WORKLIST_HISTOGRAM_CAP ? n : YVEX_B200_WORKLIST_HISTOGRAM_CAP - 1u]++;
+        if (tc_min && n >= tc_min) {
+            o.tensor_core_eligible_pairs += n;
+            if (n % width) o.tail_rows += width - n % width;
+        } else {
+            o.narrow_pairs += n;
+        }
+        emitted += n;
+        ++unique;
+    }
+    if (bucket_offsets) bucket_offsets[unique] = (int32_t)emitted;
+    o.bucket_count = unique;
+    if (emitted != pairs) raise(status, YVEX_B200_STATUS_ARGUMENT);
+    if (obs) *obs = o;
+}
+
+__global__ void worklist_rows_kernel(const int *order, uint64_t pairs, uint64_t topk, int32_t *source_rows, int32_t *destination_rows) {
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < pairs; i += (uint64_t)gridDim.x * blockDim.x) {
+        const int p = order[i];
+        if (source_rows) source_rows[i] = (int32_t)(p / topk);
+        if (destination_rows) destination_rows[i] = p;
+    }
+}
+
+// The whole worklist of a narrow batch in one CTA (pairs <= kSmallWorklistPairs): shared-memory
+// counts, a serial scan over the experts, and the reference's stable emission (thread e walks
+// the pairs in order and emits those of expert e).
+constexpr int kSmallWorklistPairs = 2048;
+__global__ void __launch_bounds__(256)
+worklist_small_kernel(const int32_t *selected, uint64_t rows, uint64_t topk, int experts, uint64_t tc_min, uint64_t width,
+                      unsigned provenance, int32_t *order, int32_t *source_rows, int32_t *destination_rows, int32_t *expert_ids,
+                      int32_t *bucket_offsets, int32_t *bucket_populations, yvex_b200_worklist_observation *obs, int *status) {
+    __shared__ int counts[257], offsets[257], bad;
+    const int pairs = (int)(rows * topk);
+    for (int e = threadIdx.x; e <= 256; e += blockDim.x) counts[e] = 0;
+    if (threadIdx.x == 0) bad = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = selected[p];
+        if (e < 0 || e >= experts) bad = 1; else atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (bad) { if (threadIdx.x == 0) raise(status, YVEX_B200_STATUS_ARGUMENT); return; }
+    if (threadIdx.x == 0) {
+        int off = 0;
+        for (int e = 0; e < experts; ++e) { offsets[e] = off; off += counts[e]; }
+        offsets[experts] = off;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        yvex_b200_worklist_observation o;
+        memset(&o, 0, sizeof(o));
+        o.schema_version = 1u; o.worklist_count = 1ull; o.pair_count = (uint64_t)pairs;
+        o.width_histogram[rows < YVEX_B200_WORKLIST_HISTOGRAM_CAP ? rows : YVEX_B200_WORKLIST_HISTOGRAM_CAP - 1u] = 1ull;
+        o.provenance_counts[provenance] = 1ull;
+        uint64_t unique = 0;
+        for (int e = 0; e < experts; ++e) {
+            const uint64_t n = (uint64_t)counts[e];
+            if (!n) continue;
+            if (expert_ids) expert_ids[unique] = e;
+            if (bucket_offsets) bucket_offsets[unique] = offsets[e];
+            if (bucket_populations) bucket_populations[unique] = (int32_t)n;
+            if (n > o.maximum_bucket_population) o.maximum_bucket_population = n;
+            o.population_histogram[n < YVEX_B200_WORKLIST_HISTOGRAM_CAP ? n : YVEX_B200_WORKLIST_HISTOGRAM_CAP - 1u]++;
+            if (tc_min && n >= tc_min) {
+                o.tensor_core_eligible_pairs += n;
+                if (n % width) o.tail_rows += width - n % width;
+            } else {
+                o.narrow_pairs += n;
+            }
+            ++unique;
+        }
+        if (bucket_offsets) bucket_offsets[unique] = offsets[experts];
+        o.bucket_count = unique;
+        if (obs) *obs = o;
+    }
+    if (!order && !source_rows && !destination_rows) return;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        int cursor = offsets[e];
+        if (!counts[e]) continue;
+        for (int p = 0; p < pairs; ++p)
+            if (selected[p] == e) {
+                if (order) order[cursor] = p;
+                if (source_rows) source_rows[cursor] = (int32_t)(p / (int)topk);
+                if (destination_rows) destination_rows[cursor] = p;
+                ++cursor;
+            }
+    }
 }
 
 // ---- expert-parallel dispatch plan -----------------------------------------------------------------
@@ -542,6 +657,54 @@ extern "C" int yvex_b200_ep_dispatch(const int32_t *selected, const float *weigh
     wide_gather_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(static_cast<const __half *>(rows_f16), order, src, pairs, hidden,
                                                               static_cast<__half *>(send_rows_f16));
     return launch_status(5);
+}
+
+extern "C" uint64_t yvex_b200_expert_worklist_workspace_bytes(uint64_t pairs, uint64_t experts) {
+    const uint64_t blocks = pairs / 128 + experts + 2;
+    return 256 * 8 + (2 * experts + 8) * 4 + 2 * pairs * 4 + 2 * blocks * sizeof(ColBlock) + 64;
+}
+
+extern "C" int yvex_b200_expert_worklist(const int32_t *selected, uint64_t rows, uint64_t topk, uint64_t experts,
+                                         uint64_t tensor_core_minimum, uint64_t admitted_width, unsigned int provenance,
+                                         int32_t *source_pairs, int32_t *source_rows, int32_t *destination_rows,
+                                         int32_t *expert_ids, int32_t *bucket_offsets, int32_t *bucket_populations,
+                                         yvex_b200_worklist_observation *observation, void *workspace,
+                                         uint64_t workspace_bytes, int *status, void *stream) {
+    if (!selected || !status || !rows || !topk || !experts || experts > 256 || topk > experts || !admitted_width ||
+        provenance >= YVEX_B200_WORKLIST_PROVENANCE_COUNT)
+        return ERR_INVALID_ARG;
+    if (rows > 0x7fffff00ull / topk) return ERR_BOUNDS;
+    const uint64_t pairs = rows * topk;
+    cudaStream_t s = as_stream(stream);
+    if (pairs <= (uint64_t)kSmallWorklistPairs) {
+        worklist_small_kernel<<<1, 256, 0, s>>>(selected, rows, topk, (int)experts, tensor_core_minimum, admitted_width, provenance,
+                                                source_pairs, source_rows, destination_rows, expert_ids, bucket_offsets,
+                                                bucket_populations, observation, status);
+        return launch_status(1);
+    }
+    if (!workspace || workspace_bytes < yvex_b200_expert_worklist_workspace_bytes(pairs, experts)) return ERR_NOMEM;
+    // the sort of the wide path itself: count, plan (offsets), stable scatter
+    uint8_t *base = static_cast<uint8_t *>(workspace);
+    auto take = [&](uint64_t bytes) { uint8_t *at = base; base += (bytes + 255) & ~255ull; return at; };
+    const int max_blocks = (int)(pairs / 128 + experts + 2);
+    int *counts = reinterpret_cast<int *>(take((experts + 2) * 4)), *offsets = reinterpret_cast<int *>(take((experts + 3) * 4));
+    int *num_blocks = reinterpret_cast<int *>(take(8));
+    int *order = source_pairs ? source_pairs : reinterpret_cast<int *>(take(pairs * 4));
+    int *pos = reinterpret_cast<int *>(take(pairs * 4));
+    ColBlock *b0 = reinterpret_cast<ColBlock *>(take((uint64_t)max_blocks * sizeof(ColBlock)));
+    ColBlock *b1 = reinterpret_cast<ColBlock *>(take((uint64_t)max_blocks * sizeof(ColBlock)));
+    cudaMemsetAsync(counts, 0, (experts + 2) * 4, s);
+    wide_count_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(selected, pairs, (int)experts + 1, counts, status);
+    wide_plan_kernel<<<2, 32, 0, s>>>(counts, (int)experts, pairs, offsets, b0, b1, num_blocks, max_blocks, 256, 128, status);
+    worklist_observe_kernel<<<1, 32, 0, s>>>(counts, offsets, (int)experts, pairs, rows, tensor_core_minimum, admitted_width, provenance,
+                                             observation, expert_ids, bucket_offsets, bucket_populations, status);
+    int launches = 3;
+    if (source_pairs || source_rows || destination_rows) {
+        wide_scatter_kernel<<<(unsigned)experts + 1, 512, 0, s>>>(selected, pairs, offsets, order, pos);
+        worklist_rows_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(order, pairs, topk, source_rows, destination_rows);
+        launches += 2;
+    }
+    return launch_status(launches);
 }
 
 extern "C" int yvex_b200_moe_combine_indexed(const void *y_routed_bf16, const int32_t *routed_rows, const void *y_shared_bf16,

@@ -9,7 +9,16 @@
 namespace yb {
 namespace sm100 {
 
-constexpr uint32_t kSpinLimit = 1u << 22;     // bounded waits: ~seconds, then the kernel gives up
+// Bounded waits: a wait gives up once this much time has passed on the device's nanosecond clock
+// (%globaltimer), whatever a single poll costs; the poll count is only a backstop.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+constexpr uint32_t kSpinLimit = 1u << 30;
+
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -37,15 +46,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Waits for the phase with the given parity to complete. Gives up after kSpinLimit polls (or as
-// soon as another thread of the CTA gave up), raising `abort` so every role unwinds.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+// Waits for the phase with the given parity to complete. Gives up after `limit_ns` (or as soon as
+// another thread of the CTA gave up), raising `abort` so every role unwinds.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort,
+                                          uint64_t limit_ns = kWaitLimitNs) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    for (uint32_t i = 1; i < kSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *abort) return false;
+        if ((i & 63u) == 0u) {
+            if (*abort) return false;
+            if (global_ns() - t0 > limit_ns) break;
+        }
     }
     *abort = 1;
     return false;
+}
+
+// The same wait for a whole warp: every lane waits, and all 32 lanes get the same answer, so a warp
+// never splits between lanes that saw the phase complete and lanes that gave up (the code after
+// such waits uses warp-wide synchronising instructions).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, volatile int *abort,
+                                               uint64_t limit_ns = kWaitLimitNs) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort, limit_ns)) != 0;
 }
 
 // generic-proxy writes (st.shared) -> visible to the async proxy (UMMA / TMA reads)

@@ -61,6 +61,24 @@ int yvex_backend_fail(yvex_backend *backend, const char *where, yvex_error *err)
     return yvex_refuse(err, YVEX_ERR_BACKEND, where, "CUDA call failed; backend demoted to FAILED");
 }
 
+int yvex_test_seam(const char *name, const char *value) {
+    const char *v = getenv(name);
+    return v && !strcmp(v, value);
+}
+
+/* Creates (or destroys) the events of the copy pipeline; 1 on success. */
+static int backend_events(yvex_backend *b, int create) {
+    cudaEvent_t *all[2 + 2 * YVEX_MOE_MAX_CHUNKS];
+    int n = 0, ok = 1;
+    all[n++] = &b->ev_begin; all[n++] = &b->ev_end;
+    for (int i = 0; i < YVEX_MOE_MAX_CHUNKS; ++i) { all[n++] = &b->ev_in[i]; all[n++] = &b->ev_done[i]; }
+    for (int i = 0; i < n; ++i) {
+        if (create) ok &= cudaEventCreateWithFlags(all[i], cudaEventDisableTiming) == cudaSuccess;
+        else if (*all[i]) { ok &= cudaEventDestroy(*all[i]) == cudaSuccess; *all[i] = NULL; }
+    }
+    return ok;
+}
+
 int yvex_backend_open(yvex_backend **out, const yvex_backend_options *options, yvex_error *err) {
     int device = 0, count = 0;
     yvex_backend *b;
@@ -83,9 +101,11 @@ int yvex_backend_open(yvex_backend **out, const yvex_backend_options *options, y
     b->next_owner_id = 1;
     atomic_init(&b->status, YVEX_BACKEND_STATUS_READY);
     if (cudaSetDevice(device) != cudaSuccess || cudaStreamCreateWithFlags(&b->stream, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaMalloc((void **)&b->status_word, 256) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&b->copy_in, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&b->copy_out, cudaStreamNonBlocking) != cudaSuccess || !backend_events(b, 1) ||
+        cudaMalloc((void **)&b->status_word, YVEX_DEVICE_STATE_BYTES) != cudaSuccess ||
         cudaMallocHost((void **)&b->host_scratch, YVEX_HOST_SCRATCH_BYTES) != cudaSuccess ||
-        cudaMemsetAsync(b->status_word, 0, 256, b->stream) != cudaSuccess) {
+        cudaMemsetAsync(b->status_word, 0, YVEX_DEVICE_STATE_BYTES, b->stream) != cudaSuccess) {
         cudaGetLastError();
         yvex_backend_close(b);
         return yvex_refuse(err, YVEX_ERR_BACKEND, "yvex_backend_open", "CUDA context, stream or status word unavailable");
@@ -109,6 +129,9 @@ int yvex_backend_close_checked(yvex_backend **backend, yvex_error *err) {
     }
     if (b->status_word) ok &= cudaFree(b->status_word) == cudaSuccess;
     if (b->host_scratch) ok &= cudaFreeHost(b->host_scratch) == cudaSuccess;
+    ok &= backend_events(b, 0);
+    if (b->copy_in) ok &= cudaStreamDestroy(b->copy_in) == cudaSuccess;
+    if (b->copy_out) ok &= cudaStreamDestroy(b->copy_out) == cudaSuccess;
     if (b->stream) ok &= cudaStreamDestroy(b->stream) == cudaSuccess;
     free(b);
     *backend = NULL;
@@ -120,7 +143,11 @@ int yvex_backend_close_checked(yvex_backend **backend, yvex_error *err) {
 void yvex_backend_close(yvex_backend *backend) {
     if (!backend) return;
     cudaSetDevice(backend->device);
-    if (backend->stream) { cudaStreamSynchronize(backend->stream); cudaStreamDestroy(backend->stream); }
+    if (backend->stream) cudaStreamSynchronize(backend->stream);
+    backend_events(backend, 0);
+    if (backend->copy_in) { cudaStreamSynchronize(backend->copy_in); cudaStreamDestroy(backend->copy_in); }
+    if (backend->copy_out) { cudaStreamSynchronize(backend->copy_out); cudaStreamDestroy(backend->copy_out); }
+    if (backend->stream) cudaStreamDestroy(backend->stream);
     if (backend->status_word) cudaFree(backend->status_word);
     if (backend->host_scratch) cudaFreeHost(backend->host_scratch);
     cudaGetLastError();
@@ -380,6 +407,26 @@ int yvex_backend_take_status(yvex_backend *backend, int *code) {
     return 1;
 }
 
+int yvex_backend_selftest_bounded_wait(yvex_backend *backend, unsigned long long limit_ns, unsigned long long *elapsed_ns,
+                                       yvex_error *err) {
+    const char *where = "cuda.selftest.bounded-wait";
+    unsigned long long *dev_elapsed, *host_elapsed;
+    int rc = yvex_backend_admit(backend, where, err), code;
+    if (elapsed_ns) *elapsed_ns = 0ull;
+    if (rc != YVEX_OK) return rc;
+    dev_elapsed = (unsigned long long *)((unsigned char *)backend->status_word + 64);
+    host_elapsed = (unsigned long long *)(backend->host_scratch + 64);
+    rc = yvex_b200_selftest_bounded_wait(limit_ns, (uint64_t *)dev_elapsed, backend->status_word, backend->stream);
+    if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
+    if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "limit must be between 1 ns and 5 s");
+    if (cudaMemcpyAsync(host_elapsed, dev_elapsed, sizeof(*host_elapsed), cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess ||
+        !yvex_backend_take_status(backend, &code))
+        return yvex_backend_fail(backend, where, err);
+    if (elapsed_ns) *elapsed_ns = *host_elapsed;
+    if (code == YVEX_B200_STATUS_TIMEOUT) return yvex_refuse(err, YVEX_ERR_TIMEOUT, where, "a bounded device wait expired");
+    return yvex_refuse(err, YVEX_ERR_BACKEND, where, "the wait did not expire or reported another status");
+}
+
 /* ---- encoded matvec -------------------------------------------------------------------------------- */
 
 int yvex_backend_cuda_encoded_matvec(yvex_backend *backend, const unsigned char *resident_encoded,
@@ -411,6 +458,12 @@ int yvex_backend_cuda_encoded_matvec(yvex_backend *backend, const unsigned char 
         yvex_backend_resident_resolve(backend, resident_encoded, encoded_bytes, &device_address) != YVEX_BACKEND_RESIDENT_HIT)
         return yvex_refuse(err, YVEX_ERR_FORMAT, where, "resident encoded matvec geometry or ownership is incompatible");
     output->is_written = 0;
+    /* host-side fault seams, as the reference has them in front of its copies and its launch
+     * (src/backend/cuda/qtype.c:625-661): a refused copy fails the call and the backend recovers,
+     * a failed launch demotes the backend for good */
+    if (yvex_test_seam("YVEX_TEST_CUDA_QTYPE_COPY_FAILURE", "input"))
+        return yvex_refuse(err, YVEX_ERR_BACKEND, "cuda.encoded-matvec.copy_input", "injected CUDA qtype input copy failure");
+    if (yvex_test_seam("YVEX_TEST_CUDA_LAUNCH_FAILURE", "encoded-matvec")) return yvex_backend_fail(backend, "cuda.encoded-matvec.launch", err);
     launches0 = yvex_b200_launch_count();
     rc = yvex_b200_gemv(qtype, (const void *)(uintptr_t)device_address, row_count, row_width, row_bytes, (const float *)input->data,
                         input_rows, additive ? (const float *)additive->data : NULL, (float *)output->data, 0, backend->status_word,
@@ -419,6 +472,8 @@ int yvex_backend_cuda_encoded_matvec(yvex_backend *backend, const unsigned char 
     if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the matvec geometry");
     if (!yvex_backend_take_status(backend, &code)) return yvex_backend_fail(backend, "cuda.encoded-matvec.sync", err);
     if (code) return yvex_refuse(err, code == 3 ? YVEX_ERR_TIMEOUT : YVEX_ERR_FORMAT, where, "encoded CUDA projection produced invalid numerics");
+    if (yvex_test_seam("YVEX_TEST_CUDA_QTYPE_COPY_FAILURE", "output"))
+        return yvex_refuse(err, YVEX_ERR_BACKEND, "cuda.encoded-matvec.copy_output", "injected CUDA qtype output copy failure");
     output->is_written = 1;
     facts->kernel_launches = yvex_b200_launch_count() - launches0;
     facts->tensor_core_launches = facts->kernel_launches;
@@ -488,8 +543,7 @@ int yvex_backend_attention_gqa_decode(yvex_backend *backend, const yvex_device_t
         values->dtype != YVEX_DTYPE_BF16 || out->dtype != YVEX_DTYPE_F32 || !query->is_written || !keys->is_written || !values->is_written)
         return yvex_refuse(err, YVEX_ERR_FORMAT, where, "GQA decode takes written BF16 Q/K/V and an F32 output of this backend");
     if (!sessions || !q_heads || !kv_heads || !head_dim || !context || query->bytes < sessions * q_heads * head_dim * 2 ||
-        keys->bytes < sessions * kv_heads * context * head_dim * 2 || values->bytes < keys->bytes - 0 * 1 ||
-        values->bytes < sessions * kv_heads * context * head_dim * 2 || out->bytes < sessions * q_heads * head_dim * 4)
+        keys->bytes < sessions * kv_heads * context * head_dim * 2 || values->bytes < sessions * kv_heads * context * head_dim * 2 || out->bytes < sessions * q_heads * head_dim * 4)
         return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "tensor bytes do not cover the stated geometry");
     need = yvex_b200_attention_workspace_bytes(sessions, q_heads, kv_heads, head_dim, context);
     scratch = yvex_workspace_take(backend, &cursor, need);

@@ -8,6 +8,7 @@
 #include "yvex_b200_backend.h"
 #include "yvex_b200_kernels.h"
 
+#define YVEX_MOE_MAX_CHUNKS 4
 #define YVEX_HOST_SCRATCH_BYTES (1u << 20)   /* pinned: status read-back and router selections of narrow batches */
 
 struct yvex_backend {
@@ -23,7 +24,13 @@ struct yvex_backend {
     int *status_word;                 /* device: first fault of the enqueued kernels */
     unsigned char *host_scratch;      /* pinned */
     yvex_moe_device_completion_slot *pending_slot;   /* deferred completion in flight */
+    /* copy pipeline of the wide entry: host rows go in on copy_in and come back on copy_out while the
+     * compute stream works on another chunk of rows */
+    cudaStream_t copy_in, copy_out;
+    cudaEvent_t ev_begin, ev_end, ev_in[YVEX_MOE_MAX_CHUNKS], ev_done[YVEX_MOE_MAX_CHUNKS];
 };
+#define YVEX_DEVICE_OBSERVATION_OFFSET 256   /* the worklist summary lives behind the status word */
+#define YVEX_DEVICE_STATE_BYTES 1024
 
 int yvex_refuse(yvex_error *err, yvex_status code, const char *where, const char *message);
 int yvex_backend_admit(const yvex_backend *backend, const char *where, yvex_error *err);
@@ -31,4 +38,6 @@ int yvex_backend_fail(yvex_backend *backend, const char *where, yvex_error *err)
 int yvex_tensor_owned(const yvex_backend *backend, const yvex_device_tensor *t);
 unsigned char *yvex_workspace_take(yvex_backend *backend, unsigned long long *cursor, unsigned long long bytes);
 int yvex_backend_take_status(yvex_backend *backend, int *code);
+/* Test seam of the reference (src/backend/cuda/qtype.c:625-661): 1 if the environment variable `name` is set to `value`. */
+int yvex_test_seam(const char *name, const char *value);
 #endif

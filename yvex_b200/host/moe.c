@@ -16,6 +16,15 @@
 
 #include <string.h>
 
+/* Row chunks of the wide entry's copy pipeline. Rows are independent, so a batch of host rows may
+ * run as consecutive row ranges: while range i is computed, range i + 1 is on its way in and range
+ * i - 1 on its way out. A range still has to fill the grouped GEMM's token tiles, so the count
+ * follows the average pairs per expert (about 160 per range, at most YVEX_MOE_MAX_CHUNKS). */
+static unsigned long long wide_chunks(const yvex_b200_moe_geometry *g, unsigned long long rows) {
+    const unsigned long long per_expert = rows * g->topk / (g->experts ? g->experts : 1ull), n = per_expert / 160ull;
+    return n < 1ull ? 1ull : n > (unsigned long long)YVEX_MOE_MAX_CHUNKS ? (unsigned long long)YVEX_MOE_MAX_CHUNKS : n;
+}
+
 #define YVEX_MOE_NARROW_MAX_ROWS 62ull       /* src/graph/worklist.c:316, src/backend/cuda/moe.c:1840-1843 */
 
 static int family_admitted(const char *family) {
@@ -73,7 +82,11 @@ static int workspace_for(const yvex_moe_layer_plan *layer, unsigned long long ro
     if (!wide && rows > YVEX_MOE_NARROW_MAX_ROWS)
         return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, "moe.workspace_required", "execute_rows admits at most 62 rows; use the wide entry");
     plan_geometry(layer, NULL, &g);
-    *bytes = staging_bytes(&g, rows, envelope_streams(layer)) + (wide ? yvex_b200_moe_wide_workspace_bytes(&g, rows) : yvex_b200_moe_workspace_bytes(&g, rows));
+    {
+        unsigned long long kernel = wide ? yvex_b200_moe_wide_workspace_bytes(&g, rows) : yvex_b200_moe_workspace_bytes(&g, rows);
+        const unsigned long long list = yvex_b200_expert_worklist_workspace_bytes(rows * g.topk, g.experts);
+        *bytes = staging_bytes(&g, rows, envelope_streams(layer)) + (kernel > list ? kernel : list);
+    }
     yvex_error_clear(err);
     return YVEX_OK;
 }
@@ -129,13 +142,15 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     yvex_b200_moe_weights w;
     yvex_b200_mhc mhc;
     unsigned long long rows, cursor = 0, need, kernel_ws, launches0, in_bytes, hid_bytes, sel_count, streams, mhc_ws = 0;
+    unsigned long long chunks = 1ull, tensor_path, list_ws;
+    yvex_expert_worklist_observation *dev_obs, *host_obs;
     unsigned char *ws_in, *ws_out, *ws_logits, *ws_sel, *ws_wts, *ws_ids, *ws_kernel;
     unsigned char *ws_norm = NULL, *ws_core = NULL, *ws_post = NULL, *ws_comb = NULL, *ws_mhc = NULL, *ws_coeff[4] = {NULL, NULL, NULL, NULL};
     unsigned long long coeff_count[4] = {0, 0, 0, 0};
     static const int coeff[4] = {YVEX_MOE_WEIGHT_FFN_NORM, YVEX_MOE_WEIGHT_MHC_FUNCTION, YVEX_MOE_WEIGHT_MHC_BASE, YVEX_MOE_WEIGHT_MHC_SCALE};
     const float *dev_in, *dev_logits = NULL, *layer_in;
     float *dev_out, *layer_out;
-    int rc, code, defer, slot;
+    int rc, code, defer, slot, pipelined;
     static const int required[YVEX_MOE_WEIGHT_COUNT] = {0, 0, 0, 0, 0, 0, 0, 1, 1, 1, 1, 1, 1};
     const void *addr[YVEX_MOE_WEIGHT_COUNT];
 
@@ -144,6 +159,8 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     rc = yvex_backend_admit(backend, where, err);
     if (rc != YVEX_OK) return rc;
     if (backend->pending_slot) return yvex_refuse(err, YVEX_ERR_STATE, where, "a deferred MoE completion is still pending");
+    /* host-side launch-failure seam (src/backend/cuda/qtype.c:625-661, src/backend/cuda/capability.c:611-629) */
+    if (yvex_test_seam("YVEX_TEST_CUDA_LAUNCH_FAILURE", "moe-rows")) return yvex_backend_fail(backend, where, err);
     rows = batch->row_count;
     if (!rows) return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "row batch is empty");
     if (!wide && rows > YVEX_MOE_NARROW_MAX_ROWS)
@@ -218,6 +235,9 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     hid_bytes = rows * g.hidden * 4ull;
     in_bytes = hid_bytes * streams;
     kernel_ws = wide ? yvex_b200_moe_wide_workspace_bytes(&g, rows) : yvex_b200_moe_workspace_bytes(&g, rows);
+    list_ws = yvex_b200_expert_worklist_workspace_bytes(rows * g.topk, g.experts);      /* reuses the kernel scratch afterwards */
+    if (kernel_ws < list_ws) kernel_ws = list_ws;
+    tensor_path = wide ? (unsigned long long)yvex_b200_moe_wide_uses_gemm(&g, &w) : 1ull;
     need = staging_bytes(&g, rows, streams) + kernel_ws;
     if (!backend->workspace || backend->workspace->bytes < need)
         return yvex_refuse(err, YVEX_ERR_NOMEM, where, "attached device workspace is smaller than workspace_required");
@@ -240,15 +260,27 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
         (streams > 1ull && (!ws_norm || !ws_core || !ws_post || !ws_comb || !ws_mhc || !ws_coeff[0] || !ws_coeff[1] || !ws_coeff[2] || !ws_coeff[3])))
         return yvex_refuse(err, YVEX_ERR_NOMEM, where, "attached device workspace is smaller than workspace_required");
 
+    defer = job->device_completion && job->device_completion->defer && job->device_completion->host;
+    /* the copy pipeline: host rows in, host rows out, no envelope, nothing deferred */
+    pipelined = wide && batch->expanded_rows && !batch->device_outputs && output && output->combined_rows && !defer && streams == 1ull &&
+                !batch->device_router_logits;
+    if (pipelined) chunks = wide_chunks(&g, rows);
+    if (chunks < 2ull) pipelined = 0;
+    if (output && output->combined_rows && output->combined_capacity < rows * g.hidden * streams)
+        return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "combined output capacity is too small");
+    sel_count = rows * g.topk;
+    if (output && (output->selected_experts || output->selected_weights) && output->selection_capacity < sel_count)
+        return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "selection output capacity is too small");
     if (batch->device_rows) {
         if (!yvex_tensor_owned(backend, batch->device_rows) || !batch->device_rows->is_written ||
             batch->device_rows->dtype != YVEX_DTYPE_F32 || batch->device_rows->bytes < in_bytes)
             return yvex_refuse(err, YVEX_ERR_FORMAT, where, "device rows must be a written F32 tensor of this backend");
         dev_in = (const float *)batch->device_rows->data;
     } else {
-        if (cudaMemcpyAsync(ws_in, batch->expanded_rows, in_bytes, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess)
+        if (!pipelined && cudaMemcpyAsync(ws_in, batch->expanded_rows, in_bytes, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess)
             return yvex_backend_fail(backend, where, err);
         result->h2d_bytes += in_bytes;
+        result->upload_count++;
         dev_in = (const float *)ws_in;
     }
     if (batch->device_router_logits) {
@@ -256,15 +288,17 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
             return yvex_refuse(err, YVEX_ERR_FORMAT, where, "device router logits must be an F32 tensor of this backend");
         dev_logits = (const float *)batch->device_router_logits->data;
     } else if (batch->router_logits) {
-        if (cudaMemcpyAsync(ws_logits, batch->router_logits, rows * g.experts * 4ull, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess)
+        if (!pipelined && cudaMemcpyAsync(ws_logits, batch->router_logits, rows * g.experts * 4ull, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess)
             return yvex_backend_fail(backend, where, err);
         result->h2d_bytes += rows * g.experts * 4ull;
+        result->upload_count++;
         dev_logits = (const float *)ws_logits;
     }
     if (batch->token_ids_present && batch->token_ids) {
-        if (cudaMemcpyAsync(ws_ids, batch->token_ids, rows * 4ull, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess)
+        if (!pipelined && cudaMemcpyAsync(ws_ids, batch->token_ids, rows * 4ull, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess)
             return yvex_backend_fail(backend, where, err);
         result->h2d_bytes += rows * 4ull;
+        result->upload_count++;
     }
     if (batch->device_outputs) {
         if (!yvex_tensor_owned(backend, batch->device_outputs) || batch->device_outputs->dtype != YVEX_DTYPE_F32 ||
@@ -276,11 +310,6 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
         if (!output || !output->combined_rows) return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "a device or host output is required");
         dev_out = (float *)ws_out;
     }
-    if (output && output->combined_rows && output->combined_capacity < rows * g.hidden * streams)
-        return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "combined output capacity is too small");
-    sel_count = rows * g.topk;
-    if (output && (output->selected_experts || output->selected_weights) && output->selection_capacity < sel_count)
-        return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "selection output capacity is too small");
 
     launches0 = yvex_b200_launch_count();
     layer_in = dev_in;
@@ -302,11 +331,54 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
         layer_in = (const float *)ws_norm;
         layer_out = (float *)ws_core;
     }
-    rc = (wide ? yvex_b200_moe_wide : yvex_b200_moe_decode)(
-        &g, &w, layer_in, dev_logits, batch->token_ids_present && batch->token_ids ? (const uint32_t *)ws_ids : NULL, rows, layer_out,
-        (int32_t *)ws_sel, (float *)ws_wts, ws_kernel, kernel_ws, backend->status_word, backend->stream);
-    if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
-    if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the MoE layer geometry");
+    if (pipelined) {
+        /* row range c: copied in on copy_in, computed on the backend's stream, copied out on copy_out */
+        const unsigned char *host_in = (const unsigned char *)batch->expanded_rows, *host_lg = (const unsigned char *)batch->router_logits;
+        const int ids = batch->token_ids_present && batch->token_ids;
+        int ok = cudaEventRecord(backend->ev_begin, backend->stream) == cudaSuccess &&
+                 cudaStreamWaitEvent(backend->copy_in, backend->ev_begin, 0) == cudaSuccess &&
+                 cudaStreamWaitEvent(backend->copy_out, backend->ev_begin, 0) == cudaSuccess;
+        for (unsigned long long c = 0; c < chunks && ok; ++c) {
+            const unsigned long long r0 = rows * c / chunks, n = rows * (c + 1ull) / chunks - r0;
+            ok = cudaMemcpyAsync(ws_in + r0 * g.hidden * 4ull, host_in + r0 * g.hidden * 4ull, n * g.hidden * 4ull, cudaMemcpyHostToDevice,
+                                 backend->copy_in) == cudaSuccess;
+            if (ok && host_lg)
+                ok = cudaMemcpyAsync(ws_logits + r0 * g.experts * 4ull, host_lg + r0 * g.experts * 4ull, n * g.experts * 4ull,
+                                     cudaMemcpyHostToDevice, backend->copy_in) == cudaSuccess;
+            if (ok && ids)
+                ok = cudaMemcpyAsync(ws_ids + r0 * 4ull, batch->token_ids + r0, n * 4ull, cudaMemcpyHostToDevice, backend->copy_in) == cudaSuccess;
+            ok = ok && cudaEventRecord(backend->ev_in[c], backend->copy_in) == cudaSuccess;
+        }
+        if (!ok) return yvex_backend_fail(backend, where, err);
+        for (unsigned long long c = 0; c < chunks; ++c) {
+            const unsigned long long r0 = rows * c / chunks, n = rows * (c + 1ull) / chunks - r0;
+            if (cudaStreamWaitEvent(backend->stream, backend->ev_in[c], 0) != cudaSuccess) return yvex_backend_fail(backend, where, err);
+            rc = yvex_b200_moe_wide(&g, &w, (const float *)ws_in + r0 * g.hidden, dev_logits ? dev_logits + r0 * g.experts : NULL,
+                                    ids ? (const uint32_t *)ws_ids + r0 : NULL, n, (float *)ws_out + r0 * g.hidden,
+                                    (int32_t *)ws_sel + r0 * g.topk, (float *)ws_wts + r0 * g.topk, ws_kernel, kernel_ws,
+                                    backend->status_word, backend->stream);
+            if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
+            if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the MoE layer geometry");
+            if (cudaEventRecord(backend->ev_done[c], backend->stream) != cudaSuccess ||
+                cudaStreamWaitEvent(backend->copy_out, backend->ev_done[c], 0) != cudaSuccess ||
+                cudaMemcpyAsync((unsigned char *)output->combined_rows + r0 * g.hidden * 4ull, ws_out + r0 * g.hidden * 4ull,
+                                n * g.hidden * 4ull, cudaMemcpyDeviceToHost, backend->copy_out) != cudaSuccess)
+                return yvex_backend_fail(backend, where, err);
+        }
+        /* the backend's stream ends behind the last copy out, so its synchronisation covers the whole call */
+        if (cudaEventRecord(backend->ev_end, backend->copy_out) != cudaSuccess ||
+            cudaStreamWaitEvent(backend->stream, backend->ev_end, 0) != cudaSuccess)
+            return yvex_backend_fail(backend, where, err);
+        result->d2h_bytes += in_bytes;
+        result->download_count++;
+        result->pipeline_chunks = chunks;
+    } else {
+        rc = (wide ? yvex_b200_moe_wide : yvex_b200_moe_decode)(
+            &g, &w, layer_in, dev_logits, batch->token_ids_present && batch->token_ids ? (const uint32_t *)ws_ids : NULL, rows, layer_out,
+            (int32_t *)ws_sel, (float *)ws_wts, ws_kernel, kernel_ws, backend->status_word, backend->stream);
+        if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
+        if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the MoE layer geometry");
+    }
     if (streams > 1ull) {
         rc = yvex_b200_mhc_post(&mhc, (const float *)ws_core, dev_in, (const float *)ws_post, (const float *)ws_comb, rows, dev_out,
                                 backend->status_word, backend->stream);
@@ -314,16 +386,28 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
         if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the mHC envelope geometry");
     }
 
-    defer = job->device_completion && job->device_completion->defer && job->device_completion->host;
-    if (output && output->combined_rows) {
+    /* The worklist summary of the batch (src/backend/cuda/moe.c:1710-1726), built on the device from the
+     * router's selection. The wide path sends every pair through the tensor-core GEMM tiles; the narrow
+     * path has no admission threshold, which the reference's summary counts as narrow pairs. */
+    dev_obs = (yvex_expert_worklist_observation *)((unsigned char *)backend->status_word + YVEX_DEVICE_OBSERVATION_OFFSET);
+    host_obs = (yvex_expert_worklist_observation *)(backend->host_scratch + YVEX_DEVICE_OBSERVATION_OFFSET);
+    rc = yvex_b200_expert_worklist((const int32_t *)ws_sel, rows, g.topk, g.experts, wide && tensor_path ? 1ull : 0ull,
+                                   wide && tensor_path ? yvex_b200_moe_wide_tile_columns(g.gate_qtype) : 1ull,
+                                   rows == 1ull ? 0u : wide ? 3u : 2u, NULL, NULL, NULL, NULL, NULL, NULL, dev_obs, ws_kernel, kernel_ws,
+                                   backend->status_word, backend->stream);
+    if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
+    if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the expert worklist geometry");
+    if (!pipelined && output && output->combined_rows) {
         if (cudaMemcpyAsync(output->combined_rows, dev_out, in_bytes, cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess)
             return yvex_backend_fail(backend, where, err);
         result->d2h_bytes += in_bytes;
+        result->download_count++;
     }
     if (!defer && output && output->selected_weights) {
         if (cudaMemcpyAsync(output->selected_weights, ws_wts, sel_count * 4ull, cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess)
             return yvex_backend_fail(backend, where, err);
         result->d2h_bytes += sel_count * 4ull;
+        result->download_count++;
     }
     if (!defer && output && output->selected_experts) {
         /* int32 ids land in the upper half of the caller's u64 array and are widened in place after the sync */
@@ -331,14 +415,22 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
                             backend->stream) != cudaSuccess)
             return yvex_backend_fail(backend, where, err);
         result->d2h_bytes += sel_count * 4ull;
+        result->download_count++;
     }
+    if (cudaMemcpyAsync(defer ? &job->device_completion->host->worklist : host_obs, dev_obs, sizeof(*dev_obs), cudaMemcpyDeviceToHost,
+                        backend->stream) != cudaSuccess)
+        return yvex_backend_fail(backend, where, err);
+    result->d2h_bytes += sizeof(*dev_obs);
+    result->download_count++;
+    /* counters as the reference publishes them (src/backend/cuda/moe.c:1757-1786) */
     result->row_count = rows;
     result->row_expert_pairs = sel_count;
-    result->grouped_expert_operations = 1;
-    result->shared_expert_operations = 1;
+    result->grouped_expert_operations = sel_count;
+    result->shared_expert_operations = rows;
     result->expert_subviews_accessed = sel_count * 3ull;
     result->kernel_launches = yvex_b200_launch_count() - launches0;
-    result->tensor_core_launches = wide ? 2ull : 2ull;
+    /* launches whose contraction runs on the tensor cores: the gate/up and down kernels of each row range */
+    result->tensor_core_launches = tensor_path ? 2ull * chunks : 0ull;
     if (streams > 1ull)
         result->active_weight_base_bytes += job->weights[YVEX_MOE_WEIGHT_FFN_NORM].encoded_bytes +
                                             job->weights[YVEX_MOE_WEIGHT_MHC_FUNCTION].encoded_bytes +
@@ -351,12 +443,11 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     result->active_weight_per_unique_expert_bytes = (job->weights[YVEX_MOE_WEIGHT_ROUTED_GATE].encoded_bytes +
                                                      job->weights[YVEX_MOE_WEIGHT_ROUTED_UP].encoded_bytes +
                                                      job->weights[YVEX_MOE_WEIGHT_ROUTED_DOWN].encoded_bytes) / g.experts;
-    result->encoded_bytes_read = result->active_weight_base_bytes + g.topk * result->active_weight_per_unique_expert_bytes * rows;
     result->activation_bytes = 2ull * in_bytes;
     result->temporary_bytes = need;
     if (defer) {
         yvex_moe_device_completion_slot *s = job->device_completion->host;
-        memset(s, 0, sizeof(*s));
+        s->status = 0;                       /* the worklist summary behind these fields is already on its way */
         s->pending = 1;
         s->row_count = rows;
         s->row_expert_pairs = sel_count;
@@ -372,7 +463,19 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     if (!yvex_backend_take_status(backend, &code)) return yvex_backend_fail(backend, where, err);
     result->stream_synchronizations = 1;
     result->d2h_bytes += sizeof(int);
+    result->download_count++;
     if (code) { memset(result, 0, sizeof(*result)); return status_error(code, err); }
+    if (!host_obs->bucket_count || host_obs->bucket_count > g.experts || !host_obs->maximum_bucket_population ||
+        host_obs->narrow_pairs != sel_count - host_obs->tensor_core_eligible_pairs) {       /* src/backend/cuda/moe.c:1744-1755 */
+        memset(result, 0, sizeof(*result));
+        return yvex_refuse(err, YVEX_ERR_STATE, where, "CUDA expert worklist completion is invalid");
+    }
+    result->worklists = *host_obs;
+    result->worklists.tensor_core_executed_pairs = result->worklists.tensor_core_eligible_pairs;
+    result->unique_experts = host_obs->bucket_count;
+    /* every active weight byte once: the replicated tensors plus the experts some row selected (:1905-1915) */
+    result->active_weight_bytes = result->active_weight_base_bytes + result->active_weight_per_unique_expert_bytes * result->unique_experts;
+    result->encoded_bytes_read = result->active_weight_bytes;
     if (output && output->selected_experts) {
         const int32_t *src = (const int32_t *)output->selected_experts + sel_count;
         for (unsigned long long i = 0; i < sel_count; ++i) output->selected_experts[i] = (unsigned long long)src[i];
@@ -411,6 +514,13 @@ static int moe_complete_rows(yvex_backend *backend, int barrier_observed, yvex_m
         result->device_completion_pending = 0;
         result->completed = code == 0;
         result->stream_synchronizations += barrier_observed ? 0ull : 1ull;
+        if (!code) {
+            result->worklists = s->worklist;
+            result->worklists.tensor_core_executed_pairs = s->worklist.tensor_core_eligible_pairs;
+            result->unique_experts = s->worklist.bucket_count;
+            result->active_weight_bytes = result->active_weight_base_bytes + result->active_weight_per_unique_expert_bytes * result->unique_experts;
+            result->encoded_bytes_read = result->active_weight_bytes;
+        }
     }
     if (code) return status_error(code, err);
     yvex_error_clear(err);

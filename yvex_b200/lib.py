@@ -32,6 +32,14 @@ class MoeWeights(C.Structure):
                 ("shared_gate", vp), ("shared_up", vp), ("shared_down", vp)]
 
 
+class WorklistObservation(C.Structure):
+    _fields_ = [("schema_version", C.c_uint), ("worklist_count", C.c_ulonglong), ("pair_count", C.c_ulonglong),
+                ("bucket_count", C.c_ulonglong), ("maximum_bucket_population", C.c_ulonglong),
+                ("tensor_core_eligible_pairs", C.c_ulonglong), ("tensor_core_executed_pairs", C.c_ulonglong),
+                ("narrow_pairs", C.c_ulonglong), ("tail_rows", C.c_ulonglong), ("width_histogram", C.c_ulonglong * 17),
+                ("population_histogram", C.c_ulonglong * 17), ("provenance_counts", C.c_ulonglong * 5)]
+
+
 class Mhc(C.Structure):
     _fields_ = [("hidden", u64), ("streams", u64), ("sinkhorn_iterations", u64), ("rms_epsilon", C.c_double),
                 ("mhc_epsilon", C.c_double), ("post_multiplier", C.c_double), ("mhc_fn", vp), ("scale", vp),
@@ -72,6 +80,13 @@ def _load():
     lib.yvex_b200_mhc_workspace_bytes.argtypes = [u64, u64]
     lib.yvex_b200_mhc_prepare.argtypes = [vp, vp, u64, vp, vp, vp, vp, u64, vp, vp]
     lib.yvex_b200_mhc_post.argtypes = [vp, vp, vp, vp, vp, u64, vp, vp, vp]
+    lib.yvex_b200_expert_worklist_workspace_bytes.restype = u64
+    lib.yvex_b200_expert_worklist_workspace_bytes.argtypes = [u64, u64]
+    lib.yvex_b200_expert_worklist.argtypes = [vp, u64, u64, u64, u64, u64, C.c_uint, vp, vp, vp, vp, vp, vp, vp, vp, u64, vp, vp]
+    lib.yvex_b200_selftest_bounded_wait.argtypes = [u64, vp, vp, vp]
+    lib.yvex_b200_moe_wide_uses_gemm.argtypes = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights)]
+    lib.yvex_b200_moe_wide_tile_columns.restype = u64
+    lib.yvex_b200_moe_wide_tile_columns.argtypes = [C.c_uint]
     lib.yvex_b200_attention_static_scratch_bytes.restype = u64
     lib.yvex_b200_attention_static_scratch_bytes.argtypes = []
     lib.yvex_b200_attention_gqa_decode_static.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, C.c_float,
@@ -90,7 +105,8 @@ EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_ge
            "yvex_b200_attention_workspace_bytes", "yvex_b200_attention_gqa_decode",
            "yvex_b200_attention_f32", "yvex_b200_attention_static_scratch_bytes",
            "yvex_b200_attention_gqa_decode_static", "yvex_b200_mhc_workspace_bytes", "yvex_b200_mhc_prepare",
-           "yvex_b200_mhc_post"]
+           "yvex_b200_mhc_post", "yvex_b200_expert_worklist_workspace_bytes", "yvex_b200_expert_worklist",
+           "yvex_b200_selftest_bounded_wait", "yvex_b200_moe_wide_uses_gemm", "yvex_b200_moe_wide_tile_columns"]
 
 
 def _torch():
@@ -245,6 +261,27 @@ def ep_dispatch(rows_f16, selected, route_weights, experts_per_rank, world, stat
                                      world, _p(send_rows), _p(meta), _p(inverse), _p(counts), _p(ws), ws.numel(),
                                      _p(status.word), _stream()), "ep_dispatch")
     return send_rows, meta, inverse, counts
+
+
+def expert_worklist(selected, experts, status, tensor_core_minimum=0, admitted_width=1, provenance=3):
+    """selected [rows, topk] int32 -> dict of the device-built worklist (order, source_rows, destination_rows,
+    expert_ids, bucket_offsets, bucket_populations as CPU numpy arrays) and its observation struct."""
+    torch = _torch()
+    rows, topk = selected.shape
+    pairs, dev = rows * topk, selected.device
+    i32 = lambda n: torch.full((n,), -1, dtype=torch.int32, device=dev)
+    order, src, dst = i32(pairs), i32(pairs), i32(pairs)
+    ids, offs, pops = i32(experts), i32(experts + 1), i32(experts)
+    obs = torch.zeros(C.sizeof(WorklistObservation), dtype=torch.uint8, device=dev)
+    ws = torch.empty(int(lib.yvex_b200_expert_worklist_workspace_bytes(pairs, experts)), dtype=torch.uint8, device=dev)
+    _check(lib.yvex_b200_expert_worklist(_p(selected.contiguous()), rows, topk, experts, tensor_core_minimum, admitted_width,
+                                         provenance, _p(order), _p(src), _p(dst), _p(ids), _p(offs), _p(pops), _p(obs), _p(ws),
+                                         ws.numel(), _p(status.word), _stream()), "expert_worklist")
+    o = WorklistObservation.from_buffer_copy(obs.cpu().numpy().tobytes())
+    n = int(o.bucket_count)
+    return dict(order=order.cpu().numpy(), source_rows=src.cpu().numpy(), destination_rows=dst.cpu().numpy(),
+                expert_ids=ids.cpu().numpy()[:n], bucket_offsets=offs.cpu().numpy()[:n + 1],
+                bucket_populations=pops.cpu().numpy()[:n], observation=o)
 
 
 def moe_route(geom, weights, status, rows_f32=None, logits=None, token_ids=None):
