@@ -706,16 +706,80 @@ def _timed_events(torch, fn, steps, before=None):
     return [a.elapsed_time(b) for a, b in zip(starts, stops)]
 
 
+def gemv_records(torch, lib, synth, dev, peaks, steps, warmup, status, gen):
+    """HBM throughput of the dequant-fused matvec, every case streaming >= 1.1 GB of distinct weight
+    bytes per step (inputs larger than L2): `batch` = 256 (128, 64) DIFFERENT 4096 x 4096 matrices with
+    their own input rows in one persistent launch; `one_matrix` = the same bytes as a single tall
+    matrix; `per_launch` = one launch per matrix, replayed from a CUDA graph; `output_head` = a BF16
+    [129280 x 4096] matrix, the shape of the reference model's logits projection."""
+    from yvex_b200.workloads import device_blocks
+    rows = width = 4096
+    out = {}
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        ms = _timed_events(torch, lambda i: fn(), steps)
+        return sum(ms) / len(ms) * 1e-3
+
+    def rec(algo, t):
+        gbs = algo / t / 1e9
+        return {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "frac_of_8TBs": gbs / 8000.0, "ms": t * 1e3}
+
+    for name, q, count in (("IQ2_XXS", synth.IQ2_XXS, 256), ("Q4_K", synth.Q4_K, 128), ("Q8_0", synth.Q8_0, 64)):
+        rb = synth.row_bytes(q, width)
+        enc = device_blocks(torch, q, rows * count, width, gen, dev)
+        xs = torch.randn((count, width), device=dev, generator=gen)
+        ys = torch.empty((count, rows), dtype=torch.float32, device=dev)
+        algo = count * (rows * rb + 4 * width + 4 * rows)
+        case = {"matrices": count, "bytes_per_step": algo}
+        case["batch"] = rec(algo, timed(lambda: lib.gemv_batch(q, enc, count, rows, width, xs, status, out=ys, row_bytes=rb)))
+        tall = torch.empty((1, rows * count), dtype=torch.float32, device=dev)
+        case["one_matrix"] = rec(count * rows * rb + 4 * width + 4 * rows * count,
+                                 timed(lambda: lib.gemv(q, enc, rows * count, width, xs[0], status, out=tall, row_bytes=rb)))
+        mats = [enc[i * rows * rb:(i + 1) * rows * rb] for i in range(count)]
+
+        def launch_all():
+            for i in range(count):
+                lib.gemv(q, mats[i], rows, width, xs[i], status, out=ys[i:i + 1], row_bytes=rb)
+        launch_all()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            launch_all()
+        case["per_launch"] = rec(algo, timed(graph.replay))
+        if name == "IQ2_XXS":
+            one = _timed_events(torch, lambda i: lib.gemv(q, mats[i % count], rows, width, xs[i % count], status, out=ys[0:1],
+                                                          row_bytes=rb), 50)
+            case["single_launch_us"] = sorted(one)[len(one) // 2] * 1e3
+            keep = (enc, xs, ys, mats, rb)
+        out[name] = case
+        del graph
+        if name != "IQ2_XXS":
+            del enc, xs, ys, mats, tall
+    vocab, hidden = 129280, 4096
+    head = torch.randn((vocab, hidden), device=dev, generator=gen).to(torch.bfloat16).view(torch.uint8).reshape(-1)
+    hx = torch.randn(hidden, device=dev, generator=gen)
+    hy = torch.empty((1, vocab), dtype=torch.float32, device=dev)
+    algo = vocab * hidden * 2 + 4 * hidden + 4 * vocab
+    out["output_head_BF16"] = dict(rec(algo, timed(lambda: lib.gemv(synth.BF16, head, vocab, hidden, hx, status, out=hy,
+                                                                    row_bytes=hidden * 2))),
+                                   rows=vocab, width=hidden, bytes_per_step=algo)
+    if status.read() != 0:
+        raise RuntimeError(f"device status word = {status.read()} in the matvec records")
+    return out, keep
+
+
 def run_gemv_stream(args):
     """Config 1: the 4096 x 4096 IQ2_XXS dequant GEMV. One matrix (4.3 MB) fits in L2, so a step is
-    256 DIFFERENT matrices back to back (1.1 GB streamed once, no reuse), replayed from one CUDA
-    graph; GB/s = algorithmic bytes of the 256 products / step time. Q4_K and Q8_0 variants and the
-    latency of a single launch are reported beside it."""
+    256 DIFFERENT matrices (1.1 GB streamed once, no reuse) in one persistent batch launch; GB/s =
+    algorithmic bytes of the 256 products / step time. Q4_K, Q8_0, the one-launch-per-matrix graph, a
+    single tall matrix and the BF16 output-head shape are reported beside it."""
     import ctypes as C
     import torch
     from yvex_b200 import backend as B
     from yvex_b200 import lib, synth
-    from yvex_b200.workloads import device_blocks
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if int(os.environ.get("RANK", "0")) != 0:
@@ -727,47 +791,18 @@ def run_gemv_stream(args):
     gen = torch.Generator(device=dev)
     gen.manual_seed(synth.BASE_SEED + 0)
     status = lib.Status(dev)
-
-    def stream_case(qtype, count):
-        rb = synth.row_bytes(qtype, width)
-        enc = device_blocks(torch, qtype, rows * count, width, gen, dev)
-        xs = torch.randn((count, width), device=dev, generator=gen)
-        ys = torch.empty((count, rows), dtype=torch.float32, device=dev)
-        mats = [enc[i * rows * rb:(i + 1) * rows * rb] for i in range(count)]
-
-        def launch_all():
-            for i in range(count):
-                lib.gemv(qtype, mats[i], rows, width, xs[i], status, out=ys[i:i + 1], row_bytes=rb)
-        launch_all()
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            launch_all()
-        algo = count * (rows * rb + 4 * width + 4 * rows)
-        return enc, xs, ys, mats, graph, algo, rb
-
-    count = 256
-    enc, xs, ys, mats, graph, algo, rb = stream_case(synth.IQ2_XXS, count)
-    for _ in range(args.warmup):
-        graph.replay()
-    torch.cuda.synchronize()
     with ClockSampler(local) as clocks:
-        ms = _timed_events(torch, lambda i: graph.replay(), args.steps)
-        # latency of one launch of one matrix (L2-warm after the first)
-        one = _timed_events(torch, lambda i: lib.gemv(synth.IQ2_XXS, mats[i % count], rows, width, xs[i % count], status,
-                                                       out=ys[0:1], row_bytes=rb), 50)
-    if status.read() != 0:
-        raise RuntimeError(f"device status word = {status.read()}")
-    t = sum(ms) / len(ms) * 1e-3
-    gbs = algo / t / 1e9
-    variants = {}
-    for name, q, n in (("Q4_K", synth.Q4_K, 128), ("Q8_0", synth.Q8_0, 64)):
-        _, _, _, _, g2, algo2, _ = stream_case(q, n)
-        for _ in range(3):
-            g2.replay()
-        m2 = _timed_events(torch, lambda i: g2.replay(), args.steps)
-        variants[name] = {"GB/s": algo2 / (sum(m2) / len(m2) * 1e-3) / 1e9, "matrices_per_step": n}
-        del g2
+        records, (enc, xs, ys, mats, rb) = gemv_records(torch, lib, synth, dev, peaks, args.steps, args.warmup, status, gen)
+    count = records["IQ2_XXS"]["matrices"]
+    gbs, t = records["IQ2_XXS"]["batch"]["GB/s"], records["IQ2_XXS"]["batch"]["ms"] * 1e-3
+    # result check of the timed configuration: 4 of the 256 products against the CPU port
+    port, kind = oracle_backend(False)
+    got = lib.gemv_batch(synth.IQ2_XXS, enc, count, rows, width, xs, status, row_bytes=rb).cpu().numpy()
+    for m in (0, 85, 170, 255):
+        rc, want = port.matvec(synth.IQ2_XXS, mats[m].cpu().numpy().reshape(rows, rb), rows, width, xs[m].cpu().numpy(), threads=os.cpu_count() or 1)
+        err = float(np.abs(got[m] - want).max() / max(np.abs(want).max(), 1e-30))
+        if rc != 0 or not err <= 2e-5:
+            raise RuntimeError(f"batched matvec {m} differs from the CPU port: {err:.3e}")
     # end to end through the host boundary: host x in, resident weights, host y out, one call per matrix
     be = B.Backend(device=f"cuda:{local}".encode())
     e2e_n = 64
@@ -794,7 +829,6 @@ def run_gemv_stream(args):
     e2e_algo = e2e_n * (rows * rb + 4 * width + 4 * rows)
     be.close()
     # CPU baseline: the port's matvec on one matrix, all cores over rows
-    port, kind = oracle_backend(False)
     cores = os.cpu_count() or 1
     w0 = mats[0].cpu().numpy()
     x0 = xs[0].cpu().numpy()
@@ -803,20 +837,20 @@ def run_gemv_stream(args):
     t_cpu = time.perf_counter() - t0
     line = {"metric": "dequant_gemv_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f16-mma/f32-accum (exact-integer weights), f32 in/out", "data": "synthetic",
+            "vs_baseline": None, "dtype": "s8-mma/s32-accum (exact integer products), f32 in/out", "data": "synthetic",
             "config": {"workload": "c1", "rows": rows, "width": width, "qtype": "IQ2_XXS", "matrices_per_step": count,
-                       "l2": "inputs larger than L2: 256 distinct matrices (1.1 GB) per step, one CUDA graph",
+                       "l2": "inputs larger than L2: 256 distinct matrices (1.1 GB) per step, one batch launch",
                        "parallelism": f"replicas only (1 of {world} ranks measures)"},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_algo / t_e2e / 1e9, "unit": "GB/s", "h2d_bytes_per_step": e2e_n * width * 4,
                     "d2h_bytes_per_step": e2e_n * rows * 4,
                     "api": f"yvex_backend_cuda_encoded_matvec, {e2e_n} calls per step, host x in / host y out per call"},
-            "gpu_launches": count * args.steps,
-            "single_launch_us": sorted(one)[len(one) // 2] * 1e3,
-            "variants": variants,
-            "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<Iq2Decoder>", "achieved": gbs, "peak": peaks["hbm_gbs"],
-                         "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": TRAFFIC["c1"],
-                         "algorithmic_bytes": rows * rb + 4 * width + 4 * rows, "peak_source": peaks["source"],
+            "gpu_launches": args.steps,
+            "parity": {"checked_matrices": 4, "against": "CPU port, max abs error / max |y| <= 2e-5"},
+            "gemv": records,
+            "roofline": {"bound": "hbm", "kernel": "gemv_stream_kernel<StreamIq2>", "achieved": gbs, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                         "algorithmic_bytes": count * (rows * rb + 4 * width + 4 * rows), "peak_source": peaks["source"],
                          "frac_of_nominal_8TBs": gbs / 8000.0},
             "cpu_baseline": {"value": (rows * rb + 4 * width + 4 * rows) / t_cpu / 1e9, "unit": "GB/s", "cores": cores,
                              "kind": kind, "sample": "one 4096x4096 IQ2_XXS matvec, rows split over all cores"}}

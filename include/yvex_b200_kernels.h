@@ -73,6 +73,20 @@ int yvex_b200_gemv(unsigned int qtype, const void *encoded, uint64_t rows, uint6
                    uint64_t row_bytes, const float *input, uint64_t input_rows,
                    const float *additive, float *out, int round_bf16, int *status, void *stream);
 
+/*
+ * A batch of independent matvecs of one shape in one launch: matrix m is the canonical row layout at
+ * encoded + m * matrix_stride, its input vector at input + m * input_stride (f32 elements), its
+ * result (and optional additive row) at out + m * out_stride. What a decode step does for several
+ * projections or experts of one geometry at once; no reference counterpart (the reference issues
+ * one yvex_qtype_matvec per matrix, src/backend/cuda/qtype.c:340-379). IQ2_XXS, Q4_K and Q8_0 with
+ * width a multiple of 256 (<= 8192), a 16-byte aligned base and stride run on the persistent
+ * streaming kernel; everything else falls back to one yvex_b200_gemv per matrix.
+ */
+int yvex_b200_gemv_batch(unsigned int qtype, const void *encoded, uint64_t matrix_stride, uint64_t count,
+                         uint64_t rows, uint64_t width, uint64_t row_bytes, const float *input,
+                         uint64_t input_stride, const float *additive, float *out, uint64_t out_stride,
+                         int round_bf16, int *status, void *stream);
+
 /* Geometry and policy of one MoE FFN layer: the fields of yvex_moe_layer_plan
  * (include/yvex/internal/moe.h:54-84) that the execution path reads. */
 typedef struct {

@@ -161,6 +161,51 @@ def test_gemv_input_rows_additive_and_bf16(L, port, qtype):
         assert (synth.bf16_round(y[i]).view(np.uint32) == y[i].view(np.uint32)).all()
 
 
+@pytest.mark.parametrize("qtype,count,rows,width", [(synth.IQ2_XXS, 5, 300, 4096), (synth.Q4_K, 3, 77, 1536), (synth.Q8_0, 4, 33, 2048),
+                                                    (synth.IQ2_XXS, 40, 16, 256), (synth.Q2_K, 3, 20, 512)])
+def test_gemv_batch_vs_oracle(L, port, qtype, count, rows, width):
+    """Independent matrices with their own input rows in one launch (ragged tiles, tiles of different
+    matrices inside one CTA's task range, a qtype that falls back to one matvec per matrix)."""
+    w = synth.random_blocks(qtype, rows * count, width, 500 + rows)
+    rng = np.random.default_rng(count)
+    x = (rng.standard_normal((count, width)) * np.logspace(-3, 2, count)[:, None]).astype(np.float32)      # rows of very different scale
+    add = rng.standard_normal((count, rows)).astype(np.float32)
+    st = L.Status()
+    y = L.gemv_batch(qtype, dev(w.reshape(-1)), count, rows, width, dev(x), st).cpu().numpy()
+    ya = L.gemv_batch(qtype, dev(w.reshape(-1)), count, rows, width, dev(x), st, additive=dev(add)).cpu().numpy()
+    assert st.read() == 0
+    for m in range(count):
+        wm = w[m * rows:(m + 1) * rows]
+        rc, want = port.matvec(qtype, wm, rows, width, x[m], threads=4, allow_q4k=True)
+        _, dec = port.decode_rows(qtype, wm, rows, width, allow_q4k=True)
+        assert rc == 0 and matvec_close(y[m], want, dec, x[m]).all(), (m, np.abs(y[m] - want).max())
+        assert matvec_close(ya[m] - add[m], want, dec, x[m]).all() or np.abs(ya[m] - (want + add[m])).max() <= 1e-5 * (1 + np.abs(want + add[m]).max())
+
+
+def test_gemv_streaming_kernel_edge_cases(L, port):
+    """A zero input row, one huge element among tiny ones (the fixed-point planes follow the row's largest
+    magnitude), a malformed block scale in an existing row, and a non-finite input."""
+    rows, width = 50, 1024
+    w = synth.random_blocks(synth.IQ2_XXS, rows, width, 61)
+    st = L.Status()
+    y = L.gemv(synth.IQ2_XXS, dev(w), rows, width, dev(np.zeros(width, np.float32)), st).cpu().numpy()[0]
+    assert st.read() == 0 and not y.any()
+    x = (np.random.default_rng(2).standard_normal(width) * 1e-3).astype(np.float32)
+    x[17] = 900.0
+    y = L.gemv(synth.IQ2_XXS, dev(w), rows, width, dev(x), st).cpu().numpy()[0]
+    rc, want = port.matvec(synth.IQ2_XXS, w, rows, width, x)
+    _, dec = port.decode_rows(synth.IQ2_XXS, w, rows, width)
+    assert rc == 0 and st.read() == 0 and matvec_close(y, want, dec, x).all()
+    bad = w.copy()
+    bad[49, 66:68] = [0x00, 0xFC]                    # d = -inf in the second block of the last row
+    L.gemv(synth.IQ2_XXS, dev(bad), rows, width, dev(x), st)
+    assert st.read() == 1
+    st.reset()
+    x[5] = np.nan
+    L.gemv(synth.IQ2_XXS, dev(w), rows, width, dev(x), st)
+    assert st.read() == 1
+
+
 def test_gemv_linearity_at_full_size(L):
     """Size-independent property: W(a*x1 + x2) == a*W(x1) + W(x2) up to f32 rounding."""
     rows = width = 4096

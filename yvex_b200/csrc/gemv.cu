@@ -10,6 +10,7 @@
 //     split of the f32 activation, with the per-superblock f16 scale applied to the drained
 //     accumulator.
 #include "gemv_mma.cuh"
+#include "gemv_stream.cuh"
 #include "qtype_decode.cuh"
 #include "tcgen05.cuh"
 
@@ -55,6 +56,81 @@ __global__ void gemv_rows_kernel(unsigned q, const uint8_t *enc, uint64_t rows, 
             out[job] = round_bf16 ? bf16_round(acc) : acc;
         }
     }
+}
+
+// ---- scalar-qtype matvec: F32 / F16 / BF16 rows streamed with 16-byte loads ---------------------------
+// The output-head projection of the reference model is such a matrix (BF16 rows, about 1 GB per call,
+// src/runtime/logits.c:644-649): pure streaming, one warp per row, the activation row in shared
+// memory, every lane four independent 16-byte loads ahead of its multiply-adds.
+template <unsigned kQ> __device__ __forceinline__ void dense_chunk(const uint4 v, const float *xs, float &acc) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    if (kQ == Q_F32) {
+        const float4 xv = *reinterpret_cast<const float4 *>(xs);
+        acc = fmaf(__uint_as_float(w[0]), xv.x, acc); acc = fmaf(__uint_as_float(w[1]), xv.y, acc);
+        acc = fmaf(__uint_as_float(w[2]), xv.z, acc); acc = fmaf(__uint_as_float(w[3]), xv.w, acc);
+    } else {
+        const float4 x0 = reinterpret_cast<const float4 *>(xs)[0], x1 = reinterpret_cast<const float4 *>(xs)[1];
+        const float xe[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float lo, hi;
+            if (kQ == Q_BF16) { lo = __uint_as_float(w[i] << 16); hi = __uint_as_float(w[i] & 0xffff0000u); }
+            else { const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i])); lo = f.x; hi = f.y; }
+            acc = fmaf(lo, xe[2 * i], acc);
+            acc = fmaf(hi, xe[2 * i + 1], acc);
+        }
+    }
+}
+
+template <unsigned kQ>
+__global__ void __launch_bounds__(512) gemv_dense_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row_bytes,
+                                                         const float *input, const float *additive, float *out, int round_bf16,
+                                                         int *status) {
+    extern __shared__ __align__(16) float dense_x[];
+    constexpr int kPer = kQ == Q_F32 ? 4 : 8;                               // elements per 16-byte chunk
+    const float *x = input + (uint64_t)blockIdx.y * width;
+    bool bad = false;
+    for (uint32_t i = threadIdx.x; i < (uint32_t)width; i += blockDim.x) { const float v = __ldg(x + i); bad |= !isfinite(v); dense_x[i] = v; }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const uint32_t chunks = (uint32_t)(row_bytes / 16);
+    for (uint64_t r = (uint64_t)blockIdx.x * warps + warp; r < rows; r += (uint64_t)gridDim.x * warps) {
+        const uint4 *rp = reinterpret_cast<const uint4 *>(enc + r * row_bytes);
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        uint32_t c = lane;
+        for (; c + 96 < chunks; c += 128) {
+            const uint4 v0 = __ldcs(rp + c), v1 = __ldcs(rp + c + 32), v2 = __ldcs(rp + c + 64), v3 = __ldcs(rp + c + 96);
+            dense_chunk<kQ>(v0, dense_x + (size_t)c * kPer, a0);
+            dense_chunk<kQ>(v1, dense_x + (size_t)(c + 32) * kPer, a1);
+            dense_chunk<kQ>(v2, dense_x + (size_t)(c + 64) * kPer, a2);
+            dense_chunk<kQ>(v3, dense_x + (size_t)(c + 96) * kPer, a3);
+        }
+        for (; c < chunks; c += 32) dense_chunk<kQ>(__ldcs(rp + c), dense_x + (size_t)c * kPer, a0);
+        float acc = warp_sum((a0 + a1) + (a2 + a3));
+        if (lane == 0) {
+            const uint64_t job = (uint64_t)blockIdx.y * rows + r;
+            if (additive) acc += additive[job];
+            if (!isfinite(acc)) bad = true;
+            out[job] = round_bf16 ? bf16_round(acc) : acc;
+        }
+    }
+    if (bad) raise(status, YVEX_B200_STATUS_NUMERIC);
+}
+
+static bool gemv_dense_eligible(unsigned q, uint64_t width, uint64_t row_bytes, const uint8_t *enc, const float *input, uint64_t input_rows) {
+    return (q == Q_F32 || q == Q_F16 || q == Q_BF16) && row_bytes % 16 == 0 && width * 4 <= 48 * 1024 && input_rows <= 65535 &&
+           ((reinterpret_cast<uintptr_t>(enc) | reinterpret_cast<uintptr_t>(input)) & 15u) == 0 && (width * 4) % 16 == 0;
+}
+
+static int gemv_dense_launch(unsigned q, const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row_bytes, const float *input,
+                             uint64_t input_rows, const float *additive, float *out, int round_bf16, int *status, cudaStream_t s) {
+    const uint64_t want = (rows + 15) / 16, cap = (uint64_t)kSmCount * 4;
+    const dim3 grid((unsigned)(want < cap ? want : cap), (unsigned)input_rows);
+    const size_t smem = width * 4;
+    if (q == Q_F32) gemv_dense_kernel<Q_F32><<<grid, 512, smem, s>>>(enc, rows, width, row_bytes, input, additive, out, round_bf16, status);
+    else if (q == Q_F16) gemv_dense_kernel<Q_F16><<<grid, 512, smem, s>>>(enc, rows, width, row_bytes, input, additive, out, round_bf16, status);
+    else gemv_dense_kernel<Q_BF16><<<grid, 512, smem, s>>>(enc, rows, width, row_bytes, input, additive, out, round_bf16, status);
+    return launch_status();
 }
 
 // ---- Q8_0 streaming matvec ------------------------------------------------------------------------
@@ -237,11 +313,17 @@ extern "C" int yvex_b200_gemv(unsigned int qtype, const void *encoded, uint64_t 
     int rc = check_rows(qtype, rows, width, row_bytes);
     if (rc != OK) return rc;
     const uint8_t *enc = static_cast<const uint8_t *>(encoded);
+    // input rows are a batch that shares one matrix
+    if (gs::stream_eligible(qtype, rows, width, row_bytes, enc, 0, input_rows))
+        return gs::stream_launch(qtype, enc, 0, input_rows, rows, width, row_bytes, input, width, additive, out, rows, round_bf16, status,
+                                 as_stream(stream));
     if (gemv_mma_eligible(qtype, rows, width, enc) &&
         (reinterpret_cast<uintptr_t>(input) & 15u) == 0) {
         return gemv_mma_launch(qtype, enc, rows, width, row_bytes, input, input_rows, additive, out, round_bf16, status,
                                as_stream(stream));
     }
+    if (gemv_dense_eligible(qtype, width, row_bytes, enc, input, input_rows))
+        return gemv_dense_launch(qtype, enc, rows, width, row_bytes, input, input_rows, additive, out, round_bf16, status, as_stream(stream));
     if (gemv_q8_0_eligible(qtype, width, row_bytes, enc) && input_rows <= 65535)
         return gemv_q8_0_launch(enc, rows, width, row_bytes, input, input_rows, additive, out, round_bf16, status, as_stream(stream));
     uint64_t jobs = rows * input_rows;
@@ -251,4 +333,25 @@ extern "C" int yvex_b200_gemv(unsigned int qtype, const void *encoded, uint64_t 
                                                           input_rows, additive, out, round_bf16,
                                                           status);
     return launch_status();
+}
+
+extern "C" int yvex_b200_gemv_batch(unsigned int qtype, const void *encoded, uint64_t matrix_stride, uint64_t count,
+                                    uint64_t rows, uint64_t width, uint64_t row_bytes, const float *input,
+                                    uint64_t input_stride, const float *additive, float *out, uint64_t out_stride,
+                                    int round_bf16, int *status, void *stream) {
+    if (!encoded || !input || !out || !status || !count) return ERR_INVALID_ARG;
+    int rc = check_rows(qtype, rows, width, row_bytes);
+    if (rc != OK) return rc;
+    if (input_stride < width || out_stride < rows || (count > 1 && matrix_stride < rows * row_bytes)) return ERR_BOUNDS;
+    const uint8_t *enc = static_cast<const uint8_t *>(encoded);
+    if (gs::stream_eligible(qtype, rows, width, row_bytes, enc, matrix_stride, count))
+        return gs::stream_launch(qtype, enc, matrix_stride, count, rows, width, row_bytes, input, input_stride, additive, out, out_stride,
+                                 round_bf16, status, as_stream(stream));
+    // shapes and qtypes the streaming kernel does not take: one matvec per matrix
+    for (uint64_t m = 0; m < count; ++m) {
+        rc = yvex_b200_gemv(qtype, enc + m * matrix_stride, rows, width, row_bytes, input + m * input_stride, 1,
+                            additive ? additive + m * out_stride : nullptr, out + m * out_stride, round_bf16, status, stream);
+        if (rc != OK) return rc;
+    }
+    return OK;
 }

@@ -69,6 +69,7 @@ def _load():
     lib.yvex_b200_attention_workspace_bytes.argtypes = [u64] * 5
     lib.yvex_b200_dequant_rows.argtypes = [C.c_uint, vp, u64, u64, u64, vp, vp, vp]
     lib.yvex_b200_gemv.argtypes = [C.c_uint, vp, u64, u64, u64, vp, u64, vp, vp, C.c_int, vp, vp]
+    lib.yvex_b200_gemv_batch.argtypes = [C.c_uint, vp, u64, u64, u64, u64, u64, vp, u64, vp, vp, u64, C.c_int, vp, vp]
     moe_args = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights), vp, vp, vp, u64, vp, vp, vp, vp, u64, vp, vp]
     lib.yvex_b200_moe_route.argtypes = moe_args
     lib.yvex_b200_moe_decode.argtypes = moe_args
@@ -97,7 +98,7 @@ def _load():
 lib = _load()
 
 EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_geometry",
-           "yvex_b200_dequant_rows", "yvex_b200_gemv", "yvex_b200_moe_workspace_bytes",
+           "yvex_b200_dequant_rows", "yvex_b200_gemv", "yvex_b200_gemv_batch", "yvex_b200_moe_workspace_bytes",
            "yvex_b200_moe_route", "yvex_b200_moe_decode", "yvex_b200_moe_wide",
            "yvex_b200_moe_wide_workspace_bytes", "yvex_b200_launch_count", "yvex_b200_phase_events",
            "yvex_b200_moe_expert_rows_workspace_bytes", "yvex_b200_moe_expert_rows", "yvex_b200_moe_combine",
@@ -180,6 +181,20 @@ def gemv(qtype, enc, rows, width, x, status, additive=None, round_bf16=False, ou
     rb = row_bytes if row_bytes is not None else enc.numel() // rows
     _check(lib.yvex_b200_gemv(qtype, _p(enc), rows, width, rb, _p(x2), x2.shape[0], _p(additive), _p(out),
                               int(round_bf16), _p(status.word), _stream()), "gemv")
+    return out
+
+
+def gemv_batch(qtype, enc, count, rows, width, xs, status, additive=None, round_bf16=False, out=None, row_bytes=None,
+               matrix_stride=None):
+    """`count` matrices of one shape stored back to back in `enc` (matrix_stride bytes apart), one input row each
+    (xs [count, width] f32) -> out [count, rows] f32, one launch."""
+    torch = _torch()
+    rb = row_bytes if row_bytes is not None else enc.numel() // (rows * count)
+    stride = matrix_stride if matrix_stride is not None else rows * rb
+    if out is None:
+        out = torch.empty((count, rows), dtype=torch.float32, device=xs.device)
+    _check(lib.yvex_b200_gemv_batch(qtype, _p(enc), stride, count, rows, width, rb, _p(xs), width, _p(additive), _p(out), rows,
+                                    int(round_bf16), _p(status.word), _stream()), "gemv_batch")
     return out
 
 
