@@ -192,6 +192,27 @@ int yvex_b200_ep_dispatch(const int32_t *selected, const float *weights, const v
                           uint64_t topk, uint64_t hidden, uint64_t experts_per_rank, uint64_t world,
                           void *send_rows_f16, int32_t *meta, int32_t *inverse, long long *send_counts,
                           void *workspace, uint64_t workspace_bytes, int *status, void *stream);
+/*
+ * The same dispatch for an exchange that is pipelined against the expert GEMMs. Each destination
+ * rank's experts are cut into `segments` equal ranges, and the pairs are grouped by (segment,
+ * destination rank), so that segment 0 of every rank can travel and be computed while segment 1 is
+ * still on its way. A row travels as one record of yvex_b200_ep_payload_pitch(hidden) bytes: its
+ * hidden fp16 values followed by a 16-byte trailer {int32 expert id local to its rank, f32 route
+ * weight, int32 pair index at home, 0}, so no second message carries the metadata. send_counts has
+ * world * segments entries, [segment][rank]. yvex_b200_moe_expert_rows_payload runs such records as
+ * a pair list (ids and weights from the trailers; a negative id names the shared expert).
+ * yvex_b200_moe_wide_set_cta_limit bounds the CTAs of the persistent grouped GEMM (default: one per
+ * SM) so that communication kernels find free SMs beside it; process-wide.
+ */
+uint64_t yvex_b200_ep_payload_pitch(uint64_t hidden);
+int yvex_b200_ep_dispatch_payload(const int32_t *selected, const float *weights, const void *rows_f16, uint64_t tokens,
+                                  uint64_t topk, uint64_t hidden, uint64_t experts_per_rank, uint64_t world,
+                                  uint64_t segments, void *payload, int32_t *inverse, long long *send_counts,
+                                  void *workspace, uint64_t workspace_bytes, int *status, void *stream);
+int yvex_b200_moe_expert_rows_payload(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w,
+                                      const void *payload, uint64_t pairs, void *y_bf16, void *workspace,
+                                      uint64_t workspace_bytes, int *status, void *stream);
+int yvex_b200_moe_wide_set_cta_limit(int ctas);
 /* The same sum with the rows named by index: routed row (t, r) is y_routed[routed_rows[t*topk + r]],
  * the shared row of token t is y_shared[shared_rows[t]]; a NULL index means the identity order.
  * Lets an expert-parallel home rank combine straight from its receive buffer. */

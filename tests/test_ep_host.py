@@ -9,12 +9,12 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from yvex_b200.ep import ExpertParallelLayer
+from yvex_b200.ep import ExpertParallelLayer, TorchOps
 
 E, K, H, T = 8, 3, 32, 10
 
 
-class FakeOps:
+class FakeOps(TorchOps):
     """Deterministic stand-ins: expert e multiplies a row by (e + 1) * weight, shared by 0.5."""
 
     def __init__(self, rank, per_rank):
@@ -86,3 +86,62 @@ def test_two_rank_layer_matches_single_process_bit_for_bit(skew):
     assert torch.equal(got_sel, want_sel)
     assert torch.equal(got.view(torch.int32), want.view(torch.int32))
 
+
+
+def worker_segments(rank, world, port, segments, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    x, logits = inputs(False)
+    lo, hi = rank * T // world, (rank + 1) * T // world
+    layer = ExpertParallelLayer(E, K, FakeOps(rank, E // world), segments=segments)
+    ret[rank] = layer.forward(x[lo:hi].contiguous(), logits[lo:hi].contiguous())[0]
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("segments", [1, 2, 4])
+def test_expert_segments_do_not_change_the_result(segments):
+    """The exchange pipelined over 1, 2 or 4 ranges of each rank's experts gives the same bits."""
+    world = 2
+    ret = mp.Manager().dict()
+    mp.spawn(worker_segments, args=(world, free_port(), segments, ret), nprocs=world, join=True)
+    want, _ = single(False)
+    got = torch.cat([ret[r] for r in range(world)])
+    assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+
+
+def worker_leaver(rank, world, port, mode, ret):
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    x, logits = inputs(False)
+    lo, hi = rank * T // world, (rank + 1) * T // world
+    layer = ExpertParallelLayer(E, K, FakeOps(rank, E // world))
+    layer.forward(x[lo:hi].contiguous(), logits[lo:hi].contiguous())         # one good step first
+    if rank == 1:
+        # the failure is made on the host: this rank stalls past the deadline (or leaves) before the next exchange
+        if mode == "stall":
+            time.sleep(9)
+        ret[rank] = "left"
+        os._exit(0)
+    from yvex_b200.ep import ERR_TIMEOUT, ExchangeError
+    t0 = time.time()
+    try:
+        layer.forward(x[lo:hi].contiguous(), logits[lo:hi].contiguous())
+        ret[rank] = "no error"
+    except ExchangeError as exc:
+        ret[rank] = ("timeout" if exc.code == ERR_TIMEOUT else f"code {exc.code}", time.time() - t0)
+    os._exit(0)
+
+
+@pytest.mark.parametrize("mode", ["stall", "leave"])
+def test_a_rank_that_stalls_or_leaves_ends_the_exchange_with_a_timeout(mode):
+    """The surviving rank gets an error from the host wrapper within the process group's deadline
+    (never a hang): YVEX_ERR_TIMEOUT. The failing rank does its failing between steps, on the host."""
+    world = 2
+    ret = mp.Manager().dict()
+    mp.spawn(worker_leaver, args=(world, free_port(), mode, ret), nprocs=world, join=True)
+    assert ret[1] == "left"
+    kind, seconds = ret[0]
+    assert kind == "timeout" and seconds < 30.0, ret[0]

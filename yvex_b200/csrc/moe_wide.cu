@@ -13,6 +13,7 @@
 // yvex_b200_moe_combine is the unpermute on its own.
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "moe_gemm.cuh"
@@ -118,14 +119,30 @@ __global__ void wide_scatter_kernel(const int *expert_of_pair, uint64_t pairs, c
     }
 }
 
-// act_h[pos] = fp16 source row of the pair sorted to position pos.
+// act_h[pos] = fp16 source row of the pair sorted to position pos. Source rows are `src_pitch` bytes apart
+// (a multiple of 16; rows that travelled between ranks carry a trailer behind their hidden values).
 __global__ void wide_gather_kernel(const __half *rows_h, const int *perm, const int *src_of_pair, uint64_t pairs,
-                                   uint64_t hidden, __half *act_h) {
+                                   uint64_t hidden, __half *act_h, uint64_t src_pitch) {
     const uint32_t chunks = (uint32_t)(hidden / 8);           // 16-byte chunks per row
     for (uint64_t row = blockIdx.x; row < pairs; row += gridDim.x) {          // a CTA copies whole rows
-        const uint4 *src = reinterpret_cast<const uint4 *>(rows_h) + (uint64_t)src_of_pair[perm[row]] * chunks;
+        const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(rows_h) +
+                                                           (uint64_t)src_of_pair[perm[row]] * src_pitch);
         uint4 *dst = reinterpret_cast<uint4 *>(act_h) + row * chunks;
         for (uint32_t c = threadIdx.x; c < chunks; c += blockDim.x) dst[c] = __ldg(src + c);
+    }
+}
+
+// Trailer of a row that travels between expert-parallel ranks: behind its hidden fp16 values.
+struct EpTrailer { int32_t local_expert; float weight; int32_t home_pair; int32_t pad; };
+
+// Pair list from the trailers of received rows: pair p reads source row p.
+__global__ void wide_list_payload_kernel(const uint8_t *payload, uint64_t pitch, uint64_t hidden, uint64_t pairs, int experts,
+                                         int *expert_of_pair, int *src_of_pair, float *weight_of_pair) {
+    for (uint64_t p = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; p < pairs; p += (uint64_t)gridDim.x * blockDim.x) {
+        const EpTrailer t = *reinterpret_cast<const EpTrailer *>(payload + p * pitch + hidden * 2);
+        expert_of_pair[p] = t.local_expert < 0 ? experts : t.local_expert;
+        src_of_pair[p] = (int)p;
+        weight_of_pair[p] = t.weight;
     }
 }
 
@@ -292,12 +309,16 @@ static int fuse_of(uint64_t row_bytes) {
     return fuse;
 }
 
+// CTAs of the persistent grouped GEMM. One per SM by default; an expert-parallel caller that runs its
+// exchange beside the GEMM leaves a few SMs to the communication kernels.
+static std::atomic<int> g_gemm_ctas{kSmCount};
+
 template <class Dec>
 static int launch_gemm(const GemmMaps &map, const GemmParams &p, cudaStream_t s) {
     const size_t smem = GemmPlan<Dec>::kBytes;
     static SmemOptIn opt_in;
     if (opt_in.ensure(moe_grouped_gemm_kernel<Dec>, (int)smem) != OK) return ERR_BACKEND;
-    moe_grouped_gemm_kernel<Dec><<<kSmCount, GemmPlan<Dec>::kThreads, smem, s>>>(map, p);
+    moe_grouped_gemm_kernel<Dec><<<g_gemm_ctas.load(std::memory_order_relaxed), GemmPlan<Dec>::kThreads, smem, s>>>(map, p);
     return launch_status(1);
 }
 
@@ -345,7 +366,8 @@ bool moe_wide_gemm_eligible(const MoeGeom &g, const MoeWeights &w) {
 // down GEMM's epilogue then stores through the permutation, so no separate unsort pass is needed).
 // rows_h: the fp16 source rows the list indexes.
 static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorkspace &pw, const __half *rows_h, uint64_t pairs,
-                         int *status, cudaStream_t s, uint16_t *y_list = nullptr) {
+                         int *status, cudaStream_t s, uint16_t *y_list = nullptr, uint64_t src_pitch = 0) {
+    if (!src_pitch) src_pitch = g.hidden * 2;
     const Geometry gg = geometry_of(g.gate_qtype), dg = geometry_of(g.down_qtype);
     const int bins = (int)g.experts + 1;
     cudaMemsetAsync(pw.counts, 0, (g.experts + 2) * 4, s);
@@ -353,7 +375,7 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     wide_plan_kernel<<<2, 32, 0, s>>>(pw.counts, (int)g.experts, pairs, pw.offsets, pw.blocks, pw.blocks_down, pw.num_blocks,
                                       pw.max_blocks, gemm_tile_n(g.gate_qtype), gemm_tile_n(g.down_qtype), status);
     wide_scatter_kernel<<<(unsigned)bins, 512, 0, s>>>(pw.expert_of_pair, pairs, pw.offsets, pw.perm, pw.pos_of_pair);
-    wide_gather_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(rows_h, pw.perm, pw.src_of_pair, pairs, g.hidden, pw.act_h);
+    wide_gather_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(rows_h, pw.perm, pw.src_of_pair, pairs, g.hidden, pw.act_h, src_pitch);
     int rc = launch_status(4);
     if (rc != OK) return rc;
     mark_phase(2, s);
@@ -655,8 +677,98 @@ extern "C" int yvex_b200_ep_dispatch(const int32_t *selected, const float *weigh
     wide_scatter_kernel<<<(unsigned)world, 512, 0, s>>>(dest, pairs, offsets, order, inverse);
     ep_meta_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(selected, weights, order, pairs, (int)experts_per_rank, meta);
     wide_gather_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(static_cast<const __half *>(rows_f16), order, src, pairs, hidden,
-                                                              static_cast<__half *>(send_rows_f16));
+                                                              static_cast<__half *>(send_rows_f16), hidden * 2);
     return launch_status(5);
+}
+
+// Segmented dispatch: pairs grouped by (segment of the destination's local experts, destination rank), each
+// row sent with its trailer. bin = segment * world + rank, so one segment's rows for all ranks are contiguous.
+__global__ void ep_bin_kernel(const int32_t *selected, uint64_t pairs, uint64_t topk, int per_rank, int world, int segments, int *bin_of,
+                              int *src_token, int *counts, int *status) {
+    for (uint64_t p = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; p < pairs; p += (uint64_t)gridDim.x * blockDim.x) {
+        const int e = selected[p];
+        int d = e >= 0 ? e / per_rank : world, local = e >= 0 ? e % per_rank : 0;
+        src_token[p] = (int)(p / topk);
+        if (d >= world) { raise(status, YVEX_B200_STATUS_ARGUMENT); d = 0; local = 0; }      // keeps counts and order consistent
+        const int bin = (int)((int64_t)local * segments / per_rank) * world + d;
+        bin_of[p] = bin;
+        atomicAdd(&counts[bin], 1);
+    }
+}
+
+__global__ void ep_payload_kernel(const __half *rows_h, const int32_t *selected, const float *weights, const int *order,
+                                  const int *src_token, uint64_t pairs, uint64_t hidden, int per_rank, uint8_t *payload, uint64_t pitch) {
+    const uint32_t chunks = (uint32_t)(hidden / 8);
+    for (uint64_t pos = blockIdx.x; pos < pairs; pos += gridDim.x) {
+        const int p = order[pos];
+        const uint4 *src = reinterpret_cast<const uint4 *>(rows_h) + (uint64_t)src_token[p] * chunks;
+        uint4 *dst = reinterpret_cast<uint4 *>(payload + pos * pitch);
+        for (uint32_t c = threadIdx.x; c < chunks; c += blockDim.x) dst[c] = __ldg(src + c);
+        if (threadIdx.x == 0) {
+            const int e = selected[p];
+            const EpTrailer t{e >= 0 ? e % per_rank : 0, weights[p], p, 0};
+            *reinterpret_cast<EpTrailer *>(payload + pos * pitch + hidden * 2) = t;
+        }
+    }
+}
+
+extern "C" uint64_t yvex_b200_ep_payload_pitch(uint64_t hidden) { return hidden * 2 + sizeof(EpTrailer); }
+
+extern "C" int yvex_b200_ep_dispatch_payload(const int32_t *selected, const float *weights, const void *rows_f16, uint64_t tokens,
+                                             uint64_t topk, uint64_t hidden, uint64_t experts_per_rank, uint64_t world,
+                                             uint64_t segments, void *payload, int32_t *inverse, long long *send_counts,
+                                             void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
+    if (!selected || !weights || !rows_f16 || !payload || !inverse || !send_counts || !status || !workspace) return ERR_INVALID_ARG;
+    if (!tokens || !topk || !experts_per_rank || !world || !segments || world * segments > 1024 || segments > experts_per_rank ||
+        hidden % 8)
+        return ERR_INVALID_ARG;
+    const uint64_t pairs = tokens * topk, bins = world * segments;
+    if (pairs > 0x7fffff00ull || ((reinterpret_cast<uintptr_t>(rows_f16) | reinterpret_cast<uintptr_t>(payload)) & 15u)) return ERR_BOUNDS;
+    if (workspace_bytes < yvex_b200_ep_dispatch_workspace_bytes(pairs, bins)) return ERR_NOMEM;
+    int *bin_of = static_cast<int *>(workspace), *src = bin_of + pairs, *order = src + pairs;
+    int *counts = order + pairs, *offsets = counts + bins + 1;
+    cudaStream_t s = as_stream(stream);
+    cudaMemsetAsync(counts, 0, (bins + 1) * sizeof(int), s);
+    ep_bin_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(selected, pairs, topk, (int)experts_per_rank, (int)world, (int)segments, bin_of,
+                                                         src, counts, status);
+    ep_offsets_kernel<<<1, 32, 0, s>>>(counts, (int)bins, offsets, send_counts);
+    wide_scatter_kernel<<<(unsigned)bins, 512, 0, s>>>(bin_of, pairs, offsets, order, inverse);
+    ep_payload_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(static_cast<const __half *>(rows_f16), selected, weights, order, src, pairs,
+                                                             hidden, (int)experts_per_rank, static_cast<uint8_t *>(payload),
+                                                             yvex_b200_ep_payload_pitch(hidden));
+    return launch_status(4);
+}
+
+extern "C" int yvex_b200_moe_expert_rows_payload(const yvex_b200_moe_geometry *geom, const yvex_b200_moe_weights *w,
+                                                 const void *payload, uint64_t pairs, void *y_bf16, void *workspace,
+                                                 uint64_t workspace_bytes, int *status, void *stream) {
+    int rc = moe_check_geometry(geom, w);
+    if (rc != OK) return rc;
+    if (!pairs) return OK;
+    if (!payload || !y_bf16 || !status) return ERR_INVALID_ARG;
+    if (pairs > 0x7fffff00ull / 2 || (reinterpret_cast<uintptr_t>(payload) & 15u) || (reinterpret_cast<uintptr_t>(y_bf16) & 15u))
+        return ERR_BOUNDS;
+    MoeGeom g = *geom;
+    if (!moe_wide_gemm_eligible(g, *w)) return ERR_UNSUPPORTED;
+    PairWorkspace pw;
+    if (!workspace || workspace_bytes < pair_layout(g, pairs, 0, &pw)) return ERR_NOMEM;
+    pw.rebase(workspace);
+    cudaStream_t s = as_stream(stream);
+    const uint64_t pitch = yvex_b200_ep_payload_pitch(g.hidden);
+    mark_phase(0, s);
+    wide_list_payload_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(static_cast<const uint8_t *>(payload), pitch, g.hidden, pairs,
+                                                                   (int)g.experts, pw.expert_of_pair, pw.src_of_pair, pw.weight_of_pair);
+    mark_phase(1, s);
+    rc = run_pair_list(g, *w, pw, static_cast<const __half *>(payload), pairs, status, s, static_cast<uint16_t *>(y_bf16), pitch);
+    if (rc != OK) return rc;
+    mark_phase(5, s);
+    return launch_status(1);
+}
+
+extern "C" int yvex_b200_moe_wide_set_cta_limit(int ctas) {
+    if (ctas < 1 || ctas > kSmCount) return ERR_INVALID_ARG;
+    g_gemm_ctas.store(ctas, std::memory_order_relaxed);
+    return OK;
 }
 
 extern "C" uint64_t yvex_b200_expert_worklist_workspace_bytes(uint64_t pairs, uint64_t experts) {

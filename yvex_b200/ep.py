@@ -2,30 +2,156 @@
 
 Routed experts are sharded in contiguous blocks (expert e lives on rank e // (E / world)); the
 router, the shared expert and the tokens' home ranks are replicated / sharded by token. One
-layer is: route locally -> all-to-all-v dispatch of the bf16-exact token rows (as fp16) with
-their (local expert id, route weight) -> grouped dequant GEMMs on the receiving rank -> all-to-all-v
-of the per-pair bf16 rows back -> the home rank sums its k rows in rank order (f32) + its shared
-row -> bf16. Because per-pair rows (not partial sums) travel, the result is bit-identical to the
-single-device layer. The reference has no multi-device path at all (single process, one GPU);
-per-pair semantics are those of its CPU path (src/graph/moe.c:587-622, src/runtime/moe.c:619-632).
+layer is: route locally -> all-to-all-v dispatch of the bf16-exact token rows (as fp16, each with
+a 16-byte trailer naming its local expert and route weight) -> grouped dequant GEMMs on the
+receiving rank -> all-to-all-v of the per-pair bf16 rows back -> the home rank sums its k rows in
+rank order (f32) + its shared row -> bf16. Because per-pair rows (not partial sums) travel, the
+result is bit-identical to the single-device layer. The reference has no multi-device path at all
+(single process, one GPU); per-pair semantics are those of its CPU path
+(src/graph/moe.c:587-622, src/runtime/moe.c:619-632).
+
+Pipelining. A rank's local experts are cut into `segments` equal ranges and the pairs travel
+segment by segment: while the GEMMs of segment s run on the compute stream, the rows of segment
+s + 1 arrive and the results of segment s - 1 leave on the communication stream. Cutting by EXPERT
+keeps every expert's rows together, so the GEMM tiles are as full as without the pipeline. The
+shared expert needs no exchange: its GEMMs are enqueued first and cover the one host read of the
+split sizes and the first dispatch. All per-step buffers are allocated once and reused.
 
 Collectives go through torch.distributed (NCCL over NVLink on GPUs, gloo in the CPU tests); the
 compute calls go through the C-ABI of libyvex_b200.so (`DeviceOps`). The host logic takes the ops
-as a parameter so the world_size-2 gloo tests can drive it without a GPU.
+as a parameter so the world_size-2 gloo tests can drive it without a GPU (`TorchOps` is the plain
+tensor formulation of every step; `DeviceOps` replaces each with a library call).
 """
 from __future__ import annotations
+
+import contextlib
 
 import torch
 import torch.distributed as dist
 
+TRAILER_BYTES = 16
+ERR_TIMEOUT, ERR_BACKEND = -11, -6                    # yvex_status values (include/yvex_b200_backend.h)
 
-class DeviceOps:
-    """The layer's compute steps on the current CUDA device, via the C-ABI."""
 
-    def __init__(self, geom_full, geom_local, weights_local, status):
+class ExchangeError(RuntimeError):
+    """A collective of the layer failed on the host side: a peer left or stalled past the process group's
+    timeout (code ERR_TIMEOUT), or the communication backend reported another error (ERR_BACKEND). Nothing
+    was enqueued behind the failed exchange; the device is not waiting for anyone."""
+
+    def __init__(self, code, what):
+        super().__init__(f"expert-parallel exchange failed ({'timeout' if code == ERR_TIMEOUT else 'backend'}): {what}")
+        self.code = code
+
+
+class TorchOps:
+    """Every step of the layer as plain tensor operations: the specification of `DeviceOps`, and
+    what the CPU tests run (subclasses supply ingress / route / expert_rows / combine)."""
+
+    streams = None                                    # no side stream: steps run in program order
+    buf = {}                                          # step buffers (none: every step allocates what it returns)
+
+    def prepare(self, tokens, hidden, topk, world, segments):
+        pass
+
+    def pack(self, rows_h, ids, wts, home_pairs):
+        """rows_h [n, H] fp16 + trailer {int32 id, f32 weight, int32 home pair, 0} -> uint8 [n, 2H + 16]."""
+        n = rows_h.shape[0]
+        trailer = torch.zeros((n, 4), dtype=torch.int32, device=rows_h.device)
+        trailer[:, 0] = ids
+        trailer[:, 1] = wts.contiguous().view(torch.int32)
+        trailer[:, 2] = home_pairs
+        return torch.cat((rows_h.contiguous().view(torch.uint8).reshape(n, -1), trailer.view(torch.uint8).reshape(n, -1)), dim=1)
+
+    def unpack(self, payload, hidden):
+        n = payload.shape[0]
+        rows = payload[:, :2 * hidden].contiguous().view(torch.float16).reshape(n, hidden)
+        trailer = payload[:, 2 * hidden:].contiguous().view(torch.int32).reshape(n, 4)
+        return rows, trailer[:, 0].contiguous(), trailer[:, 1].contiguous().view(torch.float32)
+
+    def dispatch(self, xh, sel, wts, per_rank, world, segments):
+        """-> (payload [T*k, 2H+16] uint8 in send order, inverse [T*k] int32, counts [segments*world] int64).
+        Send order: by (segment of the local expert, destination rank), stable in the pair index."""
+        k = sel.shape[1]
+        flat = sel.reshape(-1).to(torch.int64)
+        dest, local = flat // per_rank, flat % per_rank
+        bins = (local * segments // per_rank) * world + dest
+        order = torch.argsort(bins, stable=True)
+        counts = torch.bincount(bins, minlength=world * segments)
+        rows = xh.index_select(0, torch.div(order, k, rounding_mode="floor"))
+        payload = self.pack(rows, local[order].to(torch.int32), wts.reshape(-1)[order], order.to(torch.int32))
+        inverse = torch.empty(order.numel(), dtype=torch.int32, device=order.device)
+        inverse[order] = torch.arange(order.numel(), dtype=torch.int32, device=order.device)
+        return payload, inverse, counts
+
+    def expert_rows_payload(self, payload, hidden, out=None):
+        rows, ids, wts = self.unpack(payload, hidden)
+        y = self.expert_rows(rows, ids, wts)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+
+    def shared_rows(self, xh):
+        t = xh.shape[0]
+        return self.expert_rows(xh, torch.full((t,), -1, dtype=torch.int32, device=xh.device),
+                                torch.ones(t, dtype=torch.float32, device=xh.device))
+
+
+class DeviceOps(TorchOps):
+    """The layer's compute steps on the current CUDA device, via the C-ABI. Owns the step buffers."""
+
+    def __init__(self, geom_full, geom_local, weights_local, status, overlap=True):
         from . import lib
         self.lib, self.geom_full, self.geom_local = lib, geom_full, geom_local
         self.weights, self.status = weights_local, status
+        self.overlap = overlap
+        self.streams = None
+        self.buf = {}
+
+    def prepare(self, tokens, hidden, topk, world, segments):
+        """Allocates (once per shape) everything a step needs: send / receive records, returned rows,
+        pair-list workspaces. Receive-side capacities start at twice the balanced load and grow on demand."""
+        key = (tokens, hidden, topk, world, segments)
+        if self.buf.get("key") == key:
+            return
+        dev = torch.device("cuda", torch.cuda.current_device())
+        pairs, pitch = tokens * topk, 2 * hidden + TRAILER_BYTES
+        b = {"key": key, "pitch": pitch}
+        b["payload"] = torch.empty((pairs, pitch), dtype=torch.uint8, device=dev)
+        b["inverse"] = torch.empty(pairs, dtype=torch.int32, device=dev)
+        b["counts"] = torch.empty(world * segments, dtype=torch.int64, device=dev)
+        b["counts_in"] = torch.empty(world * segments, dtype=torch.int64, device=dev)
+        b["counts_host"] = torch.empty(2 * world * segments, dtype=torch.int64).pin_memory()
+        b["plan_ws"] = torch.empty(int(self.lib.lib.yvex_b200_ep_dispatch_workspace_bytes(pairs, world * segments)),
+                                   dtype=torch.uint8, device=dev)
+        b["y_back"] = torch.empty((pairs, hidden), dtype=torch.bfloat16, device=dev)
+        b["y_shared"] = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
+        b["shared_ids"] = torch.full((tokens,), -1, dtype=torch.int32, device=dev)
+        b["shared_w"] = torch.ones(tokens, dtype=torch.float32, device=dev)
+        b["out"] = torch.empty((tokens, hidden), dtype=torch.float32, device=dev)
+        b["shared_ws"] = torch.empty(int(self.lib.lib.yvex_b200_moe_expert_rows_workspace_bytes(self.geom_local, tokens)),
+                                     dtype=torch.uint8, device=dev)
+        b["seg"] = [None] * segments
+        self.buf = b
+        if self.overlap and world > 1 and self.streams is None:
+            self.streams = (torch.cuda.Stream(device=dev, priority=-1),)          # communication stream, high priority
+            # the persistent GEMM leaves a few SMs to the exchange kernels that run beside it
+            self.lib.lib.yvex_b200_moe_wide_set_cta_limit(140)
+
+    def segment_buffers(self, seg, rows):
+        """Receive records, result rows and pair-list workspace of one segment, grown when a step needs more."""
+        b = self.buf
+        cur = b["seg"][seg]
+        if cur is None or cur["cap"] < rows:
+            cap = max(rows + rows // 4, 2 * b["key"][0] * b["key"][2] // b["key"][4], 1024)
+            dev = b["payload"].device
+            cur = {"cap": cap,
+                   "recv": torch.empty((cap, b["pitch"]), dtype=torch.uint8, device=dev),
+                   "y": torch.empty((cap, b["key"][1]), dtype=torch.bfloat16, device=dev),
+                   "ws": torch.empty(int(self.lib.lib.yvex_b200_moe_expert_rows_workspace_bytes(self.geom_local, cap)),
+                                     dtype=torch.uint8, device=dev)}
+            b["seg"][seg] = cur
+        return cur
 
     def ingress(self, x):
         return x.to(torch.bfloat16).to(torch.float16)          # RNE to bf16, then its fp16 image
@@ -36,75 +162,146 @@ class DeviceOps:
                                          logits=logits)
         return sel, wts
 
-    def dispatch(self, xh, sel, wts, per_rank, world):
-        """Send order, send rows, metadata, inverse index and split sizes in one library call."""
-        return self.lib.ep_dispatch(xh, sel.contiguous(), wts.contiguous(), per_rank, world, self.status)
+    def dispatch(self, xh, sel, wts, per_rank, world, segments):
+        b = self.buf
+        self.lib.ep_dispatch_payload(xh, sel.contiguous(), wts.contiguous(), per_rank, world, segments, self.status,
+                                     b["payload"], b["inverse"], b["counts"], b["plan_ws"])
+        return b["payload"], b["inverse"], b["counts"]
 
-    def expert_rows(self, rows_h, ids, wts):
-        return self.lib.moe_expert_rows(self.geom_local, self.weights, rows_h, ids, wts, self.status)
+    def expert_rows(self, rows_h, ids, wts, workspace=None, out=None):
+        return self.lib.moe_expert_rows(self.geom_local, self.weights, rows_h, ids, wts, self.status, workspace=workspace, out=out)
+
+    def shared_rows(self, xh):
+        b = self.buf
+        return self.expert_rows(xh, b["shared_ids"], b["shared_w"], workspace=b["shared_ws"], out=b["y_shared"])
+
+    def expert_rows_payload(self, payload, hidden, out=None, workspace=None):
+        return self.lib.moe_expert_rows_payload(self.geom_local, self.weights, payload, self.status, workspace=workspace, out=out)
 
     def combine(self, y_routed, y_shared, topk, routed_rows=None):
-        return self.lib.moe_combine(y_routed, y_shared, topk, self.status, routed_rows=routed_rows)
+        return self.lib.moe_combine(y_routed, y_shared, topk, self.status, routed_rows=routed_rows, out=self.buf.get("out"))
 
 
 class ExpertParallelLayer:
-    def __init__(self, experts, topk, ops, group=None):
+    def __init__(self, experts, topk, ops, group=None, segments=None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if experts % self.world:
             raise ValueError("experts must divide evenly over the ranks")
         self.experts, self.topk, self.per_rank, self.ops = experts, topk, experts // self.world, ops
+        if segments is None:
+            segments = 2 if self.world > 1 and self.per_rank % 2 == 0 else 1
+        if self.per_rank % segments:
+            raise ValueError("segments must divide the experts of a rank")
+        self.segments = segments
+        self.timings = None                    # when a dict: host-side cuda events of the last step's phases
 
-    def _all_to_all(self, send, send_counts, recv_counts, recv=None):
-        if recv is None:
-            recv = send.new_empty((sum(recv_counts),) + tuple(send.shape[1:]))
+    def _collective(self, recv, send, recv_counts=None, send_counts=None):
+        """all_to_all_single with the failure of a peer turned into ExchangeError: the process group's
+        timeout bounds the wait on the host, so a rank that left or stalled cannot hang this one."""
+        try:
+            dist.all_to_all_single(recv, send, recv_counts, send_counts, group=self.group)
+        except Exception as exc:                                            # DistBackendError, RuntimeError("Timed out ...")
+            text = str(exc)
+            late = any(w in text.lower() for w in ("timed out", "timeout", "connection closed", "connection reset", "peer"))
+            raise ExchangeError(ERR_TIMEOUT if late else ERR_BACKEND, text.splitlines()[0] if text else type(exc).__name__) from exc
+
+    def _all_to_all(self, recv, send, recv_counts, send_counts):
         if self.world == 1:
             recv.copy_(send)
         else:
-            dist.all_to_all_single(recv, send, recv_counts, send_counts, group=self.group)
-        return recv
+            self._collective(recv, send, recv_counts, send_counts)
 
     def forward(self, x, logits=None):
-        """x [t, hidden] f32 (this rank's tokens), logits [t, experts] or None -> out [t, hidden] f32."""
-        k, ops = self.topk, self.ops
-        t = x.shape[0]
+        """x [t, hidden] f32 (this rank's tokens), logits [t, experts] or None -> (out [t, hidden] f32, sel, wts)."""
+        k, ops, W, S = self.topk, self.ops, self.world, self.segments
+        t, hidden = x.shape
+        ops.prepare(t, hidden, k, W, S)
+        side = ops.streams[0] if ops.streams else None
+        on_side = (lambda: torch.cuda.stream(side)) if side is not None else contextlib.nullcontext
+        main = torch.cuda.current_stream() if side is not None else None
+
+        def after(stream_from, stream_to):
+            if side is not None:
+                ev = torch.cuda.Event()
+                ev.record(stream_from)
+                stream_to.wait_event(ev)
+
         xh = ops.ingress(x)
         sel, wts = ops.route(x, logits)                                   # [t, k] int32 / f32
-        fused = getattr(ops, "dispatch", None)
-        if fused is not None:                                             # one call instead of the tensor ops below
-            send_rows, meta, inverse, send_counts_t = fused(xh, sel, wts, self.per_rank, self.world)
+        payload, inverse, counts = ops.dispatch(xh, sel, wts, self.per_rank, W, S)
+        # split sizes: one tiny exchange and the step's only host read
+        after(main, side)
+        host = ops.buf.get("counts_host")
+        with on_side():
+            counts_in = ops.buf.get("counts_in")
+            if counts_in is None:
+                counts_in = torch.empty_like(counts)
+            if W == 1:
+                counts_in.copy_(counts)
+            else:
+                self._exchange_counts(counts_in, counts)
+            if host is not None:
+                host[:W * S].copy_(counts, non_blocking=True)
+                host[W * S:].copy_(counts_in, non_blocking=True)
+                done = torch.cuda.Event()
+                done.record()
+        # the shared expert needs nothing from other ranks: its GEMMs cover the host read and the first dispatch
+        y_shared = ops.shared_rows(xh)
+        if host is not None:
+            done.synchronize()
+            send_c, recv_c = host[:W * S].view(S, W).tolist(), host[W * S:].view(S, W).tolist()
         else:
-            dest = (sel // self.per_rank).reshape(-1).to(torch.int64)
-            order = torch.argsort(dest, stable=True)                      # pairs grouped by destination rank
-            send_counts_t = torch.bincount(dest, minlength=self.world)
-        recv_counts_t = torch.empty_like(send_counts_t)
-        if self.world == 1:
-            recv_counts_t.copy_(send_counts_t)
-        else:
-            dist.all_to_all_single(recv_counts_t, send_counts_t, group=self.group)
-        # the send buffers do not depend on the counts: enqueue them before the host reads the counts,
-        # so the device has work while the host waits
-        if fused is None:
-            send_rows = xh.index_select(0, torch.div(order, k, rounding_mode="floor"))
-            meta = torch.stack(((sel % self.per_rank).reshape(-1).to(torch.int32),
-                                wts.reshape(-1).contiguous().view(torch.int32)), dim=1).index_select(0, order).contiguous()
-            inverse = torch.empty(order.numel(), dtype=torch.int32, device=order.device)
-            inverse[order] = torch.arange(order.numel(), dtype=torch.int32, device=order.device)
-        send_counts, recv_counts = send_counts_t.tolist(), recv_counts_t.tolist()
-        # One pair list per rank: the received routed pairs, then this rank's own tokens for the (replicated)
-        # shared expert as pairs of expert -1 with weight 1 - one set of grouped GEMM launches instead of two.
-        # The routed rows are received straight into the head of the list's row buffer.
-        n_recv = sum(recv_counts)
-        rows_all = xh.new_empty((n_recv + t, xh.shape[1]))
-        self._all_to_all(send_rows, send_counts, recv_counts, recv=rows_all[:n_recv])
-        rows_all[n_recv:].copy_(xh)
-        recv_meta = self._all_to_all(meta, send_counts, recv_counts)
-        ids = torch.cat((recv_meta[:, 0], torch.full((t,), -1, dtype=torch.int32, device=x.device)))
-        pair_w = torch.cat((recv_meta[:, 1].contiguous().view(torch.float32), torch.ones(t, dtype=torch.float32, device=x.device)))
-        y_all = ops.expert_rows(rows_all, ids, pair_w)
-        y_recv, y_shared = y_all[:n_recv], y_all[n_recv:]
+            send_c, recv_c = counts.view(S, W).tolist(), counts_in.view(S, W).tolist()
 
-        y_back = self._all_to_all(y_recv, recv_counts, send_counts)      # reverse direction, same splits
+        hidden_pitch = payload.shape[1]
+        y_back = ops.buf.get("y_back")
+        if y_back is None:
+            y_back = torch.empty((t * k, hidden), dtype=torch.bfloat16, device=x.device)
+        send_off, seg_bufs = 0, []
+        # dispatch of every segment, in order, on the communication stream
+        with on_side():
+            for s in range(S):
+                n_send, n_recv = sum(send_c[s]), sum(recv_c[s])
+                if hasattr(ops, "segment_buffers"):
+                    sb = ops.segment_buffers(s, n_recv)
+                    recv, y_seg, ws = sb["recv"][:n_recv], sb["y"][:n_recv], sb["ws"]
+                else:
+                    recv, y_seg, ws = payload.new_empty((n_recv, hidden_pitch)), None, None
+                self._all_to_all(recv, payload[send_off:send_off + n_send], recv_c[s], send_c[s])
+                ev = None
+                if side is not None:
+                    ev = torch.cuda.Event()
+                    ev.record(side)
+                seg_bufs.append((recv, y_seg, ws, ev, send_off, n_send, n_recv))
+                send_off += n_send
+        # GEMMs of segment s on the compute stream, its results leave while segment s + 1 computes
+        back_events = []
+        for s, (recv, y_seg, ws, ev, off, n_send, n_recv) in enumerate(seg_bufs):
+            if ev is not None:
+                main.wait_event(ev)
+            if n_recv:
+                y_seg = ops.expert_rows_payload(recv, hidden, out=y_seg, workspace=ws) if ws is not None \
+                    else ops.expert_rows_payload(recv, hidden)
+            else:
+                y_seg = y_back.new_empty((0, hidden))
+            after(main, side)
+            with on_side():
+                self._all_to_all(y_back[off:off + n_send], y_seg, send_c[s], recv_c[s])      # reverse direction, same splits
+                if side is not None:
+                    e2 = torch.cuda.Event()
+                    e2.record(side)
+                    back_events.append(e2)
+        for e2 in back_events:
+            main.wait_event(e2)
         # pair (token, rank) sits at row inverse[...] of y_back: the combine reads through that index
         return ops.combine(y_back, y_shared, k, routed_rows=inverse), sel, wts
+
+    def _exchange_counts(self, counts_in, counts):
+        """counts is [segments][world]; rank r must receive entry [s][me] of every rank r' as its [s][r']."""
+        S, W = self.segments, self.world
+        send = counts.view(S, W).t().contiguous().view(-1)                 # [world][segments]
+        recv = torch.empty_like(send)
+        self._collective(recv, send)
+        counts_in.copy_(recv.view(W, S).t().contiguous().view(-1))

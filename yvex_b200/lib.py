@@ -65,6 +65,11 @@ def _load():
     lib.yvex_b200_ep_dispatch_workspace_bytes.restype = u64
     lib.yvex_b200_ep_dispatch_workspace_bytes.argtypes = [u64, u64]
     lib.yvex_b200_ep_dispatch.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, vp, vp, vp, vp, vp, u64, vp, vp]
+    lib.yvex_b200_ep_payload_pitch.restype = u64
+    lib.yvex_b200_ep_payload_pitch.argtypes = [u64]
+    lib.yvex_b200_ep_dispatch_payload.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, vp, vp, vp, vp, u64, vp, vp]
+    lib.yvex_b200_moe_expert_rows_payload.argtypes = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights), vp, u64, vp, vp, u64, vp, vp]
+    lib.yvex_b200_moe_wide_set_cta_limit.argtypes = [C.c_int]
     lib.yvex_b200_attention_workspace_bytes.restype = u64
     lib.yvex_b200_attention_workspace_bytes.argtypes = [u64] * 5
     lib.yvex_b200_dequant_rows.argtypes = [C.c_uint, vp, u64, u64, u64, vp, vp, vp]
@@ -107,7 +112,9 @@ EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_ge
            "yvex_b200_attention_f32", "yvex_b200_attention_static_scratch_bytes",
            "yvex_b200_attention_gqa_decode_static", "yvex_b200_mhc_workspace_bytes", "yvex_b200_mhc_prepare",
            "yvex_b200_mhc_post", "yvex_b200_expert_worklist_workspace_bytes", "yvex_b200_expert_worklist",
-           "yvex_b200_selftest_bounded_wait", "yvex_b200_moe_wide_uses_gemm", "yvex_b200_moe_wide_tile_columns"]
+           "yvex_b200_selftest_bounded_wait", "yvex_b200_moe_wide_uses_gemm", "yvex_b200_moe_wide_tile_columns",
+           "yvex_b200_ep_payload_pitch", "yvex_b200_ep_dispatch_payload", "yvex_b200_moe_expert_rows_payload",
+           "yvex_b200_moe_wide_set_cta_limit"]
 
 
 def _torch():
@@ -297,6 +304,44 @@ def expert_worklist(selected, experts, status, tensor_core_minimum=0, admitted_w
     return dict(order=order.cpu().numpy(), source_rows=src.cpu().numpy(), destination_rows=dst.cpu().numpy(),
                 expert_ids=ids.cpu().numpy()[:n], bucket_offsets=offs.cpu().numpy()[:n + 1],
                 bucket_populations=pops.cpu().numpy()[:n], observation=o)
+
+
+def ep_dispatch_payload(rows_f16, selected, route_weights, experts_per_rank, world, segments, status, payload=None, inverse=None,
+                        counts=None, workspace=None):
+    """Segmented sending side: rows_f16 [T, hidden] fp16, selected / route_weights [T, k] -> (payload [T*k, 2*hidden + 16] uint8
+    in send order (segment, destination rank), inverse [T*k] int32, counts [segments * world] int64)."""
+    torch = _torch()
+    tokens, hidden = rows_f16.shape
+    pairs, dev, bins = tokens * selected.shape[1], rows_f16.device, world * segments
+    pitch = int(lib.yvex_b200_ep_payload_pitch(hidden))
+    if payload is None:
+        payload = torch.empty((pairs, pitch), dtype=torch.uint8, device=dev)
+    if inverse is None:
+        inverse = torch.empty(pairs, dtype=torch.int32, device=dev)
+    if counts is None:
+        counts = torch.empty(bins, dtype=torch.int64, device=dev)
+    if workspace is None:
+        workspace = torch.empty(int(lib.yvex_b200_ep_dispatch_workspace_bytes(pairs, bins)), dtype=torch.uint8, device=dev)
+    _check(lib.yvex_b200_ep_dispatch_payload(_p(selected), _p(route_weights), _p(rows_f16), tokens, selected.shape[1], hidden,
+                                             experts_per_rank, world, segments, _p(payload), _p(inverse), _p(counts), _p(workspace),
+                                             workspace.numel(), _p(status.word), _stream()), "ep_dispatch_payload")
+    return payload, inverse, counts
+
+
+def moe_expert_rows_payload(geom, weights, payload, status, workspace=None, out=None):
+    """Received records (hidden fp16 values + trailer per row) on this device's expert shard -> bf16 rows [P, hidden]."""
+    torch = _torch()
+    pairs = payload.shape[0]
+    if out is None:
+        out = torch.empty((pairs, geom.hidden), dtype=torch.bfloat16, device=payload.device)
+    if pairs == 0:
+        return out
+    if workspace is None:
+        workspace = torch.empty(int(lib.yvex_b200_moe_expert_rows_workspace_bytes(C.byref(geom), pairs)),
+                                dtype=torch.uint8, device=payload.device)
+    _check(lib.yvex_b200_moe_expert_rows_payload(C.byref(geom), C.byref(weights), _p(payload), pairs, _p(out), _p(workspace),
+                                                 workspace.numel(), _p(status.word), _stream()), "moe_expert_rows_payload")
+    return out
 
 
 def moe_route(geom, weights, status, rows_f32=None, logits=None, token_ids=None):
