@@ -314,7 +314,7 @@ extern "C" int yvex_b200_gemv(unsigned int qtype, const void *encoded, uint64_t 
     if (rc != OK) return rc;
     const uint8_t *enc = static_cast<const uint8_t *>(encoded);
     // input rows are a batch that shares one matrix
-    if (gs::stream_eligible(qtype, rows, width, row_bytes, enc, 0, input_rows))
+    if (gs::stream_eligible(qtype, rows, width, row_bytes, enc, 0, input_rows, input, width))
         return gs::stream_launch(qtype, enc, 0, input_rows, rows, width, row_bytes, input, width, additive, out, rows, round_bf16, status,
                                  as_stream(stream));
     if (gemv_mma_eligible(qtype, rows, width, enc) &&
@@ -344,7 +344,7 @@ extern "C" int yvex_b200_gemv_batch(unsigned int qtype, const void *encoded, uin
     if (rc != OK) return rc;
     if (input_stride < width || out_stride < rows || (count > 1 && matrix_stride < rows * row_bytes)) return ERR_BOUNDS;
     const uint8_t *enc = static_cast<const uint8_t *>(encoded);
-    if (gs::stream_eligible(qtype, rows, width, row_bytes, enc, matrix_stride, count))
+    if (gs::stream_eligible(qtype, rows, width, row_bytes, enc, matrix_stride, count, input, input_stride))
         return gs::stream_launch(qtype, enc, matrix_stride, count, rows, width, row_bytes, input, input_stride, additive, out, out_stride,
                                  round_bf16, status, as_stream(stream));
     // shapes and qtypes the streaming kernel does not take: one matvec per matrix

@@ -28,6 +28,8 @@
 // that ONE byte permute builds a lookup address from the raw index byte. The 64 KiB image is a
 // constant of the module and arrives by one bulk copy while the first tiles are in flight.
 #pragma once
+#include <cstdlib>
+
 #include "qtype_decode.cuh"
 #include "tcgen05.cuh"
 
@@ -37,15 +39,14 @@ namespace gs {
 constexpr int kMaxDepth = 6, kMaxConsumers = 16, kTileRows = 16;
 constexpr uint32_t kTableBytes = 64 * 1024;
 
-__device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, bool first) {
-    if (first) {
-        asm(
-            "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+template <bool kFirst>
+__device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if (kFirst) {
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
             : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
     } else {
-        asm(
-            "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
             : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
     }
@@ -74,79 +75,109 @@ constexpr Iq2StreamTable make_iq2_stream_table() {
 }
 __device__ const Iq2StreamTable kIq2StreamTable = make_iq2_stream_table();
 
+// Loads by 32-bit shared-window address. Not volatile, so that the compiler may schedule them freely;
+// every address they are given derives from a register that was redefined (an empty volatile asm)
+// after the wait that made the data visible, which keeps them behind that wait.
+__device__ __forceinline__ uint32_t lds32(uint32_t a) { uint32_t v; asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t lds16(uint32_t a) { uint16_t v; asm("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint32_t lds8(uint32_t a) { uint32_t v; asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ uint2 lds64(uint32_t a) { uint2 v; asm("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+// Byte permute as the hardware does it (the CUDA intrinsic first masks bit 3 of every selector nibble, one
+// more instruction per call; the selectors used here never set it) and a right shift by a constant on the
+// multiplier pipe instead of the half-rate integer pipe that the decode saturates.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+template <int kBits> __device__ __forceinline__ uint32_t shr_mul(uint32_t v) { return kBits ? __umulhi(v, 1u << (32 - kBits)) : v; }
+
+__device__ __forceinline__ float ldsf(uint32_t a) { float v; asm("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a)); return v; }
+// A block scale is acceptable when it is a finite, non-negative f16: as an unsigned pattern, anything above
+// 65504.0f is larger than that, infinite, NaN or negative.
+__device__ __forceinline__ bool scale_bad(float d) { return __float_as_uint(d) > 0x477fe000u; }
+
 // ---- per-lane state shared by the decoders ---------------------------------------------------------------
 struct Lane {
     int g, t;                         // MMA row (and row + 8) / quad lane = group within a half block
-    const uint8_t *b_hi, *b_lo;       // this lane's B source for digit planes (3,2) / (1,0) at k = 0 of its K-slice
     uint32_t nib_base, sgn_base;      // IQ2_XXS: table address with the lane's bank in byte 0, index byte still 0
 };
+
+// The B operand of one 256-weight unit: bh[4h + j] / bl[4h + j] are this lane's fragments of digit planes
+// (3,2) / (1,0) for half h, subgroup j - non-zero only in the lane that owns the column's group.
+struct BUnit { uint2 bh[8], bl[8]; };
+
+__device__ __forceinline__ float comb(int a_hi, int a_lo, int b_hi, int b_lo) {
+    return fmaf((float)(a_hi * 128 + a_lo), 16384.0f, (float)(b_hi * 128 + b_lo));
+}
 
 // What a decoder provides:
 //   kBlockBytes / kBlockK   bytes and weights of the unit a warp walks (IQ2_XXS, Q4_K: one 256-weight
 //                           superblock; Q8_0: eight 32-weight blocks, so that every qtype has 8 groups per unit)
 //   unit(...)               adds this lane's share of the dot products of rows g and g + 8 with the
-//                           activation over one unit to acc[0] / acc[1] (in units of 2^-27 * x scale)
+//                           activation over one unit to acc[0] / acc[1] (in units of 2^-27 * x scale);
+//                           bad bit 0 / 1: a malformed block scale in row g / g + 8
 struct StreamIq2 {
     static constexpr unsigned kQtype = Q_IQ2_XXS;
     static constexpr int kBlockBytes = 66, kBlockK = 256;
     static constexpr bool kTables = true, kSums = false;
 
-    __device__ __forceinline__ static void group(const uint8_t *p, uint32_t &grids, uint32_t &ss) {
+    __device__ __forceinline__ static void group(uint32_t a, uint32_t &grids, uint32_t &ss) {
         // a group starts on a 2-byte boundary: three aligned words, funnel-shifted when it sits mid-word
-        const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-        const uint32_t sh = (uint32_t)(a & 2u) * 8u;
-        const uint32_t *w = reinterpret_cast<const uint32_t *>(a & ~static_cast<uintptr_t>(3));
-        const uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
+        const uint32_t sh = (a & 2u) * 8u, w = a & ~3u;
+        const uint32_t w0 = lds32(w), w1 = lds32(w + 4), w2 = lds32(w + 8);
         grids = __funnelshift_r(w0, w1, sh);
         ss = __funnelshift_r(w1, w2, sh);
     }
     // One subgroup of 8 weights -> two registers of signed bytes.
     template <int J> __device__ __forceinline__ static void sub(uint32_t grids, uint32_t ss, const Lane &l, uint32_t &lo, uint32_t &hi) {
         constexpr uint32_t kPos = 8u | (25u << 8) | (43u << 16), kNeg = 0xf8u | (0xe7u << 8) | (0xd5u << 16);
-        const uint32_t na = __byte_perm(grids, l.nib_base, 0x7604u | ((uint32_t)J << 4));
-        const uint32_t sa = __byte_perm(J ? ss >> (7 * J) : ss, l.sgn_base, 0x7604u);
+        const uint32_t na = prmt(grids, l.nib_base, 0x7604u | ((uint32_t)J << 4));
+        const uint32_t sa = prmt(shr_mul<7 * J>(ss), l.sgn_base, 0x7604u);
         uint32_t nib, sgn;
         // reads of a table that never changes once it has arrived: free to be scheduled anywhere after
         // the point where the lane's table base registers were (re)defined, i.e. after the arrival wait
         asm("ld.shared.u32 %0, [%1];" : "=r"(nib) : "r"(na));
         asm("ld.shared.u32 %0, [%1];" : "=r"(sgn) : "r"(sa));
         const uint32_t sel = nib | sgn;
-        lo = __byte_perm(kPos, kNeg, sel);
-        hi = __byte_perm(kPos, kNeg, sel >> 16);
+        lo = prmt(kPos, kNeg, sel);
+        hi = prmt(kPos, kNeg, shr_mul<16>(sel));
     }
-    __device__ __forceinline__ static float comb(int a_hi, int a_lo, int b_hi, int b_lo) {
-        return fmaf((float)(a_hi * 128 + a_lo), 16384.0f, (float)(b_hi * 128 + b_lo));
+    // Everything below is written out over compile-time (half, subgroup) indices: the table addresses, shift
+    // counts and fragment registers are then all static.
+    template <int H, int J> __device__ __forceinline__ static void step(uint32_t g0, uint32_t s0, uint32_t g1, uint32_t s1, const BUnit &b,
+                                                                        const Lane &l, int (&ca)[4], int (&cb)[4]) {
+        uint32_t a[4];
+        sub<J>(g0, s0, l, a[0], a[2]);
+        sub<J>(g1, s1, l, a[1], a[3]);
+        mma_s8<J == 0>(ca, a, b.bh[4 * H + J].x, b.bh[4 * H + J].y);
+        mma_s8<J == 0>(cb, a, b.bl[4 * H + J].x, b.bl[4 * H + J].y);
     }
-    __device__ __forceinline__ static void unit(const uint8_t *row0, const uint8_t *row1, int kofs, const Lane &l, const float *,
+    template <int H> __device__ __forceinline__ static void half(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, float &blk0,
+                                                                 float &blk1) {
+        uint32_t g0, s0, g1, s1;
+        group(row0 + 2 + 8 * (4 * H + l.t), g0, s0);
+        group(row1 + 2 + 8 * (4 * H + l.t), g1, s1);
+        int ca[4], cb[4];
+        step<H, 0>(g0, s0, g1, s1, b, l, ca, cb);
+        step<H, 1>(g0, s0, g1, s1, b, l, ca, cb);
+        step<H, 2>(g0, s0, g1, s1, b, l, ca, cb);
+        step<H, 3>(g0, s0, g1, s1, b, l, ca, cb);
+        blk0 = fmaf(comb(ca[0], ca[1], cb[0], cb[1]), (float)((s0 >> 27) | 1u), blk0);       // 2 * sub + 1
+        blk1 = fmaf(comb(ca[2], ca[3], cb[2], cb[3]), (float)((s1 >> 27) | 1u), blk1);
+    }
+    __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t,
                                                 float (&acc)[2], int &bad) {
         float blk0 = 0.0f, blk1 = 0.0f;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            uint32_t g0, s0, g1, s1;
-            group(row0 + 2 + 8 * (4 * h + l.t), g0, s0);
-            group(row1 + 2 + 8 * (4 * h + l.t), g1, s1);
-            int ca[4], cb[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t a[4];
-                switch (j) {
-                case 0: sub<0>(g0, s0, l, a[0], a[2]); sub<0>(g1, s1, l, a[1], a[3]); break;
-                case 1: sub<1>(g0, s0, l, a[0], a[2]); sub<1>(g1, s1, l, a[1], a[3]); break;
-                case 2: sub<2>(g0, s0, l, a[0], a[2]); sub<2>(g1, s1, l, a[1], a[3]); break;
-                default: sub<3>(g0, s0, l, a[0], a[2]); sub<3>(g1, s1, l, a[1], a[3]); break;
-                }
-                const int k = kofs + 128 * h + 8 * j;
-                const uint2 bh = *reinterpret_cast<const uint2 *>(l.b_hi + k), bl = *reinterpret_cast<const uint2 *>(l.b_lo + k);
-                mma_s8(ca, a, bh.x, bh.y, j == 0);
-                mma_s8(cb, a, bl.x, bl.y, j == 0);
-            }
-            blk0 = fmaf(comb(ca[0], ca[1], cb[0], cb[1]), (float)((s0 >> 27) | 1u), blk0);       // 2 * sub + 1
-            blk1 = fmaf(comb(ca[2], ca[3], cb[2], cb[3]), (float)((s1 >> 27) | 1u), blk1);
-        }
-        const float f0 = f16_bits_to_float(*reinterpret_cast<const uint16_t *>(row0));
-        const float f1 = f16_bits_to_float(*reinterpret_cast<const uint16_t *>(row1));
-        bad |= !(f0 >= 0.0f && f0 <= 65504.0f) ? 1 : 0;
-        bad |= !(f1 >= 0.0f && f1 <= 65504.0f) ? 2 : 0;
+        half<0>(row0, row1, b, l, blk0, blk1);
+        half<1>(row0, row1, b, l, blk0, blk1);
+        const float f0 = f16_bits_to_float((uint16_t)lds16(row0)), f1 = f16_bits_to_float((uint16_t)lds16(row1));
+        bad |= (scale_bad(f0) ? 1 : 0) | (scale_bad(f1) ? 2 : 0);
         acc[0] = fmaf(blk0, 0.125f * f0, acc[0]);
         acc[1] = fmaf(blk1, 0.125f * f1, acc[1]);
     }
@@ -160,46 +191,56 @@ struct StreamQ4k {
     static constexpr int kBlockBytes = 144, kBlockK = 256;
     static constexpr bool kTables = false, kSums = true;
 
-    __device__ __forceinline__ static void scale_min(const uint8_t *s, int j, uint32_t &sc, uint32_t &m) {
-        if (j < 4) { sc = s[j] & 63u; m = s[j + 4] & 63u; }
-        else { sc = (s[j + 4] & 15u) | ((s[j - 4] >> 6) << 4); m = (s[j + 4] >> 4) | ((s[j] >> 6) << 4); }
+    // 6-bit (scale, min) of sub-block j from the 12 packed bytes behind d and dmin (three aligned words)
+    __device__ __forceinline__ static void scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int h, int t, uint32_t &sc, uint32_t &m) {
+        if (h == 0) {                                   // sub-blocks 0..3: low six bits of bytes t and t + 4
+            sc = (s0 >> (8 * t)) & 63u;
+            m = (s1 >> (8 * t)) & 63u;
+        } else {                                        // sub-blocks 4..7: nibbles of byte t + 8, top bits from bytes t and t + 4
+            const uint32_t b = (s2 >> (8 * t)) & 255u;
+            sc = (b & 15u) | (((s0 >> (8 * t + 6)) & 3u) << 4);
+            m = (b >> 4) | (((s1 >> (8 * t + 6)) & 3u) << 4);
+        }
     }
-    __device__ __forceinline__ static void unit(const uint8_t *row0, const uint8_t *row1, int kofs, const Lane &l, const float *sums,
+    template <int H, int J> __device__ __forceinline__ static void step(const uint32_t (&w0)[8], const uint32_t (&w1)[8], int shift,
+                                                                        const BUnit &b, int (&ca)[4], int (&cb)[4]) {
+        uint32_t a[4];
+        a[0] = (w0[2 * J] >> shift) & 0x0f0f0f0fu; a[2] = (w0[2 * J + 1] >> shift) & 0x0f0f0f0fu;
+        a[1] = (w1[2 * J] >> shift) & 0x0f0f0f0fu; a[3] = (w1[2 * J + 1] >> shift) & 0x0f0f0f0fu;
+        mma_s8<J == 0>(ca, a, b.bh[4 * H + J].x, b.bh[4 * H + J].y);
+        mma_s8<J == 0>(cb, a, b.bl[4 * H + J].x, b.bl[4 * H + J].y);
+    }
+    template <int H> __device__ __forceinline__ static void half(uint32_t row0, uint32_t row1, const uint4 &head0, const uint4 &head1,
+                                                                 const BUnit &b, const Lane &l, uint32_t sums, float &blk0, float &blk1,
+                                                                 float &min0, float &min1) {
+        const int sb = 4 * H + l.t, shift = 4 * (sb & 1);
+        const uint32_t c0 = row0 + 16 + 32 * (sb >> 1), c1 = row1 + 16 + 32 * (sb >> 1);
+        const uint4 x0 = lds128(c0), x1 = lds128(c0 + 16), y0 = lds128(c1), y1 = lds128(c1 + 16);
+        const uint32_t w0[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        const uint32_t w1[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+        int ca[4], cb[4];
+        step<H, 0>(w0, w1, shift, b, ca, cb);
+        step<H, 1>(w0, w1, shift, b, ca, cb);
+        step<H, 2>(w0, w1, shift, b, ca, cb);
+        step<H, 3>(w0, w1, shift, b, ca, cb);
+        uint32_t sc0, m0, sc1, m1;
+        scale_min(head0.y, head0.z, head0.w, H, l.t, sc0, m0);
+        scale_min(head1.y, head1.z, head1.w, H, l.t, sc1, m1);
+        const float xs = ldsf(sums + 4 * sb);                    // sum of the activation over this sub-block, in the same units
+        blk0 = fmaf(comb(ca[0], ca[1], cb[0], cb[1]), (float)sc0, blk0);
+        blk1 = fmaf(comb(ca[2], ca[3], cb[2], cb[3]), (float)sc1, blk1);
+        min0 = fmaf((float)m0, xs, min0);
+        min1 = fmaf((float)m1, xs, min1);
+    }
+    __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t sums,
                                                 float (&acc)[2], int &bad) {
         float blk0 = 0.0f, blk1 = 0.0f, min0 = 0.0f, min1 = 0.0f;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int sb = 4 * h + l.t, shift = 4 * (sb & 1);
-            const uint4 *q0 = reinterpret_cast<const uint4 *>(row0 + 16 + 32 * (sb >> 1));
-            const uint4 *q1 = reinterpret_cast<const uint4 *>(row1 + 16 + 32 * (sb >> 1));
-            const uint4 x0 = q0[0], x1 = q0[1], y0 = q1[0], y1 = q1[1];
-            const uint32_t w0[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-            const uint32_t w1[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
-            int ca[4], cb[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t a[4];
-                a[0] = (w0[2 * j] >> shift) & 0x0f0f0f0fu; a[2] = (w0[2 * j + 1] >> shift) & 0x0f0f0f0fu;
-                a[1] = (w1[2 * j] >> shift) & 0x0f0f0f0fu; a[3] = (w1[2 * j + 1] >> shift) & 0x0f0f0f0fu;
-                const int k = kofs + 128 * h + 8 * j;
-                const uint2 bh = *reinterpret_cast<const uint2 *>(l.b_hi + k), bl = *reinterpret_cast<const uint2 *>(l.b_lo + k);
-                mma_s8(ca, a, bh.x, bh.y, j == 0);
-                mma_s8(cb, a, bl.x, bl.y, j == 0);
-            }
-            uint32_t sc0, m0, sc1, m1;
-            scale_min(row0 + 4, sb, sc0, m0);
-            scale_min(row1 + 4, sb, sc1, m1);
-            const float xs = sums[(kofs >> 5) + sb];                 // sum of the activation over this sub-block, in the same units
-            blk0 = fmaf(StreamIq2::comb(ca[0], ca[1], cb[0], cb[1]), (float)sc0, blk0);
-            blk1 = fmaf(StreamIq2::comb(ca[2], ca[3], cb[2], cb[3]), (float)sc1, blk1);
-            min0 = fmaf((float)m0, xs, min0);
-            min1 = fmaf((float)m1, xs, min1);
-        }
-        const uint32_t dd0 = *reinterpret_cast<const uint32_t *>(row0), dd1 = *reinterpret_cast<const uint32_t *>(row1);
-        const float d0 = f16_bits_to_float((uint16_t)dd0), n0 = f16_bits_to_float((uint16_t)(dd0 >> 16));
-        const float d1 = f16_bits_to_float((uint16_t)dd1), n1 = f16_bits_to_float((uint16_t)(dd1 >> 16));
-        bad |= !(d0 >= 0.0f && d0 <= 65504.0f && n0 >= 0.0f && n0 <= 65504.0f) ? 1 : 0;
-        bad |= !(d1 >= 0.0f && d1 <= 65504.0f && n1 >= 0.0f && n1 <= 65504.0f) ? 2 : 0;
+        const uint4 head0 = lds128(row0), head1 = lds128(row1);          // d, dmin and the 12 scale bytes
+        half<0>(row0, row1, head0, head1, b, l, sums, blk0, blk1, min0, min1);
+        half<1>(row0, row1, head0, head1, b, l, sums, blk0, blk1, min0, min1);
+        const float d0 = f16_bits_to_float((uint16_t)head0.x), n0 = f16_bits_to_float((uint16_t)(head0.x >> 16));
+        const float d1 = f16_bits_to_float((uint16_t)head1.x), n1 = f16_bits_to_float((uint16_t)(head1.x >> 16));
+        bad |= (scale_bad(d0) || scale_bad(n0) ? 1 : 0) | (scale_bad(d1) || scale_bad(n1) ? 2 : 0);
         acc[0] += fmaf(d0, blk0, -n0 * min0);
         acc[1] += fmaf(d1, blk1, -n1 * min1);
     }
@@ -212,41 +253,43 @@ struct StreamQ80 {
     static constexpr int kBlockBytes = 8 * 34, kBlockK = 256;
     static constexpr bool kTables = false, kSums = false;
 
-    __device__ __forceinline__ static void block(const uint8_t *p, uint32_t (&q)[8], float &d, int &bad, int flag) {
+    __device__ __forceinline__ static void block(uint32_t a, uint32_t (&q)[8], float &d, int &bad, int flag) {
         // the block starts on a 2-byte boundary: nine aligned words, funnel-shifted when it sits mid-word
-        const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-        const uint32_t sh = (uint32_t)(a & 2u) * 8u;
-        const uint32_t *w = reinterpret_cast<const uint32_t *>(a & ~static_cast<uintptr_t>(3));
+        const uint32_t sh = (a & 2u) * 8u, w = a & ~3u;
         uint32_t v[9];
 #pragma unroll
-        for (int i = 0; i < 9; ++i) v[i] = w[i];
+        for (int i = 0; i < 9; ++i) v[i] = lds32(w + 4 * i);
         const uint32_t head = __funnelshift_r(v[0], v[1], sh);
         d = f16_bits_to_float((uint16_t)head);
-        bad |= !(d >= 0.0f && d <= 65504.0f) ? flag : 0;
+        bad |= scale_bad(d) ? flag : 0;
         // quants start 2 bytes into the block
 #pragma unroll
         for (int i = 0; i < 8; ++i) q[i] = sh ? v[i + 1] : __funnelshift_r(v[i], v[i + 1], 16);
     }
-    __device__ __forceinline__ static void unit(const uint8_t *row0, const uint8_t *row1, int kofs, const Lane &l, const float *,
+    template <int H, int J> __device__ __forceinline__ static void step(const uint32_t (&q0)[8], const uint32_t (&q1)[8], const BUnit &b,
+                                                                        int (&ca)[4], int (&cb)[4]) {
+        const uint32_t a[4] = {q0[2 * J], q1[2 * J], q0[2 * J + 1], q1[2 * J + 1]};
+        mma_s8<J == 0>(ca, a, b.bh[4 * H + J].x, b.bh[4 * H + J].y);
+        mma_s8<J == 0>(cb, a, b.bl[4 * H + J].x, b.bl[4 * H + J].y);
+    }
+    template <int H> __device__ __forceinline__ static void half(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, float (&acc)[2],
+                                                                 int &bad) {
+        uint32_t q0[8], q1[8];
+        float d0, d1;
+        block(row0 + 34 * (4 * H + l.t), q0, d0, bad, 1);
+        block(row1 + 34 * (4 * H + l.t), q1, d1, bad, 2);
+        int ca[4], cb[4];
+        step<H, 0>(q0, q1, b, ca, cb);
+        step<H, 1>(q0, q1, b, ca, cb);
+        step<H, 2>(q0, q1, b, ca, cb);
+        step<H, 3>(q0, q1, b, ca, cb);
+        acc[0] = fmaf(comb(ca[0], ca[1], cb[0], cb[1]), d0, acc[0]);
+        acc[1] = fmaf(comb(ca[2], ca[3], cb[2], cb[3]), d1, acc[1]);
+    }
+    __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t,
                                                 float (&acc)[2], int &bad) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            uint32_t q0[8], q1[8];
-            float d0, d1;
-            block(row0 + 34 * (4 * h + l.t), q0, d0, bad, 1);
-            block(row1 + 34 * (4 * h + l.t), q1, d1, bad, 2);
-            int ca[4], cb[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t a[4] = {q0[2 * j], q1[2 * j], q0[2 * j + 1], q1[2 * j + 1]};
-                const int k = kofs + 128 * h + 8 * j;
-                const uint2 bh = *reinterpret_cast<const uint2 *>(l.b_hi + k), bl = *reinterpret_cast<const uint2 *>(l.b_lo + k);
-                mma_s8(ca, a, bh.x, bh.y, j == 0);
-                mma_s8(cb, a, bl.x, bl.y, j == 0);
-            }
-            acc[0] = fmaf(StreamIq2::comb(ca[0], ca[1], cb[0], cb[1]), d0, acc[0]);
-            acc[1] = fmaf(StreamIq2::comb(ca[2], ca[3], cb[2], cb[3]), d1, acc[1]);
-        }
+        half<0>(row0, row1, b, l, acc, bad);
+        half<1>(row0, row1, b, l, acc, bad);
     }
 };
 
@@ -256,7 +299,7 @@ struct StreamParams {
     uint64_t matrix_stride;             // bytes from one matrix to the next
     uint32_t count;                     // matrices
     uint64_t rows, row_bytes;
-    int K, slices, units_per_slice, row_groups, depth;
+    int K, slices, units_per_slice, row_warps, depth;      // consumer warps = slices x row_warps
     uint32_t stage_bytes, smem_bytes;
     const float *x;                     // input vector of matrix m at x + m * x_stride
     uint64_t x_stride;
@@ -267,6 +310,8 @@ struct StreamParams {
     int *status;
 };
 
+constexpr int kMaxGroupsPerWarp = 2;    // 16-row groups one consumer warp decodes per stage (independent work in flight)
+
 struct StreamCtl {
     uint64_t full[kMaxDepth], empty[kMaxDepth], red_full[kMaxDepth + 1], tab_full;
     uint32_t stage[kMaxDepth];          // shared-window addresses
@@ -275,20 +320,29 @@ struct StreamCtl {
     int abort, layout_bad;
 };
 
-// Bytes of dynamic shared memory the kernel needs in the worst placement of the 64 KiB table window.
-__host__ __device__ inline uint32_t stream_small_bytes(int K, int consumers, int depth, int units_per_slice) {
-    return (uint32_t)(4 * K + 256 * units_per_slice + 128 + (K / 32) * 4 + 128 + (depth + 1) * consumers * kTileRows * 4 + 256);
+__host__ __device__ inline uint32_t stream_small_bytes(int K, int consumers, int depth, int units_per_slice, int groups) {
+    return (uint32_t)(4 * K + 256 * units_per_slice + 128 + (K / 32) * 4 + 128 + (depth + 1) * consumers * groups * kTileRows * 4 + 256);
 }
 
-template <class Dec>
+// The task list of one CTA, walked without divisions: tile `tile` of matrix `m`.
+struct TaskCursor {
+    uint32_t m;
+    uint64_t tile, tiles_m;
+    __device__ __forceinline__ void init(uint64_t q, uint64_t per_matrix) { tiles_m = per_matrix; m = (uint32_t)(q / per_matrix); tile = q - (uint64_t)m * per_matrix; }
+    __device__ __forceinline__ void next() { if (++tile == tiles_m) { tile = 0; ++m; } }
+};
+
+// kBReg: the warp's whole K-slice is one unit, so its B fragments live in registers from one matrix change to the next.
+// kGroupsPerWarp: 16-row groups a consumer warp decodes per stage.
+template <class Dec, bool kBReg, int kGroupsPerWarp>
 __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kernel(const StreamParams p) {
     using namespace sm100;
     extern __shared__ __align__(128) uint8_t dyn[];
     __shared__ StreamCtl ctl;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int consumers = p.slices * p.row_groups;
+    const int consumers = p.slices * p.row_warps;
     const int D = p.depth;
-    const uint32_t tile_rows = (uint32_t)(kTileRows * p.row_groups);
+    const uint32_t warp_rows = (uint32_t)(kTileRows * kGroupsPerWarp), tile_rows = warp_rows * (uint32_t)p.row_warps;
     const uint64_t tiles_m = (p.rows + tile_rows - 1) / tile_rows, Q = (uint64_t)p.count * tiles_m;
     const uint64_t q0 = Q * blockIdx.x / gridDim.x, q1 = Q * (blockIdx.x + 1) / gridDim.x;
     const uint32_t n_local = (uint32_t)(q1 - q0);
@@ -309,7 +363,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
         ctl.planes = take((uint32_t)(4 * p.K));
         ctl.zeros = take((uint32_t)(256 * p.units_per_slice + 16));
         ctl.sums = take((uint32_t)(p.K / 32) * 4u);
-        ctl.red = take((uint32_t)((D + 1) * consumers * kTileRows) * 4u);
+        ctl.red = take((uint32_t)((D + 1) * consumers * kGroupsPerWarp * kTileRows) * 4u);
         ctl.table = tab;
         ctl.layout_bad = cur > end || (Dec::kTables && tab + kTableBytes > end);
         ctl.abort = 0;
@@ -324,11 +378,9 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
         return;
     }
     auto generic = [&](uint32_t shared_addr) { return dyn + (shared_addr - smem_u32(dyn)); };
-    auto task = [&](uint32_t i, uint32_t &m, uint64_t &row0, uint32_t &nrows) {
-        const uint64_t q = q0 + i;
-        m = (uint32_t)(q / tiles_m);
-        row0 = (q - (uint64_t)m * tiles_m) * tile_rows;
-        nrows = (uint32_t)(p.rows - row0 < tile_rows ? p.rows - row0 : tile_rows);
+    auto rows_of = [&](const TaskCursor &c, uint64_t &row0) {
+        row0 = c.tile * tile_rows;
+        return (uint32_t)(p.rows - row0 < tile_rows ? p.rows - row0 : tile_rows);
     };
 
     if (warp == consumers) {
@@ -337,16 +389,20 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
             mbar_expect_tx(&ctl.tab_full, kTableBytes);
             bulk_load(generic(ctl.table), &kIq2StreamTable, kTableBytes, &ctl.tab_full);
         }
+        TaskCursor ci, cj;                                   // next tile to fetch / next tile to publish
+        ci.init(q0, tiles_m);
+        cj.init(q0, tiles_m);
         uint32_t issued = 0;
         bool ok = true;
-        for (uint32_t j = 0; j < n_local && ok; ++j) {
+        const int per_tile = consumers * kGroupsPerWarp * kTileRows;
+        for (uint32_t j = 0; j < n_local && ok; ++j, cj.next()) {
             while (issued < n_local && issued < j + (uint32_t)D && ok) {
                 const uint32_t slot = issued % D;
                 if (issued >= (uint32_t)D) ok = mbar_wait_warp(&ctl.empty[slot], ((issued / D) - 1u) & 1u, &ctl.abort);
                 if (!ok) break;
-                uint32_t m; uint64_t row0; uint32_t nrows;
-                task(issued, m, row0, nrows);
-                const uint8_t *src = p.enc + (uint64_t)m * p.matrix_stride + row0 * p.row_bytes;
+                uint64_t row0;
+                const uint32_t nrows = rows_of(ci, row0);
+                const uint8_t *src = p.enc + (uint64_t)ci.m * p.matrix_stride + row0 * p.row_bytes;
                 const uint32_t bytes = (uint32_t)(nrows * p.row_bytes), bulk = bytes & ~15u;
                 uint8_t *dst = generic(ctl.stage[slot]);
                 if (lane < (int)(bytes - bulk)) dst[bulk + lane] = __ldg(src + bulk + lane);      // the last < 16 bytes of a ragged tile
@@ -356,21 +412,23 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
                     if (bulk) bulk_load(dst, src, bulk, &ctl.full[slot]);
                 }
                 ++issued;
+                ci.next();
             }
             if (!ok) break;
             const uint32_t buf = j % (uint32_t)(D + 1);
             ok = mbar_wait_warp(&ctl.red_full[buf], (j / (uint32_t)(D + 1)) & 1u, &ctl.abort);
             if (!ok) break;
-            uint32_t m; uint64_t row0; uint32_t nrows;
-            task(j, m, row0, nrows);
-            const float *red = reinterpret_cast<const float *>(generic(ctl.red)) + (size_t)buf * consumers * kTileRows;
-            const float scale = ctl.xscale[m & 7u];
-            if ((uint32_t)lane < nrows) {
-                const int rg = lane / kTileRows, r = lane % kTileRows;
+            uint64_t row0;
+            const uint32_t nrows = rows_of(cj, row0);
+            // partial sums of the tile: [row warp][slice][group][16 rows]
+            const float *red = reinterpret_cast<const float *>(generic(ctl.red)) + (size_t)buf * per_tile;
+            const float scale = ctl.xscale[cj.m & 7u];
+            for (uint32_t r = lane; r < nrows; r += 32) {
+                const uint32_t rw = r / warp_rows, in_warp = r % warp_rows;
                 float sum = 0.0f;
-                for (int s = 0; s < p.slices; ++s) sum += red[(rg * p.slices + s) * kTileRows + r];        // fixed order
+                for (int s = 0; s < p.slices; ++s) sum += red[((size_t)rw * p.slices + s) * warp_rows + in_warp];        // fixed order
                 sum *= scale;
-                const uint64_t at = (uint64_t)m * p.out_stride + row0 + lane;
+                const uint64_t at = (uint64_t)cj.m * p.out_stride + row0 + r;
                 if (p.additive) sum += p.additive[at];
                 if (!isfinite(sum)) raise(p.status, YVEX_B200_STATUS_NUMERIC);
                 p.out[at] = p.round_bf16 ? bf16_round(sum) : sum;
@@ -389,23 +447,30 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
     // ---------------- consumer warps ----------------
     Lane l;
     l.g = lane >> 2; l.t = lane & 3;
-    const int sl = warp % p.slices, rg = warp / p.slices;
+    const int sl = warp % p.slices, rw = warp / p.slices;
     const int unit0 = sl * p.units_per_slice, nunits_total = p.K / Dec::kBlockK;
     const int my_units = min(p.units_per_slice, nunits_total - unit0);
     const bool b_active = (lane & 3) == (lane >> 3);                        // column n = lane >> 2 belongs to group n >> 1
-    const uint8_t *planes = generic(ctl.planes), *zeros = generic(ctl.zeros);
     // column 2t' carries the higher plane of a pair, column 2t' + 1 the lower one
     const int col_plane = (lane >> 2) & 1;
-    l.b_hi = b_active ? planes + (size_t)(0 + col_plane) * p.K + unit0 * Dec::kBlockK + 32 * (lane >> 3) : zeros;
-    l.b_lo = b_active ? planes + (size_t)(2 + col_plane) * p.K + unit0 * Dec::kBlockK + 32 * (lane >> 3) : zeros;
+    uint32_t b_hi = b_active ? ctl.planes + (uint32_t)((0 + col_plane) * p.K + unit0 * Dec::kBlockK + 32 * (lane >> 3)) : ctl.zeros;
+    uint32_t b_lo = b_active ? ctl.planes + (uint32_t)((2 + col_plane) * p.K + unit0 * Dec::kBlockK + 32 * (lane >> 3)) : ctl.zeros;
     l.nib_base = (ctl.table & 0xffff0000u) | (uint32_t)(lane * 4);
     l.sgn_base = l.nib_base + 128u;
-    const float *sums = reinterpret_cast<const float *>(generic(ctl.sums)) + unit0 * (Dec::kBlockK / 32);
+    uint32_t sums = ctl.sums + (uint32_t)(unit0 * (Dec::kBlockK / 32) * 4);
+    const uint32_t row_bytes = (uint32_t)p.row_bytes;
     float *red_all = reinterpret_cast<float *>(generic(ctl.red));
     const int cthreads = consumers * 32;
     if (threadIdx.x < 64 * p.units_per_slice + 4) reinterpret_cast<uint32_t *>(generic(ctl.zeros))[threadIdx.x] = 0u;
+    auto load_b = [&](BUnit &b, int u) {
+#pragma unroll
+        for (int hj = 0; hj < 8; ++hj) {
+            const uint32_t k = (uint32_t)(u * Dec::kBlockK + 128 * (hj >> 2) + 8 * (hj & 3));
+            b.bh[hj] = lds64(b_hi + k);
+            b.bl[hj] = lds64(b_lo + k);
+        }
+    };
 
-    uint32_t cur_m = 0xffffffffu;
     // A warp whose wait ran out keeps walking the task list without touching data, so that it still
     // meets the other consumers at the named barriers of every matrix change and nobody waits for it.
     bool dead = false;
@@ -413,14 +478,18 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
         if (!mbar_wait_warp(&ctl.tab_full, 0u, &ctl.abort)) dead = true;
         asm volatile("" : "+r"(l.nib_base), "+r"(l.sgn_base));      // table reads may not move above this point
     }
-    for (uint32_t i = 0; i < n_local; ++i) {
-        uint32_t m; uint64_t row0; uint32_t nrows;
-        task(i, m, row0, nrows);
-        if (m != cur_m) {
+    BUnit breg;
+    uint32_t cur_m = 0xffffffffu;
+    TaskCursor c;
+    c.init(q0, tiles_m);
+    for (uint32_t i = 0; i < n_local; ++i, c.next()) {
+        uint64_t row0;
+        const uint32_t nrows = rows_of(c, row0);
+        if (c.m != cur_m) {
             // a new matrix: its activation row becomes four planes of signed base-128 digits. Every
             // consumer has finished the previous matrix once it is past this barrier.
             asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
-            const float *x = p.x + (uint64_t)m * p.x_stride;
+            const float *x = p.x + (uint64_t)c.m * p.x_stride;
             float mx = 0.0f;
             bool badx = false;
             for (int k = threadIdx.x; k < p.K; k += cthreads) {
@@ -439,16 +508,17 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
             int e = 0;
             if (mx > 0.0f && isfinite(mx)) frexpf(mx, &e);
             const float to_q = ldexpf(1.0f, 27 - e);
-            if (threadIdx.x == 0) ctl.xscale[m & 7u] = ldexpf(1.0f, e - 27);
+            if (threadIdx.x == 0) ctl.xscale[c.m & 7u] = ldexpf(1.0f, e - 27);
             int8_t *pl = reinterpret_cast<int8_t *>(generic(ctl.planes));
             float *sm = reinterpret_cast<float *>(generic(ctl.sums));
             for (int k8 = threadIdx.x; k8 < p.K / 8; k8 += cthreads) {
                 uint32_t d[4][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}, {0u, 0u}};
                 float s = 0.0f;
+                const float4 xa = __ldg(reinterpret_cast<const float4 *>(x + 8 * k8)), xb = __ldg(reinterpret_cast<const float4 *>(x + 8 * k8) + 1);
+                const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
 #pragma unroll
                 for (int i8 = 0; i8 < 8; ++i8) {
-                    const float v = __ldg(x + 8 * k8 + i8);
-                    int q = isfinite(v) ? __float2int_rn(v * to_q) : 0;
+                    int q = isfinite(xv[i8]) ? __float2int_rn(xv[i8] * to_q) : 0;
                     s += (float)q;
                     // balanced digits: d0..d2 in [-64, 63], the top digit takes what is left (|d3| <= 64)
                     const int d0 = ((q + 64) & 127) - 64; q = (q - d0) >> 7;
@@ -468,58 +538,75 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
                 }
             }
             asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
-            cur_m = m;
+            asm volatile("" : "+r"(b_hi), "+r"(b_lo), "+r"(sums));      // reads of the new planes stay behind the barrier
+            if (kBReg) load_b(breg, 0);
+            cur_m = c.m;
         }
         const uint32_t slot = i % D, buf = i % (uint32_t)(D + 1);
         if (!dead && !mbar_wait_warp(&ctl.full[slot], (i / D) & 1u, &ctl.abort)) dead = true;
-        float acc[2] = {0.0f, 0.0f};
-        int bad = 0;
-        if (!dead && (uint32_t)(kTileRows * rg) < nrows) {
-            const uint8_t *stage = generic(ctl.stage[slot]);
-            const uint8_t *row0p = stage + (size_t)(kTileRows * rg + l.g) * p.row_bytes + (size_t)unit0 * Dec::kBlockBytes;
-            const uint8_t *row1p = row0p + 8 * p.row_bytes;
-            for (int u = 0; u < my_units; ++u)
-                Dec::unit(row0p + (size_t)u * Dec::kBlockBytes, row1p + (size_t)u * Dec::kBlockBytes, u * Dec::kBlockK, l, sums, acc, bad);
+        float acc[kGroupsPerWarp][2];
+        int bad[kGroupsPerWarp];
+#pragma unroll
+        for (int gi = 0; gi < kGroupsPerWarp; ++gi) { acc[gi][0] = acc[gi][1] = 0.0f; bad[gi] = 0; }
+        const uint32_t first = warp_rows * (uint32_t)rw;                     // this warp's first row within the tile
+        if (!dead && first < nrows) {
+            uint32_t base = ctl.stage[slot] + (first + (uint32_t)l.g) * row_bytes + (uint32_t)(unit0 * Dec::kBlockBytes);
+            asm volatile("" : "+r"(base));                              // reads of the stage stay behind the wait above
+            for (int u = 0; u < my_units; ++u) {
+                BUnit bmem;
+                if (!kBReg) load_b(bmem, u);
+                const BUnit &b = kBReg ? breg : bmem;
+#pragma unroll
+                for (int gi = 0; gi < kGroupsPerWarp; ++gi) {
+                    // groups past a ragged tile's last row decode stale bytes; their results are never stored
+                    const uint32_t r0 = base + (uint32_t)(kTileRows * gi) * row_bytes + (uint32_t)(u * Dec::kBlockBytes);
+                    Dec::unit(r0, r0 + 8 * row_bytes, b, l, sums + (uint32_t)(u * (Dec::kBlockK / 32) * 4), acc[gi], bad[gi]);
+                }
+            }
         }
         // this warp is done with the stage
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl.empty[slot]);
-        acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
-        acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 2);
-        acc[1] += __shfl_xor_sync(0xffffffffu, acc[1], 1);
-        acc[1] += __shfl_xor_sync(0xffffffffu, acc[1], 2);
-        float *red = red_all + ((size_t)buf * consumers + warp) * kTileRows;
-        if (l.t == 0) { red[l.g] = acc[0]; red[l.g + 8] = acc[1]; }
-        // a malformed block scale only counts for rows that exist (rows past a ragged tile hold stale bytes)
-        const uint32_t r_lo = (uint32_t)(kTileRows * rg + l.g), r_hi = r_lo + 8;
-        if (((bad & 1) && r_lo < nrows) || ((bad & 2) && r_hi < nrows)) raise(p.status, YVEX_B200_STATUS_NUMERIC);
+        float *red = red_all + ((size_t)buf * consumers + warp) * warp_rows;
+#pragma unroll
+        for (int gi = 0; gi < kGroupsPerWarp; ++gi) {
+            float a0 = acc[gi][0], a1 = acc[gi][1];
+            a0 += __shfl_xor_sync(0xffffffffu, a0, 1); a0 += __shfl_xor_sync(0xffffffffu, a0, 2);
+            a1 += __shfl_xor_sync(0xffffffffu, a1, 1); a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+            if (l.t == 0) { red[kTileRows * gi + l.g] = a0; red[kTileRows * gi + l.g + 8] = a1; }
+            // a malformed block scale only counts for rows that exist
+            const uint32_t r_lo = first + (uint32_t)(kTileRows * gi + l.g), r_hi = r_lo + 8;
+            if (((bad[gi] & 1) && r_lo < nrows) || ((bad[gi] & 2) && r_hi < nrows)) raise(p.status, YVEX_B200_STATUS_NUMERIC);
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl.red_full[buf]);
     }
 }
 
 // ---- host side -----------------------------------------------------------------------------------------------
-struct StreamShape { int slices, units_per_slice, row_groups, consumers, depth; uint32_t stage_bytes, smem_bytes; };
+struct StreamShape { int slices, units_per_slice, row_warps, consumers, depth, groups; uint32_t stage_bytes, smem_bytes; };
 
-// K-slices (consumer warps along K), units per slice, row groups per stage and the deepest ring that fits.
+// K-slices (consumer warps along K), units per slice, warps along the rows of a stage and the deepest ring that fits.
 inline bool stream_shape(uint64_t width, uint64_t row_bytes, bool tables, StreamShape &sh) {
     const int units = (int)(width / 256);
     if (!units || width % 256 || width > 8192) return false;
     sh.units_per_slice = (units + kMaxConsumers - 1) / kMaxConsumers;
     sh.slices = (units + sh.units_per_slice - 1) / sh.units_per_slice;
-    sh.row_groups = sh.slices <= kMaxConsumers / 2 ? 2 : 1;
-    sh.consumers = sh.slices * sh.row_groups;
-    sh.stage_bytes = (uint32_t)(kTileRows * sh.row_groups * row_bytes);
-    const uint32_t limit = 227u * 1024u - 1024u;
-    for (sh.depth = kMaxDepth; sh.depth >= 2; --sh.depth) {
-        // every piece is rounded up to 128 bytes; one piece may have to step over the table window
-        const uint32_t pieces = (uint32_t)sh.depth * (sh.stage_bytes + 16 + 128) + stream_small_bytes((int)width, sh.consumers, sh.depth, sh.units_per_slice) + 5 * 128;
-        sh.smem_bytes = pieces + (tables ? 2 * kTableBytes : 0u);
-        // with tables: the window starts at most 64 KiB - 1 into the allocation and whatever lies before it stays
-        // usable, so the worst case is one stage of slack, not a second 64 KiB
-        if (tables) sh.smem_bytes = pieces + kTableBytes + sh.stage_bytes + 16 + 128;
-        if (tables && sh.smem_bytes < 2 * kTableBytes) sh.smem_bytes = 2 * kTableBytes;
-        if (sh.smem_bytes <= limit) return true;
+    sh.row_warps = sh.slices <= kMaxConsumers / 2 ? 2 : 1;
+    sh.consumers = sh.slices * sh.row_warps;
+    const uint32_t limit = 226u * 1024u;                   // the kernel also has a few hundred bytes of static shared memory
+    // two row groups per warp when at least three such stages fit, else one
+    for (sh.groups = kMaxGroupsPerWarp; sh.groups >= 1; --sh.groups) {
+        sh.stage_bytes = (uint32_t)(kTileRows * sh.groups * sh.row_warps * row_bytes);
+        for (sh.depth = kMaxDepth; sh.depth >= (sh.groups > 1 ? 3 : 2); --sh.depth) {
+            // every piece is rounded up to 128 bytes; with tables one piece may have to step over the table window,
+            // which starts at most 64 KiB - 1 into the allocation (what lies before it stays usable)
+            const uint32_t pieces = (uint32_t)sh.depth * (sh.stage_bytes + 16 + 128) +
+                                    stream_small_bytes((int)width, sh.consumers, sh.depth, sh.units_per_slice, sh.groups) + 5 * 128;
+            sh.smem_bytes = tables ? pieces + kTableBytes + sh.stage_bytes + 16 + 128 : pieces;
+            if (tables && sh.smem_bytes < 2 * kTableBytes) sh.smem_bytes = 2 * kTableBytes;
+            if (sh.smem_bytes <= limit) return true;
+        }
     }
     return false;
 }
@@ -527,21 +614,30 @@ inline bool stream_shape(uint64_t width, uint64_t row_bytes, bool tables, Stream
 inline bool stream_qtype(unsigned q) { return q == Q_IQ2_XXS || q == Q_Q4_K || q == Q_Q8_0; }
 
 inline bool stream_eligible(unsigned q, uint64_t rows, uint64_t width, uint64_t row_bytes, const void *enc, uint64_t matrix_stride,
-                            uint64_t count) {
+                            uint64_t count, const float *x, uint64_t x_stride) {
     StreamShape sh;
     return stream_qtype(q) && rows && count && count <= 0xffffffffull && (reinterpret_cast<uintptr_t>(enc) & 15u) == 0 &&
-           matrix_stride % 16 == 0 && stream_shape(width, row_bytes, q == Q_IQ2_XXS, sh);
+           matrix_stride % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && x_stride % 4 == 0 &&
+           stream_shape(width, row_bytes, q == Q_IQ2_XXS, sh);
+}
+
+template <class Dec, bool kBReg, int kG>
+inline int stream_launch_v(StreamParams &p, const StreamShape &sh, cudaStream_t stream) {
+    static SmemOptIn opt_in;
+    if (opt_in.ensure(gemv_stream_kernel<Dec, kBReg, kG>, 226 * 1024) != OK) return ERR_BACKEND;
+    const uint64_t tile_rows = (uint64_t)kTileRows * kG * sh.row_warps;
+    const uint64_t tasks = (uint64_t)p.count * ((p.rows + tile_rows - 1) / tile_rows);
+    const unsigned grid = (unsigned)(tasks < (uint64_t)kSmCount ? tasks : (uint64_t)kSmCount);
+    gemv_stream_kernel<Dec, kBReg, kG><<<grid, 32 * (sh.consumers + 1), sh.smem_bytes, stream>>>(p);
+    return launch_status(1);
 }
 
 template <class Dec>
 inline int stream_launch_t(StreamParams &p, const StreamShape &sh, cudaStream_t stream) {
-    static SmemOptIn opt_in;
-    if (opt_in.ensure(gemv_stream_kernel<Dec>, 227 * 1024) != OK) return ERR_BACKEND;
-    const uint64_t tile_rows = (uint64_t)kTileRows * sh.row_groups;
-    const uint64_t tasks = (uint64_t)p.count * ((p.rows + tile_rows - 1) / tile_rows);
-    const unsigned grid = (unsigned)(tasks < (uint64_t)kSmCount ? tasks : (uint64_t)kSmCount);
-    gemv_stream_kernel<Dec><<<grid, 32 * (sh.consumers + 1), sh.smem_bytes, stream>>>(p);
-    return launch_status(1);
+    static const bool allow_breg = !getenv("YVEX_B200_STREAM_NO_BREG");
+    const bool breg = sh.units_per_slice == 1 && allow_breg;
+    if (sh.groups == 2) return breg ? stream_launch_v<Dec, true, 2>(p, sh, stream) : stream_launch_v<Dec, false, 2>(p, sh, stream);
+    return breg ? stream_launch_v<Dec, true, 1>(p, sh, stream) : stream_launch_v<Dec, false, 1>(p, sh, stream);
 }
 
 inline int stream_launch(unsigned q, const uint8_t *enc, uint64_t matrix_stride, uint64_t count, uint64_t rows, uint64_t width,
@@ -551,7 +647,7 @@ inline int stream_launch(unsigned q, const uint8_t *enc, uint64_t matrix_stride,
     if (!stream_shape(width, row_bytes, q == Q_IQ2_XXS, sh)) return ERR_BOUNDS;
     StreamParams p{};
     p.enc = enc; p.matrix_stride = matrix_stride; p.count = (uint32_t)count; p.rows = rows; p.row_bytes = row_bytes;
-    p.K = (int)width; p.slices = sh.slices; p.units_per_slice = sh.units_per_slice; p.row_groups = sh.row_groups; p.depth = sh.depth;
+    p.K = (int)width; p.slices = sh.slices; p.units_per_slice = sh.units_per_slice; p.row_warps = sh.row_warps; p.depth = sh.depth;
     p.stage_bytes = sh.stage_bytes; p.smem_bytes = sh.smem_bytes;
     p.x = x; p.x_stride = x_stride; p.additive = additive; p.out = out; p.out_stride = out_stride;
     p.round_bf16 = round_bf16; p.status = status;

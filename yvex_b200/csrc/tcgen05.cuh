@@ -13,6 +13,7 @@ namespace sm100 {
 // (%globaltimer), whatever a single poll costs; the poll count is only a backstop.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 constexpr uint32_t kSpinLimit = 1u << 30;
+constexpr uint32_t kTryWaitHintNs = 2000u;      // how long one try_wait may keep the thread suspended before it reports "not yet"
 
 __device__ __forceinline__ uint64_t global_ns() {
     uint64_t t;
@@ -41,9 +42,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(kTryWaitHintNs) : "memory");
     return ok != 0;
 }
 // Waits for the phase with the given parity to complete. Gives up after `limit_ns` (or as soon as
