@@ -494,8 +494,13 @@ def run_native_ep(args):
     spec_local = type(spec)(H, e_loc, spec.topk, I, down_qtype=spec.down_qtype)
     geom_local = lib.geometry_of(spec_local)
     status = lib.Status(dev)
-    ops = DeviceOps(geom_full, geom_local, lib.weights_of(shard), status)
-    layer = ExpertParallelLayer(E, spec.topk, ops)
+    # experiment knobs (defaults are what the library picks): segments of the exchange pipeline, whether the exchange runs
+    # on its own stream beside the GEMMs, CTAs of the persistent GEMM
+    ops = DeviceOps(geom_full, geom_local, lib.weights_of(shard), status, overlap=os.environ.get("YVEX_EP_OVERLAP", "1") != "0")
+    seg_env = os.environ.get("YVEX_EP_SEGMENTS")
+    layer = ExpertParallelLayer(E, spec.topk, ops, segments=int(seg_env) if seg_env else None)
+    if os.environ.get("YVEX_EP_CTAS"):
+        ops.cta_limit = int(os.environ["YVEX_EP_CTAS"])
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     host_x, host_lg = x.cpu().pin_memory(), lg.cpu().pin_memory()
     host_out = torch.empty((t_loc, H), dtype=torch.float32).pin_memory()
@@ -576,50 +581,55 @@ def run_native_ep(args):
         ms = timed(step, args.steps)
         launches = lib.lib.yvex_b200_launch_count() - launches0
         ms_e2e = timed(step_e2e, args.steps, wall=world == 1)
-        # GEMM phases of the routed pair list, timed with the library's phase events
-        n_ph, gemm_ms, pair_counts = 7, [[], [], []], []       # events 0..5 in order, 6 = after SwiGLU
-        real_rows = ops.expert_rows
+        # GEMM phases of one pair list, timed with the library's phase events, and (N > 1) the spans of the
+        # pipelined step on the compute stream
+        n_ph, gemm_ms, pair_counts, spans = 7, [[], [], []], [], {}       # events 0..5 in order, 6 = after SwiGLU
 
-        def probed(rows_h, ids, wts):
-            if rows_h.shape[0] and not probed.done:
-                probed.done = True
-                evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_ph)]
-                for e in evs:
-                    e.record()
-                arr = (C.c_void_p * n_ph)(*[e.cuda_event for e in evs])
-                lib.lib.yvex_b200_phase_events(arr, n_ph)
-                y = real_rows(rows_h, ids, wts)
-                lib.lib.yvex_b200_phase_events(None, 0)
-                torch.cuda.synchronize()
-                gemm_ms[0].append(evs[2].elapsed_time(evs[3]))
-                gemm_ms[1].append(evs[6].elapsed_time(evs[4]))
-                gemm_ms[2].append(evs[3].elapsed_time(evs[6]))
-                pair_counts.append(rows_h.shape[0])
-                return y
-            return real_rows(rows_h, ids, wts)
+        def phase_probe(run):
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_ph)]
+            for e in evs:
+                e.record()
+            arr = (C.c_void_p * n_ph)(*[e.cuda_event for e in evs])
+            lib.lib.yvex_b200_phase_events(arr, n_ph)
+            y = run()
+            lib.lib.yvex_b200_phase_events(None, 0)
+            torch.cuda.synchronize()
+            gemm_ms[0].append(evs[2].elapsed_time(evs[3]))
+            gemm_ms[1].append(evs[6].elapsed_time(evs[4]))
+            gemm_ms[2].append(evs[3].elapsed_time(evs[6]))
+            return y
 
         if world == 1:
             for i in range(min(args.steps, 5)):
-                evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_ph)]
-                for e in evs:
-                    e.record()
-                arr = (C.c_void_p * n_ph)(*[e.cuda_event for e in evs])
                 flush.fill_(i & 0xFF)
-                lib.lib.yvex_b200_phase_events(arr, n_ph)
-                step(i)
-                lib.lib.yvex_b200_phase_events(None, 0)
-                torch.cuda.synchronize()
-                gemm_ms[0].append(evs[2].elapsed_time(evs[3]))
-                gemm_ms[1].append(evs[6].elapsed_time(evs[4]))
-                gemm_ms[2].append(evs[3].elapsed_time(evs[6]))
+                phase_probe(lambda: step(i))
                 pair_counts.append(T * (spec.topk + 1))
         else:
-            ops.expert_rows = probed
+            real_payload = ops.expert_rows_payload
+
+            def probed(payload, hidden, out=None, workspace=None):
+                if payload.shape[0] and not probed.done:
+                    probed.done = True
+                    pair_counts.append(payload.shape[0])
+                    return phase_probe(lambda: real_payload(payload, hidden, out=out, workspace=workspace))
+                return real_payload(payload, hidden, out=out, workspace=workspace)
+
+            ops.expert_rows_payload = probed
             for i in range(min(args.steps, 5)):
                 probed.done = False
                 flush.fill_(i & 0xFF)
                 step(i)
-            ops.expert_rows = real_rows
+            ops.expert_rows_payload = real_payload
+            layer.timings = {}
+            for i in range(min(args.steps, 5)):
+                flush.fill_(i & 0xFF)
+                barrier()
+                step(i)
+                torch.cuda.synchronize()
+                marks = layer.timings["marks"]
+                for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+                    spans.setdefault(name, []).append(a.elapsed_time(b))
+            layer.timings = None
         torch.cuda.synchronize()
     if status.read() != 0:
         raise RuntimeError(f"device status word = {status.read()} after the timed region")
@@ -679,13 +689,16 @@ def run_native_ep(args):
                 "data": "synthetic",
                 "config": {"workload": wl.name, **cfg, "gate_up_qtype": "IQ2_XXS", "down_qtype": "Q4_K",
                            "l2": "flushed between steps (256 MiB rewrite)",
-                           "parallelism": (f"ep{world}: {e_loc} experts and {t_loc} tokens per rank, NCCL all-to-all-v" if world > 1
+                           "parallelism": (f"ep{world}: {e_loc} experts and {t_loc} tokens per rank, NCCL all-to-all-v in "
+                                           f"{layer.segments} expert segments pipelined against the GEMMs" if world > 1
                                            else "ep1: all experts on one device, fused wide layer, no exchange")},
                 "clocks": clocks.summary(),
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(T * (H + E) * 4),
                         "d2h_bytes_per_step": int(T * H * 4), "api": e2e_api},
                 "gpu_launches": int(launches * world),
-                "phases_ms": {"gate_up_gemm": gu, "swiglu": sw, "down_gemm": dn},
+                "phases_ms": {"gate_up_gemm": gu, "swiglu": sw, "down_gemm": dn,
+                              **({"pairs_in_timed_gemm": pairs, "step_spans_rank0": {k: sum(v) / len(v) for k, v in spans.items()}}
+                                 if world > 1 else {})},
                 "parity": parity, "twin": twin,
                 "roofline": roofline, "cpu_baseline": cpu}
         print(json.dumps(line), flush=True)

@@ -105,6 +105,7 @@ class DeviceOps(TorchOps):
         self.lib, self.geom_full, self.geom_local = lib, geom_full, geom_local
         self.weights, self.status = weights_local, status
         self.overlap = overlap
+        self.cta_limit = 140                   # CTAs of the persistent GEMM while an exchange runs beside it
         self.streams = None
         self.buf = {}
 
@@ -136,7 +137,7 @@ class DeviceOps(TorchOps):
         if self.overlap and world > 1 and self.streams is None:
             self.streams = (torch.cuda.Stream(device=dev, priority=-1),)          # communication stream, high priority
             # the persistent GEMM leaves a few SMs to the exchange kernels that run beside it
-            self.lib.lib.yvex_b200_moe_wide_set_cta_limit(140)
+            self.lib.lib.yvex_b200_moe_wide_set_cta_limit(self.cta_limit)
 
     def segment_buffers(self, seg, rows):
         """Receive records, result rows and pair-list workspace of one segment, grown when a step needs more."""
@@ -228,9 +229,20 @@ class ExpertParallelLayer:
                 ev.record(stream_from)
                 stream_to.wait_event(ev)
 
+        marks = []
+
+        def mark(name):
+            """Phase boundary on the compute stream (only while self.timings is a dict)."""
+            if self.timings is not None and x.is_cuda:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
         xh = ops.ingress(x)
         sel, wts = ops.route(x, logits)                                   # [t, k] int32 / f32
         payload, inverse, counts = ops.dispatch(xh, sel, wts, self.per_rank, W, S)
+        mark("route_plan")
         # split sizes: one tiny exchange and the step's only host read
         after(main, side)
         host = ops.buf.get("counts_host")
@@ -249,6 +261,7 @@ class ExpertParallelLayer:
                 done.record()
         # the shared expert needs nothing from other ranks: its GEMMs cover the host read and the first dispatch
         y_shared = ops.shared_rows(xh)
+        mark("shared_expert")
         if host is not None:
             done.synchronize()
             send_c, recv_c = host[:W * S].view(S, W).tolist(), host[W * S:].view(S, W).tolist()
@@ -286,6 +299,7 @@ class ExpertParallelLayer:
                     else ops.expert_rows_payload(recv, hidden)
             else:
                 y_seg = y_back.new_empty((0, hidden))
+            mark(f"segment{s}_wait_and_gemm")
             after(main, side)
             with on_side():
                 self._all_to_all(y_back[off:off + n_send], y_seg, send_c[s], recv_c[s])      # reverse direction, same splits
@@ -296,7 +310,12 @@ class ExpertParallelLayer:
         for e2 in back_events:
             main.wait_event(e2)
         # pair (token, rank) sits at row inverse[...] of y_back: the combine reads through that index
-        return ops.combine(y_back, y_shared, k, routed_rows=inverse), sel, wts
+        out = ops.combine(y_back, y_shared, k, routed_rows=inverse)
+        mark("return_wait_and_combine")
+        if marks:
+            self.timings["marks"] = marks
+            self.timings["pairs_received"] = [b[6] for b in seg_bufs]
+        return out, sel, wts
 
     def _exchange_counts(self, counts_in, counts):
         """counts is [segments][world]; rank r must receive entry [s][me] of every rank r' as its [s][r']."""
