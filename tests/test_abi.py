@@ -36,7 +36,7 @@ def test_library_exports_every_declared_symbol(lib):
 
 def test_qtype_registry_is_fail_closed(lib):
     supported = [q for q in range(0, 64) if lib.lib.yvex_b200_qtype_supported(q)]
-    assert supported == [0, 1, 8, 10, 12, 16, 30]
+    assert supported == [0, 1, 8, 10, 12, 16, 30, 39]
     e, b = C.c_uint(), C.c_uint()
     assert lib.lib.yvex_b200_qtype_geometry(16, C.byref(e), C.byref(b)) == 1 and (e.value, b.value) == (256, 66)
     assert lib.lib.yvex_b200_qtype_geometry(12, C.byref(e), C.byref(b)) == 1 and (e.value, b.value) == (256, 144)
@@ -48,8 +48,8 @@ def test_entry_points_refuse_before_launch(lib):
     # dummies that must never be dereferenced.
     dummy = C.c_void_p(0x1000)
     L = lib.lib
-    # unsupported qtype ids (Q3_K = 11, MXFP4 = 39 has no kernel here, 43 unknown)
-    for q in (11, 39, 43):
+    # unsupported qtype ids (Q3_K = 11 and Q5_K = 13 have no codec, 43 is unknown)
+    for q in (11, 13, 43):
         assert L.yvex_b200_gemv(q, dummy, 8, 256, 110, dummy, 1, None, dummy, 0, dummy, None) == -5
         assert L.yvex_b200_dequant_rows(q, dummy, 8, 256, 110, dummy, dummy, None) == -5
     # row width not block divisible / inconsistent row bytes -> bounds

@@ -76,6 +76,29 @@ def test_dequant_q4_k_matches_restatement(L, port):
     assert rc == 0 and st.read() == 0 and (bits(out) == bits(want)).all()
 
 
+def test_mxfp4_decode_and_matvec(L, port):
+    """MXFP4 (the other block qtype the reference decodes): the golden block of tests/unit/quant_numeric.c:529-540,
+    random blocks bit-exact against the pinned port, the E8M0 NaN code refused, and the matvec."""
+    blk = np.zeros((1, 17), np.uint8)
+    blk[0, 0], blk[0, 1:] = 127, 0x21
+    st = L.Status()
+    out = L.dequant_rows(synth.MXFP4, dev(blk), 1, 32, st).cpu().numpy()[0]
+    assert st.read() == 0 and (out[:16] == 0.5).all() and (out[16:] == 1.0).all()
+    rows, width = 37, 1024
+    w = synth.random_blocks(synth.MXFP4, rows, width, 9)
+    rc, want = port.decode_rows(synth.MXFP4, w, rows, width)
+    got = L.dequant_rows(synth.MXFP4, dev(w), rows, width, st).cpu().numpy()
+    assert rc == 0 and st.read() == 0 and (bits(got) == bits(want)).all()
+    x = np.random.default_rng(10).standard_normal(width).astype(np.float32)
+    rc, y0 = port.matvec(synth.MXFP4, w, rows, width, x, threads=4)
+    y = L.gemv(synth.MXFP4, dev(w), rows, width, dev(x), st).cpu().numpy()[0]
+    assert rc == 0 and st.read() == 0 and matvec_close(y, y0, want, x).all()
+    bad = w.copy()
+    bad[3, 17] = 0xFF
+    L.dequant_rows(synth.MXFP4, dev(bad), rows, width, st)
+    assert st.read() == 1
+
+
 def test_malformed_scale_sets_status_word(L):
     w = synth.random_blocks(synth.IQ2_XXS, 2, 256, 3)
     w[1, 0:2] = [0x00, 0xBC]          # d = -1.0: the reference refuses negative scales

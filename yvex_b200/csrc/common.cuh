@@ -15,7 +15,7 @@ enum : int { OK = 0, ERR = -1, ERR_NOMEM = -2, ERR_FORMAT = -4, ERR_UNSUPPORTED 
              ERR_BACKEND = -6, ERR_BOUNDS = -7, ERR_STATE = -8, ERR_INVALID_ARG = -10 };
 
 enum : unsigned { Q_F32 = 0, Q_F16 = 1, Q_Q8_0 = 8, Q_Q2_K = 10, Q_Q4_K = 12, Q_IQ2_XXS = 16,
-                  Q_BF16 = 30 };
+                  Q_BF16 = 30, Q_MXFP4 = 39 };
 
 constexpr int kSmCount = 148;
 

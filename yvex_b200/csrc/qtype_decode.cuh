@@ -22,7 +22,7 @@ __host__ __device__ inline Geometry geometry_of(unsigned q) {
 // The only qtypes any kernel here will touch. Everything else is refused before a launch.
 __host__ __device__ inline bool qtype_supported(unsigned q) {
     return q == Q_F32 || q == Q_F16 || q == Q_BF16 || q == Q_Q8_0 || q == Q_Q2_K ||
-           q == Q_Q4_K || q == Q_IQ2_XXS;
+           q == Q_Q4_K || q == Q_IQ2_XXS || q == Q_MXFP4;
 }
 
 // Returns 0 when (rows, width, row_bytes) is a consistent canonical layout for q.
@@ -65,6 +65,19 @@ __device__ inline float decode_element(unsigned q, const uint8_t *blk, unsigned 
         float d = f16_bits_to_float(ldg_u16(blk));
         if (!isfinite(d) || d < 0.0f) raise(status, YVEX_B200_STATUS_NUMERIC);
         return __fmul_rn(d, static_cast<float>(static_cast<int8_t>(__ldg(blk + 2 + i))));
+    }
+    case Q_MXFP4: {
+        // 17 bytes: an E8M0 scale, then 16 bytes whose low nibbles are elements 0..15 and high nibbles 16..31;
+        // value = level(code) * (2^(e - 127) / 2), levels {0,1,2,3,4,6,8,12} with bit 3 as the sign
+        // (src/backend/cuda/kernel_primitives.h:100-111; golden block tests/unit/quant_numeric.c:529-540)
+        const unsigned e = __ldg(blk);
+        if (e == 0xffu) raise(status, YVEX_B200_STATUS_NUMERIC);
+        const float scale = __fmul_rn(__uint_as_float(e ? e << 23 : 0x00400000u), 0.5f);
+        const unsigned byte = __ldg(blk + 1 + (i & 15u)), code = i < 16u ? byte & 15u : byte >> 4;
+        unsigned mag = code & 7u;
+        mag += (mag & 3u) * (mag >> 2);
+        mag += mag == 10u ? 2u : 0u;
+        return __fmul_rn(__uint_as_float(__float_as_uint(static_cast<float>(mag)) | ((code & 8u) << 28)), scale);
     }
     case Q_Q2_K: {
         float d = f16_bits_to_float(ldg_u16(blk + 80)), dmin = f16_bits_to_float(ldg_u16(blk + 82));

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import numpy as np
 
-F32, F16, Q8_0, Q2_K, Q4_K, IQ2_XXS, I32, BF16 = 0, 1, 8, 10, 12, 16, 26, 30
+F32, F16, Q8_0, Q2_K, Q4_K, IQ2_XXS, I32, BF16, MXFP4 = 0, 1, 8, 10, 12, 16, 26, 30, 39
 
 # qtype -> (elements per block, bytes per block, byte offsets of the f16 scale fields)
 BLOCKS = {
@@ -17,6 +17,7 @@ BLOCKS = {
     Q2_K: (256, 84, (80, 82)),
     Q4_K: (256, 144, (0, 2)),
     IQ2_XXS: (256, 66, (0,)),
+    MXFP4: (32, 17, ()),                # byte 0 is an E8M0 exponent, not an f16 scale: see random_blocks
 }
 SCALAR_BYTES = {F32: 4, F16: 2, BF16: 2, I32: 4}
 BASE_SEED = 0x5EED0000
@@ -41,6 +42,8 @@ def random_blocks(qtype: int, rows: int, width: int, seed: int, lo: float = 1e-4
     for off in scale_at:
         d = rng.uniform(lo, hi, size=nblk).astype(np.float16)
         raw[:, off:off + 2] = d.view(np.uint8).reshape(nblk, 2)
+    if qtype == MXFP4:
+        raw[:, 0] = rng.integers(110, 124, size=nblk, dtype=np.uint8)      # scales 2^-17 .. 2^-4 (0xff would be NaN)
     return raw.reshape(rows, -1)
 
 
