@@ -641,7 +641,7 @@ def run_native_ep(args):
         torch.cuda.synchronize()
         if not torch.equal(host_out.view(torch.int32), step(0).cpu().view(torch.int32)):
             raise RuntimeError("execute_rows_wide (host rows) differs from the device-resident layer")
-    twin = None
+    twin = gemv = None
     if world == 1 and rank == 0:
         try:
             twin = pinned_twin(torch, lib, args, flush, status, dev)
@@ -649,6 +649,15 @@ def run_native_ep(args):
             raise
         except Exception as exc:                                # e.g. out of memory beside the main workload
             twin = {"workload": "c5-q2k-down", "value": None, "failed": str(exc)}
+        # the second half of the metric: HBM GB/s of the dequant-fused matvec (config 1 and its variants)
+        from yvex_b200 import synth
+        torch.cuda.empty_cache()
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(synth.BASE_SEED + 0)
+        with ClockSampler(local) as gemv_clocks:
+            gemv, _keep = gemv_records(torch, lib, synth, dev, peaks, max(3, min(args.steps, 10)), args.warmup, status, gen)
+        del _keep
+        gemv["clocks"] = gemv_clocks.summary()
     # per-step max over ranks, then summed: every step is bracketed by a barrier
     tm = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
@@ -699,7 +708,7 @@ def run_native_ep(args):
                 "phases_ms": {"gate_up_gemm": gu, "swiglu": sw, "down_gemm": dn,
                               **({"pairs_in_timed_gemm": pairs, "step_spans_rank0": {k: sum(v) / len(v) for k, v in spans.items()}}
                                  if world > 1 else {})},
-                "parity": parity, "twin": twin,
+                "parity": parity, "twin": twin, "gemv": gemv,
                 "roofline": roofline, "cpu_baseline": cpu}
         print(json.dumps(line), flush=True)
     if world > 1:
