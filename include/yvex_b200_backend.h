@@ -260,6 +260,43 @@ typedef struct {
 /* NULL unless the backend is an open CUDA backend (src/backend/cuda/moe.c:1968-1981). */
 const yvex_backend_moe_operations *yvex_backend_moe_operations_get(const yvex_backend *backend);
 
+/* ---- external MoE input fixtures: include/yvex/internal/moe.h:120-160, src/runtime/moe_input.c ------------- */
+#define YVEX_SHA256_HEX_CAP 65u
+#define YVEX_MOE_INPUT_SUFFIX ".yvex-moe-input"
+typedef struct {
+    unsigned int schema_version;
+    unsigned long long token_start, token_count, layer_count;
+    unsigned long long activation_payload_bytes, token_id_payload_bytes;
+    char logical_model_identity[YVEX_SHA256_HEX_CAP];
+    char runtime_numeric_identity[YVEX_SHA256_HEX_CAP];
+    char runtime_descriptor_identity[YVEX_SHA256_HEX_CAP];
+    char moe_plan_identity[YVEX_SHA256_HEX_CAP];
+    char activation_payload_digest[YVEX_SHA256_HEX_CAP];
+    char token_id_payload_digest[YVEX_SHA256_HEX_CAP];
+    char input_identity[YVEX_SHA256_HEX_CAP];
+} yvex_moe_input_summary;
+typedef struct {
+    unsigned long long ordinal, layer_index, width, stride;
+    unsigned long long payload_offset, payload_bytes;
+    char layer_identity[YVEX_SHA256_HEX_CAP];
+} yvex_moe_input_layer_record;
+typedef struct yvex_moe_input yvex_moe_input;
+typedef struct { unsigned long long maximum_file_bytes; } yvex_moe_input_limits;
+/* Opens and verifies a fixture file (regular, not a symbolic link, at most limits->maximum_file_bytes):
+ * sizes, ordering, finite activations, both payload digests and the input identity (src/runtime/moe_input.c:279-412). */
+int yvex_moe_input_open_file(yvex_moe_input **out, const char *path, const yvex_moe_input_limits *limits, yvex_error *err);
+/* The same admission for a serialized fixture already in memory (copied; the caller keeps its buffer). */
+int yvex_moe_input_open_image(yvex_moe_input **out, const void *image, unsigned long long bytes, yvex_error *err);
+const yvex_moe_input_summary *yvex_moe_input_summary_get(const yvex_moe_input *input);
+const yvex_moe_input_layer_record *yvex_moe_input_layer_record_at(const yvex_moe_input *input, unsigned long long ordinal);
+int yvex_moe_input_layer_view(const yvex_moe_input *input, unsigned long long ordinal, const float **values,
+                              unsigned long long *stride, yvex_error *err);
+const unsigned int *yvex_moe_input_token_ids(const yvex_moe_input *input);
+void yvex_moe_input_close(yvex_moe_input **input);
+/* The rows of one fixture layer as the host-row batch execute_rows / execute_rows_wide take
+ * (what the reference's `graph execute moe` operator feeds the backend, src/runtime/moe.c:1290-1330). */
+int yvex_moe_input_row_batch(const yvex_moe_input *input, unsigned long long ordinal, yvex_moe_row_batch *batch, yvex_error *err);
+
 #ifdef __cplusplus
 }
 #endif

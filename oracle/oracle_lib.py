@@ -242,3 +242,20 @@ class Ref(_Base):
 
     def bf16_encode(self, v):
         return self.lib.ref_bf16_encode(C.c_float(v))
+
+
+def ref_moe_input_image(ref, token_start, widths, activations, token_ids):
+    """A fixture file image sealed and written by the reference (Ref instance): bytes."""
+    import tempfile
+    tokens, layers = len(token_ids), len(widths)
+    acts = np.ascontiguousarray(activations, np.float32)
+    tids = np.ascontiguousarray(token_ids, np.uint32)
+    w = (C.c_ulonglong * layers)(*widths)
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "fixture.yvex-moe-input")
+        ref.lib.ref_moe_input_write.argtypes = [C.c_char_p, C.c_ulonglong, C.c_ulonglong, C.c_ulonglong, C.c_void_p,
+                                                C.c_void_p, C.c_void_p]
+        rc = ref.lib.ref_moe_input_write(path.encode(), token_start, tokens, layers, w, acts.ctypes.data, tids.ctypes.data)
+        if rc != 0:
+            raise RuntimeError(f"reference refused the fixture: {rc}")
+        return open(path, "rb").read()

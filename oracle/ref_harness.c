@@ -16,6 +16,7 @@
  *   yvex_moe_route_cpu                 src/graph/moe.c:520
  *   yvex_moe_expert_cpu                src/graph/moe.c:587
  *   yvex_backend_op_attention (CPU)    src/backend/core.c:990, src/backend/cpu.c:319
+ *   yvex_moe_input_seal / _write       src/runtime/moe_input.c:196, :279 (fixture files for the reader tests)
  * The routed+shared combine restates the ten lines of src/runtime/moe.c:607-632 because that
  * function is static and needs a full runtime context.
  */
@@ -459,4 +460,48 @@ int ref_attention_head(const float *q, const float *keys, const float *values,
     if (to) yvex_backend_tensor_free(backend, to);
     yvex_backend_close(backend);
     return rc;
+}
+
+/* ---- external MoE input fixture, sealed and serialized by the reference itself ------------------- */
+
+/* Builds a fixture of `layers` layers (layer index 3 * ordinal + 1, the given widths) over `tokens`
+ * tokens, has the reference seal it and write it to `path` (which must not exist). */
+int ref_moe_input_write(const char *path, unsigned long long token_start, unsigned long long tokens,
+                        unsigned long long layers, const unsigned long long *widths, const float *activations,
+                        const unsigned int *token_ids) {
+    yvex_moe_input_summary summary;
+    yvex_moe_input_layer_record records[16];
+    yvex_error err;
+    unsigned long long offset = 0, i;
+    static const char *ids[5] = {
+        "1111111111111111111111111111111111111111111111111111111111111111",
+        "2222222222222222222222222222222222222222222222222222222222222222",
+        "3333333333333333333333333333333333333333333333333333333333333333",
+        "4444444444444444444444444444444444444444444444444444444444444444",
+        "abcdefabcdefabcdefabcdefabcdefabcdefabcdefabcdefabcdefabcdefabcd"};
+    if (layers > 16) return YVEX_ERR_BOUNDS;
+    memset(&summary, 0, sizeof(summary));
+    memset(records, 0, sizeof(records));
+    summary.schema_version = YVEX_MOE_INPUT_SCHEMA_V1;
+    summary.token_start = token_start;
+    summary.token_count = tokens;
+    summary.layer_count = layers;
+    summary.token_id_payload_bytes = tokens * sizeof(unsigned int);
+    memcpy(summary.logical_model_identity, ids[0], 65);
+    memcpy(summary.runtime_numeric_identity, ids[1], 65);
+    memcpy(summary.runtime_descriptor_identity, ids[2], 65);
+    memcpy(summary.moe_plan_identity, ids[3], 65);
+    for (i = 0; i < layers; ++i) {
+        records[i].ordinal = i;
+        records[i].layer_index = 3 * i + 1;
+        records[i].width = records[i].stride = widths[i];
+        records[i].payload_offset = offset;
+        records[i].payload_bytes = tokens * widths[i] * sizeof(float);
+        memcpy(records[i].layer_identity, ids[4], 65);
+        offset += records[i].payload_bytes;
+    }
+    summary.activation_payload_bytes = offset;
+    int rc = yvex_moe_input_seal(&summary, records, activations, token_ids, &err);
+    if (rc != YVEX_OK) return rc;
+    return yvex_moe_input_write(path, &summary, records, activations, token_ids, &err);
 }

@@ -84,3 +84,41 @@ def envelope_inputs(name):
     norm = (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32)
     expanded = rng.standard_normal((T, S * H)).astype(np.float32)
     return fn, scale, base, norm, expanded
+
+
+def moe_input_case():
+    """(token_start, widths per layer, activations (all layers back to back, [tokens x width] each), token ids)."""
+    rng = np.random.default_rng(51)
+    widths, tokens = [4, 6], 3
+    acts = rng.standard_normal(tokens * sum(widths)).astype(np.float32)
+    return 7, widths, acts, np.array([5, 19, 1000003], np.uint32)
+
+
+def moe_input_image(token_start, widths, activations, token_ids, layer_indices=None):
+    """Serializes an external MoE input fixture (the reference's *.yvex-moe-input layout, src/runtime/moe_input.c:226-277)
+    with its SHA-256 payload digests and input identity. The frozen reference-written image in tests/golden/ pins this
+    writer (tests/test_moe_input.py re-derives that image's identities with the same arithmetic)."""
+    import hashlib
+    import struct
+    acts = np.ascontiguousarray(activations, np.float32).tobytes()
+    tids = np.ascontiguousarray(token_ids, np.uint32).tobytes()
+    tokens, layers = len(token_ids), len(widths)
+    ids = [bytes([c]) * 64 for c in b"1234"]
+    records, offset = b"", 0
+    for i, w in enumerate(widths):
+        nbytes = 4 * w * tokens
+        records += struct.pack("<6Q", i, layer_indices[i] if layer_indices else 3 * i + 1, w, w, offset, nbytes) + b"ab" * 32
+        offset += nbytes
+    head = struct.pack("<6Q", 1, token_start, tokens, layers, len(acts), len(tids))
+    digests = [hashlib.sha256(acts).hexdigest().encode(), hashlib.sha256(tids).hexdigest().encode()]
+    h = hashlib.sha256()
+    text = lambda t: h.update(struct.pack("<Q", len(t)) + t)
+    text(b"yvex.runtime.moe-input.v1")
+    h.update(head)
+    for t in ids + digests:
+        text(t)
+    for i in range(layers):
+        r = records[112 * i:112 * (i + 1)]
+        h.update(r[:48])
+        text(r[48:])
+    return b"YVEXMOEINPUT001\0" + head + b"".join(ids + digests) + h.hexdigest().encode() + records + acts + tids

@@ -7,7 +7,7 @@ import ctypes as C
 import numpy as np
 import pytest
 
-from golden_cases import CASES, ENVELOPE_POLICY, attention_inputs, envelope_inputs, layer_inputs
+from golden_cases import CASES, ENVELOPE_POLICY, attention_inputs, envelope_inputs, layer_inputs, moe_input_image
 from yvex_b200 import synth
 
 pytestmark = pytest.mark.gpu
@@ -441,3 +441,29 @@ def test_two_backends_on_two_devices(B):
         outs.append(out)
         assert be.close() == B.OK
     assert (outs[0].view(np.uint32) == outs[1].view(np.uint32)).all()
+
+
+def test_fixture_file_drives_execute_rows(B, golden, tmp_path):
+    """An external MoE input fixture (*.yvex-moe-input: activations of two layers + token ids) is opened by the
+    library's reader and its rows run through execute_rows unchanged, like the reference's `graph execute moe`."""
+    be, arena, job, spec, x, logits = layer_setup(B, "small_router")
+    other = np.random.default_rng(5).standard_normal(x.shape).astype(np.float32)
+    image = moe_input_image(0, [spec.hidden, spec.hidden], np.concatenate([other.reshape(-1), x.reshape(-1)]),
+                            np.arange(x.shape[0], dtype=np.uint32), layer_indices=[0, 1])
+    path = tmp_path / "layer.yvex-moe-input"
+    path.write_bytes(image)
+    handle = B.vp()
+    limits = B.MoeInputLimits(1 << 20)
+    assert B._lib.yvex_moe_input_open_file(C.byref(handle), str(path).encode(), C.byref(limits), C.byref(be.err)) == B.OK, be.message()
+    batch = B.RowBatch()
+    assert B._lib.yvex_moe_input_row_batch(handle, 1, C.byref(batch), C.byref(be.err)) == B.OK
+    ops, _ = attach_workspace(B, be, job, x.shape[0])
+    rows, H, k = x.shape[0], spec.hidden, spec.topk
+    out, sel, wts = np.zeros((rows, H), np.float32), np.zeros((rows, k), np.uint64), np.zeros((rows, k), np.float32)
+    o = B.RowBatchOutput(out.ctypes.data_as(B.vp), out.size, sel.ctypes.data_as(B.vp), wts.ctypes.data_as(B.vp), sel.size)
+    res = B.RowBatchResult()
+    assert ops.execute_rows(be.h, C.byref(job), C.byref(batch), C.byref(o), C.byref(res), C.byref(be.err)) == B.OK, be.message()
+    assert (sel == golden["layer_small_router_sel"]).all()
+    assert rel_l2(out, golden["layer_small_router_out"].view(np.float32)) <= 1e-3
+    B._lib.yvex_moe_input_close(C.byref(handle))
+    assert be.close() == B.OK

@@ -143,6 +143,33 @@ _lib.yvex_backend_attention_gqa_decode.argtypes = [vp] + [C.POINTER(DeviceTensor
                                                                                                     C.POINTER(DeviceTensor),
                                                                                                     C.POINTER(Error)]
 _lib.yvex_backend_op_matmul.argtypes = [vp] + [C.POINTER(DeviceTensor)] * 3 + [C.POINTER(Error)]
+class MoeInputSummary(C.Structure):
+    _fields_ = [("schema_version", C.c_uint), ("token_start", ull), ("token_count", ull), ("layer_count", ull),
+                ("activation_payload_bytes", ull), ("token_id_payload_bytes", ull)] + [
+        (n, C.c_char * 65) for n in ("logical_model_identity", "runtime_numeric_identity", "runtime_descriptor_identity",
+                                     "moe_plan_identity", "activation_payload_digest", "token_id_payload_digest", "input_identity")]
+
+
+class MoeInputRecord(C.Structure):
+    _fields_ = [(n, ull) for n in ("ordinal", "layer_index", "width", "stride", "payload_offset", "payload_bytes")] + [
+        ("layer_identity", C.c_char * 65)]
+
+
+class MoeInputLimits(C.Structure):
+    _fields_ = [("maximum_file_bytes", ull)]
+
+
+_lib.yvex_moe_input_open_file.argtypes = [C.POINTER(vp), C.c_char_p, C.POINTER(MoeInputLimits), C.POINTER(Error)]
+_lib.yvex_moe_input_open_image.argtypes = [C.POINTER(vp), vp, ull, C.POINTER(Error)]
+_lib.yvex_moe_input_summary_get.restype = C.POINTER(MoeInputSummary)
+_lib.yvex_moe_input_summary_get.argtypes = [vp]
+_lib.yvex_moe_input_layer_record_at.restype = C.POINTER(MoeInputRecord)
+_lib.yvex_moe_input_layer_record_at.argtypes = [vp, ull]
+_lib.yvex_moe_input_layer_view.argtypes = [vp, ull, C.POINTER(C.POINTER(C.c_float)), C.POINTER(ull), C.POINTER(Error)]
+_lib.yvex_moe_input_token_ids.restype = C.POINTER(C.c_uint)
+_lib.yvex_moe_input_token_ids.argtypes = [vp]
+_lib.yvex_moe_input_close.argtypes = [C.POINTER(vp)]
+_lib.yvex_moe_input_row_batch.argtypes = [vp, ull, C.POINTER(RowBatch), C.POINTER(Error)]
 _lib.yvex_backend_selftest_bounded_wait.argtypes = [vp, ull, C.POINTER(ull), C.POINTER(Error)]
 _lib.yvex_status_name.restype = C.c_char_p
 
