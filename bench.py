@@ -496,7 +496,7 @@ def run_native_ep(args):
     status = lib.Status(dev)
     # experiment knobs (defaults are what the library picks): segments of the exchange pipeline, whether the exchange runs
     # on its own stream beside the GEMMs, CTAs of the persistent GEMM
-    ops = DeviceOps(geom_full, geom_local, lib.weights_of(shard), status, overlap=os.environ.get("YVEX_EP_OVERLAP", "1") != "0")
+    ops = DeviceOps(geom_full, geom_local, lib.weights_of(shard), status, overlap=os.environ.get("YVEX_EP_OVERLAP", "0") != "0")
     seg_env = os.environ.get("YVEX_EP_SEGMENTS")
     layer = ExpertParallelLayer(E, spec.topk, ops, segments=int(seg_env) if seg_env else None)
     if os.environ.get("YVEX_EP_CTAS"):
@@ -698,8 +698,9 @@ def run_native_ep(args):
                 "data": "synthetic",
                 "config": {"workload": wl.name, **cfg, "gate_up_qtype": "IQ2_XXS", "down_qtype": "Q4_K",
                            "l2": "flushed between steps (256 MiB rewrite)",
-                           "parallelism": (f"ep{world}: {e_loc} experts and {t_loc} tokens per rank, NCCL all-to-all-v in "
-                                           f"{layer.segments} expert segments pipelined against the GEMMs" if world > 1
+                           "parallelism": (f"ep{world}: {e_loc} experts and {t_loc} tokens per rank, NCCL all-to-all-v, "
+                                           f"{layer.segments} expert segment(s), exchange {'beside' if ops.streams else 'between'} the GEMMs"
+                                           if world > 1
                                            else "ep1: all experts on one device, fused wide layer, no exchange")},
                 "clocks": clocks.summary(),
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(T * (H + E) * 4),

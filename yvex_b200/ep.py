@@ -10,12 +10,15 @@ result is bit-identical to the single-device layer. The reference has no multi-d
 (single process, one GPU); per-pair semantics are those of its CPU path
 (src/graph/moe.c:587-622, src/runtime/moe.c:619-632).
 
-Pipelining. A rank's local experts are cut into `segments` equal ranges and the pairs travel
-segment by segment: while the GEMMs of segment s run on the compute stream, the rows of segment
-s + 1 arrive and the results of segment s - 1 leave on the communication stream. Cutting by EXPERT
-keeps every expert's rows together, so the GEMM tiles are as full as without the pipeline. The
-shared expert needs no exchange: its GEMMs are enqueued first and cover the one host read of the
-split sizes and the first dispatch. All per-step buffers are allocated once and reused.
+Order of a step. The shared expert needs no exchange: its GEMMs are enqueued first and cover the one
+host read of the split sizes and most of the dispatch. All per-step buffers are allocated once and
+reused. Optionally (`segments` > 1, `DeviceOps(overlap=True)`) a rank's local experts are cut into
+equal ranges and the pairs travel range by range on a communication stream while the GEMMs of the
+previous range run on the compute stream; cutting by EXPERT keeps every expert's rows together, so
+the GEMM tiles stay as full as without the pipeline. Measured on two B200s at the config-5 size the
+pipeline hides the exchange but loses more in the GEMMs (three smaller launch sets, SMs left to the
+exchange kernels, which slow the GEMM they run beside): 14.9 ms against 14.3 ms per step, so the
+default is one range on one stream.
 
 Collectives go through torch.distributed (NCCL over NVLink on GPUs, gloo in the CPU tests); the
 compute calls go through the C-ABI of libyvex_b200.so (`DeviceOps`). The host logic takes the ops
@@ -100,7 +103,7 @@ class TorchOps:
 class DeviceOps(TorchOps):
     """The layer's compute steps on the current CUDA device, via the C-ABI. Owns the step buffers."""
 
-    def __init__(self, geom_full, geom_local, weights_local, status, overlap=True):
+    def __init__(self, geom_full, geom_local, weights_local, status, overlap=False):
         from . import lib
         self.lib, self.geom_full, self.geom_local = lib, geom_full, geom_local
         self.weights, self.status = weights_local, status
@@ -192,7 +195,7 @@ class ExpertParallelLayer:
             raise ValueError("experts must divide evenly over the ranks")
         self.experts, self.topk, self.per_rank, self.ops = experts, topk, experts // self.world, ops
         if segments is None:
-            segments = 2 if self.world > 1 and self.per_rank % 2 == 0 else 1
+            segments = 1
         if self.per_rank % segments:
             raise ValueError("segments must divide the experts of a rank")
         self.segments = segments
