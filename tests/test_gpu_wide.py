@@ -73,6 +73,23 @@ def test_wide_layer_ragged_groups_vs_oracle(L, port, down):
     assert per_token.max() <= 4e-3, per_token.max()
 
 
+@pytest.mark.parametrize("gate", [synth.Q2_K, synth.Q4_K])
+def test_wide_layer_affine_gate_and_up_vs_oracle(L, port, gate):
+    """Gate and up weights of a qtype with a min term: the fused gate/up GEMM then needs the sub-block
+    sums of the ACTIVATION rows as its second operand. 300 tokens over 8 experts, ragged groups."""
+    H, E, k, I, T = 512, 8, 2, 256, 300
+    spec = synth.MoELayerSpec(H, E, k, I, gate_qtype=gate, down_qtype=synth.IQ2_XXS)
+    rng = np.random.default_rng(70 + gate)
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    logits = rng.standard_normal((T, E)).astype(np.float32)
+    weights = synth.moe_weights(spec, 71 + gate)
+    Lp = port.layer(spec, weights, allow_q4k=True)
+    rc, want, sel0, w0 = port.moe_tokens(Lp, x, logits=logits, threads=8)
+    out, sel, w, status = run_layer(L, spec, weights, None, x, logits)
+    assert rc == 0 and status == 0 and (sel == sel0).all()
+    assert rel_l2(out, want) <= 1e-3, rel_l2(out, want)
+
+
 def test_expert_parallel_building_blocks_match_single_device_layer_bit_for_bit(L):
     """The expert-parallel decomposition (route -> per-pair rows on the expert shard -> combine on
     the home rank), run here on one rank that owns every expert, and again with the experts split

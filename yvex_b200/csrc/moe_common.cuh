@@ -9,11 +9,17 @@ using MoeWeights = yvex_b200_moe_weights;
 
 // SwiGLU with the reference's clamps and its single bf16 rounding point after the route weight
 // (src/graph/moe.c:605-613).
-__device__ __forceinline__ float swiglu_mid(float g, float u, float route_weight, float limit, int *status) {
+// silu(g) = g / (1 + exp(-g)) for g >= 0 and g * exp(g) / (1 + exp(g)) below: with t = exp(-|g|) both
+// are (g or g * t) / (1 + t), the same operations on the same values, evaluated without a branch.
+__device__ __forceinline__ float swiglu_product(float g, float u, float route_weight, float limit) {
     g = fminf(g, limit);
     u = fmaxf(-limit, fminf(u, limit));
-    float silu = g >= 0.0f ? g / (1.0f + expf(-g)) : g * expf(g) / (1.0f + expf(g));
-    float mid = silu * u * route_weight;
+    const float t = expf(-fabsf(g));
+    const float silu = (g >= 0.0f ? g : g * t) / (1.0f + t);
+    return silu * u * route_weight;
+}
+__device__ __forceinline__ float swiglu_mid(float g, float u, float route_weight, float limit, int *status) {
+    const float mid = swiglu_product(g, u, route_weight, limit);
     if (!isfinite(mid)) raise(status, YVEX_B200_STATUS_NUMERIC);
     return bf16_round(mid);
 }

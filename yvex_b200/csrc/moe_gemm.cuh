@@ -29,6 +29,15 @@
 //   warps 12-27 epilogue, one warp per (32 TMEM lanes, 64 or 32 columns): TMEM -> registers
 //               (tcgen05.ld), scale, accumulate, final store
 // Every mbarrier wait is bounded; on expiry the CTA sets status 3, unwinds and frees its TMEM.
+//
+// Two forms. The plain one multiplies by ONE matrix and stores bf16 rows (down projection). The
+// fused one computes gate and up together: a tile's 128 A rows are 64 gate rows and the 64 up rows
+// of the same intermediates, interleaved (A row 2i = gate row i, 2i + 1 = up row i; the producers
+// are free to choose which weight row feeds which tile row). Gate and up of an intermediate then
+// sit in neighbouring TMEM lanes, i.e. in neighbouring threads of an epilogue warp, which pairs
+// them with one shuffle, applies the clamps, SiLU, the route weight and the single bf16 rounding
+// (src/graph/moe.c:605-613) and stores the fp16 image the down GEMM reads. Neither projection is
+// ever written to memory.
 #pragma once
 #include <type_traits>
 
@@ -66,9 +75,11 @@ struct GemmParams {
     int M, K, nmat;
     const ColBlock *colblocks;
     const int *num_colblocks;
-    float *out_f32[2];                          // [rows][M] f32 (gate/up results) ...
-    uint16_t *out_bf16;                         // ... or [rows][M] bf16 bits (down results)
-    const int *out_rows;                        // optional: result row of sorted row r is out_rows[r] (bf16 output only)
+    uint16_t *out_bf16;                         // [rows][M] bf16 bits (plain kernel: down results) ...
+    const int *out_rows;                        // optional: result row of sorted row r is out_rows[r]
+    __half *mid;                                // ... or [rows][M] SwiGLU intermediates as fp16 (fused gate/up kernel)
+    const float *col_weight;                    // route weight of sorted row r (fused kernel)
+    float limit;                                // SwiGLU clamp (fused kernel)
     const __half *sums;                         // [rows][K/256][32] hi/lo sub-block sums (affine qtypes)
     int *status;
 };
@@ -123,6 +134,14 @@ __device__ __forceinline__ float2 checked_scales(uint32_t d_bits, uint32_t dmin_
     return make_float2(d * d_mul, dmin);
 }
 
+// prmt.b32 with a run-time selector. (__byte_perm masks the selector with 0x7777 first; the decoders'
+// selectors never have bit 3 of a nibble set, and the instruction reads only the low 16 bits.)
+__device__ __forceinline__ uint32_t prmt_raw(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
 struct GemmIq2 {
     static constexpr int kBlockBytes = 66, kMinSlots = 0, kBoxBytes = 80;     // 66 bytes from a 2-byte aligned start
     static constexpr int kParts = 2;
@@ -140,7 +159,7 @@ struct GemmIq2 {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t sel = tab->nib[(grids >> (8 * j)) & 255u] | tab->sign[(ss >> (7 * j)) & 127u];
-            store_scaled8(tile, row, 4 * h + j, __byte_perm(kLo, kHi, sel), __byte_perm(kLo, kHi, sel >> 16), sc2, nb2);
+            store_scaled8(tile, row, 4 * h + j, prmt_raw(kLo, kHi, sel), prmt_raw(kLo, kHi, sel >> 16), sc2, nb2);
         }
     }
     __device__ static float2 scales(const uint32_t *raw, uint32_t mis, bool &bad) {
@@ -246,7 +265,8 @@ template <class Dec> struct GemmPlan {
     static constexpr size_t kScaleBytes = (size_t)kScaleRing * kTileM * sizeof(Scale);
     static constexpr size_t kBytes = kTilesBytes + kRawBytes + kScaleBytes + sizeof(MmaTables) + sizeof(GemmSmem);
     static_assert(kBytes <= 227 * 1024, "shared memory plan exceeds the 227 KiB a CTA can have");
-    static_assert(kRawStageBytes % 128 == 0 && (kTileM / 8) * Dec::kBoxBytes % 128 == 0, "TMA destinations are 128-byte aligned");
+    static_assert(kRawStageBytes % 128 == 0 && (kTileM / 16) * Dec::kBoxBytes % 128 == 0,
+                  "TMA destinations are 128-byte aligned (boxes of 64 rows, up to 8 rows fused)");
 };
 
 // Sets this warpgroup's registers per thread to N, given the count the kernel was launched with. An
@@ -256,7 +276,7 @@ template <int N, int kLaunched> __device__ __forceinline__ void set_registers() 
     else if constexpr (N < kLaunched) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
-template <class Dec>
+template <class Dec, bool kFused>
 __global__ void __launch_bounds__(GemmPlan<Dec>::kThreads, 1)
 moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
     using namespace sm100;
@@ -301,7 +321,8 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
     volatile int *abort = &sm->abort;
 
     const int ncb = *p.num_colblocks;
-    const int mtiles = p.M / kTileM, nsb = p.K / 256;
+    constexpr int kRowsPerMat = kFused ? kTileM / 2 : kTileM;      // weight rows of one matrix in a tile
+    const int mtiles = p.M / kRowsPerMat, nsb = p.K / 256;
     const long long tiles_total = (long long)ncb * mtiles * p.nmat;
 
     // Every role walks the same tile sequence: group of column blocks -> (matrix, m tile) -> column block.
@@ -318,7 +339,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
     // indexed parameter array makes the compiler copy the parameter block to local memory.)
     auto weights_of = [&](const ColBlock &cb, int mat, int mt, int &y) {
         const CUtensorMap *shared = mat ? &maps.w_shared[1] : &maps.w_shared[0], *routed = mat ? &maps.w_routed[1] : &maps.w_routed[0];
-        y = ((cb.expert < 0 ? 0 : cb.expert * p.M) + mt * kTileM) / p.fuse;
+        y = ((cb.expert < 0 ? 0 : cb.expert * p.M) + mt * kRowsPerMat) / p.fuse;
         return cb.expert < 0 ? shared : routed;
     };
 
@@ -340,21 +361,25 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
             prefetch_tensormap(&maps.act);
             // Raw weight superblocks run kRawStages - 1 ahead of the producers: one box per fused row
             // r, [128 / fuse tensor rows] x [kBoxBytes from the 16-byte boundary at or below the block].
-            struct { long long t; int sb, y; uint32_t n; const CUtensorMap *map; } raw{(long long)blockIdx.x, 0, 0, 0u, nullptr};
+            // (the fused form: the same from each of the two matrices, 64 / fuse tensor rows per box)
+            struct { long long t; int sb, y; uint32_t n; const CUtensorMap *map, *map2; } raw{(long long)blockIdx.x, 0, 0, 0u, nullptr, nullptr};
             auto issue_raw = [&]() -> bool {
                 if (raw.t >= tiles_total) return true;
                 if (raw.sb == 0) {
                     ColBlock cb; int mat, mt;
                     tile_of(raw.t, cb, mat, mt);
                     raw.map = weights_of(cb, mat, mt, raw.y);
+                    if constexpr (kFused) raw.map2 = weights_of(cb, 1, mt, raw.y);
                 }
                 const uint32_t s = raw.n % kRawStages, ph = (raw.n / kRawStages) & 1u;
                 if (!mbar_wait(&sm->raw_empty[s], ph ^ 1u, abort)) return false;
                 mbar_expect_tx(&sm->raw_full[s], Plan::kRawStageBytes);
-                const int rows = kTileM / p.fuse;
+                const int rows = kRowsPerMat / p.fuse;
                 for (int r = 0; r < p.fuse; ++r) {
                     const int x = (int)(r * p.row_bytes + raw.sb * Dec::kBlockBytes) & ~15;
-                    tma_load_2d(raw_stage + s * Plan::kRawStageBytes + r * rows * Dec::kBoxBytes, raw.map, x, raw.y, &sm->raw_full[s]);
+                    uint8_t *dst = raw_stage + s * Plan::kRawStageBytes + r * rows * Dec::kBoxBytes;
+                    tma_load_2d(dst, raw.map, x, raw.y, &sm->raw_full[s]);
+                    if constexpr (kFused) tma_load_2d(dst + kRowsPerMat * Dec::kBoxBytes, raw.map2, x, raw.y, &sm->raw_full[s]);
                 }
                 ++raw.n;
                 if (++raw.sb == nsb) { raw.sb = 0; raw.t += gridDim.x; }
@@ -464,8 +489,10 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
         const int pw = warp - 4, rl = lane % kRowsPerWarp, h = lane / kRowsPerWarp;     // h: this thread's part of a chunk
         const uint32_t row = (uint32_t)(kRowsPerWarp * pw + rl);
         // where the row's bytes land in a raw stage, and where its superblock 0 starts in the tensor row
-        const uint32_t sub = row % (uint32_t)p.fuse;
-        const uint32_t slot = (sub * (uint32_t)(kTileM / p.fuse) + row / (uint32_t)p.fuse) * Dec::kBoxBytes;
+        // (fused form: tile row 2i is row i of the first matrix, 2i + 1 row i of the second, whose boxes follow)
+        const uint32_t wrow = kFused ? row >> 1 : row, wmat = kFused ? row & 1u : 0u;
+        const uint32_t sub = wrow % (uint32_t)p.fuse;
+        const uint32_t slot = ((wmat * (uint32_t)p.fuse + sub) * (uint32_t)(kRowsPerMat / p.fuse) + wrow / (uint32_t)p.fuse) * Dec::kBoxBytes;
         const uint32_t x_row = sub * p.row_bytes;
         const long long my_tiles = tiles_total > blockIdx.x ? (tiles_total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         uint32_t sb_it = 0;
@@ -519,6 +546,14 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
 #pragma unroll
             for (int i = 0; i < kCols; ++i) acc[i] = 0.0f;
             const int ncols_here = cb.ncols - kCols * colhalf;    // columns this warp owns that are real
+            // fused form: the route weights of this warp's columns, lane l holding those of columns l and
+            // 32 + l; loaded here so that their latency is long gone when the tile ends
+            float w_lo = 0.0f, w_hi = 0.0f;
+            if constexpr (kFused) {
+                const float *wcol = p.col_weight + cb.row0 + kCols * colhalf;
+                if (lane < ncols_here) w_lo = __ldg(wcol + lane);
+                if (kCols > 32 && 32 + lane < ncols_here) w_hi = __ldg(wcol + 32 + lane);
+            }
             for (int sb = 0; sb < nsb; ++sb, ++sb_it) {
                 const uint32_t buf = sb_it & 1u, bph = (sb_it >> 1) & 1u;
                 if (!mbar_wait_warp(&sm->acc_full[buf], bph, abort)) goto done;
@@ -527,9 +562,13 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
                 float d, dmin = 0.0f;
                 if constexpr (kHasMin) { const float2 dd = dscale[(sb_it % kScaleRing) * kTileM + row]; d = dd.x; dmin = dd.y; }
                 else d = dscale[(sb_it % kScaleRing) * kTileM + row];
-                if (ncols_here > 0) {
+                {
+                    // (16-column groups without a real column are skipped: their sums stay zero, and the
+                    // columns of a ragged group hold sums over neighbouring real rows, so every sum is
+                    // finite unless real data is not)
 #pragma unroll
                     for (int q = 0; q < kCols / 16; ++q) {
+                        if (16 * q >= ncols_here) break;
                         uint32_t v[16];
                         tmem_ld16(tmem + lane_addr + buf * kTileN + kCols * colhalf + 16 * q, v);
                         tmem_ld_wait();
@@ -547,39 +586,105 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sm->acc_empty[buf]);
             }
-            // store: out[(row0 + n)][mt*128 + row]. A thread holds 64 token columns of ONE weight row, so a
-            // direct store is one instruction per column and 2 or 4 bytes per lane; the store path then takes
-            // longer than two superblocks of MMA work and the pipeline drains at every tile end. Instead
-            // every aligned group of four lanes transposes 4 x 4 blocks with shuffles: lane 4a+j ends up
-            // with weight rows 4a..4a+3 of token column 4b+j and stores them as one 8- or 16-byte vector
-            // (a quarter of the store instructions).
-            uint32_t nonfinite = 0;
+            // non-finite sums are refused: x * 0 is zero for finite x and NaN otherwise
+            float poison = 0.0f;
 #pragma unroll
-            for (int i = 0; i < kCols; ++i) nonfinite |= (~__float_as_uint(acc[i]) & 0x7f800000u) == 0u;
-            if (nonfinite) raise(p.status, YVEX_B200_STATUS_NUMERIC);
-            const bool odd = lane & 1, hi = lane & 2;
-            const int j4 = lane & 3;
-            const uint64_t m0 = (uint64_t)mt * kTileM + 32 * quarter + (lane & ~3);
-            float *out_f32 = mat ? p.out_f32[1] : p.out_f32[0];
+            for (int i = 0; i < kCols; ++i) poison = fmaf(acc[i], 0.0f, poison);
+            if (poison != poison) raise(p.status, YVEX_B200_STATUS_NUMERIC);
+            if constexpr (kFused) {
+                // Even lanes hold the gate row of intermediate i = row / 2, odd lanes its up row. A pair of
+                // lanes swaps every other column, so the even lane ends up with gate and up of the even
+                // columns, the odd lane of the odd ones, and each evaluates half of the pair's SwiGLUs.
+                // Then the four lanes of equal parity in every aligned group of eight transpose 4 x 4
+                // blocks (intermediates x columns) with shuffles: lane (a, r, parity) ends up with
+                // intermediates 4a..4a+3 of column 8b + 2r + parity, multiplies by that column's route
+                // weight and stores them as one 8-byte vector.
+                // Shuffles share the shared-memory pipe with the producers' table lookups and tile stores,
+                // which keep it busy, so a shuffle takes long to come back. The tile end is therefore
+                // written in ROUNDS of independent shuffles (all swaps; all first transpose steps; all
+                // second steps) rather than block by block with three dependent shuffles each.
+                const bool odd = lane & 1, o2 = lane & 2, o4 = lane & 4;
+                const int rr = (lane >> 1) & 3;
+                const uint64_t m0 = (uint64_t)mt * kRowsPerMat + 16 * quarter + 4 * (lane >> 3);
 #pragma unroll
-            for (int b = 0; b < kCols / 4; ++b) {
-                float r0 = acc[4 * b], r1 = acc[4 * b + 1], r2 = acc[4 * b + 2], r3 = acc[4 * b + 3];
-                float s0 = __shfl_xor_sync(0xffffffffu, odd ? r0 : r1, 1), s1 = __shfl_xor_sync(0xffffffffu, odd ? r2 : r3, 1);
-                if (odd) { r0 = s0; r2 = s1; } else { r1 = s0; r3 = s1; }
-                s0 = __shfl_xor_sync(0xffffffffu, hi ? r0 : r2, 2);
-                s1 = __shfl_xor_sync(0xffffffffu, hi ? r1 : r3, 2);
-                if (hi) { r0 = s0; r1 = s1; } else { r2 = s0; r3 = s1; }
-                const int col = 4 * b + j4;
-                if (col < ncols_here) {
-                    const uint64_t srow = (uint64_t)cb.row0 + kCols * colhalf + col;
-                    const uint64_t at = (p.out_rows ? (uint64_t)__ldg(p.out_rows + srow) : srow) * p.M + m0;
-                    // streaming stores: the results are not read again by this kernel and must not push the
-                    // activation tiles and weight rows that other CTAs are about to reuse out of L2
-                    if (p.out_bf16) {
-                        const uint2 v = make_uint2(bf16_bits(r0) | ((uint32_t)bf16_bits(r1) << 16), bf16_bits(r2) | ((uint32_t)bf16_bits(r3) << 16));
+                for (int m = 0; m < kCols / 2; ++m) {               // acc[2m] = gate, acc[2m + 1] = up of column 2m + parity
+                    const float keep = odd ? acc[2 * m + 1] : acc[2 * m];
+                    const float got = __shfl_xor_sync(0xffffffffu, odd ? acc[2 * m] : acc[2 * m + 1], 1);
+                    acc[2 * m] = odd ? got : keep;
+                    acc[2 * m + 1] = odd ? keep : got;
+                }
+#pragma unroll
+                for (int m = 0; m < kCols / 2; ++m)                 // acc[m] = silu(gate) * up
+                    acc[m] = swiglu_product(acc[2 * m], acc[2 * m + 1], 1.0f, p.limit);
+                float wv[kCols / 8];                                // route weight of column 8b + 2rr + parity
+#pragma unroll
+                for (int b = 0; b < kCols / 8; ++b) wv[b] = __shfl_sync(0xffffffffu, b < 4 ? w_lo : w_hi, (8 * b + 2 * rr + (odd ? 1 : 0)) & 31);
+#pragma unroll
+                for (int b0 = 0; b0 < kCols / 8; b0 += 4) {           // four blocks (eight shuffles) per round
+#pragma unroll
+                    for (int b = b0; b < b0 + 4; ++b) {
+                        float *r = acc + 4 * b;
+                        const float s0 = __shfl_xor_sync(0xffffffffu, o2 ? r[0] : r[1], 2), s1 = __shfl_xor_sync(0xffffffffu, o2 ? r[2] : r[3], 2);
+                        if (o2) { r[0] = s0; r[2] = s1; } else { r[1] = s0; r[3] = s1; }
+                    }
+#pragma unroll
+                    for (int b = b0; b < b0 + 4; ++b) {
+                        float *r = acc + 4 * b;
+                        const float s0 = __shfl_xor_sync(0xffffffffu, o4 ? r[0] : r[2], 4), s1 = __shfl_xor_sync(0xffffffffu, o4 ? r[1] : r[3], 4);
+                        if (o4) { r[0] = s0; r[1] = s1; } else { r[2] = s0; r[3] = s1; }
+                    }
+                }
+                bool bad = false;
+#pragma unroll
+                for (int b = 0; b < kCols / 8; ++b) {
+                    const int col = 8 * b + 2 * rr + (odd ? 1 : 0);
+                    if (col < ncols_here) {
+                        const uint64_t srow = (uint64_t)cb.row0 + kCols * colhalf + col;
+                        const float r0 = acc[4 * b] * wv[b], r1 = acc[4 * b + 1] * wv[b], r2 = acc[4 * b + 2] * wv[b], r3 = acc[4 * b + 3] * wv[b];
+                        bad |= !isfinite(r0) || !isfinite(r1) || !isfinite(r2) || !isfinite(r3);
+                        // f32 -> bf16 (round to nearest even; the product is finite or the launch is refused) -> the same values as fp16
+                        const __nv_bfloat162 b01 = __floats2bfloat162_rn(r0, r1), b23 = __floats2bfloat162_rn(r2, r3);
+                        const __half2 h01 = __float22half2_rn(__bfloat1622float2(b01)), h23 = __float22half2_rn(__bfloat1622float2(b23));
+                        *reinterpret_cast<uint2 *>(p.mid + srow * p.M + m0) =
+                            make_uint2(*reinterpret_cast<const uint32_t *>(&h01), *reinterpret_cast<const uint32_t *>(&h23));
+                    }
+                }
+                if (bad) raise(p.status, YVEX_B200_STATUS_NUMERIC);
+            } else {
+                // store: out[(row0 + n)][mt*128 + row]. A thread holds 64 token columns of ONE weight row, so a
+                // direct store is one instruction per column and 2 bytes per lane. Instead every aligned
+                // group of four lanes transposes 4 x 4 blocks with shuffles: lane 4a+j ends up with weight
+                // rows 4a..4a+3 of token column 4b+j and stores them as one 8-byte vector (a quarter of
+                // the store instructions). Two rounds of independent shuffles, as above.
+                const bool odd = lane & 1, hi = lane & 2;
+                const int j4 = lane & 3;
+                const uint64_t m0 = (uint64_t)mt * kTileM + 32 * quarter + (lane & ~3);
+#pragma unroll
+                for (int b0 = 0; b0 < kCols / 4; b0 += 4) {           // four blocks (eight shuffles) per round
+#pragma unroll
+                    for (int b = b0; b < b0 + 4; ++b) {
+                        float *r = acc + 4 * b;
+                        const float s0 = __shfl_xor_sync(0xffffffffu, odd ? r[0] : r[1], 1), s1 = __shfl_xor_sync(0xffffffffu, odd ? r[2] : r[3], 1);
+                        if (odd) { r[0] = s0; r[2] = s1; } else { r[1] = s0; r[3] = s1; }
+                    }
+#pragma unroll
+                    for (int b = b0; b < b0 + 4; ++b) {
+                        float *r = acc + 4 * b;
+                        const float s0 = __shfl_xor_sync(0xffffffffu, hi ? r[0] : r[2], 2), s1 = __shfl_xor_sync(0xffffffffu, hi ? r[1] : r[3], 2);
+                        if (hi) { r[0] = s0; r[1] = s1; } else { r[2] = s0; r[3] = s1; }
+                    }
+                }
+#pragma unroll
+                for (int b = 0; b < kCols / 4; ++b) {
+                    const int col = 4 * b + j4;
+                    if (col < ncols_here) {
+                        const uint64_t srow = (uint64_t)cb.row0 + kCols * colhalf + col;
+                        const uint64_t at = (p.out_rows ? (uint64_t)__ldg(p.out_rows + srow) : srow) * p.M + m0;
+                        // streaming stores: the results are not read again by this kernel and must not push the
+                        // activation tiles and weight rows that other CTAs are about to reuse out of L2
+                        const uint2 v = make_uint2(bf16_bits(acc[4 * b]) | ((uint32_t)bf16_bits(acc[4 * b + 1]) << 16),
+                                                   bf16_bits(acc[4 * b + 2]) | ((uint32_t)bf16_bits(acc[4 * b + 3]) << 16));
                         __stcs(reinterpret_cast<uint2 *>(p.out_bf16 + at), v);
-                    } else {
-                        __stcs(reinterpret_cast<float4 *>(out_f32 + at), make_float4(r0, r1, r2, r3));
                     }
                 }
             }

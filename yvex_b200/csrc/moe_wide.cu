@@ -3,8 +3,9 @@
 // The unit of work is a PAIR LIST: pair p = (source row src[p], expert e[p], route weight w[p]),
 // e[p] == experts meaning the shared expert. The pipeline is
 //   expert-major stable counting sort (the reference's worklist order, src/graph/worklist.c:369-441)
-//   -> gather source rows to expert-major fp16 -> grouped dequant GEMM gate & up (tcgen05)
-//   -> SwiGLU * route weight -> bf16 (+ sub-block sums for affine down qtypes)
+//   -> gather source rows to expert-major fp16
+//   -> grouped dequant GEMM gate & up (tcgen05) with SwiGLU * route weight -> bf16 in its epilogue
+//   (-> sub-block sums of the intermediates for affine down qtypes)
 //   -> grouped dequant GEMM down -> one bf16 row per pair.
 // yvex_b200_moe_wide builds the list from its own router output (T*k routed pairs + T shared
 // pairs) and finishes with the rank-ordered unpermute: routed rows summed in rank order in f32,
@@ -121,14 +122,40 @@ __global__ void wide_scatter_kernel(const int *expert_of_pair, uint64_t pairs, c
 
 // act_h[pos] = fp16 source row of the pair sorted to position pos. Source rows are `src_pitch` bytes apart
 // (a multiple of 16; rows that travelled between ranks carry a trailer behind their hidden values).
-__global__ void wide_gather_kernel(const __half *rows_h, const int *perm, const int *src_of_pair, uint64_t pairs,
-                                   uint64_t hidden, __half *act_h, uint64_t src_pitch) {
+// weight_sorted[pos] = its route weight (refused unless finite). group != 0 (affine gate/up qtypes: 32
+// for Q4_K, 16 for Q2_K): also the hi/lo fp16 sums over `group` consecutive values of the row, the
+// B' operand of the gate/up GEMM's min term.
+__global__ void wide_gather_kernel(const __half *rows_h, const int *perm, const int *src_of_pair, const float *weight_of_pair,
+                                   uint64_t pairs, uint64_t hidden, __half *act_h, float *weight_sorted, uint64_t src_pitch,
+                                   int group, __half *act_sums, int *status) {
     const uint32_t chunks = (uint32_t)(hidden / 8);           // 16-byte chunks per row
     for (uint64_t row = blockIdx.x; row < pairs; row += gridDim.x) {          // a CTA copies whole rows
+        const int pair = perm[row];
+        if (weight_of_pair && threadIdx.x == 0) {               // (a plain row gather passes no weights)
+            const float w = weight_of_pair[pair];
+            if (!isfinite(w)) raise(status, YVEX_B200_STATUS_NUMERIC);
+            weight_sorted[row] = w;
+        }
         const uint4 *src = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(rows_h) +
-                                                           (uint64_t)src_of_pair[perm[row]] * src_pitch);
+                                                           (uint64_t)src_of_pair[pair] * src_pitch);
         uint4 *dst = reinterpret_cast<uint4 *>(act_h) + row * chunks;
-        for (uint32_t c = threadIdx.x; c < chunks; c += blockDim.x) dst[c] = __ldg(src + c);
+        for (uint32_t c = threadIdx.x; c < chunks; c += blockDim.x) {      // chunks is a multiple of 32: whole warps
+            const uint4 v = __ldg(src + c);
+            dst[c] = v;
+            if (group) {
+                const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&v.x)), b = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
+                const float2 e = __half22float2(*reinterpret_cast<const __half2 *>(&v.z)), f = __half22float2(*reinterpret_cast<const __half2 *>(&v.w));
+                float sum = ((a.x + a.y) + (b.x + b.y)) + ((e.x + e.y) + (f.x + f.y));
+                for (int o = group / 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);     // group / 8 lanes per sum
+                if ((c & (uint32_t)(group / 8 - 1)) == 0) {
+                    const __half hi = __float2half_rn(sum), lo = __float2half_rn(sum - __half2float(hi));
+                    const uint32_t k = 8 * c, sb = k / 256, sub = (k % 256) / group, per = 256 / group;
+                    __half *out = act_sums + (row * (hidden / 256) + sb) * 32;
+                    out[sub] = hi;
+                    out[per + sub] = lo;
+                }
+            }
+        }
     }
 }
 
@@ -146,30 +173,33 @@ __global__ void wide_list_payload_kernel(const uint8_t *payload, uint64_t pitch,
     }
 }
 
-// mid = bf16(silu(min(g,L)) * clamp(u,+-L) * w) as fp16, plus hi/lo fp16 sums over `group`
-// consecutive intermediates (32 for Q4_K, 16 for Q2_K, 0 = none) for the down GEMM's min term.
-// blockIdx.x covers a row in 4-element pieces (inter is a multiple of 256, blocks of 64 threads
-// are therefore always full), blockIdx.y strides the rows: no per-element division.
-__global__ void __launch_bounds__(64)
-wide_swiglu_kernel(const float *gate, const float *up, const int *perm, const float *weight_of_pair,
-                   uint64_t rows, uint64_t inter, float limit, int group, __half *mid_h, __half *sums, int *status) {
-    const uint32_t q = (uint32_t)(inter / 4), col4 = blockIdx.x * blockDim.x + threadIdx.x, col = 4 * col4;
-    for (uint64_t row = blockIdx.y; row < rows; row += gridDim.y) {
-        const float w = weight_of_pair[perm[row]];
-        if (!isfinite(w)) raise(status, YVEX_B200_STATUS_NUMERIC);
-        const float4 g4 = __ldcs(reinterpret_cast<const float4 *>(gate) + row * q + col4);
-        const float4 u4 = __ldcs(reinterpret_cast<const float4 *>(up) + row * q + col4);
-        const float v0 = swiglu_mid(g4.x, u4.x, w, limit, status), v1 = swiglu_mid(g4.y, u4.y, w, limit, status);
-        const float v2 = swiglu_mid(g4.z, u4.z, w, limit, status), v3 = swiglu_mid(g4.w, u4.w, w, limit, status);
-        const __half2 h01 = __floats2half2_rn(v0, v1), h23 = __floats2half2_rn(v2, v3);
-        *reinterpret_cast<uint2 *>(mid_h + row * inter + col) =
-            make_uint2(*reinterpret_cast<const uint32_t *>(&h01), *reinterpret_cast<const uint32_t *>(&h23));
-        if (group) {
-            float s = (v0 + v1) + (v2 + v3);
-            for (int o = group / 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);     // group / 4 lanes per sum
-            if ((threadIdx.x & (group / 4 - 1)) == 0) {
-                const __half hi = __float2half_rn(s), lo = __float2half_rn(s - __half2float(hi));
-                const uint32_t sb = col / 256, sub = (col % 256) / group, per = 256 / group;
+// hi/lo fp16 sums over `group` consecutive intermediates of a row (32 for Q4_K, 16 for Q2_K) for the
+// down GEMM's min term: sums[(row, superblock)][sub] = hi, [256 / group + sub] = lo. A thread adds the
+// eight values of a 16-byte chunk as a balanced tree and group / 8 neighbouring lanes finish the tree
+// (inter is a multiple of 256, so rows start on warp boundaries of the flattened chunk index).
+__global__ void __launch_bounds__(256)
+wide_mid_sums_kernel(const __half *mid_h, uint64_t rows, uint64_t inter, int group, __half *sums) {
+    const uint64_t chunks = rows * (inter / 8), stride = (uint64_t)gridDim.x * blockDim.x;
+    const uint32_t per_row = (uint32_t)(inter / 8);
+    constexpr int kUnroll = 4;
+    for (uint64_t base = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; base < chunks; base += kUnroll * stride) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int i = 0; i < kUnroll; ++i) {
+            const uint64_t c = base + i * stride;
+            v[i] = c < chunks ? __ldcs(reinterpret_cast<const uint4 *>(mid_h) + c) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < kUnroll; ++i) {
+            const uint64_t c = base + i * stride;                  // (chunks and stride are multiples of 32: whole warps)
+            const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&v[i].x)), b = __half22float2(*reinterpret_cast<const __half2 *>(&v[i].y));
+            const float2 e = __half22float2(*reinterpret_cast<const __half2 *>(&v[i].z)), f = __half22float2(*reinterpret_cast<const __half2 *>(&v[i].w));
+            float sum = ((a.x + a.y) + (b.x + b.y)) + ((e.x + e.y) + (f.x + f.y));
+            for (int o = 1; o < group / 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (c < chunks && (c & (uint64_t)(group / 8 - 1)) == 0) {
+                const __half hi = __float2half_rn(sum), lo = __float2half_rn(sum - __half2float(hi));
+                const uint64_t row = c / per_row;
+                const uint32_t k = 8 * (uint32_t)(c - row * per_row), sb = k / 256, sub = (k % 256) / group, per = 256 / group;
                 __half *dst = sums + (row * (inter / 256) + sb) * 32;
                 dst[sub] = hi;
                 dst[per + sub] = lo;
@@ -221,17 +251,16 @@ wide_combine_kernel(const uint16_t *y, const uint16_t *y_shared, const int *pos,
 // ---- workspace -------------------------------------------------------------------------------------
 struct PairWorkspace {
     int *counts, *offsets, *perm, *pos_of_pair, *num_blocks, *expert_of_pair, *src_of_pair;
-    float *weight_of_pair;
+    float *weight_of_pair, *weight_sorted;
     ColBlock *blocks, *blocks_down;         // column-block lists of the gate/up and the down GEMM (num_blocks[0], [1])
-    __half *act_h, *mid_h, *sums;
-    float *gate, *up;
+    __half *act_h, *mid_h, *sums, *act_sums;
     uint16_t *y;
     int max_blocks;
     void rebase(void *base) {
         auto fix = [&](auto *&ptr) { ptr = reinterpret_cast<std::remove_reference_t<decltype(ptr)>>(
                                          reinterpret_cast<uintptr_t>(base) + reinterpret_cast<uintptr_t>(ptr)); };
         fix(counts); fix(offsets); fix(perm); fix(pos_of_pair); fix(num_blocks); fix(expert_of_pair); fix(src_of_pair);
-        fix(weight_of_pair); fix(blocks); fix(blocks_down); fix(act_h); fix(mid_h); fix(sums); fix(gate); fix(up); fix(y);
+        fix(weight_of_pair); fix(weight_sorted); fix(blocks); fix(blocks_down); fix(act_h); fix(mid_h); fix(sums); fix(act_sums); fix(y);
     }
 };
 
@@ -249,13 +278,13 @@ static uint64_t pair_layout(const MoeGeom &g, uint64_t pairs, uint64_t base_off,
     l.expert_of_pair = reinterpret_cast<int *>(take(pairs * 4));
     l.src_of_pair = reinterpret_cast<int *>(take(pairs * 4));
     l.weight_of_pair = reinterpret_cast<float *>(take(pairs * 4));
+    l.weight_sorted = reinterpret_cast<float *>(take(pairs * 4));
     l.blocks = reinterpret_cast<ColBlock *>(take((uint64_t)l.max_blocks * sizeof(ColBlock)));
     l.blocks_down = reinterpret_cast<ColBlock *>(take((uint64_t)l.max_blocks * sizeof(ColBlock)));
     l.act_h = reinterpret_cast<__half *>(take(pairs * g.hidden * 2));
     l.mid_h = reinterpret_cast<__half *>(take(pairs * g.inter * 2));
     l.sums = reinterpret_cast<__half *>(take(pairs * (g.inter / 256) * 64));
-    l.gate = reinterpret_cast<float *>(take(pairs * g.inter * 4));
-    l.up = reinterpret_cast<float *>(take(pairs * g.inter * 4));
+    l.act_sums = reinterpret_cast<__half *>(take(pairs * (g.hidden / 256) * 64));
     l.y = reinterpret_cast<uint16_t *>(take(pairs * g.hidden * 2));
     if (ws) *ws = l;
     return off;
@@ -290,12 +319,14 @@ static int make_act_map(CUtensorMap *map, const __half *base, uint64_t rows, uin
 }
 
 // A weight pack of `rows` rows as u8 [rows / fuse][fuse * row_bytes], boxes of [128 / fuse][box_bytes].
-static int make_weight_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes, int fuse, uint32_t box_bytes) {
+// (box_rows: 128, or 64 for the fused gate/up kernel, which takes half of a tile's rows from each matrix)
+static int make_weight_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t row_bytes, int fuse, uint32_t box_bytes,
+                           int box_rows) {
     auto fn = encode_fn();
     if (!fn) return ERR_BACKEND;
     if (reinterpret_cast<uintptr_t>(base) & 15u) return ERR_INVALID_ARG;        // weight packs must start on a 16-byte boundary
     cuuint64_t dims[2] = {fuse * row_bytes, rows / fuse}, strides[1] = {fuse * row_bytes};
-    cuuint32_t box[2] = {box_bytes, (cuuint32_t)(kTileM / fuse)}, estr[2] = {1, 1};
+    cuuint32_t box[2] = {box_bytes, (cuuint32_t)(box_rows / fuse)}, estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -313,12 +344,12 @@ static int fuse_of(uint64_t row_bytes) {
 // exchange beside the GEMM leaves a few SMs to the communication kernels.
 static std::atomic<int> g_gemm_ctas{kSmCount};
 
-template <class Dec>
+template <class Dec, bool kFused>
 static int launch_gemm(const GemmMaps &map, const GemmParams &p, cudaStream_t s) {
     const size_t smem = GemmPlan<Dec>::kBytes;
     static SmemOptIn opt_in;
-    if (opt_in.ensure(moe_grouped_gemm_kernel<Dec>, (int)smem) != OK) return ERR_BACKEND;
-    moe_grouped_gemm_kernel<Dec><<<g_gemm_ctas.load(std::memory_order_relaxed), GemmPlan<Dec>::kThreads, smem, s>>>(map, p);
+    if (opt_in.ensure(moe_grouped_gemm_kernel<Dec, kFused>, (int)smem) != OK) return ERR_BACKEND;
+    moe_grouped_gemm_kernel<Dec, kFused><<<g_gemm_ctas.load(std::memory_order_relaxed), GemmPlan<Dec>::kThreads, smem, s>>>(map, p);
     return launch_status(1);
 }
 
@@ -331,20 +362,22 @@ static int make_weight_maps(GemmMaps *maps, unsigned qtype, const void *const ro
                             uint64_t routed_rows, uint64_t shared_rows, const GemmParams &p) {
     for (int m = 0; m < 2; ++m) {
         const int src = m < nmat ? m : 0;              // unused slots repeat matrix 0 so every map is valid
-        int rc = make_weight_map(&maps->w_routed[m], routed[src], routed_rows, p.row_bytes, p.fuse, gemm_box_bytes(qtype));
+        const int box_rows = nmat == 2 ? kTileM / 2 : kTileM;
+        int rc = make_weight_map(&maps->w_routed[m], routed[src], routed_rows, p.row_bytes, p.fuse, gemm_box_bytes(qtype), box_rows);
         if (rc != OK) return rc;
         rc = make_weight_map(&maps->w_shared[m], shared[src] ? shared[src] : routed[src], shared[src] ? shared_rows : routed_rows,
-                             p.row_bytes, p.fuse, gemm_box_bytes(qtype));
+                             p.row_bytes, p.fuse, gemm_box_bytes(qtype), box_rows);
         if (rc != OK) return rc;
     }
     return OK;
 }
 
-static int run_gemm(unsigned qtype, const GemmMaps &map, const GemmParams &p, cudaStream_t s) {
+// fused: the gate/up form (two matrices, SwiGLU epilogue); otherwise the one-matrix bf16 form.
+static int run_gemm(unsigned qtype, bool fused, const GemmMaps &map, const GemmParams &p, cudaStream_t s) {
     switch (qtype) {
-    case Q_IQ2_XXS: return launch_gemm<GemmIq2>(map, p, s);
-    case Q_Q4_K: return launch_gemm<GemmQ4k>(map, p, s);
-    case Q_Q2_K: return launch_gemm<GemmQ2k>(map, p, s);
+    case Q_IQ2_XXS: return fused ? launch_gemm<GemmIq2, true>(map, p, s) : launch_gemm<GemmIq2, false>(map, p, s);
+    case Q_Q4_K: return fused ? launch_gemm<GemmQ4k, true>(map, p, s) : launch_gemm<GemmQ4k, false>(map, p, s);
+    case Q_Q2_K: return fused ? launch_gemm<GemmQ2k, true>(map, p, s) : launch_gemm<GemmQ2k, false>(map, p, s);
     default: return ERR_UNSUPPORTED;
     }
 }
@@ -375,7 +408,10 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     wide_plan_kernel<<<2, 32, 0, s>>>(pw.counts, (int)g.experts, pairs, pw.offsets, pw.blocks, pw.blocks_down, pw.num_blocks,
                                       pw.max_blocks, gemm_tile_n(g.gate_qtype), gemm_tile_n(g.down_qtype), status);
     wide_scatter_kernel<<<(unsigned)bins, 512, 0, s>>>(pw.expert_of_pair, pairs, pw.offsets, pw.perm, pw.pos_of_pair);
-    wide_gather_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(rows_h, pw.perm, pw.src_of_pair, pairs, g.hidden, pw.act_h, src_pitch);
+    const auto sum_group = [](unsigned q) { return q == Q_Q4_K ? 32 : q == Q_Q2_K ? 16 : 0; };
+    wide_gather_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(rows_h, pw.perm, pw.src_of_pair, pw.weight_of_pair, pairs, g.hidden,
+                                                              pw.act_h, pw.weight_sorted, src_pitch, sum_group(g.gate_qtype),
+                                                              pw.act_sums, status);
     int rc = launch_status(4);
     if (rc != OK) return rc;
     mark_phase(2, s);
@@ -386,22 +422,23 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     GemmParams gu{};
     gu.row_bytes = (uint32_t)(g.hidden / gg.elems * gg.bytes);
     gu.fuse = fuse_of(gu.row_bytes);
-    gu.M = (int)g.inter; gu.K = (int)g.hidden; gu.nmat = 2;
+    gu.M = (int)g.inter; gu.K = (int)g.hidden; gu.nmat = 1;              // one fused pass over both matrices
     {
         const void *routed[2] = {w.gate, w.up}, *shared[2] = {w.shared_gate, w.shared_up};
         rc = make_weight_maps(&gu_maps, g.gate_qtype, routed, shared, 2, (uint64_t)g.experts * g.inter, g.inter, gu);
         if (rc != OK) return rc;
     }
     gu.colblocks = pw.blocks; gu.num_colblocks = pw.num_blocks;
-    gu.out_f32[0] = pw.gate; gu.out_f32[1] = pw.up; gu.out_bf16 = nullptr; gu.sums = nullptr; gu.status = status;
-    rc = run_gemm(g.gate_qtype, gu_maps, gu, s);
+    gu.mid = pw.mid_h; gu.col_weight = pw.weight_sorted; gu.limit = (float)g.limit; gu.out_bf16 = nullptr; gu.sums = pw.act_sums;
+    gu.status = status;
+    rc = run_gemm(g.gate_qtype, true, gu_maps, gu, s);
     if (rc != OK) return rc;
     mark_phase(3, s);
 
-    const int group = g.down_qtype == Q_Q4_K ? 32 : g.down_qtype == Q_Q2_K ? 16 : 0;
-    wide_swiglu_kernel<<<dim3((unsigned)(g.inter / 256), (unsigned)grid_for(pairs, 1, 16)), 64, 0, s>>>(
-        pw.gate, pw.up, pw.perm, pw.weight_of_pair, pairs, g.inter, (float)g.limit, group, pw.mid_h, pw.sums, status);
-    mark_phase(6, s);                                   // SwiGLU done (an extra probe point, outside the 0..5 sequence)
+    const int group = sum_group(g.down_qtype);
+    if (group)
+        wide_mid_sums_kernel<<<grid_for(pairs * (g.inter / 8), 256, 8), 256, 0, s>>>(pw.mid_h, pairs, g.inter, group, pw.sums);
+    mark_phase(6, s);                                   // sums done (an extra probe point, outside the 0..5 sequence)
     GemmParams dn{};
     dn.row_bytes = (uint32_t)(g.inter / dg.elems * dg.bytes);
     dn.fuse = fuse_of(dn.row_bytes);
@@ -413,7 +450,7 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     }
     dn.colblocks = pw.blocks_down; dn.num_colblocks = pw.num_blocks + 1;
     dn.out_bf16 = y_list ? y_list : pw.y; dn.out_rows = y_list ? pw.perm : nullptr; dn.sums = pw.sums; dn.status = status;
-    rc = run_gemm(g.down_qtype, dn_maps, dn, s);
+    rc = run_gemm(g.down_qtype, false, dn_maps, dn, s);
     if (rc != OK) return rc;
     mark_phase(4, s);
     return launch_status(1);
@@ -676,8 +713,9 @@ extern "C" int yvex_b200_ep_dispatch(const int32_t *selected, const float *weigh
     ep_offsets_kernel<<<1, 32, 0, s>>>(counts, (int)world, offsets, send_counts);
     wide_scatter_kernel<<<(unsigned)world, 512, 0, s>>>(dest, pairs, offsets, order, inverse);
     ep_meta_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(selected, weights, order, pairs, (int)experts_per_rank, meta);
-    wide_gather_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(static_cast<const __half *>(rows_f16), order, src, pairs, hidden,
-                                                              static_cast<__half *>(send_rows_f16), hidden * 2);
+    wide_gather_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(static_cast<const __half *>(rows_f16), order, src, nullptr, pairs, hidden,
+                                                              static_cast<__half *>(send_rows_f16), nullptr, hidden * 2, 0, nullptr,
+                                                              status);
     return launch_status(5);
 }
 
