@@ -191,7 +191,7 @@ gemv_q8_0_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row
         const uint32_t slot = (uint32_t)(n % kQ8Depth), ph = (uint32_t)((n / kQ8Depth) & 1u);
         // Every thread of the CTA takes the same way out: a warp that left alone would leave its row
         // partner at the pair barrier below, and lanes that left alone would break the warp shuffles.
-        const bool landed = mbar_wait(&ctl->full[slot], ph, &ctl->abort) && !ctl->abort;
+        const bool landed = mbar_wait<kTryWaitHintNs>(&ctl->full[slot], ph, &ctl->abort) && !ctl->abort;
         if (!__syncthreads_and(landed)) break;
         const uint64_t r = (blockIdx.x + n * gridDim.x) * kQ8Rows + rw;
         if (r < rows) {                                                       // uniform over the row's warp pair
@@ -243,14 +243,14 @@ gemv_q8_0_kernel(const uint8_t *enc, uint64_t rows, uint64_t width, uint64_t row
         if (threadIdx.x == 0 && n + kQ8Depth < mine) {
             // every warp is done with the stage; when this wait runs out the abort flag is up and the
             // whole CTA leaves together at the top of the next iteration
-            if (mbar_wait(&ctl->empty[slot], ph, &ctl->abort)) { issue(n + kQ8Depth); issued = n + kQ8Depth + 1; }
+            if (mbar_wait<kTryWaitHintNs>(&ctl->empty[slot], ph, &ctl->abort)) { issue(n + kQ8Depth); issued = n + kQ8Depth + 1; }
         }
         done = n + 1;
     }
     if (threadIdx.x == 0 && ctl->abort) {
         // copies still in flight land in this CTA's shared memory: give them a bounded time to finish
         int ignore = 0;
-        for (uint64_t m = done; m < issued; ++m) mbar_wait(&ctl->full[m % kQ8Depth], (uint32_t)((m / kQ8Depth) & 1u), &ignore);
+        for (uint64_t m = done; m < issued; ++m) mbar_wait<kTryWaitHintNs>(&ctl->full[m % kQ8Depth], (uint32_t)((m / kQ8Depth) & 1u), &ignore);
     }
     if (bad) raise(status, YVEX_B200_STATUS_NUMERIC);
     if (lane == 0 && ctl->abort) raise(status, YVEX_B200_STATUS_TIMEOUT);

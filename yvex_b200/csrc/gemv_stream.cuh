@@ -398,7 +398,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
         for (uint32_t j = 0; j < n_local && ok; ++j, cj.next()) {
             while (issued < n_local && issued < j + (uint32_t)D && ok) {
                 const uint32_t slot = issued % D;
-                if (issued >= (uint32_t)D) ok = mbar_wait_warp(&ctl.empty[slot], ((issued / D) - 1u) & 1u, &ctl.abort);
+                if (issued >= (uint32_t)D) ok = mbar_wait_warp<kTryWaitHintNs>(&ctl.empty[slot], ((issued / D) - 1u) & 1u, &ctl.abort);
                 if (!ok) break;
                 uint64_t row0;
                 const uint32_t nrows = rows_of(ci, row0);
@@ -416,7 +416,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
             }
             if (!ok) break;
             const uint32_t buf = j % (uint32_t)(D + 1);
-            ok = mbar_wait_warp(&ctl.red_full[buf], (j / (uint32_t)(D + 1)) & 1u, &ctl.abort);
+            ok = mbar_wait_warp<kTryWaitHintNs>(&ctl.red_full[buf], (j / (uint32_t)(D + 1)) & 1u, &ctl.abort);
             if (!ok) break;
             uint64_t row0;
             const uint32_t nrows = rows_of(cj, row0);
@@ -437,7 +437,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
         if (!ok && lane == 0) {
             // copies still in flight land in this CTA's shared memory: give them a bounded time to finish
             int ignore = 0;
-            if (Dec::kTables) mbar_wait(&ctl.tab_full, 0u, &ignore);
+            if (Dec::kTables) mbar_wait<kTryWaitHintNs>(&ctl.tab_full, 0u, &ignore);
             raise(p.status, YVEX_B200_STATUS_TIMEOUT);
         }
         return;
@@ -475,7 +475,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
     // meets the other consumers at the named barriers of every matrix change and nobody waits for it.
     bool dead = false;
     if (Dec::kTables && n_local) {
-        if (!mbar_wait_warp(&ctl.tab_full, 0u, &ctl.abort)) dead = true;
+        if (!mbar_wait_warp<kTryWaitHintNs>(&ctl.tab_full, 0u, &ctl.abort)) dead = true;
         asm volatile("" : "+r"(l.nib_base), "+r"(l.sgn_base));      // table reads may not move above this point
     }
     BUnit breg;
@@ -543,7 +543,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
             cur_m = c.m;
         }
         const uint32_t slot = i % D, buf = i % (uint32_t)(D + 1);
-        if (!dead && !mbar_wait_warp(&ctl.full[slot], (i / D) & 1u, &ctl.abort)) dead = true;
+        if (!dead && !mbar_wait_warp<kTryWaitHintNs>(&ctl.full[slot], (i / D) & 1u, &ctl.abort)) dead = true;
         float acc[kGroupsPerWarp][2];
         int bad[kGroupsPerWarp];
 #pragma unroll
