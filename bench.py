@@ -539,8 +539,8 @@ def run_native_ep(args):
         assert bops.workspace_required_wide(job.layer, T, C.byref(need), C.byref(be.err)) == B.OK
         rcw, bws, _ = be.tensor(need.value)
         assert rcw == B.OK and B._lib.yvex_backend_workspace_attach(be.h, bws, C.byref(be.err)) == B.OK
-        batch = B.RowBatch(T, H, H, host_x.data_ptr(), None, None, host_lg.data_ptr(), None, None, 0)
-        bout = B.RowBatchOutput(host_out.data_ptr(), T * H, None, None, 0)
+        batch = B.row_batch(T, H, host_rows=host_x.data_ptr(), router_logits=host_lg.data_ptr())
+        bout = B.row_output(host_out.data_ptr(), T * H)
         bres = B.RowBatchResult()
         e2e_api = "yvex_backend_moe_operations.execute_rows_wide (C11 host boundary), pinned host rows in/out"
 

@@ -174,73 +174,150 @@ typedef enum {
     YVEX_MOE_WEIGHT_ROUTED_UP, YVEX_MOE_WEIGHT_ROUTED_DOWN, YVEX_MOE_WEIGHT_SHARED_GATE, YVEX_MOE_WEIGHT_SHARED_UP,
     YVEX_MOE_WEIGHT_SHARED_DOWN, YVEX_MOE_WEIGHT_COUNT
 } yvex_moe_weight_slot;
+/*
+ * The structs below are laid out field for field as the reference's (include/yvex/internal/moe.h:54-84,
+ * :182-271, include/yvex/internal/execution.h:329-333, include/yvex/internal/execution_batch.h:126-137),
+ * so a caller compiled against the reference's headers can pass its own objects: no field-copying
+ * adaptor. Enumerations this backend does not interpret are declared as `int` (the same size and
+ * alignment); fields it does not use are ignored, not removed. tests/abi_probe.c prints every size and
+ * offset and is compared with the table the same file produced against the reference's headers.
+ */
+#define YVEX_RUNTIME_DESCRIPTOR_QTYPE_CAP 43u
+#define YVEX_SHA256_HEX_CAP 65u                  /* include/yvex/artifact.h:68 */
+#define YVEX_MOE_ROW_BATCH_SCHEMA_V1 1u
+#define YVEX_MOE_ROW_BATCH_RESULT_SCHEMA_V4 4u
+/* Extension: a row batch whose schema_version is this value is a yvex_moe_row_batch_logits. */
+#define YVEX_MOE_ROW_BATCH_SCHEMA_B200_LOGITS 0x42320001u
+typedef enum { YVEX_EXECUTION_CLASS_PORTABLE_REFERENCE = 0, YVEX_EXECUTION_CLASS_DEVICE_NATIVE, YVEX_EXECUTION_CLASS_FORENSIC_REFERENCE } yvex_execution_class;
+typedef enum { YVEX_EXECUTION_LAYOUT_CANONICAL_ROW = 0, YVEX_EXECUTION_LAYOUT_CONTIGUOUS_DENSE, YVEX_EXECUTION_LAYOUT_EXPERT_MAJOR,
+               YVEX_EXECUTION_LAYOUT_DERIVED_BACKEND } yvex_execution_layout_class;
+typedef struct yvex_execution_batch yvex_execution_batch;                 /* only ever pointed to */
+typedef struct yvex_execution_batch_source yvex_execution_batch_source;
+typedef struct yvex_execution_batch_row yvex_execution_batch_row;
+typedef struct yvex_expert_worklist_policy yvex_expert_worklist_policy;
 typedef struct {
+    unsigned long long active_weight_bytes, state_bytes, activation_bytes, temporary_bytes;
+    unsigned long long measured_operations, missing_operations;
+    int complete;
+} yvex_execution_memory_facts;
+typedef struct {
+    unsigned long long tensor_id, expert_index;
+    int role;                            /* yvex_tensor_role */
     unsigned int qtype;
+    yvex_execution_layout_class layout;  /* a backend-derived layout is refused: none is offered */
+    int activation;                      /* yvex_execution_activation_class */
     const char *kernel_family;           /* NULL or one of the YVEX_MOE_KERNEL_SM100_* names; others are refused */
     const unsigned char *encoded;        /* HOST pointer into the resident arena */
-    size_t encoded_bytes;
+    size_t encoded_bytes, storage_bytes;
     unsigned long long row_bytes, row_width, row_count;
+    unsigned long long device_address;   /* when non-zero, used as is (src/backend/cuda/moe.c:235-236); else `encoded` is resolved */
 } yvex_moe_weight_view;
 typedef struct {
+    unsigned int schema_version;
+    unsigned long long ordinal, layer_index, predictor_index;
+    int tensor_scope;                    /* yvex_tensor_scope */
     yvex_moe_router_class router_class;
+    int scoring, topk_policy, activation;     /* sqrt-softplus / no-aux top-k / SiLU: the only values (include/yvex/internal/moe.h:35-37) */
     /* residual_streams > 1 selects the mHC envelope: rows are expanded_width = residual_streams *
      * hidden_width wide on both sides, the FFN_NORM / MHC_FUNCTION / MHC_BASE / MHC_SCALE weight slots
-     * (F32) are required and mhc_mixing_rows = (residual_streams + 2) * residual_streams. */
+     * are required and mhc_mixing_rows = (residual_streams + 2) * residual_streams. */
     unsigned long long hidden_width, residual_streams, expanded_width;
     unsigned long long mhc_mixing_rows, mhc_sinkhorn_iterations;
     unsigned long long routed_experts, shared_experts, experts_per_token;
     unsigned long long expert_intermediate_width, shared_intermediate_width;
-    unsigned long long hash_table_rows;
+    unsigned long long hash_table_rows, hash_table_columns, correction_bias_width;
     double rms_epsilon, mhc_epsilon, mhc_post_multiplier;
     double routed_scaling_factor, activation_limit;
-    int normalize_topk_probabilities;
+    int requires_token_ids, requires_correction_bias, normalize_topk_probabilities;
+    unsigned long long tensor_ids[YVEX_MOE_WEIGHT_COUNT];
+    unsigned int qtypes[YVEX_MOE_WEIGHT_COUNT];
+    char layer_identity[YVEX_SHA256_HEX_CAP];
 } yvex_moe_layer_plan;
 /* Pointer-free worklist summary, laid out as include/yvex/internal/execution_batch.h:126-137. */
 typedef yvex_b200_worklist_observation yvex_expert_worklist_observation;
 typedef struct {
-    int status, pending;
     unsigned long long row_count, row_expert_pairs;
     yvex_expert_worklist_observation worklist;       /* copied with the status word in deferred mode (src/backend/cuda/moe.c:1710-1716) */
+    unsigned long long tensor_core_executed_pairs;
+    unsigned long long routed_experts, active_base_bytes, active_per_expert_bytes;
+    unsigned long long activation_bytes, temporary_bytes;
+    int status, pending;
 } yvex_moe_device_completion_slot;
 typedef struct { int defer; yvex_moe_device_completion_slot *host; } yvex_moe_device_completion;
 typedef struct {
     const yvex_moe_layer_plan *layer;
     yvex_moe_weight_view weights[YVEX_MOE_WEIGHT_COUNT];
+    const float *expanded_input;               /* single-token entry points only; unused by the row-batch table */
+    const yvex_device_tensor *device_input;
+    yvex_device_tensor *device_output;
+    unsigned int token_id;
+    int token_id_present;
     int (*cancel_requested)(void *context);
     void *cancel_context;
+    int evidence_level;                        /* yvex_attention_evidence_level; FULL (3) is refused like the reference's width-N path */
+    int eager_execution;
     const yvex_moe_device_completion *device_completion;
+    const yvex_execution_batch *execution_batch;
+    const yvex_expert_worklist_policy *worklist_policy;
 } yvex_moe_layer_job;
 typedef struct {
+    unsigned int schema_version;               /* YVEX_MOE_ROW_BATCH_SCHEMA_V1, or the logits extension below */
     unsigned long long row_count, row_width, row_stride;
     const float *expanded_rows;                /* host rows (copied in), or NULL when device_rows is given */
     const yvex_device_tensor *device_rows;     /* f32 [row_count x row_stride] */
     yvex_device_tensor *device_outputs;        /* f32 [row_count x row_stride], optional when host output is given */
-    const float *router_logits;                /* extension: host logits [row_count x routed_experts] replacing the router projection */
-    const yvex_device_tensor *device_router_logits;
     const unsigned int *token_ids;
     int token_ids_present;
+    int provenance;                            /* yvex_execution_batch_provenance: counted in the worklist summary */
+    unsigned int phase;
+    yvex_execution_class execution_class;
+    const char *execution_profile_identity;
+    const yvex_execution_batch_source *execution_sources;
+    const yvex_execution_batch_row *execution_rows;
+    unsigned long long execution_source_count;
+    int complete_after_operation;
 } yvex_moe_row_batch;
+/* Extension: router logits supplied by the caller replace the router projection. base.schema_version
+ * must be YVEX_MOE_ROW_BATCH_SCHEMA_B200_LOGITS; the table's entry points take a pointer to `base`. */
 typedef struct {
-    float *combined_rows;                      /* host [row_count x hidden_width], optional */
-    unsigned long long combined_capacity;
+    yvex_moe_row_batch base;
+    const float *router_logits;                /* host [row_count x routed_experts] */
+    const yvex_device_tensor *device_router_logits;
+} yvex_moe_row_batch_logits;
+typedef struct {
+    /* host arrays, each optional here (the reference's width-N path requires all of them): the combined rows,
+     * the f32 rank-ordered routed sum and the shared expert's row [row_count x hidden_width], and with the
+     * mHC envelope its post gates [row_count x streams] and combination matrices [row_count x streams^2] */
+    float *combined_rows, *routed_rows, *shared_rows, *post_rows, *combination_rows;
+    unsigned long long combined_capacity, routed_capacity, shared_capacity;
+    unsigned long long post_capacity, combination_capacity;
     unsigned long long *selected_experts;      /* host [row_count x experts_per_token], optional */
     float *selected_weights;
     unsigned long long selection_capacity;
 } yvex_moe_row_batch_output;
 typedef struct {
-    int completed, device_completion_pending;
-    unsigned long long row_count, row_expert_pairs;
+    unsigned int schema_version;
+    int completed, execution_profile_available, device_completion_pending;
+    yvex_execution_class execution_class;
+    unsigned long long row_count, row_expert_pairs, unique_experts;
+    yvex_expert_worklist_observation worklists;
     unsigned long long grouped_expert_operations, shared_expert_operations;
     unsigned long long expert_subviews_accessed, encoded_bytes_read;
-    unsigned long long h2d_bytes, d2h_bytes, d2d_bytes, kernel_launches, tensor_core_launches;
-    unsigned long long stream_synchronizations;
-    unsigned long long active_weight_base_bytes, active_weight_per_unique_expert_bytes;
-    unsigned long long activation_bytes, temporary_bytes;
-    /* as the reference publishes them (src/backend/cuda/moe.c:1757-1786, :1905-1915): populated experts,
-     * the device-built worklist summary, copies counted, bytes of weights the batch had to read */
-    unsigned long long unique_experts, upload_count, download_count, active_weight_bytes;
-    unsigned long long pipeline_chunks;        /* row chunks whose host copies overlapped compute (wide entry, host rows) */
-    yvex_expert_worklist_observation worklists;
+    unsigned long long h2d_bytes, d2h_bytes, d2d_bytes, kernel_launches;
+    unsigned long long tensor_core_launches;
+    unsigned long long graph_launches, graph_captures, graph_replays;
+    unsigned long long upload_count, download_count, cache_hits, cache_misses;
+    unsigned long long stream_synchronizations, device_synchronizations;
+    unsigned long long active_weight_base_bytes;
+    unsigned long long active_weight_per_unique_expert_bytes;
+    yvex_execution_memory_facts memory;        /* active weight bytes (each byte once), activation and temporary bytes */
+    unsigned long long total_ns, synchronization_ns;
+    char execution_profile_identity[YVEX_SHA256_HEX_CAP];
+    char execution_batch_identity[YVEX_SHA256_HEX_CAP];
+    char worklist_policy_identity[YVEX_SHA256_HEX_CAP];
+    char expert_worklist_identity[YVEX_SHA256_HEX_CAP];
+    char routing_digest[YVEX_SHA256_HEX_CAP];
+    char execution_identity[YVEX_SHA256_HEX_CAP];
 } yvex_moe_row_batch_result;
 typedef struct {
     /* Derived layouts are not offered: both return YVEX_ERR_UNSUPPORTED and the canonical row layout is used. */
@@ -257,11 +334,16 @@ typedef struct {
     int (*execute_rows_wide)(yvex_backend *backend, const yvex_moe_layer_job *job, const yvex_moe_row_batch *batch,
                              const yvex_moe_row_batch_output *output, yvex_moe_row_batch_result *result, yvex_error *err);
 } yvex_backend_moe_operations;
+/* "sizeof type N" / "offsetof type.field N" lines for every entry of yvex_b200_abi_fields.h, as this
+ * library was compiled; a binding compares its own table with it. No reference counterpart. */
+const char *yvex_backend_abi_layout(void);
+/* Row ranges whose host copies overlapped compute in the last execute_rows_wide call (0: the call did
+ * not use the copy pipeline). No reference counterpart. */
+unsigned long long yvex_backend_moe_last_pipeline_chunks(const yvex_backend *backend);
 /* NULL unless the backend is an open CUDA backend (src/backend/cuda/moe.c:1968-1981). */
 const yvex_backend_moe_operations *yvex_backend_moe_operations_get(const yvex_backend *backend);
 
 /* ---- external MoE input fixtures: include/yvex/internal/moe.h:120-160, src/runtime/moe_input.c ------------- */
-#define YVEX_SHA256_HEX_CAP 65u
 #define YVEX_MOE_INPUT_SUFFIX ".yvex-moe-input"
 typedef struct {
     unsigned int schema_version;

@@ -137,6 +137,15 @@ int yvex_b200_moe_decode(const yvex_b200_moe_geometry *g, const yvex_b200_moe_we
                          const float *x, const float *logits, const uint32_t *token_ids,
                          uint64_t rows, float *out, int32_t *selected_out, float *weights_out,
                          void *workspace, uint64_t workspace_bytes, int *status, void *stream);
+/* The same with the parts of the sum published too (either may be NULL): routed_out = the f32
+ * rank-ordered sum of the routed experts' bf16 rows, shared_out = the shared expert's bf16 row, both
+ * [rows x hidden] f32 on the device, as the reference's routed_output / shared_output
+ * (src/runtime/moe.c:606-637); out = bf16(routed + shared) as before. */
+int yvex_b200_moe_decode_parts(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w,
+                               const float *x, const float *logits, const uint32_t *token_ids,
+                               uint64_t rows, float *out, float *routed_out, float *shared_out,
+                               int32_t *selected_out, float *weights_out,
+                               void *workspace, uint64_t workspace_bytes, int *status, void *stream);
 
 /*
  * The same layer for a wide batch (prefill / expert-parallel shard): route, expert-major
@@ -157,6 +166,12 @@ int yvex_b200_moe_wide(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weig
                        const float *x, const float *logits, const uint32_t *token_ids,
                        uint64_t rows, float *out, int32_t *selected_out, float *weights_out,
                        void *workspace, uint64_t workspace_bytes, int *status, void *stream);
+/* With routed_out / shared_out as in yvex_b200_moe_decode_parts. */
+int yvex_b200_moe_wide_parts(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w,
+                             const float *x, const float *logits, const uint32_t *token_ids,
+                             uint64_t rows, float *out, float *routed_out, float *shared_out,
+                             int32_t *selected_out, float *weights_out,
+                             void *workspace, uint64_t workspace_bytes, int *status, void *stream);
 
 /*
  * Expert-parallel building blocks (no reference counterpart: the reference is single-device,

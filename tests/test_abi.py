@@ -100,3 +100,45 @@ def test_compute_without_device_fails_loudly(lib):
         pytest.skip("device present")
     with pytest.raises(RuntimeError):
         lib.Status()
+
+
+def layout_table(text):
+    return dict(line.rsplit(" ", 1) for line in text.strip().splitlines())
+
+
+def test_boundary_structs_are_laid_out_as_the_reference_declares_them(lib):
+    """Every sizeof / offsetof of the structs that cross the host boundary equals the table
+    tests/abi_probe.c printed when it was compiled against the reference's own headers
+    (tests/golden/abi_layout.txt, written by tests/golden/make_abi_layout.py), so a caller built
+    against those headers can hand its structs over as they are."""
+    from yvex_b200 import backend as B
+    ours = layout_table(B._lib.yvex_backend_abi_layout().decode())
+    want = layout_table(open(os.path.join(ROOT, "tests", "golden", "abi_layout.txt")).read())
+    assert ours == want
+    assert len(ours) > 190
+    # where the reference checkout is at hand, the committed table is still what its headers give
+    ref = os.environ.get("YVEX_REF") or os.path.join(os.path.dirname(ROOT), "reference")
+    if os.path.isdir(os.path.join(ref, "include", "yvex")):
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("make_abi_layout", os.path.join(ROOT, "tests", "golden", "make_abi_layout.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        assert layout_table(mod.reference_table(ref)) == want
+
+
+def test_ctypes_mirror_matches_the_compiled_layout(lib):
+    from yvex_b200 import backend as B
+    table = layout_table(B._lib.yvex_backend_abi_layout().decode())
+    mirror = {"yvex_moe_weight_view": B.WeightView, "yvex_moe_layer_plan": B.LayerPlan,
+              "yvex_execution_memory_facts": B.MemoryFacts, "yvex_expert_worklist_observation": B.WorklistObservation,
+              "yvex_moe_device_completion_slot": B.CompletionSlot, "yvex_moe_device_completion": B.Completion,
+              "yvex_moe_layer_job": B.LayerJob, "yvex_moe_row_batch": B.RowBatch, "yvex_moe_row_batch_output": B.RowBatchOutput,
+              "yvex_moe_row_batch_result": B.RowBatchResult, "yvex_moe_input_summary": B.MoeInputSummary,
+              "yvex_moe_input_layer_record": B.MoeInputRecord, "yvex_error": B.Error}
+    for name, cls in mirror.items():
+        assert C.sizeof(cls) == int(table[f"sizeof {name}"]), name
+        for field, _ in cls._fields_:
+            assert getattr(cls, field).offset == int(table[f"offsetof {name}.{field}"]), (name, field)
+    ops = {f: getattr(B.MoeOperations, f).offset for f, _ in B.MoeOperations._fields_}
+    for f in ("derived_layout_plan", "derived_layout_build", "workspace_required", "execute_rows", "complete_rows"):
+        assert ops[f] == int(table[f"offsetof yvex_backend_moe_operations.{f}"])

@@ -56,10 +56,10 @@ def run_rows(B, be, ops, job, x, logits, wide=False, selection=True):
     out = np.zeros((rows, H), np.float32)
     sel = np.zeros((rows, k), np.uint64)
     wts = np.zeros((rows, k), np.float32)
-    batch = B.RowBatch(rows, H, H, x.ctypes.data_as(B.vp), None, None,
-                       None if logits is None else logits.ctypes.data_as(B.vp), None, None, 0)
-    o = B.RowBatchOutput(out.ctypes.data_as(B.vp), out.size, sel.ctypes.data_as(B.vp) if selection else None,
-                         wts.ctypes.data_as(B.vp) if selection else None, sel.size)
+    batch = B.row_batch(rows, H, host_rows=x.ctypes.data_as(B.vp),
+                        router_logits=None if logits is None else logits.ctypes.data_as(B.vp))
+    o = B.row_output(out.ctypes.data_as(B.vp), out.size, sel.ctypes.data_as(B.vp) if selection else None,
+                     wts.ctypes.data_as(B.vp) if selection else None, sel.size)
     res = B.RowBatchResult()
     fn = ops.execute_rows_wide if wide else ops.execute_rows
     rc = fn(be.h, C.byref(job), C.byref(batch), C.byref(o), C.byref(res), C.byref(be.err))
@@ -90,7 +90,7 @@ def test_execute_rows_device_tensors_and_deferred_completion(B, golden):
     slot = B.CompletionSlot()
     comp = B.Completion(1, C.pointer(slot))
     job.device_completion = C.pointer(comp)
-    batch = B.RowBatch(rows, H, H, None, tin, tout, None, None, None, 0)
+    batch = B.row_batch(rows, H, device_rows=tin, device_outputs=tout)
     res = B.RowBatchResult()
     rc = ops.execute_rows(be.h, C.byref(job), C.byref(batch), None, C.byref(res), C.byref(be.err))
     assert rc == B.OK and res.device_completion_pending == 1 and res.completed == 0
@@ -101,6 +101,72 @@ def test_execute_rows_device_tensors_and_deferred_completion(B, golden):
     assert ops.complete_rows(be.h, 0, C.byref(res), C.byref(be.err)) == B.STATE
     rc, out = be.read(tout, np.float32, rows * H)
     assert rc == B.OK and rel_l2(out.reshape(rows, H), golden["layer_small_router_out"].view(np.float32)) <= 1e-3
+    assert be.close() == B.OK
+
+
+@pytest.mark.parametrize("wide", [False, True])
+def test_partial_outputs_routed_shared_post_combination(B, golden, wide):
+    """routed_rows / shared_rows (and with the envelope post_rows / combination_rows) are published when the
+    caller gives room for them: the f32 rank-ordered routed sum and the shared expert's row, whose bf16-rounded
+    sum is the combined row bit for bit (src/runtime/moe.c:606-637, :1501-1508)."""
+    be, arena, job, spec, x, logits = layer_setup(B, "small_logits")
+    rows, H = x.shape
+    ops, _ = attach_workspace(B, be, job, rows, wide=wide)
+    out, routed, shared = (np.zeros((rows, H), np.float32) for _ in range(3))
+    batch = B.row_batch(rows, H, host_rows=x.ctypes.data_as(B.vp), router_logits=logits.ctypes.data_as(B.vp))
+    o = B.row_output(out.ctypes.data_as(B.vp), out.size, routed=routed.ctypes.data_as(B.vp), shared=shared.ctypes.data_as(B.vp),
+                     routed_capacity=routed.size, shared_capacity=shared.size)
+    res = B.RowBatchResult()
+    fn = ops.execute_rows_wide if wide else ops.execute_rows
+    assert fn(be.h, C.byref(job), C.byref(batch), C.byref(o), C.byref(res), C.byref(be.err)) == B.OK, be.message()
+    assert rel_l2(out, golden["layer_small_logits_out"].view(np.float32)) <= 1e-3
+    assert (synth.bf16_round(routed + shared).view(np.uint32) == out.view(np.uint32)).all()
+    assert (synth.bf16_round(shared).view(np.uint32) == shared.view(np.uint32)).all() and np.abs(routed).max() > 0
+    assert res.schema_version == 4 and res.execution_class == B.EXECUTION_CLASS_DEVICE_NATIVE and res.memory.complete == 1
+    # too small a capacity is refused before anything runs
+    o.routed_capacity = routed.size - 1
+    assert fn(be.h, C.byref(job), C.byref(batch), C.byref(o), C.byref(res), C.byref(be.err)) == B.BOUNDS
+    # a batch of an unknown schema, and a full-evidence job, are refused like the reference's width-N entry
+    o.routed_capacity = routed.size
+    batch.base.schema_version = 7
+    assert fn(be.h, C.byref(job), C.byref(batch), C.byref(o), C.byref(res), C.byref(be.err)) == B.INVALID_ARG
+    batch.base.schema_version = B.ROW_BATCH_SCHEMA_LOGITS
+    job.evidence_level = 3
+    assert fn(be.h, C.byref(job), C.byref(batch), C.byref(o), C.byref(res), C.byref(be.err)) == B.INVALID_ARG
+    job.evidence_level = 0
+    # a weight view that names its device address directly needs no arena lookup
+    addr = B.ull()
+    v = job.weights[B.W_DOWN]
+    assert B._lib.yvex_backend_resident_resolve(be.h, v.encoded, v.encoded_bytes, C.byref(addr)) == 1
+    v.device_address, keep = addr.value, v.encoded
+    v.encoded = None
+    out2 = np.zeros_like(out)
+    o2 = B.row_output(out2.ctypes.data_as(B.vp), out2.size)
+    assert fn(be.h, C.byref(job), C.byref(batch), C.byref(o2), C.byref(res), C.byref(be.err)) == B.OK, be.message()
+    assert (out2.view(np.uint32) == out.view(np.uint32)).all()
+    v.encoded, v.device_address = keep, 0
+    assert be.close() == B.OK
+
+
+def test_envelope_publishes_post_and_combination_rows(B, golden):
+    H, S, T, seed = CASES["envelope"]["small"]
+    fn_, scale, base, norm, expanded = envelope_inputs("small")
+    spec, weights, router, _, _ = layer_inputs("small_router")
+    be = B.Backend()
+    arena = B.ResidentArena(be, dict(weights, router=router, ffn_norm=norm, mhc_fn=fn_, mhc_base=base, mhc_scale=scale))
+    job = B.moe_job(arena, spec, residual_streams=S, envelope_policy=ENVELOPE_POLICY)
+    ops, _ = attach_workspace(B, be, job, T)
+    out = np.zeros((T, S * H), np.float32)
+    post, comb = np.zeros((T, S), np.float32), np.zeros((T, S, S), np.float32)
+    batch = B.row_batch(T, S * H, host_rows=expanded.ctypes.data_as(B.vp))
+    o = B.row_output(out.ctypes.data_as(B.vp), out.size, post=post.ctypes.data_as(B.vp), combination=comb.ctypes.data_as(B.vp),
+                     post_capacity=post.size, combination_capacity=comb.size)
+    res = B.RowBatchResult()
+    assert ops.execute_rows(be.h, C.byref(job), C.byref(batch), C.byref(o), C.byref(res), C.byref(be.err)) == B.OK, be.message()
+    assert rel_l2(out, golden["envelope_small_out"].view(np.float32)) <= 1e-3
+    # post gates are multiplier * sigmoid(.) in (0, multiplier); Sinkhorn leaves every combination matrix doubly stochastic
+    assert (post > 0).all() and (post < ENVELOPE_POLICY["post_multiplier"]).all()
+    assert np.abs(comb.sum(axis=2) - 1.0).max() < 1e-3 and np.abs(comb.sum(axis=1) - 1.0).max() < 1e-3
     assert be.close() == B.OK
 
 
@@ -331,7 +397,7 @@ def test_execute_rows_result_counters_match_the_reference_contract(B):
     assert list(w.width_histogram) == [1 if i == min(rows, 16) else 0 for i in range(17)]
     base = sum(job.weights[s].encoded_bytes for s in (B.W_SHARED_GATE, B.W_SHARED_UP, B.W_SHARED_DOWN, B.W_ROUTER))
     assert res.active_weight_base_bytes == base
-    assert res.encoded_bytes_read == base + unique * spec.weight_bytes_per_expert() == res.active_weight_bytes
+    assert res.encoded_bytes_read == base + unique * spec.weight_bytes_per_expert() == res.memory.active_weight_bytes
     assert be.close() == B.OK
 
 
@@ -349,16 +415,16 @@ def test_execute_rows_wide_copy_pipeline_is_bit_identical(B):
     ops, _ = attach_workspace(B, be, job, T, wide=True)
     rc, out, sel, wts, res = run_rows(B, be, ops, job, x, logits, wide=True)
     assert rc == B.OK, be.message()
-    assert res.pipeline_chunks == 4 and res.tensor_core_launches == 8 and res.completed == 1
+    assert B._lib.yvex_backend_moe_last_pipeline_chunks(be.h) == 4 and res.tensor_core_launches == 8 and res.completed == 1
     tin, tlg = be.from_array(x, B.F32), be.from_array(logits, B.F32)
     tout = be.tensor(x.nbytes, B.F32, [T, H])[1]
     sel2, wts2 = np.zeros((T, k), np.uint64), np.zeros((T, k), np.float32)
-    batch = B.RowBatch(T, H, H, None, tin, tout, None, tlg, None, 0)
-    o = B.RowBatchOutput(None, 0, sel2.ctypes.data_as(B.vp), wts2.ctypes.data_as(B.vp), sel2.size)
+    batch = B.row_batch(T, H, device_rows=tin, device_outputs=tout, device_router_logits=tlg)
+    o = B.row_output(None, 0, sel2.ctypes.data_as(B.vp), wts2.ctypes.data_as(B.vp), sel2.size)
     res2 = B.RowBatchResult()
     assert ops.execute_rows_wide(be.h, C.byref(job), C.byref(batch), C.byref(o), C.byref(res2), C.byref(be.err)) == B.OK, be.message()
     rc, whole = be.read(tout, np.float32, T * H)
-    assert res2.pipeline_chunks == 0 and res2.tensor_core_launches == 2
+    assert B._lib.yvex_backend_moe_last_pipeline_chunks(be.h) == 0 and res2.tensor_core_launches == 2
     assert (sel == sel2).all() and (wts.view(np.uint32) == wts2.view(np.uint32)).all()
     assert (out.view(np.uint32) == whole.reshape(T, H).view(np.uint32)).all()
     assert res.unique_experts == res2.unique_experts == E
@@ -460,7 +526,7 @@ def test_fixture_file_drives_execute_rows(B, golden, tmp_path):
     ops, _ = attach_workspace(B, be, job, x.shape[0])
     rows, H, k = x.shape[0], spec.hidden, spec.topk
     out, sel, wts = np.zeros((rows, H), np.float32), np.zeros((rows, k), np.uint64), np.zeros((rows, k), np.float32)
-    o = B.RowBatchOutput(out.ctypes.data_as(B.vp), out.size, sel.ctypes.data_as(B.vp), wts.ctypes.data_as(B.vp), sel.size)
+    o = B.row_output(out.ctypes.data_as(B.vp), out.size, sel.ctypes.data_as(B.vp), wts.ctypes.data_as(B.vp), sel.size)
     res = B.RowBatchResult()
     assert ops.execute_rows(be.h, C.byref(job), C.byref(batch), C.byref(o), C.byref(res), C.byref(be.err)) == B.OK, be.message()
     assert (sel == golden["layer_small_router_sel"]).all()

@@ -39,19 +39,38 @@ class Facts(C.Structure):
                                    "activation_bytes", "temporary_bytes", "tensor_core_launches")] + [("available", C.c_int)]
 
 
+HEX = C.c_char * 65
+ROW_BATCH_SCHEMA_V1, ROW_BATCH_SCHEMA_LOGITS, ROW_BATCH_RESULT_SCHEMA_V4 = 1, 0x42320001, 4
+EXECUTION_CLASS_DEVICE_NATIVE = 1
+
+
+class MemoryFacts(C.Structure):
+    """yvex_execution_memory_facts (include/yvex/internal/execution.h:329-333)."""
+    _fields_ = [(n, ull) for n in ("active_weight_bytes", "state_bytes", "activation_bytes", "temporary_bytes",
+                                   "measured_operations", "missing_operations")] + [("complete", C.c_int)]
+
+
 class WeightView(C.Structure):
-    _fields_ = [("qtype", C.c_uint), ("kernel_family", C.c_char_p), ("encoded", vp), ("encoded_bytes", C.c_size_t),
-                ("row_bytes", ull), ("row_width", ull), ("row_count", ull)]
+    """yvex_moe_weight_view, field for field (include/yvex/internal/moe.h:54-64)."""
+    _fields_ = [("tensor_id", ull), ("expert_index", ull), ("role", C.c_int), ("qtype", C.c_uint), ("layout", C.c_int),
+                ("activation", C.c_int), ("kernel_family", C.c_char_p), ("encoded", vp), ("encoded_bytes", C.c_size_t),
+                ("storage_bytes", C.c_size_t), ("row_bytes", ull), ("row_width", ull), ("row_count", ull), ("device_address", ull)]
 
 
 class LayerPlan(C.Structure):
-    _fields_ = [("router_class", C.c_int), ("hidden_width", ull), ("residual_streams", ull), ("expanded_width", ull),
+    """yvex_moe_layer_plan (include/yvex/internal/moe.h:65-84)."""
+    _fields_ = [("schema_version", C.c_uint), ("ordinal", ull), ("layer_index", ull), ("predictor_index", ull),
+                ("tensor_scope", C.c_int), ("router_class", C.c_int), ("scoring", C.c_int), ("topk_policy", C.c_int),
+                ("activation", C.c_int),
+                ("hidden_width", ull), ("residual_streams", ull), ("expanded_width", ull),
                 ("mhc_mixing_rows", ull), ("mhc_sinkhorn_iterations", ull),
                 ("routed_experts", ull), ("shared_experts", ull), ("experts_per_token", ull),
                 ("expert_intermediate_width", ull), ("shared_intermediate_width", ull), ("hash_table_rows", ull),
+                ("hash_table_columns", ull), ("correction_bias_width", ull),
                 ("rms_epsilon", C.c_double), ("mhc_epsilon", C.c_double), ("mhc_post_multiplier", C.c_double),
                 ("routed_scaling_factor", C.c_double), ("activation_limit", C.c_double),
-                ("normalize_topk_probabilities", C.c_int)]
+                ("requires_token_ids", C.c_int), ("requires_correction_bias", C.c_int), ("normalize_topk_probabilities", C.c_int),
+                ("tensor_ids", ull * W_COUNT), ("qtypes", C.c_uint * W_COUNT), ("layer_identity", HEX)]
 
 
 class WorklistObservation(C.Structure):
@@ -63,8 +82,11 @@ class WorklistObservation(C.Structure):
 
 
 class CompletionSlot(C.Structure):
-    _fields_ = [("status", C.c_int), ("pending", C.c_int), ("row_count", ull), ("row_expert_pairs", ull),
-                ("worklist", WorklistObservation)]
+    """yvex_moe_device_completion_slot (include/yvex/internal/moe.h:182-189)."""
+    _fields_ = [("row_count", ull), ("row_expert_pairs", ull), ("worklist", WorklistObservation),
+                ("tensor_core_executed_pairs", ull), ("routed_experts", ull), ("active_base_bytes", ull),
+                ("active_per_expert_bytes", ull), ("activation_bytes", ull), ("temporary_bytes", ull),
+                ("status", C.c_int), ("pending", C.c_int)]
 
 
 class Completion(C.Structure):
@@ -75,33 +97,71 @@ CANCEL_FN = C.CFUNCTYPE(C.c_int, vp)
 
 
 class LayerJob(C.Structure):
-    _fields_ = [("layer", C.POINTER(LayerPlan)), ("weights", WeightView * W_COUNT), ("cancel_requested", CANCEL_FN),
-                ("cancel_context", vp), ("device_completion", C.POINTER(Completion))]
+    """yvex_moe_layer_job (include/yvex/internal/moe.h:194-209)."""
+    _fields_ = [("layer", C.POINTER(LayerPlan)), ("weights", WeightView * W_COUNT), ("expanded_input", vp),
+                ("device_input", C.POINTER(DeviceTensor)), ("device_output", C.POINTER(DeviceTensor)),
+                ("token_id", C.c_uint), ("token_id_present", C.c_int), ("cancel_requested", CANCEL_FN),
+                ("cancel_context", vp), ("evidence_level", C.c_int), ("eager_execution", C.c_int),
+                ("device_completion", C.POINTER(Completion)), ("execution_batch", vp), ("worklist_policy", vp)]
 
 
 class RowBatch(C.Structure):
-    _fields_ = [("row_count", ull), ("row_width", ull), ("row_stride", ull), ("expanded_rows", vp),
-                ("device_rows", C.POINTER(DeviceTensor)), ("device_outputs", C.POINTER(DeviceTensor)), ("router_logits", vp),
-                ("device_router_logits", C.POINTER(DeviceTensor)), ("token_ids", vp), ("token_ids_present", C.c_int)]
+    """yvex_moe_row_batch (include/yvex/internal/moe.h:232-247)."""
+    _fields_ = [("schema_version", C.c_uint), ("row_count", ull), ("row_width", ull), ("row_stride", ull),
+                ("expanded_rows", vp), ("device_rows", C.POINTER(DeviceTensor)), ("device_outputs", C.POINTER(DeviceTensor)),
+                ("token_ids", vp), ("token_ids_present", C.c_int), ("provenance", C.c_int), ("phase", C.c_uint),
+                ("execution_class", C.c_int), ("execution_profile_identity", C.c_char_p), ("execution_sources", vp),
+                ("execution_rows", vp), ("execution_source_count", ull), ("complete_after_operation", C.c_int)]
+
+
+class RowBatchLogits(C.Structure):
+    """The extension that carries caller-supplied router logits behind a reference-shaped batch."""
+    _fields_ = [("base", RowBatch), ("router_logits", vp), ("device_router_logits", C.POINTER(DeviceTensor))]
+
+
+def row_batch(rows, width, host_rows=None, device_rows=None, device_outputs=None, router_logits=None,
+              device_router_logits=None, token_ids=None, provenance=None):
+    """A row batch; with logits the extended struct (pass it to the table by reference like a plain batch)."""
+    base = RowBatch(ROW_BATCH_SCHEMA_V1, rows, width, width, host_rows, device_rows, device_outputs, token_ids,
+                    1 if token_ids else 0, (0 if rows == 1 else 2) if provenance is None else provenance, 0,
+                    EXECUTION_CLASS_DEVICE_NATIVE, None, None, None, 0, 0)
+    if router_logits is None and device_router_logits is None:
+        return base
+    base.schema_version = ROW_BATCH_SCHEMA_LOGITS
+    return RowBatchLogits(base, router_logits, device_router_logits)
 
 
 class RowBatchOutput(C.Structure):
-    _fields_ = [("combined_rows", vp), ("combined_capacity", ull), ("selected_experts", vp), ("selected_weights", vp),
-                ("selection_capacity", ull)]
+    """yvex_moe_row_batch_output (include/yvex/internal/moe.h:249-256)."""
+    _fields_ = [("combined_rows", vp), ("routed_rows", vp), ("shared_rows", vp), ("post_rows", vp), ("combination_rows", vp),
+                ("combined_capacity", ull), ("routed_capacity", ull), ("shared_capacity", ull), ("post_capacity", ull),
+                ("combination_capacity", ull), ("selected_experts", vp), ("selected_weights", vp), ("selection_capacity", ull)]
+
+
+def row_output(combined=None, combined_capacity=0, selected_experts=None, selected_weights=None, selection_capacity=0,
+               routed=None, shared=None, post=None, combination=None, routed_capacity=0, shared_capacity=0, post_capacity=0,
+               combination_capacity=0):
+    return RowBatchOutput(combined, routed, shared, post, combination, combined_capacity, routed_capacity, shared_capacity,
+                          post_capacity, combination_capacity, selected_experts, selected_weights, selection_capacity)
 
 
 class RowBatchResult(C.Structure):
-    _fields_ = [("completed", C.c_int), ("device_completion_pending", C.c_int)] + [
-        (n, ull) for n in ("row_count", "row_expert_pairs", "grouped_expert_operations", "shared_expert_operations",
-                           "expert_subviews_accessed", "encoded_bytes_read", "h2d_bytes", "d2h_bytes", "d2d_bytes",
-                           "kernel_launches", "tensor_core_launches", "stream_synchronizations", "active_weight_base_bytes",
-                           "active_weight_per_unique_expert_bytes", "activation_bytes", "temporary_bytes",
-                           "unique_experts", "upload_count", "download_count", "active_weight_bytes", "pipeline_chunks")] + [
-        ("worklists", WorklistObservation)]
+    """yvex_moe_row_batch_result (include/yvex/internal/moe.h:258-281)."""
+    _fields_ = [("schema_version", C.c_uint), ("completed", C.c_int), ("execution_profile_available", C.c_int),
+                ("device_completion_pending", C.c_int), ("execution_class", C.c_int)] + [
+        (n, ull) for n in ("row_count", "row_expert_pairs", "unique_experts")] + [("worklists", WorklistObservation)] + [
+        (n, ull) for n in ("grouped_expert_operations", "shared_expert_operations", "expert_subviews_accessed", "encoded_bytes_read",
+                           "h2d_bytes", "d2h_bytes", "d2d_bytes", "kernel_launches", "tensor_core_launches", "graph_launches",
+                           "graph_captures", "graph_replays", "upload_count", "download_count", "cache_hits", "cache_misses",
+                           "stream_synchronizations", "device_synchronizations", "active_weight_base_bytes",
+                           "active_weight_per_unique_expert_bytes")] + [("memory", MemoryFacts), ("total_ns", ull),
+                                                                        ("synchronization_ns", ull)] + [
+        (n, HEX) for n in ("execution_profile_identity", "execution_batch_identity", "worklist_policy_identity",
+                           "expert_worklist_identity", "routing_digest", "execution_identity")]
 
 
-_EXEC = C.CFUNCTYPE(C.c_int, vp, C.POINTER(LayerJob), C.POINTER(RowBatch), C.POINTER(RowBatchOutput), C.POINTER(RowBatchResult),
-                    C.POINTER(Error))
+_EXEC = C.CFUNCTYPE(C.c_int, vp, C.POINTER(LayerJob), vp, C.POINTER(RowBatchOutput), C.POINTER(RowBatchResult),
+                    C.POINTER(Error))          # the batch by address: a RowBatch or a RowBatchLogits
 _WSREQ = C.CFUNCTYPE(C.c_int, C.POINTER(LayerPlan), ull, C.POINTER(ull), C.POINTER(Error))
 
 
@@ -170,6 +230,9 @@ _lib.yvex_moe_input_token_ids.restype = C.POINTER(C.c_uint)
 _lib.yvex_moe_input_token_ids.argtypes = [vp]
 _lib.yvex_moe_input_close.argtypes = [C.POINTER(vp)]
 _lib.yvex_moe_input_row_batch.argtypes = [vp, ull, C.POINTER(RowBatch), C.POINTER(Error)]
+_lib.yvex_backend_moe_last_pipeline_chunks.restype = ull
+_lib.yvex_backend_moe_last_pipeline_chunks.argtypes = [vp]
+_lib.yvex_backend_abi_layout.restype = C.c_char_p
 _lib.yvex_backend_selftest_bounded_wait.argtypes = [vp, ull, C.POINTER(ull), C.POINTER(Error)]
 _lib.yvex_status_name.restype = C.c_char_p
 
@@ -264,10 +327,15 @@ def moe_job(arena, spec, router=True, router_class=1, hash_rows=0, family=None, 
     S = max(residual_streams, 1)
     policy = dict(sinkhorn_iterations=20, rms_epsilon=1e-6, mhc_epsilon=1e-6, post_multiplier=2.0)
     policy.update(envelope_policy or {})
-    plan = LayerPlan(router_class, spec.hidden, residual_streams, spec.hidden * S, (S + 2) * S if residual_streams > 1 else 0,
-                     policy["sinkhorn_iterations"] if residual_streams > 1 else 0, spec.experts, 1,
-                     spec.topk, spec.inter, spec.shared_inter, hash_rows, policy["rms_epsilon"], policy["mhc_epsilon"],
-                     policy["post_multiplier"], spec.scaling, spec.limit, spec.normalize)
+    plan = LayerPlan(schema_version=1, router_class=router_class, hidden_width=spec.hidden, residual_streams=residual_streams,
+                     expanded_width=spec.hidden * S, mhc_mixing_rows=(S + 2) * S if residual_streams > 1 else 0,
+                     mhc_sinkhorn_iterations=policy["sinkhorn_iterations"] if residual_streams > 1 else 0,
+                     routed_experts=spec.experts, shared_experts=1, experts_per_token=spec.topk,
+                     expert_intermediate_width=spec.inter, shared_intermediate_width=spec.shared_inter, hash_table_rows=hash_rows,
+                     hash_table_columns=spec.topk if hash_rows else 0, rms_epsilon=policy["rms_epsilon"],
+                     mhc_epsilon=policy["mhc_epsilon"], mhc_post_multiplier=policy["post_multiplier"],
+                     routed_scaling_factor=spec.scaling, activation_limit=spec.limit,
+                     requires_token_ids=1 if router_class == 0 else 0, normalize_topk_probabilities=spec.normalize)
     job = LayerJob()
     job.layer = C.pointer(plan)
 

@@ -233,7 +233,7 @@ __global__ void expert_up_rows_kernel(MoeGeom g, MoeWeights w, const float *xr, 
 }
 
 __global__ void expert_down_rows_kernel(MoeGeom g, MoeWeights w, const int32_t *selected, const float *mid,
-                                        uint64_t rows, float *out, int *status) {
+                                        uint64_t rows, float *out, float *routed_out, float *shared_out, int *status) {
     const int lane = threadIdx.x & 31;
     const uint64_t ppr = g.topk + 1, imax = max(g.inter, g.shared_inter);
     const uint64_t warps = (uint64_t)gridDim.x * (blockDim.x >> 5);
@@ -257,7 +257,11 @@ __global__ void expert_down_rows_kernel(MoeGeom g, MoeWeights w, const int32_t *
             acc = bf16_round(acc);
             if (is_shared) shared = acc; else routed += acc;
         }
-        if (lane == 0) out[job] = bf16_round(routed + shared);
+        if (lane == 0) {
+            out[job] = bf16_round(routed + shared);
+            if (routed_out) routed_out[job] = routed;
+            if (shared_out) shared_out[job] = shared;
+        }
     }
 }
 
@@ -354,6 +358,15 @@ extern "C" int yvex_b200_moe_decode(const yvex_b200_moe_geometry *geom, const yv
                                     const float *x, const float *logits, const uint32_t *token_ids,
                                     uint64_t rows, float *out, int32_t *selected_out, float *weights_out,
                                     void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
+    return yvex_b200_moe_decode_parts(geom, w, x, logits, token_ids, rows, out, nullptr, nullptr, selected_out, weights_out, workspace,
+                                      workspace_bytes, status, stream);
+}
+
+extern "C" int yvex_b200_moe_decode_parts(const yvex_b200_moe_geometry *geom, const yvex_b200_moe_weights *w,
+                                          const float *x, const float *logits, const uint32_t *token_ids,
+                                          uint64_t rows, float *out, float *routed_out, float *shared_out,
+                                          int32_t *selected_out, float *weights_out,
+                                          void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
     int rc = check_geometry(geom, w);
     if (rc != OK) return rc;
     if (!x || !out || !status || !rows || rows > 64) return rows > 64 ? ERR_UNSUPPORTED : ERR_INVALID_ARG;
@@ -361,6 +374,8 @@ extern "C" int yvex_b200_moe_decode(const yvex_b200_moe_geometry *geom, const yv
     MoeWorkspace ws;
     if (!workspace || workspace_bytes < moe_workspace_layout(g, rows, &ws)) return ERR_NOMEM;
     ws.rebase(workspace);
+    ws.routed_out = routed_out;
+    ws.shared_out = shared_out;
     cudaStream_t s = as_stream(stream);
     mark_phase(0, s);
     rc = moe_ingress_and_route(g, *w, ws, x, logits, token_ids, rows, status, s);
@@ -387,7 +402,7 @@ int yb::moe_down_rows(const MoeGeom &g, const yvex_b200_moe_weights &w, const Mo
                       uint64_t rows, float *out, int *status, cudaStream_t s) {
     const uint64_t jobs = rows * g.hidden;
     expert_down_rows_kernel<<<grid_for(jobs, 8, 16), 256, 0, s>>>(
-        g, w, ws.selected, ws.mid, rows, out, status);
+        g, w, ws.selected, ws.mid, rows, out, ws.routed_out, ws.shared_out, status);
     return launch_status(1);
 }
 

@@ -35,6 +35,9 @@ struct MoeWorkspace {
     float *mid;         // [rows x (topk+1) x max(inter, shared_inter)]  SwiGLU intermediates
     __half *xr_h;       // fp16 image of xr (bf16-exact values; B operand of the tensor-core matvecs)
     __half *mid_h;      // fp16 image of mid
+    // optional parts of the result, set by the entry point (not scratch): [rows x hidden] f32 each, the
+    // rank-ordered sum of the routed experts' rows and the shared expert's row (src/runtime/moe.c:606-637)
+    float *routed_out = nullptr, *shared_out = nullptr;
     void rebase(void *base) {
         auto b = reinterpret_cast<uintptr_t>(base);
         xr_h = reinterpret_cast<__half *>(b + reinterpret_cast<uintptr_t>(xr_h));

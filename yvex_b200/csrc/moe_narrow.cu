@@ -251,7 +251,10 @@ __global__ void __launch_bounds__(512, 2) moe_down_mma_kernel(NarrowParams p) {
             }
             const float ys = red[(par * (kMaxPairs + 3) + topk) * 8 + threadIdx.x];
             if (!isfinite(ys)) raise(p.status, YVEX_B200_STATUS_NUMERIC);
-            p.out[(uint64_t)r * g.hidden + (uint64_t)ct * 8 + threadIdx.x] = bf16_round(routed + bf16_round(ys));
+            const uint64_t at = (uint64_t)r * g.hidden + (uint64_t)ct * 8 + threadIdx.x;
+            p.out[at] = bf16_round(routed + bf16_round(ys));
+            if (p.ws.routed_out) p.ws.routed_out[at] = routed;
+            if (p.ws.shared_out) p.ws.shared_out[at] = bf16_round(ys);
         }
     }
     cp_async_wait<0>();

@@ -213,7 +213,8 @@ wide_mid_sums_kernel(const __half *mid_h, uint64_t rows, uint64_t inter, int gro
 // source row); blockIdx.y strides the tokens.
 __global__ void __launch_bounds__(128)
 wide_combine_kernel(const uint16_t *y, const uint16_t *y_shared, const int *pos, const int *pos_shared,
-                    uint64_t tokens, uint64_t topk, uint64_t hidden, float *out) {
+                    uint64_t tokens, uint64_t topk, uint64_t hidden, float *out, float *routed_out = nullptr,
+                    float *shared_out = nullptr) {
     const uint32_t chunks = (uint32_t)(hidden / 8), c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= chunks) return;
     for (uint64_t t = blockIdx.y; t < tokens; t += gridDim.y) {
@@ -245,6 +246,18 @@ wide_combine_kernel(const uint16_t *y, const uint16_t *y_shared, const int *pos,
         float4 *dst = reinterpret_cast<float4 *>(out + t * hidden) + 2 * c;
         dst[0] = o0;
         dst[1] = o1;
+        if (routed_out) {                       // the parts of the sum, unrounded routed total and the shared row
+            float4 *r = reinterpret_cast<float4 *>(routed_out + t * hidden) + 2 * c;
+            r[0] = make_float4(routed[0], routed[1], routed[2], routed[3]);
+            r[1] = make_float4(routed[4], routed[5], routed[6], routed[7]);
+        }
+        if (shared_out) {
+            float4 *sh = reinterpret_cast<float4 *>(shared_out + t * hidden) + 2 * c;
+            sh[0] = make_float4(__uint_as_float(sw[0] << 16), __uint_as_float(sw[0] & 0xffff0000u), __uint_as_float(sw[1] << 16),
+                                __uint_as_float(sw[1] & 0xffff0000u));
+            sh[1] = make_float4(__uint_as_float(sw[2] << 16), __uint_as_float(sw[2] & 0xffff0000u), __uint_as_float(sw[3] << 16),
+                                __uint_as_float(sw[3] & 0xffff0000u));
+        }
     }
 }
 
@@ -464,6 +477,15 @@ extern "C" int yvex_b200_moe_wide(const yvex_b200_moe_geometry *geom, const yvex
                                   const float *x, const float *logits, const uint32_t *token_ids,
                                   uint64_t rows, float *out, int32_t *selected_out, float *weights_out,
                                   void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
+    return yvex_b200_moe_wide_parts(geom, w, x, logits, token_ids, rows, out, nullptr, nullptr, selected_out, weights_out, workspace,
+                                    workspace_bytes, status, stream);
+}
+
+extern "C" int yvex_b200_moe_wide_parts(const yvex_b200_moe_geometry *geom, const yvex_b200_moe_weights *w,
+                                        const float *x, const float *logits, const uint32_t *token_ids,
+                                        uint64_t rows, float *out, float *routed_out, float *shared_out,
+                                        int32_t *selected_out, float *weights_out,
+                                        void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
     int rc = moe_check_geometry(geom, w);
     if (rc != OK) return rc;
     if (!x || !out || !status || !rows) return ERR_INVALID_ARG;
@@ -475,6 +497,8 @@ extern "C" int yvex_b200_moe_wide(const yvex_b200_moe_geometry *geom, const yvex
     const uint64_t need = gemm ? moe_wide_workspace_bytes(g, rows) : base;
     if (!workspace || workspace_bytes < need) return ERR_NOMEM;
     ws.rebase(workspace);
+    ws.routed_out = routed_out;
+    ws.shared_out = shared_out;
     cudaStream_t s = as_stream(stream);
     mark_phase(0, s);
     rc = moe_ingress_and_route(g, *w, ws, x, logits, token_ids, rows, status, s);
@@ -490,7 +514,7 @@ extern "C" int yvex_b200_moe_wide(const yvex_b200_moe_geometry *geom, const yvex
         rc = run_pair_list(g, *w, pw, ws.xr_h, pairs, status, s);
         if (rc != OK) return rc;
         wide_combine_kernel<<<dim3((unsigned)((g.hidden / 8 + 127) / 128), (unsigned)grid_for(rows, 1, 16)), 128, 0, s>>>(
-            pw.y, pw.y, pw.pos_of_pair, pw.pos_of_pair + routed, rows, g.topk, g.hidden, out);
+            pw.y, pw.y, pw.pos_of_pair, pw.pos_of_pair + routed, rows, g.topk, g.hidden, out, routed_out, shared_out);
         mark_phase(5, s);
         rc = launch_status(2);
     } else {

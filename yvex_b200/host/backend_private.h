@@ -24,6 +24,7 @@ struct yvex_backend {
     int *status_word;                 /* device: first fault of the enqueued kernels */
     unsigned char *host_scratch;      /* pinned */
     yvex_moe_device_completion_slot *pending_slot;   /* deferred completion in flight */
+    unsigned long long last_pipeline_chunks;         /* row ranges of the last wide call's copy pipeline */
     /* copy pipeline of the wide entry: host rows go in on copy_in and come back on copy_out while the
      * compute stream works on another chunk of rows */
     cudaStream_t copy_in, copy_out;

@@ -63,8 +63,10 @@ static unsigned long long envelope_streams(const yvex_moe_layer_plan *layer) {
 /* Rows in and out are `streams` times wider with the envelope, which also needs the normalized and
  * combined hidden rows, the gates and the device layer's own scratch. */
 static unsigned long long staging_bytes(const yvex_b200_moe_geometry *g, unsigned long long rows, unsigned long long streams) {
+    /* rows in and out, logits, selection, token ids, and the routed / shared parts of the sum */
     unsigned long long bytes = 2ull * align256(rows * g->hidden * streams * 4ull) + align256(rows * g->experts * 4ull) +
-                               2ull * align256(rows * g->topk * 4ull) + align256(rows * 4ull) + 256ull;
+                               2ull * align256(rows * g->topk * 4ull) + align256(rows * 4ull) + 2ull * align256(rows * g->hidden * 4ull) +
+                               256ull;
     if (streams > 1ull) {
         const unsigned long long mix_rows = (streams + 2ull) * streams;
         bytes += 2ull * align256(rows * g->hidden * 4ull) + align256(rows * streams * 4ull) + align256(rows * streams * streams * 4ull) +
@@ -115,6 +117,7 @@ static int derived_build(const void *decision, const unsigned char *canonical, u
 static int resolve_view(const yvex_backend *backend, const yvex_moe_weight_view *v, int required, const void **out) {
     unsigned long long address = 0;
     *out = NULL;
+    if (v->device_address) { *out = (const void *)(uintptr_t)v->device_address; return 1; }
     if (!v->encoded || !v->encoded_bytes) return required ? 0 : 1;
     if (yvex_backend_resident_resolve(backend, v->encoded, v->encoded_bytes, &address) != YVEX_BACKEND_RESIDENT_HIT) return 0;
     *out = (const void *)(uintptr_t)address;
@@ -143,6 +146,10 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     yvex_b200_mhc mhc;
     unsigned long long rows, cursor = 0, need, kernel_ws, launches0, in_bytes, hid_bytes, sel_count, streams, mhc_ws = 0;
     unsigned long long chunks = 1ull, tensor_path, list_ws;
+    const float *host_logits = NULL;
+    const yvex_device_tensor *tensor_logits = NULL;
+    unsigned char *ws_routed = NULL, *ws_shared = NULL;
+    int want_parts;
     yvex_expert_worklist_observation *dev_obs, *host_obs;
     unsigned char *ws_in, *ws_out, *ws_logits, *ws_sel, *ws_wts, *ws_ids, *ws_kernel;
     unsigned char *ws_norm = NULL, *ws_core = NULL, *ws_post = NULL, *ws_comb = NULL, *ws_mhc = NULL, *ws_coeff[4] = {NULL, NULL, NULL, NULL};
@@ -161,6 +168,14 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     if (backend->pending_slot) return yvex_refuse(err, YVEX_ERR_STATE, where, "a deferred MoE completion is still pending");
     /* host-side launch-failure seam (src/backend/cuda/qtype.c:625-661, src/backend/cuda/capability.c:611-629) */
     if (yvex_test_seam("YVEX_TEST_CUDA_LAUNCH_FAILURE", "moe-rows")) return yvex_backend_fail(backend, where, err);
+    if (batch->schema_version == YVEX_MOE_ROW_BATCH_SCHEMA_B200_LOGITS) {
+        host_logits = ((const yvex_moe_row_batch_logits *)batch)->router_logits;
+        tensor_logits = ((const yvex_moe_row_batch_logits *)batch)->device_router_logits;
+    } else if (batch->schema_version != YVEX_MOE_ROW_BATCH_SCHEMA_V1) {
+        return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "row batch schema is not one this backend reads");
+    }
+    if (job->evidence_level == 3 || (job->eager_execution != 0 && job->eager_execution != 1))       /* src/backend/cuda/moe.c:1028-1030 */
+        return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "full-evidence or malformed eager execution is not a device-native batch");
     rows = batch->row_count;
     if (!rows) return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "row batch is empty");
     if (!wide && rows > YVEX_MOE_NARROW_MAX_ROWS)
@@ -178,6 +193,8 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     for (slot = YVEX_MOE_WEIGHT_ROUTED_GATE; slot < YVEX_MOE_WEIGHT_COUNT; ++slot) {
         if (!family_admitted(job->weights[slot].kernel_family))
             return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "kernel family is not one this backend executes");
+        if (job->weights[slot].layout == YVEX_EXECUTION_LAYOUT_DERIVED_BACKEND)
+            return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "this backend offers no derived weight layout");
         if (!yvex_b200_qtype_supported(job->weights[slot].qtype))
             return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "expert qtype has no device decoder in this backend");
     }
@@ -206,7 +223,7 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     if (w.router && (job->weights[YVEX_MOE_WEIGHT_ROUTER].qtype != 0u ||
                      job->weights[YVEX_MOE_WEIGHT_ROUTER].encoded_bytes != g.experts * g.hidden * 4ull))
         return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "router weights must be F32 [experts x hidden]");
-    if (!w.router && !batch->router_logits && !batch->device_router_logits)
+    if (!w.router && !host_logits && !tensor_logits)
         return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "either resident router weights or router logits are required");
     if (g.router_class == 0 && (!batch->token_ids_present || !batch->token_ids))
         return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "MoE hash router requires token IDs");
@@ -220,7 +237,7 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
             if (!((v->qtype == 0u && v->encoded_bytes == coeff_count[i] * 4ull) || (v->qtype == 30u && v->encoded_bytes == coeff_count[i] * 2ull)))
                 return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "mHC envelope coefficients must be F32 or BF16 tensors of the layer's geometry");
         }
-        if (batch->router_logits || batch->device_router_logits)
+        if (host_logits || tensor_logits)
             return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "supplied router logits cannot be combined with the mHC envelope");
         memset(&mhc, 0, sizeof(mhc));
         mhc.hidden = g.hidden; mhc.streams = streams; mhc.sinkhorn_iterations = layer->mhc_sinkhorn_iterations;
@@ -238,6 +255,7 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     list_ws = yvex_b200_expert_worklist_workspace_bytes(rows * g.topk, g.experts);      /* reuses the kernel scratch afterwards */
     if (kernel_ws < list_ws) kernel_ws = list_ws;
     tensor_path = wide ? (unsigned long long)yvex_b200_moe_wide_uses_gemm(&g, &w) : 1ull;
+    want_parts = output && (output->routed_rows || output->shared_rows);
     need = staging_bytes(&g, rows, streams) + kernel_ws;
     if (!backend->workspace || backend->workspace->bytes < need)
         return yvex_refuse(err, YVEX_ERR_NOMEM, where, "attached device workspace is smaller than workspace_required");
@@ -248,6 +266,11 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     ws_wts = yvex_workspace_take(backend, &cursor, rows * g.topk * 4ull);
     ws_ids = yvex_workspace_take(backend, &cursor, rows * 4ull);
     ws_kernel = yvex_workspace_take(backend, &cursor, kernel_ws);
+    if (want_parts) {
+        ws_routed = yvex_workspace_take(backend, &cursor, hid_bytes);
+        ws_shared = yvex_workspace_take(backend, &cursor, hid_bytes);
+        if (!ws_routed || !ws_shared) return yvex_refuse(err, YVEX_ERR_NOMEM, where, "attached device workspace is smaller than workspace_required");
+    }
     if (streams > 1ull) {
         ws_norm = yvex_workspace_take(backend, &cursor, hid_bytes);
         ws_core = yvex_workspace_take(backend, &cursor, hid_bytes);
@@ -263,7 +286,8 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     defer = job->device_completion && job->device_completion->defer && job->device_completion->host;
     /* the copy pipeline: host rows in, host rows out, no envelope, nothing deferred */
     pipelined = wide && batch->expanded_rows && !batch->device_outputs && output && output->combined_rows && !defer && streams == 1ull &&
-                !batch->device_router_logits;
+                !tensor_logits && !want_parts;
+    backend->last_pipeline_chunks = 0ull;
     if (pipelined) chunks = wide_chunks(&g, rows);
     if (chunks < 2ull) pipelined = 0;
     if (output && output->combined_rows && output->combined_capacity < rows * g.hidden * streams)
@@ -271,6 +295,11 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     sel_count = rows * g.topk;
     if (output && (output->selected_experts || output->selected_weights) && output->selection_capacity < sel_count)
         return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "selection output capacity is too small");
+    if (output && ((output->routed_rows && output->routed_capacity < rows * g.hidden) ||
+                   (output->shared_rows && output->shared_capacity < rows * g.hidden) ||
+                   (output->post_rows && output->post_capacity < rows * streams) ||
+                   (output->combination_rows && output->combination_capacity < rows * streams * streams)))
+        return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "a partial output's capacity is too small");
     if (batch->device_rows) {
         if (!yvex_tensor_owned(backend, batch->device_rows) || !batch->device_rows->is_written ||
             batch->device_rows->dtype != YVEX_DTYPE_F32 || batch->device_rows->bytes < in_bytes)
@@ -283,12 +312,12 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
         result->upload_count++;
         dev_in = (const float *)ws_in;
     }
-    if (batch->device_router_logits) {
-        if (!yvex_tensor_owned(backend, batch->device_router_logits) || batch->device_router_logits->bytes < rows * g.experts * 4ull)
+    if (tensor_logits) {
+        if (!yvex_tensor_owned(backend, tensor_logits) || tensor_logits->bytes < rows * g.experts * 4ull)
             return yvex_refuse(err, YVEX_ERR_FORMAT, where, "device router logits must be an F32 tensor of this backend");
-        dev_logits = (const float *)batch->device_router_logits->data;
-    } else if (batch->router_logits) {
-        if (!pipelined && cudaMemcpyAsync(ws_logits, batch->router_logits, rows * g.experts * 4ull, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess)
+        dev_logits = (const float *)tensor_logits->data;
+    } else if (host_logits) {
+        if (!pipelined && cudaMemcpyAsync(ws_logits, host_logits, rows * g.experts * 4ull, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess)
             return yvex_backend_fail(backend, where, err);
         result->h2d_bytes += rows * g.experts * 4ull;
         result->upload_count++;
@@ -333,7 +362,7 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     }
     if (pipelined) {
         /* row range c: copied in on copy_in, computed on the backend's stream, copied out on copy_out */
-        const unsigned char *host_in = (const unsigned char *)batch->expanded_rows, *host_lg = (const unsigned char *)batch->router_logits;
+        const unsigned char *host_in = (const unsigned char *)batch->expanded_rows, *host_lg = (const unsigned char *)host_logits;
         const int ids = batch->token_ids_present && batch->token_ids;
         int ok = cudaEventRecord(backend->ev_begin, backend->stream) == cudaSuccess &&
                  cudaStreamWaitEvent(backend->copy_in, backend->ev_begin, 0) == cudaSuccess &&
@@ -371,11 +400,12 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
             return yvex_backend_fail(backend, where, err);
         result->d2h_bytes += in_bytes;
         result->download_count++;
-        result->pipeline_chunks = chunks;
+        backend->last_pipeline_chunks = chunks;
     } else {
-        rc = (wide ? yvex_b200_moe_wide : yvex_b200_moe_decode)(
+        rc = (wide ? yvex_b200_moe_wide_parts : yvex_b200_moe_decode_parts)(
             &g, &w, layer_in, dev_logits, batch->token_ids_present && batch->token_ids ? (const uint32_t *)ws_ids : NULL, rows, layer_out,
-            (int32_t *)ws_sel, (float *)ws_wts, ws_kernel, kernel_ws, backend->status_word, backend->stream);
+            (float *)ws_routed, (float *)ws_shared, (int32_t *)ws_sel, (float *)ws_wts, ws_kernel, kernel_ws, backend->status_word,
+            backend->stream);
         if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
         if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the MoE layer geometry");
     }
@@ -393,7 +423,8 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     host_obs = (yvex_expert_worklist_observation *)(backend->host_scratch + YVEX_DEVICE_OBSERVATION_OFFSET);
     rc = yvex_b200_expert_worklist((const int32_t *)ws_sel, rows, g.topk, g.experts, wide && tensor_path ? 1ull : 0ull,
                                    wide && tensor_path ? yvex_b200_moe_wide_tile_columns(g.gate_qtype) : 1ull,
-                                   rows == 1ull ? 0u : wide ? 3u : 2u, NULL, NULL, NULL, NULL, NULL, NULL, dev_obs, ws_kernel, kernel_ws,
+                                   (unsigned)batch->provenance <= 4u ? (unsigned)batch->provenance : rows == 1ull ? 0u : wide ? 3u : 2u, NULL,
+                                   NULL, NULL, NULL, NULL, NULL, dev_obs, ws_kernel, kernel_ws,
                                    backend->status_word, backend->stream);
     if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
     if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the expert worklist geometry");
@@ -402,6 +433,21 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
             return yvex_backend_fail(backend, where, err);
         result->d2h_bytes += in_bytes;
         result->download_count++;
+    }
+    /* the parts of the sum and of the envelope, when the caller has room for them (src/runtime/moe.c:1501-1508) */
+    {
+        const struct { float *host; const unsigned char *dev; unsigned long long bytes; } part[4] = {
+            {output ? output->routed_rows : NULL, ws_routed, hid_bytes},
+            {output ? output->shared_rows : NULL, ws_shared, hid_bytes},
+            {output && streams > 1ull ? output->post_rows : NULL, ws_post, rows * streams * 4ull},
+            {output && streams > 1ull ? output->combination_rows : NULL, ws_comb, rows * streams * streams * 4ull}};
+        for (int i = 0; i < 4; ++i) {
+            if (!part[i].host || !part[i].dev) continue;
+            if (cudaMemcpyAsync(part[i].host, part[i].dev, part[i].bytes, cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess)
+                return yvex_backend_fail(backend, where, err);
+            result->d2h_bytes += part[i].bytes;
+            result->download_count++;
+        }
     }
     if (!defer && output && output->selected_weights) {
         if (cudaMemcpyAsync(output->selected_weights, ws_wts, sel_count * 4ull, cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess)
@@ -443,14 +489,22 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     result->active_weight_per_unique_expert_bytes = (job->weights[YVEX_MOE_WEIGHT_ROUTED_GATE].encoded_bytes +
                                                      job->weights[YVEX_MOE_WEIGHT_ROUTED_UP].encoded_bytes +
                                                      job->weights[YVEX_MOE_WEIGHT_ROUTED_DOWN].encoded_bytes) / g.experts;
-    result->activation_bytes = 2ull * in_bytes;
-    result->temporary_bytes = need;
+    result->schema_version = YVEX_MOE_ROW_BATCH_RESULT_SCHEMA_V4;
+    result->execution_class = YVEX_EXECUTION_CLASS_DEVICE_NATIVE;
+    result->memory.activation_bytes = 2ull * in_bytes;
+    result->memory.temporary_bytes = need;
+    result->memory.measured_operations = 1ull;
     if (defer) {
         yvex_moe_device_completion_slot *s = job->device_completion->host;
         s->status = 0;                       /* the worklist summary behind these fields is already on its way */
         s->pending = 1;
         s->row_count = rows;
         s->row_expert_pairs = sel_count;
+        s->routed_experts = g.experts;
+        s->active_base_bytes = result->active_weight_base_bytes;
+        s->active_per_expert_bytes = result->active_weight_per_unique_expert_bytes;
+        s->activation_bytes = result->memory.activation_bytes;
+        s->temporary_bytes = result->memory.temporary_bytes;
         if (cudaMemcpyAsync(&s->status, backend->status_word, sizeof(int), cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess)
             return yvex_backend_fail(backend, where, err);
         backend->pending_slot = s;
@@ -474,8 +528,9 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     result->worklists.tensor_core_executed_pairs = result->worklists.tensor_core_eligible_pairs;
     result->unique_experts = host_obs->bucket_count;
     /* every active weight byte once: the replicated tensors plus the experts some row selected (:1905-1915) */
-    result->active_weight_bytes = result->active_weight_base_bytes + result->active_weight_per_unique_expert_bytes * result->unique_experts;
-    result->encoded_bytes_read = result->active_weight_bytes;
+    result->memory.active_weight_bytes = result->active_weight_base_bytes + result->active_weight_per_unique_expert_bytes * result->unique_experts;
+    result->memory.complete = 1;
+    result->encoded_bytes_read = result->memory.active_weight_bytes;
     if (output && output->selected_experts) {
         const int32_t *src = (const int32_t *)output->selected_experts + sel_count;
         for (unsigned long long i = 0; i < sel_count; ++i) output->selected_experts[i] = (unsigned long long)src[i];
@@ -518,8 +573,10 @@ static int moe_complete_rows(yvex_backend *backend, int barrier_observed, yvex_m
             result->worklists = s->worklist;
             result->worklists.tensor_core_executed_pairs = s->worklist.tensor_core_eligible_pairs;
             result->unique_experts = s->worklist.bucket_count;
-            result->active_weight_bytes = result->active_weight_base_bytes + result->active_weight_per_unique_expert_bytes * result->unique_experts;
-            result->encoded_bytes_read = result->active_weight_bytes;
+            s->tensor_core_executed_pairs = s->worklist.tensor_core_eligible_pairs;
+            result->memory.active_weight_bytes = result->active_weight_base_bytes + result->active_weight_per_unique_expert_bytes * result->unique_experts;
+            result->memory.complete = 1;
+            result->encoded_bytes_read = result->memory.active_weight_bytes;
         }
     }
     if (code) return status_error(code, err);
@@ -530,6 +587,10 @@ static int moe_complete_rows(yvex_backend *backend, int barrier_observed, yvex_m
 static const yvex_backend_moe_operations moe_operations = {
     derived_plan, derived_build, moe_workspace_required, moe_execute_rows, moe_complete_rows,
     moe_workspace_required_wide, moe_execute_rows_wide};
+
+unsigned long long yvex_backend_moe_last_pipeline_chunks(const yvex_backend *backend) {
+    return backend ? backend->last_pipeline_chunks : 0ull;
+}
 
 const yvex_backend_moe_operations *yvex_backend_moe_operations_get(const yvex_backend *backend) {
     if (!backend || backend->kind != YVEX_BACKEND_KIND_CUDA || backend->closing ||

@@ -301,6 +301,9 @@ int yvex_moe_input_row_batch(const yvex_moe_input *input, unsigned long long ord
     memset(batch, 0, sizeof(*batch));
     rc = yvex_moe_input_layer_view(input, ordinal, &values, &stride, err);
     if (rc != YVEX_OK) return rc;
+    batch->schema_version = YVEX_MOE_ROW_BATCH_SCHEMA_V1;
+    batch->execution_class = YVEX_EXECUTION_CLASS_DEVICE_NATIVE;
+    batch->provenance = input->summary.token_count > 1ull ? 3 : 0;      /* prefill rows, or a single row */
     batch->row_count = input->summary.token_count;
     batch->row_width = batch->row_stride = stride;
     batch->expanded_rows = values;
