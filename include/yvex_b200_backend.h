@@ -140,13 +140,26 @@ typedef struct yvex_backend_cuda_operation_facts {
     int compulsory_memory_facts_available;
 } yvex_backend_cuda_operation_facts;
 /* output[input_row][row] = dot(row, input[input_row]) (+ additive). resident_encoded is a HOST pointer
- * into the attached resident arena. input_tail / activation_q8 = 1 (the reference's split-input and
- * Q8_K-activation variants) are refused with YVEX_ERR_UNSUPPORTED. Synchronises like the reference. */
+ * into the attached resident arena. Synchronises like the reference. The reference's two variants:
+ *   activation_q8 = 1  for IQ2_XXS, Q2_K, Q8_0 and MXFP4 rows of a width that is a multiple of 256 the input
+ *                      rows go through the Q8_K quantiser first (src/backend/cuda/qtype.c:252-253; other
+ *                      qtypes, widths or a split input take the plain path, as there): the result is the
+ *                      product with the de-quantised activations, within 1e-5 (1 + |.|) of the CPU codec
+ *                      on those values like the reference's own (tests/unit/cuda/quant_qtype.c:389-396);
+ *   input_tail         the row is input[0 : input_head_width] ++ input_tail, rounded to bf16
+ *                      (yvex_qtype_split_matvec, src/backend/cuda/kernels.cu:736-781). */
 int yvex_backend_cuda_encoded_matvec(yvex_backend *backend, const unsigned char *resident_encoded,
     unsigned long long encoded_bytes, unsigned int qtype, unsigned long long row_count,
     unsigned long long row_width, unsigned long long row_bytes, unsigned long long input_rows,
     const yvex_device_tensor *input, const yvex_device_tensor *input_tail, unsigned long long input_head_width,
     const yvex_device_tensor *additive, yvex_device_tensor *output, int activation_q8,
+    yvex_backend_cuda_operation_facts *facts, yvex_error *err);
+
+/* Decodes selected rows of a resident matrix into a backend-owned F32 tensor [selected_rows x row_width]
+ * (src/backend/cuda/qtype.c:404-520): row_ids is a HOST array, an id >= row_count is YVEX_ERR_BOUNDS. */
+int yvex_backend_cuda_encoded_gather(yvex_backend *backend, const unsigned char *resident_encoded,
+    unsigned long long encoded_bytes, unsigned int qtype, unsigned long long row_count, unsigned long long row_width,
+    unsigned long long row_bytes, const unsigned int *row_ids, unsigned long long selected_rows, yvex_device_tensor *output,
     yvex_backend_cuda_operation_facts *facts, yvex_error *err);
 
 /* ---- attention: include/yvex/backend.h:246-257 (public op) ------------------------------------------------- */

@@ -58,6 +58,20 @@ int yvex_b200_phase_events(void **events, int count);
  */
 int yvex_b200_dequant_rows(unsigned int qtype, const void *encoded, uint64_t rows, uint64_t width,
                            uint64_t row_bytes, float *out, int *status, void *stream);
+/* The same for selected rows: out row i = decoded matrix row row_ids[i] (device array, ids < rows or
+ * status 2). Replaces yvex_qtype_gather behind yvex_backend_cuda_encoded_gather
+ * (src/backend/cuda/qtype.c:404-520). out is [selected_rows x width]. */
+int yvex_b200_dequant_gather(unsigned int qtype, const void *encoded, uint64_t rows, uint64_t width, uint64_t row_bytes,
+                             const uint32_t *row_ids, uint64_t selected_rows, float *out, int *status, void *stream);
+/* Activation rows as the reference's Q8_K activation path sees them: per 256 values the element of
+ * largest magnitude sets inverse = -127 / value, each value becomes rint(inverse * x) clamped to
+ * [-128, 127], divided by inverse again (quantiser src/backend/cuda/kernels.cu:436-489; the definition
+ * of its results tests/unit/cuda/quant_qtype.c:161-186). width % 256 == 0, 16-byte aligned rows. */
+int yvex_b200_q8k_round_trip(const float *x, uint64_t rows, uint64_t width, float *out, int *status, void *stream);
+/* out[r] = bf16(head[r] ++ tail[r]) with head_width and width - head_width values: the input row of the
+ * reference's split-input matvec (src/backend/cuda/kernels.cu:736-781). */
+int yvex_b200_concat_bf16(const float *head, const float *tail, uint64_t head_width, uint64_t width, uint64_t rows,
+                          float *out, int *status, void *stream);
 
 /*
  * Dequant-fused matvec: out[i][r] = dot(row r, input[i]) (+ additive[i][r]), optional bf16

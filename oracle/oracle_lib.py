@@ -259,3 +259,21 @@ def ref_moe_input_image(ref, token_start, widths, activations, token_ids):
         if rc != 0:
             raise RuntimeError(f"reference refused the fixture: {rc}")
         return open(path, "rb").read()
+
+
+def q8k_round_trip(x):
+    """The values the reference's Q8_K activation path multiplies by, as its own test restates them
+    (tests/unit/cuda/quant_qtype.c:161-186; device quantiser src/backend/cuda/kernels.cu:436-489): per 256
+    values the FIRST element of largest magnitude gives inverse = -127 / value, every value becomes
+    nearbyint(inverse * x) clamped to [-128, 127], divided by inverse. All arithmetic in float32."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    blocks = x.reshape(-1, 256)
+    at = np.argmax(np.abs(blocks), axis=1)                      # first maximum
+    peak = blocks[np.arange(blocks.shape[0]), at]
+    out = np.zeros_like(blocks)
+    live = np.abs(peak) > 0
+    with np.errstate(divide="ignore", invalid="ignore"):
+        inverse = np.where(live, np.float32(-127.0) / peak, np.float32(0)).astype(np.float32)
+        q = np.clip(np.rint(inverse[:, None] * blocks), -128, 127).astype(np.int32).astype(np.float32)     # an int: no -0
+        out[live] = (q[live] / inverse[live, None]).astype(np.float32)
+    return out.reshape(x.shape)

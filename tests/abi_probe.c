@@ -7,6 +7,8 @@
 #include <stddef.h>
 #include <stdio.h>
 #ifdef YVEX_ABI_REF
+#include <yvex/backend.h>
+#include <yvex/internal/backend.h>
 #include <yvex/internal/moe.h>
 #else
 #include "yvex_b200_backend.h"

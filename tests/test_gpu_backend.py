@@ -309,12 +309,9 @@ def test_encoded_matvec_resident_pointer_contract(B, port):
         _, want = port.matvec(synth.IQ2_XXS, w, rows, width, x[i], threads=4)
         assert rel_l2(y.reshape(2, rows)[i], want) <= 1e-5
     assert facts.kernel_launches == 1 and facts.active_weight_bytes == w.size and facts.stream_synchronizations == 1
-    # refusals: Q4_0 has no codec anywhere; Q8_K activations are not built; a pointer outside the arena
+    # refusals: Q4_0 has no codec anywhere; a pointer outside the arena
     bad = list(args)
     bad[2] = 2
-    assert B._lib.yvex_backend_cuda_encoded_matvec(be.h, *bad) == B.UNSUPPORTED
-    bad = list(args)
-    bad[12] = 1
     assert B._lib.yvex_backend_cuda_encoded_matvec(be.h, *bad) == B.UNSUPPORTED
     bad = list(args)
     bad[12] = 2
@@ -326,6 +323,88 @@ def test_encoded_matvec_resident_pointer_contract(B, port):
     bad = list(args)
     bad[7] = unwritten
     assert B._lib.yvex_backend_cuda_encoded_matvec(be.h, *bad) == B.FORMAT
+    assert be.close() == B.OK
+
+
+@pytest.mark.parametrize("qtype", [synth.IQ2_XXS, synth.Q2_K, synth.Q8_0, synth.MXFP4, synth.Q4_K])
+def test_encoded_matvec_with_q8k_activations(B, port, qtype):
+    """activation_q8 = 1: the rows of the four qtypes the reference admits are multiplied by the Q8_K round trip
+    of the input (5 x 4096 weights, 3 input rows, as tests/unit/cuda/quant_qtype.c:273-396 runs it), within its
+    bound against the CPU codec on those values and its looser bound against the exact product; Q4_K is not
+    one of the four and takes the plain path."""
+    from oracle.oracle_lib import q8k_round_trip
+    rows, width, inputs = 5, 4096, 3
+    w = synth.random_blocks(qtype, rows, width, 21)
+    idx = np.arange(width)
+    x = np.stack([((idx + 5 * i) % 29 - 14).astype(np.float32) / np.float32(13 + i) for i in range(inputs)])
+    be = B.Backend()
+    arena = B.ResidentArena(be, {"w": w})
+    tin = be.from_array(x, B.F32)
+    rc, tout, _ = be.tensor(inputs * rows * 4, B.F32, [inputs, rows])
+    facts = B.Facts()
+    args = (arena.host_ptr("w"), w.size, qtype, rows, width, w.shape[1], inputs, tin, None, 0, None, tout, 1, C.byref(facts),
+            C.byref(be.err))
+    assert B._lib.yvex_backend_cuda_encoded_matvec(be.h, *args) == B.OK, be.message()
+    rc, y = be.read(tout, np.float32, inputs * rows)
+    y = y.reshape(inputs, rows)
+    eligible = qtype != synth.Q4_K
+    xq = q8k_round_trip(x) if eligible else x
+    assert eligible == (not np.array_equal(xq, x))
+    for i in range(inputs):
+        _, want = port.matvec(qtype, w, rows, width, xq[i], threads=2, allow_q4k=True)
+        _, exact = port.matvec(qtype, w, rows, width, x[i], threads=2, allow_q4k=True)
+        assert (np.abs(y[i] - want) <= 1e-5 * (1 + np.abs(want))).all(), np.abs(y[i] - want).max()
+        assert (np.abs(y[i] - exact) <= 0.1 * (1 + np.abs(exact))).all()
+    assert facts.kernel_launches == (2 if eligible else 1)
+    assert facts.temporary_bytes == 4 + (inputs * width * 4 if eligible else 0)
+    assert be.close() == B.OK
+
+
+def test_encoded_matvec_with_split_input(B, port):
+    """input_tail: the row is head ++ tail rounded to bf16 (173 + 3923 values, tests/unit/cuda/quant_qtype.c:275,306-311)."""
+    rows, width, head = 5, 4096, 173
+    w = synth.random_blocks(synth.IQ2_XXS, rows, width, 22)
+    x = np.random.default_rng(23).standard_normal((2, width)).astype(np.float32)
+    be = B.Backend()
+    arena = B.ResidentArena(be, {"w": w})
+    thead, ttail = be.from_array(np.ascontiguousarray(x[:, :head]), B.F32), be.from_array(np.ascontiguousarray(x[:, head:]), B.F32)
+    rc, tout, _ = be.tensor(2 * rows * 4, B.F32, [2, rows])
+    facts = B.Facts()
+    args = [arena.host_ptr("w"), w.size, synth.IQ2_XXS, rows, width, w.shape[1], 2, thead, ttail, head, None, tout, 0, C.byref(facts),
+            C.byref(be.err)]
+    assert B._lib.yvex_backend_cuda_encoded_matvec(be.h, *args) == B.OK, be.message()
+    rc, y = be.read(tout, np.float32, 2 * rows)
+    for i in range(2):
+        _, want = port.matvec(synth.IQ2_XXS, w, rows, width, synth.bf16_round(x[i]), threads=2)
+        assert (np.abs(y.reshape(2, rows)[i] - want) <= 1e-5 * (1 + np.abs(want))).all()
+    # a head width without a tail (or the reverse), or a head as wide as the row, is refused
+    for tail, hw in ((None, head), (ttail, 0), (ttail, width)):
+        bad = list(args)
+        bad[8], bad[9] = tail, hw
+        assert B._lib.yvex_backend_cuda_encoded_matvec(be.h, *bad) == B.FORMAT
+    assert be.close() == B.OK
+
+
+@pytest.mark.parametrize("qtype", [synth.IQ2_XXS, synth.Q8_0, synth.Q2_K])
+def test_encoded_gather_decodes_selected_rows_bit_exactly(B, port, qtype):
+    rows, width = 40, 512
+    w = synth.random_blocks(qtype, rows, width, 31)
+    ids = np.array([7, 0, 39, 7, 12], np.uint32)
+    be = B.Backend()
+    arena = B.ResidentArena(be, {"w": w})
+    rc, tout, _ = be.tensor(ids.size * width * 4, B.F32, [ids.size, width])
+    facts = B.Facts()
+    args = [arena.host_ptr("w"), w.size, qtype, rows, width, w.shape[1], ids.ctypes.data_as(B.vp), ids.size, tout, C.byref(facts),
+            C.byref(be.err)]
+    assert B._lib.yvex_backend_cuda_encoded_gather(be.h, *args) == B.OK, be.message()
+    rc, got = be.read(tout, np.float32, ids.size * width)
+    _, full = port.decode_rows(qtype, w, rows, width)
+    assert (got.reshape(ids.size, width).view(np.uint32) == full.reshape(rows, width)[ids].view(np.uint32)).all()
+    assert facts.kernel_launches == 1 and facts.active_weight_bytes == ids.size * w.shape[1] and facts.h2d_bytes == ids.nbytes
+    far = np.array([3, rows], np.uint32)
+    bad = list(args)
+    bad[6], bad[7] = far.ctypes.data_as(B.vp), far.size
+    assert B._lib.yvex_backend_cuda_encoded_gather(be.h, *bad) == B.BOUNDS
     assert be.close() == B.OK
 
 

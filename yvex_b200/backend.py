@@ -197,6 +197,8 @@ _lib.yvex_backend_qtype_supported.argtypes = [vp, C.c_uint]
 _lib.yvex_backend_cuda_encoded_matvec.argtypes = [vp, vp, ull, C.c_uint, ull, ull, ull, ull, C.POINTER(DeviceTensor),
                                                   C.POINTER(DeviceTensor), ull, C.POINTER(DeviceTensor), C.POINTER(DeviceTensor),
                                                   C.c_int, C.POINTER(Facts), C.POINTER(Error)]
+_lib.yvex_backend_cuda_encoded_gather.argtypes = [vp, vp, ull, C.c_uint, ull, ull, ull, vp, ull, C.POINTER(DeviceTensor),
+                                                  C.POINTER(Facts), C.POINTER(Error)]
 _lib.yvex_backend_op_attention.argtypes = [vp] + [C.POINTER(DeviceTensor)] * 3 + [ull, ull, C.c_float, C.c_int] + \
     [C.POINTER(DeviceTensor)] * 3 + [C.POINTER(Error)]
 _lib.yvex_backend_attention_gqa_decode.argtypes = [vp] + [C.POINTER(DeviceTensor)] * 3 + [ull] * 6 + [C.c_float,

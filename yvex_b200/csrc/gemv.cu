@@ -17,17 +17,76 @@
 namespace yb {
 
 // ---- elementwise decode (reference: yvex_encoded_row_decode, src/backend/cuda/kernels.cu:784) ----
+// row_ids (optional): output row r decodes matrix row row_ids[r] (yvex_qtype_gather, the decode of selected
+// rows behind yvex_backend_cuda_encoded_gather, src/backend/cuda/qtype.c:404-520); `matrix_rows` bounds the ids.
 __global__ void dequant_rows_kernel(unsigned q, const uint8_t *enc, uint64_t rows, uint64_t width,
-                                    uint64_t row_bytes, float *out, int *status) {
+                                    uint64_t row_bytes, const uint32_t *row_ids, uint64_t matrix_rows, float *out, int *status) {
     const Geometry g = geometry_of(q);
     const uint64_t total = rows * width;
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total;
          i += (uint64_t)gridDim.x * blockDim.x) {
         uint64_t r = i / width, c = i % width;
+        if (row_ids) {
+            r = row_ids[r];
+            if (r >= matrix_rows) { raise(status, YVEX_B200_STATUS_ARGUMENT); continue; }
+        }
         const uint8_t *blk = enc + r * row_bytes + (c / g.elems) * g.bytes;
         float v = decode_element(q, blk, static_cast<unsigned>(c % g.elems), status);
         if (!isfinite(v)) raise(status, YVEX_B200_STATUS_NUMERIC);
         out[i] = v;
+    }
+}
+
+// ---- activation preparation ---------------------------------------------------------------------
+// Q8_K round trip of an activation row, one warp per 256-value block: the element of largest magnitude
+// (the first of equals) sets inverse = -127 / value, every element becomes rint(inverse * x) clamped to
+// [-128, 127] and is published as that integer / inverse. These are the values the reference's Q8_K
+// activation path multiplies the weights by (quantiser src/backend/cuda/kernels.cu:436-489; the
+// definition its own test restates, tests/unit/cuda/quant_qtype.c:161-186).
+__global__ void __launch_bounds__(256) q8k_round_trip_kernel(const float *x, uint64_t blocks, float *out, int *status) {
+    const int lane = threadIdx.x & 31;
+    for (uint64_t b = blockIdx.x * (uint64_t)(blockDim.x >> 5) + (threadIdx.x >> 5); b < blocks; b += (uint64_t)gridDim.x * (blockDim.x >> 5)) {
+        const float4 lo = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + 2 * lane), hi = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + 2 * lane + 1);
+        const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        float best = 0.0f, best_signed = 0.0f;
+        int best_at = 0;
+        bool bad = false;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            bad |= !isfinite(v[i]);
+            if (fabsf(v[i]) > best) { best = fabsf(v[i]); best_signed = v[i]; best_at = 8 * lane + i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o), os = __shfl_xor_sync(0xffffffffu, best_signed, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, best_at, o);
+            if (ob > best || (ob == best && oa < best_at)) { best = ob; best_signed = os; best_at = oa; }
+        }
+        if (bad) raise(status, YVEX_B200_STATUS_NUMERIC);
+        const float inverse = best == 0.0f ? 0.0f : -127.0f / best_signed;
+        float r[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            int q = inverse == 0.0f ? 0 : __float2int_rn(inverse * v[i]);
+            q = q > 127 ? 127 : q < -128 ? -128 : q;
+            r[i] = inverse == 0.0f ? 0.0f : (float)q / inverse;
+        }
+        float4 *dst = reinterpret_cast<float4 *>(out + b * 256) + 2 * lane;
+        dst[0] = make_float4(r[0], r[1], r[2], r[3]);
+        dst[1] = make_float4(r[4], r[5], r[6], r[7]);
+    }
+}
+
+// A row given in two parts (head_width values, then the rest) as one bf16-rounded row: what the
+// reference's split-input matvec multiplies by (yvex_qtype_split_matvec, src/backend/cuda/kernels.cu:736-781).
+__global__ void concat_bf16_kernel(const float *head, const float *tail, uint64_t head_width, uint64_t width, uint64_t rows,
+                                   float *out, int *status) {
+    const uint64_t total = rows * width, tail_width = width - head_width;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t r = i / width, c = i % width;
+        const float v = c < head_width ? head[r * head_width + c] : tail[r * tail_width + (c - head_width)];
+        if (!isfinite(v)) raise(status, YVEX_B200_STATUS_NUMERIC);
+        out[i] = bf16_round(v);
     }
 }
 
@@ -301,7 +360,33 @@ extern "C" int yvex_b200_dequant_rows(unsigned int qtype, const void *encoded, u
     int grid = (int)((total + 255) / 256 < (uint64_t)kSmCount * 16 ? (total + 255) / 256
                                                                      : (uint64_t)kSmCount * 16);
     dequant_rows_kernel<<<grid, 256, 0, as_stream(stream)>>>(
-        qtype, static_cast<const uint8_t *>(encoded), rows, width, row_bytes, out, status);
+        qtype, static_cast<const uint8_t *>(encoded), rows, width, row_bytes, nullptr, rows, out, status);
+    return launch_status();
+}
+
+extern "C" int yvex_b200_dequant_gather(unsigned int qtype, const void *encoded, uint64_t rows, uint64_t width, uint64_t row_bytes,
+                                        const uint32_t *row_ids, uint64_t selected_rows, float *out, int *status, void *stream) {
+    if (!encoded || !out || !status || !row_ids || !selected_rows) return ERR_INVALID_ARG;
+    int rc = check_rows(qtype, rows, width, row_bytes);
+    if (rc != OK) return rc;
+    dequant_rows_kernel<<<grid_for(selected_rows * width, 256, 16), 256, 0, as_stream(stream)>>>(
+        qtype, static_cast<const uint8_t *>(encoded), selected_rows, width, row_bytes, row_ids, rows, out, status);
+    return launch_status();
+}
+
+extern "C" int yvex_b200_q8k_round_trip(const float *x, uint64_t rows, uint64_t width, float *out, int *status, void *stream) {
+    if (!x || !out || !status || !rows || !width) return ERR_INVALID_ARG;
+    if (width % 256 || ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15u)) return ERR_BOUNDS;
+    const uint64_t blocks = rows * (width / 256);
+    q8k_round_trip_kernel<<<grid_for(blocks, 8, 16), 256, 0, as_stream(stream)>>>(x, blocks, out, status);
+    return launch_status();
+}
+
+extern "C" int yvex_b200_concat_bf16(const float *head, const float *tail, uint64_t head_width, uint64_t width, uint64_t rows,
+                                     float *out, int *status, void *stream) {
+    if (!head || !tail || !out || !status || !rows) return ERR_INVALID_ARG;
+    if (!head_width || head_width >= width) return ERR_BOUNDS;
+    concat_bf16_kernel<<<grid_for(rows * width, 256, 16), 256, 0, as_stream(stream)>>>(head, tail, head_width, width, rows, out, status);
     return launch_status();
 }
 

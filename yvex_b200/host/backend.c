@@ -128,6 +128,7 @@ int yvex_backend_close_checked(yvex_backend **backend, yvex_error *err) {
         return yvex_refuse(err, YVEX_ERR_STATE, "yvex_backend_close_checked", "backend still owns tensors");
     }
     if (b->status_word) ok &= cudaFree(b->status_word) == cudaSuccess;
+    if (b->act_scratch) ok &= cudaFree(b->act_scratch) == cudaSuccess;
     if (b->host_scratch) ok &= cudaFreeHost(b->host_scratch) == cudaSuccess;
     ok &= backend_events(b, 0);
     if (b->copy_in) ok &= cudaStreamDestroy(b->copy_in) == cudaSuccess;
@@ -149,6 +150,7 @@ void yvex_backend_close(yvex_backend *backend) {
     if (backend->copy_out) { cudaStreamSynchronize(backend->copy_out); cudaStreamDestroy(backend->copy_out); }
     if (backend->stream) cudaStreamDestroy(backend->stream);
     if (backend->status_word) cudaFree(backend->status_word);
+    if (backend->act_scratch) cudaFree(backend->act_scratch);
     if (backend->host_scratch) cudaFreeHost(backend->host_scratch);
     cudaGetLastError();
     free(backend);
@@ -429,6 +431,24 @@ int yvex_backend_selftest_bounded_wait(yvex_backend *backend, unsigned long long
 
 /* ---- encoded matvec -------------------------------------------------------------------------------- */
 
+/* Backend-owned device scratch of at least `bytes` (prepared activation rows, row ids); grown on demand. */
+static unsigned char *act_scratch(yvex_backend *backend, unsigned long long bytes) {
+    if (backend->act_scratch_bytes < bytes) {
+        void *fresh = NULL;
+        if (cudaStreamSynchronize(backend->stream) != cudaSuccess) return NULL;
+        if (backend->act_scratch && cudaFree(backend->act_scratch) != cudaSuccess) return NULL;
+        backend->act_scratch = NULL;
+        backend->act_scratch_bytes = 0ull;
+        if (cudaMalloc(&fresh, (size_t)bytes) != cudaSuccess) { cudaGetLastError(); return NULL; }
+        backend->act_scratch = (unsigned char *)fresh;
+        backend->act_scratch_bytes = bytes;
+    }
+    return backend->act_scratch;
+}
+
+/* The qtypes whose rows the reference multiplies by Q8_K activations (src/backend/cuda/kernel_primitives.h:556-564). */
+static int q8_activation_eligible(unsigned int qtype) { return qtype == 16u || qtype == 10u || qtype == 8u || qtype == 39u; }
+
 int yvex_backend_cuda_encoded_matvec(yvex_backend *backend, const unsigned char *resident_encoded,
     unsigned long long encoded_bytes, unsigned int qtype, unsigned long long row_count,
     unsigned long long row_width, unsigned long long row_bytes, unsigned long long input_rows,
@@ -436,8 +456,10 @@ int yvex_backend_cuda_encoded_matvec(yvex_backend *backend, const unsigned char 
     const yvex_device_tensor *additive, yvex_device_tensor *output, int activation_q8,
     yvex_backend_cuda_operation_facts *facts, yvex_error *err) {
     const char *where = "cuda.encoded-matvec";
-    unsigned long long device_address = 0ull, launches0;
-    int rc, code;
+    unsigned long long device_address = 0ull, launches0, temporary = sizeof(int);
+    const int split = input_tail != NULL;
+    const float *rows_in;
+    int rc, code, q8_path;
     if (facts) memset(facts, 0, sizeof(*facts));
     if (activation_q8 != 0 && activation_q8 != 1)
         return yvex_refuse(err, YVEX_ERR_INVALID_ARG, "cuda.encoded-matvec.activation",
@@ -446,12 +468,15 @@ int yvex_backend_cuda_encoded_matvec(yvex_backend *backend, const unsigned char 
     if (rc != YVEX_OK) return rc;
     if (!yvex_b200_qtype_supported(qtype))
         return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "qtype has no device decoder in this backend");
-    if (activation_q8 || input_tail || input_head_width)
-        return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "Q8_K activations and split inputs are not built in this backend");
+    q8_path = activation_q8 && !split && row_width % 256ull == 0ull && q8_activation_eligible(qtype);
     if (!resident_encoded || !encoded_bytes || !row_count || !input_rows || !row_width || !row_bytes || !facts ||
+        split != (input_head_width != 0ull) || (split && input_head_width >= row_width) ||
         row_count > UINT64_MAX / row_bytes || row_count * row_bytes != encoded_bytes ||
         !yvex_tensor_owned(backend, input) || !input->is_written || input->dtype != YVEX_DTYPE_F32 ||
-        input->bytes < input_rows * row_width * 4ull || !yvex_tensor_owned(backend, output) || output->dtype != YVEX_DTYPE_F32 ||
+        input->bytes < input_rows * (split ? input_head_width : row_width) * 4ull ||
+        (split && (!yvex_tensor_owned(backend, input_tail) || !input_tail->is_written || input_tail->dtype != YVEX_DTYPE_F32 ||
+                   input_tail->bytes < input_rows * (row_width - input_head_width) * 4ull || input_tail == output)) ||
+        !yvex_tensor_owned(backend, output) || output->dtype != YVEX_DTYPE_F32 ||
         output->bytes < input_rows * row_count * 4ull ||
         (additive && (!yvex_tensor_owned(backend, additive) || additive->dtype != YVEX_DTYPE_F32 || !additive->is_written ||
                       additive->bytes < input_rows * row_count * 4ull || additive == output)) ||
@@ -465,7 +490,20 @@ int yvex_backend_cuda_encoded_matvec(yvex_backend *backend, const unsigned char 
         return yvex_refuse(err, YVEX_ERR_BACKEND, "cuda.encoded-matvec.copy_input", "injected CUDA qtype input copy failure");
     if (yvex_test_seam("YVEX_TEST_CUDA_LAUNCH_FAILURE", "encoded-matvec")) return yvex_backend_fail(backend, "cuda.encoded-matvec.launch", err);
     launches0 = yvex_b200_launch_count();
-    rc = yvex_b200_gemv(qtype, (const void *)(uintptr_t)device_address, row_count, row_width, row_bytes, (const float *)input->data,
+    rows_in = (const float *)input->data;
+    if (q8_path || split) {
+        /* the variant's view of the input rows, written once to backend-owned scratch */
+        float *prepared = (float *)act_scratch(backend, input_rows * row_width * 4ull);
+        if (!prepared) return yvex_refuse(err, YVEX_ERR_NOMEM, where, "no device memory for the prepared activation rows");
+        rc = q8_path ? yvex_b200_q8k_round_trip(rows_in, input_rows, row_width, prepared, backend->status_word, backend->stream)
+                     : yvex_b200_concat_bf16(rows_in, (const float *)input_tail->data, input_head_width, row_width, input_rows, prepared,
+                                             backend->status_word, backend->stream);
+        if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
+        if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the activation rows");
+        rows_in = prepared;
+        temporary += input_rows * row_width * 4ull;
+    }
+    rc = yvex_b200_gemv(qtype, (const void *)(uintptr_t)device_address, row_count, row_width, row_bytes, rows_in,
                         input_rows, additive ? (const float *)additive->data : NULL, (float *)output->data, 0, backend->status_word,
                         backend->stream);
     if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
@@ -482,7 +520,57 @@ int yvex_backend_cuda_encoded_matvec(yvex_backend *backend, const unsigned char 
     facts->download_count = 1;
     facts->active_weight_bytes = encoded_bytes;
     facts->activation_bytes = input_rows * row_width * 4ull + input_rows * row_count * 4ull * (additive ? 2ull : 1ull);
-    facts->temporary_bytes = sizeof(int);
+    facts->temporary_bytes = temporary;
+    facts->compulsory_memory_facts_available = 1;
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+int yvex_backend_cuda_encoded_gather(yvex_backend *backend, const unsigned char *resident_encoded,
+    unsigned long long encoded_bytes, unsigned int qtype, unsigned long long row_count, unsigned long long row_width,
+    unsigned long long row_bytes, const unsigned int *row_ids, unsigned long long selected_rows, yvex_device_tensor *output,
+    yvex_backend_cuda_operation_facts *facts, yvex_error *err) {
+    const char *where = "cuda.encoded-gather";
+    unsigned long long device_address = 0ull, i;
+    unsigned int be = 0, bb = 0;
+    unsigned char *ids;
+    int rc, code;
+    if (facts) memset(facts, 0, sizeof(*facts));
+    rc = yvex_backend_admit(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    if (!yvex_b200_qtype_supported(qtype) || !yvex_b200_qtype_geometry(qtype, &be, &bb) || !be)
+        return yvex_refuse(err, YVEX_ERR_FORMAT, where, "resident encoded gather geometry or ownership is incompatible");
+    if (!resident_encoded || !encoded_bytes || !row_count || !row_width || !row_bytes || !row_ids || !selected_rows || !facts ||
+        row_width % be || row_width / be * bb != row_bytes || row_count > UINT64_MAX / row_bytes || row_count * row_bytes != encoded_bytes ||
+        selected_rows > UINT64_MAX / (row_width * 4ull) || !yvex_tensor_owned(backend, output) || output->dtype != YVEX_DTYPE_F32 ||
+        output->bytes < selected_rows * row_width * 4ull ||
+        yvex_backend_resident_resolve(backend, resident_encoded, encoded_bytes, &device_address) != YVEX_BACKEND_RESIDENT_HIT)
+        return yvex_refuse(err, YVEX_ERR_FORMAT, where, "resident encoded gather geometry or ownership is incompatible");
+    output->is_written = 0;
+    for (i = 0; i < selected_rows; ++i)
+        if ((unsigned long long)row_ids[i] >= row_count)
+            return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "encoded gather row identifier exceeds the resident matrix");
+    ids = act_scratch(backend, selected_rows * 4ull);
+    if (!ids) return yvex_refuse(err, YVEX_ERR_NOMEM, where, "no device memory for the row identifiers");
+    /* the ids are copied from pageable memory: the call returns only after the stream is idle, so the source stays valid */
+    if (cudaMemcpyAsync(ids, row_ids, (size_t)(selected_rows * 4ull), cudaMemcpyHostToDevice, backend->stream) != cudaSuccess)
+        return yvex_backend_fail(backend, where, err);
+    rc = yvex_b200_dequant_gather(qtype, (const void *)(uintptr_t)device_address, row_count, row_width, row_bytes, (const uint32_t *)ids,
+                                  selected_rows, (float *)output->data, backend->status_word, backend->stream);
+    if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
+    if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the gather geometry");
+    if (!yvex_backend_take_status(backend, &code)) return yvex_backend_fail(backend, "cuda.encoded-gather.sync", err);
+    if (code) return yvex_refuse(err, YVEX_ERR_FORMAT, where, "encoded CUDA gather produced invalid numerics");
+    output->is_written = 1;
+    facts->h2d_bytes = selected_rows * 4ull;
+    facts->d2h_bytes = sizeof(int);
+    facts->kernel_launches = 1ull;
+    facts->upload_count = 1ull;
+    facts->download_count = 1ull;
+    facts->stream_synchronizations = 1ull;
+    facts->active_weight_bytes = selected_rows * row_bytes;
+    facts->activation_bytes = selected_rows * row_width * 4ull;
+    facts->temporary_bytes = selected_rows * 4ull + sizeof(int);
     facts->compulsory_memory_facts_available = 1;
     yvex_error_clear(err);
     return YVEX_OK;

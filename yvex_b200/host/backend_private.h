@@ -25,6 +25,8 @@ struct yvex_backend {
     unsigned char *host_scratch;      /* pinned */
     yvex_moe_device_completion_slot *pending_slot;   /* deferred completion in flight */
     unsigned long long last_pipeline_chunks;         /* row ranges of the last wide call's copy pipeline */
+    unsigned char *act_scratch;                      /* prepared activation rows / row ids of the encoded matvec family */
+    unsigned long long act_scratch_bytes;            /* (grown on demand, freed at close) */
     /* copy pipeline of the wide entry: host rows go in on copy_in and come back on copy_out while the
      * compute stream works on another chunk of rows */
     cudaStream_t copy_in, copy_out;

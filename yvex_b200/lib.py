@@ -114,7 +114,8 @@ EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_ge
            "yvex_b200_mhc_post", "yvex_b200_expert_worklist_workspace_bytes", "yvex_b200_expert_worklist",
            "yvex_b200_selftest_bounded_wait", "yvex_b200_moe_wide_uses_gemm", "yvex_b200_moe_wide_tile_columns",
            "yvex_b200_ep_payload_pitch", "yvex_b200_ep_dispatch_payload", "yvex_b200_moe_expert_rows_payload",
-           "yvex_b200_moe_wide_set_cta_limit", "yvex_b200_moe_decode_parts", "yvex_b200_moe_wide_parts"]
+           "yvex_b200_moe_wide_set_cta_limit", "yvex_b200_moe_decode_parts", "yvex_b200_moe_wide_parts",
+           "yvex_b200_dequant_gather", "yvex_b200_q8k_round_trip", "yvex_b200_concat_bf16"]
 
 
 def _torch():
