@@ -298,6 +298,11 @@ struct StreamParams {
     const uint8_t *enc;
     uint64_t matrix_stride;             // bytes from one matrix to the next
     uint32_t count;                     // matrices
+    // optional device tables for matrices that are not evenly spaced (the experts a router picked):
+    // matrix m starts at matrix_ptrs[m] (16-byte aligned, or the launch reports status 2) and reads
+    // input row x_rows[m]; consecutive matrices with the same input row share one activation preparation
+    const uint8_t *const *matrix_ptrs;
+    const uint32_t *x_rows;
     uint64_t rows, row_bytes;
     int K, slices, units_per_slice, row_warps, depth;      // consumer warps = slices x row_warps
     uint32_t stage_bytes, smem_bytes;
@@ -402,7 +407,13 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
                 if (!ok) break;
                 uint64_t row0;
                 const uint32_t nrows = rows_of(ci, row0);
-                const uint8_t *src = p.enc + (uint64_t)ci.m * p.matrix_stride + row0 * p.row_bytes;
+                const uint8_t *mat = p.matrix_ptrs ? p.matrix_ptrs[ci.m] : p.enc + (uint64_t)ci.m * p.matrix_stride;
+                if (reinterpret_cast<uintptr_t>(mat) & 15u) {            // a bulk copy from there would fault: refuse instead
+                    if (lane == 0) { raise(p.status, YVEX_B200_STATUS_ARGUMENT); ctl.abort = 1; }
+                    ok = false;
+                    break;
+                }
+                const uint8_t *src = mat + row0 * p.row_bytes;
                 const uint32_t bytes = (uint32_t)(nrows * p.row_bytes), bulk = bytes & ~15u;
                 uint8_t *dst = generic(ctl.stage[slot]);
                 if (lane < (int)(bytes - bulk)) dst[bulk + lane] = __ldg(src + bulk + lane);      // the last < 16 bytes of a ragged tile
@@ -479,17 +490,23 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
         asm volatile("" : "+r"(l.nib_base), "+r"(l.sgn_base));      // table reads may not move above this point
     }
     BUnit breg;
-    uint32_t cur_m = 0xffffffffu;
+    uint32_t cur_m = 0xffffffffu, cur_x = 0xffffffffu;
     TaskCursor c;
     c.init(q0, tiles_m);
     for (uint32_t i = 0; i < n_local; ++i, c.next()) {
         uint64_t row0;
         const uint32_t nrows = rows_of(c, row0);
+        if (c.m != cur_m && cur_m != 0xffffffffu && p.x_rows && __ldg(p.x_rows + c.m) == cur_x) {
+            // the next matrix reads the same input row: the planes, sums and B registers stand as they are
+            if (threadIdx.x == 0) ctl.xscale[c.m & 7u] = ctl.xscale[cur_m & 7u];
+            cur_m = c.m;
+        }
         if (c.m != cur_m) {
             // a new matrix: its activation row becomes four planes of signed base-128 digits. Every
             // consumer has finished the previous matrix once it is past this barrier.
             asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
-            const float *x = p.x + (uint64_t)c.m * p.x_stride;
+            cur_x = p.x_rows ? __ldg(p.x_rows + c.m) : c.m;
+            const float *x = p.x + (uint64_t)cur_x * p.x_stride;
             float mx = 0.0f;
             bool badx = false;
             for (int k = threadIdx.x; k < p.K; k += cthreads) {
@@ -642,10 +659,12 @@ inline int stream_launch_t(StreamParams &p, const StreamShape &sh, cudaStream_t 
 
 inline int stream_launch(unsigned q, const uint8_t *enc, uint64_t matrix_stride, uint64_t count, uint64_t rows, uint64_t width,
                          uint64_t row_bytes, const float *x, uint64_t x_stride, const float *additive, float *out,
-                         uint64_t out_stride, int round_bf16, int *status, cudaStream_t stream) {
+                         uint64_t out_stride, int round_bf16, int *status, cudaStream_t stream,
+                         const uint8_t *const *matrix_ptrs = nullptr, const uint32_t *x_rows = nullptr) {
     StreamShape sh;
     if (!stream_shape(width, row_bytes, q == Q_IQ2_XXS, sh)) return ERR_BOUNDS;
     StreamParams p{};
+    p.matrix_ptrs = matrix_ptrs; p.x_rows = x_rows;
     p.enc = enc; p.matrix_stride = matrix_stride; p.count = (uint32_t)count; p.rows = rows; p.row_bytes = row_bytes;
     p.K = (int)width; p.slices = sh.slices; p.units_per_slice = sh.units_per_slice; p.row_warps = sh.row_warps; p.depth = sh.depth;
     p.stage_bytes = sh.stage_bytes; p.smem_bytes = sh.smem_bytes;

@@ -288,7 +288,8 @@ static int check_geometry(const yvex_b200_moe_geometry *g, const yvex_b200_moe_w
 }
 
 extern "C" uint64_t yvex_b200_moe_workspace_bytes(const yvex_b200_moe_geometry *g, uint64_t rows) {
-    return g ? moe_workspace_layout(*g, rows, nullptr) : 0;
+    // the fixed part, then the streaming decode path's tables and per-pair rows (narrow batches)
+    return g ? moe_decode_stream_layout(*g, rows < 64 ? rows : 64, moe_workspace_layout(*g, rows, nullptr), nullptr) : 0;
 }
 
 static int route_into(const MoeGeom &g, const yvex_b200_moe_weights *w, const float *xr,
@@ -372,8 +373,11 @@ extern "C" int yvex_b200_moe_decode_parts(const yvex_b200_moe_geometry *geom, co
     if (!x || !out || !status || !rows || rows > 64) return rows > 64 ? ERR_UNSUPPORTED : ERR_INVALID_ARG;
     MoeGeom g = *geom;
     MoeWorkspace ws;
-    if (!workspace || workspace_bytes < moe_workspace_layout(g, rows, &ws)) return ERR_NOMEM;
+    DecodeStreamScratch stream_scratch;
+    const uint64_t fixed = moe_workspace_layout(g, rows, &ws);
+    if (!workspace || workspace_bytes < moe_decode_stream_layout(g, rows, fixed, &stream_scratch)) return ERR_NOMEM;
     ws.rebase(workspace);
+    stream_scratch.rebase(workspace);
     ws.routed_out = routed_out;
     ws.shared_out = shared_out;
     cudaStream_t s = as_stream(stream);
@@ -381,7 +385,8 @@ extern "C" int yvex_b200_moe_decode_parts(const yvex_b200_moe_geometry *geom, co
     rc = moe_ingress_and_route(g, *w, ws, x, logits, token_ids, rows, status, s);
     if (rc != OK) return rc;
     mark_phase(1, s);
-    rc = moe_experts_narrow(g, *w, ws, rows, out, status, s);
+    rc = moe_decode_stream_eligible(g, *w) ? moe_experts_stream(g, *w, ws, stream_scratch, rows, out, status, s)
+                                           : moe_experts_narrow(g, *w, ws, rows, out, status, s);
     if (rc != OK) return rc;
     if (selected_out) cudaMemcpyAsync(selected_out, ws.selected, rows * g.topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, s);
     if (weights_out) cudaMemcpyAsync(weights_out, ws.weights, rows * g.topk * sizeof(float), cudaMemcpyDeviceToDevice, s);

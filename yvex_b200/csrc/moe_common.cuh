@@ -69,6 +69,28 @@ inline uint64_t moe_workspace_layout(const MoeGeom &g, uint64_t rows, MoeWorkspa
     return off;
 }
 
+// Scratch of the streaming decode path, behind the fixed part of the MoE workspace (narrow batches only).
+struct DecodeStreamScratch {
+    const uint8_t **gu_ptrs, **down_ptrs;      // [pairs * 2], [pairs] matrix addresses
+    uint32_t *gu_rows;                         // input row of each gate/up matrix
+    float *gu;                                 // [pairs][2][inter]
+    float *y;                                  // [pairs][hidden] (bf16-rounded)
+    void rebase(void *base) {
+        auto b = reinterpret_cast<uintptr_t>(base);
+        gu_ptrs = reinterpret_cast<const uint8_t **>(b + reinterpret_cast<uintptr_t>(gu_ptrs));
+        down_ptrs = reinterpret_cast<const uint8_t **>(b + reinterpret_cast<uintptr_t>(down_ptrs));
+        gu_rows = reinterpret_cast<uint32_t *>(b + reinterpret_cast<uintptr_t>(gu_rows));
+        gu = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(gu));
+        y = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(y));
+    }
+};
+// Offsets (rebase() turns them into pointers) from `base`; returns the end.
+uint64_t moe_decode_stream_layout(const MoeGeom &g, uint64_t rows, uint64_t base, DecodeStreamScratch *out);
+bool moe_decode_stream_eligible(const MoeGeom &g, const MoeWeights &w);
+// The (k + 1) experts of every row as two batched launches of the streaming matvec (gate/up, down).
+int moe_experts_stream(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, const DecodeStreamScratch &t, uint64_t rows,
+                       float *out, int *status, cudaStream_t s);
+
 // Expert execution for a narrow batch; picks the streaming tensor-core matvec kernels when the
 // layer's qtypes have decoders for them and the reference-shaped kernels otherwise.
 int moe_experts_narrow(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, uint64_t rows,
