@@ -496,7 +496,8 @@ def run_native_ep(args):
     status = lib.Status(dev)
     # experiment knobs (defaults are what the library picks): segments of the exchange pipeline, whether the exchange runs
     # on its own stream beside the GEMMs, CTAs of the persistent GEMM
-    ops = DeviceOps(geom_full, geom_local, lib.weights_of(shard), status, overlap=os.environ.get("YVEX_EP_OVERLAP", "0") != "0")
+    ops = DeviceOps(geom_full, geom_local, lib.weights_of(shard), status, overlap=os.environ.get("YVEX_EP_OVERLAP", "0") != "0",
+                    peer_return=os.environ.get("YVEX_EP_PEER_RETURN", "1") != "0")
     seg_env = os.environ.get("YVEX_EP_SEGMENTS")
     layer = ExpertParallelLayer(E, spec.topk, ops, segments=int(seg_env) if seg_env else None)
     if os.environ.get("YVEX_EP_CTAS"):
@@ -607,12 +608,12 @@ def run_native_ep(args):
         else:
             real_payload = ops.expert_rows_payload
 
-            def probed(payload, hidden, out=None, workspace=None):
+            def probed(payload, hidden, **kw):
                 if payload.shape[0] and not probed.done:
                     probed.done = True
                     pair_counts.append(payload.shape[0])
-                    return phase_probe(lambda: real_payload(payload, hidden, out=out, workspace=workspace))
-                return real_payload(payload, hidden, out=out, workspace=workspace)
+                    return phase_probe(lambda: real_payload(payload, hidden, **kw))
+                return real_payload(payload, hidden, **kw)
 
             ops.expert_rows_payload = probed
             for i in range(min(args.steps, 5)):

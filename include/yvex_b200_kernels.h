@@ -227,7 +227,7 @@ int yvex_b200_ep_dispatch(const int32_t *selected, const float *weights, const v
  * destination rank), so that segment 0 of every rank can travel and be computed while segment 1 is
  * still on its way. A row travels as one record of yvex_b200_ep_payload_pitch(hidden) bytes: its
  * hidden fp16 values followed by a 16-byte trailer {int32 expert id local to its rank, f32 route
- * weight, int32 pair index at home, 0}, so no second message carries the metadata. send_counts has
+ * weight, int32 pair index at home, int32 home rank}, so no second message carries the metadata. send_counts has
  * world * segments entries, [segment][rank]. yvex_b200_moe_expert_rows_payload runs such records as
  * a pair list (ids and weights from the trailers; a negative id names the shared expert).
  * yvex_b200_moe_wide_set_cta_limit bounds the CTAs of the persistent grouped GEMM (default: one per
@@ -236,11 +236,23 @@ int yvex_b200_ep_dispatch(const int32_t *selected, const float *weights, const v
 uint64_t yvex_b200_ep_payload_pitch(uint64_t hidden);
 int yvex_b200_ep_dispatch_payload(const int32_t *selected, const float *weights, const void *rows_f16, uint64_t tokens,
                                   uint64_t topk, uint64_t hidden, uint64_t experts_per_rank, uint64_t world,
-                                  uint64_t segments, void *payload, int32_t *inverse, long long *send_counts,
+                                  uint64_t rank, uint64_t segments, void *payload, int32_t *inverse, long long *send_counts,
                                   void *workspace, uint64_t workspace_bytes, int *status, void *stream);
 int yvex_b200_moe_expert_rows_payload(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w,
                                       const void *payload, uint64_t pairs, void *y_bf16, void *workspace,
                                       uint64_t workspace_bytes, int *status, void *stream);
+/*
+ * The same GEMMs with the return exchange fused into the down projection: the epilogue stores every
+ * pair's bf16 row straight into its HOME rank's buffer, at home_bases[home rank] + home pair * hidden * 2
+ * (home_bases: device array of `world` byte addresses, this GPU's own buffer and its peers' mapped into
+ * this address space; plain stores over NVLink, no multicast). Nothing is returned by a collective: the
+ * caller only has to know that every rank's kernel has finished (any barrier) before it sums the rows.
+ * A trailer that names a rank >= world or a pair >= home_pairs sets status 2 and its row is dropped.
+ */
+int yvex_b200_moe_expert_rows_scatter(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w,
+                                      const void *payload, uint64_t pairs, const unsigned long long *home_bases,
+                                      uint64_t world, uint64_t home_pairs, void *workspace, uint64_t workspace_bytes,
+                                      int *status, void *stream);
 int yvex_b200_moe_wide_set_cta_limit(int ctas);
 /* The same sum with the rows named by index: routed row (t, r) is y_routed[routed_rows[t*topk + r]],
  * the shared row of token t is y_shared[shared_rows[t]]; a NULL index means the identity order.

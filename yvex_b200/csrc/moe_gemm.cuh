@@ -77,6 +77,10 @@ struct GemmParams {
     const int *num_colblocks;
     uint16_t *out_bf16;                         // [rows][M] bf16 bits (plain kernel: down results) ...
     const int *out_rows;                        // optional: result row of sorted row r is out_rows[r]
+    // optional: sorted row r is stored at this byte address instead, which may lie in ANOTHER GPU's memory
+    // (plain peer stores over NVLink: an expert-parallel rank returns a pair's row straight to its home
+    // rank from the epilogue, so no separate exchange carries it back); 0 = the row is dropped
+    const unsigned long long *out_addr;
     __half *mid;                                // ... or [rows][M] SwiGLU intermediates as fp16 (fused gate/up kernel)
     const float *col_weight;                    // route weight of sorted row r (fused kernel)
     float limit;                                // SwiGLU clamp (fused kernel)
@@ -679,12 +683,14 @@ moe_grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, GemmParams p) {
                     const int col = 4 * b + j4;
                     if (col < ncols_here) {
                         const uint64_t srow = (uint64_t)cb.row0 + kCols * colhalf + col;
-                        const uint64_t at = (p.out_rows ? (uint64_t)__ldg(p.out_rows + srow) : srow) * p.M + m0;
+                        uint16_t *dst;
+                        if (p.out_addr) dst = reinterpret_cast<uint16_t *>(__ldg(p.out_addr + srow));
+                        else dst = p.out_bf16 + (p.out_rows ? (uint64_t)__ldg(p.out_rows + srow) : srow) * p.M;
                         // streaming stores: the results are not read again by this kernel and must not push the
                         // activation tiles and weight rows that other CTAs are about to reuse out of L2
                         const uint2 v = make_uint2(bf16_bits(acc[4 * b]) | ((uint32_t)bf16_bits(acc[4 * b + 1]) << 16),
                                                    bf16_bits(acc[4 * b + 2]) | ((uint32_t)bf16_bits(acc[4 * b + 3]) << 16));
-                        __stcs(reinterpret_cast<uint2 *>(p.out_bf16 + at), v);
+                        if (dst) __stcs(reinterpret_cast<uint2 *>(dst + m0), v);
                     }
                 }
             }

@@ -160,7 +160,22 @@ __global__ void wide_gather_kernel(const __half *rows_h, const int *perm, const 
 }
 
 // Trailer of a row that travels between expert-parallel ranks: behind its hidden fp16 values.
-struct EpTrailer { int32_t local_expert; float weight; int32_t home_pair; int32_t pad; };
+struct EpTrailer { int32_t local_expert; float weight; int32_t home_pair; int32_t home_rank; };
+
+// Where the result of the pair sorted to position pos goes: its home rank's buffer, row home_pair.
+__global__ void wide_dest_kernel(const uint8_t *payload, uint64_t pitch, uint64_t hidden, const int *perm, uint64_t pairs,
+                                 const unsigned long long *home_bases, int home_world, uint64_t home_pairs,
+                                 unsigned long long *dest, int *status) {
+    for (uint64_t pos = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; pos < pairs; pos += (uint64_t)gridDim.x * blockDim.x) {
+        const EpTrailer t = *reinterpret_cast<const EpTrailer *>(payload + (uint64_t)perm[pos] * pitch + hidden * 2);
+        if (t.home_rank < 0 || t.home_rank >= home_world || t.home_pair < 0 || (uint64_t)t.home_pair >= home_pairs) {
+            raise(status, YVEX_B200_STATUS_ARGUMENT);
+            dest[pos] = 0ull;                                   // the row is dropped, never stored through a bad address
+        } else {
+            dest[pos] = home_bases[t.home_rank] + (unsigned long long)t.home_pair * hidden * 2ull;
+        }
+    }
+}
 
 // Pair list from the trailers of received rows: pair p reads source row p.
 __global__ void wide_list_payload_kernel(const uint8_t *payload, uint64_t pitch, uint64_t hidden, uint64_t pairs, int experts,
@@ -267,13 +282,14 @@ struct PairWorkspace {
     float *weight_of_pair, *weight_sorted;
     ColBlock *blocks, *blocks_down;         // column-block lists of the gate/up and the down GEMM (num_blocks[0], [1])
     __half *act_h, *mid_h, *sums, *act_sums;
+    unsigned long long *dest;               // byte address of each sorted row's result (results returned to their home ranks)
     uint16_t *y;
     int max_blocks;
     void rebase(void *base) {
         auto fix = [&](auto *&ptr) { ptr = reinterpret_cast<std::remove_reference_t<decltype(ptr)>>(
                                          reinterpret_cast<uintptr_t>(base) + reinterpret_cast<uintptr_t>(ptr)); };
         fix(counts); fix(offsets); fix(perm); fix(pos_of_pair); fix(num_blocks); fix(expert_of_pair); fix(src_of_pair);
-        fix(weight_of_pair); fix(weight_sorted); fix(blocks); fix(blocks_down); fix(act_h); fix(mid_h); fix(sums); fix(act_sums); fix(y);
+        fix(weight_of_pair); fix(weight_sorted); fix(blocks); fix(blocks_down); fix(act_h); fix(mid_h); fix(sums); fix(act_sums); fix(dest); fix(y);
     }
 };
 
@@ -298,6 +314,7 @@ static uint64_t pair_layout(const MoeGeom &g, uint64_t pairs, uint64_t base_off,
     l.mid_h = reinterpret_cast<__half *>(take(pairs * g.inter * 2));
     l.sums = reinterpret_cast<__half *>(take(pairs * (g.inter / 256) * 64));
     l.act_sums = reinterpret_cast<__half *>(take(pairs * (g.hidden / 256) * 64));
+    l.dest = reinterpret_cast<unsigned long long *>(take(pairs * 8));
     l.y = reinterpret_cast<uint16_t *>(take(pairs * g.hidden * 2));
     if (ws) *ws = l;
     return off;
@@ -411,8 +428,11 @@ bool moe_wide_gemm_eligible(const MoeGeom &g, const MoeWeights &w) {
 // pair in pw.y at row pw.pos_of_pair[pair] or, when y_list is given, in y_list at row `pair` (the
 // down GEMM's epilogue then stores through the permutation, so no separate unsort pass is needed).
 // rows_h: the fp16 source rows the list indexes.
+// home_bases (optional, device array of `home_world` addresses; rows_h then are payload rows with trailers):
+// the row of a pair is stored at home_bases[trailer.home_rank] + trailer.home_pair * hidden * 2 instead.
 static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorkspace &pw, const __half *rows_h, uint64_t pairs,
-                         int *status, cudaStream_t s, uint16_t *y_list = nullptr, uint64_t src_pitch = 0) {
+                         int *status, cudaStream_t s, uint16_t *y_list = nullptr, uint64_t src_pitch = 0,
+                         const unsigned long long *home_bases = nullptr, int home_world = 0, uint64_t home_pairs = 0) {
     if (!src_pitch) src_pitch = g.hidden * 2;
     const Geometry gg = geometry_of(g.gate_qtype), dg = geometry_of(g.down_qtype);
     const int bins = (int)g.experts + 1;
@@ -425,6 +445,9 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     wide_gather_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(rows_h, pw.perm, pw.src_of_pair, pw.weight_of_pair, pairs, g.hidden,
                                                               pw.act_h, pw.weight_sorted, src_pitch, sum_group(g.gate_qtype),
                                                               pw.act_sums, status);
+    if (home_bases)
+        wide_dest_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(reinterpret_cast<const uint8_t *>(rows_h), src_pitch, g.hidden, pw.perm,
+                                                               pairs, home_bases, home_world, home_pairs, pw.dest, status);
     int rc = launch_status(4);
     if (rc != OK) return rc;
     mark_phase(2, s);
@@ -463,6 +486,7 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     }
     dn.colblocks = pw.blocks_down; dn.num_colblocks = pw.num_blocks + 1;
     dn.out_bf16 = y_list ? y_list : pw.y; dn.out_rows = y_list ? pw.perm : nullptr; dn.sums = pw.sums; dn.status = status;
+    dn.out_addr = home_bases ? pw.dest : nullptr;
     rc = run_gemm(g.down_qtype, false, dn_maps, dn, s);
     if (rc != OK) return rc;
     mark_phase(4, s);
@@ -759,7 +783,8 @@ __global__ void ep_bin_kernel(const int32_t *selected, uint64_t pairs, uint64_t 
 }
 
 __global__ void ep_payload_kernel(const __half *rows_h, const int32_t *selected, const float *weights, const int *order,
-                                  const int *src_token, uint64_t pairs, uint64_t hidden, int per_rank, uint8_t *payload, uint64_t pitch) {
+                                  const int *src_token, uint64_t pairs, uint64_t hidden, int per_rank, int home_rank, uint8_t *payload,
+                                  uint64_t pitch) {
     const uint32_t chunks = (uint32_t)(hidden / 8);
     for (uint64_t pos = blockIdx.x; pos < pairs; pos += gridDim.x) {
         const int p = order[pos];
@@ -768,7 +793,7 @@ __global__ void ep_payload_kernel(const __half *rows_h, const int32_t *selected,
         for (uint32_t c = threadIdx.x; c < chunks; c += blockDim.x) dst[c] = __ldg(src + c);
         if (threadIdx.x == 0) {
             const int e = selected[p];
-            const EpTrailer t{e >= 0 ? e % per_rank : 0, weights[p], p, 0};
+            const EpTrailer t{e >= 0 ? e % per_rank : 0, weights[p], p, home_rank};
             *reinterpret_cast<EpTrailer *>(payload + pos * pitch + hidden * 2) = t;
         }
     }
@@ -778,11 +803,11 @@ extern "C" uint64_t yvex_b200_ep_payload_pitch(uint64_t hidden) { return hidden 
 
 extern "C" int yvex_b200_ep_dispatch_payload(const int32_t *selected, const float *weights, const void *rows_f16, uint64_t tokens,
                                              uint64_t topk, uint64_t hidden, uint64_t experts_per_rank, uint64_t world,
-                                             uint64_t segments, void *payload, int32_t *inverse, long long *send_counts,
+                                             uint64_t rank, uint64_t segments, void *payload, int32_t *inverse, long long *send_counts,
                                              void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
     if (!selected || !weights || !rows_f16 || !payload || !inverse || !send_counts || !status || !workspace) return ERR_INVALID_ARG;
-    if (!tokens || !topk || !experts_per_rank || !world || !segments || world * segments > 1024 || segments > experts_per_rank ||
-        hidden % 8)
+    if (!tokens || !topk || !experts_per_rank || !world || rank >= world || !segments || world * segments > 1024 ||
+        segments > experts_per_rank || hidden % 8)
         return ERR_INVALID_ARG;
     const uint64_t pairs = tokens * topk, bins = world * segments;
     if (pairs > 0x7fffff00ull || ((reinterpret_cast<uintptr_t>(rows_f16) | reinterpret_cast<uintptr_t>(payload)) & 15u)) return ERR_BOUNDS;
@@ -796,7 +821,7 @@ extern "C" int yvex_b200_ep_dispatch_payload(const int32_t *selected, const floa
     ep_offsets_kernel<<<1, 32, 0, s>>>(counts, (int)bins, offsets, send_counts);
     wide_scatter_kernel<<<(unsigned)bins, 512, 0, s>>>(bin_of, pairs, offsets, order, inverse);
     ep_payload_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(static_cast<const __half *>(rows_f16), selected, weights, order, src, pairs,
-                                                             hidden, (int)experts_per_rank, static_cast<uint8_t *>(payload),
+                                                             hidden, (int)experts_per_rank, (int)rank, static_cast<uint8_t *>(payload),
                                                              yvex_b200_ep_payload_pitch(hidden));
     return launch_status(4);
 }
@@ -822,6 +847,33 @@ extern "C" int yvex_b200_moe_expert_rows_payload(const yvex_b200_moe_geometry *g
                                                                    (int)g.experts, pw.expert_of_pair, pw.src_of_pair, pw.weight_of_pair);
     mark_phase(1, s);
     rc = run_pair_list(g, *w, pw, static_cast<const __half *>(payload), pairs, status, s, static_cast<uint16_t *>(y_bf16), pitch);
+    if (rc != OK) return rc;
+    mark_phase(5, s);
+    return launch_status(1);
+}
+
+extern "C" int yvex_b200_moe_expert_rows_scatter(const yvex_b200_moe_geometry *geom, const yvex_b200_moe_weights *w,
+                                                 const void *payload, uint64_t pairs, const unsigned long long *home_bases,
+                                                 uint64_t world, uint64_t home_pairs, void *workspace, uint64_t workspace_bytes,
+                                                 int *status, void *stream) {
+    int rc = moe_check_geometry(geom, w);
+    if (rc != OK) return rc;
+    if (!pairs) return OK;
+    if (!payload || !home_bases || !status || !world || world > 1024 || !home_pairs) return ERR_INVALID_ARG;
+    if (pairs > 0x7fffff00ull / 2 || home_pairs > 0x7fffff00ull || (reinterpret_cast<uintptr_t>(payload) & 15u)) return ERR_BOUNDS;
+    MoeGeom g = *geom;
+    if (!moe_wide_gemm_eligible(g, *w)) return ERR_UNSUPPORTED;
+    PairWorkspace pw;
+    if (!workspace || workspace_bytes < pair_layout(g, pairs, 0, &pw)) return ERR_NOMEM;
+    pw.rebase(workspace);
+    cudaStream_t s = as_stream(stream);
+    const uint64_t pitch = yvex_b200_ep_payload_pitch(g.hidden);
+    mark_phase(0, s);
+    wide_list_payload_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(static_cast<const uint8_t *>(payload), pitch, g.hidden, pairs,
+                                                                   (int)g.experts, pw.expert_of_pair, pw.src_of_pair, pw.weight_of_pair);
+    mark_phase(1, s);
+    rc = run_pair_list(g, *w, pw, static_cast<const __half *>(payload), pairs, status, s, nullptr, pitch, home_bases, (int)world,
+                       home_pairs);
     if (rc != OK) return rc;
     mark_phase(5, s);
     return launch_status(1);

@@ -28,6 +28,7 @@ tensor formulation of every step; `DeviceOps` replaces each with a library call)
 from __future__ import annotations
 
 import contextlib
+import os
 
 import torch
 import torch.distributed as dist
@@ -103,11 +104,14 @@ class TorchOps:
 class DeviceOps(TorchOps):
     """The layer's compute steps on the current CUDA device, via the C-ABI. Owns the step buffers."""
 
-    def __init__(self, geom_full, geom_local, weights_local, status, overlap=False):
+    def __init__(self, geom_full, geom_local, weights_local, status, overlap=False, peer_return=True):
         from . import lib
         self.lib, self.geom_full, self.geom_local = lib, geom_full, geom_local
         self.weights, self.status = weights_local, status
         self.overlap = overlap
+        self.peer_return = peer_return          # results go home by peer stores from the down GEMM's epilogue
+        self.home, self.home_flip = None, 0
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
         self.cta_limit = 140                   # CTAs of the persistent GEMM while an exchange runs beside it
         self.streams = None
         self.buf = {}
@@ -137,10 +141,32 @@ class DeviceOps(TorchOps):
                                      dtype=torch.uint8, device=dev)
         b["seg"] = [None] * segments
         self.buf = b
+        self.home = self._home_buffers(pairs, hidden, dev) if self.peer_return and world > 1 else None
         if self.overlap and world > 1 and self.streams is None:
             self.streams = (torch.cuda.Stream(device=dev, priority=-1),)          # communication stream, high priority
             # the persistent GEMM leaves a few SMs to the exchange kernels that run beside it
             self.lib.lib.yvex_b200_moe_wide_set_cta_limit(self.cta_limit)
+
+    def _home_buffers(self, pairs, hidden, dev):
+        """Two buffers [pairs, hidden] bf16 that every peer can store into (symmetric memory; the rendezvous is a
+        collective, every rank reaches it in its first step), used alternately so that a fast peer's next step
+        never lands in rows this rank is still summing. None when peer access cannot be set up: the rows then
+        come back by an exchange."""
+        try:
+            import torch.distributed._symmetric_memory as symm
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")       # plain peer stores only
+            out = []
+            for _ in range(2):
+                t = symm.empty(pairs * hidden, dtype=torch.bfloat16, device=dev)
+                hdl = symm.rendezvous(t, dist.group.WORLD)
+                bases = torch.tensor([int(p) for p in hdl.buffer_ptrs], dtype=torch.int64, device=dev)
+                out.append((t.view(pairs, hidden), bases, hdl))
+            self.home_flag = torch.zeros(1, dtype=torch.float32, device=dev)
+            return out
+        except Exception as exc:                                                 # no peer access on this box
+            import warnings
+            warnings.warn(f"peer return disabled: {type(exc).__name__}: {exc}")
+            return None
 
     def segment_buffers(self, seg, rows):
         """Receive records, result rows and pair-list workspace of one segment, grown when a step needs more."""
@@ -169,7 +195,7 @@ class DeviceOps(TorchOps):
     def dispatch(self, xh, sel, wts, per_rank, world, segments):
         b = self.buf
         self.lib.ep_dispatch_payload(xh, sel.contiguous(), wts.contiguous(), per_rank, world, segments, self.status,
-                                     b["payload"], b["inverse"], b["counts"], b["plan_ws"])
+                                     b["payload"], b["inverse"], b["counts"], b["plan_ws"], rank=self.rank)
         return b["payload"], b["inverse"], b["counts"]
 
     def expert_rows(self, rows_h, ids, wts, workspace=None, out=None):
@@ -179,7 +205,11 @@ class DeviceOps(TorchOps):
         b = self.buf
         return self.expert_rows(xh, b["shared_ids"], b["shared_w"], workspace=b["shared_ws"], out=b["y_shared"])
 
-    def expert_rows_payload(self, payload, hidden, out=None, workspace=None):
+    def expert_rows_payload(self, payload, hidden, out=None, workspace=None, home=None):
+        if home is not None:                   # (rows [pairs, hidden], bases): store every row at its home rank
+            self.lib.moe_expert_rows_scatter(self.geom_local, self.weights, payload, home[1], home[0].shape[0], self.status,
+                                             workspace=workspace)
+            return None
         return self.lib.moe_expert_rows_payload(self.geom_local, self.weights, payload, self.status, workspace=workspace, out=out)
 
     def combine(self, y_routed, y_shared, topk, routed_rows=None):
@@ -275,6 +305,10 @@ class ExpertParallelLayer:
         y_back = ops.buf.get("y_back")
         if y_back is None:
             y_back = torch.empty((t * k, hidden), dtype=torch.bfloat16, device=x.device)
+        home = None
+        if W > 1 and getattr(ops, "home", None):
+            ops.home_flip ^= 1
+            home = ops.home[ops.home_flip]
         send_off, seg_bufs = 0, []
         # dispatch of every segment, in order, on the communication stream
         with on_side():
@@ -297,6 +331,11 @@ class ExpertParallelLayer:
         for s, (recv, y_seg, ws, ev, off, n_send, n_recv) in enumerate(seg_bufs):
             if ev is not None:
                 main.wait_event(ev)
+            if home is not None:
+                if n_recv:
+                    ops.expert_rows_payload(recv, hidden, workspace=ws, home=home)
+                mark(f"segment{s}_wait_and_gemm")
+                continue
             if n_recv:
                 y_seg = ops.expert_rows_payload(recv, hidden, out=y_seg, workspace=ws) if ws is not None \
                     else ops.expert_rows_payload(recv, hidden)
@@ -312,8 +351,16 @@ class ExpertParallelLayer:
                     back_events.append(e2)
         for e2 in back_events:
             main.wait_event(e2)
-        # pair (token, rank) sits at row inverse[...] of y_back: the combine reads through that index
-        out = ops.combine(y_back, y_shared, k, routed_rows=inverse)
+        if home is not None:
+            # every rank's GEMMs have stored their rows once this (tiny) collective has passed on every stream
+            try:
+                dist.all_reduce(ops.home_flag, group=self.group)
+            except Exception as exc:
+                raise ExchangeError(ERR_TIMEOUT, str(exc).splitlines()[0] if str(exc) else type(exc).__name__) from exc
+            out = ops.combine(home[0], y_shared, k)                             # rows already sit in pair order
+        else:
+            # pair (token, rank) sits at row inverse[...] of y_back: the combine reads through that index
+            out = ops.combine(y_back, y_shared, k, routed_rows=inverse)
         mark("return_wait_and_combine")
         if marks:
             self.timings["marks"] = marks

@@ -67,7 +67,9 @@ def _load():
     lib.yvex_b200_ep_dispatch.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, vp, vp, vp, vp, vp, u64, vp, vp]
     lib.yvex_b200_ep_payload_pitch.restype = u64
     lib.yvex_b200_ep_payload_pitch.argtypes = [u64]
-    lib.yvex_b200_ep_dispatch_payload.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, vp, vp, vp, vp, u64, vp, vp]
+    lib.yvex_b200_ep_dispatch_payload.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, u64, vp, vp, vp, vp, u64, vp, vp]
+    lib.yvex_b200_moe_expert_rows_scatter.argtypes = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights), vp, u64, vp, u64, u64, vp, u64,
+                                                      vp, vp]
     lib.yvex_b200_moe_expert_rows_payload.argtypes = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights), vp, u64, vp, vp, u64, vp, vp]
     lib.yvex_b200_moe_wide_set_cta_limit.argtypes = [C.c_int]
     lib.yvex_b200_attention_workspace_bytes.restype = u64
@@ -115,7 +117,8 @@ EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_ge
            "yvex_b200_selftest_bounded_wait", "yvex_b200_moe_wide_uses_gemm", "yvex_b200_moe_wide_tile_columns",
            "yvex_b200_ep_payload_pitch", "yvex_b200_ep_dispatch_payload", "yvex_b200_moe_expert_rows_payload",
            "yvex_b200_moe_wide_set_cta_limit", "yvex_b200_moe_decode_parts", "yvex_b200_moe_wide_parts",
-           "yvex_b200_dequant_gather", "yvex_b200_q8k_round_trip", "yvex_b200_concat_bf16"]
+           "yvex_b200_dequant_gather", "yvex_b200_q8k_round_trip", "yvex_b200_concat_bf16",
+           "yvex_b200_moe_expert_rows_scatter"]
 
 
 def _torch():
@@ -308,7 +311,7 @@ def expert_worklist(selected, experts, status, tensor_core_minimum=0, admitted_w
 
 
 def ep_dispatch_payload(rows_f16, selected, route_weights, experts_per_rank, world, segments, status, payload=None, inverse=None,
-                        counts=None, workspace=None):
+                        counts=None, workspace=None, rank=0):
     """Segmented sending side: rows_f16 [T, hidden] fp16, selected / route_weights [T, k] -> (payload [T*k, 2*hidden + 16] uint8
     in send order (segment, destination rank), inverse [T*k] int32, counts [segments * world] int64)."""
     torch = _torch()
@@ -324,9 +327,24 @@ def ep_dispatch_payload(rows_f16, selected, route_weights, experts_per_rank, wor
     if workspace is None:
         workspace = torch.empty(int(lib.yvex_b200_ep_dispatch_workspace_bytes(pairs, bins)), dtype=torch.uint8, device=dev)
     _check(lib.yvex_b200_ep_dispatch_payload(_p(selected), _p(route_weights), _p(rows_f16), tokens, selected.shape[1], hidden,
-                                             experts_per_rank, world, segments, _p(payload), _p(inverse), _p(counts), _p(workspace),
+                                             experts_per_rank, world, rank, segments, _p(payload), _p(inverse), _p(counts), _p(workspace),
                                              workspace.numel(), _p(status.word), _stream()), "ep_dispatch_payload")
     return payload, inverse, counts
+
+
+def moe_expert_rows_scatter(geom, weights, payload, home_bases, home_pairs, status, workspace=None):
+    """The same GEMMs with every pair's bf16 row stored straight into its home rank's buffer (home_bases: int64 device
+    tensor of one byte address per rank; peers' buffers mapped into this process). Returns nothing: the rows are elsewhere."""
+    torch = _torch()
+    pairs = payload.shape[0]
+    if pairs == 0:
+        return
+    if workspace is None:
+        workspace = torch.empty(int(lib.yvex_b200_moe_expert_rows_workspace_bytes(C.byref(geom), pairs)),
+                                dtype=torch.uint8, device=payload.device)
+    _check(lib.yvex_b200_moe_expert_rows_scatter(C.byref(geom), C.byref(weights), _p(payload), pairs, _p(home_bases), home_bases.numel(),
+                                                 home_pairs, _p(workspace), workspace.numel(), _p(status.word), _stream()),
+           "moe_expert_rows_scatter")
 
 
 def moe_expert_rows_payload(geom, weights, payload, status, workspace=None, out=None):
