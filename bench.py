@@ -497,7 +497,8 @@ def run_native_ep(args):
     # experiment knobs (defaults are what the library picks): segments of the exchange pipeline, whether the exchange runs
     # on its own stream beside the GEMMs, CTAs of the persistent GEMM
     ops = DeviceOps(geom_full, geom_local, lib.weights_of(shard), status, overlap=os.environ.get("YVEX_EP_OVERLAP", "0") != "0",
-                    peer_return=os.environ.get("YVEX_EP_PEER_RETURN", "1") != "0")
+                    peer_return=os.environ.get("YVEX_EP_PEER_RETURN", "1") != "0",
+                    peer_dispatch=os.environ.get("YVEX_EP_PEER_DISPATCH", "1") != "0")
     seg_env = os.environ.get("YVEX_EP_SEGMENTS")
     layer = ExpertParallelLayer(E, spec.topk, ops, segments=int(seg_env) if seg_env else None)
     if os.environ.get("YVEX_EP_CTAS"):

@@ -242,6 +242,24 @@ int yvex_b200_moe_expert_rows_payload(const yvex_b200_moe_geometry *g, const yve
                                       const void *payload, uint64_t pairs, void *y_bf16, void *workspace,
                                       uint64_t workspace_bytes, int *status, void *stream);
 /*
+ * The dispatch without a bulk collective, in two calls around one all-gather of the counts.
+ * yvex_b200_ep_dispatch_plan groups the pairs as above (inverse index, send_counts[segments * world]) and
+ * leaves the plan in `workspace`. Once every rank knows every rank's counts (counts_all[world][segments *
+ * world], device), yvex_b200_ep_dispatch_push (same workspace) writes each payload row straight into the
+ * destination rank's receive buffer of its segment: recv_bases[bin] is that buffer's byte address (bin =
+ * segment * world + destination; peers' buffers mapped into this address space; plain stores over NVLink,
+ * no multicast), rows of one bin ordered by source rank. A row that would land at or past capacity_rows
+ * sets status 2 and is not stored. The receiver may read its buffers once every rank's push has finished
+ * (any barrier).
+ */
+int yvex_b200_ep_dispatch_plan(const int32_t *selected, uint64_t tokens, uint64_t topk, uint64_t experts_per_rank, uint64_t world,
+                               uint64_t segments, int32_t *inverse, long long *send_counts, void *workspace, uint64_t workspace_bytes,
+                               int *status, void *stream);
+int yvex_b200_ep_dispatch_push(const int32_t *selected, const float *weights, const void *rows_f16, uint64_t tokens, uint64_t topk,
+                               uint64_t hidden, uint64_t experts_per_rank, uint64_t world, uint64_t rank, uint64_t segments,
+                               const long long *counts_all, const unsigned long long *recv_bases, uint64_t capacity_rows,
+                               void *workspace, uint64_t workspace_bytes, int *status, void *stream);
+/*
  * The same GEMMs with the return exchange fused into the down projection: the epilogue stores every
  * pair's bf16 row straight into its HOME rank's buffer, at home_bases[home rank] + home pair * hidden * 2
  * (home_bases: device array of `world` byte addresses, this GPU's own buffer and its peers' mapped into

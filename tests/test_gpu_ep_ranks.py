@@ -16,7 +16,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, segments, overlap, peer_return, ret):
+def _worker(rank, world, port, segments, overlap, peer_return, peer_dispatch, ret):
     import torch
     import torch.distributed as dist
     from yvex_b200 import lib, synth
@@ -40,7 +40,8 @@ def _worker(rank, world, port, segments, overlap, peer_return, ret):
     st = lib.Status(dev)
     g_full = lib.geometry_of(spec)
     g_local = lib.geometry_of(synth.MoELayerSpec(H, per, k, I, down_qtype=synth.Q2_K))
-    layer = ExpertParallelLayer(E, k, DeviceOps(g_full, g_local, lib.weights_of(shard), st, overlap=overlap, peer_return=peer_return),
+    layer = ExpertParallelLayer(E, k, DeviceOps(g_full, g_local, lib.weights_of(shard), st, overlap=overlap, peer_return=peer_return,
+                                                    peer_dispatch=peer_dispatch),
                                 segments=segments)
     x, lg = x_all[rank * T:(rank + 1) * T].contiguous(), lg_all[rank * T:(rank + 1) * T].contiguous()
     ok = True
@@ -49,14 +50,15 @@ def _worker(rank, world, port, segments, overlap, peer_return, ret):
         want, sel0, _ = lib.moe_layer(g_full, lib.weights_of(full), x, st, logits=lg, wide=True)
         torch.cuda.synchronize()
         ok = ok and torch.equal(sel, sel0) and torch.equal(out.view(torch.int32), want.view(torch.int32))
-    ret[rank] = (bool(ok), st.read(), layer.ops.home is not None)
+    ret[rank] = (bool(ok), st.read(), layer.ops.home is not None, layer.ops.inbox is not None)
     dist.barrier()
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("segments,overlap,peer_return", [(1, False, True), (2, True, True), (2, True, False), (1, False, False),
-                                                          (4, True, False)])
-def test_two_ranks_match_the_single_device_layer_bit_for_bit(segments, overlap, peer_return):
+@pytest.mark.parametrize("segments,overlap,peer_return,peer_dispatch", [
+    (1, False, True, True), (2, False, True, True), (1, False, False, True), (1, False, True, False), (2, True, True, False),
+    (2, True, False, False), (1, False, False, False), (4, True, False, False)])
+def test_two_ranks_match_the_single_device_layer_bit_for_bit(segments, overlap, peer_return, peer_dispatch):
     """peer_return: the down GEMM's epilogue stores every pair's row straight into its home rank's memory
     (plain peer stores), else the rows come back by a second all-to-all-v."""
     import torch
@@ -64,5 +66,5 @@ def test_two_ranks_match_the_single_device_layer_bit_for_bit(segments, overlap, 
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two CUDA devices")
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(2, _free_port(), segments, overlap, peer_return, ret), nprocs=2, join=True)
-    assert dict(ret) == {0: (True, 0, peer_return), 1: (True, 0, peer_return)}
+    mp.spawn(_worker, args=(2, _free_port(), segments, overlap, peer_return, peer_dispatch, ret), nprocs=2, join=True)
+    assert dict(ret) == {0: (True, 0, peer_return, peer_dispatch), 1: (True, 0, peer_return, peer_dispatch)}

@@ -738,7 +738,8 @@ __global__ void ep_meta_kernel(const int32_t *selected, const float *weights, co
 }
 
 extern "C" uint64_t yvex_b200_ep_dispatch_workspace_bytes(uint64_t pairs, uint64_t world) {
-    return (3 * pairs + 2 * world + 8) * sizeof(int) + 256;
+    // bin of pair, source token, send order; counts and offsets per bin; the pushed dispatch's write offsets
+    return (3 * pairs + 2 * world + 8) * sizeof(int) + 256 + 8 * world + 64;
 }
 
 extern "C" int yvex_b200_ep_dispatch(const int32_t *selected, const float *weights, const void *rows_f16, uint64_t tokens,
@@ -801,6 +802,44 @@ __global__ void ep_payload_kernel(const __half *rows_h, const int32_t *selected,
 
 extern "C" uint64_t yvex_b200_ep_payload_pitch(uint64_t hidden) { return hidden * 2 + sizeof(EpTrailer); }
 
+// ---- dispatch by peer stores ----------------------------------------------------------------------------
+// Every rank knows how many rows every rank sends into every bin (counts_all[src][bin], all-gathered).
+// A bin's rows land in the destination rank's receive buffer grouped by source rank, ascending: this
+// rank writes behind the rows of the ranks below it.
+__global__ void ep_push_offsets_kernel(const long long *counts_all, int bins, int rank, long long *row_base) {
+    for (int b = threadIdx.x; b < bins; b += blockDim.x) {
+        long long off = 0;
+        for (int r = 0; r < rank; ++r) off += counts_all[(size_t)r * bins + b];
+        row_base[b] = off;
+    }
+}
+
+// The payload row of send position pos goes straight to recv_bases[bin] + (row_base[bin] + its index in the bin) * pitch,
+// an address in the destination rank's memory (plain 16-byte stores; the own rank's bins are local stores).
+__global__ void ep_push_kernel(const __half *rows_h, const int32_t *selected, const float *weights, const int *order, const int *bin_of,
+                               const int *src_token, const int *bin_start, const long long *row_base,
+                               const unsigned long long *recv_bases, uint64_t capacity_rows, uint64_t pairs, uint64_t hidden,
+                               int per_rank, int home_rank, uint64_t pitch, int *status) {
+    const uint32_t chunks = (uint32_t)(hidden / 8);
+    for (uint64_t pos = blockIdx.x; pos < pairs; pos += gridDim.x) {
+        const int p = order[pos], b = bin_of[p];
+        const uint64_t at = (uint64_t)row_base[b] + (pos - (uint64_t)bin_start[b]);
+        if (at >= capacity_rows) {                       // never a store past the receiver's buffer
+            if (threadIdx.x == 0) raise(status, YVEX_B200_STATUS_ARGUMENT);
+            continue;
+        }
+        uint8_t *row = reinterpret_cast<uint8_t *>(recv_bases[b]) + at * pitch;
+        const uint4 *src = reinterpret_cast<const uint4 *>(rows_h) + (uint64_t)src_token[p] * chunks;
+        uint4 *dst = reinterpret_cast<uint4 *>(row);
+        for (uint32_t c = threadIdx.x; c < chunks; c += blockDim.x) dst[c] = __ldg(src + c);
+        if (threadIdx.x == 0) {
+            const int e = selected[p];
+            const EpTrailer t{e >= 0 ? e % per_rank : 0, weights[p], p, home_rank};
+            *reinterpret_cast<EpTrailer *>(row + hidden * 2) = t;
+        }
+    }
+}
+
 extern "C" int yvex_b200_ep_dispatch_payload(const int32_t *selected, const float *weights, const void *rows_f16, uint64_t tokens,
                                              uint64_t topk, uint64_t hidden, uint64_t experts_per_rank, uint64_t world,
                                              uint64_t rank, uint64_t segments, void *payload, int32_t *inverse, long long *send_counts,
@@ -824,6 +863,49 @@ extern "C" int yvex_b200_ep_dispatch_payload(const int32_t *selected, const floa
                                                              hidden, (int)experts_per_rank, (int)rank, static_cast<uint8_t *>(payload),
                                                              yvex_b200_ep_payload_pitch(hidden));
     return launch_status(4);
+}
+
+extern "C" int yvex_b200_ep_dispatch_plan(const int32_t *selected, uint64_t tokens, uint64_t topk, uint64_t experts_per_rank,
+                                          uint64_t world, uint64_t segments, int32_t *inverse, long long *send_counts, void *workspace,
+                                          uint64_t workspace_bytes, int *status, void *stream) {
+    if (!selected || !inverse || !send_counts || !status || !workspace) return ERR_INVALID_ARG;
+    if (!tokens || !topk || !experts_per_rank || !world || !segments || world * segments > 1024 || segments > experts_per_rank)
+        return ERR_INVALID_ARG;
+    const uint64_t pairs = tokens * topk, bins = world * segments;
+    if (pairs > 0x7fffff00ull) return ERR_BOUNDS;
+    if (workspace_bytes < yvex_b200_ep_dispatch_workspace_bytes(pairs, bins)) return ERR_NOMEM;
+    int *bin_of = static_cast<int *>(workspace), *src = bin_of + pairs, *order = src + pairs;
+    int *counts = order + pairs, *offsets = counts + bins + 1;
+    cudaStream_t s = as_stream(stream);
+    cudaMemsetAsync(counts, 0, (bins + 1) * sizeof(int), s);
+    ep_bin_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(selected, pairs, topk, (int)experts_per_rank, (int)world, (int)segments, bin_of,
+                                                         src, counts, status);
+    ep_offsets_kernel<<<1, 32, 0, s>>>(counts, (int)bins, offsets, send_counts);
+    wide_scatter_kernel<<<(unsigned)bins, 512, 0, s>>>(bin_of, pairs, offsets, order, inverse);
+    return launch_status(3);
+}
+
+extern "C" int yvex_b200_ep_dispatch_push(const int32_t *selected, const float *weights, const void *rows_f16, uint64_t tokens,
+                                          uint64_t topk, uint64_t hidden, uint64_t experts_per_rank, uint64_t world, uint64_t rank,
+                                          uint64_t segments, const long long *counts_all, const unsigned long long *recv_bases,
+                                          uint64_t capacity_rows, void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
+    if (!selected || !weights || !rows_f16 || !counts_all || !recv_bases || !status || !workspace) return ERR_INVALID_ARG;
+    if (!tokens || !topk || !experts_per_rank || !world || rank >= world || !segments || world * segments > 1024 ||
+        segments > experts_per_rank || hidden % 8 || !capacity_rows)
+        return ERR_INVALID_ARG;
+    const uint64_t pairs = tokens * topk, bins = world * segments;
+    if (pairs > 0x7fffff00ull || (reinterpret_cast<uintptr_t>(rows_f16) & 15u)) return ERR_BOUNDS;
+    if (workspace_bytes < yvex_b200_ep_dispatch_workspace_bytes(pairs, bins)) return ERR_NOMEM;
+    // the plan of yvex_b200_ep_dispatch_plan, left in the same workspace; the write offsets go behind it
+    int *bin_of = static_cast<int *>(workspace), *src = bin_of + pairs, *order = src + pairs;
+    int *counts = order + pairs, *offsets = counts + bins + 1;
+    long long *row_base = reinterpret_cast<long long *>((reinterpret_cast<uintptr_t>(offsets + bins + 2) + 7u) & ~uintptr_t(7));
+    cudaStream_t s = as_stream(stream);
+    ep_push_offsets_kernel<<<1, 256, 0, s>>>(counts_all, (int)bins, (int)rank, row_base);
+    ep_push_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(static_cast<const __half *>(rows_f16), selected, weights, order, bin_of, src,
+                                                          offsets, row_base, recv_bases, capacity_rows, pairs, hidden,
+                                                          (int)experts_per_rank, (int)rank, yvex_b200_ep_payload_pitch(hidden), status);
+    return launch_status(2);
 }
 
 extern "C" int yvex_b200_moe_expert_rows_payload(const yvex_b200_moe_geometry *geom, const yvex_b200_moe_weights *w,

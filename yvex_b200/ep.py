@@ -104,13 +104,15 @@ class TorchOps:
 class DeviceOps(TorchOps):
     """The layer's compute steps on the current CUDA device, via the C-ABI. Owns the step buffers."""
 
-    def __init__(self, geom_full, geom_local, weights_local, status, overlap=False, peer_return=True):
+    def __init__(self, geom_full, geom_local, weights_local, status, overlap=False, peer_return=True, peer_dispatch=True):
         from . import lib
         self.lib, self.geom_full, self.geom_local = lib, geom_full, geom_local
         self.weights, self.status = weights_local, status
         self.overlap = overlap
         self.peer_return = peer_return          # results go home by peer stores from the down GEMM's epilogue
         self.home, self.home_flip = None, 0
+        self.peer_dispatch = peer_dispatch      # rows reach their expert's rank by peer stores from the dispatch kernel
+        self.inbox = None
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         self.cta_limit = 140                   # CTAs of the persistent GEMM while an exchange runs beside it
         self.streams = None
@@ -142,6 +144,7 @@ class DeviceOps(TorchOps):
         b["seg"] = [None] * segments
         self.buf = b
         self.home = self._home_buffers(pairs, hidden, dev) if self.peer_return and world > 1 else None
+        self.inbox = self._inbox(pairs, pitch, world, segments, dev) if self.peer_dispatch and world > 1 else None
         if self.overlap and world > 1 and self.streams is None:
             self.streams = (torch.cuda.Stream(device=dev, priority=-1),)          # communication stream, high priority
             # the persistent GEMM leaves a few SMs to the exchange kernels that run beside it
@@ -167,6 +170,44 @@ class DeviceOps(TorchOps):
             import warnings
             warnings.warn(f"peer return disabled: {type(exc).__name__}: {exc}")
             return None
+
+    def _inbox(self, pairs, pitch, world, segments, dev):
+        """Receive buffers every peer can store into, one per segment, of a fixed capacity (twice the balanced
+        load plus a quarter; a step that needs more takes the exchange instead), with their pair-list
+        workspaces, the per-bin addresses and the all-gathered counts. None when peer access cannot be set up."""
+        try:
+            import torch.distributed._symmetric_memory as symm
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            cap = max(2 * pairs // segments + pairs // (4 * segments), 1024)
+            bases = torch.empty(segments * world, dtype=torch.int64)
+            recv = []
+            for s in range(segments):
+                t = symm.empty(cap * pitch, dtype=torch.uint8, device=dev)
+                hdl = symm.rendezvous(t, dist.group.WORLD)
+                for d in range(world):
+                    bases[s * world + d] = int(hdl.buffer_ptrs[d])
+                recv.append((t.view(cap, pitch), hdl))
+            bins = world * segments
+            return {"cap": cap, "recv": recv, "bases": bases.to(dev),
+                    "ws": [torch.empty(int(self.lib.lib.yvex_b200_moe_expert_rows_workspace_bytes(self.geom_local, cap)),
+                                       dtype=torch.uint8, device=dev) for _ in range(segments)],
+                    "y": [None] * segments,
+                    "counts_all": torch.empty(world * bins, dtype=torch.int64, device=dev),
+                    "counts_all_host": torch.empty(world * bins, dtype=torch.int64).pin_memory(),
+                    "flag": torch.zeros(1, dtype=torch.float32, device=dev)}
+        except Exception as exc:
+            import warnings
+            warnings.warn(f"peer dispatch disabled: {type(exc).__name__}: {exc}")
+            return None
+
+    def plan(self, sel, per_rank, world, segments):
+        b = self.buf
+        return self.lib.ep_dispatch_plan(sel.contiguous(), per_rank, world, segments, self.status, b["inverse"], b["counts"], b["plan_ws"])
+
+    def push(self, xh, sel, wts, per_rank, world, segments):
+        box = self.inbox
+        self.lib.ep_dispatch_push(xh, sel.contiguous(), wts.contiguous(), per_rank, world, self.rank, segments, box["counts_all"],
+                                  box["bases"], box["cap"], self.status, self.buf["plan_ws"])
 
     def segment_buffers(self, seg, rows):
         """Receive records, result rows and pair-list workspace of one segment, grown when a step needs more."""
@@ -274,6 +315,12 @@ class ExpertParallelLayer:
         mark("start")
         xh = ops.ingress(x)
         sel, wts = ops.route(x, logits)                                   # [t, k] int32 / f32
+        if W > 1 and getattr(ops, "inbox", None):
+            out = self._forward_pushed(x, xh, sel, wts, mark)
+            if out is not None:
+                if marks:
+                    self.timings["marks"] = marks
+                return out, sel, wts
         payload, inverse, counts = ops.dispatch(xh, sel, wts, self.per_rank, W, S)
         mark("route_plan")
         # split sizes: one tiny exchange and the step's only host read
@@ -366,6 +413,69 @@ class ExpertParallelLayer:
             self.timings["marks"] = marks
             self.timings["pairs_received"] = [b[6] for b in seg_bufs]
         return out, sel, wts
+
+    def _forward_pushed(self, x, xh, sel, wts, mark):
+        """The step without a bulk collective: the dispatch kernel stores every row straight into its expert's rank
+        (symmetric receive buffers), the down GEMM's epilogue stores every result straight into its home rank. What
+        remains of NCCL is one all-gather of the counts and two one-element all-reduces used as barriers.
+        Returns None (nothing stored anywhere yet) when a receive buffer would overflow: the caller then runs
+        the exchange-based step."""
+        k, ops, W, S = self.topk, self.ops, self.world, self.segments
+        t, hidden = x.shape
+        box, bins = ops.inbox, W * S
+        inverse, counts = ops.plan(sel, self.per_rank, W, S)
+        try:
+            dist.all_gather_into_tensor(box["counts_all"], counts, group=self.group)
+        except Exception as exc:
+            raise ExchangeError(ERR_TIMEOUT, str(exc).splitlines()[0] if str(exc) else type(exc).__name__) from exc
+        box["counts_all_host"].copy_(box["counts_all"], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        mark("route_plan")
+        y_shared = ops.shared_rows(xh)                                    # covers the host read of the counts
+        mark("shared_expert")
+        done.synchronize()
+        table = box["counts_all_host"].view(W, S, W)                      # [source][segment][destination]
+        n_recv = [int(table[:, s, self.rank].sum()) for s in range(S)]
+        if max(int(table[:, s, d].sum()) for s in range(S) for d in range(W)) > box["cap"]:
+            return None                                                    # the same decision on every rank: all see one table
+        ops.push(xh, sel, wts, self.per_rank, W, S)
+        self._barrier(box["flag"])                                        # every rank's rows have landed
+        home = None
+        if getattr(ops, "home", None):
+            ops.home_flip ^= 1
+            home = ops.home[ops.home_flip]
+        y_back = ops.buf.get("y_back")
+        for s in range(S):
+            recv = box["recv"][s][0][:n_recv[s]]
+            if home is not None:
+                if n_recv[s]:
+                    ops.expert_rows_payload(recv, hidden, workspace=box["ws"][s], home=home)
+            else:
+                if box["y"][s] is None:
+                    box["y"][s] = torch.empty((box["cap"], hidden), dtype=torch.bfloat16, device=x.device)
+                y_seg = box["y"][s][:n_recv[s]]
+                if n_recv[s]:
+                    ops.expert_rows_payload(recv, hidden, out=y_seg, workspace=box["ws"][s])
+                off = int(table[self.rank, :s, :].sum())
+                n_send = int(table[self.rank, s, :].sum())
+                self._all_to_all(y_back[off:off + n_send], y_seg, table[self.rank, s, :].tolist(), table[:, s, self.rank].tolist())
+            mark(f"segment{s}_wait_and_gemm")
+        if home is not None:
+            self._barrier(ops.home_flag)                                  # every rank's GEMMs have stored their rows
+            out = ops.combine(home[0], y_shared, k)
+        else:
+            out = ops.combine(y_back, y_shared, k, routed_rows=inverse)
+        mark("return_wait_and_combine")
+        if self.timings is not None:
+            self.timings["pairs_received"] = n_recv
+        return out
+
+    def _barrier(self, flag):
+        try:
+            dist.all_reduce(flag, group=self.group)
+        except Exception as exc:
+            raise ExchangeError(ERR_TIMEOUT, str(exc).splitlines()[0] if str(exc) else type(exc).__name__) from exc
 
     def _exchange_counts(self, counts_in, counts):
         """counts is [segments][world]; rank r must receive entry [s][me] of every rank r' as its [s][r']."""

@@ -68,6 +68,8 @@ def _load():
     lib.yvex_b200_ep_payload_pitch.restype = u64
     lib.yvex_b200_ep_payload_pitch.argtypes = [u64]
     lib.yvex_b200_ep_dispatch_payload.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, u64, vp, vp, vp, vp, u64, vp, vp]
+    lib.yvex_b200_ep_dispatch_plan.argtypes = [vp, u64, u64, u64, u64, u64, vp, vp, vp, u64, vp, vp]
+    lib.yvex_b200_ep_dispatch_push.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, u64, vp, vp, u64, vp, u64, vp, vp]
     lib.yvex_b200_moe_expert_rows_scatter.argtypes = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights), vp, u64, vp, u64, u64, vp, u64,
                                                       vp, vp]
     lib.yvex_b200_moe_expert_rows_payload.argtypes = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights), vp, u64, vp, vp, u64, vp, vp]
@@ -118,7 +120,7 @@ EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_ge
            "yvex_b200_ep_payload_pitch", "yvex_b200_ep_dispatch_payload", "yvex_b200_moe_expert_rows_payload",
            "yvex_b200_moe_wide_set_cta_limit", "yvex_b200_moe_decode_parts", "yvex_b200_moe_wide_parts",
            "yvex_b200_dequant_gather", "yvex_b200_q8k_round_trip", "yvex_b200_concat_bf16",
-           "yvex_b200_moe_expert_rows_scatter"]
+           "yvex_b200_moe_expert_rows_scatter", "yvex_b200_ep_dispatch_plan", "yvex_b200_ep_dispatch_push"]
 
 
 def _torch():
@@ -330,6 +332,25 @@ def ep_dispatch_payload(rows_f16, selected, route_weights, experts_per_rank, wor
                                              experts_per_rank, world, rank, segments, _p(payload), _p(inverse), _p(counts), _p(workspace),
                                              workspace.numel(), _p(status.word), _stream()), "ep_dispatch_payload")
     return payload, inverse, counts
+
+
+def ep_dispatch_plan(selected, experts_per_rank, world, segments, status, inverse, counts, workspace):
+    """Groups the pairs by (segment, destination rank): inverse [T*k] int32, counts [segments * world] int64; the plan stays in
+    `workspace` for ep_dispatch_push."""
+    tokens, topk = selected.shape
+    _check(lib.yvex_b200_ep_dispatch_plan(_p(selected), tokens, topk, experts_per_rank, world, segments, _p(inverse), _p(counts),
+                                          _p(workspace), workspace.numel(), _p(status.word), _stream()), "ep_dispatch_plan")
+    return inverse, counts
+
+
+def ep_dispatch_push(rows_f16, selected, route_weights, experts_per_rank, world, rank, segments, counts_all, recv_bases,
+                     capacity_rows, status, workspace):
+    """Writes every payload row straight into its destination rank's receive buffer (recv_bases: int64 device tensor, one
+    byte address per bin; counts_all: int64 device tensor [world, segments * world])."""
+    tokens, hidden = rows_f16.shape
+    _check(lib.yvex_b200_ep_dispatch_push(_p(selected), _p(route_weights), _p(rows_f16), tokens, selected.shape[1], hidden,
+                                          experts_per_rank, world, rank, segments, _p(counts_all), _p(recv_bases), capacity_rows,
+                                          _p(workspace), workspace.numel(), _p(status.word), _stream()), "ep_dispatch_push")
 
 
 def moe_expert_rows_scatter(geom, weights, payload, home_bases, home_pairs, status, workspace=None):
