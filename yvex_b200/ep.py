@@ -2,28 +2,33 @@
 
 Routed experts are sharded in contiguous blocks (expert e lives on rank e // (E / world)); the
 router, the shared expert and the tokens' home ranks are replicated / sharded by token. One
-layer is: route locally -> all-to-all-v dispatch of the bf16-exact token rows (as fp16, each with
-a 16-byte trailer naming its local expert and route weight) -> grouped dequant GEMMs on the
-receiving rank -> all-to-all-v of the per-pair bf16 rows back -> the home rank sums its k rows in
-rank order (f32) + its shared row -> bf16. Because per-pair rows (not partial sums) travel, the
-result is bit-identical to the single-device layer. The reference has no multi-device path at all
-(single process, one GPU); per-pair semantics are those of its CPU path
-(src/graph/moe.c:587-622, src/runtime/moe.c:619-632).
+layer is: route locally -> every pair's bf16-exact token row (as fp16, with a 16-byte trailer naming
+its local expert, route weight, home pair and home rank) reaches its expert's rank -> grouped dequant
+GEMMs there -> the per-pair bf16 rows reach their home rank -> it sums its k rows in rank order
+(f32) + its shared row -> bf16. Because per-pair rows (not partial sums) travel, the result is
+bit-identical to the single-device layer. The reference has no multi-device path at all (single
+process, one GPU); per-pair semantics are those of its CPU path (src/graph/moe.c:587-622,
+src/runtime/moe.c:619-632).
+
+How rows travel. On GPUs whose memory can be mapped into each other (symmetric memory), both
+movements are fused into the kernels beside them and use plain peer stores over NVLink: the dispatch
+kernel writes every record straight into the expert rank's receive buffer (offsets from an
+all-gather of the counts), and the down GEMM's epilogue writes every result row straight into its
+home rank's buffer; two one-element all-reduces serve as barriers and no row goes through a
+collective (`DeviceOps(peer_dispatch=True, peer_return=True)`, the default). Either movement, or
+both, can instead be an all-to-all-v (`False`, or no peer access, or a receive buffer that would
+overflow in this step: the all-gathered table is the same on every rank, so all take the same path).
+The exchange-based step can be pipelined: with `segments` > 1 and `DeviceOps(overlap=True)` a rank's
+local experts are cut into equal ranges whose rows travel on a communication stream while the GEMMs of
+the previous range run (cutting by EXPERT keeps every expert's rows together, so tiles stay full).
 
 Order of a step. The shared expert needs no exchange: its GEMMs are enqueued first and cover the one
-host read of the split sizes and most of the dispatch. All per-step buffers are allocated once and
-reused. Optionally (`segments` > 1, `DeviceOps(overlap=True)`) a rank's local experts are cut into
-equal ranges and the pairs travel range by range on a communication stream while the GEMMs of the
-previous range run on the compute stream; cutting by EXPERT keeps every expert's rows together, so
-the GEMM tiles stay as full as without the pipeline. Measured on two B200s at the config-5 size the
-pipeline hides the exchange but loses more in the GEMMs (three smaller launch sets, SMs left to the
-exchange kernels, which slow the GEMM they run beside): 14.9 ms against 14.3 ms per step, so the
-default is one range on one stream.
+host read of the counts. All per-step buffers are allocated once and reused.
 
-Collectives go through torch.distributed (NCCL over NVLink on GPUs, gloo in the CPU tests); the
-compute calls go through the C-ABI of libyvex_b200.so (`DeviceOps`). The host logic takes the ops
-as a parameter so the world_size-2 gloo tests can drive it without a GPU (`TorchOps` is the plain
-tensor formulation of every step; `DeviceOps` replaces each with a library call).
+Collectives go through torch.distributed (NCCL on GPUs, gloo in the CPU tests); the compute calls go
+through the C-ABI of libyvex_b200.so (`DeviceOps`). The host logic takes the ops as a parameter so the
+world_size-2 gloo tests can drive it without a GPU (`TorchOps` is the plain tensor formulation of
+every step; `DeviceOps` replaces each with a library call).
 """
 from __future__ import annotations
 
