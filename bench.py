@@ -32,8 +32,8 @@ UNIT = "tokens/s"
 # DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum, one capture per workload).
 TRAFFIC = {"c1": 4389376, "c2": 22777600, "c4": 2160352104,
-           "c3_gate_up_gemm": 462726912, "c3_down_gemm": 365073920,
-           "c5_gate_up_gemm": 13417347840, "c5_down_gemm": 4945628416}
+           "c3_gate_up_gemm": 361532672, "c3_down_gemm": 367173120,
+           "c5_gate_up_gemm": 10006566912, "c5_down_gemm": 5925237760}
 
 
 def measured_peaks():
