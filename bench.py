@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the quantized MoE hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference] [--workload c2|c3|c5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference] [--workload c1|c2|c3|c4|c5]
 
 One "step" is one pass of the MoE FFN layer over one batch of synthetic tokens. Prints ONE JSON
 line (rank 0). `value` is device-timed throughput with inputs resident in HBM; `e2e` is the same
@@ -9,6 +9,10 @@ metric through the host-buffer call (pinned host rows in, host rows out, copies 
 region). L2 is flushed between timed steps (a 256 MiB buffer is rewritten outside the timed
 region). `--impl reference` times the reference's own CPU implementation of the same layer on
 the host cores (the compiled reference when oracle/_ref is present, else the plain-C port).
+
+At N > 1 the expert-parallel layer runs with the library's defaults; for experiments the environment can
+turn its peer-memory paths off (YVEX_EP_PEER_DISPATCH=0, YVEX_EP_PEER_RETURN=0: rows then travel by NCCL
+all-to-all-v) and shape the exchange-based pipeline (YVEX_EP_SEGMENTS, YVEX_EP_OVERLAP=1, YVEX_EP_CTAS).
 """
 from __future__ import annotations
 

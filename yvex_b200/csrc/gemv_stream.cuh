@@ -651,8 +651,7 @@ inline int stream_launch_v(StreamParams &p, const StreamShape &sh, cudaStream_t 
 
 template <class Dec>
 inline int stream_launch_t(StreamParams &p, const StreamShape &sh, cudaStream_t stream) {
-    static const bool allow_breg = !getenv("YVEX_B200_STREAM_NO_BREG");
-    const bool breg = sh.units_per_slice == 1 && allow_breg;
+    const bool breg = sh.units_per_slice == 1;
     if (sh.groups == 2) return breg ? stream_launch_v<Dec, true, 2>(p, sh, stream) : stream_launch_v<Dec, false, 2>(p, sh, stream);
     return breg ? stream_launch_v<Dec, true, 1>(p, sh, stream) : stream_launch_v<Dec, false, 1>(p, sh, stream);
 }

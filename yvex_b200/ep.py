@@ -16,8 +16,9 @@ kernel writes every record straight into the expert rank's receive buffer (offse
 all-gather of the counts), and the down GEMM's epilogue writes every result row straight into its
 home rank's buffer; two one-element all-reduces serve as barriers and no row goes through a
 collective (`DeviceOps(peer_dispatch=True, peer_return=True)`, the default). Either movement, or
-both, can instead be an all-to-all-v (`False`, or no peer access, or a receive buffer that would
-overflow in this step: the all-gathered table is the same on every rank, so all take the same path).
+both, can instead be an all-to-all-v (`False`, or no peer access). The receive buffers hold the worst
+routing (every pair of every rank), so the push starts as soon as the counts are on the device, on a
+stream of its own beside the shared expert's GEMMs.
 The exchange-based step can be pipelined: with `segments` > 1 and `DeviceOps(overlap=True)` a rank's
 local experts are cut into equal ranges whose rows travel on a communication stream while the GEMMs of
 the previous range run (cutting by EXPERT keeps every expert's rows together, so tiles stay full).
@@ -177,13 +178,14 @@ class DeviceOps(TorchOps):
             return None
 
     def _inbox(self, pairs, pitch, world, segments, dev):
-        """Receive buffers every peer can store into, one per segment, of a fixed capacity (twice the balanced
-        load plus a quarter; a step that needs more takes the exchange instead), with their pair-list
-        workspaces, the per-bin addresses and the all-gathered counts. None when peer access cannot be set up."""
+        """Receive buffers every peer can store into, one per segment, each large enough for the worst routing
+        (every pair of every rank: the push then needs no decision from the host and can start as soon as the
+        counts are known on the device), with their pair-list workspaces, the per-bin addresses and the
+        all-gathered counts. None when peer access cannot be set up."""
         try:
             import torch.distributed._symmetric_memory as symm
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-            cap = max(2 * pairs // segments + pairs // (4 * segments), 1024)
+            cap = world * pairs
             bases = torch.empty(segments * world, dtype=torch.int64)
             recv = []
             for s in range(segments):
@@ -199,7 +201,8 @@ class DeviceOps(TorchOps):
                     "y": [None] * segments,
                     "counts_all": torch.empty(world * bins, dtype=torch.int64, device=dev),
                     "counts_all_host": torch.empty(world * bins, dtype=torch.int64).pin_memory(),
-                    "flag": torch.zeros(1, dtype=torch.float32, device=dev)}
+                    "flag": torch.zeros(1, dtype=torch.float32, device=dev),
+                    "stream": torch.cuda.Stream(device=dev, priority=-1)}
         except Exception as exc:
             import warnings
             warnings.warn(f"peer dispatch disabled: {type(exc).__name__}: {exc}")
@@ -322,10 +325,9 @@ class ExpertParallelLayer:
         sel, wts = ops.route(x, logits)                                   # [t, k] int32 / f32
         if W > 1 and getattr(ops, "inbox", None):
             out = self._forward_pushed(x, xh, sel, wts, mark)
-            if out is not None:
-                if marks:
-                    self.timings["marks"] = marks
-                return out, sel, wts
+            if marks:
+                self.timings["marks"] = marks
+            return out, sel, wts
         payload, inverse, counts = ops.dispatch(xh, sel, wts, self.per_rank, W, S)
         mark("route_plan")
         # split sizes: one tiny exchange and the step's only host read
@@ -423,8 +425,7 @@ class ExpertParallelLayer:
         """The step without a bulk collective: the dispatch kernel stores every row straight into its expert's rank
         (symmetric receive buffers), the down GEMM's epilogue stores every result straight into its home rank. What
         remains of NCCL is one all-gather of the counts and two one-element all-reduces used as barriers.
-        Returns None (nothing stored anywhere yet) when a receive buffer would overflow: the caller then runs
-        the exchange-based step."""
+        """
         k, ops, W, S = self.topk, self.ops, self.world, self.segments
         t, hidden = x.shape
         box, bins = ops.inbox, W * S
@@ -437,14 +438,20 @@ class ExpertParallelLayer:
         done = torch.cuda.Event()
         done.record()
         mark("route_plan")
-        y_shared = ops.shared_rows(xh)                                    # covers the host read of the counts
+        # the rows leave on a stream of their own, beside the shared expert's GEMMs, which also cover the host's
+        # read of the counts (the receive buffers hold the worst case, so nothing has to be decided first)
+        main, side = torch.cuda.current_stream(), box["stream"]
+        side.wait_event(done)
+        with torch.cuda.stream(side):
+            ops.push(xh, sel, wts, self.per_rank, W, S)
+            pushed = torch.cuda.Event()
+            pushed.record()
+        y_shared = ops.shared_rows(xh)
         mark("shared_expert")
         done.synchronize()
         table = box["counts_all_host"].view(W, S, W)                      # [source][segment][destination]
         n_recv = [int(table[:, s, self.rank].sum()) for s in range(S)]
-        if max(int(table[:, s, d].sum()) for s in range(S) for d in range(W)) > box["cap"]:
-            return None                                                    # the same decision on every rank: all see one table
-        ops.push(xh, sel, wts, self.per_rank, W, S)
+        main.wait_event(pushed)
         self._barrier(box["flag"])                                        # every rank's rows have landed
         home = None
         if getattr(ops, "home", None):
