@@ -251,6 +251,12 @@ int yvex_b200_moe_expert_rows_payload(const yvex_b200_moe_geometry *g, const yve
  * no multicast), rows of one bin ordered by source rank. A row that would land at or past capacity_rows
  * sets status 2 and is not stored. The receiver may read its buffers once every rank's push has finished
  * (any barrier).
+ * expert_major = 1 (needs segments == experts_per_rank, i.e. one bin per (local expert, destination), and ONE
+ * receive buffer per destination rank: recv_bases[bin] = that rank's buffer for every bin): the bins of a
+ * destination follow each other in local-expert order, so its rows arrive already sorted the way the grouped
+ * GEMM walks them; yvex_b200_moe_expert_rows_sorted then runs them where they lie (activation tiles fetched
+ * with the records' pitch, no count / sort / gather pass), storing the results at their home ranks like
+ * yvex_b200_moe_expert_rows_scatter. It refuses gate/up qtypes with a min term (YVEX_ERR_UNSUPPORTED).
  */
 int yvex_b200_ep_dispatch_plan(const int32_t *selected, uint64_t tokens, uint64_t topk, uint64_t experts_per_rank, uint64_t world,
                                uint64_t segments, int32_t *inverse, long long *send_counts, void *workspace, uint64_t workspace_bytes,
@@ -258,7 +264,11 @@ int yvex_b200_ep_dispatch_plan(const int32_t *selected, uint64_t tokens, uint64_
 int yvex_b200_ep_dispatch_push(const int32_t *selected, const float *weights, const void *rows_f16, uint64_t tokens, uint64_t topk,
                                uint64_t hidden, uint64_t experts_per_rank, uint64_t world, uint64_t rank, uint64_t segments,
                                const long long *counts_all, const unsigned long long *recv_bases, uint64_t capacity_rows,
-                               void *workspace, uint64_t workspace_bytes, int *status, void *stream);
+                               int expert_major, void *workspace, uint64_t workspace_bytes, int *status, void *stream);
+int yvex_b200_moe_expert_rows_sorted(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w, const void *payload,
+                                     uint64_t pairs, const long long *counts_all, uint64_t world, uint64_t rank,
+                                     const unsigned long long *home_bases, uint64_t home_pairs, void *workspace,
+                                     uint64_t workspace_bytes, int *status, void *stream);
 /*
  * The same GEMMs with the return exchange fused into the down projection: the epilogue stores every
  * pair's bf16 row straight into its HOME rank's buffer, at home_bases[home rank] + home pair * hidden * 2

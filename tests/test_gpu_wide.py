@@ -130,6 +130,43 @@ def test_expert_parallel_building_blocks_match_single_device_layer_bit_for_bit(L
     assert st.read() == 0 and torch.equal(out2.view(torch.int32), want.view(torch.int32))
 
 
+def test_rows_stored_by_address_and_bad_trailers_are_dropped(L):
+    """The down GEMM's epilogue stores every pair's row at home_bases[home rank] + home pair * hidden * 2 (here both
+    "ranks" are buffers of this device): equal to the rows the list-order entry returns; a trailer that names a rank or
+    a pair out of range sets status 2 and leaves its row unwritten."""
+    import torch
+    H, E, k, I, T = 512, 8, 2, 256, 150
+    spec = synth.MoELayerSpec(H, E, k, I, down_qtype=synth.Q2_K)
+    rng = np.random.default_rng(77)
+    x, logits = dev(rng.standard_normal((T, H)).astype(np.float32)), dev(rng.standard_normal((T, E)).astype(np.float32))
+    t = {kk: dev(v.reshape(-1)) for kk, v in synth.moe_weights(spec, 78).items()}
+    st = L.Status()
+    g, w = L.geometry_of(spec), L.weights_of(t)
+    xh = x.to(torch.bfloat16).to(torch.float16)
+    sel, wts, _ = L.moe_route(g, w, st, logits=logits)
+    payload, inverse, counts = L.ep_dispatch_payload(xh, sel, wts, E, 1, 1, st, rank=0)
+    want = L.moe_expert_rows_payload(g, w, payload, st)                     # rows in payload order
+    home = torch.zeros((2, T * k, H), dtype=torch.bfloat16, device="cuda")
+    bases = torch.tensor([home[0].data_ptr(), home[1].data_ptr()], dtype=torch.int64, device="cuda")
+    trailers = payload[:, 2 * H:].view(torch.int32)                        # {local expert, weight, home pair, home rank}
+    trailers[::2, 3] = 1                                                    # every other pair lives on "rank" 1
+    L.moe_expert_rows_scatter(g, w, payload, bases, T * k, st)
+    torch.cuda.synchronize()
+    assert st.read() == 0
+    pair = trailers[:, 2].long()
+    rank = trailers[:, 3].long()
+    got = home[rank, pair]
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert int((home.view(torch.int16) != 0).any(dim=2).sum()) == T * k    # nothing stored anywhere else
+    home.zero_()
+    trailers[0, 3] = 2                                                      # no such rank
+    trailers[1, 2] = T * k                                                  # no such pair
+    L.moe_expert_rows_scatter(g, w, payload, bases, T * k, st)
+    torch.cuda.synchronize()
+    assert st.read() == 2
+    assert int((home.view(torch.int16) != 0).any(dim=2).sum()) == T * k - 2
+
+
 def tokens_covering_all_experts(sel, count):
     """Indices of `count` rows of `sel` [T, k] chosen greedily so that every expert is selected by at least one."""
     sel = np.asarray(sel)

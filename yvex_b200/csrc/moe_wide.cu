@@ -337,10 +337,11 @@ static PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 }
 
 // Row-major fp16 [rows][width] -> boxes of [kBoxN rows][64 columns], 128-byte swizzle, zero fill.
-static int make_act_map(CUtensorMap *map, const __half *base, uint64_t rows, uint64_t width) {
+// (pitch_bytes: distance between rows when they are not packed, a multiple of 16; 0 = packed)
+static int make_act_map(CUtensorMap *map, const __half *base, uint64_t rows, uint64_t width, uint64_t pitch_bytes = 0) {
     auto fn = encode_fn();
     if (!fn) return ERR_BACKEND;
-    cuuint64_t dims[2] = {width, rows}, strides[1] = {width * 2};
+    cuuint64_t dims[2] = {width, rows}, strides[1] = {pitch_bytes ? pitch_bytes : width * 2};
     cuuint32_t box[2] = {kChunkK, kBoxN}, estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -428,6 +429,10 @@ bool moe_wide_gemm_eligible(const MoeGeom &g, const MoeWeights &w) {
 // pair in pw.y at row pw.pos_of_pair[pair] or, when y_list is given, in y_list at row `pair` (the
 // down GEMM's epilogue then stores through the permutation, so no separate unsort pass is needed).
 // rows_h: the fp16 source rows the list indexes.
+static int run_sorted_gemms(const MoeGeom &g, const MoeWeights &w, const PairWorkspace &pw, const __half *act, uint64_t act_pitch,
+                            uint64_t pairs, int *status, cudaStream_t s, uint16_t *y, const int *out_rows,
+                            const unsigned long long *out_addr);
+
 // home_bases (optional, device array of `home_world` addresses; rows_h then are payload rows with trailers):
 // the row of a pair is stored at home_bases[trailer.home_rank] + trailer.home_pair * hidden * 2 instead.
 static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorkspace &pw, const __half *rows_h, uint64_t pairs,
@@ -451,9 +456,21 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
     int rc = launch_status(4);
     if (rc != OK) return rc;
     mark_phase(2, s);
+    return run_sorted_gemms(g, w, pw, pw.act_h, 0, pairs, status, s, y_list ? y_list : pw.y, y_list ? pw.perm : nullptr,
+                            home_bases ? pw.dest : nullptr);
+}
 
+// The two grouped GEMMs over rows that already stand in expert-major order (`act`, `act_pitch` bytes apart,
+// 0 = packed), with pw.blocks / pw.blocks_down / pw.num_blocks / pw.weight_sorted (and pw.act_sums for an
+// affine gate/up qtype) prepared. Results: bf16 rows into y (through out_rows when given), or at out_addr.
+static int run_sorted_gemms(const MoeGeom &g, const MoeWeights &w, const PairWorkspace &pw, const __half *act, uint64_t act_pitch,
+                            uint64_t pairs, int *status, cudaStream_t s, uint16_t *y, const int *out_rows,
+                            const unsigned long long *out_addr) {
+    const Geometry gg = geometry_of(g.gate_qtype), dg = geometry_of(g.down_qtype);
+    const auto sum_group = [](unsigned q) { return q == Q_Q4_K ? 32 : q == Q_Q2_K ? 16 : 0; };
+    int rc;
     GemmMaps gu_maps, dn_maps;
-    if (make_act_map(&gu_maps.act, pw.act_h, pairs, g.hidden) != OK || make_act_map(&dn_maps.act, pw.mid_h, pairs, g.inter) != OK)
+    if (make_act_map(&gu_maps.act, act, pairs, g.hidden, act_pitch) != OK || make_act_map(&dn_maps.act, pw.mid_h, pairs, g.inter) != OK)
         return ERR_BACKEND;
     GemmParams gu{};
     gu.row_bytes = (uint32_t)(g.hidden / gg.elems * gg.bytes);
@@ -485,8 +502,8 @@ static int run_pair_list(const MoeGeom &g, const MoeWeights &w, const PairWorksp
         if (rc != OK) return rc;
     }
     dn.colblocks = pw.blocks_down; dn.num_colblocks = pw.num_blocks + 1;
-    dn.out_bf16 = y_list ? y_list : pw.y; dn.out_rows = y_list ? pw.perm : nullptr; dn.sums = pw.sums; dn.status = status;
-    dn.out_addr = home_bases ? pw.dest : nullptr;
+    dn.out_bf16 = y; dn.out_rows = out_rows; dn.sums = pw.sums; dn.status = status;
+    dn.out_addr = out_addr;
     rc = run_gemm(g.down_qtype, false, dn_maps, dn, s);
     if (rc != OK) return rc;
     mark_phase(4, s);
@@ -806,11 +823,53 @@ extern "C" uint64_t yvex_b200_ep_payload_pitch(uint64_t hidden) { return hidden 
 // Every rank knows how many rows every rank sends into every bin (counts_all[src][bin], all-gathered).
 // A bin's rows land in the destination rank's receive buffer grouped by source rank, ascending: this
 // rank writes behind the rows of the ranks below it.
-__global__ void ep_push_offsets_kernel(const long long *counts_all, int bins, int rank, long long *row_base) {
+// expert_major (bins = local expert * world + destination, one receive buffer per destination): the bins of
+// one destination follow each other in its buffer in local-expert order, so that the rows arrive already
+// sorted the way the grouped GEMM walks them.
+__global__ void ep_push_offsets_kernel(const long long *counts_all, int bins, int world, int rank, int expert_major,
+                                       long long *row_base) {
     for (int b = threadIdx.x; b < bins; b += blockDim.x) {
         long long off = 0;
         for (int r = 0; r < rank; ++r) off += counts_all[(size_t)r * bins + b];
+        if (expert_major)
+            for (int b2 = b % world; b2 < b; b2 += world)
+                for (int r = 0; r < world; ++r) off += counts_all[(size_t)r * bins + b2];
         row_base[b] = off;
+    }
+}
+
+// Receiver of an expert-major push: rows of local expert l = what every rank sent into bin l * world + rank.
+__global__ void ep_sorted_counts_kernel(const long long *counts_all, int world, int rank, int per_rank, uint64_t pairs, int *counts,
+                                        int *status) {
+    __shared__ long long total;
+    if (threadIdx.x == 0) total = 0;
+    __syncthreads();
+    const int bins = per_rank * world;
+    for (int l = threadIdx.x; l <= per_rank; l += blockDim.x) {
+        long long n = 0;
+        if (l < per_rank)
+            for (int r = 0; r < world; ++r) n += counts_all[(size_t)r * bins + (size_t)l * world + rank];
+        counts[l] = (int)n;                                  // bin per_rank is the shared expert: none here
+        atomicAdd(reinterpret_cast<unsigned long long *>(&total), (unsigned long long)n);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && (uint64_t)total != pairs) raise(status, YVEX_B200_STATUS_ARGUMENT);
+}
+
+// Sorted rows' route weights and result addresses from their trailers; a trailer that names another expert
+// than the group its row stands in, a rank or a pair out of range sets status 2 and its row is dropped.
+__global__ void wide_trailer_kernel(const uint8_t *payload, uint64_t pitch, uint64_t hidden, uint64_t pairs, const int *offsets,
+                                    int experts, const unsigned long long *home_bases, int home_world, uint64_t home_pairs,
+                                    float *weight_sorted, unsigned long long *dest, int *status) {
+    for (uint64_t pos = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; pos < pairs; pos += (uint64_t)gridDim.x * blockDim.x) {
+        const EpTrailer t = *reinterpret_cast<const EpTrailer *>(payload + pos * pitch + hidden * 2);
+        int lo = 0, hi = experts;                            // group of pos: offsets[lo] <= pos < offsets[lo + 1]
+        while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if ((uint64_t)offsets[mid] <= pos) lo = mid; else hi = mid; }
+        const bool ok = t.local_expert == lo && t.home_rank >= 0 && t.home_rank < home_world && t.home_pair >= 0 &&
+                        (uint64_t)t.home_pair < home_pairs && isfinite(t.weight);
+        if (!ok) raise(status, YVEX_B200_STATUS_ARGUMENT);
+        weight_sorted[pos] = ok ? t.weight : 0.0f;
+        dest[pos] = ok ? home_bases[t.home_rank] + (unsigned long long)t.home_pair * hidden * 2ull : 0ull;
     }
 }
 
@@ -888,7 +947,8 @@ extern "C" int yvex_b200_ep_dispatch_plan(const int32_t *selected, uint64_t toke
 extern "C" int yvex_b200_ep_dispatch_push(const int32_t *selected, const float *weights, const void *rows_f16, uint64_t tokens,
                                           uint64_t topk, uint64_t hidden, uint64_t experts_per_rank, uint64_t world, uint64_t rank,
                                           uint64_t segments, const long long *counts_all, const unsigned long long *recv_bases,
-                                          uint64_t capacity_rows, void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
+                                          uint64_t capacity_rows, int expert_major, void *workspace, uint64_t workspace_bytes,
+                                          int *status, void *stream) {
     if (!selected || !weights || !rows_f16 || !counts_all || !recv_bases || !status || !workspace) return ERR_INVALID_ARG;
     if (!tokens || !topk || !experts_per_rank || !world || rank >= world || !segments || world * segments > 1024 ||
         segments > experts_per_rank || hidden % 8 || !capacity_rows)
@@ -901,7 +961,8 @@ extern "C" int yvex_b200_ep_dispatch_push(const int32_t *selected, const float *
     int *counts = order + pairs, *offsets = counts + bins + 1;
     long long *row_base = reinterpret_cast<long long *>((reinterpret_cast<uintptr_t>(offsets + bins + 2) + 7u) & ~uintptr_t(7));
     cudaStream_t s = as_stream(stream);
-    ep_push_offsets_kernel<<<1, 256, 0, s>>>(counts_all, (int)bins, (int)rank, row_base);
+    if (expert_major && segments != experts_per_rank) return ERR_INVALID_ARG;
+    ep_push_offsets_kernel<<<1, 256, 0, s>>>(counts_all, (int)bins, (int)world, (int)rank, expert_major, row_base);
     ep_push_kernel<<<grid_for(pairs, 1, 16), 128, 0, s>>>(static_cast<const __half *>(rows_f16), selected, weights, order, bin_of, src,
                                                           offsets, row_base, recv_bases, capacity_rows, pairs, hidden,
                                                           (int)experts_per_rank, (int)rank, yvex_b200_ep_payload_pitch(hidden), status);
@@ -956,6 +1017,40 @@ extern "C" int yvex_b200_moe_expert_rows_scatter(const yvex_b200_moe_geometry *g
     mark_phase(1, s);
     rc = run_pair_list(g, *w, pw, static_cast<const __half *>(payload), pairs, status, s, nullptr, pitch, home_bases, (int)world,
                        home_pairs);
+    if (rc != OK) return rc;
+    mark_phase(5, s);
+    return launch_status(1);
+}
+
+extern "C" int yvex_b200_moe_expert_rows_sorted(const yvex_b200_moe_geometry *geom, const yvex_b200_moe_weights *w,
+                                                const void *payload, uint64_t pairs, const long long *counts_all, uint64_t world,
+                                                uint64_t rank, const unsigned long long *home_bases, uint64_t home_pairs,
+                                                void *workspace, uint64_t workspace_bytes, int *status, void *stream) {
+    int rc = moe_check_geometry(geom, w);
+    if (rc != OK) return rc;
+    if (!pairs) return OK;
+    if (!payload || !counts_all || !home_bases || !status || !world || world > 1024 || rank >= world || !home_pairs) return ERR_INVALID_ARG;
+    if (pairs > 0x7fffff00ull / 2 || home_pairs > 0x7fffff00ull || (reinterpret_cast<uintptr_t>(payload) & 15u)) return ERR_BOUNDS;
+    MoeGeom g = *geom;
+    // the activation sums an affine gate/up qtype needs are made by the gather this path does without
+    if (!moe_wide_gemm_eligible(g, *w) || g.gate_qtype == Q_Q4_K || g.gate_qtype == Q_Q2_K) return ERR_UNSUPPORTED;
+    PairWorkspace pw;
+    if (!workspace || workspace_bytes < pair_layout(g, pairs, 0, &pw)) return ERR_NOMEM;
+    pw.rebase(workspace);
+    cudaStream_t s = as_stream(stream);
+    const uint64_t pitch = yvex_b200_ep_payload_pitch(g.hidden);
+    mark_phase(0, s);
+    ep_sorted_counts_kernel<<<1, 256, 0, s>>>(counts_all, (int)world, (int)rank, (int)g.experts, pairs, pw.counts, status);
+    wide_plan_kernel<<<2, 32, 0, s>>>(pw.counts, (int)g.experts, pairs, pw.offsets, pw.blocks, pw.blocks_down, pw.num_blocks,
+                                      pw.max_blocks, gemm_tile_n(g.gate_qtype), gemm_tile_n(g.down_qtype), status);
+    wide_trailer_kernel<<<grid_for(pairs, 256, 4), 256, 0, s>>>(static_cast<const uint8_t *>(payload), pitch, g.hidden, pairs, pw.offsets,
+                                                              (int)g.experts, home_bases, (int)world, home_pairs, pw.weight_sorted,
+                                                              pw.dest, status);
+    rc = launch_status(3);
+    if (rc != OK) return rc;
+    mark_phase(1, s);
+    mark_phase(2, s);
+    rc = run_sorted_gemms(g, *w, pw, static_cast<const __half *>(payload), pitch, pairs, status, s, nullptr, nullptr, pw.dest);
     if (rc != OK) return rc;
     mark_phase(5, s);
     return launch_status(1);

@@ -186,16 +186,23 @@ class DeviceOps(TorchOps):
             import torch.distributed._symmetric_memory as symm
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
             cap = world * pairs
-            bases = torch.empty(segments * world, dtype=torch.int64)
+            # with both peer paths, one range and gate/up weights without a min term the rows can be pushed straight
+            # into expert-major order (one bin per (local expert, destination)): the receiver then sorts nothing
+            per = int(self.geom_local.experts)
+            ordered = segments == 1 and self.home is not None and int(self.geom_local.gate_qtype) not in (10, 12) and per * world <= 1024
+            bins = world * (per if ordered else segments)
+            bases = torch.empty(bins, dtype=torch.int64)
             recv = []
             for s in range(segments):
                 t = symm.empty(cap * pitch, dtype=torch.uint8, device=dev)
                 hdl = symm.rendezvous(t, dist.group.WORLD)
-                for d in range(world):
-                    bases[s * world + d] = int(hdl.buffer_ptrs[d])
+                for b in range(bins) if ordered else range(s * world, (s + 1) * world):
+                    bases[b] = int(hdl.buffer_ptrs[b % world])
                 recv.append((t.view(cap, pitch), hdl))
-            bins = world * segments
-            return {"cap": cap, "recv": recv, "bases": bases.to(dev),
+            return {"cap": cap, "recv": recv, "bases": bases.to(dev), "ordered": ordered, "bin_segments": per if ordered else segments,
+                    "counts": torch.empty(bins, dtype=torch.int64, device=dev),
+                    "plan_ws": torch.empty(int(self.lib.lib.yvex_b200_ep_dispatch_workspace_bytes(pairs, bins)), dtype=torch.uint8,
+                                           device=dev),
                     "ws": [torch.empty(int(self.lib.lib.yvex_b200_moe_expert_rows_workspace_bytes(self.geom_local, cap)),
                                        dtype=torch.uint8, device=dev) for _ in range(segments)],
                     "y": [None] * segments,
@@ -209,13 +216,14 @@ class DeviceOps(TorchOps):
             return None
 
     def plan(self, sel, per_rank, world, segments):
-        b = self.buf
-        return self.lib.ep_dispatch_plan(sel.contiguous(), per_rank, world, segments, self.status, b["inverse"], b["counts"], b["plan_ws"])
+        box = self.inbox
+        return self.lib.ep_dispatch_plan(sel.contiguous(), per_rank, world, box["bin_segments"], self.status, self.buf["inverse"],
+                                         box["counts"], box["plan_ws"])
 
     def push(self, xh, sel, wts, per_rank, world, segments):
         box = self.inbox
-        self.lib.ep_dispatch_push(xh, sel.contiguous(), wts.contiguous(), per_rank, world, self.rank, segments, box["counts_all"],
-                                  box["bases"], box["cap"], self.status, self.buf["plan_ws"])
+        self.lib.ep_dispatch_push(xh, sel.contiguous(), wts.contiguous(), per_rank, world, self.rank, box["bin_segments"],
+                                  box["counts_all"], box["bases"], box["cap"], self.status, box["plan_ws"], expert_major=box["ordered"])
 
     def segment_buffers(self, seg, rows):
         """Receive records, result rows and pair-list workspace of one segment, grown when a step needs more."""
@@ -254,7 +262,11 @@ class DeviceOps(TorchOps):
         b = self.buf
         return self.expert_rows(xh, b["shared_ids"], b["shared_w"], workspace=b["shared_ws"], out=b["y_shared"])
 
-    def expert_rows_payload(self, payload, hidden, out=None, workspace=None, home=None):
+    def expert_rows_payload(self, payload, hidden, out=None, workspace=None, home=None, ordered=None):
+        if ordered is not None:                # the records already stand in expert-major order: (counts_all, world)
+            self.lib.moe_expert_rows_sorted(self.geom_local, self.weights, payload, ordered[0], ordered[1], self.rank, home[1],
+                                            home[0].shape[0], self.status, workspace)
+            return None
         if home is not None:                   # (rows [pairs, hidden], bases): store every row at its home rank
             self.lib.moe_expert_rows_scatter(self.geom_local, self.weights, payload, home[1], home[0].shape[0], self.status,
                                              workspace=workspace)
@@ -449,8 +461,11 @@ class ExpertParallelLayer:
         y_shared = ops.shared_rows(xh)
         mark("shared_expert")
         done.synchronize()
-        table = box["counts_all_host"].view(W, S, W)                      # [source][segment][destination]
-        n_recv = [int(table[:, s, self.rank].sum()) for s in range(S)]
+        table = box["counts_all_host"].view(W, box["bin_segments"], W)   # [source][segment or local expert][destination]
+        if box["ordered"]:
+            n_recv = [int(table[:, :, self.rank].sum())]
+        else:
+            n_recv = [int(table[:, s, self.rank].sum()) for s in range(S)]
         main.wait_event(pushed)
         self._barrier(box["flag"])                                        # every rank's rows have landed
         home = None
@@ -460,7 +475,10 @@ class ExpertParallelLayer:
         y_back = ops.buf.get("y_back")
         for s in range(S):
             recv = box["recv"][s][0][:n_recv[s]]
-            if home is not None:
+            if box["ordered"]:
+                if n_recv[s]:
+                    ops.expert_rows_payload(recv, hidden, workspace=box["ws"][s], home=home, ordered=(box["counts_all"], W))
+            elif home is not None:
                 if n_recv[s]:
                     ops.expert_rows_payload(recv, hidden, workspace=box["ws"][s], home=home)
             else:

@@ -69,7 +69,9 @@ def _load():
     lib.yvex_b200_ep_payload_pitch.argtypes = [u64]
     lib.yvex_b200_ep_dispatch_payload.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, u64, vp, vp, vp, vp, u64, vp, vp]
     lib.yvex_b200_ep_dispatch_plan.argtypes = [vp, u64, u64, u64, u64, u64, vp, vp, vp, u64, vp, vp]
-    lib.yvex_b200_ep_dispatch_push.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, u64, vp, vp, u64, vp, u64, vp, vp]
+    lib.yvex_b200_ep_dispatch_push.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, u64, vp, vp, u64, C.c_int, vp, u64, vp, vp]
+    lib.yvex_b200_moe_expert_rows_sorted.argtypes = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights), vp, u64, vp, u64, u64, vp, u64,
+                                                     vp, u64, vp, vp]
     lib.yvex_b200_moe_expert_rows_scatter.argtypes = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights), vp, u64, vp, u64, u64, vp, u64,
                                                       vp, vp]
     lib.yvex_b200_moe_expert_rows_payload.argtypes = [C.POINTER(MoeGeometry), C.POINTER(MoeWeights), vp, u64, vp, vp, u64, vp, vp]
@@ -120,7 +122,8 @@ EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_ge
            "yvex_b200_ep_payload_pitch", "yvex_b200_ep_dispatch_payload", "yvex_b200_moe_expert_rows_payload",
            "yvex_b200_moe_wide_set_cta_limit", "yvex_b200_moe_decode_parts", "yvex_b200_moe_wide_parts",
            "yvex_b200_dequant_gather", "yvex_b200_q8k_round_trip", "yvex_b200_concat_bf16",
-           "yvex_b200_moe_expert_rows_scatter", "yvex_b200_ep_dispatch_plan", "yvex_b200_ep_dispatch_push"]
+           "yvex_b200_moe_expert_rows_scatter", "yvex_b200_ep_dispatch_plan", "yvex_b200_ep_dispatch_push",
+           "yvex_b200_moe_expert_rows_sorted"]
 
 
 def _torch():
@@ -344,13 +347,25 @@ def ep_dispatch_plan(selected, experts_per_rank, world, segments, status, invers
 
 
 def ep_dispatch_push(rows_f16, selected, route_weights, experts_per_rank, world, rank, segments, counts_all, recv_bases,
-                     capacity_rows, status, workspace):
+                     capacity_rows, status, workspace, expert_major=False):
     """Writes every payload row straight into its destination rank's receive buffer (recv_bases: int64 device tensor, one
-    byte address per bin; counts_all: int64 device tensor [world, segments * world])."""
+    byte address per bin; counts_all: int64 device tensor [world, segments * world]). expert_major (segments ==
+    experts_per_rank, one buffer per destination): the rows land sorted by local expert."""
     tokens, hidden = rows_f16.shape
     _check(lib.yvex_b200_ep_dispatch_push(_p(selected), _p(route_weights), _p(rows_f16), tokens, selected.shape[1], hidden,
                                           experts_per_rank, world, rank, segments, _p(counts_all), _p(recv_bases), capacity_rows,
-                                          _p(workspace), workspace.numel(), _p(status.word), _stream()), "ep_dispatch_push")
+                                          1 if expert_major else 0, _p(workspace), workspace.numel(), _p(status.word), _stream()),
+           "ep_dispatch_push")
+
+
+def moe_expert_rows_sorted(geom, weights, payload, counts_all, world, rank, home_bases, home_pairs, status, workspace):
+    """Grouped GEMMs on records that an expert-major push left sorted by local expert; results stored at their home ranks."""
+    pairs = payload.shape[0]
+    if pairs == 0:
+        return
+    _check(lib.yvex_b200_moe_expert_rows_sorted(C.byref(geom), C.byref(weights), _p(payload), pairs, _p(counts_all), world, rank,
+                                                _p(home_bases), home_pairs, _p(workspace), workspace.numel(), _p(status.word),
+                                                _stream()), "moe_expert_rows_sorted")
 
 
 def moe_expert_rows_scatter(geom, weights, payload, home_bases, home_pairs, status, workspace=None):
