@@ -125,7 +125,8 @@ def test_gemv_vs_frozen_reference(L, golden, port, name):
 @pytest.mark.parametrize("qtype,rows,width", [(synth.IQ2_XXS, 4096, 4096), (synth.IQ2_XXS, 1, 256),
                                               (synth.IQ2_XXS, 13, 7168), (synth.IQ2_XXS, 100, 1536),
                                               (synth.Q4_K, 257, 1536), (synth.Q4_K, 64, 2048),
-                                              (synth.Q8_0, 300, 4096), (synth.Q2_K, 129, 2048),
+                                              (synth.Q8_0, 300, 4096), (synth.Q2_K, 129, 2048), (synth.Q2_K, 4096, 4096),
+                                              (synth.Q2_K, 13, 7168), (synth.Q2_K, 100, 1536), (synth.Q2_K, 1, 256),
                                               (synth.Q8_0, 4096, 4096), (synth.Q8_0, 37, 1280), (synth.Q8_0, 5, 256),
                                               (synth.Q8_0, 3000, 7168)])
 def test_gemv_vs_oracle_shapes(L, port, qtype, rows, width):
@@ -185,7 +186,8 @@ def test_gemv_input_rows_additive_and_bf16(L, port, qtype):
 
 
 @pytest.mark.parametrize("qtype,count,rows,width", [(synth.IQ2_XXS, 5, 300, 4096), (synth.Q4_K, 3, 77, 1536), (synth.Q8_0, 4, 33, 2048),
-                                                    (synth.IQ2_XXS, 40, 16, 256), (synth.Q2_K, 3, 20, 512)])
+                                                    (synth.IQ2_XXS, 40, 16, 256), (synth.Q2_K, 3, 20, 512), (synth.Q2_K, 6, 300, 2048),
+                                                    (synth.MXFP4, 2, 20, 512)])
 def test_gemv_batch_vs_oracle(L, port, qtype, count, rows, width):
     """Independent matrices with their own input rows in one launch (ragged tiles, tiles of different
     matrices inside one CTA's task range, a qtype that falls back to one matvec per matrix)."""

@@ -125,7 +125,8 @@ __device__ __forceinline__ float comb(int a_hi, int a_lo, int b_hi, int b_lo) {
 struct StreamIq2 {
     static constexpr unsigned kQtype = Q_IQ2_XXS;
     static constexpr int kBlockBytes = 66, kBlockK = 256;
-    static constexpr bool kTables = true, kSums = false;
+    static constexpr bool kTables = true;
+    static constexpr int kSumGroup = 0;                  // activation sums over this many values (0: none needed)
 
     __device__ __forceinline__ static void group(uint32_t a, uint32_t &grids, uint32_t &ss) {
         // a group starts on a 2-byte boundary: three aligned words, funnel-shifted when it sits mid-word
@@ -189,7 +190,8 @@ struct StreamIq2 {
 struct StreamQ4k {
     static constexpr unsigned kQtype = Q_Q4_K;
     static constexpr int kBlockBytes = 144, kBlockK = 256;
-    static constexpr bool kTables = false, kSums = true;
+    static constexpr bool kTables = false;
+    static constexpr int kSumGroup = 32;
 
     // 6-bit (scale, min) of sub-block j from the 12 packed bytes behind d and dmin (three aligned words)
     __device__ __forceinline__ static void scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int h, int t, uint32_t &sc, uint32_t &m) {
@@ -246,12 +248,69 @@ struct StreamQ4k {
     }
 };
 
+// Q2_K (src/gguf/quant_block.c:769-817): 84 bytes = 16 bytes of (4-bit scale | 4-bit min << 4) per 16-weight
+// sub-block, 64 bytes of 2-bit codes, f16 d, f16 dmin. Weight k = 128 h + 32 p + i (i < 32) is
+// (q[32 h + i] >> 2 p) & 3 of sub-block 8 h + 2 p + (i >= 16): value = d * sc * code - dmin * m.
+// Lane t of half h owns plane p = t, i.e. K indices 128 h + 32 t .. + 31: the same 32 code bytes for all four
+// lanes, shifted by 2 t. Its two sub-blocks have different scales, so the codes are multiplied by their scale
+// BEFORE the MMA (4 codes per word at once: 3 * 15 = 45 fits a byte); the group sum then needs no factor.
+// Blocks are only 4-byte aligned, hence the word loads.
+struct StreamQ2k {
+    static constexpr unsigned kQtype = Q_Q2_K;
+    static constexpr int kBlockBytes = 84, kBlockK = 256;
+    static constexpr bool kTables = false;
+    static constexpr int kSumGroup = 16;
+
+    template <int H, int J> __device__ __forceinline__ static void step(const uint32_t (&w0)[8], const uint32_t (&w1)[8], int shift,
+                                                                        uint32_t sc0, uint32_t sc1, const BUnit &b, int (&ca)[4],
+                                                                        int (&cb)[4]) {
+        uint32_t a[4];
+        a[0] = ((w0[2 * J] >> shift) & 0x03030303u) * sc0; a[2] = ((w0[2 * J + 1] >> shift) & 0x03030303u) * sc0;
+        a[1] = ((w1[2 * J] >> shift) & 0x03030303u) * sc1; a[3] = ((w1[2 * J + 1] >> shift) & 0x03030303u) * sc1;
+        mma_s8<J == 0>(ca, a, b.bh[4 * H + J].x, b.bh[4 * H + J].y);
+        mma_s8<J == 0>(cb, a, b.bl[4 * H + J].x, b.bl[4 * H + J].y);
+    }
+    template <int H> __device__ __forceinline__ static void half(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t sums,
+                                                                 float &blk0, float &blk1, float &min0, float &min1) {
+        uint32_t w0[8], w1[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { w0[i] = lds32(row0 + 16 + 32 * H + 4 * i); w1[i] = lds32(row1 + 16 + 32 * H + 4 * i); }
+        // scale bytes 8 H + 2 t and 8 H + 2 t + 1: a 16-bit field of word 2 H + (t >> 1)
+        const uint32_t s0 = lds32(row0 + 8 * H + 4 * (l.t >> 1)) >> (16 * (l.t & 1)), s1 = lds32(row1 + 8 * H + 4 * (l.t >> 1)) >> (16 * (l.t & 1));
+        const int shift = 2 * l.t;
+        int ca[4], cb[4];
+        step<H, 0>(w0, w1, shift, s0 & 15u, s1 & 15u, b, ca, cb);
+        step<H, 1>(w0, w1, shift, s0 & 15u, s1 & 15u, b, ca, cb);
+        step<H, 2>(w0, w1, shift, (s0 >> 8) & 15u, (s1 >> 8) & 15u, b, ca, cb);
+        step<H, 3>(w0, w1, shift, (s0 >> 8) & 15u, (s1 >> 8) & 15u, b, ca, cb);
+        const int sub = 8 * H + 2 * l.t;
+        const float xa = ldsf(sums + 4 * sub), xb = ldsf(sums + 4 * sub + 4);       // activation sums over the two sub-blocks
+        blk0 += comb(ca[0], ca[1], cb[0], cb[1]);
+        blk1 += comb(ca[2], ca[3], cb[2], cb[3]);
+        min0 = fmaf((float)((s0 >> 4) & 15u), xa, fmaf((float)((s0 >> 12) & 15u), xb, min0));
+        min1 = fmaf((float)((s1 >> 4) & 15u), xa, fmaf((float)((s1 >> 12) & 15u), xb, min1));
+    }
+    __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t sums,
+                                                float (&acc)[2], int &bad) {
+        float blk0 = 0.0f, blk1 = 0.0f, min0 = 0.0f, min1 = 0.0f;
+        half<0>(row0, row1, b, l, sums, blk0, blk1, min0, min1);
+        half<1>(row0, row1, b, l, sums, blk0, blk1, min0, min1);
+        const uint32_t h0 = lds32(row0 + 80), h1 = lds32(row1 + 80);                 // d, dmin
+        const float d0 = f16_bits_to_float((uint16_t)h0), n0 = f16_bits_to_float((uint16_t)(h0 >> 16));
+        const float d1 = f16_bits_to_float((uint16_t)h1), n1 = f16_bits_to_float((uint16_t)(h1 >> 16));
+        bad |= (scale_bad(d0) || scale_bad(n0) ? 1 : 0) | (scale_bad(d1) || scale_bad(n1) ? 2 : 0);
+        acc[0] += fmaf(d0, blk0, -n0 * min0);
+        acc[1] += fmaf(d1, blk1, -n1 * min1);
+    }
+};
+
 // Q8_0 (src/gguf/quant_block.c:819-833): 34 bytes = f16 d + 32 int8. A unit is eight blocks (256 weights);
 // lane t of half h owns block 4h + t, whose quants are the A operand as they are.
 struct StreamQ80 {
     static constexpr unsigned kQtype = Q_Q8_0;
     static constexpr int kBlockBytes = 8 * 34, kBlockK = 256;
-    static constexpr bool kTables = false, kSums = false;
+    static constexpr bool kTables = false;
+    static constexpr int kSumGroup = 0;
 
     __device__ __forceinline__ static void block(uint32_t a, uint32_t (&q)[8], float &d, int &bad, int flag) {
         // the block starts on a 2-byte boundary: nine aligned words, funnel-shifted when it sits mid-word
@@ -326,7 +385,7 @@ struct StreamCtl {
 };
 
 __host__ __device__ inline uint32_t stream_small_bytes(int K, int consumers, int depth, int units_per_slice, int groups) {
-    return (uint32_t)(4 * K + 256 * units_per_slice + 128 + (K / 32) * 4 + 128 + (depth + 1) * consumers * groups * kTileRows * 4 + 256);
+    return (uint32_t)(4 * K + 256 * units_per_slice + 128 + (K / 16) * 4 + 128 + (depth + 1) * consumers * groups * kTileRows * 4 + 256);
 }
 
 // The task list of one CTA, walked without divisions: tile `tile` of matrix `m`.
@@ -367,7 +426,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
         for (int i = 0; i < D; ++i) ctl.stage[i] = take(p.stage_bytes + 16);
         ctl.planes = take((uint32_t)(4 * p.K));
         ctl.zeros = take((uint32_t)(256 * p.units_per_slice + 16));
-        ctl.sums = take((uint32_t)(p.K / 32) * 4u);
+        ctl.sums = take((uint32_t)(p.K / 16) * 4u);
         ctl.red = take((uint32_t)((D + 1) * consumers * kGroupsPerWarp * kTileRows) * 4u);
         ctl.table = tab;
         ctl.layout_bad = cur > end || (Dec::kTables && tab + kTableBytes > end);
@@ -468,7 +527,8 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
     uint32_t b_lo = b_active ? ctl.planes + (uint32_t)((2 + col_plane) * p.K + unit0 * Dec::kBlockK + 32 * (lane >> 3)) : ctl.zeros;
     l.nib_base = (ctl.table & 0xffff0000u) | (uint32_t)(lane * 4);
     l.sgn_base = l.nib_base + 128u;
-    uint32_t sums = ctl.sums + (uint32_t)(unit0 * (Dec::kBlockK / 32) * 4);
+    constexpr int kSumsPerUnit = Dec::kSumGroup ? Dec::kBlockK / Dec::kSumGroup : 0;
+    uint32_t sums = ctl.sums + (uint32_t)(unit0 * kSumsPerUnit * 4);
     const uint32_t row_bytes = (uint32_t)p.row_bytes;
     float *red_all = reinterpret_cast<float *>(generic(ctl.red));
     const int cthreads = consumers * 32;
@@ -548,10 +608,13 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
 #pragma unroll
                 for (int pi = 0; pi < 4; ++pi)
                     *reinterpret_cast<uint2 *>(pl + (size_t)pi * p.K + 8 * k8) = make_uint2(d[pi][0], d[pi][1]);
-                if (Dec::kSums) {
+                if (Dec::kSumGroup == 32) {
                     s += __shfl_xor_sync(0xffffffffu, s, 1);
                     s += __shfl_xor_sync(0xffffffffu, s, 2);
                     if ((threadIdx.x & 3) == 0) sm[k8 >> 2] = s;
+                } else if (Dec::kSumGroup == 16) {
+                    s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    if ((threadIdx.x & 1) == 0) sm[k8 >> 1] = s;
                 }
             }
             asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
@@ -577,7 +640,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
                 for (int gi = 0; gi < kGroupsPerWarp; ++gi) {
                     // groups past a ragged tile's last row decode stale bytes; their results are never stored
                     const uint32_t r0 = base + (uint32_t)(kTileRows * gi) * row_bytes + (uint32_t)(u * Dec::kBlockBytes);
-                    Dec::unit(r0, r0 + 8 * row_bytes, b, l, sums + (uint32_t)(u * (Dec::kBlockK / 32) * 4), acc[gi], bad[gi]);
+                    Dec::unit(r0, r0 + 8 * row_bytes, b, l, sums + (uint32_t)(u * kSumsPerUnit * 4), acc[gi], bad[gi]);
                 }
             }
         }
@@ -628,7 +691,7 @@ inline bool stream_shape(uint64_t width, uint64_t row_bytes, bool tables, Stream
     return false;
 }
 
-inline bool stream_qtype(unsigned q) { return q == Q_IQ2_XXS || q == Q_Q4_K || q == Q_Q8_0; }
+inline bool stream_qtype(unsigned q) { return q == Q_IQ2_XXS || q == Q_Q4_K || q == Q_Q8_0 || q == Q_Q2_K; }
 
 inline bool stream_eligible(unsigned q, uint64_t rows, uint64_t width, uint64_t row_bytes, const void *enc, uint64_t matrix_stride,
                             uint64_t count, const float *x, uint64_t x_stride) {
@@ -673,6 +736,7 @@ inline int stream_launch(unsigned q, const uint8_t *enc, uint64_t matrix_stride,
     case Q_IQ2_XXS: return stream_launch_t<StreamIq2>(p, sh, stream);
     case Q_Q4_K: return stream_launch_t<StreamQ4k>(p, sh, stream);
     case Q_Q8_0: return stream_launch_t<StreamQ80>(p, sh, stream);
+    case Q_Q2_K: return stream_launch_t<StreamQ2k>(p, sh, stream);
     default: return ERR_UNSUPPORTED;
     }
 }
