@@ -757,7 +757,7 @@ def gemv_records(torch, lib, synth, dev, peaks, steps, warmup, status, gen):
         return {"GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"], "frac_of_8TBs": gbs / 8000.0, "ms": t * 1e3}
 
     for name, q, count in (("IQ2_XXS", synth.IQ2_XXS, 256), ("Q4_K", synth.Q4_K, 128), ("Q8_0", synth.Q8_0, 64),
-                           ("Q2_K", synth.Q2_K, 200)):
+                           ("Q2_K", synth.Q2_K, 200), ("MXFP4", synth.MXFP4, 128)):
         rb = synth.row_bytes(q, width)
         enc = device_blocks(torch, q, rows * count, width, gen, dev)
         xs = torch.randn((count, width), device=dev, generator=gen)

@@ -97,6 +97,19 @@ def test_mxfp4_decode_and_matvec(L, port):
     bad[3, 17] = 0xFF
     L.dequant_rows(synth.MXFP4, dev(bad), rows, width, st)
     assert st.read() == 1
+    st.reset()
+    L.gemv(synth.MXFP4, dev(bad), rows, width, dev(x), st)
+    assert st.read() == 1
+    # scale code 0 (2^-128, a subnormal) and negative zeros (code 8) in the streaming matvec
+    edge = w.copy()
+    edge[:, 0] = 0
+    edge[5, 1:17] = 0x88
+    edge[6, 17 * 3] = 200
+    _, dec = port.decode_rows(synth.MXFP4, edge, rows, width)
+    rc, y0 = port.matvec(synth.MXFP4, edge, rows, width, x, threads=4)
+    st.reset()
+    y = L.gemv(synth.MXFP4, dev(edge), rows, width, dev(x), st).cpu().numpy()[0]
+    assert rc == 0 and st.read() == 0 and matvec_close(y, y0, dec, x).all()
 
 
 def test_malformed_scale_sets_status_word(L):
@@ -187,7 +200,8 @@ def test_gemv_input_rows_additive_and_bf16(L, port, qtype):
 
 @pytest.mark.parametrize("qtype,count,rows,width", [(synth.IQ2_XXS, 5, 300, 4096), (synth.Q4_K, 3, 77, 1536), (synth.Q8_0, 4, 33, 2048),
                                                     (synth.IQ2_XXS, 40, 16, 256), (synth.Q2_K, 3, 20, 512), (synth.Q2_K, 6, 300, 2048),
-                                                    (synth.MXFP4, 2, 20, 512)])
+                                                    (synth.MXFP4, 2, 20, 512), (synth.MXFP4, 3, 77, 1536), (synth.MXFP4, 2, 300, 4096),
+                                                    (synth.MXFP4, 1, 40, 8192), (synth.MXFP4, 2, 20, 768)])
 def test_gemv_batch_vs_oracle(L, port, qtype, count, rows, width):
     """Independent matrices with their own input rows in one launch (ragged tiles, tiles of different
     matrices inside one CTA's task range, a qtype that falls back to one matvec per matrix)."""

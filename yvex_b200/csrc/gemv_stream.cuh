@@ -3,7 +3,7 @@
 // independent matrices with their own input vectors.
 //
 // Arithmetic. The weights enter the tensor cores as signed bytes (mma.sync.m16n8k32, s8 x s8 ->
-// s32): IQ2_XXS +-{8,25,43}, Q4_K codes 0..15, Q8_0 its int8 quants. The f32 activation row is
+// s32): IQ2_XXS +-{8,25,43}, Q4_K codes 0..15, Q8_0 its int8 quants, MXFP4 its levels + 16. The f32 activation row is
 // quantised once per matrix to a 28-bit fixed-point number relative to a power of two above its
 // largest magnitude and split into four balanced base-128 digits (planes of signed bytes), so
 // products and the 32-term sums are exact integers and only the 2^-27 input quantisation and
@@ -29,6 +29,7 @@
 // constant of the module and arrives by one bulk copy while the first tiles are in flight.
 #pragma once
 #include <cstdlib>
+#include <type_traits>
 
 #include "qtype_decode.cuh"
 #include "tcgen05.cuh"
@@ -127,6 +128,8 @@ struct StreamIq2 {
     static constexpr int kBlockBytes = 66, kBlockK = 256;
     static constexpr bool kTables = true;
     static constexpr int kSumGroup = 0;                  // activation sums over this many values (0: none needed)
+    static constexpr bool kInterleave = false;           // order of the activation digits within a group of 32 (see StreamMxfp4)
+    static constexpr bool kParity = false;               // unit<1> for odd units of a row, unit<0> for even ones
 
     __device__ __forceinline__ static void group(uint32_t a, uint32_t &grids, uint32_t &ss) {
         // a group starts on a 2-byte boundary: three aligned words, funnel-shifted when it sits mid-word
@@ -172,7 +175,7 @@ struct StreamIq2 {
         blk0 = fmaf(comb(ca[0], ca[1], cb[0], cb[1]), (float)((s0 >> 27) | 1u), blk0);       // 2 * sub + 1
         blk1 = fmaf(comb(ca[2], ca[3], cb[2], cb[3]), (float)((s1 >> 27) | 1u), blk1);
     }
-    __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t,
+    template <int> __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t,
                                                 float (&acc)[2], int &bad) {
         float blk0 = 0.0f, blk1 = 0.0f;
         half<0>(row0, row1, b, l, blk0, blk1);
@@ -192,6 +195,7 @@ struct StreamQ4k {
     static constexpr int kBlockBytes = 144, kBlockK = 256;
     static constexpr bool kTables = false;
     static constexpr int kSumGroup = 32;
+    static constexpr bool kInterleave = false, kParity = false;
 
     // 6-bit (scale, min) of sub-block j from the 12 packed bytes behind d and dmin (three aligned words)
     __device__ __forceinline__ static void scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int h, int t, uint32_t &sc, uint32_t &m) {
@@ -234,7 +238,7 @@ struct StreamQ4k {
         min0 = fmaf((float)m0, xs, min0);
         min1 = fmaf((float)m1, xs, min1);
     }
-    __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t sums,
+    template <int> __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t sums,
                                                 float (&acc)[2], int &bad) {
         float blk0 = 0.0f, blk1 = 0.0f, min0 = 0.0f, min1 = 0.0f;
         const uint4 head0 = lds128(row0), head1 = lds128(row1);          // d, dmin and the 12 scale bytes
@@ -260,6 +264,7 @@ struct StreamQ2k {
     static constexpr int kBlockBytes = 84, kBlockK = 256;
     static constexpr bool kTables = false;
     static constexpr int kSumGroup = 16;
+    static constexpr bool kInterleave = false, kParity = false;
 
     template <int H, int J> __device__ __forceinline__ static void step(const uint32_t (&w0)[8], const uint32_t (&w1)[8], int shift,
                                                                         uint32_t sc0, uint32_t sc1, const BUnit &b, int (&ca)[4],
@@ -290,7 +295,7 @@ struct StreamQ2k {
         min0 = fmaf((float)((s0 >> 4) & 15u), xa, fmaf((float)((s0 >> 12) & 15u), xb, min0));
         min1 = fmaf((float)((s1 >> 4) & 15u), xa, fmaf((float)((s1 >> 12) & 15u), xb, min1));
     }
-    __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t sums,
+    template <int> __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t sums,
                                                 float (&acc)[2], int &bad) {
         float blk0 = 0.0f, blk1 = 0.0f, min0 = 0.0f, min1 = 0.0f;
         half<0>(row0, row1, b, l, sums, blk0, blk1, min0, min1);
@@ -311,6 +316,7 @@ struct StreamQ80 {
     static constexpr int kBlockBytes = 8 * 34, kBlockK = 256;
     static constexpr bool kTables = false;
     static constexpr int kSumGroup = 0;
+    static constexpr bool kInterleave = false, kParity = false;
 
     __device__ __forceinline__ static void block(uint32_t a, uint32_t (&q)[8], float &d, int &bad, int flag) {
         // the block starts on a 2-byte boundary: nine aligned words, funnel-shifted when it sits mid-word
@@ -345,10 +351,91 @@ struct StreamQ80 {
         acc[0] = fmaf(comb(ca[0], ca[1], cb[0], cb[1]), d0, acc[0]);
         acc[1] = fmaf(comb(ca[2], ca[3], cb[2], cb[3]), d1, acc[1]);
     }
-    __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t,
+    template <int> __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t,
                                                 float (&acc)[2], int &bad) {
         half<0>(row0, row1, b, l, acc, bad);
         half<1>(row0, row1, b, l, acc, bad);
+    }
+};
+
+// MXFP4 (src/backend/cuda/kernel_primitives.h:100-111): 17 bytes = an E8M0 scale byte e, then 16 bytes whose low
+// nibbles are weights 0..15 and high nibbles weights 16..31; value = level(code) * 2^(e - 128), levels
+// {0,1,2,3,4,6,8,12} with bit 3 of the code as the sign. A unit is eight blocks (136 bytes); lane t of half h owns
+// block 4h + t.
+//   Decode. A byte permute is a lookup of four 3-bit indices in an 8-byte pool, and an index nibble whose bit 3 is
+// set returns the pool byte's sign bit replicated - zero for a pool of small positive bytes. So the raw data word
+// as the selector looks up the non-negative codes (and yields 0 for the others), the word with every bit 3
+// flipped looks up the negative ones in a second pool, and the OR of the two is the weight. The pools hold
+// level + 16 and 16 - level, i.e. bytes 4..28, so both are positive; the 16 comes off again as 16 x the sum of the
+// group's activation digits (the same sums the Q4_K minimum term uses).
+//   Order. The low 16 bits of a data word select for output bytes (w_i, w_16+i, w_i+1, w_17+i): nibble order, not
+// weight order. Rather than sort the bytes, the activation digits of a group are stored in that order
+// (kInterleave): position 8 j + 2 i + hi <- weight 16 hi + 4 j + i.
+//   Alignment. A row is a multiple of 272 bytes (an even number of units, checked by the host), so a unit starts
+// 0 or 8 bytes past a 16-byte boundary, the same for every row of a stage: unit<0> / unit<1>. Block b starts b
+// bytes into the 16-byte chunk at 16 b (0 mod 16 units) and its 17 bytes end within 24: one 16-byte and one
+// 8-byte load, in the order the alignment allows, give six words of which five are used from word h on.
+struct StreamMxfp4 {
+    static constexpr unsigned kQtype = Q_MXFP4;
+    static constexpr int kBlockBytes = 8 * 17, kBlockK = 256;
+    static constexpr bool kTables = false;
+    static constexpr int kSumGroup = 32;
+    static constexpr bool kInterleave = true, kParity = true;
+
+    template <int H, int kOdd> __device__ __forceinline__ static void block(uint32_t unit, int t, uint32_t (&x)[4], float &scale, int &bad,
+                                                                            int flag) {
+        const uint32_t at = unit + 16u * (uint32_t)(4 * H + t);
+        uint32_t w[6];
+        if (kOdd) {
+            const uint2 lo = lds64(at);
+            const uint4 hi = lds128(at + 8);
+            w[0] = lo.x; w[1] = lo.y; w[2] = hi.x; w[3] = hi.y; w[4] = hi.z; w[5] = hi.w;
+        } else {
+            const uint4 lo = lds128(at);
+            const uint2 hi = lds64(at + 16);
+            w[0] = lo.x; w[1] = lo.y; w[2] = lo.z; w[3] = lo.w; w[4] = hi.x; w[5] = hi.y;
+        }
+        const uint32_t e = (w[H] >> (8 * t)) & 255u;
+        bad |= e == 255u ? flag : 0;
+        scale = __uint_as_float(e ? e << 23 : 0x00400000u) * 0.5f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[i] = __funnelshift_rc(w[H + i], w[H + i + 1], 8 * (t + 1));
+    }
+    // eight codes of one data word -> two registers of bytes level + 16
+    __device__ __forceinline__ static void codes(uint32_t x, uint32_t &lo, uint32_t &hi) {
+        constexpr uint32_t kP0 = 0x13121110u, kP1 = 0x1c181614u;        // 16 + {0,1,2,3}, 16 + {4,6,8,12}
+        constexpr uint32_t kN0 = 0x0d0e0f10u, kN1 = 0x04080a0cu;        // 16 - the same
+        const uint32_t xf = x ^ 0x88888888u;
+        lo = prmt(kP0, kP1, x) | prmt(kN0, kN1, xf);
+        hi = prmt(kP0, kP1, x >> 16) | prmt(kN0, kN1, xf >> 16);
+    }
+    template <int H, int J> __device__ __forceinline__ static void step(const uint32_t (&x0)[4], const uint32_t (&x1)[4], const BUnit &b,
+                                                                        int (&ca)[4], int (&cb)[4]) {
+        uint32_t a[4];
+        codes(x0[J], a[0], a[2]);
+        codes(x1[J], a[1], a[3]);
+        mma_s8<J == 0>(ca, a, b.bh[4 * H + J].x, b.bh[4 * H + J].y);
+        mma_s8<J == 0>(cb, a, b.bl[4 * H + J].x, b.bl[4 * H + J].y);
+    }
+    template <int H, int kOdd> __device__ __forceinline__ static void half(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l,
+                                                                           uint32_t sums, float (&acc)[2], int &bad) {
+        uint32_t x0[4], x1[4];
+        float s0, s1;
+        block<H, kOdd>(row0, l.t, x0, s0, bad, 1);
+        block<H, kOdd>(row1, l.t, x1, s1, bad, 2);
+        int ca[4], cb[4];
+        step<H, 0>(x0, x1, b, ca, cb);
+        step<H, 1>(x0, x1, b, ca, cb);
+        step<H, 2>(x0, x1, b, ca, cb);
+        step<H, 3>(x0, x1, b, ca, cb);
+        const float off = 16.0f * ldsf(sums + 4 * (4 * H + l.t));        // 16 x the sum of the activation over this block
+        acc[0] = fmaf(comb(ca[0], ca[1], cb[0], cb[1]) - off, s0, acc[0]);
+        acc[1] = fmaf(comb(ca[2], ca[3], cb[2], cb[3]) - off, s1, acc[1]);
+    }
+    template <int kOdd> __device__ __forceinline__ static void unit(uint32_t row0, uint32_t row1, const BUnit &b, const Lane &l, uint32_t sums,
+                                                                    float (&acc)[2], int &bad) {
+        half<0, kOdd>(row0, row1, b, l, sums, acc, bad);
+        half<1, kOdd>(row0, row1, b, l, sums, acc, bad);
     }
 };
 
@@ -605,9 +692,23 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
 #pragma unroll
                     for (int pi = 0; pi < 4; ++pi) d[pi][i8 >> 2] |= (uint32_t)(dig[pi] & 0xff) << (8 * (i8 & 3));
                 }
+                if (Dec::kInterleave) {
+                    // lanes s and s + 2 of a quad hold weights 8 s .. and 16 + 8 s ..: lane s builds the 8-byte chunk 2 s
+                    // (its own first word and the partner's, bytes alternating), lane s + 2 chunk 2 s + 1 (the second words)
+                    const int sub = k8 & 3;
 #pragma unroll
-                for (int pi = 0; pi < 4; ++pi)
-                    *reinterpret_cast<uint2 *>(pl + (size_t)pi * p.K + 8 * k8) = make_uint2(d[pi][0], d[pi][1]);
+                    for (int pi = 0; pi < 4; ++pi) {
+                        const uint32_t got = __shfl_xor_sync(0xffffffffu, sub < 2 ? d[pi][1] : d[pi][0], 2);
+                        const uint32_t lo = sub < 2 ? d[pi][0] : got, hi = sub < 2 ? got : d[pi][1];
+                        const int chunk = sub < 2 ? 2 * sub : 2 * (sub - 2) + 1;
+                        *reinterpret_cast<uint2 *>(pl + (size_t)pi * p.K + 32 * (k8 >> 2) + 8 * chunk) =
+                            make_uint2(prmt(lo, hi, 0x5140u), prmt(lo, hi, 0x7362u));
+                    }
+                } else {
+#pragma unroll
+                    for (int pi = 0; pi < 4; ++pi)
+                        *reinterpret_cast<uint2 *>(pl + (size_t)pi * p.K + 8 * k8) = make_uint2(d[pi][0], d[pi][1]);
+                }
                 if (Dec::kSumGroup == 32) {
                     s += __shfl_xor_sync(0xffffffffu, s, 1);
                     s += __shfl_xor_sync(0xffffffffu, s, 2);
@@ -636,12 +737,17 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
                 BUnit bmem;
                 if (!kBReg) load_b(bmem, u);
                 const BUnit &b = kBReg ? breg : bmem;
+                auto groups = [&](auto odd) {
 #pragma unroll
-                for (int gi = 0; gi < kGroupsPerWarp; ++gi) {
-                    // groups past a ragged tile's last row decode stale bytes; their results are never stored
-                    const uint32_t r0 = base + (uint32_t)(kTileRows * gi) * row_bytes + (uint32_t)(u * Dec::kBlockBytes);
-                    Dec::unit(r0, r0 + 8 * row_bytes, b, l, sums + (uint32_t)(u * kSumsPerUnit * 4), acc[gi], bad[gi]);
-                }
+                    for (int gi = 0; gi < kGroupsPerWarp; ++gi) {
+                        // groups past a ragged tile's last row decode stale bytes; their results are never stored
+                        const uint32_t r0 = base + (uint32_t)(kTileRows * gi) * row_bytes + (uint32_t)(u * Dec::kBlockBytes);
+                        Dec::template unit<decltype(odd)::value>(r0, r0 + 8 * row_bytes, b, l, sums + (uint32_t)(u * kSumsPerUnit * 4), acc[gi],
+                                                                 bad[gi]);
+                    }
+                };
+                if (Dec::kParity && ((unit0 + u) & 1)) groups(std::integral_constant<int, 1>{});
+                else groups(std::integral_constant<int, 0>{});
             }
         }
         // this warp is done with the stage
@@ -667,9 +773,11 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
 struct StreamShape { int slices, units_per_slice, row_warps, consumers, depth, groups; uint32_t stage_bytes, smem_bytes; };
 
 // K-slices (consumer warps along K), units per slice, warps along the rows of a stage and the deepest ring that fits.
-inline bool stream_shape(uint64_t width, uint64_t row_bytes, bool tables, StreamShape &sh) {
+inline bool stream_shape(unsigned q, uint64_t width, uint64_t row_bytes, StreamShape &sh) {
+    const bool tables = q == Q_IQ2_XXS;
     const int units = (int)(width / 256);
     if (!units || width % 256 || width > 8192) return false;
+    if (q == Q_MXFP4 && units % 2) return false;           // its loads want rows that are multiples of 16 bytes
     sh.units_per_slice = (units + kMaxConsumers - 1) / kMaxConsumers;
     sh.slices = (units + sh.units_per_slice - 1) / sh.units_per_slice;
     sh.row_warps = sh.slices <= kMaxConsumers / 2 ? 2 : 1;
@@ -691,14 +799,14 @@ inline bool stream_shape(uint64_t width, uint64_t row_bytes, bool tables, Stream
     return false;
 }
 
-inline bool stream_qtype(unsigned q) { return q == Q_IQ2_XXS || q == Q_Q4_K || q == Q_Q8_0 || q == Q_Q2_K; }
+inline bool stream_qtype(unsigned q) { return q == Q_IQ2_XXS || q == Q_Q4_K || q == Q_Q8_0 || q == Q_Q2_K || q == Q_MXFP4; }
 
 inline bool stream_eligible(unsigned q, uint64_t rows, uint64_t width, uint64_t row_bytes, const void *enc, uint64_t matrix_stride,
                             uint64_t count, const float *x, uint64_t x_stride) {
     StreamShape sh;
     return stream_qtype(q) && rows && count && count <= 0xffffffffull && (reinterpret_cast<uintptr_t>(enc) & 15u) == 0 &&
            matrix_stride % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && x_stride % 4 == 0 &&
-           stream_shape(width, row_bytes, q == Q_IQ2_XXS, sh);
+           stream_shape(q, width, row_bytes, sh);
 }
 
 template <class Dec, bool kBReg, int kG>
@@ -724,7 +832,7 @@ inline int stream_launch(unsigned q, const uint8_t *enc, uint64_t matrix_stride,
                          uint64_t out_stride, int round_bf16, int *status, cudaStream_t stream,
                          const uint8_t *const *matrix_ptrs = nullptr, const uint32_t *x_rows = nullptr) {
     StreamShape sh;
-    if (!stream_shape(width, row_bytes, q == Q_IQ2_XXS, sh)) return ERR_BOUNDS;
+    if (!stream_shape(q, width, row_bytes, sh)) return ERR_BOUNDS;
     StreamParams p{};
     p.matrix_ptrs = matrix_ptrs; p.x_rows = x_rows;
     p.enc = enc; p.matrix_stride = matrix_stride; p.count = (uint32_t)count; p.rows = rows; p.row_bytes = row_bytes;
@@ -737,6 +845,7 @@ inline int stream_launch(unsigned q, const uint8_t *enc, uint64_t matrix_stride,
     case Q_Q4_K: return stream_launch_t<StreamQ4k>(p, sh, stream);
     case Q_Q8_0: return stream_launch_t<StreamQ80>(p, sh, stream);
     case Q_Q2_K: return stream_launch_t<StreamQ2k>(p, sh, stream);
+    case Q_MXFP4: return stream_launch_t<StreamMxfp4>(p, sh, stream);
     default: return ERR_UNSUPPORTED;
     }
 }

@@ -30,7 +30,7 @@ bool moe_decode_stream_eligible(const MoeGeom &g, const MoeWeights &w) {
     if (g.inter != g.shared_inter || g.hidden % 256 || g.inter % 256) return false;
     const uint64_t grb = g.hidden / gg.elems * gg.bytes, drb = g.inter / dg.elems * dg.bytes;
     gs::StreamShape sh;
-    if (!gs::stream_shape(g.hidden, grb, g.gate_qtype == Q_IQ2_XXS, sh) || !gs::stream_shape(g.inter, drb, g.down_qtype == Q_IQ2_XXS, sh))
+    if (!gs::stream_shape(g.gate_qtype, g.hidden, grb, sh) || !gs::stream_shape(g.down_qtype, g.inter, drb, sh))
         return false;
     const uintptr_t ptrs = (uintptr_t)w.gate | (uintptr_t)w.up | (uintptr_t)w.down | (uintptr_t)w.shared_gate |
                            (uintptr_t)w.shared_up | (uintptr_t)w.shared_down;

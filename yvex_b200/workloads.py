@@ -25,6 +25,8 @@ def device_blocks(torch, qtype, rows, width, gen, device):
     for off in scale_at:
         d = (torch.rand(nblk, device=device, generator=gen) * 9e-4 + 1e-4).to(torch.float16)
         raw[:, off:off + 2] = d.view(torch.uint8).reshape(nblk, 2)
+    if qtype == synth.MXFP4:                 # byte 0 is an E8M0 exponent: scales 2^-17 .. 2^-4, as synth.random_blocks
+        raw[:, 0] = torch.randint(110, 124, (nblk,), dtype=torch.uint8, device=device, generator=gen)
     return raw.reshape(-1)
 
 
