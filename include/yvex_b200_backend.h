@@ -163,6 +163,30 @@ int yvex_backend_cuda_encoded_gather(yvex_backend *backend, const unsigned char 
     yvex_backend_cuda_operation_facts *facts, yvex_error *err);
 
 /* ---- attention: include/yvex/backend.h:246-257 (public op) ------------------------------------------------- */
+/*
+ * One encoded row times one f32 vector, both HOST memory, result to host: yvex_cuda_quant_row_dot
+ * (src/backend/cuda/private.h:588-596, src/backend/cuda/qtype.c:527-700). `failure` (optional) is zeroed on
+ * success and filled on every refusal as the reference fills it (code, expected, actual, qtype; the index
+ * fields all-ones, operation = the operation count): INVALID_ARGUMENT for missing or misaligned pointers,
+ * CUDA_COMPUTE_UNAVAILABLE + YVEX_ERR_UNSUPPORTED for a qtype without a device decoder (here Q4_K has one),
+ * ROW_DIVISIBILITY / BYTE_OVERFLOW + YVEX_ERR_BOUNDS for a row that is not whole blocks or whose byte count
+ * differs, WORKER for a failed copy or launch, NONFINITE + YVEX_ERR_FORMAT for a malformed block scale.
+ * The YVEX_TEST_CUDA_QTYPE_COPY_FAILURE=input|output seams fail the call before / after the device work.
+ */
+typedef enum {
+    YVEX_QUANT_FAILURE_NONE = 0, YVEX_QUANT_FAILURE_INVALID_ARGUMENT = 1, YVEX_QUANT_FAILURE_CUDA_COMPUTE_UNAVAILABLE = 21,
+    YVEX_QUANT_FAILURE_ROW_DIVISIBILITY = 28, YVEX_QUANT_FAILURE_BYTE_OVERFLOW = 30, YVEX_QUANT_FAILURE_NONFINITE = 37,
+    YVEX_QUANT_FAILURE_WORKER = 45, YVEX_QUANT_FAILURE_CLEANUP = 46
+} yvex_quant_failure_code;                       /* the values of include/yvex/internal/quant_numeric.h:31-82 that this backend reports */
+#define YVEX_TRANSFORM_OP_COUNT 9                /* include/yvex/internal/compilation.h:112-122 */
+typedef struct yvex_quant_failure {
+    int code;                                    /* yvex_quant_failure_code */
+    unsigned long long terminal_ordinal, source_index, row_index, block_index, expected, actual;
+    unsigned int qtype;
+    int operation;                               /* yvex_transform_operation_kind */
+} yvex_quant_failure;
+int yvex_cuda_quant_row_dot(yvex_backend *backend, unsigned int qtype, const unsigned char *encoded, size_t encoded_bytes,
+                            const float *vector, unsigned long long elements, float *out, yvex_quant_failure *failure, yvex_error *err);
 int yvex_backend_op_attention(yvex_backend *backend, const yvex_device_tensor *query, const yvex_device_tensor *keys,
                               const yvex_device_tensor *values, unsigned long long seq_len, unsigned long long position,
                               float scale, int causal, yvex_device_tensor *score_scratch,
@@ -347,6 +371,55 @@ typedef struct {
     int (*execute_rows_wide)(yvex_backend *backend, const yvex_moe_layer_job *job, const yvex_moe_row_batch *batch,
                              const yvex_moe_row_batch_output *output, yvex_moe_row_batch_result *result, yvex_error *err);
 } yvex_backend_moe_operations;
+/*
+ * Token-local MoE transaction (include/yvex/internal/moe.h:160-166, :198-214, :308-319;
+ * src/backend/cuda/moe.c:504-848; caller src/runtime/moe.c:647-694): one token, one expert per call.
+ *   begin       uploads job->expanded_input (or reads job->device_input), runs the envelope's prepare step
+ *               (or, without an envelope, the bf16 ingress rounding), the router projection, scoring and top-k,
+ *               and publishes result->router. When the caller will not add the routed experts itself (a
+ *               device output, evidence below FULL and device addresses on all three routed packs: the
+ *               condition at src/runtime/moe.c:654-658) begin adds the selected experts.
+ *   add_expert  gate and up matvecs of the normalized row, SwiGLU * weight -> bf16, down matvec -> bf16, added to
+ *               the routed (f32, call order) or shared aggregate. Weights must be resident on the backend
+ *               (YVEX_ERR_STATE otherwise); any qtype with a device decoder is taken.
+ *   finish      combined = bf16(routed + shared), the envelope's post step into job->device_output when there is
+ *               one, downloads (everything without a device output or at FULL evidence; the selection
+ *               otherwise), one synchronisation, the status word, the counters.
+ *   close       frees the transaction; nothing of the backend is released.
+ * Scratch comes from the attached workspace (workspace_required(layer, 1) covers it) and is reset by begin,
+ * like backend_workspace_reset in the reference: one transaction at a time per backend.
+ */
+typedef struct {
+    unsigned long long selected_count;
+    unsigned long long selected_experts[YVEX_MOE_MAX_SELECTED];
+    float router_logits[256], router_scores[256];
+    float selected_weights[YVEX_MOE_MAX_SELECTED];
+} yvex_moe_router_result;
+typedef struct {
+    float *combined_output, *post, *combination;
+    unsigned long long combined_capacity, post_capacity, combination_capacity;
+    float *routed_output, *shared_output;
+    unsigned long long routed_capacity, shared_capacity;
+    yvex_moe_router_result router;
+    unsigned long long expert_subviews_accessed, encoded_bytes_read;
+    unsigned long long host_to_device_bytes, device_to_host_bytes, kernel_launches;
+    unsigned long long cache_hits, cache_misses, upload_count, download_count;
+    unsigned long long stream_synchronizations, device_synchronizations, device_to_device_bytes;
+    yvex_execution_memory_facts memory;
+    unsigned long long ingress_ns, routing_ns, routed_ns, shared_ns, post_ns, total_ns;
+    unsigned long long synchronization_ns;
+    unsigned long long qtype_counts[YVEX_RUNTIME_DESCRIPTOR_QTYPE_CAP];
+    char routed_digest[YVEX_SHA256_HEX_CAP], shared_digest[YVEX_SHA256_HEX_CAP];
+    char combined_digest[YVEX_SHA256_HEX_CAP], routing_digest[YVEX_SHA256_HEX_CAP];
+} yvex_moe_layer_result;
+typedef struct yvex_backend_moe_execution yvex_backend_moe_execution;
+int yvex_backend_moe_begin(yvex_backend_moe_execution **out, yvex_backend *backend, const yvex_moe_layer_job *job,
+                           yvex_moe_layer_result *result, yvex_error *err);
+int yvex_backend_moe_add_expert(yvex_backend_moe_execution *execution, const yvex_moe_weight_view *gate,
+                                const yvex_moe_weight_view *up, const yvex_moe_weight_view *down, float route_weight,
+                                int shared, yvex_error *err);
+int yvex_backend_moe_finish(yvex_backend_moe_execution *execution, yvex_moe_layer_result *result, yvex_error *err);
+int yvex_backend_moe_close(yvex_backend_moe_execution **execution, yvex_error *err);
 /* "sizeof type N" / "offsetof type.field N" lines for every entry of yvex_b200_abi_fields.h, as this
  * library was compiled; a binding compares its own table with it. No reference counterpart. */
 const char *yvex_backend_abi_layout(void);

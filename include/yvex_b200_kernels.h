@@ -209,6 +209,21 @@ int yvex_b200_moe_expert_rows(const yvex_b200_moe_geometry *g, const yvex_b200_m
 int yvex_b200_moe_combine(const void *y_routed_bf16, const void *y_shared_bf16, uint64_t tokens,
                           uint64_t topk, uint64_t hidden, float *out, int *status, void *stream);
 /*
+ * Elementwise steps of the token-local transaction, which runs one expert at a time between
+ * yvex_b200_gemv calls like yvex_backend_moe_add_expert (src/backend/cuda/moe.c:673-724). All arrays
+ * are device f32 of n elements. _round: out = bf16(x), the ingress rounding of the normalized row
+ * (src/graph/moe.c:487-489); _scores: (float)sqrt(softplus(logit)) in double (src/graph/moe.c:497-506);
+ * _swiglu: mid = bf16(silu(min(g, limit)) * clamp(u, +-limit) * weight) (src/graph/moe.c:604-616);
+ * _accumulate: dst += src (src/runtime/moe.c:620-622); _sum_round: out = bf16(a + b)
+ * (src/runtime/moe.c:630-634). Non-finite values set the status word.
+ */
+int yvex_b200_moe_token_round(const float *x, uint64_t n, float *out, int *status, void *stream);
+int yvex_b200_moe_token_scores(const float *logits, uint64_t n, float *scores, int *status, void *stream);
+int yvex_b200_moe_token_swiglu(const float *gate, const float *up, uint64_t n, double limit, float weight, float *mid,
+                               int *status, void *stream);
+int yvex_b200_moe_token_accumulate(const float *src, uint64_t n, float *dst, int *status, void *stream);
+int yvex_b200_moe_token_sum_round(const float *a, const float *b, uint64_t n, float *out, int *status, void *stream);
+/*
  * The sending side of the expert-parallel dispatch in one call: groups the (token, rank) pairs of
  * `selected` [tokens x topk] by destination rank e / experts_per_rank (stable: ascending pair index
  * within a rank) and writes, in that send order, the fp16 rows (row of pair p = rows_f16[p / topk]),

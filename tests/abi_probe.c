@@ -10,6 +10,7 @@
 #include <yvex/backend.h>
 #include <yvex/internal/backend.h>
 #include <yvex/internal/moe.h>
+#include <yvex/internal/quant_numeric.h>
 #else
 #include "yvex_b200_backend.h"
 #endif

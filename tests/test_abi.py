@@ -134,7 +134,9 @@ def test_ctypes_mirror_matches_the_compiled_layout(lib):
               "yvex_moe_device_completion_slot": B.CompletionSlot, "yvex_moe_device_completion": B.Completion,
               "yvex_moe_layer_job": B.LayerJob, "yvex_moe_row_batch": B.RowBatch, "yvex_moe_row_batch_output": B.RowBatchOutput,
               "yvex_moe_row_batch_result": B.RowBatchResult, "yvex_moe_input_summary": B.MoeInputSummary,
-              "yvex_moe_input_layer_record": B.MoeInputRecord, "yvex_error": B.Error}
+              "yvex_moe_input_layer_record": B.MoeInputRecord, "yvex_error": B.Error,
+              "yvex_moe_router_result": B.RouterResult, "yvex_moe_layer_result": B.LayerResult,
+              "yvex_quant_failure": B.QuantFailure}
     for name, cls in mirror.items():
         assert C.sizeof(cls) == int(table[f"sizeof {name}"]), name
         for field, _ in cls._fields_:

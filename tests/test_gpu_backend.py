@@ -612,3 +612,224 @@ def test_fixture_file_drives_execute_rows(B, golden, tmp_path):
     assert rel_l2(out, golden["layer_small_router_out"].view(np.float32)) <= 1e-3
     B._lib.yvex_moe_input_close(C.byref(handle))
     assert be.close() == B.OK
+
+
+# ---- token-local transaction: begin / add_expert / finish / close (src/backend/cuda/moe.c:504-848) ----------
+
+def token_result(B, H, S=1):
+    """A yvex_moe_layer_result with host room for every publication, and the arrays behind it."""
+    a = dict(combined=np.zeros(H, np.float32), routed=np.zeros(H, np.float32), shared=np.zeros(H, np.float32),
+             post=np.zeros(max(S, 1), np.float32), comb=np.zeros(max(S, 1) ** 2, np.float32))
+    r = B.LayerResult()
+    r.combined_output, r.combined_capacity = a["combined"].ctypes.data, H
+    r.routed_output, r.routed_capacity = a["routed"].ctypes.data, H
+    r.shared_output, r.shared_capacity = a["shared"].ctypes.data, H
+    r.post, r.post_capacity = a["post"].ctypes.data, a["post"].size
+    r.combination, r.combination_capacity = a["comb"].ctypes.data, a["comb"].size
+    return r, a
+
+
+def run_token(B, be, job, spec, row, add_routed=True, shared_first=False):
+    """The call sequence of runtime_moe_layer_cuda (src/runtime/moe.c:647-694) for one token."""
+    H = spec.hidden
+    res, arrays = token_result(B, H, int(job._plan.residual_streams))
+    keep = np.ascontiguousarray(row, np.float32)
+    job.expanded_input = keep.ctypes.data if not job.device_input else None
+    ex = B.vp()
+    rc = B._lib.yvex_backend_moe_begin(C.byref(ex), be.h, C.byref(job), C.byref(res), C.byref(be.err))
+    if rc != B.OK:
+        return rc, res, arrays
+    shared = [B.WeightView() for _ in range(3)]
+    for v, slot in zip(shared, (B.W_SHARED_GATE, B.W_SHARED_UP, B.W_SHARED_DOWN)):
+        C.memmove(C.byref(v), C.byref(job.weights[slot]), C.sizeof(B.WeightView))
+    if shared_first:
+        rc = B._lib.yvex_backend_moe_add_expert(ex, shared[0], shared[1], shared[2], 1.0, 1, C.byref(be.err))
+    for rank in range(int(res.router.selected_count) if add_routed else 0):
+        e = int(res.router.selected_experts[rank])
+        views = [B.expert_view(job, B.W_GATE, e, spec.inter), B.expert_view(job, B.W_UP, e, spec.inter),
+                 B.expert_view(job, B.W_DOWN, e, spec.hidden)]
+        if rc == B.OK:
+            rc = B._lib.yvex_backend_moe_add_expert(ex, views[0], views[1], views[2], res.router.selected_weights[rank], 0, C.byref(be.err))
+    if rc == B.OK and not shared_first:
+        rc = B._lib.yvex_backend_moe_add_expert(ex, shared[0], shared[1], shared[2], 1.0, 1, C.byref(be.err))
+    if rc == B.OK:
+        rc = B._lib.yvex_backend_moe_finish(ex, C.byref(res), C.byref(be.err))
+        # a finished transaction takes no more experts and finishes only once
+        assert B._lib.yvex_backend_moe_add_expert(ex, shared[0], shared[1], shared[2], 1.0, 1, C.byref(be.err)) == B.INVALID_ARG
+        assert B._lib.yvex_backend_moe_finish(ex, C.byref(res), C.byref(be.err)) == B.INVALID_ARG
+    assert B._lib.yvex_backend_moe_close(C.byref(ex), C.byref(be.err)) == B.OK and not ex.value
+    return rc, res, arrays
+
+
+@pytest.mark.parametrize("name", ["small_router", "c2_shape"])
+def test_token_transaction_vs_frozen_reference(B, golden, name):
+    """One token at a time, one expert per call: selection, weights and the combined row against the frozen
+    outputs of the reference's CPU layer; bf16(routed + shared) is the combined row bit for bit."""
+    be, arena, job, spec, x, _ = layer_setup(B, name)
+    attach_workspace(B, be, job, 1)
+    want = golden[f"layer_{name}_out"].view(np.float32).reshape(x.shape)
+    for t in range(x.shape[0]):
+        rc, res, a = run_token(B, be, job, spec, x[t])
+        assert rc == B.OK, be.message()
+        assert res.router.selected_count == spec.topk
+        assert (np.array(res.router.selected_experts[:spec.topk], np.uint64) == golden[f"layer_{name}_sel"].reshape(x.shape[0], -1)[t]).all()
+        assert np.abs(np.array(res.router.selected_weights[:spec.topk], np.float32) -
+                      golden[f"layer_{name}_w"].view(np.float32).reshape(x.shape[0], -1)[t]).max() <= 2e-7
+        assert rel_l2(a["combined"], want[t]) <= 1e-3
+        assert (synth.bf16_round(a["routed"] + a["shared"]).view(np.uint32) == a["combined"].view(np.uint32)).all()
+        scores = np.array(res.router.router_scores[:spec.experts], np.float64)
+        logits = np.array(res.router.router_logits[:spec.experts], np.float64)
+        assert np.abs(scores - np.sqrt(np.logaddexp(0.0, logits))).max() <= 1e-6
+        assert res.expert_subviews_accessed == 3 * spec.topk and res.kernel_launches >= 5 * (spec.topk + 1)
+        assert res.host_to_device_bytes >= x[t].nbytes and res.device_to_host_bytes >= 3 * x[t].nbytes and res.stream_synchronizations == 2
+    # the aggregates are f32 sums in call order: the shared expert first changes nothing (it has its own aggregate)
+    rc, _, b = run_token(B, be, job, spec, x[0], shared_first=True)
+    rc2, _, c = run_token(B, be, job, spec, x[0])
+    assert rc == B.OK and rc2 == B.OK and (b["combined"].view(np.uint32) == c["combined"].view(np.uint32)).all()
+    assert be.close() == B.OK
+
+
+def test_token_transaction_device_views_add_the_selected_experts_in_begin(B, golden):
+    """With a device input and output, evidence below FULL and device addresses on the routed packs, begin runs the
+    selected experts itself (src/runtime/moe.c:654-664 then skips its loop) and finish writes the device output."""
+    be, arena, job, spec, x, _ = layer_setup(B, "small_router")
+    attach_workspace(B, be, job, 1)
+    H = spec.hidden
+    rc, res0, host = run_token(B, be, job, spec, x[1])
+    assert rc == B.OK
+    tin = be.from_array(x[1:2], B.F32)
+    rc, tout, _ = be.tensor(H * 4, B.F32, [1, H])
+    job.device_input, job.device_output = tin, tout
+    for slot in (B.W_GATE, B.W_UP, B.W_DOWN):
+        addr = B.ull()
+        v = job.weights[slot]
+        assert B._lib.yvex_backend_resident_resolve(be.h, v.encoded, v.encoded_bytes, C.byref(addr)) == 1
+        v.device_address = addr.value
+    rc, res, a = run_token(B, be, job, spec, x[1], add_routed=False)
+    assert rc == B.OK, be.message()
+    rc, out = be.read(tout, np.float32, H)
+    assert rc == B.OK and (out.view(np.uint32) == host["combined"].view(np.uint32)).all()
+    assert not a["combined"].any()                       # nothing but the selection is downloaded in this mode
+    assert list(res.router.selected_experts[:spec.topk]) == list(res0.router.selected_experts[:spec.topk])
+    assert res.expert_subviews_accessed == 3 * spec.topk and res.memory.activation_bytes == 2 * H * 4
+    # at FULL evidence the caller adds the experts and everything is published to the host as well
+    job.evidence_level = 3
+    rc, res, a = run_token(B, be, job, spec, x[1])
+    assert rc == B.OK and (a["combined"].view(np.uint32) == host["combined"].view(np.uint32)).all()
+    assert be.close() == B.OK
+
+
+def test_token_transaction_with_envelope_matches_execute_rows(B, golden):
+    H, S, T, seed = CASES["envelope"]["small"]
+    fn, scale, base, norm, expanded = envelope_inputs("small")
+    spec, weights, router, _, _ = layer_inputs("small_router")
+    be = B.Backend()
+    arena = B.ResidentArena(be, dict(weights, router=router, ffn_norm=norm, mhc_fn=fn, mhc_base=base, mhc_scale=scale))
+    job = B.moe_job(arena, spec, residual_streams=S, envelope_policy=ENVELOPE_POLICY)
+    ops, _ = attach_workspace(B, be, job, T)
+    out = np.zeros((T, S * H), np.float32)
+    post, comb, routed, shared = np.zeros((T, S), np.float32), np.zeros((T, S * S), np.float32), np.zeros((T, H), np.float32), np.zeros((T, H), np.float32)
+    batch = B.row_batch(T, S * H, host_rows=expanded.ctypes.data_as(B.vp))
+    o = B.row_output(out.ctypes.data_as(B.vp), out.size, post=post.ctypes.data_as(B.vp), combination=comb.ctypes.data_as(B.vp),
+                     post_capacity=post.size, combination_capacity=comb.size, routed=routed.ctypes.data_as(B.vp),
+                     shared=shared.ctypes.data_as(B.vp), routed_capacity=routed.size, shared_capacity=shared.size)
+    assert ops.execute_rows(be.h, C.byref(job), C.byref(batch), C.byref(o), C.byref(B.RowBatchResult()), C.byref(be.err)) == B.OK
+    for t in range(T):
+        rc, res, a = run_token(B, be, job, spec, expanded[t])
+        assert rc == B.OK, be.message()
+        assert (np.array(res.router.selected_experts[:spec.topk], np.uint64) == golden["envelope_small_sel"].reshape(T, -1)[t]).all()
+        assert (a["post"].view(np.uint32) == post[t].view(np.uint32)).all() and (a["comb"].view(np.uint32) == comb[t].view(np.uint32)).all()
+        assert rel_l2(a["combined"], synth.bf16_round(routed[t] + shared[t])) <= 1e-3
+    # the post step into a device output equals the row batch's expanded output row
+    tin = be.from_array(expanded[0:1], B.F32)
+    rc, tout, _ = be.tensor(S * H * 4, B.F32, [1, S * H])
+    job.device_input, job.device_output, job.evidence_level = tin, tout, 3
+    rc, res, a = run_token(B, be, job, spec, expanded[0])
+    assert rc == B.OK, be.message()
+    rc, got = be.read(tout, np.float32, S * H)
+    assert rc == B.OK and rel_l2(got, out[0]) <= 1e-3
+    assert be.close() == B.OK
+
+
+def test_token_transaction_refusals(B):
+    be, arena, job, spec, x, _ = layer_setup(B, "small_router")
+    H = spec.hidden
+    res, arrays = token_result(B, H)
+    ex = B.vp()
+    row = np.ascontiguousarray(x[0])
+    job.expanded_input = row.ctypes.data
+    begin = lambda: B._lib.yvex_backend_moe_begin(C.byref(ex), be.h, C.byref(job), C.byref(res), C.byref(be.err))
+    assert begin() == B.NOMEM and not ex.value                       # no workspace attached
+    attach_workspace(B, be, job, 1)
+    res.combined_capacity = H - 1
+    assert begin() == B.INVALID_ARG
+    res.combined_capacity = H
+    keep = job.weights[B.W_ROUTER].encoded
+    job.weights[B.W_ROUTER].encoded = None
+    assert begin() == B.STATE                                        # the router is not resident
+    job.weights[B.W_ROUTER].encoded = keep
+    job.weights[B.W_ROUTER].qtype = 11                               # Q3_K: storage only, no decoder
+    assert begin() == B.UNSUPPORTED
+    job.weights[B.W_ROUTER].qtype = synth.F32
+    assert begin() == B.OK and ex.value
+    gate, up, down = (B.expert_view(job, B.W_GATE, 1, spec.inter), B.expert_view(job, B.W_UP, 1, spec.inter),
+                      B.expert_view(job, B.W_DOWN, 1, spec.hidden))
+    add = lambda g, u, d: B._lib.yvex_backend_moe_add_expert(ex, g, u, d, 0.5, 0, C.byref(be.err))
+    assert add(gate, up, None) == B.INVALID_ARG
+    bad = B.expert_view(job, B.W_GATE, 1, spec.inter - 32)
+    assert add(bad, up, down) == B.INVALID_ARG                       # gate and up disagree
+    bad = B.expert_view(job, B.W_DOWN, 1, spec.hidden)
+    bad.qtype = 13                                                   # Q5_K
+    assert add(gate, up, bad) == B.UNSUPPORTED
+    bad = B.expert_view(job, B.W_DOWN, 1, spec.hidden)
+    bad.row_bytes += 2
+    assert add(gate, up, bad) == B.FORMAT
+    bad = B.expert_view(job, B.W_DOWN, 1, spec.hidden)
+    bad.encoded = 0x10                                               # not in the resident arena
+    assert add(gate, up, bad) == B.STATE
+    assert add(gate, up, down) == B.OK
+    res.routed_capacity = H - 1
+    assert B._lib.yvex_backend_moe_finish(ex, C.byref(res), C.byref(be.err)) == B.INVALID_ARG
+    res.routed_capacity = H
+    assert B._lib.yvex_backend_moe_finish(ex, C.byref(res), C.byref(be.err)) == B.OK
+    assert B._lib.yvex_backend_moe_close(C.byref(ex), C.byref(be.err)) == B.OK
+    assert B._lib.yvex_backend_moe_close(C.byref(ex), C.byref(be.err)) == B.OK       # closing nothing is fine
+    assert be.close() == B.OK
+
+
+@pytest.mark.parametrize("qtype", [synth.IQ2_XXS, synth.Q2_K, synth.Q8_0, synth.MXFP4, synth.Q4_K, synth.F32])
+def test_quant_row_dot_host_row_and_vector(B, port, qtype, monkeypatch):
+    """yvex_cuda_quant_row_dot: one encoded row and one vector from host memory (src/backend/cuda/qtype.c:527-700),
+    the result against the CPU row dot, and the failure record of each refusal."""
+    width = 1024
+    if qtype == synth.F32:
+        row = np.random.default_rng(3).standard_normal(width).astype(np.float32).view(np.uint8).reshape(1, -1)
+    else:
+        row = synth.random_blocks(qtype, 1, width, 90 + qtype)
+    x = np.random.default_rng(4).standard_normal(width).astype(np.float32)
+    rc, want = port.matvec(qtype, row, 1, width, x, allow_q4k=True)
+    assert rc == 0
+    be = B.Backend()
+    out, fail = C.c_float(), B.QuantFailure()
+    dot = lambda q, r, nbytes, v, n: B._lib.yvex_cuda_quant_row_dot(be.h, q, r.ctypes.data if r is not None else None, nbytes,
+                                                                   v.ctypes.data, n, C.byref(out), C.byref(fail), C.byref(be.err))
+    assert dot(qtype, row, row.nbytes, x, width) == B.OK, be.message()
+    assert abs(out.value - want[0]) <= 1e-5 * (1 + abs(want[0])) + 2e-6 * np.abs(x).sum() * 4 and fail.code == 0
+    assert dot(qtype, None, row.nbytes, x, width) == B.INVALID_ARG and fail.code == 1 and fail.qtype == qtype and fail.operation == 9
+    assert dot(11, row, row.nbytes, x, width) == B.UNSUPPORTED and fail.code == 21 and fail.terminal_ordinal == 2 ** 64 - 1
+    assert dot(qtype, row, row.nbytes - 1, x, width) == B.BOUNDS and fail.code == 30 and (fail.expected, fail.actual) == (row.nbytes, row.nbytes - 1)
+    if qtype not in (synth.F32,):
+        elems = synth.BLOCKS[qtype][0]
+        assert dot(qtype, row, row.nbytes, x, width - 1) == B.BOUNDS and fail.code == 28 and (fail.expected, fail.actual) == (elems, width - 1)
+    monkeypatch.setenv("YVEX_TEST_CUDA_QTYPE_COPY_FAILURE", "input")
+    assert dot(qtype, row, row.nbytes, x, width) == B.BACKEND and fail.code == 45
+    monkeypatch.setenv("YVEX_TEST_CUDA_QTYPE_COPY_FAILURE", "output")
+    assert dot(qtype, row, row.nbytes, x, width) == B.BACKEND and fail.code == 45
+    monkeypatch.delenv("YVEX_TEST_CUDA_QTYPE_COPY_FAILURE")
+    assert dot(qtype, row, row.nbytes, x, width) == B.OK and fail.code == 0      # a refused copy does not demote the backend
+    if qtype == synth.IQ2_XXS:
+        bad = row.copy()
+        bad[0, 0:2] = [0x00, 0xFC]                                               # d = -inf
+        assert dot(qtype, bad, bad.nbytes, x, width) == B.FORMAT and fail.code == 37
+        assert dot(qtype, row, row.nbytes, x, width) == B.OK
+    assert be.close() == B.OK

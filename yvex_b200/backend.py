@@ -160,6 +160,25 @@ class RowBatchResult(C.Structure):
                            "expert_worklist_identity", "routing_digest", "execution_identity")]
 
 
+class RouterResult(C.Structure):
+    """yvex_moe_router_result (include/yvex/internal/moe.h:160-166)."""
+    _fields_ = [("selected_count", ull), ("selected_experts", ull * 16), ("router_logits", C.c_float * 256),
+                ("router_scores", C.c_float * 256), ("selected_weights", C.c_float * 16)]
+
+
+class LayerResult(C.Structure):
+    """yvex_moe_layer_result (include/yvex/internal/moe.h:198-214): the token-local transaction's outputs and counters."""
+    _fields_ = [("combined_output", vp), ("post", vp), ("combination", vp)] + [
+        (n, ull) for n in ("combined_capacity", "post_capacity", "combination_capacity")] + [("routed_output", vp), ("shared_output", vp)] + [
+        (n, ull) for n in ("routed_capacity", "shared_capacity")] + [("router", RouterResult)] + [
+        (n, ull) for n in ("expert_subviews_accessed", "encoded_bytes_read", "host_to_device_bytes", "device_to_host_bytes",
+                           "kernel_launches", "cache_hits", "cache_misses", "upload_count", "download_count",
+                           "stream_synchronizations", "device_synchronizations", "device_to_device_bytes")] + [
+        ("memory", MemoryFacts)] + [(n, ull) for n in ("ingress_ns", "routing_ns", "routed_ns", "shared_ns", "post_ns", "total_ns",
+                                                       "synchronization_ns")] + [("qtype_counts", ull * 43)] + [
+        (n, HEX) for n in ("routed_digest", "shared_digest", "combined_digest", "routing_digest")]
+
+
 _EXEC = C.CFUNCTYPE(C.c_int, vp, C.POINTER(LayerJob), vp, C.POINTER(RowBatchOutput), C.POINTER(RowBatchResult),
                     C.POINTER(Error))          # the batch by address: a RowBatch or a RowBatchLogits
 _WSREQ = C.CFUNCTYPE(C.c_int, C.POINTER(LayerPlan), ull, C.POINTER(ull), C.POINTER(Error))
@@ -175,6 +194,18 @@ class MoeOperations(C.Structure):
 
 _lib.yvex_backend_moe_operations_get.restype = C.POINTER(MoeOperations)
 _lib.yvex_backend_moe_operations_get.argtypes = [vp]
+_lib.yvex_backend_moe_begin.argtypes = [C.POINTER(vp), vp, C.POINTER(LayerJob), C.POINTER(LayerResult), C.POINTER(Error)]
+_lib.yvex_backend_moe_add_expert.argtypes = [vp, C.POINTER(WeightView), C.POINTER(WeightView), C.POINTER(WeightView), C.c_float, C.c_int,
+                                             C.POINTER(Error)]
+_lib.yvex_backend_moe_finish.argtypes = [vp, C.POINTER(LayerResult), C.POINTER(Error)]
+_lib.yvex_backend_moe_close.argtypes = [C.POINTER(vp), C.POINTER(Error)]
+class QuantFailure(C.Structure):
+    """yvex_quant_failure (include/yvex/internal/quant_numeric.h:83-93)."""
+    _fields_ = [("code", C.c_int)] + [(n, ull) for n in ("terminal_ordinal", "source_index", "row_index", "block_index", "expected", "actual")] + [
+        ("qtype", C.c_uint), ("operation", C.c_int)]
+
+
+_lib.yvex_cuda_quant_row_dot.argtypes = [vp, C.c_uint, vp, C.c_size_t, vp, ull, C.POINTER(C.c_float), C.POINTER(QuantFailure), C.POINTER(Error)]
 _lib.yvex_backend_open.argtypes = [C.POINTER(vp), C.POINTER(Options), C.POINTER(Error)]
 _lib.yvex_backend_close_checked.argtypes = [C.POINTER(vp), C.POINTER(Error)]
 _lib.yvex_backend_close.argtypes = [vp]
@@ -366,6 +397,20 @@ def moe_job(arena, spec, router=True, router_class=1, hash_rows=0, family=None, 
     view(W_SHARED_DOWN, "shared_down", spec.down_qtype, H, Is)
     job._plan = plan
     return job
+
+
+def expert_view(job, slot, expert, rows_per_expert):
+    """The weight view of one expert of a routed pack (what runtime_moe_load_expert of src/runtime/moe.c hands to add_expert)."""
+    pack = job.weights[slot]
+    v = WeightView()
+    C.memmove(C.byref(v), C.byref(pack), C.sizeof(WeightView))
+    offset = expert * rows_per_expert * pack.row_bytes
+    v.expert_index, v.row_count = expert, rows_per_expert
+    v.encoded_bytes = v.storage_bytes = rows_per_expert * pack.row_bytes
+    v.encoded = pack.encoded + offset
+    if pack.device_address:
+        v.device_address = pack.device_address + offset
+    return v
 
 
 def moe_ops(backend):

@@ -576,6 +576,84 @@ int yvex_backend_cuda_encoded_gather(yvex_backend *backend, const unsigned char 
     return YVEX_OK;
 }
 
+/* One encoded row against one f32 vector, both in HOST memory (src/backend/cuda/qtype.c:527-700): the row and the
+ * vector go up, a one-row dequant matvec runs, the f32 result comes back. Every refusal fills `failure` the way
+ * cuda_quant_fail does (src/backend/cuda/qtype.c:81-103) besides the error. */
+static int row_dot_fail(yvex_quant_failure *failure, int code, unsigned int qtype, unsigned long long expected, unsigned long long actual,
+                        yvex_error *err, int status, const char *message) {
+    if (failure) {
+        memset(failure, 0, sizeof(*failure));
+        failure->code = code;
+        failure->terminal_ordinal = failure->source_index = failure->block_index = ~0ull;
+        failure->expected = expected;
+        failure->actual = actual;
+        failure->qtype = qtype;
+        failure->operation = YVEX_TRANSFORM_OP_COUNT;
+    }
+    return yvex_refuse(err, (yvex_status)status, "cuda.quant.row_dot", message);
+}
+
+int yvex_cuda_quant_row_dot(yvex_backend *backend, unsigned int qtype, const unsigned char *encoded, size_t encoded_bytes,
+                            const float *vector, unsigned long long elements, float *out, yvex_quant_failure *failure, yvex_error *err) {
+    const char *where = "cuda.quant.row_dot";
+    unsigned int be = 0, bb = 0;
+    unsigned long long row_bytes, vector_bytes, enc_room;
+    unsigned char *scratch;
+    float *host_out;
+    int rc, code;
+    if (failure) memset(failure, 0, sizeof(*failure));
+    yvex_error_clear(err);
+    if (!backend || !encoded || !vector || !out || !elements || ((uintptr_t)vector % 4u) != 0u || ((uintptr_t)out % 4u) != 0u ||
+        ((qtype == 0u || qtype == 26u) && ((uintptr_t)encoded % 4u) != 0u) || ((qtype == 1u || qtype == 30u) && ((uintptr_t)encoded % 2u) != 0u))
+        return row_dot_fail(failure, YVEX_QUANT_FAILURE_INVALID_ARGUMENT, qtype, 1ull, 0ull, err, YVEX_ERR_INVALID_ARG,
+                            "CUDA encoded row, aligned vector/result, and backend are required");
+    rc = yvex_backend_admit(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    if (!yvex_b200_qtype_supported(qtype) || !yvex_b200_qtype_geometry(qtype, &be, &bb) || !be)
+        return row_dot_fail(failure, YVEX_QUANT_FAILURE_CUDA_COMPUTE_UNAVAILABLE, qtype, 1ull, 0ull, err, YVEX_ERR_UNSUPPORTED,
+                            "qtype has no dedicated CUDA numeric contract");
+    if (elements % be)
+        return row_dot_fail(failure, YVEX_QUANT_FAILURE_ROW_DIVISIBILITY, qtype, be, elements, err, YVEX_ERR_BOUNDS,
+                            "CUDA qtype row does not satisfy canonical block geometry");
+    row_bytes = elements / be * bb;
+    if (row_bytes != (unsigned long long)encoded_bytes || elements > SIZE_MAX / sizeof(float))
+        return row_dot_fail(failure, YVEX_QUANT_FAILURE_BYTE_OVERFLOW, qtype, row_bytes, encoded_bytes, err, YVEX_ERR_BOUNDS,
+                            "CUDA encoded row byte geometry is inconsistent");
+    vector_bytes = elements * 4ull;
+    enc_room = (row_bytes + 255ull) & ~255ull;
+    scratch = act_scratch(backend, enc_room + vector_bytes + 256ull);
+    if (!scratch) return row_dot_fail(failure, YVEX_QUANT_FAILURE_WORKER, qtype, 1ull, 0ull, err, YVEX_ERR_NOMEM, "no device memory for the row and the vector");
+    if (yvex_test_seam("YVEX_TEST_CUDA_QTYPE_COPY_FAILURE", "input"))
+        return row_dot_fail(failure, YVEX_QUANT_FAILURE_WORKER, qtype, 1ull, 0ull, err, YVEX_ERR_BACKEND, "injected CUDA qtype input copy failure");
+    /* pageable sources: the call returns only after the stream is idle, so they stay valid */
+    if (cudaMemcpyAsync(scratch, encoded, (size_t)row_bytes, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess ||
+        cudaMemcpyAsync(scratch + enc_room, vector, (size_t)vector_bytes, cudaMemcpyHostToDevice, backend->stream) != cudaSuccess) {
+        row_dot_fail(failure, YVEX_QUANT_FAILURE_WORKER, qtype, 1ull, 0ull, NULL, YVEX_ERR_BACKEND, "");
+        return yvex_backend_fail(backend, where, err);
+    }
+    rc = yvex_b200_gemv(qtype, scratch, 1ull, elements, row_bytes, (const float *)(scratch + enc_room), 1ull, NULL,
+                        (float *)(scratch + enc_room + vector_bytes), 0, backend->status_word, backend->stream);
+    if (rc == YVEX_ERR_BACKEND) {
+        row_dot_fail(failure, YVEX_QUANT_FAILURE_WORKER, qtype, 1ull, 0ull, NULL, YVEX_ERR_BACKEND, "");
+        return yvex_backend_fail(backend, where, err);
+    }
+    if (rc != YVEX_OK) return row_dot_fail(failure, YVEX_QUANT_FAILURE_WORKER, qtype, 1ull, 0ull, err, rc, "CUDA qtype encoded-row execution failed");
+    host_out = (float *)(backend->host_scratch + 1024);
+    if (cudaMemcpyAsync(host_out, scratch + enc_room + vector_bytes, sizeof(float), cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess ||
+        !yvex_backend_take_status(backend, &code)) {
+        row_dot_fail(failure, YVEX_QUANT_FAILURE_WORKER, qtype, 1ull, 0ull, NULL, YVEX_ERR_BACKEND, "");
+        return yvex_backend_fail(backend, where, err);
+    }
+    if (code) return row_dot_fail(failure, YVEX_QUANT_FAILURE_NONFINITE, qtype, 1ull, 0ull, err, YVEX_ERR_FORMAT,
+                                  "CUDA qtype row held a malformed block or produced a non-finite sum");
+    if (yvex_test_seam("YVEX_TEST_CUDA_QTYPE_COPY_FAILURE", "output"))
+        return row_dot_fail(failure, YVEX_QUANT_FAILURE_WORKER, qtype, 1ull, 0ull, err, YVEX_ERR_BACKEND, "injected CUDA qtype output copy failure");
+    *out = *host_out;
+    if (failure) memset(failure, 0, sizeof(*failure));
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
 /* ---- attention ---------------------------------------------------------------------------------------- */
 
 int yvex_backend_op_attention(yvex_backend *backend, const yvex_device_tensor *query, const yvex_device_tensor *keys,

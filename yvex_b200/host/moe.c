@@ -2,7 +2,8 @@
  * The MoE operation table of the host boundary: workspace_required / execute_rows / complete_rows
  * with the reference's contract (include/yvex/internal/moe.h:277-297, src/backend/cuda/moe.c:1826-1966),
  * plus the unbounded-width extension. The layer itself runs in the device layer
- * (yvex_b200_moe_decode for <= 62 rows, yvex_b200_moe_wide beyond).
+ * (yvex_b200_moe_decode for <= 62 rows, yvex_b200_moe_wide beyond). At the end of the file: the
+ * token-local transaction (begin / add_expert / finish / close), one expert per call.
  *
  * Two row shapes. Without the envelope (residual_streams <= 1, expanded_width == hidden_width) the
  * input rows are the normalized hidden rows, rounded to bf16 at ingress like the reference's
@@ -12,9 +13,12 @@
  * RMSNorm; src/graph/moe.c:446-495) -> layer -> post (src/graph/numeric.c:826-875). The envelope's
  * coefficient tensors must be resident F32; anything else is refused, never skipped.
  */
+#define _POSIX_C_SOURCE 200809L
 #include "backend_private.h"
 
+#include <stdlib.h>
 #include <string.h>
+#include <time.h>
 
 /* Row chunks of the wide entry's copy pipeline. Rows are independent, so a batch of host rows may
  * run as consecutive row ranges: while range i is computed, range i + 1 is on its way in and range
@@ -77,6 +81,19 @@ static unsigned long long staging_bytes(const yvex_b200_moe_geometry *g, unsigne
     return bytes;
 }
 
+/* Scratch of the token-local transaction (one row, one expert at a time). */
+static unsigned long long token_inter(const yvex_b200_moe_geometry *g) { return g->inter > g->shared_inter ? g->inter : g->shared_inter; }
+static unsigned long long token_bytes(const yvex_b200_moe_geometry *g, unsigned long long streams) {
+    unsigned long long bytes = 2ull * align256(streams * g->hidden * 4ull) + 5ull * align256(g->hidden * 4ull) + 3ull * align256(token_inter(g) * 4ull) +
+                               2ull * align256(g->experts * 4ull) + 2ull * align256(g->topk * 4ull) + 512ull;
+    if (streams > 1ull) {
+        const unsigned long long mix_rows = (streams + 2ull) * streams;
+        bytes += align256(streams * 4ull) + align256(streams * streams * 4ull) + align256(yvex_b200_mhc_workspace_bytes(streams, 1ull)) +
+                 align256(g->hidden * 4ull) + align256(mix_rows * streams * g->hidden * 4ull) + align256(mix_rows * 4ull) + align256(12ull);
+    }
+    return bytes;
+}
+
 static int workspace_for(const yvex_moe_layer_plan *layer, unsigned long long rows, int wide, unsigned long long *bytes, yvex_error *err) {
     yvex_b200_moe_geometry g;
     if (bytes) *bytes = 0;
@@ -88,6 +105,7 @@ static int workspace_for(const yvex_moe_layer_plan *layer, unsigned long long ro
         unsigned long long kernel = wide ? yvex_b200_moe_wide_workspace_bytes(&g, rows) : yvex_b200_moe_workspace_bytes(&g, rows);
         const unsigned long long list = yvex_b200_expert_worklist_workspace_bytes(rows * g.topk, g.experts);
         *bytes = staging_bytes(&g, rows, envelope_streams(layer)) + (kernel > list ? kernel : list);
+        if (*bytes < token_bytes(&g, envelope_streams(layer))) *bytes = token_bytes(&g, envelope_streams(layer));
     }
     yvex_error_clear(err);
     return YVEX_OK;
@@ -580,6 +598,394 @@ static int moe_complete_rows(yvex_backend *backend, int barrier_observed, yvex_m
         }
     }
     if (code) return status_error(code, err);
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+/* ---- token-local transaction (src/backend/cuda/moe.c:504-848) ---------------------------------------- */
+
+static unsigned long long monotonic_ns(void) {
+    struct timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return (unsigned long long)ts.tv_sec * 1000000000ull + (unsigned long long)ts.tv_nsec;
+}
+
+struct yvex_backend_moe_execution {
+    yvex_backend *backend;
+    const yvex_moe_layer_job *job;
+    yvex_b200_moe_geometry g;
+    yvex_b200_mhc mhc;
+    unsigned long long streams, scratch_bytes;
+    const float *expanded;                     /* device: the expanded input row */
+    float *normalized, *post, *combination, *logits, *scores, *weights;
+    int32_t *selected;
+    float *gate, *up, *mid, *expert, *routed, *shared, *combined;
+    unsigned long long launches0, h2d, d2h, uploads, downloads, subviews, direct_weights, syncs, d2d;
+    unsigned long long started_ns, ingress_ns, routing_ns, routed_ns, shared_ns, sync_ns;
+    int full_evidence, grouped_selected, finished;
+};
+
+#define TOKEN_FULL_EVIDENCE 3                  /* YVEX_ATTENTION_EVIDENCE_FULL */
+
+static int token_device_rc(yvex_backend *backend, int rc, const char *where, const char *message, yvex_error *err) {
+    if (rc == YVEX_OK) return YVEX_OK;
+    if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
+    return yvex_refuse(err, (yvex_status)rc, where, message);
+}
+
+static int token_download(yvex_backend_moe_execution *x, void *host, const void *dev, unsigned long long bytes, const char *where, yvex_error *err) {
+    if (cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, x->backend->stream) != cudaSuccess)
+        return yvex_backend_fail(x->backend, where, err);
+    x->d2h += bytes;
+    x->downloads++;
+    return YVEX_OK;
+}
+
+static int token_sync(yvex_backend_moe_execution *x, const char *where, yvex_error *err) {
+    const unsigned long long t0 = monotonic_ns();
+    int code;
+    if (!yvex_backend_take_status(x->backend, &code)) return yvex_backend_fail(x->backend, where, err);
+    x->sync_ns += monotonic_ns() - t0;
+    x->syncs++;
+    x->d2h += sizeof(int);
+    return status_error(code, err);
+}
+
+/* One expert: gate and up matvecs, SwiGLU * weight -> bf16, down matvec -> bf16, added to `aggregate`. */
+static int token_expert(yvex_backend_moe_execution *x, const yvex_moe_weight_view *gate, const void *gate_at, const yvex_moe_weight_view *up,
+                        const void *up_at, const yvex_moe_weight_view *down, const void *down_at, float weight, float *aggregate,
+                        yvex_error *err) {
+    yvex_backend *b = x->backend;
+    const unsigned long long inter = gate->row_count, hidden = x->g.hidden;
+    int rc = yvex_b200_gemv(gate->qtype, gate_at, inter, hidden, gate->row_bytes, x->normalized, 1ull, NULL, x->gate, 0, b->status_word, b->stream);
+    if (rc == YVEX_OK)
+        rc = yvex_b200_gemv(up->qtype, up_at, inter, hidden, up->row_bytes, x->normalized, 1ull, NULL, x->up, 0, b->status_word, b->stream);
+    if (rc == YVEX_OK) rc = yvex_b200_moe_token_swiglu(x->gate, x->up, inter, x->g.limit, weight, x->mid, b->status_word, b->stream);
+    if (rc == YVEX_OK)
+        rc = yvex_b200_gemv(down->qtype, down_at, hidden, inter, down->row_bytes, x->mid, 1ull, NULL, x->expert, 1, b->status_word, b->stream);
+    if (rc == YVEX_OK) rc = yvex_b200_moe_token_accumulate(x->expert, hidden, aggregate, b->status_word, b->stream);
+    return token_device_rc(b, rc, "cuda.moe.add_expert", "device layer refused the expert geometry", err);
+}
+
+static int token_expert_views(yvex_backend_moe_execution *x, const yvex_moe_weight_view *gate, const yvex_moe_weight_view *up,
+                              const yvex_moe_weight_view *down, float weight, int shared, yvex_error *err) {
+    const char *where = "cuda.moe.add_expert";
+    const yvex_moe_weight_view *v[3] = {gate, up, down};
+    const void *at[3];
+    const unsigned long long started = monotonic_ns();
+    int rc;
+    if (gate->row_count != up->row_count || down->row_width != gate->row_count || down->row_count != x->g.hidden ||
+        gate->row_width != x->g.hidden || up->row_width != x->g.hidden)
+        return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "CUDA MoE expert geometry is invalid");
+    if (gate->row_count > token_inter(&x->g)) return yvex_refuse(err, YVEX_ERR_BOUNDS, where, "expert is wider than the layer's intermediate width");
+    for (int i = 0; i < 3; ++i) {
+        if (!family_admitted(v[i]->kernel_family) || v[i]->layout == YVEX_EXECUTION_LAYOUT_DERIVED_BACKEND)
+            return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "kernel family or weight layout is not one this backend executes");
+        if (!yvex_b200_qtype_supported(v[i]->qtype))
+            return yvex_refuse(err, YVEX_ERR_UNSUPPORTED, where, "expert qtype has no device decoder in this backend");
+        if (!view_consistent(v[i], v[i]->row_count, v[i]->row_width))
+            return yvex_refuse(err, YVEX_ERR_FORMAT, where, "expert weight view is inconsistent with its qtype");
+        if (!resolve_view(x->backend, v[i], 1, &at[i]))
+            return yvex_refuse(err, YVEX_ERR_STATE, where, "MoE weights are not resident on this backend");
+    }
+    rc = token_expert(x, gate, at[0], up, at[1], down, at[2], shared ? 1.0f : weight, shared ? x->shared : x->routed, err);
+    if (rc != YVEX_OK) return rc;
+    x->direct_weights += 3ull;
+    x->subviews += shared ? 0ull : 3ull;
+    if (shared) x->shared_ns += monotonic_ns() - started;
+    else x->routed_ns += monotonic_ns() - started;
+    return YVEX_OK;
+}
+
+/* The selected experts out of the routed packs, in rank order (moe_cuda_add_selected, src/backend/cuda/moe.c:586-671). */
+static int token_add_selected(yvex_backend_moe_execution *x, const yvex_moe_router_result *router, yvex_error *err) {
+    const yvex_moe_layer_job *job = x->job;
+    static const int slots[3] = {YVEX_MOE_WEIGHT_ROUTED_GATE, YVEX_MOE_WEIGHT_ROUTED_UP, YVEX_MOE_WEIGHT_ROUTED_DOWN};
+    const unsigned long long rows_per[3] = {x->g.inter, x->g.inter, x->g.hidden}, width[3] = {x->g.hidden, x->g.hidden, x->g.inter};
+    for (int i = 0; i < 3; ++i)
+        if (!view_consistent(&job->weights[slots[i]], x->g.experts * rows_per[i], width[i]))
+            return yvex_refuse(err, YVEX_ERR_FORMAT, "cuda.moe.begin", "CUDA grouped selected-expert geometry is incompatible");
+    for (unsigned long long rank = 0; rank < router->selected_count; ++rank) {
+        yvex_moe_weight_view v[3];
+        const unsigned long long e = router->selected_experts[rank];
+        int rc;
+        if (e >= x->g.experts) return yvex_refuse(err, YVEX_ERR_BOUNDS, "cuda.moe.begin", "router selected an expert outside the layer");
+        for (int i = 0; i < 3; ++i) {
+            const unsigned long long offset = e * rows_per[i] * job->weights[slots[i]].row_bytes;
+            v[i] = job->weights[slots[i]];
+            v[i].expert_index = e;
+            v[i].row_count = rows_per[i];
+            v[i].encoded_bytes = v[i].storage_bytes = (size_t)(rows_per[i] * v[i].row_bytes);
+            v[i].encoded = v[i].encoded ? v[i].encoded + offset : NULL;
+            v[i].device_address += offset;
+        }
+        rc = token_expert_views(x, &v[0], &v[1], &v[2], router->selected_weights[rank], 0, err);
+        if (rc != YVEX_OK) return rc;
+    }
+    return YVEX_OK;
+}
+
+int yvex_backend_moe_close(yvex_backend_moe_execution **execution, yvex_error *err) {
+    if (execution && *execution) {
+        free(*execution);
+        *execution = NULL;
+    }
+    yvex_error_clear(err);
+    return YVEX_OK;
+}
+
+int yvex_backend_moe_begin(yvex_backend_moe_execution **out, yvex_backend *backend, const yvex_moe_layer_job *job,
+                           yvex_moe_layer_result *result, yvex_error *err) {
+    const char *where = "cuda.moe.begin";
+    const yvex_moe_layer_plan *layer = job ? job->layer : NULL;
+    static const int coeff[4] = {YVEX_MOE_WEIGHT_FFN_NORM, YVEX_MOE_WEIGHT_MHC_FUNCTION, YVEX_MOE_WEIGHT_MHC_BASE, YVEX_MOE_WEIGHT_MHC_SCALE};
+    static const int routing[3] = {YVEX_MOE_WEIGHT_ROUTER, YVEX_MOE_WEIGHT_ROUTER_TABLE, YVEX_MOE_WEIGHT_ROUTER_BIAS};
+    yvex_backend_moe_execution *x;
+    yvex_b200_moe_weights w;
+    unsigned long long cursor = 0, streams, in_bytes, hid_bytes, inter_bytes, coeff_count[4] = {0, 0, 0, 0}, mhc_ws = 0, routed_started;
+    unsigned char *ws_in, *ws_token, *ws_mhc = NULL, *ws_coeff[4] = {NULL, NULL, NULL, NULL};
+    const void *addr[YVEX_MOE_WEIGHT_COUNT];
+    const yvex_moe_weight_view *router;
+    int rc;
+    if (out) *out = NULL;
+    if (!out || !backend || !job || !layer || !result || (!job->expanded_input && !job->device_input) || !result->combined_output ||
+        result->combined_capacity < layer->hidden_width)
+        return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "CUDA MoE begin arguments are invalid");
+    streams = envelope_streams(layer);
+    if (streams > 1ull && (!result->post || result->post_capacity < streams || !result->combination || result->combination_capacity < streams * streams))
+        return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "CUDA MoE begin arguments are invalid");
+    rc = yvex_backend_admit(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    if (backend->pending_slot) return yvex_refuse(err, YVEX_ERR_STATE, where, "a deferred MoE completion is still pending");
+    if (yvex_test_seam("YVEX_TEST_CUDA_LAUNCH_FAILURE", "moe-token")) return yvex_backend_fail(backend, where, err);
+    if (layer->expanded_width && layer->expanded_width != streams * layer->hidden_width)
+        return yvex_refuse(err, YVEX_ERR_FORMAT, where, "expanded width is not residual streams x hidden width");
+    if (streams > 1ull && layer->mhc_mixing_rows != (streams + 2ull) * streams)
+        return yvex_refuse(err, YVEX_ERR_FORMAT, where, "mHC mixing rows must be (streams + 2) x streams");
+    in_bytes = streams * layer->hidden_width * 4ull;
+    if ((job->device_input || job->device_output) &&
+        (!yvex_tensor_owned(backend, job->device_input) || !yvex_tensor_owned(backend, job->device_output) ||
+         job->device_input->dtype != YVEX_DTYPE_F32 || job->device_output->dtype != YVEX_DTYPE_F32 || job->device_input->bytes != in_bytes ||
+         job->device_output->bytes != in_bytes || !job->device_input->is_written))
+        return yvex_refuse(err, YVEX_ERR_FORMAT, where, "CUDA MoE device activation views are incompatible");
+    if (job->cancel_requested && job->cancel_requested(job->cancel_context))
+        return yvex_refuse(err, YVEX_ERR_CANCELLED, where, "MoE execution was cancelled");
+    x = (yvex_backend_moe_execution *)calloc(1u, sizeof(*x));
+    if (!x) return yvex_refuse(err, YVEX_ERR_NOMEM, where, "CUDA MoE owner allocation failed");
+    x->backend = backend;
+    x->job = job;
+    x->streams = streams;
+    x->started_ns = monotonic_ns();
+    x->launches0 = yvex_b200_launch_count();
+    x->full_evidence = job->evidence_level == TOKEN_FULL_EVIDENCE;
+    x->grouped_selected = job->device_output && !x->full_evidence && job->weights[YVEX_MOE_WEIGHT_ROUTED_GATE].device_address &&
+                          job->weights[YVEX_MOE_WEIGHT_ROUTED_UP].device_address && job->weights[YVEX_MOE_WEIGHT_ROUTED_DOWN].device_address;
+    plan_geometry(layer, job, &x->g);
+#define TOKEN_FAIL(code_, message_) do { rc = yvex_refuse(err, (code_), where, (message_)); goto fail; } while (0)
+    if (x->g.experts > 256ull || x->g.topk > YVEX_MOE_MAX_SELECTED || !x->g.topk || x->g.topk > x->g.experts)
+        TOKEN_FAIL(YVEX_ERR_BOUNDS, "router geometry exceeds the router result's capacity");
+    for (int i = 0; i < 3; ++i)
+        if (!resolve_view(backend, &job->weights[routing[i]], 0, &addr[routing[i]])) TOKEN_FAIL(YVEX_ERR_STATE, "MoE weights are not resident on this backend");
+    router = &job->weights[YVEX_MOE_WEIGHT_ROUTER];
+    if (!addr[YVEX_MOE_WEIGHT_ROUTER]) TOKEN_FAIL(YVEX_ERR_STATE, "router weights are not resident on this backend");
+    if (!yvex_b200_qtype_supported(router->qtype)) TOKEN_FAIL(YVEX_ERR_UNSUPPORTED, "router qtype has no device decoder in this backend");
+    if (!view_consistent(router, x->g.experts, x->g.hidden)) TOKEN_FAIL(YVEX_ERR_FORMAT, "router weight view is inconsistent with the layer geometry");
+    if (x->g.router_class == 0 && (!job->token_id_present || job->token_id >= layer->hash_table_rows || !addr[YVEX_MOE_WEIGHT_ROUTER_TABLE]))
+        TOKEN_FAIL(YVEX_ERR_BOUNDS, "CUDA hash router token ID is invalid");
+    memset(&w, 0, sizeof(w));
+    w.router = router->qtype == 0u ? (const float *)addr[YVEX_MOE_WEIGHT_ROUTER] : NULL;
+    w.bias = (const float *)addr[YVEX_MOE_WEIGHT_ROUTER_BIAS];
+    w.hash_table = (const int32_t *)addr[YVEX_MOE_WEIGHT_ROUTER_TABLE];
+    if (streams > 1ull) {
+        const unsigned long long mix_rows = (streams + 2ull) * streams;
+        coeff_count[0] = x->g.hidden; coeff_count[1] = mix_rows * streams * x->g.hidden; coeff_count[2] = mix_rows; coeff_count[3] = 3ull;
+        for (int i = 0; i < 4; ++i) {
+            const yvex_moe_weight_view *v = &job->weights[coeff[i]];
+            if (!resolve_view(backend, v, 1, &addr[coeff[i]])) TOKEN_FAIL(YVEX_ERR_STATE, "mHC envelope coefficients are not resident on this backend");
+            if (!((v->qtype == 0u && v->encoded_bytes == coeff_count[i] * 4ull) || (v->qtype == 30u && v->encoded_bytes == coeff_count[i] * 2ull)))
+                TOKEN_FAIL(YVEX_ERR_UNSUPPORTED, "mHC envelope coefficients must be F32 or BF16 tensors of the layer's geometry");
+        }
+        x->mhc.hidden = x->g.hidden; x->mhc.streams = streams; x->mhc.sinkhorn_iterations = layer->mhc_sinkhorn_iterations;
+        x->mhc.rms_epsilon = layer->rms_epsilon; x->mhc.mhc_epsilon = layer->mhc_epsilon; x->mhc.post_multiplier = layer->mhc_post_multiplier;
+        x->mhc.norm = (const float *)addr[YVEX_MOE_WEIGHT_FFN_NORM];
+        x->mhc.mhc_fn = (const float *)addr[YVEX_MOE_WEIGHT_MHC_FUNCTION];
+        x->mhc.base = (const float *)addr[YVEX_MOE_WEIGHT_MHC_BASE];
+        x->mhc.scale = (const float *)addr[YVEX_MOE_WEIGHT_MHC_SCALE];
+        mhc_ws = yvex_b200_mhc_workspace_bytes(streams, 1ull);
+    }
+    /* ranges of the attached workspace, from its start: a transaction owns it until finish */
+    hid_bytes = x->g.hidden * 4ull;
+    inter_bytes = token_inter(&x->g) * 4ull;
+    ws_in = yvex_workspace_take(backend, &cursor, in_bytes);
+    x->normalized = (float *)yvex_workspace_take(backend, &cursor, hid_bytes);
+    x->expert = (float *)yvex_workspace_take(backend, &cursor, hid_bytes);
+    x->routed = (float *)yvex_workspace_take(backend, &cursor, hid_bytes);
+    x->shared = (float *)yvex_workspace_take(backend, &cursor, hid_bytes);
+    x->combined = (float *)yvex_workspace_take(backend, &cursor, hid_bytes);
+    x->gate = (float *)yvex_workspace_take(backend, &cursor, inter_bytes);
+    x->up = (float *)yvex_workspace_take(backend, &cursor, inter_bytes);
+    x->mid = (float *)yvex_workspace_take(backend, &cursor, inter_bytes);
+    x->logits = (float *)yvex_workspace_take(backend, &cursor, x->g.experts * 4ull);
+    x->scores = (float *)yvex_workspace_take(backend, &cursor, x->g.experts * 4ull);
+    x->selected = (int32_t *)yvex_workspace_take(backend, &cursor, x->g.topk * 4ull);
+    x->weights = (float *)yvex_workspace_take(backend, &cursor, x->g.topk * 4ull);
+    ws_token = yvex_workspace_take(backend, &cursor, 4ull);
+    if (streams > 1ull) {
+        x->post = (float *)yvex_workspace_take(backend, &cursor, streams * 4ull);
+        x->combination = (float *)yvex_workspace_take(backend, &cursor, streams * streams * 4ull);
+        ws_mhc = yvex_workspace_take(backend, &cursor, mhc_ws);
+        for (int i = 0; i < 4; ++i) ws_coeff[i] = yvex_workspace_take(backend, &cursor, coeff_count[i] * 4ull);
+    }
+    if (!ws_in || !x->normalized || !x->expert || !x->routed || !x->shared || !x->combined || !x->gate || !x->up || !x->mid || !x->logits ||
+        !x->scores || !x->selected || !x->weights || !ws_token ||
+        (streams > 1ull && (!x->post || !x->combination || !ws_mhc || !ws_coeff[0] || !ws_coeff[1] || !ws_coeff[2] || !ws_coeff[3])))
+        TOKEN_FAIL(YVEX_ERR_NOMEM, "attached device workspace is smaller than workspace_required");
+    x->scratch_bytes = cursor;
+#define TOKEN_CUDA(call_) do { if ((call_) != cudaSuccess) { rc = yvex_backend_fail(backend, where, err); goto fail; } } while (0)
+#define TOKEN_DEVICE(call_, message_) do { rc = token_device_rc(backend, (call_), where, (message_), err); if (rc != YVEX_OK) goto fail; } while (0)
+    /* ingress */
+    if (job->device_input) {
+        x->expanded = (const float *)job->device_input->data;
+    } else {
+        TOKEN_CUDA(cudaMemcpyAsync(ws_in, job->expanded_input, in_bytes, cudaMemcpyHostToDevice, backend->stream));
+        x->h2d += in_bytes;
+        x->uploads++;
+        x->expanded = (const float *)ws_in;
+    }
+    TOKEN_CUDA(cudaMemsetAsync(x->routed, 0, hid_bytes, backend->stream));
+    TOKEN_CUDA(cudaMemsetAsync(x->shared, 0, hid_bytes, backend->stream));
+    if (streams > 1ull) {
+        const float **slot_ptr[4] = {&x->mhc.norm, &x->mhc.mhc_fn, &x->mhc.base, &x->mhc.scale};
+        for (int i = 0; i < 4; ++i) {
+            if (job->weights[coeff[i]].qtype != 30u) continue;
+            TOKEN_DEVICE(yvex_b200_dequant_rows(30u, addr[coeff[i]], 1ull, coeff_count[i], coeff_count[i] * 2ull, (float *)ws_coeff[i],
+                                                backend->status_word, backend->stream), "device layer refused an mHC coefficient tensor");
+            *slot_ptr[i] = (const float *)ws_coeff[i];
+        }
+        TOKEN_DEVICE(yvex_b200_mhc_prepare(&x->mhc, x->expanded, 1ull, x->normalized, x->post, x->combination, ws_mhc, mhc_ws,
+                                           backend->status_word, backend->stream), "device layer refused the mHC envelope geometry");
+    } else {
+        TOKEN_DEVICE(yvex_b200_moe_token_round(x->expanded, x->g.hidden, x->normalized, backend->status_word, backend->stream),
+                     "device layer refused the ingress row");
+    }
+    routed_started = monotonic_ns();
+    x->ingress_ns = routed_started - x->started_ns;
+    /* router: projection (double accumulation for F32 rows, the dequant matvec otherwise), scores, top-k or the hash row */
+    if (x->g.router_class == 0) {
+        TOKEN_CUDA(cudaMemcpyAsync(ws_token, &job->token_id, 4ull, cudaMemcpyHostToDevice, backend->stream));
+        x->h2d += 4ull;
+    }
+    if (!w.router)
+        TOKEN_DEVICE(yvex_b200_gemv(router->qtype, addr[YVEX_MOE_WEIGHT_ROUTER], x->g.experts, x->g.hidden, router->row_bytes, x->normalized, 1ull,
+                                    NULL, x->logits, 0, backend->status_word, backend->stream), "device layer refused the router projection");
+    TOKEN_DEVICE(yvex_b200_moe_route(&x->g, &w, x->normalized, w.router ? NULL : x->logits, x->g.router_class == 0 ? (const uint32_t *)ws_token : NULL,
+                                     1ull, x->selected, x->weights, x->logits, NULL, 0ull, backend->status_word, backend->stream),
+                 "device layer refused the router geometry");
+    TOKEN_DEVICE(yvex_b200_moe_token_scores(x->logits, x->g.experts, x->scores, backend->status_word, backend->stream),
+                 "device layer refused the router scores");
+    x->direct_weights += 1ull + (w.bias ? 1ull : 0ull);
+    {
+        int32_t *host_selected = (int32_t *)(backend->host_scratch + 2048);
+        memset(&result->router, 0, sizeof(result->router));
+        if (!job->device_output || x->full_evidence) {
+            rc = token_download(x, result->router.router_logits, x->logits, x->g.experts * 4ull, where, err);
+            if (rc == YVEX_OK) rc = token_download(x, result->router.router_scores, x->scores, x->g.experts * 4ull, where, err);
+            if (rc != YVEX_OK) goto fail;
+        }
+        rc = token_download(x, host_selected, x->selected, x->g.topk * 4ull, where, err);
+        if (rc == YVEX_OK) rc = token_download(x, result->router.selected_weights, x->weights, x->g.topk * 4ull, where, err);
+        if (rc == YVEX_OK) rc = token_sync(x, where, err);
+        if (rc != YVEX_OK) goto fail;
+        result->router.selected_count = x->g.topk;
+        for (unsigned long long r = 0; r < x->g.topk; ++r)
+            result->router.selected_experts[r] = host_selected[r] < 0 ? ~0ull : (unsigned long long)host_selected[r];
+    }
+    x->routing_ns = monotonic_ns() - routed_started;
+    if (x->grouped_selected) {
+        rc = token_add_selected(x, &result->router, err);
+        if (rc != YVEX_OK) goto fail;
+    }
+    *out = x;
+    yvex_error_clear(err);
+    return YVEX_OK;
+fail:
+    free(x);
+    return rc;
+}
+
+int yvex_backend_moe_add_expert(yvex_backend_moe_execution *execution, const yvex_moe_weight_view *gate, const yvex_moe_weight_view *up,
+                                const yvex_moe_weight_view *down, float route_weight, int shared, yvex_error *err) {
+    int rc;
+    if (!execution || !execution->job || !gate || !up || !down || execution->finished)
+        return yvex_refuse(err, YVEX_ERR_INVALID_ARG, "cuda.moe.add_expert", "CUDA MoE expert geometry is invalid");
+    rc = yvex_backend_admit(execution->backend, "cuda.moe.add_expert", err);
+    if (rc != YVEX_OK) return rc;
+    rc = token_expert_views(execution, gate, up, down, route_weight, shared, err);
+    if (rc == YVEX_OK) yvex_error_clear(err);
+    return rc;
+}
+
+int yvex_backend_moe_finish(yvex_backend_moe_execution *execution, yvex_moe_layer_result *result, yvex_error *err) {
+    const char *where = "cuda.moe.finish";
+    yvex_backend_moe_execution *x = execution;
+    const yvex_moe_layer_job *job = x ? x->job : NULL;
+    yvex_backend *backend = x ? x->backend : NULL;
+    unsigned long long hid_bytes;
+    int rc;
+    if (!x || !job || !result || x->finished) return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "CUDA MoE finish is invalid");
+    if (!result->routed_output || result->routed_capacity < x->g.hidden || !result->shared_output || result->shared_capacity < x->g.hidden)
+        return yvex_refuse(err, YVEX_ERR_INVALID_ARG, where, "CUDA MoE routed/shared publication capacity is invalid");
+    rc = yvex_backend_admit(backend, where, err);
+    if (rc != YVEX_OK) return rc;
+    hid_bytes = x->g.hidden * 4ull;
+    rc = token_device_rc(backend, yvex_b200_moe_token_sum_round(x->routed, x->shared, x->g.hidden, x->combined, backend->status_word, backend->stream),
+                         where, "device layer refused the combination", err);
+    if (rc != YVEX_OK) return rc;
+    if (job->device_output) {
+        job->device_output->is_written = 0;
+        if (x->streams > 1ull) {
+            rc = token_device_rc(backend, yvex_b200_mhc_post(&x->mhc, x->combined, x->expanded, x->post, x->combination, 1ull,
+                                                             (float *)job->device_output->data, backend->status_word, backend->stream),
+                                 where, "device layer refused the mHC envelope geometry", err);
+            if (rc != YVEX_OK) return rc;
+        } else {
+            if (cudaMemcpyAsync(job->device_output->data, x->combined, hid_bytes, cudaMemcpyDeviceToDevice, backend->stream) != cudaSuccess)
+                return yvex_backend_fail(backend, where, err);
+            x->d2d += hid_bytes;
+        }
+    }
+    if (!job->device_output || x->full_evidence) {
+        rc = token_download(x, result->combined_output, x->combined, hid_bytes, where, err);
+        if (rc == YVEX_OK) rc = token_download(x, result->routed_output, x->routed, hid_bytes, where, err);
+        if (rc == YVEX_OK) rc = token_download(x, result->shared_output, x->shared, hid_bytes, where, err);
+        if (rc == YVEX_OK && x->streams > 1ull) rc = token_download(x, result->post, x->post, x->streams * 4ull, where, err);
+        if (rc == YVEX_OK && x->streams > 1ull)
+            rc = token_download(x, result->combination, x->combination, x->streams * x->streams * 4ull, where, err);
+        if (rc != YVEX_OK) return rc;
+    }
+    rc = token_sync(x, where, err);
+    if (rc != YVEX_OK) return rc;
+    if (job->device_output) job->device_output->is_written = 1;
+    if (job->device_input && job->device_output) {
+        result->memory.activation_bytes = 2ull * x->streams * hid_bytes;
+        result->memory.temporary_bytes = x->scratch_bytes;
+    }
+    result->expert_subviews_accessed += x->subviews;
+    result->host_to_device_bytes += x->h2d;
+    result->device_to_host_bytes += x->d2h;
+    result->kernel_launches += yvex_b200_launch_count() - x->launches0;
+    result->upload_count += x->uploads;
+    result->download_count += x->downloads;
+    result->cache_hits += x->direct_weights;
+    result->device_to_device_bytes += x->d2d;
+    result->stream_synchronizations += x->syncs;
+    result->synchronization_ns += x->sync_ns;
+    result->ingress_ns += x->ingress_ns;
+    result->routing_ns += x->routing_ns;
+    result->routed_ns += x->routed_ns;
+    result->shared_ns += x->shared_ns;
+    result->total_ns += monotonic_ns() - x->started_ns;
+    x->finished = 1;
     yvex_error_clear(err);
     return YVEX_OK;
 }
