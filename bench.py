@@ -555,6 +555,60 @@ def run_native_ep(args):
             if rc_b != B.OK:
                 raise RuntimeError("execute_rows_wide: " + be.message())
 
+        def two_sessions(steps):
+            """The same steps issued the way a server with two execution sessions issues them: two backend objects
+            (each with its own resident copy of the weights, workspace and stream) take alternate steps with deferred
+            completion, so one session's host copies run beside the other's GEMMs. Every step still copies its rows
+            in from pinned host memory and its result rows back out inside the timed region."""
+            be2 = B.Backend(device=f"cuda:{local}".encode())
+            if be2.rc != B.OK:
+                raise RuntimeError("second session failed to open: " + be2.message())
+            arena2 = B.ResidentArena(be2, {k: v.cpu().numpy() for k, v in wl.tensors.items()})
+            job2 = B.moe_job(arena2, spec, router=False, family=b"sm100-f16-tcgen05-expert")
+            rc2, ws2, _ = be2.tensor(need.value)
+            assert rc2 == B.OK and B._lib.yvex_backend_workspace_attach(be2.h, ws2, C.byref(be2.err)) == B.OK
+            out2 = torch.empty((T, H), dtype=torch.float32).pin_memory()
+            sess = []
+            for b_, j_, o_ in ((be, job, host_out), (be2, job2, out2)):
+                slot = B.CompletionSlot()
+                comp = B.Completion(1, C.pointer(slot))
+                j_.device_completion = C.pointer(comp)
+                sess.append(dict(be=b_, job=j_, out=B.row_output(o_.data_ptr(), T * H), res=B.RowBatchResult(), ops=B.moe_ops(b_),
+                                 keep=(slot, comp), pending=False))
+
+            def finish(s_):
+                if s_["pending"] and s_["ops"].complete_rows(s_["be"].h, 0, C.byref(s_["res"]), C.byref(s_["be"].err)) != B.OK:
+                    raise RuntimeError("complete_rows: " + s_["be"].message())
+                s_["pending"] = False
+
+            def run(n):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for i in range(n):
+                    s_ = sess[i & 1]
+                    finish(s_)
+                    if s_["ops"].execute_rows_wide(s_["be"].h, C.byref(s_["job"]), C.byref(batch), C.byref(s_["out"]), C.byref(s_["res"]),
+                                                   C.byref(s_["be"].err)) != B.OK:
+                        raise RuntimeError("execute_rows_wide (deferred): " + s_["be"].message())
+                    s_["pending"] = True
+                for s_ in sess:
+                    finish(s_)
+                return time.perf_counter() - t0
+
+            try:
+                run(2)
+                n = max(4, steps + (steps & 1))
+                t = run(n)
+                same = torch.equal(out2.view(torch.int32), host_out.view(torch.int32))
+            finally:
+                job.device_completion = None
+                be2.close()
+            if not same:
+                raise RuntimeError("the two sessions' result rows differ")
+            return {"value": T * n / t, "unit": UNIT, "steps": n, "ms_per_step": t / n * 1e3, "l2": "inputs larger than L2 (4.5 GB per step)",
+                    "api": "two yvex_backend objects alternate steps: execute_rows_wide with deferred completion, complete_rows "
+                           "before a session's next step; pinned host rows in and out every step"}
+
     def barrier():
         if world > 1:
             dist.barrier()
@@ -647,8 +701,14 @@ def run_native_ep(args):
         torch.cuda.synchronize()
         if not torch.equal(host_out.view(torch.int32), step(0).cpu().view(torch.int32)):
             raise RuntimeError("execute_rows_wide (host rows) differs from the device-resident layer")
-    twin = gemv = None
+    twin = gemv = sessions2 = None
     if world == 1 and rank == 0:
+        try:
+            sessions2 = two_sessions(args.steps)
+        except RuntimeError:
+            raise
+        except Exception as exc:                                # e.g. out of memory for the second resident copy
+            sessions2 = {"value": None, "failed": str(exc)}
         try:
             twin = pinned_twin(torch, lib, args, flush, status, dev)
         except RuntimeError:
@@ -711,6 +771,7 @@ def run_native_ep(args):
                 "clocks": clocks.summary(),
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(T * (H + E) * 4),
                         "d2h_bytes_per_step": int(T * H * 4), "api": e2e_api},
+                **({"e2e_two_sessions": sessions2} if sessions2 else {}),
                 "gpu_launches": int(launches * world),
                 "phases_ms": {"gate_up_gemm": gu, "swiglu": sw, "down_gemm": dn,
                               **({"pairs_in_timed_gemm": pairs, "step_spans_rank0": {k: sum(v) / len(v) for k, v in spans.items()}}

@@ -274,7 +274,7 @@ typedef struct {
 typedef yvex_b200_worklist_observation yvex_expert_worklist_observation;
 typedef struct {
     unsigned long long row_count, row_expert_pairs;
-    yvex_expert_worklist_observation worklist;       /* copied with the status word in deferred mode (src/backend/cuda/moe.c:1710-1716) */
+    yvex_expert_worklist_observation worklist;       /* with the status word in deferred mode (src/backend/cuda/moe.c:1710-1716): filled by complete_rows */
     unsigned long long tensor_core_executed_pairs;
     unsigned long long routed_experts, active_base_bytes, active_per_expert_bytes;
     unsigned long long activation_bytes, temporary_bytes;

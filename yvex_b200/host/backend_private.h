@@ -34,6 +34,7 @@ struct yvex_backend {
 };
 #define YVEX_DEVICE_OBSERVATION_OFFSET 256   /* the worklist summary lives behind the status word */
 #define YVEX_DEVICE_STATE_BYTES 1024
+#define YVEX_HOST_DEFERRED_STATUS_OFFSET 128   /* in the pinned host scratch: the status word of a deferred completion */
 
 int yvex_refuse(yvex_error *err, yvex_status code, const char *where, const char *message);
 int yvex_backend_admit(const yvex_backend *backend, const char *where, yvex_error *err);

@@ -481,8 +481,9 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
         result->d2h_bytes += sel_count * 4ull;
         result->download_count++;
     }
-    if (cudaMemcpyAsync(defer ? &job->device_completion->host->worklist : host_obs, dev_obs, sizeof(*dev_obs), cudaMemcpyDeviceToHost,
-                        backend->stream) != cudaSuccess)
+    /* into the backend's own page-locked scratch also when the completion is deferred: a copy into a slot in pageable
+     * memory would hold the call until the stream has drained; complete_rows moves the summary and the status on */
+    if (cudaMemcpyAsync(host_obs, dev_obs, sizeof(*dev_obs), cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess)
         return yvex_backend_fail(backend, where, err);
     result->d2h_bytes += sizeof(*dev_obs);
     result->download_count++;
@@ -523,7 +524,8 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
         s->active_per_expert_bytes = result->active_weight_per_unique_expert_bytes;
         s->activation_bytes = result->memory.activation_bytes;
         s->temporary_bytes = result->memory.temporary_bytes;
-        if (cudaMemcpyAsync(&s->status, backend->status_word, sizeof(int), cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess)
+        if (cudaMemcpyAsync(backend->host_scratch + YVEX_HOST_DEFERRED_STATUS_OFFSET, backend->status_word, sizeof(int), cudaMemcpyDeviceToHost,
+                            backend->stream) != cudaSuccess)
             return yvex_backend_fail(backend, where, err);
         backend->pending_slot = s;
         result->device_completion_pending = 1;
@@ -580,6 +582,8 @@ static int moe_complete_rows(yvex_backend *backend, int barrier_observed, yvex_m
         return yvex_backend_fail(backend, "cuda.moe.complete_rows", err);
     backend->pending_slot = NULL;
     s->pending = 0;
+    s->worklist = *(const yvex_expert_worklist_observation *)(backend->host_scratch + YVEX_DEVICE_OBSERVATION_OFFSET);
+    s->status = *(const int *)(backend->host_scratch + YVEX_HOST_DEFERRED_STATUS_OFFSET);
     code = s->status;
     if (code && cudaMemsetAsync(backend->status_word, 0, sizeof(int), backend->stream) != cudaSuccess)
         return yvex_backend_fail(backend, "cuda.moe.complete_rows", err);
