@@ -833,3 +833,40 @@ def test_quant_row_dot_host_row_and_vector(B, port, qtype, monkeypatch):
         assert dot(qtype, bad, bad.nbytes, x, width) == B.FORMAT and fail.code == 37
         assert dot(qtype, row, row.nbytes, x, width) == B.OK
     assert be.close() == B.OK
+
+
+@pytest.mark.parametrize("case", ["small_router", "envelope"])
+def test_execute_rows_replays_a_launch_graph_from_the_third_call(B, golden, case, monkeypatch):
+    """The narrow entry runs a (layer, row count, buffers) combination eagerly the first time, captures its kernel
+    sequence into a launch graph the second time and replays it afterwards (src/backend/cuda/moe.c:1645-1681);
+    the rows are the same bit for bit and the result reports launches / captures / replays like the reference."""
+    if case == "envelope":
+        H, S, T, seed = CASES["envelope"]["small"]
+        fn, scale, base, norm, x = envelope_inputs("small")
+        spec, weights, router, _, _ = layer_inputs("small_router")
+        be = B.Backend()
+        arena = B.ResidentArena(be, dict(weights, router=router, ffn_norm=norm, mhc_fn=fn, mhc_base=base, mhc_scale=scale))
+        job = B.moe_job(arena, spec, residual_streams=S, envelope_policy=ENVELOPE_POLICY)
+        want, logits = golden["envelope_small_out"].view(np.float32), None
+    else:
+        be, arena, job, spec, x, logits = layer_setup(B, case)
+        want = golden[f"layer_{case}_out"].view(np.float32)
+    ops, _ = attach_workspace(B, be, job, x.shape[0])
+    runs = [run_rows(B, be, ops, job, x, logits) for _ in range(4)]
+    assert all(r[0] == B.OK for r in runs), be.message()
+    assert rel_l2(runs[0][1], want) <= 1e-3
+    for rc, out, sel, wts, res in runs[1:]:
+        assert (out.view(np.uint32) == runs[0][1].view(np.uint32)).all() and (sel == runs[0][2]).all()
+        assert res.completed == 1 and res.unique_experts == runs[0][4].unique_experts
+    counters = [(r[4].graph_launches, r[4].graph_captures, r[4].graph_replays) for r in runs]
+    assert counters == [(0, 0, 0), (1, 1, 1), (1, 0, 1), (1, 0, 1)]
+    assert runs[0][4].kernel_launches == runs[1][4].kernel_launches == runs[3][4].kernel_launches >= 3
+    # another row count is another combination: eager again
+    fewer = run_rows(B, be, ops, job, x[:1].copy(), None if logits is None else logits[:1].copy())
+    assert fewer[0] == B.OK and fewer[4].graph_launches == 0
+    assert (fewer[1].view(np.uint32) == runs[0][1][:1].view(np.uint32)).all()
+    # the switch that keeps every call eager
+    monkeypatch.setenv("YVEX_B200_MOE_GRAPH", "off")
+    off = run_rows(B, be, ops, job, x, logits)
+    assert off[0] == B.OK and off[4].graph_launches == 0 and (off[1].view(np.uint32) == runs[0][1].view(np.uint32)).all()
+    assert be.close() == B.OK

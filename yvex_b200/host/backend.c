@@ -127,6 +127,7 @@ int yvex_backend_close_checked(yvex_backend **backend, yvex_error *err) {
         b->closing = 0;
         return yvex_refuse(err, YVEX_ERR_STATE, "yvex_backend_close_checked", "backend still owns tensors");
     }
+    yvex_moe_graphs_release(b);
     if (b->status_word) ok &= cudaFree(b->status_word) == cudaSuccess;
     if (b->act_scratch) ok &= cudaFree(b->act_scratch) == cudaSuccess;
     if (b->host_scratch) ok &= cudaFreeHost(b->host_scratch) == cudaSuccess;
@@ -145,6 +146,7 @@ void yvex_backend_close(yvex_backend *backend) {
     if (!backend) return;
     cudaSetDevice(backend->device);
     if (backend->stream) cudaStreamSynchronize(backend->stream);
+    yvex_moe_graphs_release(backend);
     backend_events(backend, 0);
     if (backend->copy_in) { cudaStreamSynchronize(backend->copy_in); cudaStreamDestroy(backend->copy_in); }
     if (backend->copy_out) { cudaStreamSynchronize(backend->copy_out); cudaStreamDestroy(backend->copy_out); }

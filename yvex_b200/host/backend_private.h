@@ -11,6 +11,17 @@
 #define YVEX_MOE_MAX_CHUNKS 4
 #define YVEX_HOST_SCRATCH_BYTES (1u << 20)   /* pinned: status read-back and router selections of narrow batches */
 
+/* Launch graphs of the narrow MoE entry (counterpart of yvex_cuda_graph_execute, src/backend/cuda/moe.c:1645-1681): the kernel
+ * sequence of one (layer, row count, buffers) combination, captured the second time the combination is seen. */
+#define YVEX_MOE_GRAPH_SLOTS 8
+#define YVEX_MOE_GRAPH_KEY_WORDS 56
+typedef struct {
+    unsigned long long key[YVEX_MOE_GRAPH_KEY_WORDS];
+    int seen;                         /* 0 free, 1 seen once (ran eagerly), 2 captured, -1 capture failed: stays eager */
+    cudaGraphExec_t exec;
+    unsigned long long launches, stamp;
+} yvex_moe_graph_slot;
+
 struct yvex_backend {
     yvex_backend_kind kind;
     _Atomic int status;
@@ -29,6 +40,8 @@ struct yvex_backend {
     unsigned long long act_scratch_bytes;            /* (grown on demand, freed at close) */
     /* copy pipeline of the wide entry: host rows go in on copy_in and come back on copy_out while the
      * compute stream works on another chunk of rows */
+    yvex_moe_graph_slot moe_graphs[YVEX_MOE_GRAPH_SLOTS];
+    unsigned long long moe_graph_stamp;
     cudaStream_t copy_in, copy_out;
     cudaEvent_t ev_begin, ev_end, ev_in[YVEX_MOE_MAX_CHUNKS], ev_done[YVEX_MOE_MAX_CHUNKS];
 };
@@ -44,4 +57,5 @@ unsigned char *yvex_workspace_take(yvex_backend *backend, unsigned long long *cu
 int yvex_backend_take_status(yvex_backend *backend, int *code);
 /* Test seam of the reference (src/backend/cuda/qtype.c:625-661): 1 if the environment variable `name` is set to `value`. */
 int yvex_test_seam(const char *name, const char *value);
+void yvex_moe_graphs_release(yvex_backend *backend);
 #endif

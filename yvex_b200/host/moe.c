@@ -155,6 +155,168 @@ static int status_error(int code, yvex_error *err) {
     return yvex_refuse(err, YVEX_ERR_BACKEND, "cuda.moe", "CUDA MoE kernel reported invalid or non-finite numerics");
 }
 
+/* What the kernels of one row batch read and write: everything the enqueue below needs, and (as plain words) the
+ * identity of a launch graph that replays it. */
+typedef struct {
+    yvex_backend *backend;
+    const yvex_moe_layer_job *job;
+    yvex_b200_moe_geometry g;
+    yvex_b200_moe_weights w;
+    yvex_b200_mhc mhc;
+    unsigned long long streams, rows, mhc_ws, kernel_ws, tensor_path, coeff_count[4];
+    int wide;
+    unsigned int provenance;
+    const void *coeff_addr[4];
+    unsigned int coeff_qtype[4];
+    const float *dev_in, *dev_logits;
+    float *dev_out;
+    const uint32_t *ids;
+    unsigned char *ws_norm, *ws_core, *ws_post, *ws_comb, *ws_mhc, *ws_coeff[4], *ws_routed, *ws_shared, *ws_sel, *ws_wts, *ws_kernel;
+    yvex_expert_worklist_observation *dev_obs;
+} rows_run;
+
+/* The layer of a batch that is not pipelined: envelope prepare, the MoE layer, envelope post. */
+static int rows_layer(rows_run *r, const char **message) {
+    yvex_backend *backend = r->backend;
+    const float *layer_in = r->dev_in;
+    float *layer_out = r->dev_out;
+    int rc;
+    if (r->streams > 1ull) {
+        const float **slot_ptr[4] = {&r->mhc.norm, &r->mhc.mhc_fn, &r->mhc.base, &r->mhc.scale};
+        *message = "device layer refused an mHC coefficient tensor";
+        for (int i = 0; i < 4; ++i) {
+            if (r->coeff_qtype[i] != 30u) continue;
+            rc = yvex_b200_dequant_rows(30u, r->coeff_addr[i], 1ull, r->coeff_count[i], r->coeff_count[i] * 2ull, (float *)r->ws_coeff[i],
+                                        backend->status_word, backend->stream);
+            if (rc != YVEX_OK) return rc;
+            *slot_ptr[i] = (const float *)r->ws_coeff[i];
+        }
+        *message = "device layer refused the mHC envelope geometry";
+        rc = yvex_b200_mhc_prepare(&r->mhc, r->dev_in, r->rows, (float *)r->ws_norm, (float *)r->ws_post, (float *)r->ws_comb, r->ws_mhc,
+                                   r->mhc_ws, backend->status_word, backend->stream);
+        if (rc != YVEX_OK) return rc;
+        layer_in = (const float *)r->ws_norm;
+        layer_out = (float *)r->ws_core;
+    }
+    *message = "device layer refused the MoE layer geometry";
+    rc = (r->wide ? yvex_b200_moe_wide_parts : yvex_b200_moe_decode_parts)(
+        &r->g, &r->w, layer_in, r->dev_logits, r->ids, r->rows, layer_out, (float *)r->ws_routed, (float *)r->ws_shared, (int32_t *)r->ws_sel,
+        (float *)r->ws_wts, r->ws_kernel, r->kernel_ws, backend->status_word, backend->stream);
+    if (rc != YVEX_OK) return rc;
+    if (r->streams > 1ull) {
+        *message = "device layer refused the mHC envelope geometry";
+        rc = yvex_b200_mhc_post(&r->mhc, (const float *)r->ws_core, r->dev_in, (const float *)r->ws_post, (const float *)r->ws_comb, r->rows,
+                                r->dev_out, backend->status_word, backend->stream);
+    }
+    return rc;
+}
+
+/* The worklist summary of the batch (src/backend/cuda/moe.c:1710-1726), built on the device from the
+ * router's selection. The wide path sends every pair through the tensor-core GEMM tiles; the narrow
+ * path has no admission threshold, which the reference's summary counts as narrow pairs. */
+static int rows_worklist(rows_run *r, const char **message) {
+    *message = "device layer refused the expert worklist geometry";
+    return yvex_b200_expert_worklist((const int32_t *)r->ws_sel, r->rows, r->g.topk, r->g.experts, r->wide && r->tensor_path ? 1ull : 0ull,
+                                     r->wide && r->tensor_path ? yvex_b200_moe_wide_tile_columns(r->g.gate_qtype) : 1ull, r->provenance, NULL,
+                                     NULL, NULL, NULL, NULL, NULL, r->dev_obs, r->ws_kernel, r->kernel_ws, r->backend->status_word,
+                                     r->backend->stream);
+}
+
+/* ---- launch graphs of the narrow entry ---------------------------------------------------------------- */
+
+void yvex_moe_graphs_release(yvex_backend *backend) {
+    for (int i = 0; i < YVEX_MOE_GRAPH_SLOTS; ++i) {
+        if (backend->moe_graphs[i].exec) cudaGraphExecDestroy(backend->moe_graphs[i].exec);
+        memset(&backend->moe_graphs[i], 0, sizeof(backend->moe_graphs[i]));
+    }
+}
+
+static unsigned long long bits_of(double v) { unsigned long long u; memcpy(&u, &v, sizeof(u)); return u; }
+
+/* Every value a captured kernel argument was computed from. Two batches with equal keys enqueue identical launches. */
+static void rows_key(const rows_run *r, int want_parts, unsigned long long *key) {
+    const unsigned long long words[] = {
+        r->rows, r->streams, (unsigned long long)want_parts, r->provenance, r->g.hidden, r->g.experts, r->g.topk, r->g.inter, r->g.shared_inter,
+        r->g.gate_qtype, r->g.up_qtype, r->g.down_qtype, (unsigned long long)r->g.router_class, (unsigned long long)r->g.normalize, r->g.hash_rows,
+        r->g.hash_stored_rows, bits_of(r->g.scaling), bits_of(r->g.limit), (uintptr_t)r->w.router, (uintptr_t)r->w.bias, (uintptr_t)r->w.hash_table,
+        (uintptr_t)r->w.gate, (uintptr_t)r->w.up, (uintptr_t)r->w.down, (uintptr_t)r->w.shared_gate, (uintptr_t)r->w.shared_up,
+        (uintptr_t)r->w.shared_down, (uintptr_t)r->coeff_addr[0], (uintptr_t)r->coeff_addr[1], (uintptr_t)r->coeff_addr[2],
+        (uintptr_t)r->coeff_addr[3], r->coeff_qtype[0], r->coeff_qtype[1], r->coeff_qtype[2], r->coeff_qtype[3], r->mhc.sinkhorn_iterations,
+        bits_of(r->mhc.rms_epsilon), bits_of(r->mhc.mhc_epsilon), bits_of(r->mhc.post_multiplier), (uintptr_t)r->dev_in, (uintptr_t)r->dev_out,
+        (uintptr_t)r->dev_logits, (uintptr_t)r->ids, (uintptr_t)r->backend->workspace->data, r->backend->workspace->bytes};
+    _Static_assert(sizeof(words) / sizeof(words[0]) <= YVEX_MOE_GRAPH_KEY_WORDS, "graph key is too small");
+    memset(key, 0, YVEX_MOE_GRAPH_KEY_WORDS * sizeof(*key));
+    memcpy(key, words, sizeof(words));
+}
+
+static yvex_moe_graph_slot *graph_slot(yvex_backend *backend, const unsigned long long *key) {
+    yvex_moe_graph_slot *oldest = &backend->moe_graphs[0];
+    for (int i = 0; i < YVEX_MOE_GRAPH_SLOTS; ++i) {
+        yvex_moe_graph_slot *s = &backend->moe_graphs[i];
+        if (s->seen && !memcmp(s->key, key, sizeof(s->key))) { s->stamp = ++backend->moe_graph_stamp; return s; }
+        if (s->stamp < oldest->stamp) oldest = s;
+    }
+    if (oldest->exec) cudaGraphExecDestroy(oldest->exec);           /* least recently used; the stream is idle between calls */
+    memset(oldest, 0, sizeof(*oldest));
+    memcpy(oldest->key, key, sizeof(oldest->key));
+    oldest->stamp = ++backend->moe_graph_stamp;
+    return oldest;
+}
+
+/* Enqueues the batch's kernels: eagerly the first time a combination is seen, captured into a launch graph and launched
+ * the second time, replayed from then on. Returns the device layer's code; *launches = kernels enqueued or replayed. */
+static int rows_enqueue_narrow(rows_run *r, int want_parts, yvex_moe_row_batch_result *result, unsigned long long *launches, const char **message) {
+    yvex_backend *backend = r->backend;
+    unsigned long long key[YVEX_MOE_GRAPH_KEY_WORDS], before = yvex_b200_launch_count();
+    yvex_moe_graph_slot *slot = NULL;
+    cudaGraph_t graph = NULL;
+    int rc;
+    if (!yvex_test_seam("YVEX_B200_MOE_GRAPH", "off")) {
+        rows_key(r, want_parts, key);
+        slot = graph_slot(backend, key);
+    }
+    if (slot && slot->seen == 2) {
+        *message = "launch graph replay failed";
+        if (cudaGraphLaunch(slot->exec, backend->stream) != cudaSuccess) return YVEX_ERR_BACKEND;
+        *launches = slot->launches;
+        result->graph_launches = result->graph_replays = 1ull;
+        return YVEX_OK;
+    }
+    if (slot && slot->seen == 1 && cudaStreamBeginCapture(backend->stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+        rc = rows_layer(r, message);
+        if (rc == YVEX_OK) rc = rows_worklist(r, message);
+        if (cudaStreamEndCapture(backend->stream, &graph) != cudaSuccess || !graph) {
+            cudaGetLastError();
+            if (graph) cudaGraphDestroy(graph);
+            graph = NULL;
+        }
+        if (rc != YVEX_OK) {                                    /* a refusal while capturing: nothing was enqueued */
+            if (graph) cudaGraphDestroy(graph);
+            return rc;
+        }
+        if (graph && cudaGraphInstantiate(&slot->exec, graph, 0ull) == cudaSuccess) {
+            cudaGraphDestroy(graph);
+            slot->launches = yvex_b200_launch_count() - before;
+            slot->seen = 2;
+            *message = "launch graph replay failed";
+            if (cudaGraphLaunch(slot->exec, backend->stream) != cudaSuccess) return YVEX_ERR_BACKEND;
+            *launches = slot->launches;
+            result->graph_launches = result->graph_replays = result->graph_captures = 1ull;
+            return YVEX_OK;
+        }
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        slot->exec = NULL;
+        slot->seen = -1;                                        /* this combination stays eager */
+        before = yvex_b200_launch_count();
+    }
+    rc = rows_layer(r, message);
+    if (rc == YVEX_OK) rc = rows_worklist(r, message);
+    if (rc == YVEX_OK && slot && slot->seen == 0) slot->seen = 1;
+    *launches = yvex_b200_launch_count() - before;
+    return rc;
+}
+
 static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, const yvex_moe_row_batch *batch,
                        const yvex_moe_row_batch_output *output, yvex_moe_row_batch_result *result, yvex_error *err, int wide) {
     const char *where = wide ? "cuda.moe.execute_rows_wide" : "cuda.moe.execute_rows";
@@ -173,9 +335,12 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     unsigned char *ws_norm = NULL, *ws_core = NULL, *ws_post = NULL, *ws_comb = NULL, *ws_mhc = NULL, *ws_coeff[4] = {NULL, NULL, NULL, NULL};
     unsigned long long coeff_count[4] = {0, 0, 0, 0};
     static const int coeff[4] = {YVEX_MOE_WEIGHT_FFN_NORM, YVEX_MOE_WEIGHT_MHC_FUNCTION, YVEX_MOE_WEIGHT_MHC_BASE, YVEX_MOE_WEIGHT_MHC_SCALE};
-    const float *dev_in, *dev_logits = NULL, *layer_in;
-    float *dev_out, *layer_out;
+    const float *dev_in, *dev_logits = NULL;
+    float *dev_out;
     int rc, code, defer, slot, pipelined;
+    rows_run run;
+    const char *refusal = "device layer refused the MoE layer geometry";
+    unsigned long long graph_kernel_launches = ~0ull;
     static const int required[YVEX_MOE_WEIGHT_COUNT] = {0, 0, 0, 0, 0, 0, 0, 1, 1, 1, 1, 1, 1};
     const void *addr[YVEX_MOE_WEIGHT_COUNT];
 
@@ -359,25 +524,23 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     }
 
     launches0 = yvex_b200_launch_count();
-    layer_in = dev_in;
-    layer_out = dev_out;
-    if (streams > 1ull) {
-        const float **slot_ptr[4] = {&mhc.norm, &mhc.mhc_fn, &mhc.base, &mhc.scale};
-        for (int i = 0; i < 4; ++i) {
-            if (job->weights[coeff[i]].qtype != 30u) continue;
-            rc = yvex_b200_dequant_rows(30u, addr[coeff[i]], 1ull, coeff_count[i], coeff_count[i] * 2ull, (float *)ws_coeff[i],
-                                        backend->status_word, backend->stream);
-            if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
-            if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused an mHC coefficient tensor");
-            *slot_ptr[i] = (const float *)ws_coeff[i];
-        }
-        rc = yvex_b200_mhc_prepare(&mhc, dev_in, rows, (float *)ws_norm, (float *)ws_post, (float *)ws_comb, ws_mhc, mhc_ws,
-                                   backend->status_word, backend->stream);
-        if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
-        if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the mHC envelope geometry");
-        layer_in = (const float *)ws_norm;
-        layer_out = (float *)ws_core;
+    memset(&run, 0, sizeof(run));
+    run.backend = backend; run.job = job; run.g = g; run.w = w; run.mhc = mhc;
+    run.streams = streams; run.rows = rows; run.mhc_ws = mhc_ws; run.kernel_ws = kernel_ws; run.tensor_path = tensor_path; run.wide = wide;
+    run.provenance = (unsigned)batch->provenance <= 4u ? (unsigned)batch->provenance : rows == 1ull ? 0u : wide ? 3u : 2u;
+    for (int i = 0; i < 4; ++i) {
+        run.coeff_addr[i] = streams > 1ull ? addr[coeff[i]] : NULL;
+        run.coeff_qtype[i] = streams > 1ull ? job->weights[coeff[i]].qtype : 0u;
+        run.coeff_count[i] = coeff_count[i];
+        run.ws_coeff[i] = ws_coeff[i];
     }
+    run.dev_in = dev_in; run.dev_logits = dev_logits; run.dev_out = dev_out;
+    run.ids = batch->token_ids_present && batch->token_ids ? (const uint32_t *)ws_ids : NULL;
+    run.ws_norm = ws_norm; run.ws_core = ws_core; run.ws_post = ws_post; run.ws_comb = ws_comb; run.ws_mhc = ws_mhc;
+    run.ws_routed = ws_routed; run.ws_shared = ws_shared; run.ws_sel = ws_sel; run.ws_wts = ws_wts; run.ws_kernel = ws_kernel;
+    dev_obs = (yvex_expert_worklist_observation *)((unsigned char *)backend->status_word + YVEX_DEVICE_OBSERVATION_OFFSET);
+    host_obs = (yvex_expert_worklist_observation *)(backend->host_scratch + YVEX_DEVICE_OBSERVATION_OFFSET);
+    run.dev_obs = dev_obs;
     if (pipelined) {
         /* row range c: copied in on copy_in, computed on the backend's stream, copied out on copy_out */
         const unsigned char *host_in = (const unsigned char *)batch->expanded_rows, *host_lg = (const unsigned char *)host_logits;
@@ -419,33 +582,16 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
         result->d2h_bytes += in_bytes;
         result->download_count++;
         backend->last_pipeline_chunks = chunks;
+        rc = rows_worklist(&run, &refusal);
+    } else if (wide) {
+        rc = rows_layer(&run, &refusal);
+        if (rc == YVEX_OK) rc = rows_worklist(&run, &refusal);
     } else {
-        rc = (wide ? yvex_b200_moe_wide_parts : yvex_b200_moe_decode_parts)(
-            &g, &w, layer_in, dev_logits, batch->token_ids_present && batch->token_ids ? (const uint32_t *)ws_ids : NULL, rows, layer_out,
-            (float *)ws_routed, (float *)ws_shared, (int32_t *)ws_sel, (float *)ws_wts, ws_kernel, kernel_ws, backend->status_word,
-            backend->stream);
-        if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
-        if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the MoE layer geometry");
+        /* the narrow entry replays a launch graph of this sequence once it has seen the combination (src/backend/cuda/moe.c:1645-1681) */
+        rc = rows_enqueue_narrow(&run, want_parts, result, &graph_kernel_launches, &refusal);
     }
-    if (streams > 1ull) {
-        rc = yvex_b200_mhc_post(&mhc, (const float *)ws_core, dev_in, (const float *)ws_post, (const float *)ws_comb, rows, dev_out,
-                                backend->status_word, backend->stream);
-        if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
-        if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the mHC envelope geometry");
-    }
-
-    /* The worklist summary of the batch (src/backend/cuda/moe.c:1710-1726), built on the device from the
-     * router's selection. The wide path sends every pair through the tensor-core GEMM tiles; the narrow
-     * path has no admission threshold, which the reference's summary counts as narrow pairs. */
-    dev_obs = (yvex_expert_worklist_observation *)((unsigned char *)backend->status_word + YVEX_DEVICE_OBSERVATION_OFFSET);
-    host_obs = (yvex_expert_worklist_observation *)(backend->host_scratch + YVEX_DEVICE_OBSERVATION_OFFSET);
-    rc = yvex_b200_expert_worklist((const int32_t *)ws_sel, rows, g.topk, g.experts, wide && tensor_path ? 1ull : 0ull,
-                                   wide && tensor_path ? yvex_b200_moe_wide_tile_columns(g.gate_qtype) : 1ull,
-                                   (unsigned)batch->provenance <= 4u ? (unsigned)batch->provenance : rows == 1ull ? 0u : wide ? 3u : 2u, NULL,
-                                   NULL, NULL, NULL, NULL, NULL, dev_obs, ws_kernel, kernel_ws,
-                                   backend->status_word, backend->stream);
     if (rc == YVEX_ERR_BACKEND) return yvex_backend_fail(backend, where, err);
-    if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, "device layer refused the expert worklist geometry");
+    if (rc != YVEX_OK) return yvex_refuse(err, (yvex_status)rc, where, refusal);
     if (!pipelined && output && output->combined_rows) {
         if (cudaMemcpyAsync(output->combined_rows, dev_out, in_bytes, cudaMemcpyDeviceToHost, backend->stream) != cudaSuccess)
             return yvex_backend_fail(backend, where, err);
@@ -493,7 +639,7 @@ static int moe_execute(yvex_backend *backend, const yvex_moe_layer_job *job, con
     result->grouped_expert_operations = sel_count;
     result->shared_expert_operations = rows;
     result->expert_subviews_accessed = sel_count * 3ull;
-    result->kernel_launches = yvex_b200_launch_count() - launches0;
+    result->kernel_launches = graph_kernel_launches != ~0ull ? graph_kernel_launches : yvex_b200_launch_count() - launches0;
     /* launches whose contraction runs on the tensor cores: the gate/up and down kernels of each row range */
     result->tensor_core_launches = tensor_path ? 2ull * chunks : 0ull;
     if (streams > 1ull)
