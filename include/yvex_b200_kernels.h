@@ -418,6 +418,19 @@ int yvex_b200_attention_f32(const float *q, const float *keys, const float *valu
                             int causal, float *scores, float *probabilities, float *out,
                             int *status, void *stream);
 
+/*
+ * Sink reducer of the graph attention op: every query head of one token against one row set that is key
+ * and value at once and is shared by all heads (reduce_head / reduce_visit_row, src/graph/core.c:428-465,
+ * :318-345). query [heads x head_dim], rows [row_count x head_dim], sinks [heads], out [heads x head_dim],
+ * all f32 on the device. Scores are f64 dot products times scale; the head's sink is the initial maximum
+ * and seeds the denominator with exp(sink - max) without contributing a value; out = sum p * row /
+ * denominator, rounded to bf16 when round_bf16 is set (the compute contract's rounding). row_count may be
+ * 0 (the output is then zero: only the sink has weight). The rotary step the reference applies to the
+ * result afterwards is not part of this entry. head_dim <= 1024.
+ */
+int yvex_b200_attention_sink(const float *query, const float *rows, const float *sinks, uint64_t heads, uint64_t row_count,
+                             uint64_t head_dim, double scale, int round_bf16, float *out, int *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

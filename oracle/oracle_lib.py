@@ -277,3 +277,28 @@ def q8k_round_trip(x):
         q = np.clip(np.rint(inverse[:, None] * blocks), -128, 127).astype(np.int32).astype(np.float32)     # an int: no -0
         out[live] = (q[live] / inverse[live, None]).astype(np.float32)
     return out.reshape(x.shape)
+
+
+def sink_attention(query, rows, sinks, scale, round_bf16=True):
+    """The sink reducer of the reference's graph attention op for one token, restated (reduce_head,
+    src/graph/core.c:428-465, with reduce_visit_row, :318-345; the rotary step that follows it there is left
+    out): per head, pass 1 takes the maximum of the head's sink and every f64 score q . row * scale, pass 2
+    seeds the denominator with exp(sink - max) and walks the rows in order, adding exp(score - max) to the
+    denominator and (float)(p * row[lane]) to an f32 destination; the destination is divided by the
+    denominator in double, narrowed to f32 and rounded to bf16 (the compute contract's rounding).
+    Parity unpinned: the function is static inside the attention op and no fixture of the reference isolates it."""
+    from yvex_b200 import synth
+    query = np.ascontiguousarray(query, np.float32)
+    rows = np.ascontiguousarray(rows, np.float32)
+    out = np.zeros_like(query)
+    for h in range(query.shape[0]):
+        scores = (rows.astype(np.float64) @ query[h].astype(np.float64)) * float(scale)
+        maximum = max(float(sinks[h]), float(scores.max())) if len(scores) else float(sinks[h])
+        denominator = np.exp(float(sinks[h]) - maximum)
+        dest = np.zeros(query.shape[1], np.float32)
+        for i in range(rows.shape[0]):
+            p = np.exp(scores[i] - maximum)
+            denominator += p
+            dest += (p * rows[i].astype(np.float64)).astype(np.float32)
+        out[h] = (dest.astype(np.float64) / denominator).astype(np.float32)
+    return synth.bf16_round(out) if round_bf16 else out

@@ -464,3 +464,30 @@ def test_attention_f32_single_head_vs_oracle(L, port):
             assert not scores.cpu().numpy()[pos + 1:].any() and not probs.cpu().numpy()[pos + 1:].any()
         assert abs(float(probs.sum()) - 1.0) < 1e-5
     assert st.read() == 0
+
+
+@pytest.mark.parametrize("heads,n,D", [(4, 37, 64), (8, 300, 512), (2, 0, 128), (3, 9, 1024), (5, 1000, 192)])
+def test_sink_attention_reducer_vs_restatement(L, heads, n, D):
+    """yvex_b200_attention_sink against the numpy restatement of reduce_head (src/graph/core.c:428-465): f32 results
+    agree to 2e-6 relative of the largest row value (the kernel merges per-warp running sums instead of walking the
+    rows in order), the bf16-rounded ones differ by at most one bf16 step on a few elements."""
+    from oracle_lib import sink_attention
+    rng = np.random.default_rng(heads * 1000 + n)
+    q = rng.standard_normal((heads, D)).astype(np.float32)
+    rows = rng.standard_normal((n, D)).astype(np.float32)
+    sinks = rng.standard_normal(heads).astype(np.float32) * 3
+    scale = 1.0 / np.sqrt(D)
+    st = L.Status()
+    got = L.attention_sink(dev(q), dev(rows), dev(sinks), scale, st, round_bf16=False).cpu().numpy()
+    want = sink_attention(q, rows, sinks, scale, round_bf16=False)
+    assert st.read() == 0 and np.abs(got - want).max() <= 2e-6 * max(1.0, np.abs(rows).max() if n else 1.0)
+    got16 = L.attention_sink(dev(q), dev(rows), dev(sinks), scale, st, round_bf16=True).cpu().numpy()
+    want16 = sink_attention(q, rows, sinks, scale, round_bf16=True)
+    assert (synth.bf16_round(got16).view(np.uint32) == got16.view(np.uint32)).all()
+    differ = got16.view(np.uint32) != want16.view(np.uint32)
+    assert differ.mean() <= 0.01 and (np.abs(got16 - want16)[differ] <= np.abs(want16)[differ] * 2.0 ** -7 + 1e-30).all()
+    if n:
+        bad = q.copy()
+        bad[0, 1] = np.inf
+        L.attention_sink(dev(bad), dev(rows), dev(sinks), scale, st)
+        assert st.read() == 1

@@ -278,3 +278,19 @@ def test_q4_k_extension_is_self_consistent(port):
         mn = (dmin * m.astype(np.float32)).astype(np.float32)
         want[:, 32 * j:32 * j + 32] = scale[:, None] * code.astype(np.float32) - mn[:, None]
     assert (bits(dec.reshape(-1, 256)) == bits(want)).all()
+
+
+def test_sink_attention_restatement_properties():
+    """The sink only adds exp(sink - max) to the denominator: a very negative sink gives plain softmax attention
+    over the rows, no rows give a zero output, and a dominant sink shrinks the output towards zero."""
+    from oracle_lib import sink_attention
+    rng = np.random.default_rng(5)
+    q, rows = rng.standard_normal((3, 64)).astype(np.float32), rng.standard_normal((40, 64)).astype(np.float32)
+    out = sink_attention(q, rows, np.full(3, -1e30, np.float32), 0.125, round_bf16=False)
+    s = (rows.astype(np.float64) @ q.astype(np.float64).T) * 0.125
+    p = np.exp(s - s.max(axis=0))
+    want = (p / p.sum(axis=0)).T @ rows.astype(np.float64)
+    assert np.abs(out - want).max() <= 1e-5
+    assert not sink_attention(q, rows[:0], np.zeros(3, np.float32), 0.125).any()
+    big = sink_attention(q, rows, np.full(3, 50.0, np.float32), 0.125, round_bf16=False)
+    assert np.abs(big).max() < 1e-12 * 1e3 + np.abs(out).max() * 1e-15 + 1e-9

@@ -261,6 +261,82 @@ __global__ void attention_f32_kernel(const float *q, const float *keys, const fl
     }
 }
 
+// ---- sink reducer: every head of one token against one shared set of rows -----------------------
+// The reference's reduce_head (src/graph/core.c:428-465) with reduce_visit_row (:318-345): the rows are key
+// and value at once (one latent row set shared by all query heads), scores are f64 dot products times
+// scale, the head's sink is the initial maximum and seeds the denominator with exp(sink - max), the
+// output is sum p * row / denominator, optionally rounded to bf16. One CTA per head; a warp walks every
+// kWarps-th row with a running maximum (f64), denominator (f64) and f32 partial sums, and the warps'
+// states are merged through shared memory at the end (the reference makes two passes in row order; the
+// results differ by f32 rounding only). D <= 1024.
+constexpr int kSinkWarps = 8, kSinkMaxPerLane = 32;
+__global__ void __launch_bounds__(32 * kSinkWarps) attention_sink_kernel(const float *query, const float *rows, const float *sinks, uint64_t n,
+                                                                         uint64_t D, double scale, int round_bf16, float *out, int *status) {
+    __shared__ double s_max[kSinkWarps], s_den[kSinkWarps];
+    __shared__ float s_acc[kSinkWarps][1024];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint64_t head = blockIdx.x;
+    const float *q = query + head * D;
+    const int per_lane = (int)((D + 31) / 32);
+    float qv[kSinkMaxPerLane], acc[kSinkMaxPerLane];
+    bool bad = false;
+#pragma unroll
+    for (int j = 0; j < kSinkMaxPerLane; ++j) {
+        const uint64_t d = (uint64_t)lane + 32u * j;
+        qv[j] = j < per_lane && d < D ? q[d] : 0.0f;
+        bad |= !isfinite(qv[j]);
+        acc[j] = 0.0f;
+    }
+    const double sink = (double)sinks[head];
+    bad |= !isfinite(sink);
+    double mx = warp == 0 ? sink : -INFINITY, den = warp == 0 ? 1.0 : 0.0;      // the sink is a row without a value
+    for (uint64_t i = warp; i < n; i += kSinkWarps) {
+        const float *row = rows + i * D;
+        float rv[kSinkMaxPerLane];
+        double s = 0.0;
+#pragma unroll
+        for (int j = 0; j < kSinkMaxPerLane; ++j) {
+            const uint64_t d = (uint64_t)lane + 32u * j;
+            rv[j] = j < per_lane && d < D ? __ldg(row + d) : 0.0f;
+            bad |= !isfinite(rv[j]);
+            s += (double)qv[j] * (double)rv[j];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        s *= scale;
+        bad |= !isfinite(s);
+        if (s > mx) {
+            const double c = exp(mx - s);                                   // 0 when nothing has been seen yet
+            den *= c;
+#pragma unroll
+            for (int j = 0; j < kSinkMaxPerLane; ++j) acc[j] = (float)((double)acc[j] * c);
+            mx = s;
+        }
+        const double p = exp(s - mx);
+        den += p;
+#pragma unroll
+        for (int j = 0; j < kSinkMaxPerLane; ++j) acc[j] += (float)(p * (double)rv[j]);
+    }
+    if (lane == 0) { s_max[warp] = mx; s_den[warp] = den; }
+#pragma unroll
+    for (int j = 0; j < kSinkMaxPerLane; ++j)
+        if (j < per_lane && (uint64_t)lane + 32u * j < D) s_acc[warp][lane + 32 * j] = acc[j];
+    if (bad) raise(status, YVEX_B200_STATUS_NUMERIC);
+    __syncthreads();
+    double gm = s_max[0];
+    for (int w = 1; w < kSinkWarps; ++w) gm = fmax(gm, s_max[w]);
+    double gd = 0.0;
+    for (int w = 0; w < kSinkWarps; ++w) gd += s_den[w] * (s_max[w] == -INFINITY ? 0.0 : exp(s_max[w] - gm));
+    if (!(gd > 0.0) || !isfinite(gd)) { if (threadIdx.x == 0) raise(status, YVEX_B200_STATUS_NUMERIC); return; }
+    for (uint64_t d = threadIdx.x; d < D; d += blockDim.x) {
+        double a = 0.0;
+        for (int w = 0; w < kSinkWarps; ++w) a += (double)s_acc[w][d] * (s_max[w] == -INFINITY ? 0.0 : exp(s_max[w] - gm));
+        const float v = (float)(a / gd);
+        if (!isfinite(v)) raise(status, YVEX_B200_STATUS_NUMERIC);
+        out[head * D + d] = round_bf16 ? bf16_round(v) : v;
+    }
+}
+
 static int pick_splits(uint64_t groups, uint64_t visible) {
     // Enough CTAs to fill 148 SMs a few times over with at least ~256 keys per slice; among those
     // prefer a count that makes groups * splits a whole number of waves (a multiple of the SM count).
@@ -333,5 +409,15 @@ extern "C" int yvex_b200_attention_f32(const float *q, const float *keys, const 
     attention_f32_kernel<<<1, 1024, 0, as_stream(stream)>>>(q, keys, values, seq_len, head_dim,
                                                             causal ? position + 1 : seq_len, scale, scores,
                                                             probabilities, out, status);
+    return launch_status();
+}
+
+extern "C" int yvex_b200_attention_sink(const float *query, const float *rows, const float *sinks, uint64_t heads, uint64_t row_count,
+                                        uint64_t head_dim, double scale, int round_bf16, float *out, int *status, void *stream) {
+    if (!query || (!rows && row_count) || !sinks || !out || !status || !heads) return ERR_INVALID_ARG;
+    if (!isfinite(scale) || scale <= 0.0) return ERR_INVALID_ARG;
+    if (!head_dim || head_dim > 1024) return ERR_BOUNDS;
+    attention_sink_kernel<<<(unsigned)heads, 32 * kSinkWarps, 0, as_stream(stream)>>>(query, rows, sinks, row_count, head_dim, scale, round_bf16,
+                                                                                      out, status);
     return launch_status();
 }

@@ -88,6 +88,7 @@ def _load():
     lib.yvex_b200_attention_gqa_decode.argtypes = [vp, vp, vp, u64, u64, u64, u64, u64, u64, C.c_float,
                                                    vp, vp, u64, vp, vp]
     lib.yvex_b200_attention_f32.argtypes = [vp, vp, vp, u64, u64, u64, C.c_float, C.c_int, vp, vp, vp, vp, vp]
+    lib.yvex_b200_attention_sink.argtypes = [vp, vp, vp, u64, u64, u64, C.c_double, C.c_int, vp, vp, vp]
     lib.yvex_b200_mhc_workspace_bytes.restype = u64
     lib.yvex_b200_mhc_workspace_bytes.argtypes = [u64, u64]
     lib.yvex_b200_mhc_prepare.argtypes = [vp, vp, u64, vp, vp, vp, vp, u64, vp, vp]
@@ -115,7 +116,7 @@ EXPORTS = ["yvex_b200_version", "yvex_b200_qtype_supported", "yvex_b200_qtype_ge
            "yvex_b200_moe_expert_rows_workspace_bytes", "yvex_b200_moe_expert_rows", "yvex_b200_moe_combine",
            "yvex_b200_moe_combine_indexed", "yvex_b200_ep_dispatch_workspace_bytes", "yvex_b200_ep_dispatch",
            "yvex_b200_attention_workspace_bytes", "yvex_b200_attention_gqa_decode",
-           "yvex_b200_attention_f32", "yvex_b200_attention_static_scratch_bytes",
+           "yvex_b200_attention_f32", "yvex_b200_attention_sink", "yvex_b200_attention_static_scratch_bytes",
            "yvex_b200_attention_gqa_decode_static", "yvex_b200_mhc_workspace_bytes", "yvex_b200_mhc_prepare",
            "yvex_b200_mhc_post", "yvex_b200_expert_worklist_workspace_bytes", "yvex_b200_expert_worklist",
            "yvex_b200_selftest_bounded_wait", "yvex_b200_moe_wide_uses_gemm", "yvex_b200_moe_wide_tile_columns",
@@ -454,6 +455,16 @@ def attention_gqa_decode(q, k, v, position, scale, status, workspace=None, out=N
     _check(lib.yvex_b200_attention_gqa_decode(_p(q), _p(k), _p(v), S, Hq, Hkv, D, ctx, position, scale, _p(out),
                                               _p(workspace), workspace.numel(), _p(status.word), _stream()),
            "attention_gqa_decode")
+    return out
+
+
+def attention_sink(query, rows, sinks, scale, status, round_bf16=True):
+    """query [heads, D], rows [n, D], sinks [heads] f32 device tensors -> out [heads, D]."""
+    torch = _torch()
+    heads, D = query.shape
+    out = torch.zeros((heads, D), dtype=torch.float32, device=query.device)
+    _check(lib.yvex_b200_attention_sink(_p(query), _p(rows), _p(sinks), heads, rows.shape[0], D, C.c_double(scale), int(round_bf16),
+                                        _p(out), _p(status.word), _stream()), "attention_sink")
     return out
 
 
