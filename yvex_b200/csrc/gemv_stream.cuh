@@ -31,6 +31,7 @@
 #include <cstdlib>
 #include <type_traits>
 
+#include "moe_common.cuh"
 #include "qtype_decode.cuh"
 #include "tcgen05.cuh"
 
@@ -454,6 +455,11 @@ struct StreamParams {
     uint32_t stage_bytes, smem_bytes;
     const float *x;                     // input vector of matrix m at x + m * x_stride
     uint64_t x_stride;
+    // optional: the input of matrix m is bf16(SwiGLU(x row, x_up row) * x_weight[m]) with the clamp x_limit
+    // (src/graph/moe.c:605-613), x_up rows spaced like the x rows; formed while the planes are prepared
+    const float *x_up;
+    const float *x_weight;
+    float x_limit;
     const float *additive;              // optional, laid out like out
     float *out;                         // result of matrix m at out + m * out_stride
     uint64_t out_stride;
@@ -656,8 +662,11 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
             const float *x = p.x + (uint64_t)cur_x * p.x_stride;
             float mx = 0.0f;
             bool badx = false;
+            const float *xu = p.x_up ? p.x_up + (uint64_t)cur_x * p.x_stride : nullptr;
+            const float xw = p.x_up ? __ldg(p.x_weight + c.m) : 1.0f;
             for (int k = threadIdx.x; k < p.K; k += cthreads) {
-                const float v = __ldg(x + k);
+                float v = __ldg(x + k);
+                if (xu) v = swiglu_mid(v, __ldg(xu + k), xw, p.x_limit, p.status);
                 badx |= !isfinite(v);
                 mx = fmaxf(mx, fabsf(v));
             }
@@ -679,7 +688,13 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
                 uint32_t d[4][2] = {{0u, 0u}, {0u, 0u}, {0u, 0u}, {0u, 0u}};
                 float s = 0.0f;
                 const float4 xa = __ldg(reinterpret_cast<const float4 *>(x + 8 * k8)), xb = __ldg(reinterpret_cast<const float4 *>(x + 8 * k8) + 1);
-                const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                if (xu) {
+                    const float4 ua = __ldg(reinterpret_cast<const float4 *>(xu + 8 * k8)), ub = __ldg(reinterpret_cast<const float4 *>(xu + 8 * k8) + 1);
+                    const float uv[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+#pragma unroll
+                    for (int i8 = 0; i8 < 8; ++i8) xv[i8] = swiglu_mid(xv[i8], uv[i8], xw, p.x_limit, p.status);
+                }
 #pragma unroll
                 for (int i8 = 0; i8 < 8; ++i8) {
                     int q = isfinite(xv[i8]) ? __float2int_rn(xv[i8] * to_q) : 0;
@@ -827,14 +842,21 @@ inline int stream_launch_t(StreamParams &p, const StreamShape &sh, cudaStream_t 
     return breg ? stream_launch_v<Dec, true, 1>(p, sh, stream) : stream_launch_v<Dec, false, 1>(p, sh, stream);
 }
 
+struct StreamActivation { const float *up; const float *weight; float limit; };
+
 inline int stream_launch(unsigned q, const uint8_t *enc, uint64_t matrix_stride, uint64_t count, uint64_t rows, uint64_t width,
                          uint64_t row_bytes, const float *x, uint64_t x_stride, const float *additive, float *out,
                          uint64_t out_stride, int round_bf16, int *status, cudaStream_t stream,
-                         const uint8_t *const *matrix_ptrs = nullptr, const uint32_t *x_rows = nullptr) {
+                         const uint8_t *const *matrix_ptrs = nullptr, const uint32_t *x_rows = nullptr,
+                         const StreamActivation *act = nullptr) {
     StreamShape sh;
     if (!stream_shape(q, width, row_bytes, sh)) return ERR_BOUNDS;
     StreamParams p{};
     p.matrix_ptrs = matrix_ptrs; p.x_rows = x_rows;
+    if (act) {
+        if (x_rows || (reinterpret_cast<uintptr_t>(act->up) & 15u)) return ERR_INVALID_ARG;
+        p.x_up = act->up; p.x_weight = act->weight; p.x_limit = act->limit;
+    }
     p.enc = enc; p.matrix_stride = matrix_stride; p.count = (uint32_t)count; p.rows = rows; p.row_bytes = row_bytes;
     p.K = (int)width; p.slices = sh.slices; p.units_per_slice = sh.units_per_slice; p.row_warps = sh.row_warps; p.depth = sh.depth;
     p.stage_bytes = sh.stage_bytes; p.smem_bytes = sh.smem_bytes;

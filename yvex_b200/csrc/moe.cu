@@ -104,7 +104,7 @@ ingress_router_kernel(const float *router, const float *x, uint64_t experts, uin
 // ---- scoring + top-k: one warp per row, experts <= 256 (8 per lane), topk <= 16 ------------------
 __global__ void route_rows_kernel(MoeGeom g, const float *logits, const float *scores_in, const float *bias,
                                   const int32_t *hash_table, const uint32_t *token_ids,
-                                  uint64_t rows, int32_t *selected, float *weights, int *status) {
+                                  uint64_t rows, int32_t *selected, float *weights, int *status, const RouteTables rt) {
     const int lane = threadIdx.x & 31;
     const uint64_t row = blockIdx.x * (uint64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
     pdl_wait();                                         // logits / scores come from the kernel before
@@ -185,6 +185,9 @@ __global__ void route_rows_kernel(MoeGeom g, const float *logits, const float *s
         v *= g.scaling;
         selected[row * g.topk + lane] = mine;
         weights[row * g.topk + lane] = (float)v;
+        if (rt.enabled) write_pair_tables(rt, row * (g.topk + 1) + lane, (uint32_t)row, false, mine, (float)v);
+    } else if (rt.enabled && (uint64_t)lane == g.topk) {
+        write_pair_tables(rt, row * (g.topk + 1) + lane, (uint32_t)row, true, 0, 1.0f);
     }
 }
 
@@ -307,14 +310,15 @@ static int route_into(const MoeGeom &g, const yvex_b200_moe_weights *w, const fl
         return ERR_INVALID_ARG;
     }
     route_rows_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, s>>>(g, logits, nullptr, w->bias, w->hash_table, token_ids, rows,
-                                                                selected, weights, status);
+                                                                selected, weights, status, RouteTables{});
     return launch_status(launches);
 }
 
 int yb::moe_ingress_and_route(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, const float *x,
                               const float *logits, const uint32_t *token_ids, uint64_t rows, int *status,
-                              cudaStream_t s) {
+                              cudaStream_t s, RouteTables *tables) {
     const uint64_t n = rows * g.hidden;
+    const RouteTables none{};
     if (w.router && rows <= 64 && g.hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
         (reinterpret_cast<uintptr_t>(w.router) & 15u) == 0) {
         // decode width: two launches (projection with ingress rounding and scoring fused; top-k)
@@ -322,10 +326,11 @@ int yb::moe_ingress_and_route(const MoeGeom &g, const MoeWeights &w, const MoeWo
         if (launch_pdl(ingress_router_kernel, dim3((unsigned)g.experts, (unsigned)rows), dim3(kRouterThreads), 0, s,
                        w.router, x, g.experts, g.hidden, ws.xr, ws.xr_h, ws.logits, ws.scores, status) != cudaSuccess ||
             launch_pdl(route_rows_kernel, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, s, g, ws.logits, ws.scores, w.bias,
-                       w.hash_table, token_ids, rows, ws.selected, ws.weights, status) != cudaSuccess)
+                       w.hash_table, token_ids, rows, ws.selected, ws.weights, status, tables ? *tables : none) != cudaSuccess)
             return ERR_BACKEND;
         return launch_status(2);
     }
+    if (tables) tables->enabled = 0;
     ingress_round_kernel<<<grid_for(n, 256, 8), 256, 0, s>>>(x, ws.xr, ws.xr_h, n, status);
     int rc = launch_status(1);
     if (rc != OK) return rc;
@@ -382,11 +387,22 @@ extern "C" int yvex_b200_moe_decode_parts(const yvex_b200_moe_geometry *geom, co
     ws.shared_out = shared_out;
     cudaStream_t s = as_stream(stream);
     mark_phase(0, s);
-    rc = moe_ingress_and_route(g, *w, ws, x, logits, token_ids, rows, status, s);
+    const bool streaming = moe_decode_stream_eligible(g, *w);
+    RouteTables tables{};
+    if (streaming) {
+        // the top-k kernel writes the streaming path's matrix tables for its row when it runs at decode width
+        const Geometry gg = geometry_of(g.gate_qtype), dg = geometry_of(g.down_qtype);
+        tables.w = *w;
+        tables.gate_bytes = g.inter * (g.hidden / gg.elems * gg.bytes);
+        tables.down_bytes = g.hidden * (g.inter / dg.elems * dg.bytes);
+        tables.t = stream_scratch;
+        tables.enabled = 1;
+    }
+    rc = moe_ingress_and_route(g, *w, ws, x, logits, token_ids, rows, status, s, streaming ? &tables : nullptr);
     if (rc != OK) return rc;
     mark_phase(1, s);
-    rc = moe_decode_stream_eligible(g, *w) ? moe_experts_stream(g, *w, ws, stream_scratch, rows, out, status, s)
-                                           : moe_experts_narrow(g, *w, ws, rows, out, status, s);
+    rc = streaming ? moe_experts_stream(g, *w, ws, stream_scratch, tables.enabled != 0, rows, out, status, s)
+                   : moe_experts_narrow(g, *w, ws, rows, out, status, s);
     if (rc != OK) return rc;
     if (selected_out) cudaMemcpyAsync(selected_out, ws.selected, rows * g.topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, s);
     if (weights_out) cudaMemcpyAsync(weights_out, ws.weights, rows * g.topk * sizeof(float), cudaMemcpyDeviceToDevice, s);

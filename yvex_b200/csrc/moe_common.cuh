@@ -75,6 +75,7 @@ struct DecodeStreamScratch {
     uint32_t *gu_rows;                         // input row of each gate/up matrix
     float *gu;                                 // [pairs][2][inter]
     float *y;                                  // [pairs][hidden] (bf16-rounded)
+    float *pair_weight;                        // [pairs] route weight of the pair (1 for the shared expert)
     void rebase(void *base) {
         auto b = reinterpret_cast<uintptr_t>(base);
         gu_ptrs = reinterpret_cast<const uint8_t **>(b + reinterpret_cast<uintptr_t>(gu_ptrs));
@@ -82,13 +83,29 @@ struct DecodeStreamScratch {
         gu_rows = reinterpret_cast<uint32_t *>(b + reinterpret_cast<uintptr_t>(gu_rows));
         gu = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(gu));
         y = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(y));
+        pair_weight = reinterpret_cast<float *>(b + reinterpret_cast<uintptr_t>(pair_weight));
     }
 };
+// What the router's top-k kernel needs to write the streaming decode path's tables itself (one launch less).
+struct RouteTables {
+    MoeWeights w;
+    uint64_t gate_bytes, down_bytes;           // bytes of one expert's gate (= up) and down matrix
+    DecodeStreamScratch t;
+    int enabled;
+};
+// pair q = row * (k + 1) + p: p < k the routed expert `expert` with route weight `weight`, p == k the shared expert
+__device__ __forceinline__ void write_pair_tables(const RouteTables &rt, uint64_t q, uint32_t row, bool shared, int64_t expert, float weight) {
+    rt.t.gu_ptrs[2 * q] = shared ? (const uint8_t *)rt.w.shared_gate : (const uint8_t *)rt.w.gate + (uint64_t)expert * rt.gate_bytes;
+    rt.t.gu_ptrs[2 * q + 1] = shared ? (const uint8_t *)rt.w.shared_up : (const uint8_t *)rt.w.up + (uint64_t)expert * rt.gate_bytes;
+    rt.t.gu_rows[2 * q] = rt.t.gu_rows[2 * q + 1] = row;
+    rt.t.down_ptrs[q] = shared ? (const uint8_t *)rt.w.shared_down : (const uint8_t *)rt.w.down + (uint64_t)expert * rt.down_bytes;
+    rt.t.pair_weight[q] = shared ? 1.0f : weight;
+}
 // Offsets (rebase() turns them into pointers) from `base`; returns the end.
 uint64_t moe_decode_stream_layout(const MoeGeom &g, uint64_t rows, uint64_t base, DecodeStreamScratch *out);
 bool moe_decode_stream_eligible(const MoeGeom &g, const MoeWeights &w);
 // The (k + 1) experts of every row as two batched launches of the streaming matvec (gate/up, down).
-int moe_experts_stream(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, const DecodeStreamScratch &t, uint64_t rows,
+int moe_experts_stream(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, const DecodeStreamScratch &t, bool tables_ready, uint64_t rows,
                        float *out, int *status, cudaStream_t s);
 
 // Expert execution for a narrow batch; picks the streaming tensor-core matvec kernels when the
@@ -104,7 +121,7 @@ int moe_down_rows(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws,
 // Ingress bf16 rounding of x into ws.xr, then router (projection or supplied logits) + top-k.
 int moe_ingress_and_route(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, const float *x,
                           const float *logits, const uint32_t *token_ids, uint64_t rows, int *status,
-                          cudaStream_t s);
+                          cudaStream_t s, RouteTables *tables = nullptr);      // tables->enabled is cleared when they were not written
 // Entry-point validation shared by the narrow and wide paths (fail-closed qtype check included).
 int moe_check_geometry(const yvex_b200_moe_geometry *g, const yvex_b200_moe_weights *w);
 

@@ -1,9 +1,11 @@
 // Decode-time expert execution on the streaming matvec: the (k + 1) experts of every row are run as
 // TWO batched launches of gemv_stream_kernel (gate and up of every active expert, then down), each a
 // persistent kernel that streams the selected experts' weight rows through shared memory once, found
-// through a device table of matrix addresses built from the router's selection. Between them one small
-// kernel applies SwiGLU * route weight -> bf16 (src/graph/moe.c:605-613) and one sums the per-pair bf16
-// rows in rank order, adds the shared expert's and rounds (src/runtime/moe.c:606-637).
+// through a device table of matrix addresses built from the router's selection (by the router's top-k
+// kernel itself at decode width, else by decode_tables_kernel). SwiGLU * route weight -> bf16
+// (src/graph/moe.c:605-613) is applied by the down launch while it prepares its input rows; one small
+// kernel sums the per-pair bf16 rows in rank order, adds the shared expert's and rounds
+// (src/runtime/moe.c:606-637).
 #include "gemv_stream.cuh"
 #include "moe_common.cuh"
 
@@ -20,6 +22,7 @@ uint64_t moe_decode_stream_layout(const MoeGeom &g, uint64_t rows, uint64_t base
     l.gu_rows = reinterpret_cast<uint32_t *>(take(pairs * 2 * sizeof(uint32_t)));
     l.gu = reinterpret_cast<float *>(take(pairs * 2 * imax * 4));
     l.y = reinterpret_cast<float *>(take(pairs * g.hidden * 4));
+    l.pair_weight = reinterpret_cast<float *>(take(pairs * 4));
     if (out) *out = l;
     return off;
 }
@@ -39,28 +42,14 @@ bool moe_decode_stream_eligible(const MoeGeom &g, const MoeWeights &w) {
 }
 
 // pair q = row * (k + 1) + p: p < k the routed expert selected[row][p], p == k the shared expert
-__global__ void decode_tables_kernel(MoeGeom g, MoeWeights w, const int32_t *selected, uint64_t rows, uint64_t gate_bytes,
-                                     uint64_t down_bytes, DecodeStreamScratch t, int *status) {
+__global__ void decode_tables_kernel(MoeGeom g, RouteTables rt, const int32_t *selected, const float *weights, uint64_t rows, int *status) {
     const uint64_t ppr = g.topk + 1, pairs = rows * ppr;
     for (uint64_t q = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; q < pairs; q += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t r = q / ppr, p = q % ppr;
         const bool shared = p == g.topk;
         int64_t e = shared ? 0 : selected[r * g.topk + p];
         if (e < 0 || (uint64_t)e >= g.experts) { raise(status, YVEX_B200_STATUS_ARGUMENT); e = 0; }
-        t.gu_ptrs[2 * q] = shared ? (const uint8_t *)w.shared_gate : (const uint8_t *)w.gate + (uint64_t)e * gate_bytes;
-        t.gu_ptrs[2 * q + 1] = shared ? (const uint8_t *)w.shared_up : (const uint8_t *)w.up + (uint64_t)e * gate_bytes;
-        t.gu_rows[2 * q] = t.gu_rows[2 * q + 1] = (uint32_t)r;
-        t.down_ptrs[q] = shared ? (const uint8_t *)w.shared_down : (const uint8_t *)w.down + (uint64_t)e * down_bytes;
-    }
-}
-
-__global__ void decode_swiglu_kernel(MoeGeom g, const float *gu, const float *weights, uint64_t rows, uint64_t imax, float *mid,
-                                     int *status) {
-    const uint64_t ppr = g.topk + 1, total = rows * ppr * g.inter;
-    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
-        const uint64_t q = i / g.inter, c = i % g.inter, r = q / ppr, p = q % ppr;
-        const float rw = p == g.topk ? 1.0f : weights[r * g.topk + p];
-        mid[q * imax + c] = swiglu_mid(gu[(2 * q) * imax + c], gu[(2 * q + 1) * imax + c], rw, (float)g.limit, status);
+        write_pair_tables(rt, q, (uint32_t)r, shared, e, shared ? 1.0f : weights[r * g.topk + p]);
     }
 }
 
@@ -77,23 +66,27 @@ __global__ void decode_combine_kernel(MoeGeom g, const float *y, uint64_t rows, 
     }
 }
 
-int moe_experts_stream(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, const DecodeStreamScratch &t, uint64_t rows,
-                       float *out, int *status, cudaStream_t s) {
+int moe_experts_stream(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace &ws, const DecodeStreamScratch &t, bool tables_ready,
+                       uint64_t rows, float *out, int *status, cudaStream_t s) {
     const Geometry gg = geometry_of(g.gate_qtype), dg = geometry_of(g.down_qtype);
     const uint64_t grb = g.hidden / gg.elems * gg.bytes, drb = g.inter / dg.elems * dg.bytes;
     const uint64_t pairs = rows * (g.topk + 1), imax = g.inter;
-    decode_tables_kernel<<<grid_for(pairs, 128, 1), 128, 0, s>>>(g, w, ws.selected, rows, g.inter * grb, g.hidden * drb, t, status);
-    int rc = launch_status(1);
-    if (rc != OK) return rc;
+    int rc;
+    if (!tables_ready) {
+        RouteTables rt{};
+        rt.w = w; rt.gate_bytes = g.inter * grb; rt.down_bytes = g.hidden * drb; rt.t = t; rt.enabled = 1;
+        decode_tables_kernel<<<grid_for(pairs, 128, 1), 128, 0, s>>>(g, rt, ws.selected, ws.weights, rows, status);
+        rc = launch_status(1);
+        if (rc != OK) return rc;
+    }
     rc = gs::stream_launch(g.gate_qtype, nullptr, 0, pairs * 2, g.inter, g.hidden, grb, ws.xr, g.hidden, nullptr, t.gu, imax, 0, status, s,
                            t.gu_ptrs, t.gu_rows);
     if (rc != OK) return rc;
-    decode_swiglu_kernel<<<grid_for(pairs * g.inter, 256, 8), 256, 0, s>>>(g, t.gu, ws.weights, rows, imax, ws.mid, status);
-    rc = launch_status(1);
-    if (rc != OK) return rc;
     mark_phase(2, s);
-    rc = gs::stream_launch(g.down_qtype, nullptr, 0, pairs, g.hidden, g.inter, drb, ws.mid, imax, nullptr, t.y, g.hidden, 1, status, s,
-                           t.down_ptrs, nullptr);
+    // input row of pair q = bf16(SwiGLU(gate row, up row) * route weight), formed while the launch prepares its activation planes
+    gs::StreamActivation act{t.gu + imax, t.pair_weight, (float)g.limit};
+    rc = gs::stream_launch(g.down_qtype, nullptr, 0, pairs, g.hidden, g.inter, drb, t.gu, 2 * imax, nullptr, t.y, g.hidden, 1, status, s,
+                           t.down_ptrs, nullptr, &act);
     if (rc != OK) return rc;
     decode_combine_kernel<<<grid_for(rows * g.hidden, 256, 8), 256, 0, s>>>(g, t.y, rows, out, ws.routed_out, ws.shared_out);
     mark_phase(3, s);
