@@ -549,13 +549,13 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
         TaskCursor ci, cj;                                   // next tile to fetch / next tile to publish
         ci.init(q0, tiles_m);
         cj.init(q0, tiles_m);
-        uint32_t issued = 0;
+        uint32_t issued = 0, i_slot = 0, i_phase = 0, j_buf = 0, j_phase = 0;      // i_phase = (issued / D) & 1, j_phase = (j / (D + 1)) & 1
         bool ok = true;
         const int per_tile = consumers * kGroupsPerWarp * kTileRows;
         for (uint32_t j = 0; j < n_local && ok; ++j, cj.next()) {
             while (issued < n_local && issued < j + (uint32_t)D && ok) {
-                const uint32_t slot = issued % D;
-                if (issued >= (uint32_t)D) ok = mbar_wait_warp<kTryWaitHintNs>(&ctl.empty[slot], ((issued / D) - 1u) & 1u, &ctl.abort);
+                const uint32_t slot = i_slot;               // issued % D; its previous use was one ring turn ago
+                if (issued >= (uint32_t)D) ok = mbar_wait_warp<kTryWaitHintNs>(&ctl.empty[slot], i_phase ^ 1u, &ctl.abort);
                 if (!ok) break;
                 uint64_t row0;
                 const uint32_t nrows = rows_of(ci, row0);
@@ -575,11 +575,13 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
                     if (bulk) bulk_load(dst, src, bulk, &ctl.full[slot]);
                 }
                 ++issued;
+                if (++i_slot == (uint32_t)D) { i_slot = 0; i_phase ^= 1u; }
                 ci.next();
             }
             if (!ok) break;
-            const uint32_t buf = j % (uint32_t)(D + 1);
-            ok = mbar_wait_warp<kTryWaitHintNs>(&ctl.red_full[buf], (j / (uint32_t)(D + 1)) & 1u, &ctl.abort);
+            const uint32_t buf = j_buf;
+            ok = mbar_wait_warp<kTryWaitHintNs>(&ctl.red_full[buf], j_phase, &ctl.abort);
+            if (++j_buf == (uint32_t)(D + 1)) { j_buf = 0; j_phase ^= 1u; }
             if (!ok) break;
             uint64_t row0;
             const uint32_t nrows = rows_of(cj, row0);
@@ -646,6 +648,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
     uint32_t cur_m = 0xffffffffu, cur_x = 0xffffffffu;
     TaskCursor c;
     c.init(q0, tiles_m);
+    uint32_t c_slot = 0, c_buf = 0, c_phase = 0;
     for (uint32_t i = 0; i < n_local; ++i, c.next()) {
         uint64_t row0;
         const uint32_t nrows = rows_of(c, row0);
@@ -738,8 +741,11 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
             if (kBReg) load_b(breg, 0);
             cur_m = c.m;
         }
-        const uint32_t slot = i % D, buf = i % (uint32_t)(D + 1);
-        if (!dead && !mbar_wait_warp<kTryWaitHintNs>(&ctl.full[slot], (i / D) & 1u, &ctl.abort)) dead = true;
+        // stage i % D with phase (i / D) & 1 and result buffer i % (D + 1), kept as counters (no divisions in this loop)
+        const uint32_t slot = c_slot, buf = c_buf;
+        if (!dead && !mbar_wait_warp<kTryWaitHintNs>(&ctl.full[slot], c_phase, &ctl.abort)) dead = true;
+        if (++c_slot == (uint32_t)D) { c_slot = 0; c_phase ^= 1u; }
+        if (++c_buf == (uint32_t)(D + 1)) c_buf = 0;
         float acc[kGroupsPerWarp][2];
         int bad[kGroupsPerWarp];
 #pragma unroll
