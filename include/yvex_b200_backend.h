@@ -420,6 +420,36 @@ int yvex_backend_moe_add_expert(yvex_backend_moe_execution *execution, const yve
                                 int shared, yvex_error *err);
 int yvex_backend_moe_finish(yvex_backend_moe_execution *execution, yvex_moe_layer_result *result, yvex_error *err);
 int yvex_backend_moe_close(yvex_backend_moe_execution **execution, yvex_error *err);
+/*
+ * Expert-parallel layer over the ranks of one box, one process per GPU (no reference counterpart: the reference is
+ * single-device). Rank r owns the tokens it passes in and the routed experts [r * E / world, (r + 1) * E / world):
+ * the job's layer plan describes the WHOLE layer (routed_experts = E), its routed weight views hold the rank's
+ * shard (E / world experts), the shared expert's and the router's views are the same on every rank. One call runs
+ * one layer for the rank's rows: router and top-k here, pairs dispatched to their experts' ranks and results brought
+ * back by all-to-all-v exchanges made of ncclSend / ncclRecv groups, rank-ordered combination here. Every rank must
+ * make the call; rows may differ between ranks.
+ *   yvex_moe_ep_unique_id   rank 0 creates the communicator's identifier (ncclGetUniqueId) and hands it to the
+ *                           other ranks by any means of the application (a file, a socket)
+ *   yvex_moe_ep_open        joins the communicator (blocks until every rank has joined); deadline_ms bounds every
+ *                           later wait for a peer
+ *   yvex_moe_ep_workspace_required / yvex_backend_workspace_attach size and provide the device scratch
+ *   yvex_moe_ep_execute_rows host rows in (batch->expanded_rows, hidden wide; router logits through the
+ *                           yvex_moe_row_batch_logits extension, or resident F32 router weights), host rows out
+ *                           (output->combined_rows; the selection when asked for). A peer that does not take part
+ *                           before the deadline aborts the communicator: YVEX_ERR_TIMEOUT now, YVEX_ERR_STATE on
+ *                           every later call; the backend itself stays usable.
+ * NCCL is loaded at run time (libnccl.so.2, or the path in YVEX_B200_NCCL_LIBRARY): YVEX_ERR_UNSUPPORTED without it.
+ */
+#define YVEX_MOE_EP_ID_BYTES 128
+typedef struct yvex_moe_ep yvex_moe_ep;
+int yvex_moe_ep_unique_id(unsigned char id[YVEX_MOE_EP_ID_BYTES], yvex_error *err);
+int yvex_moe_ep_open(yvex_moe_ep **out, yvex_backend *backend, const unsigned char id[YVEX_MOE_EP_ID_BYTES], unsigned int world,
+                     unsigned int rank, unsigned long long deadline_ms, yvex_error *err);
+int yvex_moe_ep_workspace_required(const yvex_moe_layer_plan *layer, unsigned long long rows, unsigned int world, unsigned long long *bytes,
+                                   yvex_error *err);
+int yvex_moe_ep_execute_rows(yvex_moe_ep *ep, const yvex_moe_layer_job *job, const yvex_moe_row_batch *batch,
+                             const yvex_moe_row_batch_output *output, yvex_moe_row_batch_result *result, yvex_error *err);
+int yvex_moe_ep_close(yvex_moe_ep **ep, yvex_error *err);
 /* "sizeof type N" / "offsetof type.field N" lines for every entry of yvex_b200_abi_fields.h, as this
  * library was compiled; a binding compares its own table with it. No reference counterpart. */
 const char *yvex_backend_abi_layout(void);

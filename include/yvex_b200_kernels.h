@@ -139,6 +139,10 @@ int yvex_b200_moe_route(const yvex_b200_moe_geometry *g, const yvex_b200_moe_wei
                         uint64_t rows, int32_t *selected, float *weights, float *logits_out,
                         void *workspace, uint64_t workspace_bytes, int *status, void *stream);
 
+/* Ingress rounding of n values (src/graph/moe.c:487-489): rounded_f32 = bf16(x) as f32, rounded_f16 = the same values
+ * as fp16 (the rows the expert-parallel dispatch sends and the grouped GEMM reads). Non-finite input sets the status word. */
+int yvex_b200_moe_ingress(const float *x, uint64_t n, float *rounded_f32, void *rounded_f16, int *status, void *stream);
+
 /*
  * One MoE FFN layer for a narrow batch (decode): ingress bf16 rounding, router, k routed experts
  * + the shared expert as dequant-fused matvecs with the SwiGLU*weight->bf16 epilogue, per-pair

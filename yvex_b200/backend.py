@@ -206,6 +206,11 @@ class QuantFailure(C.Structure):
 
 
 _lib.yvex_cuda_quant_row_dot.argtypes = [vp, C.c_uint, vp, C.c_size_t, vp, ull, C.POINTER(C.c_float), C.POINTER(QuantFailure), C.POINTER(Error)]
+_lib.yvex_moe_ep_unique_id.argtypes = [vp, C.POINTER(Error)]
+_lib.yvex_moe_ep_open.argtypes = [C.POINTER(vp), vp, vp, C.c_uint, C.c_uint, ull, C.POINTER(Error)]
+_lib.yvex_moe_ep_workspace_required.argtypes = [C.POINTER(LayerPlan), ull, C.c_uint, C.POINTER(ull), C.POINTER(Error)]
+_lib.yvex_moe_ep_execute_rows.argtypes = [vp, C.POINTER(LayerJob), vp, C.POINTER(RowBatchOutput), C.POINTER(RowBatchResult), C.POINTER(Error)]
+_lib.yvex_moe_ep_close.argtypes = [C.POINTER(vp), C.POINTER(Error)]
 _lib.yvex_backend_open.argtypes = [C.POINTER(vp), C.POINTER(Options), C.POINTER(Error)]
 _lib.yvex_backend_close_checked.argtypes = [C.POINTER(vp), C.POINTER(Error)]
 _lib.yvex_backend_close.argtypes = [vp]

@@ -66,7 +66,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         for log in pool.map(run, jobs):
             if log:
                 sys.stderr.write(log)
-    link = [_nvcc(), "-shared", "-o", LIB, *[o for _, o in jobs], "-lpthread"]
+    link = [_nvcc(), "-shared", "-o", LIB, *[o for _, o in jobs], "-lpthread", "-ldl"]
     r = subprocess.run(link, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("link failed:\n" + r.stdout + r.stderr)

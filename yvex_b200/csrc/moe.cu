@@ -360,6 +360,12 @@ extern "C" int yvex_b200_moe_route(const yvex_b200_moe_geometry *geom, const yve
     return route_into(g, w, rows_f32, logits, token_ids, rows, lw, selected, weights, status, as_stream(stream));
 }
 
+extern "C" int yvex_b200_moe_ingress(const float *x, uint64_t n, float *rounded_f32, void *rounded_f16, int *status, void *stream) {
+    if (!x || !rounded_f32 || !rounded_f16 || !status || !n) return ERR_INVALID_ARG;
+    ingress_round_kernel<<<grid_for(n, 256, 8), 256, 0, as_stream(stream)>>>(x, rounded_f32, static_cast<__half *>(rounded_f16), n, status);
+    return launch_status(1);
+}
+
 extern "C" int yvex_b200_moe_decode(const yvex_b200_moe_geometry *geom, const yvex_b200_moe_weights *w,
                                     const float *x, const float *logits, const uint32_t *token_ids,
                                     uint64_t rows, float *out, int32_t *selected_out, float *weights_out,

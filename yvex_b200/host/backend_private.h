@@ -58,4 +58,8 @@ int yvex_backend_take_status(yvex_backend *backend, int *code);
 /* Test seam of the reference (src/backend/cuda/qtype.c:625-661): 1 if the environment variable `name` is set to `value`. */
 int yvex_test_seam(const char *name, const char *value);
 void yvex_moe_graphs_release(yvex_backend *backend);
+int yvex_moe_plan_geometry(const yvex_moe_layer_plan *layer, const yvex_moe_layer_job *job, yvex_b200_moe_geometry *g);
+int yvex_moe_resolve_view(const yvex_backend *backend, const yvex_moe_weight_view *v, int required, const void **out);
+int yvex_moe_view_consistent(const yvex_moe_weight_view *v, unsigned long long rows, unsigned long long width);
+int yvex_moe_status_error(int code, yvex_error *err);
 #endif

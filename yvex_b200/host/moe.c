@@ -1154,3 +1154,9 @@ const yvex_backend_moe_operations *yvex_backend_moe_operations_get(const yvex_ba
         return NULL;
     return &moe_operations;
 }
+
+/* ---- helpers shared with the expert-parallel entry (host/ep.c) ------------------------------------------ */
+int yvex_moe_plan_geometry(const yvex_moe_layer_plan *layer, const yvex_moe_layer_job *job, yvex_b200_moe_geometry *g) { return plan_geometry(layer, job, g); }
+int yvex_moe_resolve_view(const yvex_backend *backend, const yvex_moe_weight_view *v, int required, const void **out) { return resolve_view(backend, v, required, out); }
+int yvex_moe_view_consistent(const yvex_moe_weight_view *v, unsigned long long rows, unsigned long long width) { return view_consistent(v, rows, width); }
+int yvex_moe_status_error(int code, yvex_error *err) { return status_error(code, err); }
