@@ -12,7 +12,8 @@ the host cores (the compiled reference when oracle/_ref is present, else the pla
 
 At N > 1 the expert-parallel layer runs with the library's defaults; for experiments the environment can
 turn its peer-memory paths off (YVEX_EP_PEER_DISPATCH=0, YVEX_EP_PEER_RETURN=0: rows then travel by NCCL
-all-to-all-v) and shape the exchange-based pipeline (YVEX_EP_SEGMENTS, YVEX_EP_OVERLAP=1, YVEX_EP_CTAS).
+all-to-all-v) and shape the exchange-based pipeline (YVEX_EP_SEGMENTS, YVEX_EP_OVERLAP=1, YVEX_EP_CTAS);
+YVEX_BENCH_C11=1 adds `c11_nccl_exchange`: the same step through the C11 orchestration over NCCL send/recv groups.
 """
 from __future__ import annotations
 
@@ -701,7 +702,14 @@ def run_native_ep(args):
         torch.cuda.synchronize()
         if not torch.equal(host_out.view(torch.int32), step(0).cpu().view(torch.int32)):
             raise RuntimeError("execute_rows_wide (host rows) differs from the device-resident layer")
-    twin = gemv = sessions2 = None
+    twin = gemv = sessions2 = c11 = None
+    if world > 1 and os.environ.get("YVEX_BENCH_C11", "0") != "0":
+        # opt-in (YVEX_BENCH_C11=1): the same step through the C11 orchestration (yvex_moe_ep_execute_rows: NCCL send/recv
+        # groups, pinned host rows in and out), beside the Python layer's peer-memory path that the headline measures
+        try:
+            c11 = c11_exchange_record(torch, dist, args, wl, spec, shard, host_x, host_lg, local, rank, world, step(0))
+        except Exception as exc:
+            c11 = {"value": None, "failed": f"{type(exc).__name__}: {exc}"}
     if world == 1 and rank == 0:
         try:
             sessions2 = two_sessions(args.steps)
@@ -772,6 +780,7 @@ def run_native_ep(args):
                 "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(T * (H + E) * 4),
                         "d2h_bytes_per_step": int(T * H * 4), "api": e2e_api},
                 **({"e2e_two_sessions": sessions2} if sessions2 else {}),
+                **({"c11_nccl_exchange": c11} if c11 else {}),
                 "gpu_launches": int(launches * world),
                 "phases_ms": {"gate_up_gemm": gu, "swiglu": sw, "down_gemm": dn,
                               **({"pairs_in_timed_gemm": pairs, "step_spans_rank0": {k: sum(v) / len(v) for k, v in spans.items()}}
@@ -781,6 +790,58 @@ def run_native_ep(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def c11_exchange_record(torch, dist, args, wl, spec, shard, host_x, host_lg, local, rank, world, want):
+    """Every rank: its shard resident on a host-boundary backend, yvex_moe_ep_open over an identifier broadcast from rank
+    0, then timed yvex_moe_ep_execute_rows calls (wall clock around a synchronous call, max over ranks)."""
+    import ctypes as C
+    from yvex_b200 import backend as B
+    T, H, E = wl.cfg["tokens"], wl.cfg["hidden"], wl.cfg["experts"]
+    t_loc, dev = T // world, torch.device("cuda", local)
+    be = B.Backend(device=f"cuda:{local}".encode())
+    if be.rc != B.OK:
+        raise RuntimeError("host boundary failed to open: " + be.message())
+    arena = B.ResidentArena(be, {k: v.cpu().numpy() for k, v in shard.items()})
+    local_spec = type(spec)(H, E // world, spec.topk, wl.cfg["inter"], down_qtype=spec.down_qtype)
+    job = B.moe_job(arena, local_spec, router=False, family=b"sm100-f16-tcgen05-expert")
+    job._plan.routed_experts = E
+    ident = (C.c_ubyte * 128)()
+    if rank == 0 and B._lib.yvex_moe_ep_unique_id(ident, C.byref(be.err)) != B.OK:
+        raise RuntimeError("yvex_moe_ep_unique_id: " + be.message())
+    box = torch.tensor(list(bytes(ident)), dtype=torch.uint8, device=dev)
+    dist.broadcast(box, 0)
+    C.memmove(ident, bytes(box.cpu().tolist()), 128)
+    ep, need = B.vp(), B.ull()
+    if B._lib.yvex_moe_ep_open(C.byref(ep), be.h, ident, world, rank, 60000, C.byref(be.err)) != B.OK:
+        raise RuntimeError("yvex_moe_ep_open: " + be.message())
+    try:
+        assert B._lib.yvex_moe_ep_workspace_required(job.layer, t_loc, world, C.byref(need), C.byref(be.err)) == B.OK
+        rcw, ws, _ = be.tensor(need.value)
+        assert rcw == B.OK and B._lib.yvex_backend_workspace_attach(be.h, ws, C.byref(be.err)) == B.OK, be.message()
+        out = torch.empty((t_loc, H), dtype=torch.float32).pin_memory()
+        batch = B.row_batch(t_loc, H, host_rows=host_x.data_ptr(), router_logits=host_lg.data_ptr())
+        bout, res = B.row_output(out.data_ptr(), t_loc * H), B.RowBatchResult()
+        times = []
+        for i in range(2 + max(3, min(args.steps, 10))):
+            dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            if B._lib.yvex_moe_ep_execute_rows(ep, C.byref(job), C.byref(batch), C.byref(bout), C.byref(res), C.byref(be.err)) != B.OK:
+                raise RuntimeError("yvex_moe_ep_execute_rows: " + be.message())
+            if i >= 2:
+                times.append(time.perf_counter() - t0)
+        same = torch.equal(out.view(torch.int32), want.cpu().view(torch.int32))
+        tm = torch.tensor(times, dtype=torch.float64, device=dev)
+        ok = torch.tensor([int(same)], device=dev)
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        t = float(tm.mean())
+        return {"value": T / t, "unit": UNIT, "ms_per_step": t * 1e3, "steps": len(times), "bitwise_equal_to_the_timed_layer": bool(ok.item()),
+                "api": "yvex_moe_ep_execute_rows (C11, ncclSend/ncclRecv groups), pinned host rows in and out, no overlap of exchange and GEMMs"}
+    finally:
+        B._lib.yvex_moe_ep_close(C.byref(ep), C.byref(be.err))
+        be.close()
 
 
 def _timed_events(torch, fn, steps, before=None):
