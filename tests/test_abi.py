@@ -144,3 +144,20 @@ def test_ctypes_mirror_matches_the_compiled_layout(lib):
     ops = {f: getattr(B.MoeOperations, f).offset for f, _ in B.MoeOperations._fields_}
     for f in ("derived_layout_plan", "derived_layout_build", "workspace_required", "execute_rows", "complete_rows"):
         assert ops[f] == int(table[f"offsetof yvex_backend_moe_operations.{f}"])
+
+
+def test_expert_parallel_entry_refuses_bad_arguments_before_touching_nccl(lib):
+    from yvex_b200 import backend as B
+    err, need, ep = B.Error(), B.ull(), B.vp()
+    plan = B.LayerPlan(schema_version=1, hidden_width=512, routed_experts=8, experts_per_token=2, expert_intermediate_width=256,
+                       shared_intermediate_width=256)
+    fn = B._lib.yvex_moe_ep_workspace_required
+    assert fn(C.byref(plan), 64, 3, C.byref(need), C.byref(err)) == B.INVALID_ARG        # 3 ranks do not divide 8 experts
+    assert fn(C.byref(plan), 0, 2, C.byref(need), C.byref(err)) == B.INVALID_ARG
+    assert fn(C.byref(plan), 64, 2, C.byref(need), C.byref(err)) == B.OK and need.value % 256 == 0 and need.value > 64 * 2 * 2 * 512
+    more = B.ull()
+    assert fn(C.byref(plan), 64, 4, C.byref(more), C.byref(err)) == B.OK and more.value > need.value      # room for every rank's pairs
+    ident = (C.c_ubyte * 128)()
+    assert B._lib.yvex_moe_ep_open(C.byref(ep), None, ident, 2, 0, 1000, C.byref(err)) == B.INVALID_ARG and not ep.value
+    assert B._lib.yvex_moe_ep_execute_rows(None, None, None, None, None, C.byref(err)) == B.INVALID_ARG
+    assert B._lib.yvex_moe_ep_close(C.byref(ep), C.byref(err)) == B.OK
