@@ -1,6 +1,6 @@
 /*
  * Expert-parallel MoE layer over the ranks of one box, orchestrated from C11 with NCCL point-to-point calls
- * (no reference counterpart: the reference is single-device, README "Project Status"; per-pair meaning
+ * (no reference counterpart: the reference is single-device, as its own README.md:184 states; per-pair meaning
  * src/graph/moe.c:587-622, combination src/runtime/moe.c:596-645).
  *
  * One process per GPU. Every rank owns the tokens it is given (its home rows) and a contiguous shard of
