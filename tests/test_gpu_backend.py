@@ -870,3 +870,49 @@ def test_execute_rows_replays_a_launch_graph_from_the_third_call(B, golden, case
     off = run_rows(B, be, ops, job, x, logits)
     assert off[0] == B.OK and off[4].graph_launches == 0 and (off[1].view(np.uint32) == runs[0][1].view(np.uint32)).all()
     assert be.close() == B.OK
+
+
+def test_token_transaction_hash_router_and_bf16_router_rows(B, port):
+    """The two other router forms of the transaction: a hash router (the token's table row names the experts, the
+    weights still come from the scores) and router weights stored as BF16 rows (projected by the dequant matvec
+    instead of the F32 double-accumulation kernel); the chosen experts' outputs against the CPU port."""
+    spec, weights, router, x, _ = layer_inputs("small_router")
+    H, E, k = spec.hidden, spec.experts, spec.topk
+    table = np.array([[5, 2], [1, 7], [0, 3]], np.int32)
+    router16 = synth.bf16_bits(router)                               # [E, H] uint16
+    be = B.Backend()
+    arena = B.ResidentArena(be, dict(weights, router=router, router16=router16, hash_table=table))
+    job = B.moe_job(arena, spec, router=True, router_class=0, hash_rows=3)
+    attach_workspace(B, be, job, 1)
+    # hash router, token 1 -> experts 1 and 7
+    job.token_id, job.token_id_present = 1, 1
+    rc, res, a = run_token(B, be, job, spec, x[0])
+    assert rc == B.OK, be.message()
+    assert list(res.router.selected_experts[:k]) == [1, 7]
+    logits = np.array(res.router.router_logits[:E], np.float64)
+    scores = np.sqrt(np.logaddexp(0.0, logits))
+    want_w = scores[[1, 7]] / scores[[1, 7]].sum() * spec.scaling if spec.normalize else scores[[1, 7]] * spec.scaling
+    assert np.abs(np.array(res.router.selected_weights[:k]) - want_w).max() <= 1e-6
+    xr = synth.bf16_round(x[0])
+    routed = np.zeros(H, np.float32)
+    for r, e in enumerate([1, 7]):
+        rc_e, y = port.expert(H, spec.inter, spec.limit, spec.gate_qtype, spec.up_qtype, spec.down_qtype, weights["gate"][e],
+                              weights["up"][e], weights["down"][e], xr, float(res.router.selected_weights[r]))
+        assert rc_e == 0
+        routed += y
+    assert rel_l2(a["routed"], routed) <= 1e-3
+    job.token_id = 3                                                 # past the table
+    assert run_token(B, be, job, spec, x[0])[0] == B.BOUNDS
+    job.token_id_present = 0
+    assert run_token(B, be, job, spec, x[0])[0] == B.BOUNDS
+    # learned router with BF16 rows: the same selection as the F32 rows rounded to bf16 give on the CPU
+    job2 = B.moe_job(arena, spec, router=True)
+    v = job2.weights[B.W_ROUTER]
+    v.qtype, v.encoded, v.encoded_bytes, v.row_bytes = synth.BF16, arena.host_ptr("router16"), router16.nbytes, H * 2
+    rc, res, a = run_token(B, be, job2, spec, x[1])
+    assert rc == B.OK, be.message()
+    lg = synth.bf16_round(router).astype(np.float64) @ synth.bf16_round(x[1]).astype(np.float64)
+    assert np.abs(np.array(res.router.router_logits[:E]) - lg).max() <= 1e-4 * (1 + np.abs(lg).max())
+    order = sorted(range(E), key=lambda e: (-np.float32(np.sqrt(np.logaddexp(0.0, np.float32(lg[e])))), e))[:k]
+    assert list(res.router.selected_experts[:k]) == order
+    assert be.close() == B.OK
