@@ -17,7 +17,9 @@
 // planes 3,2 and 1,0) share one decoded A fragment.
 //
 // Data movement. A tile is 16 (or 32) consecutive matrix rows = one contiguous byte range, fetched
-// by ONE bulk copy (cp.async.bulk + mbarrier) into a ring of stages; a control warp issues the
+// by ONE bulk copy (cp.async.bulk + mbarrier) into a ring of stages - or, for decoders whose loads would
+// otherwise meet the 8 rows of an MMA fragment on the same shared-memory banks (row sizes that are
+// multiples of 128 bytes), by one bulk copy per row into rows spaced row bytes + Dec::kRowPad apart; a control warp issues the
 // copies, and afterwards adds the K-slice partial sums of each tile in a fixed order, applies
 // additive / bf16 rounding and stores the results. Consumer warp w decodes K-slice w of the
 // staged rows straight from shared memory.
@@ -131,6 +133,7 @@ struct StreamIq2 {
     static constexpr int kSumGroup = 0;                  // activation sums over this many values (0: none needed)
     static constexpr bool kInterleave = false;           // order of the activation digits within a group of 32 (see StreamMxfp4)
     static constexpr bool kParity = false;               // unit<1> for odd units of a row, unit<0> for even ones
+    static constexpr int kRowPad = 0;                    // bytes between the rows of a stage (0: the tile arrives as one copy)
 
     __device__ __forceinline__ static void group(uint32_t a, uint32_t &grids, uint32_t &ss) {
         // a group starts on a 2-byte boundary: three aligned words, funnel-shifted when it sits mid-word
@@ -197,6 +200,7 @@ struct StreamQ4k {
     static constexpr bool kTables = false;
     static constexpr int kSumGroup = 32;
     static constexpr bool kInterleave = false, kParity = false;
+    static constexpr int kRowPad = 0;                    // (64 measured: 2.3 KB row copies are slower than the conflicts they avoid)
 
     // 6-bit (scale, min) of sub-block j from the 12 packed bytes behind d and dmin (three aligned words)
     __device__ __forceinline__ static void scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int h, int t, uint32_t &sc, uint32_t &m) {
@@ -266,6 +270,7 @@ struct StreamQ2k {
     static constexpr bool kTables = false;
     static constexpr int kSumGroup = 16;
     static constexpr bool kInterleave = false, kParity = false;
+    static constexpr int kRowPad = 0;
 
     template <int H, int J> __device__ __forceinline__ static void step(const uint32_t (&w0)[8], const uint32_t (&w1)[8], int shift,
                                                                         uint32_t sc0, uint32_t sc1, const BUnit &b, int (&ca)[4],
@@ -318,6 +323,7 @@ struct StreamQ80 {
     static constexpr bool kTables = false;
     static constexpr int kSumGroup = 0;
     static constexpr bool kInterleave = false, kParity = false;
+    static constexpr int kRowPad = 16;                   // word loads: eight rows on banks 4 apart meet two at a time instead of eight
 
     __device__ __forceinline__ static void block(uint32_t a, uint32_t (&q)[8], float &d, int &bad, int flag) {
         // the block starts on a 2-byte boundary: nine aligned words, funnel-shifted when it sits mid-word
@@ -382,6 +388,7 @@ struct StreamMxfp4 {
     static constexpr bool kTables = false;
     static constexpr int kSumGroup = 32;
     static constexpr bool kInterleave = true, kParity = true;
+    static constexpr int kRowPad = 0;
 
     template <int H, int kOdd> __device__ __forceinline__ static void block(uint32_t unit, int t, uint32_t (&x)[4], float &scale, int &bad,
                                                                             int flag) {
@@ -451,6 +458,7 @@ struct StreamParams {
     const uint8_t *const *matrix_ptrs;
     const uint32_t *x_rows;
     uint64_t rows, row_bytes;
+    uint32_t pitch;                     // bytes from one row of a stage to the next (row_bytes, or more when the rows are copied one by one)
     int K, slices, units_per_slice, row_warps, depth;      // consumer warps = slices x row_warps
     uint32_t stage_bytes, smem_bytes;
     const float *x;                     // input vector of matrix m at x + m * x_stride
@@ -566,13 +574,21 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
                     break;
                 }
                 const uint8_t *src = mat + row0 * p.row_bytes;
-                const uint32_t bytes = (uint32_t)(nrows * p.row_bytes), bulk = bytes & ~15u;
                 uint8_t *dst = generic(ctl.stage[slot]);
-                if (lane < (int)(bytes - bulk)) dst[bulk + lane] = __ldg(src + bulk + lane);      // the last < 16 bytes of a ragged tile
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_expect_tx(&ctl.full[slot], bulk);
-                    if (bulk) bulk_load(dst, src, bulk, &ctl.full[slot]);
+                if (p.pitch != (uint32_t)p.row_bytes) {
+                    // one copy per row (rows are multiples of 16 bytes here), all counted by the same barrier
+                    if (lane == 0) mbar_expect_tx(&ctl.full[slot], (uint32_t)(nrows * p.row_bytes));
+                    __syncwarp();
+                    for (uint32_t r = (uint32_t)lane; r < nrows; r += 32)
+                        bulk_load(dst + (size_t)r * p.pitch, src + (uint64_t)r * p.row_bytes, (uint32_t)p.row_bytes, &ctl.full[slot]);
+                } else {
+                    const uint32_t bytes = (uint32_t)(nrows * p.row_bytes), bulk = bytes & ~15u;
+                    if (lane < (int)(bytes - bulk)) dst[bulk + lane] = __ldg(src + bulk + lane);      // the last < 16 bytes of a ragged tile
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_expect_tx(&ctl.full[slot], bulk);
+                        if (bulk) bulk_load(dst, src, bulk, &ctl.full[slot]);
+                    }
                 }
                 ++issued;
                 if (++i_slot == (uint32_t)D) { i_slot = 0; i_phase ^= 1u; }
@@ -624,7 +640,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
     l.sgn_base = l.nib_base + 128u;
     constexpr int kSumsPerUnit = Dec::kSumGroup ? Dec::kBlockK / Dec::kSumGroup : 0;
     uint32_t sums = ctl.sums + (uint32_t)(unit0 * kSumsPerUnit * 4);
-    const uint32_t row_bytes = (uint32_t)p.row_bytes;
+    const uint32_t row_bytes = p.pitch;                                    // stage rows, as the consumers see them
     float *red_all = reinterpret_cast<float *>(generic(ctl.red));
     const int cthreads = consumers * 32;
     if (threadIdx.x < 64 * p.units_per_slice + 4) reinterpret_cast<uint32_t *>(generic(ctl.zeros))[threadIdx.x] = 0u;
@@ -791,7 +807,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
 }
 
 // ---- host side -----------------------------------------------------------------------------------------------
-struct StreamShape { int slices, units_per_slice, row_warps, consumers, depth, groups; uint32_t stage_bytes, smem_bytes; };
+struct StreamShape { int slices, units_per_slice, row_warps, consumers, depth, groups; uint32_t stage_bytes, smem_bytes, pitch; };
 
 // K-slices (consumer warps along K), units per slice, warps along the rows of a stage and the deepest ring that fits.
 inline bool stream_shape(unsigned q, uint64_t width, uint64_t row_bytes, StreamShape &sh) {
@@ -803,10 +819,17 @@ inline bool stream_shape(unsigned q, uint64_t width, uint64_t row_bytes, StreamS
     sh.slices = (units + sh.units_per_slice - 1) / sh.units_per_slice;
     sh.row_warps = sh.slices <= kMaxConsumers / 2 ? 2 : 1;
     sh.consumers = sh.slices * sh.row_warps;
+    {
+        const int pad = q == Q_Q4_K ? StreamQ4k::kRowPad : q == Q_Q8_0 ? StreamQ80::kRowPad : q == Q_MXFP4 ? StreamMxfp4::kRowPad : 0;
+        // Padded rows help where the row size is a multiple of 128 bytes (every row of a fragment on the same banks) and a
+        // row is large: an SM completes about 8.5 M bulk copies a second, so rows of 4352 bytes still stream at 5.5 TB/s
+        // over the device while rows of 2304 bytes would be held to 2.9 TB/s.
+        sh.pitch = (uint32_t)row_bytes + (pad && row_bytes % 128 == 0 && row_bytes >= 4096 ? (uint32_t)pad : 0u);
+    }
     const uint32_t limit = 226u * 1024u;                   // the kernel also has a few hundred bytes of static shared memory
     // two row groups per warp when at least three such stages fit, else one
     for (sh.groups = kMaxGroupsPerWarp; sh.groups >= 1; --sh.groups) {
-        sh.stage_bytes = (uint32_t)(kTileRows * sh.groups * sh.row_warps * row_bytes);
+        sh.stage_bytes = (uint32_t)(kTileRows * sh.groups * sh.row_warps * sh.pitch);
         for (sh.depth = kMaxDepth; sh.depth >= (sh.groups > 1 ? 3 : 2); --sh.depth) {
             // every piece is rounded up to 128 bytes; with tables one piece may have to step over the table window,
             // which starts at most 64 KiB - 1 into the allocation (what lies before it stays usable)
@@ -865,7 +888,7 @@ inline int stream_launch(unsigned q, const uint8_t *enc, uint64_t matrix_stride,
     }
     p.enc = enc; p.matrix_stride = matrix_stride; p.count = (uint32_t)count; p.rows = rows; p.row_bytes = row_bytes;
     p.K = (int)width; p.slices = sh.slices; p.units_per_slice = sh.units_per_slice; p.row_warps = sh.row_warps; p.depth = sh.depth;
-    p.stage_bytes = sh.stage_bytes; p.smem_bytes = sh.smem_bytes;
+    p.stage_bytes = sh.stage_bytes; p.smem_bytes = sh.smem_bytes; p.pitch = sh.pitch;
     p.x = x; p.x_stride = x_stride; p.additive = additive; p.out = out; p.out_stride = out_stride;
     p.round_bf16 = round_bf16; p.status = status;
     switch (q) {
