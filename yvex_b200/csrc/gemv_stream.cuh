@@ -511,6 +511,10 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
     const uint64_t tiles_m = (p.rows + tile_rows - 1) / tile_rows, Q = (uint64_t)p.count * tiles_m;
     const uint64_t q0 = Q * blockIdx.x / gridDim.x, q1 = Q * (blockIdx.x + 1) / gridDim.x;
     const uint32_t n_local = (uint32_t)(q1 - q0);
+    // Launched with programmatic stream serialization: this CTA may start while the kernel before it on the stream still
+    // runs. Everything up to pdl_wait() (shared-memory layout, barriers, the table image, which is a constant) touches
+    // nothing that kernel could write; the kernel after this one may be scheduled as soon as SMs come free.
+    pdl_trigger();
 
     if (threadIdx.x == 0) {
         // placement: a bump allocator over the dynamic window that steps over the 64 KiB-aligned table window
@@ -554,6 +558,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
             mbar_expect_tx(&ctl.tab_full, kTableBytes);
             bulk_load(generic(ctl.table), &kIq2StreamTable, kTableBytes, &ctl.tab_full);
         }
+        pdl_wait();                                          // matrix tables, weights and inputs may come from the kernel before
         TaskCursor ci, cj;                                   // next tile to fetch / next tile to publish
         ci.init(q0, tiles_m);
         cj.init(q0, tiles_m);
@@ -626,6 +631,7 @@ __global__ void __launch_bounds__(32 * (kMaxConsumers + 1), 1) gemv_stream_kerne
     if (warp > consumers) return;
 
     // ---------------- consumer warps ----------------
+    pdl_wait();
     Lane l;
     l.g = lane >> 2; l.t = lane & 3;
     const int sl = warp % p.slices, rw = warp / p.slices;
@@ -860,7 +866,8 @@ inline int stream_launch_v(StreamParams &p, const StreamShape &sh, cudaStream_t 
     const uint64_t tile_rows = (uint64_t)kTileRows * kG * sh.row_warps;
     const uint64_t tasks = (uint64_t)p.count * ((p.rows + tile_rows - 1) / tile_rows);
     const unsigned grid = (unsigned)(tasks < (uint64_t)kSmCount ? tasks : (uint64_t)kSmCount);
-    gemv_stream_kernel<Dec, kBReg, kG><<<grid, 32 * (sh.consumers + 1), sh.smem_bytes, stream>>>(p);
+    if (launch_pdl(gemv_stream_kernel<Dec, kBReg, kG>, dim3(grid), dim3(32 * (sh.consumers + 1)), sh.smem_bytes, stream, p) != cudaSuccess)
+        return ERR_BACKEND;
     return launch_status(1);
 }
 

@@ -391,6 +391,9 @@ extern "C" int yvex_b200_moe_decode_parts(const yvex_b200_moe_geometry *geom, co
     stream_scratch.rebase(workspace);
     ws.routed_out = routed_out;
     ws.shared_out = shared_out;
+    // the router writes the caller's selection arrays themselves when there are any: no copies behind the layer
+    if (selected_out) ws.selected = selected_out;
+    if (weights_out) ws.weights = weights_out;
     cudaStream_t s = as_stream(stream);
     mark_phase(0, s);
     const bool streaming = moe_decode_stream_eligible(g, *w);
@@ -410,8 +413,6 @@ extern "C" int yvex_b200_moe_decode_parts(const yvex_b200_moe_geometry *geom, co
     rc = streaming ? moe_experts_stream(g, *w, ws, stream_scratch, tables.enabled != 0, rows, out, status, s)
                    : moe_experts_narrow(g, *w, ws, rows, out, status, s);
     if (rc != OK) return rc;
-    if (selected_out) cudaMemcpyAsync(selected_out, ws.selected, rows * g.topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, s);
-    if (weights_out) cudaMemcpyAsync(weights_out, ws.weights, rows * g.topk * sizeof(float), cudaMemcpyDeviceToDevice, s);
     return launch_status(0);
 }
 

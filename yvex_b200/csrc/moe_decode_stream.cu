@@ -55,6 +55,8 @@ __global__ void decode_tables_kernel(MoeGeom g, RouteTables rt, const int32_t *s
 
 __global__ void decode_combine_kernel(MoeGeom g, const float *y, uint64_t rows, float *out, float *routed_out, float *shared_out) {
     const uint64_t ppr = g.topk + 1, total = rows * g.hidden;
+    pdl_wait();                                              // y comes from the launch before
+    pdl_trigger();
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint64_t r = i / g.hidden, h = i % g.hidden;
         float routed = 0.0f;
@@ -88,7 +90,9 @@ int moe_experts_stream(const MoeGeom &g, const MoeWeights &w, const MoeWorkspace
     rc = gs::stream_launch(g.down_qtype, nullptr, 0, pairs, g.hidden, g.inter, drb, t.gu, 2 * imax, nullptr, t.y, g.hidden, 1, status, s,
                            t.down_ptrs, nullptr, &act);
     if (rc != OK) return rc;
-    decode_combine_kernel<<<grid_for(rows * g.hidden, 256, 8), 256, 0, s>>>(g, t.y, rows, out, ws.routed_out, ws.shared_out);
+    if (launch_pdl(decode_combine_kernel, dim3(grid_for(rows * g.hidden, 256, 8)), dim3(256), 0, s, g, (const float *)t.y, rows, out, ws.routed_out,
+                   ws.shared_out) != cudaSuccess)
+        return ERR_BACKEND;
     mark_phase(3, s);
     return launch_status(1);
 }
