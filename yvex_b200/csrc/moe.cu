@@ -145,36 +145,43 @@ __global__ void route_rows_kernel(MoeGeom g, const float *logits, const float *s
             if ((uint64_t)lane < g.topk && (uint64_t)lane > r && other == mine) raise(status, YVEX_B200_STATUS_ARGUMENT);
         }
     } else {
-        for (uint64_t r = 0; r < g.topk; ++r) {
-            float best = -INFINITY;
+        // k rounds of arg-max over the biased scores, lowest index winning ties (src/graph/moe.c:541-556). A float's bit pattern
+        // becomes an unsigned key of the same order (sign bit flipped for positives, all bits for negatives; -0 was made +0), so
+        // one warp reduction finds the largest value and a second the lowest expert that holds it; a key of 0 stands for
+        // "consumed or not an expert". The winning lane hands the expert's unbiased score over in the same round.
+        const int topk = (int)g.topk, experts = (int)g.experts;
+        uint32_t key[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t bits = __float_as_uint(biased[i] + 0.0f);
+            key[i] = lane + 32 * i < experts && biased[i] == biased[i] ? bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u) : 0u;      // a NaN is never chosen
+        }
+        for (int r = 0; r < topk; ++r) {
+            uint32_t best = 0u;
             int best_e = 0x7fffffff;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int e = lane + 32 * i;
-                if ((uint64_t)e < g.experts && (biased[i] > best || (biased[i] == best && e < best_e))) {
-                    best = biased[i];
-                    best_e = e;
-                }
-            }
+            for (int i = 0; i < 8; ++i)
+                if (key[i] > best) { best = key[i]; best_e = lane + 32 * i; }        // ascending e within a lane: the first maximum stays
+            const uint32_t top = __reduce_max_sync(0xffffffffu, best);
+            if (top == 0u) { raise(status, YVEX_B200_STATUS_NUMERIC); break; }
+            const int win = (int)__reduce_min_sync(0xffffffffu, (unsigned)(best == top ? best_e : 0x7fffffff));
+            float s = 0.0f;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-                if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-            }
-            if (best_e == 0x7fffffff) { raise(status, YVEX_B200_STATUS_NUMERIC); best_e = 0; }
-            if ((best_e & 31) == lane) biased[best_e >> 5] = -INFINITY;   // consumed (scores are finite)
-            if ((uint64_t)lane == r) mine = best_e;
+            for (int i = 0; i < 8; ++i) if (win == lane + 32 * i) { s = score[i]; key[i] = 0u; }
+            s = __shfl_sync(0xffffffffu, s, win & 31);
+            if (lane == r) { mine = win; mine_w = s; }
         }
     }
-    // weight of rank r = unbiased score of its expert; total accumulated in rank order in double
-    for (uint64_t r = 0; r < g.topk; ++r) {
-        int32_t e = __shfl_sync(0xffffffffu, mine, (int)r);
-        float s = 0.0f;
+    if (g.router_class == 0) {
+        // weight of rank r = unbiased score of its expert
+        for (uint64_t r = 0; r < g.topk; ++r) {
+            int32_t e = __shfl_sync(0xffffffffu, mine, (int)r);
+            float s = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) if (e == lane + 32 * i) s = score[i];
-        s = __shfl_sync(0xffffffffu, s, e & 31);
-        if ((uint64_t)lane == r) mine_w = s;
+            for (int i = 0; i < 8; ++i) if (e == lane + 32 * i) s = score[i];
+            s = __shfl_sync(0xffffffffu, s, e & 31);
+            if ((uint64_t)lane == r) mine_w = s;
+        }
     }
     double total = 0.0;
     for (uint64_t r = 0; r < g.topk; ++r) total += (double)__shfl_sync(0xffffffffu, mine_w, (int)r);
